@@ -1,0 +1,99 @@
+"""ctypes binding of libferrum_cuda.so (the C ABI declared in include/ferrum_cuda.h).
+
+The library is the product; there is no Python or CPU implementation behind it. Loading
+fails loudly when the shared object has not been built (python -m ferrum_cpu_b200.build).
+"""
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libferrum_cuda.so")
+
+FC_OK = 0
+FC_E_SHAPE, FC_E_DIM, FC_E_FORMAT, FC_E_CUDA, FC_E_TIMEOUT, FC_E_CANCELLED, FC_E_ARG = -1, -2, -3, -4, -5, -6, -7
+FC_MATH_FP32, FC_MATH_BF16X3 = 0, 1
+
+
+class FcConfig(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("n_layer", "d_model", "n_head", "d_ff", "ctx", "vocab", "tied", "math_mode")]
+
+
+class FcLayerWeights(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in (
+        "attn_qkv_q8", "attn_qkv_b", "attn_out_q8", "attn_out_b", "ln1_g", "ln1_b", "ln2_g", "ln2_b",
+        "ffn_up_q8", "ffn_up_b", "ffn_down_q8", "ffn_down_b")]
+
+
+class FcWeights(C.Structure):
+    _fields_ = [("token_embd_q8", C.c_void_p), ("position_embd", C.c_void_p), ("layers", C.POINTER(FcLayerWeights)),
+                ("out_norm_g", C.c_void_p), ("out_norm_b", C.c_void_p), ("output_q8", C.c_void_p)]
+
+
+class FcScore(C.Structure):
+    _fields_ = [("logprob", C.c_double), ("n_tokens", C.c_int64), ("greedy", C.c_int32)]
+
+
+# name -> (restype, argtypes); every symbol include/ferrum_cuda.h declares
+SIGNATURES = {
+    "fc_last_error": (C.c_char_p, []),
+    "fc_device_count": (C.c_int, []),
+    "fc_q8_0_quantize": (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p]),
+    "fc_q8_0_dequantize": (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p]),
+    "fc_f32_to_f16": (C.c_uint16, [C.c_float]),
+    "fc_f16_to_f32": (C.c_float, [C.c_uint16]),
+    "fc_rng_seed": (C.c_uint64, [C.c_uint64]),
+    "fc_rng_fill_normal": (None, [C.POINTER(C.c_uint64), C.c_float, C.c_size_t, C.c_void_p]),
+    "fc_rng_fill_ids": (None, [C.POINTER(C.c_uint64), C.c_int32, C.c_size_t, C.c_void_p]),
+    "fc_q8_0_linear": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int]),
+    "fc_qweight_upload": (C.c_int, [C.c_int, C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_void_p)]),
+    "fc_qweight_free": (None, [C.c_void_p]),
+    "fc_q8_0_linear_dev": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
+    "fc_model_create": (C.c_int, [C.POINTER(FcConfig), C.POINTER(FcWeights), C.c_int, C.POINTER(C.c_void_p)]),
+    "fc_model_free": (None, [C.c_void_p]),
+    "fc_model_config": (C.c_int, [C.c_void_p, C.POINTER(FcConfig)]),
+    "fc_score_windows": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
+    "fc_token_logprobs": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.POINTER(FcScore), C.c_void_p, C.c_void_p]),
+    "fc_score_sequences": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.POINTER(FcScore), C.c_void_p]),
+    "fc_predict_next": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
+    "fc_stream_create": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
+    "fc_stream_free": (None, [C.c_void_p]),
+    "fc_stream_reset": (C.c_int, [C.c_void_p]),
+    "fc_cached_len": (C.c_int, [C.c_void_p]),
+    "fc_feed": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p]),
+    "fc_prime": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
+    "fc_generate_greedy": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int32, C.c_void_p, C.c_void_p, C.POINTER(C.c_int)]),
+    "fc_take_launch_count": (C.c_int64, []),
+    "fc_last_decode_ms": (C.c_float, [C.c_void_p]),
+    "fc_last_score_ms": (C.c_float, [C.c_void_p]),
+}
+
+_lib = None
+
+
+def lib():
+    """The loaded library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m ferrum_cpu_b200.build`. "
+                "There is no fallback implementation.")
+        handle = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = handle
+    return _lib
+
+
+class FerrumCudaError(RuntimeError):
+    """A negative status from the C ABI; `.code` is the FC_E_* value (InferError kinds)."""
+
+    def __init__(self, code, message):
+        super().__init__(f"[{code}] {message}")
+        self.code = code
+
+
+def check(rc):
+    if rc != FC_OK:
+        raise FerrumCudaError(rc, lib().fc_last_error().decode("utf-8", "replace"))

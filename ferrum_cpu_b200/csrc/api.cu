@@ -1,0 +1,779 @@
+// C ABI of libferrum_cuda: model upload, the standalone Q8_0 linear, windowed scoring and
+// the KV-cached decode driver. Host logic above the kernels mirrors, in C++, the Rust items
+// cited in include/ferrum_cuda.h.
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <vector>
+
+#include "fc_common.cuh"
+
+namespace fc {
+
+// ------------------------------------------------------------------------------- errors
+static thread_local char g_err[512] = "";
+thread_local int64_t g_launches = 0;
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof g_err, fmt, ap);
+    va_end(ap);
+}
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof g_err, fmt, ap);
+    va_end(ap);
+    return code;
+}
+int cuda_fail(cudaError_t e, const char* what, const char* file, int line) {
+    snprintf(g_err, sizeof g_err, "CUDA error %d (%s) at %s:%d in %s", (int)e, cudaGetErrorString(e), file, line, what);
+    return FC_E_CUDA;
+}
+
+// Refuses anything but a Blackwell data-centre part: there is no other code path.
+static int select_device(int device) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0) {
+        cudaGetLastError();
+        return fail(FC_E_CUDA, "no CUDA device is visible: libferrum_cuda has no CPU fallback");
+    }
+    if (device < 0 || device >= n) return fail(FC_E_ARG, "device %d out of range (0..%d)", device, n - 1);
+    int major = 0;
+    FC_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
+    if (major != 10) return fail(FC_E_CUDA, "device %d has compute capability %d.x; this library is built for sm_100a only", device, major);
+    FC_CUDA(cudaSetDevice(device));
+    return FC_OK;
+}
+
+// Owns device allocations; frees them in the destructor.
+struct Arena {
+    std::vector<void*> ptrs;
+    int alloc(void** p, size_t bytes) {
+        FC_CUDA(cudaMalloc(p, bytes ? bytes : 16));
+        ptrs.push_back(*p);
+        return FC_OK;
+    }
+    template <class T>
+    int alloc_n(T** p, size_t n) { return alloc((void**)p, n * sizeof(T)); }
+    void release() {
+        for (void* p : ptrs) cudaFree(p);
+        ptrs.clear();
+    }
+};
+
+static int upload_f32(Arena& ar, const float* host, size_t n, float** dev, cudaStream_t st) {
+    if (!host) return fail(FC_E_FORMAT, "a required f32 tensor is null");
+    FC_TRY(ar.alloc_n(dev, n));
+    FC_CUDA(cudaMemcpyAsync(*dev, host, n * sizeof(float), cudaMemcpyHostToDevice, st));
+    return FC_OK;
+}
+
+// loader/mod.rs:147-154: a matrix is Q8_0 only when its row length is a multiple of 32.
+static int upload_q8(Arena& ar, const void* host, int N, int K, QMat* out, cudaStream_t st) {
+    if (!host) return fail(FC_E_FORMAT, "a required Q8_0 tensor is null");
+    if (N <= 0 || K <= 0 || K % 32) return fail(FC_E_FORMAT, "Q8_0 matrix [%d][%d]: row length must be a positive multiple of 32", N, K);
+    if (K > 12288) return fail(FC_E_SHAPE, "row length %d exceeds the 12288 supported by the decode GEMV", K);
+    const int N_pad = (N + kRowPad - 1) / kRowPad * kRowPad;
+    const size_t raw_bytes = (size_t)N * (K / 32) * 34;
+    uint8_t* raw = nullptr;
+    uint8_t* qu = nullptr;
+    __half* d = nullptr;
+    FC_CUDA(cudaMalloc((void**)&raw, raw_bytes));
+    int rc = ar.alloc_n(&qu, (size_t)N_pad * K);
+    if (rc == FC_OK) rc = ar.alloc_n(&d, (size_t)N_pad * (K / 32));
+    if (rc == FC_OK && cudaMemcpyAsync(raw, host, raw_bytes, cudaMemcpyHostToDevice, st) != cudaSuccess)
+        rc = fail(FC_E_CUDA, "upload of a Q8_0 tensor failed");
+    if (rc == FC_OK) rc = launch_repack_q8(raw, N, K, N_pad, qu, d, st);
+    if (rc == FC_OK && cudaStreamSynchronize(st) != cudaSuccess) rc = fail(FC_E_CUDA, "repack of a Q8_0 tensor failed");
+    cudaFree(raw);
+    FC_TRY(rc);
+    out->qu = qu; out->d = d; out->N = N; out->K = K; out->N_pad = N_pad;
+    return FC_OK;
+}
+
+struct LayerDev {
+    QMat qkv, out, up, down;
+    float *qkv_b, *out_b, *up_b, *down_b, *ln1g, *ln1b, *ln2g, *ln2b;
+};
+
+}  // namespace fc
+
+using namespace fc;
+
+struct fc_qweight {
+    int device;
+    Arena arena;
+    QMat w;
+};
+
+struct fc_model {
+    fc_config cfg;
+    int device;
+    cudaStream_t st = nullptr;
+    Arena arena;       // weights
+    Arena ws_arena;    // prefill workspace
+    QMat tok, head;
+    float* pos = nullptr;
+    float *lnfg = nullptr, *lnfb = nullptr;
+    std::vector<LayerDev> layers;
+    // prefill workspace for ws_rows rows
+    int ws_rows = 0, head_chunk = 0;
+    float *x = nullptr, *n = nullptr, *qkv = nullptr, *att = nullptr, *hid = nullptr, *logits = nullptr, *probs_d = nullptr;
+    int *ids_d = nullptr, *targets_d = nullptr, *err_d = nullptr;
+    double* lp_d = nullptr;
+    uint8_t* gr_d = nullptr;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    float last_score_ms = 0.0f;
+};
+
+struct fc_stream {
+    fc_model* m;
+    Arena arena;
+    float *kc = nullptr, *vc = nullptr;  // [L][ctx][d]
+    float *x = nullptr, *n = nullptr, *q = nullptr, *att = nullptr, *hid = nullptr, *logits = nullptr, *probs = nullptr;
+    int* queue = nullptr;
+    int queue_cap = 0;
+    StepState* state = nullptr;
+    int host_pos = 0;
+    cudaGraphExec_t graph[3] = {nullptr, nullptr, nullptr};
+    int graph_nodes[3] = {0, 0, 0};
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    float last_decode_ms = 0.0f;
+};
+
+namespace fc {
+
+// ------------------------------------------------------------------------- decode step
+enum StepMode { STEP_NOHEAD = 0, STEP_SELECT = 1, STEP_PROBS = 2 };
+
+// One token through every block: the kernel sequence of CachedTransformer::feed
+// (slm/cached.rs:100-125) -> TransformerBlock::forward_with_cache (transformer.rs:221-294).
+static int launch_step(fc_stream* s, int mode) {
+    fc_model* m = s->m;
+    const fc_config& c = m->cfg;
+    cudaStream_t st = m->st;
+    const int d = c.d_model;
+    const size_t layer_stride = (size_t)c.ctx * d;
+    FC_TRY(launch_embed_step(m->tok, m->pos, c.ctx, s->queue, s->state, s->x, st));
+    for (int l = 0; l < c.n_layer; ++l) {
+        const LayerDev& L = m->layers[l];
+        float* kc = s->kc + l * layer_stride;
+        float* vc = s->vc + l * layer_stride;
+        FC_TRY(launch_layernorm(s->x, L.ln1g, L.ln1b, 1, d, s->n, s->state, st));
+        GemvOut o;
+        o.out[0] = s->q; o.out[1] = kc; o.out[2] = vc; o.seg = d; o.pos_stride = d;
+        FC_TRY(launch_gemv_q8(L.qkv, s->n, L.qkv_b, nullptr, EPI_NONE, o, s->state, st));
+        FC_TRY(launch_attn_decode(s->q, kc, vc, d, c.n_head, c.ctx, s->state, s->att, st));
+        GemvOut ox; ox.out[0] = s->x;
+        FC_TRY(launch_gemv_q8(L.out, s->att, L.out_b, s->x, EPI_NONE, ox, s->state, st));
+        FC_TRY(launch_layernorm(s->x, L.ln2g, L.ln2b, 1, d, s->n, s->state, st));
+        GemvOut oh; oh.out[0] = s->hid;
+        FC_TRY(launch_gemv_q8(L.up, s->n, L.up_b, nullptr, EPI_GELU, oh, s->state, st));
+        FC_TRY(launch_gemv_q8(L.down, s->hid, L.down_b, s->x, EPI_NONE, ox, s->state, st));
+    }
+    if (mode == STEP_NOHEAD) return launch_step_advance(s->state, st);
+    FC_TRY(launch_layernorm(s->x, m->lnfg, m->lnfb, 1, d, s->n, s->state, st));
+    GemvOut ol; ol.out[0] = s->logits;
+    FC_TRY(launch_gemv_q8(m->head, s->n, nullptr, nullptr, EPI_NONE, ol, s->state, st));
+    return launch_step_tail(s->logits, c.vocab, mode == STEP_PROBS ? s->probs : nullptr, mode == STEP_SELECT ? 1 : 0,
+                            s->queue, s->queue_cap, s->state, nullptr, st);
+}
+
+// The launch-bound step is captured once per mode into a CUDA graph and replayed; every
+// per-step quantity (token, position) is read from device state, so no node is updated.
+static int run_step(fc_stream* s, int mode) {
+    if (!s->graph[mode]) {
+        cudaStream_t st = s->m->st;
+        cudaGraph_t g = nullptr;
+        const int64_t before = g_launches;
+        FC_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+        const int rc = launch_step(s, mode);
+        const cudaError_t e = cudaStreamEndCapture(st, &g);
+        s->graph_nodes[mode] = (int)(g_launches - before);
+        g_launches = before;
+        if (rc != FC_OK) { if (g) cudaGraphDestroy(g); return rc; }
+        FC_CUDA(e);
+        const cudaError_t ei = cudaGraphInstantiate(&s->graph[mode], g, 0);
+        cudaGraphDestroy(g);
+        FC_CUDA(ei);
+    }
+    FC_CUDA(cudaGraphLaunch(s->graph[mode], s->m->st));
+    g_launches += s->graph_nodes[mode];
+    return FC_OK;
+}
+
+__global__ void set_state_kernel(StepState* st, int pos, int fed, int tail, int done, int eos, int keep_pos) {
+    if (!keep_pos) st->pos = pos;
+    st->fed = fed; st->tail = tail; st->done = done; st->eos = eos; st->error = 0;
+}
+static int set_state(fc_stream* s, int pos, int fed, int tail, int eos, int keep_pos) {
+    set_state_kernel<<<1, 1, 0, s->m->st>>>(s->state, pos, fed, tail, 0, eos, keep_pos);
+    FC_LAUNCHED();
+    return FC_OK;
+}
+
+static int read_state(fc_stream* s, StepState* out) {
+    FC_CUDA(cudaMemcpyAsync(out, s->state, sizeof(StepState), cudaMemcpyDeviceToHost, s->m->st));
+    FC_CUDA(cudaStreamSynchronize(s->m->st));
+    return FC_OK;
+}
+
+static int check_ids(const fc_model* m, const int32_t* ids, size_t n) {
+    for (size_t i = 0; i < n; ++i)
+        if (ids[i] < 0 || ids[i] >= m->cfg.vocab)
+            return fail(FC_E_DIM, "Token index %d out of bounds for vocab_size %d", ids[i], m->cfg.vocab);
+    return FC_OK;
+}
+
+// -------------------------------------------------------------------- prefill workspace
+static int ensure_workspace(fc_model* m, int rows) {
+    if (rows <= m->ws_rows) return FC_OK;
+    m->ws_arena.release();
+    m->ws_rows = 0;
+    const fc_config& c = m->cfg;
+    const size_t R = rows, d = c.d_model, F = c.d_ff;
+    // head logits are produced for head_chunk rows at a time (<= 1 GiB of f32)
+    size_t chunk = ((size_t)1 << 28) / (size_t)c.vocab;
+    chunk = std::max<size_t>(1, std::min<size_t>(chunk, R));
+    Arena& a = m->ws_arena;
+    FC_TRY(a.alloc_n(&m->x, R * d));
+    FC_TRY(a.alloc_n(&m->n, R * d));
+    FC_TRY(a.alloc_n(&m->qkv, R * 3 * d));
+    FC_TRY(a.alloc_n(&m->att, R * d));
+    FC_TRY(a.alloc_n(&m->hid, R * F));
+    FC_TRY(a.alloc_n(&m->logits, chunk * (size_t)c.vocab));
+    FC_TRY(a.alloc_n(&m->ids_d, R));
+    FC_TRY(a.alloc_n(&m->targets_d, R));
+    FC_TRY(a.alloc_n(&m->lp_d, R));
+    FC_TRY(a.alloc_n(&m->gr_d, R));
+    FC_TRY(a.alloc_n(&m->err_d, 1));
+    FC_TRY(a.alloc_n(&m->probs_d, (size_t)c.vocab));
+    m->ws_rows = rows;
+    m->head_chunk = (int)chunk;
+    return FC_OK;
+}
+
+static int gemm(fc_model* m, const QMat& w, const float* x, const float* bias, const float* res, int epi, float* y, int M, int ldy) {
+    // FC_MATH_BF16X3 is routed to the tensor-core kernel when it is built in; the fp32
+    // CUDA-core kernel serves FC_MATH_FP32.
+    return launch_gemm_q8_fp32(w, x, bias, res, epi, y, M, ldy, m->st);
+}
+
+// Sequential::forward (model.rs:51-71) up to the final LayerNorm, on B windows of T rows
+// whose ids are already in m->ids_d. Leaves LN_f(x) in m->n.
+static int forward_hidden(fc_model* m, int B, int T) {
+    const fc_config& c = m->cfg;
+    const int R = B * T, d = c.d_model;
+    cudaStream_t st = m->st;
+    FC_CUDA(cudaMemsetAsync(m->err_d, 0, sizeof(int), st));
+    FC_TRY(launch_embed_rows(m->tok, m->pos, m->ids_d, R, T, m->x, m->err_d, st));
+    for (int l = 0; l < c.n_layer; ++l) {
+        const LayerDev& L = m->layers[l];
+        FC_TRY(launch_layernorm(m->x, L.ln1g, L.ln1b, R, d, m->n, nullptr, st));
+        FC_TRY(gemm(m, L.qkv, m->n, L.qkv_b, nullptr, EPI_NONE, m->qkv, R, 3 * d));
+        FC_TRY(launch_attn_prefill(m->qkv, B, T, d, c.n_head, m->att, st));
+        FC_TRY(gemm(m, L.out, m->att, L.out_b, m->x, EPI_NONE, m->x, R, d));
+        FC_TRY(launch_layernorm(m->x, L.ln2g, L.ln2b, R, d, m->n, nullptr, st));
+        FC_TRY(gemm(m, L.up, m->n, L.up_b, nullptr, EPI_GELU, m->hid, R, c.d_ff));
+        FC_TRY(gemm(m, L.down, m->hid, L.down_b, m->x, EPI_NONE, m->x, R, d));
+    }
+    return launch_layernorm(m->x, m->lnfg, m->lnfb, R, d, m->n, nullptr, st);
+}
+
+// Forward + head + scoring tail for ids/targets already on the device. lp_d/gr_d filled.
+static int score_device(fc_model* m, int B, int T) {
+    const fc_config& c = m->cfg;
+    const int R = B * T;
+    FC_TRY(forward_hidden(m, B, T));
+    for (int r0 = 0; r0 < R; r0 += m->head_chunk) {
+        const int rows = std::min(m->head_chunk, R - r0);
+        FC_TRY(gemm(m, m->head, m->n + (size_t)r0 * c.d_model, nullptr, nullptr, EPI_NONE, m->logits, rows, c.vocab));
+        FC_TRY(launch_score_rows(m->logits, c.vocab, c.vocab, m->targets_d + r0, rows, m->lp_d + r0, m->gr_d + r0, m->st));
+    }
+    return FC_OK;
+}
+
+}  // namespace fc
+
+// =====================================================================================
+//                                      C ABI
+// =====================================================================================
+extern "C" {
+
+const char* fc_last_error(void) { return fc::g_err; }
+
+int fc_device_count(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) { cudaGetLastError(); return 0; }
+    int ok = 0;
+    for (int i = 0; i < n; ++i) {
+        int major = 0;
+        if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, i) == cudaSuccess && major == 10) ++ok;
+    }
+    return ok;
+}
+
+int64_t fc_take_launch_count(void) {
+    const int64_t n = g_launches;
+    g_launches = 0;
+    return n;
+}
+
+// ------------------------------------------------------------------ standalone linear
+int fc_qweight_upload(int device, const void* wq, int N, int K, fc_qweight** out) {
+    if (!out) return fail(FC_E_ARG, "fc_qweight_upload: out is null");
+    *out = nullptr;
+    FC_TRY(select_device(device));
+    fc_qweight* w = new fc_qweight;
+    w->device = device;
+    const int rc = upload_q8(w->arena, wq, N, K, &w->w, 0);
+    if (rc != FC_OK) { w->arena.release(); delete w; return rc; }
+    *out = w;
+    return FC_OK;
+}
+
+void fc_qweight_free(fc_qweight* w) {
+    if (!w) return;
+    cudaSetDevice(w->device);
+    w->arena.release();
+    delete w;
+}
+
+int fc_q8_0_linear_dev(const fc_qweight* w, const float* x_dev, const float* bias_dev, float* y_dev,
+                       int M, int math_mode, void* cuda_stream) {
+    if (!w || !x_dev || !y_dev) return fail(FC_E_ARG, "fc_q8_0_linear_dev: null argument");
+    if (M < 0) return fail(FC_E_SHAPE, "fc_q8_0_linear_dev: M = %d", M);
+    if (M == 0) return FC_OK;
+    (void)math_mode;
+    FC_CUDA(cudaSetDevice(w->device));
+    cudaStream_t st = (cudaStream_t)cuda_stream;
+    if (M == 1) {
+        GemvOut o; o.out[0] = y_dev;
+        return launch_gemv_q8(w->w, x_dev, bias_dev, nullptr, EPI_NONE, o, nullptr, st);
+    }
+    return launch_gemm_q8_fp32(w->w, x_dev, bias_dev, nullptr, EPI_NONE, y_dev, M, w->w.N, st);
+}
+
+int fc_q8_0_linear(int device, const float* x, const void* wq, const float* bias, float* y,
+                   int M, int K, int N, int math_mode) {
+    if (!x || !wq || !y) return fail(FC_E_ARG, "fc_q8_0_linear: null argument");
+    if (M < 0 || N <= 0 || K <= 0) return fail(FC_E_SHAPE, "fc_q8_0_linear: bad shape M=%d K=%d N=%d", M, K, N);
+    fc_qweight* w = nullptr;
+    FC_TRY(fc_qweight_upload(device, wq, N, K, &w));
+    int rc = FC_OK;
+    float *xd = nullptr, *bd = nullptr, *yd = nullptr;
+    if (M > 0) {
+        Arena tmp;
+        rc = tmp.alloc_n(&xd, (size_t)M * K);
+        if (rc == FC_OK) rc = tmp.alloc_n(&yd, (size_t)M * N);
+        if (rc == FC_OK && bias) rc = tmp.alloc_n(&bd, (size_t)N);
+        auto copy = [&](void* dst, const void* src, size_t bytes, cudaMemcpyKind kind) {
+            if (rc == FC_OK && cudaMemcpy(dst, src, bytes, kind) != cudaSuccess) rc = fail(FC_E_CUDA, "fc_q8_0_linear: copy failed");
+        };
+        copy(xd, x, (size_t)M * K * 4, cudaMemcpyHostToDevice);
+        if (bias) copy(bd, bias, (size_t)N * 4, cudaMemcpyHostToDevice);
+        if (rc == FC_OK) rc = fc_q8_0_linear_dev(w, xd, bd, yd, M, math_mode, nullptr);
+        if (rc == FC_OK && cudaDeviceSynchronize() != cudaSuccess) rc = cuda_fail(cudaGetLastError(), "fc_q8_0_linear kernel", __FILE__, __LINE__);
+        copy(y, yd, (size_t)M * N * 4, cudaMemcpyDeviceToHost);
+        tmp.release();
+    }
+    fc_qweight_free(w);
+    return rc;
+}
+
+// ------------------------------------------------------------------------------ model
+static int model_build(fc_model* m, const fc_weights* w) {
+    const fc_config& c = m->cfg;
+    const int d = c.d_model, F = c.d_ff, V = c.vocab;
+    cudaStream_t st = m->st;
+    Arena& a = m->arena;
+    FC_TRY(upload_q8(a, w->token_embd_q8, V, d, &m->tok, st));
+    if (c.tied) m->head = m->tok;   // loader/gpt2.rs:228-233
+    else FC_TRY(upload_q8(a, w->output_q8, V, d, &m->head, st));
+    FC_TRY(upload_f32(a, w->position_embd, (size_t)c.ctx * d, &m->pos, st));
+    FC_TRY(upload_f32(a, w->out_norm_g, d, &m->lnfg, st));
+    FC_TRY(upload_f32(a, w->out_norm_b, d, &m->lnfb, st));
+    if (!w->layers) return fail(FC_E_FORMAT, "fc_weights.layers is null");
+    m->layers.resize(c.n_layer);
+    for (int l = 0; l < c.n_layer; ++l) {
+        const fc_layer_weights& s = w->layers[l];
+        LayerDev& L = m->layers[l];
+        FC_TRY(upload_q8(a, s.attn_qkv_q8, 3 * d, d, &L.qkv, st));
+        FC_TRY(upload_q8(a, s.attn_out_q8, d, d, &L.out, st));
+        FC_TRY(upload_q8(a, s.ffn_up_q8, F, d, &L.up, st));
+        FC_TRY(upload_q8(a, s.ffn_down_q8, d, F, &L.down, st));
+        FC_TRY(upload_f32(a, s.attn_qkv_b, 3 * (size_t)d, &L.qkv_b, st));
+        FC_TRY(upload_f32(a, s.attn_out_b, d, &L.out_b, st));
+        FC_TRY(upload_f32(a, s.ffn_up_b, F, &L.up_b, st));
+        FC_TRY(upload_f32(a, s.ffn_down_b, d, &L.down_b, st));
+        FC_TRY(upload_f32(a, s.ln1_g, d, &L.ln1g, st));
+        FC_TRY(upload_f32(a, s.ln1_b, d, &L.ln1b, st));
+        FC_TRY(upload_f32(a, s.ln2_g, d, &L.ln2g, st));
+        FC_TRY(upload_f32(a, s.ln2_b, d, &L.ln2b, st));
+    }
+    FC_CUDA(cudaStreamSynchronize(st));
+    return FC_OK;
+}
+
+int fc_model_create(const fc_config* cfg, const fc_weights* w, int device, fc_model** out) {
+    if (!cfg || !w || !out) return fail(FC_E_ARG, "fc_model_create: null argument");
+    *out = nullptr;
+    const fc_config& c = *cfg;
+    if (c.n_layer <= 0 || c.d_model <= 0 || c.n_head <= 0 || c.d_ff <= 0 || c.ctx <= 0 || c.vocab <= 0)
+        return fail(FC_E_SHAPE, "fc_model_create: every dimension must be positive");
+    if (c.d_model % c.n_head) return fail(FC_E_DIM, "embedding_dim %d is not divisible by num_heads %d", c.d_model, c.n_head);
+    if (c.d_model % 32 || c.d_ff % 32) return fail(FC_E_FORMAT, "d_model %d and d_ff %d must be multiples of 32 for Q8_0 storage", c.d_model, c.d_ff);
+    const int hd = c.d_model / c.n_head;
+    if (hd != 32 && hd != 64) return fail(FC_E_SHAPE, "head_dim %d is not supported (32 or 64)", hd);
+    if (c.math_mode != FC_MATH_FP32 && c.math_mode != FC_MATH_BF16X3) return fail(FC_E_ARG, "unknown math_mode %d", c.math_mode);
+    if (!c.tied && !w->output_q8) return fail(FC_E_FORMAT, "untied model without output.weight");
+    FC_TRY(select_device(device));
+    fc_model* m = new fc_model;
+    m->cfg = c;
+    m->device = device;
+    int rc = FC_OK;
+    if (cudaStreamCreateWithFlags(&m->st, cudaStreamNonBlocking) != cudaSuccess) rc = fail(FC_E_CUDA, "stream creation failed");
+    if (rc == FC_OK && (cudaEventCreate(&m->ev0) != cudaSuccess || cudaEventCreate(&m->ev1) != cudaSuccess)) rc = fail(FC_E_CUDA, "event creation failed");
+    if (rc == FC_OK) rc = model_build(m, w);
+    if (rc != FC_OK) { fc_model_free(m); return rc; }
+    *out = m;
+    return FC_OK;
+}
+
+void fc_model_free(fc_model* m) {
+    if (!m) return;
+    cudaSetDevice(m->device);
+    if (m->st) cudaStreamSynchronize(m->st);
+    m->arena.release();
+    m->ws_arena.release();
+    if (m->ev0) cudaEventDestroy(m->ev0);
+    if (m->ev1) cudaEventDestroy(m->ev1);
+    if (m->st) cudaStreamDestroy(m->st);
+    delete m;
+}
+
+int fc_model_config(const fc_model* m, fc_config* out) {
+    if (!m || !out) return fail(FC_E_ARG, "fc_model_config: null argument");
+    *out = m->cfg;
+    return FC_OK;
+}
+
+float fc_last_score_ms(const fc_model* m) { return m ? m->last_score_ms : 0.0f; }
+
+// ---------------------------------------------------------------------------- scoring
+// Runs B windows x T rows through the model; double log-probs / flags stay on the device
+// until copied into the caller's arrays.
+static int score_windows_impl(fc_model* m, const int32_t* ids, const int32_t* targets, int B, int T,
+                              double* lp_host, uint8_t* gr_host) {
+    const fc_config& c = m->cfg;
+    if (B <= 0 || T <= 0) return fail(FC_E_SHAPE, "scoring needs B > 0 and T > 0 (got %d, %d)", B, T);
+    if (T > c.ctx) return fail(FC_E_DIM, "Sequence length %d exceeds max_seq_len %d", T, c.ctx);
+    if ((int64_t)B * T > (int64_t)1 << 24) return fail(FC_E_SHAPE, "too many rows in one forward: %lld", (long long)B * T);
+    const int R = B * T;
+    FC_TRY(check_ids(m, ids, (size_t)R));
+    FC_CUDA(cudaSetDevice(m->device));
+    FC_TRY(ensure_workspace(m, R));
+    cudaStream_t st = m->st;
+    FC_CUDA(cudaMemcpyAsync(m->ids_d, ids, (size_t)R * 4, cudaMemcpyHostToDevice, st));
+    FC_CUDA(cudaMemcpyAsync(m->targets_d, targets, (size_t)R * 4, cudaMemcpyHostToDevice, st));
+    FC_CUDA(cudaEventRecord(m->ev0, st));
+    FC_TRY(score_device(m, B, T));
+    FC_CUDA(cudaEventRecord(m->ev1, st));
+    FC_CUDA(cudaMemcpyAsync(lp_host, m->lp_d, (size_t)R * 8, cudaMemcpyDeviceToHost, st));
+    FC_CUDA(cudaMemcpyAsync(gr_host, m->gr_d, (size_t)R, cudaMemcpyDeviceToHost, st));
+    FC_CUDA(cudaStreamSynchronize(st));
+    float ms = 0.0f;
+    FC_CUDA(cudaEventElapsedTime(&ms, m->ev0, m->ev1));
+    m->last_score_ms += ms;
+    return FC_OK;
+}
+
+int fc_score_windows(fc_model* m, const int32_t* ids, const int32_t* targets, int B, int T,
+                     float* logprob, uint8_t* is_greedy) {
+    if (!m || !ids || !targets || !logprob || !is_greedy) return fail(FC_E_ARG, "fc_score_windows: null argument");
+    m->last_score_ms = 0.0f;
+    std::vector<double> lp((size_t)std::max(0, B) * std::max(0, T));
+    FC_TRY(score_windows_impl(m, ids, targets, B, T, lp.data(), is_greedy));
+    for (size_t i = 0; i < lp.size(); ++i) logprob[i] = (float)lp[i];
+    return FC_OK;
+}
+
+}  // extern "C"
+
+namespace {
+// One window of the plan of scoring.rs:164-172.
+struct Window { int seq, start, first, end; };
+
+// (start, first target, end target exclusive) for targets from..n of one sequence.
+void plan_windows(int seq, int n, int from, int T, std::vector<Window>* out) {
+    const int half = std::max(1, T / 2);
+    int next = std::max(from, 1);
+    while (next < n) {
+        const int start = next <= T ? 0 : next - half;
+        const int end = std::min(start + T + 1, n);
+        out->push_back(Window{seq, start, next, end});
+        next = end;
+    }
+}
+
+// Scores every window of `plan` in batches; seq_ids(s) gives the ids of sequence s, n its
+// length. For each scored target calls add(seq, target, logprob, greedy).
+template <class Ids, class Add>
+int run_plan(fc_model* m, const std::vector<Window>& plan, int batch, Ids seq_ids, int n, Add add) {
+    const int T = m->cfg.ctx;
+    std::vector<int32_t> ids, targets;
+    std::vector<double> lp;
+    std::vector<uint8_t> gr;
+    for (size_t w0 = 0; w0 < plan.size(); w0 += batch) {
+        const int B = (int)std::min<size_t>(batch, plan.size() - w0);
+        // rows past the longest window of the batch are never read under the causal mask
+        int Tb = 1;
+        for (int b = 0; b < B; ++b) Tb = std::max(Tb, std::min(plan[w0 + b].start + T, n) - plan[w0 + b].start);
+        ids.assign((size_t)B * Tb, 0);          // right padding with id 0 (scoring.rs:188-190)
+        targets.assign((size_t)B * Tb, -1);
+        for (int b = 0; b < B; ++b) {
+            const Window& w = plan[w0 + b];
+            const int32_t* src = seq_ids(w.seq);
+            const int wl = std::min(w.start + T, n) - w.start;
+            std::copy(src + w.start, src + w.start + wl, ids.begin() + (size_t)b * Tb);
+            for (int t = w.first; t < w.end; ++t) targets[(size_t)b * Tb + (t - 1 - w.start)] = src[t];
+        }
+        lp.resize((size_t)B * Tb);
+        gr.resize((size_t)B * Tb);
+        FC_TRY(score_windows_impl(m, ids.data(), targets.data(), B, Tb, lp.data(), gr.data()));
+        for (int b = 0; b < B; ++b) {
+            const Window& w = plan[w0 + b];
+            for (int t = w.first; t < w.end; ++t) {
+                const size_t r = (size_t)b * Tb + (t - 1 - w.start);
+                add(w.seq, t, lp[r], gr[r]);
+            }
+        }
+    }
+    return FC_OK;
+}
+}  // namespace
+
+extern "C" {
+
+int fc_token_logprobs(fc_model* m, const int32_t* ids, int n, int from, fc_score* score, float* lp, uint8_t* is_greedy) {
+    if (!m || !score || (n > 0 && !ids)) return fail(FC_E_ARG, "fc_token_logprobs: null argument");
+    score->logprob = 0.0; score->n_tokens = 0; score->greedy = 1;
+    m->last_score_ms = 0.0f;
+    if (n <= 0) return FC_OK;
+    FC_TRY(check_ids(m, ids, (size_t)n));
+    std::vector<Window> plan;
+    plan_windows(0, n, from, m->cfg.ctx, &plan);
+    // SCORE_BATCH = 32 windows per forward (scoring.rs:45)
+    return run_plan(m, plan, 32, [&](int) { return ids; }, n, [&](int, int t, double l, uint8_t g) {
+        score->logprob += l; score->n_tokens += 1; score->greedy &= (int32_t)g;
+        if (lp) lp[t] = (float)l;
+        if (is_greedy) is_greedy[t] = g;
+    });
+}
+
+int fc_score_sequences(fc_model* m, const int32_t* ids, int n_seq, int seq_len, int batch_windows,
+                       fc_score* scores, float* lp) {
+    if (!m || !ids || !scores) return fail(FC_E_ARG, "fc_score_sequences: null argument");
+    if (n_seq < 0 || seq_len < 0) return fail(FC_E_SHAPE, "fc_score_sequences: negative size");
+    m->last_score_ms = 0.0f;
+    for (int s = 0; s < n_seq; ++s) { scores[s].logprob = 0.0; scores[s].n_tokens = 0; scores[s].greedy = 1; }
+    if (n_seq == 0 || seq_len == 0) return FC_OK;
+    FC_TRY(check_ids(m, ids, (size_t)n_seq * seq_len));
+    std::vector<Window> plan;
+    for (int s = 0; s < n_seq; ++s) plan_windows(s, seq_len, 1, m->cfg.ctx, &plan);
+    if (batch_windows <= 0) batch_windows = 32;
+    if (lp) for (int s = 0; s < n_seq; ++s) lp[(size_t)s * seq_len] = 0.0f;
+    return run_plan(m, plan, batch_windows, [&](int s) { return ids + (size_t)s * seq_len; }, seq_len,
+                    [&](int s, int t, double l, uint8_t g) {
+                        scores[s].logprob += l; scores[s].n_tokens += 1; scores[s].greedy &= (int32_t)g;
+                        if (lp) lp[(size_t)s * seq_len + t] = (float)l;
+                    });
+}
+
+int fc_predict_next(fc_model* m, const int32_t* ids, int n, float* probs) {
+    if (!m || !ids || !probs) return fail(FC_E_ARG, "fc_predict_next: null argument");
+    const fc_config& c = m->cfg;
+    if (n <= 0) return fail(FC_E_SHAPE, "fc_predict_next: empty input");
+    if (n > c.ctx) return fail(FC_E_DIM, "Sequence length %d exceeds max_seq_len %d", n, c.ctx);
+    FC_TRY(check_ids(m, ids, (size_t)n));
+    FC_CUDA(cudaSetDevice(m->device));
+    FC_TRY(ensure_workspace(m, n));
+    cudaStream_t st = m->st;
+    FC_CUDA(cudaMemcpyAsync(m->ids_d, ids, (size_t)n * 4, cudaMemcpyHostToDevice, st));
+    FC_TRY(forward_hidden(m, 1, n));
+    GemvOut o; o.out[0] = m->logits;
+    FC_TRY(launch_gemv_q8(m->head, m->n + (size_t)(n - 1) * c.d_model, nullptr, nullptr, EPI_NONE, o, nullptr, st));
+    FC_TRY(launch_softmax_row(m->logits, c.vocab, m->probs_d, st));
+    FC_CUDA(cudaMemcpyAsync(probs, m->probs_d, (size_t)c.vocab * 4, cudaMemcpyDeviceToHost, st));
+    FC_CUDA(cudaStreamSynchronize(st));
+    return FC_OK;
+}
+
+// ----------------------------------------------------------------------------- streams
+int fc_stream_create(fc_model* m, fc_stream** out) {
+    if (!m || !out) return fail(FC_E_ARG, "fc_stream_create: null argument");
+    *out = nullptr;
+    FC_CUDA(cudaSetDevice(m->device));
+    const fc_config& c = m->cfg;
+    fc_stream* s = new fc_stream;
+    s->m = m;
+    Arena& a = s->arena;
+    const size_t cache = (size_t)c.n_layer * c.ctx * c.d_model;
+    s->queue_cap = c.ctx + 8;
+    int rc = a.alloc_n(&s->kc, cache);
+    if (rc == FC_OK) rc = a.alloc_n(&s->vc, cache);
+    if (rc == FC_OK) rc = a.alloc_n(&s->x, (size_t)c.d_model);
+    if (rc == FC_OK) rc = a.alloc_n(&s->n, (size_t)c.d_model);
+    if (rc == FC_OK) rc = a.alloc_n(&s->q, (size_t)c.d_model);
+    if (rc == FC_OK) rc = a.alloc_n(&s->att, (size_t)c.d_model);
+    if (rc == FC_OK) rc = a.alloc_n(&s->hid, (size_t)c.d_ff);
+    if (rc == FC_OK) rc = a.alloc_n(&s->logits, (size_t)c.vocab);
+    if (rc == FC_OK) rc = a.alloc_n(&s->probs, (size_t)c.vocab);
+    if (rc == FC_OK) rc = a.alloc_n(&s->queue, (size_t)s->queue_cap);
+    if (rc == FC_OK) rc = a.alloc_n(&s->state, 1);
+    if (rc == FC_OK && (cudaEventCreate(&s->ev0) != cudaSuccess || cudaEventCreate(&s->ev1) != cudaSuccess)) rc = fail(FC_E_CUDA, "event creation failed");
+    if (rc == FC_OK) rc = set_state(s, 0, 0, 0, -1, 0);
+    if (rc == FC_OK && cudaStreamSynchronize(m->st) != cudaSuccess) rc = fail(FC_E_CUDA, "stream initialisation failed");
+    if (rc != FC_OK) { fc_stream_free(s); return rc; }
+    *out = s;
+    return FC_OK;
+}
+
+void fc_stream_free(fc_stream* s) {
+    if (!s) return;
+    cudaSetDevice(s->m->device);
+    cudaStreamSynchronize(s->m->st);
+    for (int i = 0; i < 3; ++i) if (s->graph[i]) cudaGraphExecDestroy(s->graph[i]);
+    if (s->ev0) cudaEventDestroy(s->ev0);
+    if (s->ev1) cudaEventDestroy(s->ev1);
+    s->arena.release();
+    delete s;
+}
+
+int fc_stream_reset(fc_stream* s) {
+    if (!s) return fail(FC_E_ARG, "fc_stream_reset: null stream");
+    FC_CUDA(cudaSetDevice(s->m->device));
+    s->host_pos = 0;
+    return set_state(s, 0, 0, 0, -1, 0);
+}
+
+int fc_cached_len(const fc_stream* s) { return s ? s->host_pos : 0; }
+float fc_last_decode_ms(const fc_stream* s) { return s ? s->last_decode_ms : 0.0f; }
+
+// Feeds queue[0..n) (already uploaded) from the current position; the last step runs in
+// `last_mode`, the ones before it skip the head (its output would be discarded).
+static int feed_queued(fc_stream* s, int n, int last_mode) {
+    for (int i = 0; i < n; ++i) FC_TRY(run_step(s, i + 1 == n ? last_mode : STEP_NOHEAD));
+    return FC_OK;
+}
+
+static int feed_ids(fc_stream* s, const int32_t* ids, int n, float* probs) {
+    fc_model* m = s->m;
+    const fc_config& c = m->cfg;
+    FC_TRY(check_ids(m, ids, (size_t)n));
+    if (s->host_pos + n > c.ctx)
+        return fail(FC_E_DIM, "KvCache full (%d positions): clear and re-prime to continue", c.ctx);
+    if (n == 0) return FC_OK;
+    cudaStream_t st = m->st;
+    FC_CUDA(cudaMemcpyAsync(s->queue, ids, (size_t)n * 4, cudaMemcpyHostToDevice, st));
+    FC_TRY(set_state(s, 0, 0, n, -1, /*keep_pos=*/1));
+    FC_TRY(feed_queued(s, n, probs ? STEP_PROBS : STEP_NOHEAD));
+    if (probs) FC_CUDA(cudaMemcpyAsync(probs, s->probs, (size_t)c.vocab * 4, cudaMemcpyDeviceToHost, st));
+    StepState hs;
+    FC_TRY(read_state(s, &hs));
+    if (hs.error) return fail(hs.error, "decode step rejected a token or position on the device");
+    s->host_pos = hs.pos;
+    return FC_OK;
+}
+
+int fc_feed(fc_stream* s, int32_t token, float* probs) {
+    if (!s) return fail(FC_E_ARG, "fc_feed: null stream");
+    FC_CUDA(cudaSetDevice(s->m->device));
+    return feed_ids(s, &token, 1, probs);
+}
+
+int fc_prime(fc_stream* s, const int32_t* ids, int n, float* probs) {
+    if (!s || (n > 0 && !ids)) return fail(FC_E_ARG, "fc_prime: null argument");
+    if (n < 0) return fail(FC_E_SHAPE, "fc_prime: n = %d", n);
+    FC_TRY(fc_stream_reset(s));
+    return feed_ids(s, ids, n, probs);
+}
+
+int fc_generate_greedy(fc_stream* s, const int32_t* prompt, int n, int max_new, int32_t eos,
+                       const volatile int32_t* cancel, int32_t* out, int* n_out) {
+    if (!s || !prompt || !n_out || (max_new > 0 && !out)) return fail(FC_E_ARG, "fc_generate_greedy: null argument");
+    *n_out = 0;
+    if (n <= 0) return fail(FC_E_SHAPE, "fc_generate_greedy: empty prompt (pass the BOS id, token_stream.rs:84-86)");
+    if (max_new < 0) return fail(FC_E_SHAPE, "fc_generate_greedy: max_new = %d", max_new);
+    fc_model* m = s->m;
+    const fc_config& c = m->cfg;
+    FC_CUDA(cudaSetDevice(m->device));
+    FC_TRY(check_ids(m, prompt, (size_t)n));
+    cudaStream_t st = m->st;
+    const int cap = std::max(1, (int)c.ctx), keep = std::max(1, cap / 2);
+    s->last_decode_ms = 0.0f;
+
+    // window = the last `cap` prompt ids (token_stream.rs:87-89)
+    std::vector<int32_t> window(prompt + std::max(0, n - cap), prompt + n);
+    int made = 0;          // tokens already copied to `out` (earlier windows)
+    bool done = false, cancelled = false;
+    // Starts a window: reset, upload, prime. The last prime step selects the next token when
+    // one is still wanted.
+    auto start_window = [&](bool select) -> int {
+        FC_TRY(fc_stream_reset(s));
+        FC_CUDA(cudaMemcpyAsync(s->queue, window.data(), window.size() * 4, cudaMemcpyHostToDevice, st));
+        FC_TRY(set_state(s, 0, 0, (int)window.size(), eos, 0));
+        return feed_queued(s, (int)window.size(), select ? STEP_SELECT : STEP_PROBS);
+    };
+    // Reads back what the device appended to the current window; sets `done` on eos.
+    auto harvest = [&]() -> int {
+        StepState hs;
+        FC_TRY(read_state(s, &hs));
+        if (hs.error) return fail(hs.error, "decode step rejected a token or position on the device");
+        const int have = hs.tail - (int)window.size();
+        if (have > 0) {
+            window.resize(hs.tail);
+            FC_CUDA(cudaMemcpy(window.data() + hs.tail - have, s->queue + hs.tail - have, (size_t)have * 4, cudaMemcpyDeviceToHost));
+            for (int i = 0; i < have && made < max_new; ++i) out[made++] = window[hs.tail - have + i];
+        }
+        s->host_pos = hs.pos;
+        done = hs.done != 0;
+        return FC_OK;
+    };
+
+    FC_TRY(start_window(max_new > 0));
+    FC_CUDA(cudaEventRecord(s->ev0, st));
+    int win_start_len = (int)window.size();  // ids in the window when it was primed
+    int gen_win = max_new > 0 ? 1 : 0;       // tokens selected inside this window (issued)
+    // feed i (1-based) pushes generated token i; it selects token i+1 unless it is the last
+    for (int i = 1; i <= max_new && !done; ++i) {
+        if (cancel && *cancel) { cancelled = true; break; }
+        const bool select = i < max_new;
+        if (win_start_len + gen_win > cap) {
+            // the window outgrew the context: keep the last cap/2 ids and re-prime
+            // (token_stream.rs:162-165)
+            FC_TRY(harvest());
+            if (done) break;
+            window.erase(window.begin(), window.end() - keep);
+            FC_TRY(start_window(select));
+            win_start_len = (int)window.size();
+            gen_win = select ? 1 : 0;
+        } else {
+            FC_TRY(run_step(s, select ? STEP_SELECT : STEP_PROBS));
+            gen_win += select ? 1 : 0;
+        }
+        // eos can only be noticed on the host at a synchronisation point
+        if (eos >= 0 && (i % 32) == 0) FC_TRY(harvest());
+    }
+    FC_CUDA(cudaEventRecord(s->ev1, st));
+    FC_TRY(harvest());
+    FC_CUDA(cudaEventElapsedTime(&s->last_decode_ms, s->ev0, s->ev1));
+    *n_out = made;
+    if (cancelled) return fail(FC_E_CANCELLED, "generation cancelled after %d tokens", made);
+    return FC_OK;
+}
+
+}  // extern "C"

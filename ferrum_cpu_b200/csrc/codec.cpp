@@ -1,0 +1,126 @@
+// Host-side load-time codecs of libferrum_cuda: IEEE half conversion, the Q8_0 block
+// encoder/decoder and Ferrum's xorshift64* generator. None of this runs in the forward
+// pass; a ferrum_cuda wrapper uses it to re-encode the f32 layers the (untouched) GGUF
+// loader produces, and the benchmark uses it to synthesise seeded weights.
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "../../include/ferrum_cuda.h"
+
+namespace {
+
+inline uint32_t bits_of(float f) { uint32_t u; std::memcpy(&u, &f, sizeof u); return u; }
+inline float float_of(uint32_t u) { float f; std::memcpy(&f, &u, sizeof f); return f; }
+
+// Round-to-nearest-even right shift of `v` by `s` bits (1 <= s <= 31).
+inline uint32_t rne_shift(uint32_t v, unsigned s) {
+    const uint32_t kept = v >> s;
+    const uint32_t rest = v & ((1u << s) - 1u);
+    const uint32_t tie = 1u << (s - 1);
+    return kept + ((rest > tie || (rest == tie && (kept & 1u))) ? 1u : 0u);
+}
+
+}  // namespace
+
+extern "C" {
+
+// gguf_write/blocks.rs:12-61: RNE, overflow -> Inf, gradual underflow, NaN -> sign|0x7E00.
+uint16_t fc_f32_to_f16(float v) {
+    const uint32_t u = bits_of(v);
+    const uint16_t s = (uint16_t)((u >> 16) & 0x8000u);
+    const uint32_t e = (u >> 23) & 0xFFu;
+    const uint32_t m = u & 0x7FFFFFu;
+    if (e == 0xFFu) return (uint16_t)(s | (m ? 0x7E00u : 0x7C00u));
+    const int he = (int)e - 112;                 // half exponent field before rounding
+    if (he >= 31) return (uint16_t)(s | 0x7C00u);
+    if (he <= 0) {
+        if (he < -10) return s;                  // below half of the smallest subnormal
+        return (uint16_t)(s | rne_shift(m | 0x800000u, (unsigned)(14 - he)));
+    }
+    // A mantissa carry walks into the exponent field, which is the right answer; an
+    // exponent that reaches 31 this way is exactly Inf (0x7C00).
+    return (uint16_t)(s | (((uint32_t)he << 10) + rne_shift(m, 13)));
+}
+
+// gguf/dequant.rs:7-35.
+float fc_f16_to_f32(uint16_t h) {
+    const uint32_t s = (uint32_t)(h >> 15) << 31;
+    const uint32_t e = (h >> 10) & 31u;
+    const uint32_t m = h & 1023u;
+    if (e == 31u) return float_of(s | 0x7F800000u | (m << 13));
+    if (e) return float_of(s | ((e + 112u) << 23) | (m << 13));
+    // subnormal: m * 2^-24 is exact in f32
+    const float mag = (float)m * 5.9604644775390625e-8f;
+    return float_of(s | bits_of(mag));
+}
+
+// quant.rs:271-280 + gguf_write/blocks.rs:132-140.
+int fc_q8_0_quantize(const float* x, size_t n, void* out) {
+    if (!x || !out || n % 32) return FC_E_FORMAT;
+    uint8_t* o = (uint8_t*)out;
+    for (size_t b = 0; b < n / 32; ++b, x += 32, o += 34) {
+        float amax = 0.0f;
+        for (int i = 0; i < 32; ++i) {
+            const float a = fabsf(x[i]);
+            amax = (a > amax) ? a : amax;
+        }
+        const float d = amax / 127.0f;
+        const float inv = (d != 0.0f) ? 1.0f / d : 0.0f;
+        const uint16_t d16 = fc_f32_to_f16(d);
+        o[0] = (uint8_t)d16;
+        o[1] = (uint8_t)(d16 >> 8);
+        for (int i = 0; i < 32; ++i) {
+            float r = roundf(x[i] * inv);        // ties away from zero
+            if (!(r == r)) r = 0.0f;             // Rust `as i8`: NaN -> 0, saturating
+            r = r > 127.0f ? 127.0f : (r < -128.0f ? -128.0f : r);
+            o[2 + i] = (uint8_t)(int8_t)(int)r;
+        }
+    }
+    return FC_OK;
+}
+
+// gguf/dequant.rs:37-49.
+int fc_q8_0_dequantize(const void* raw, size_t n, float* out) {
+    if (!raw || !out || n % 32) return FC_E_FORMAT;
+    const uint8_t* p = (const uint8_t*)raw;
+    for (size_t b = 0; b < n / 32; ++b, p += 34, out += 32) {
+        const float d = fc_f16_to_f32((uint16_t)(p[0] | ((uint16_t)p[1] << 8)));
+        for (int i = 0; i < 32; ++i) out[i] = d * (float)(int8_t)p[2 + i];
+    }
+    return FC_OK;
+}
+
+// rng.rs:9-48.
+uint64_t fc_rng_seed(uint64_t seed) { return seed ? seed : 0x9E3779B97F4A7C15ull; }
+
+static inline uint64_t rng_next(uint64_t* s) {
+    uint64_t x = *s;
+    x ^= x << 13;
+    x ^= x >> 7;
+    x ^= x << 17;
+    *s = x;
+    return x * 0x2545F4914F6CDD1Dull;
+}
+static inline float rng_unit(uint64_t* s) { return (float)(rng_next(s) >> 40) * (1.0f / 16777216.0f); }
+
+void fc_rng_fill_normal(uint64_t* state, float scale, size_t n, float* out) {
+    uint64_t s = *state;
+    for (size_t i = 0; i < n; ++i) {
+        float u1 = rng_unit(&s);
+        u1 = u1 > 1e-7f ? u1 : 1e-7f;
+        const float u2 = rng_unit(&s);
+        const float z = sqrtf(-2.0f * logf(u1)) * cosf(6.28318530717958647692f * u2);
+        out[i] = z * scale;
+    }
+    *state = s;
+}
+
+void fc_rng_fill_ids(uint64_t* state, int32_t vocab, size_t n, int32_t* out) {
+    uint64_t s = *state;
+    for (size_t i = 0; i < n; ++i) out[i] = (int32_t)(rng_next(&s) % (uint64_t)vocab);
+    *state = s;
+}
+
+}  // extern "C"

@@ -1,0 +1,114 @@
+// Shared declarations of libferrum_cuda: error plumbing, the device layout of a Q8_0
+// matrix, and the launch wrappers of every kernel file.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+
+#include "../../include/ferrum_cuda.h"
+
+namespace fc {
+
+// ---- errors -------------------------------------------------------------------------
+void set_error(const char* fmt, ...);
+int cuda_fail(cudaError_t e, const char* what, const char* file, int line);
+int fail(int code, const char* fmt, ...);
+extern thread_local int64_t g_launches;
+
+#define FC_CUDA(expr)                                                               \
+    do {                                                                            \
+        cudaError_t e__ = (expr);                                                   \
+        if (e__ != cudaSuccess) return fc::cuda_fail(e__, #expr, __FILE__, __LINE__); \
+    } while (0)
+#define FC_TRY(expr)                \
+    do {                            \
+        int rc__ = (expr);          \
+        if (rc__ != FC_OK) return rc__; \
+    } while (0)
+// After a kernel launch: count it and surface launch-configuration errors.
+#define FC_LAUNCHED()                \
+    do {                             \
+        ++fc::g_launches;            \
+        FC_CUDA(cudaGetLastError()); \
+    } while (0)
+
+// ---- device layout of one Q8_0 matrix [N][K] ----------------------------------------
+// The 34-byte GGML blocks are split at upload into two planes so that every row starts
+// on a 16-byte boundary:
+//   qu [N_pad][K]      uint8  = int8 quant XOR 0x80 (i.e. q + 128), K contiguous
+//   d  [N_pad][K/32]   f16    block scales
+// Rows N..N_pad-1 are zero scale / 0x80 quants (value 0) so tiles may read them.
+struct QMat {
+    const uint8_t* qu = nullptr;
+    const __half* d = nullptr;
+    int N = 0, K = 0, N_pad = 0;
+};
+constexpr int kRowPad = 128;
+
+enum Epilogue : int { EPI_NONE = 0, EPI_GELU = 1 };
+
+// activation.rs:9-12 (tanh GELU), same constants and association as the reference.
+__device__ __forceinline__ float gelu_f(float x) {
+    const float K = 0.7978846f;
+    return 0.5f * x * (1.0f + tanhf(K * (x + 0.044715f * x * x * x)));
+}
+
+// ---- decode-step device state (one per stream) ----------------------------------------
+// The "window" of token_stream.rs lives on the device: ids fed so far and ids waiting to
+// be fed, so that a whole greedy generation runs without a host round trip.
+struct StepState {
+    int pos;       // cache position of the next fed token (== cached_len)
+    int fed;       // index in queue of the next token to feed
+    int tail;      // number of ids in queue
+    int done;      // set when eos was selected: later steps do nothing
+    int eos;       // -1: none
+    int error;     // non-zero: bad id / cache full seen on device (FC_E_DIM)
+    int pad[2];
+};
+
+// ---- kernel launchers (each returns FC_OK or FC_E_CUDA) --------------------------------
+// repack.cu
+int launch_repack_q8(const uint8_t* raw, int N, int K, int N_pad, uint8_t* qu, __half* d, cudaStream_t st);
+
+// gemv.cu — y = W·x + bias (+GELU) (+residual), one activation row.
+struct GemvOut {
+    // Row n of the result goes to out[n / seg][n % seg]; segments 1 and 2 (K and V rows of
+    // the fused QKV matrix) are offset by pos * pos_stride floats, pos read from `state`.
+    float* out[3] = {nullptr, nullptr, nullptr};
+    int seg = 0;
+    size_t pos_stride = 0;
+};
+int launch_gemv_q8(const QMat& w, const float* x, const float* bias, const float* residual, int epi,
+                   const GemvOut& out, const StepState* state, cudaStream_t st);
+
+// gemm_simt.cu — Y[M][N] = X[M][K]·Wᵀ + bias (+GELU) (+residual[M][N]), fp32 CUDA cores.
+int launch_gemm_q8_fp32(const QMat& w, const float* x, const float* bias, const float* residual, int epi,
+                        float* y, int M, int ldy, cudaStream_t st);
+
+// rowops.cu
+int launch_embed_step(const QMat& tok, const float* pos_emb, int ctx, const int* queue, StepState* state,
+                      float* x, cudaStream_t st);
+int launch_embed_rows(const QMat& tok, const float* pos_emb, const int* ids, int R, int T, float* x,
+                      int* error_flag, cudaStream_t st);
+int launch_layernorm(const float* x, const float* g, const float* b, int rows, int d, float* y,
+                     const StepState* state, cudaStream_t st);
+// Decode tail over logits[V]: softmax statistics, optional probs[V], optional greedy select
+// (append to queue) — and always the end-of-step bookkeeping (pos, fed).
+int launch_step_tail(const float* logits, int V, float* probs_or_null, int do_select, int* queue, int queue_cap,
+                     StepState* state, float* sel_logit_or_null, cudaStream_t st);
+// End-of-step bookkeeping alone (steps that skip the head).
+int launch_step_advance(StepState* state, cudaStream_t st);
+// Scoring tail: per row of logits[R][ldl], target id (or -1) -> logprob, is_greedy.
+int launch_score_rows(const float* logits, int ldl, int V, const int* targets, int R, double* logprob,
+                      uint8_t* is_greedy, cudaStream_t st);
+int launch_softmax_row(const float* logits, int V, float* probs, cudaStream_t st);
+
+// attn.cu
+int launch_attn_decode(const float* q, const float* kcache, const float* vcache, int d, int H, int ctx,
+                       const StepState* state, float* out, cudaStream_t st);
+// qkv [R][3d] (q | k | v per row), R = B·T, causal within each window of T rows.
+int launch_attn_prefill(const float* qkv, int B, int T, int d, int H, float* out, cudaStream_t st);
+
+}  // namespace fc

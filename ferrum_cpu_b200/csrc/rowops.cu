@@ -1,0 +1,282 @@
+// Row kernels of the forward path: embedding gather, LayerNorm, the decode tail
+// (softmax statistics + greedy select) and the scoring tail (per-target log-prob).
+#include "fc_common.cuh"
+
+namespace fc {
+
+// ------------------------------------------------------------------------ block reductions
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+// Fixed-order block reductions (deterministic run to run). `red` has >= 33 floats.
+__device__ float block_sum(float v, float* red) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) red[wid] = v;
+    __syncthreads();
+    if (wid == 0) {
+        float t = lane < nw ? red[lane] : 0.0f;
+        t = warp_sum(t);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+}
+__device__ float block_max(float v, float* red) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) red[wid] = v;
+    __syncthreads();
+    if (wid == 0) {
+        float t = lane < nw ? red[lane] : -INFINITY;
+        t = warp_max(t);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+}
+
+// ------------------------------------------------------------------------------ embedding
+// layer/embedding.rs:70-90 embed_one / :98-152 forward: x = tok[id] + pos[t]. The token
+// table stays Q8_0; d * q is the same single rounding gguf::dequant_q8_0 performs.
+__device__ __forceinline__ float tok_value(const QMat& tok, int id, int c) {
+    const float dq = __half2float(tok.d[(size_t)id * (tok.K >> 5) + (c >> 5)]);
+    const int q = (int)tok.qu[(size_t)id * tok.K + c] - 128;
+    return dq * (float)q;
+}
+
+__global__ void embed_step_kernel(QMat tok, const float* __restrict__ pos_emb, int ctx,
+                                  const int* __restrict__ queue, StepState* st, float* __restrict__ x) {
+    if (st->done | st->error) return;
+    const int pos = st->pos, id = queue[st->fed];
+    // embedding.rs:71-82 and transformer.rs:237-242: bad id / full cache are errors, not traps
+    if (id < 0 || id >= tok.N || pos >= ctx) {
+        __syncthreads();
+        if (threadIdx.x == 0) st->error = FC_E_DIM;
+        return;
+    }
+    for (int c = threadIdx.x; c < tok.K; c += blockDim.x) x[c] = tok_value(tok, id, c) + pos_emb[(size_t)pos * tok.K + c];
+}
+
+int launch_embed_step(const QMat& tok, const float* pos_emb, int ctx, const int* queue, StepState* state,
+                      float* x, cudaStream_t st) {
+    embed_step_kernel<<<1, 256, 0, st>>>(tok, pos_emb, ctx, queue, state, x);
+    FC_LAUNCHED();
+    return FC_OK;
+}
+
+__global__ void embed_rows_kernel(QMat tok, const float* __restrict__ pos_emb, const int* __restrict__ ids,
+                                  int T, float* __restrict__ x, int* error_flag) {
+    const int r = blockIdx.x, t = r % T;
+    int id = ids[r];
+    if (id < 0 || id >= tok.N) {
+        if (threadIdx.x == 0) atomicExch(error_flag, FC_E_DIM);
+        id = 0;
+    }
+    for (int c = threadIdx.x; c < tok.K; c += blockDim.x)
+        x[(size_t)r * tok.K + c] = tok_value(tok, id, c) + pos_emb[(size_t)t * tok.K + c];
+}
+
+int launch_embed_rows(const QMat& tok, const float* pos_emb, const int* ids, int R, int T, float* x,
+                      int* error_flag, cudaStream_t st) {
+    embed_rows_kernel<<<R, 256, 0, st>>>(tok, pos_emb, ids, T, x, error_flag);
+    FC_LAUNCHED();
+    return FC_OK;
+}
+
+// ------------------------------------------------------------------------------ LayerNorm
+// layer/norm.rs:46-82: mean, then the variance of (x - mean), std = sqrt(var + 1e-5),
+// y = ((x - mean) / std) * gamma + beta. One block per row; the row is held in registers.
+template <int PER>
+__global__ void layernorm_kernel(const float* __restrict__ x, const float* __restrict__ g, const float* __restrict__ b,
+                                 int d, float* __restrict__ y, const StepState* st) {
+    __shared__ float red[33];
+    if (st && (st->done | st->error)) return;
+    const float* xr = x + (size_t)blockIdx.x * d;
+    float v[PER];
+    float s = 0.0f;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        v[i] = c < d ? xr[c] : 0.0f;
+        s += v[i];
+    }
+    const float mean = block_sum(s, red) / (float)d;
+    float q = 0.0f;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        const float t = v[i] - mean;
+        q += c < d ? t * t : 0.0f;
+    }
+    const float var = block_sum(q, red) / (float)d;
+    const float sd = sqrtf(var + 1e-5f);
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < d) y[(size_t)blockIdx.x * d + c] = ((v[i] - mean) / sd) * g[c] + b[c];
+    }
+}
+
+int launch_layernorm(const float* x, const float* g, const float* b, int rows, int d, float* y,
+                     const StepState* state, cudaStream_t st) {
+    const int threads = 256;
+    const int per = (d + threads - 1) / threads;
+    if (per <= 4) layernorm_kernel<4><<<rows, threads, 0, st>>>(x, g, b, d, y, state);
+    else if (per <= 8) layernorm_kernel<8><<<rows, threads, 0, st>>>(x, g, b, d, y, state);
+    else if (per <= 16) layernorm_kernel<16><<<rows, threads, 0, st>>>(x, g, b, d, y, state);
+    else return fail(FC_E_SHAPE, "LayerNorm width %d exceeds 4096", d);
+    FC_LAUNCHED();
+    return FC_OK;
+}
+
+// ------------------------------------------------------------------------------ decode tail
+// ops.rs:478-502 softmax_rows on one row, then (when selecting) token_stream.rs:134 +
+// sampling.rs:96-104,147: logit_i = ln(max(p_i, 1e-12)), first index of the largest.
+// One block. The sum runs in a fixed tree order, not the reference's ascending order.
+struct ArgPair { float v; int i; };
+__device__ __forceinline__ ArgPair better(ArgPair a, ArgPair b) {
+    // larger value wins; equal values: smaller index (first on ties)
+    return (b.v > a.v || (b.v == a.v && b.i < a.i)) ? b : a;
+}
+
+__global__ void __launch_bounds__(1024) step_tail_kernel(const float* __restrict__ logits, int V, float* __restrict__ probs,
+                                                         int do_select, int* __restrict__ queue, int queue_cap,
+                                                         StepState* st, float* sel_logit) {
+    __shared__ float red[33];
+    __shared__ ArgPair pred[32];
+    if (st->done | st->error) return;
+    float mx = -INFINITY;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) mx = fmaxf(mx, logits[i]);
+    mx = block_max(mx, red);
+    float s = 0.0f;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) s += expf(logits[i] - mx);
+    const float sum = block_sum(s, red);
+    if (probs)
+        for (int i = threadIdx.x; i < V; i += blockDim.x) probs[i] = expf(logits[i] - mx) / sum;
+    if (do_select) {
+        ArgPair best{-INFINITY, 0x7fffffff};
+        for (int i = threadIdx.x; i < V; i += blockDim.x) {
+            const float p = expf(logits[i] - mx) / sum;
+            best = better(best, ArgPair{logf(fmaxf(p, 1e-12f)), i});
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            ArgPair other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+            best = better(best, other);
+        }
+        const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+        if (lane == 0) pred[wid] = best;
+        __syncthreads();
+        if (wid == 0) {
+            best = lane < (int)((blockDim.x + 31) >> 5) ? pred[lane] : ArgPair{-INFINITY, 0x7fffffff};
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                ArgPair other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+                best = better(best, other);
+            }
+            if (lane == 0) {
+                if (sel_logit) sel_logit[st->tail < queue_cap ? st->tail : queue_cap - 1] = best.v;
+                if (best.i == st->eos) {
+                    st->done = 1;
+                } else if (st->tail < queue_cap) {
+                    queue[st->tail] = best.i;
+                    st->tail += 1;
+                } else {
+                    st->error = FC_E_DIM;
+                }
+            }
+        }
+    }
+    if (threadIdx.x == 0) { st->pos += 1; st->fed += 1; }
+}
+
+int launch_step_tail(const float* logits, int V, float* probs_or_null, int do_select, int* queue, int queue_cap,
+                     StepState* state, float* sel_logit_or_null, cudaStream_t st) {
+    step_tail_kernel<<<1, 1024, 0, st>>>(logits, V, probs_or_null, do_select, queue, queue_cap, state, sel_logit_or_null);
+    FC_LAUNCHED();
+    return FC_OK;
+}
+
+__global__ void step_advance_kernel(StepState* st) {
+    if (st->done | st->error) return;
+    st->pos += 1;
+    st->fed += 1;
+}
+int launch_step_advance(StepState* state, cudaStream_t st) {
+    step_advance_kernel<<<1, 1, 0, st>>>(state);
+    FC_LAUNCHED();
+    return FC_OK;
+}
+
+// ------------------------------------------------------------------------------ scoring tail
+// scoring.rs:175-181: p = softmax(row)[target] in f32, clamp_prob (loss.rs:12-18), ln in
+// f64; greedy = argmax_first(row) == target, where the row is the probability row: the
+// first index whose exp(x - max) / sum equals the largest such value.
+__global__ void __launch_bounds__(256) score_rows_kernel(const float* __restrict__ logits, int ldl, int V,
+                                                         const int* __restrict__ targets, double* __restrict__ logprob,
+                                                         uint8_t* __restrict__ is_greedy) {
+    __shared__ float red[33];
+    __shared__ int ired[32];
+    const int r = blockIdx.x, target = targets[r];
+    if (target < 0 || target >= V) {
+        if (threadIdx.x == 0) { logprob[r] = 0.0; is_greedy[r] = 0; }
+        return;
+    }
+    const float* row = logits + (size_t)r * ldl;
+    float mx = -INFINITY;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) mx = fmaxf(mx, row[i]);
+    mx = block_max(mx, red);
+    float s = 0.0f;
+    int first = 0x7fffffff;          // first index whose probability ties the maximum's
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        const float e = expf(row[i] - mx);
+        s += e;
+        if (e == 1.0f && i < first) first = i;
+    }
+    const float sum = block_sum(s, red);
+    for (int o = 16; o > 0; o >>= 1) first = min(first, __shfl_xor_sync(0xffffffffu, first, o));
+    if ((threadIdx.x & 31) == 0) ired[threadIdx.x >> 5] = first;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (int)(blockDim.x >> 5); ++w) first = min(first, ired[w]);
+        float p = expf(row[target] - mx) / sum;
+        if (p == p) p = fmaxf(p, 1e-12f);
+        logprob[r] = log((double)p);
+        is_greedy[r] = (uint8_t)(first == target);
+    }
+}
+
+int launch_score_rows(const float* logits, int ldl, int V, const int* targets, int R, double* logprob,
+                      uint8_t* is_greedy, cudaStream_t st) {
+    score_rows_kernel<<<R, 256, 0, st>>>(logits, ldl, V, targets, logprob, is_greedy);
+    FC_LAUNCHED();
+    return FC_OK;
+}
+
+__global__ void __launch_bounds__(1024) softmax_row_kernel(const float* __restrict__ logits, int V, float* __restrict__ probs) {
+    __shared__ float red[33];
+    float mx = -INFINITY;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) mx = fmaxf(mx, logits[i]);
+    mx = block_max(mx, red);
+    float s = 0.0f;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) s += expf(logits[i] - mx);
+    const float sum = block_sum(s, red);
+    for (int i = threadIdx.x; i < V; i += blockDim.x) probs[i] = expf(logits[i] - mx) / sum;
+}
+int launch_softmax_row(const float* logits, int V, float* probs, cudaStream_t st) {
+    softmax_row_kernel<<<1, 1024, 0, st>>>(logits, V, probs);
+    FC_LAUNCHED();
+    return FC_OK;
+}
+
+}  // namespace fc

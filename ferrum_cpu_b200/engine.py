@@ -1,0 +1,182 @@
+"""Python face of the C ABI, named after the reference interfaces it stands in for.
+
+CudaSlm mirrors the numeric subset of ferrum_core's GenerativeSLM / CachedTransformer and
+the wasm TransformerSLMModel (slm/scoring.rs, slm/cached.rs, slm/token_stream.rs,
+slm_wasm/src/lib.rs:217-241) on token ids; text, tokenizer and stop strings stay with the
+caller. Every method is a thin ctypes call: the arithmetic lives in libferrum_cuda.so.
+"""
+import ctypes as C
+from dataclasses import dataclass
+
+import numpy as np
+
+from . import _lib
+from ._lib import FerrumCudaError, check  # noqa: F401
+
+
+def _ptr(a):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def _ids(ids):
+    return np.ascontiguousarray(ids, dtype=np.int32)
+
+
+@dataclass
+class Score:
+    """slm/scoring.rs Score."""
+    logprob: float
+    n_tokens: int
+    greedy: bool
+
+
+def device_count():
+    return _lib.lib().fc_device_count()
+
+
+def take_launch_count():
+    return _lib.lib().fc_take_launch_count()
+
+
+def q8_0_linear(x, wq, bias, n_out, device=0, math_mode=_lib.FC_MATH_FP32):
+    """y = x · dequant(wq)ᵀ + bias with host arrays (ops::linear_forward on a packed weight)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    m, k = x.shape
+    wq = np.ascontiguousarray(wq, dtype=np.uint8)
+    y = np.empty((m, n_out), dtype=np.float32)
+    b = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32)
+    check(_lib.lib().fc_q8_0_linear(device, _ptr(x), _ptr(wq), None if b is None else _ptr(b), _ptr(y),
+                                    m, k, n_out, math_mode))
+    return y
+
+
+class QWeight:
+    """One Q8_0 matrix resident on a GPU (the packed-weight seam of layer/linear.rs:21-35)."""
+
+    def __init__(self, wq, n_out, k_in, device=0):
+        wq = np.ascontiguousarray(wq, dtype=np.uint8)
+        self._h = C.c_void_p()
+        self.n, self.k, self.device = n_out, k_in, device
+        check(_lib.lib().fc_qweight_upload(device, _ptr(wq), n_out, k_in, C.byref(self._h)))
+
+    def linear_dev(self, x_dev_ptr, bias_dev_ptr, y_dev_ptr, m, math_mode=_lib.FC_MATH_FP32, stream=None):
+        check(_lib.lib().fc_q8_0_linear_dev(self._h, x_dev_ptr, bias_dev_ptr, y_dev_ptr, m, math_mode, stream))
+
+    def close(self):
+        if self._h:
+            _lib.lib().fc_qweight_free(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        self.close()
+
+
+class CudaSlm:
+    """A GPT-2-architecture Q8_0 model on one GPU plus one KV-cached stream."""
+
+    def __init__(self, config, weights, device=0):
+        self._m = C.c_void_p()
+        self._s = C.c_void_p()
+        check(_lib.lib().fc_model_create(C.byref(config), C.byref(weights), device, C.byref(self._m)))
+        cfg = _lib.FcConfig()
+        check(_lib.lib().fc_model_config(self._m, C.byref(cfg)))
+        self.config = cfg
+        self.device = device
+
+    # ---- scoring (slm/scoring.rs) ---------------------------------------------------
+    def token_logprobs(self, ids, from_=1, per_token=False):
+        ids = _ids(ids)
+        sc = _lib.FcScore()
+        lp = np.zeros(ids.size, dtype=np.float32) if per_token else None
+        gr = np.zeros(ids.size, dtype=np.uint8) if per_token else None
+        check(_lib.lib().fc_token_logprobs(self._m, _ptr(ids), ids.size, from_, C.byref(sc),
+                                           None if lp is None else _ptr(lp), None if gr is None else _ptr(gr)))
+        score = Score(sc.logprob, sc.n_tokens, bool(sc.greedy))
+        return (score, lp, gr) if per_token else score
+
+    def evaluate_ids(self, ids):
+        """scoring.rs:77-87: every id after the first is a target."""
+        return self.token_logprobs(ids, 1)
+
+    def score_sequences(self, ids2d, batch_windows=32, lp_out=None):
+        ids2d = _ids(ids2d)
+        n_seq, seq_len = ids2d.shape
+        scores = (_lib.FcScore * n_seq)()
+        lp = lp_out if lp_out is not None else np.zeros((n_seq, seq_len), dtype=np.float32)
+        check(_lib.lib().fc_score_sequences(self._m, _ptr(ids2d), n_seq, seq_len, batch_windows, scores, _ptr(lp)))
+        return [Score(s.logprob, s.n_tokens, bool(s.greedy)) for s in scores], lp
+
+    def score_windows(self, ids2d, targets2d):
+        ids2d, targets2d = _ids(ids2d), _ids(targets2d)
+        b, t = ids2d.shape
+        lp = np.zeros((b, t), dtype=np.float32)
+        gr = np.zeros((b, t), dtype=np.uint8)
+        check(_lib.lib().fc_score_windows(self._m, _ptr(ids2d), _ptr(targets2d), b, t, _ptr(lp), _ptr(gr)))
+        return lp, gr
+
+    def predict_next(self, ids):
+        """TransformerSLMModel::predict_next: probabilities after the last of `ids`."""
+        ids = _ids(ids)
+        probs = np.empty(self.config.vocab, dtype=np.float32)
+        check(_lib.lib().fc_predict_next(self._m, _ptr(ids), ids.size, _ptr(probs)))
+        return probs
+
+    @property
+    def last_score_ms(self):
+        return _lib.lib().fc_last_score_ms(self._m)
+
+    # ---- KV-cached decode (slm/cached.rs, slm/token_stream.rs) --------------------------
+    def _stream(self):
+        if not self._s:
+            check(_lib.lib().fc_stream_create(self._m, C.byref(self._s)))
+        return self._s
+
+    def prime(self, ids, want_probs=True):
+        ids = _ids(ids)
+        probs = np.empty(self.config.vocab, dtype=np.float32) if want_probs else None
+        check(_lib.lib().fc_prime(self._stream(), _ptr(ids), ids.size, None if probs is None else _ptr(probs)))
+        return probs
+
+    def predict_next_cached(self, token, want_probs=True):
+        """CachedTransformer::feed / TokenModel::predict_next_cached."""
+        probs = np.empty(self.config.vocab, dtype=np.float32) if want_probs else None
+        check(_lib.lib().fc_feed(self._stream(), int(token), None if probs is None else _ptr(probs)))
+        return probs
+
+    feed = predict_next_cached
+
+    def reset(self):
+        check(_lib.lib().fc_stream_reset(self._stream()))
+
+    def cached_len(self):
+        return _lib.lib().fc_cached_len(self._stream())
+
+    def generate_tokens(self, prompt_ids, max_tokens, eos=-1, cancel=None, out=None):
+        """generate_tokens with temperature <= 0: greedy ids (token_stream.rs:66-189)."""
+        prompt = _ids(prompt_ids)
+        buf = out if out is not None else np.empty(max(max_tokens, 1), dtype=np.int32)
+        n_out = C.c_int(0)
+        rc = _lib.lib().fc_generate_greedy(self._stream(), _ptr(prompt), prompt.size, max_tokens, eos,
+                                           None if cancel is None else _ptr(cancel), _ptr(buf), C.byref(n_out))
+        if rc == _lib.FC_E_CANCELLED:
+            return buf[:n_out.value].copy(), True
+        check(rc)
+        return buf[:n_out.value].copy(), False
+
+    @property
+    def last_decode_ms(self):
+        return _lib.lib().fc_last_decode_ms(self._stream())
+
+    def close(self):
+        if self._s:
+            _lib.lib().fc_stream_free(self._s)
+            self._s = C.c_void_p()
+        if self._m:
+            _lib.lib().fc_model_free(self._m)
+            self._m = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -1,0 +1,170 @@
+/* ferrum_cuda.h — C ABI of libferrum_cuda.so: the Q8_0 GPT-2 forward path of Ferrum
+ * on NVIDIA B200 (sm_100a).
+ *
+ * The reference (thomascherickal/ferrum-cpu, 100 % safe Rust) has no FFI surface; the
+ * entry points below are what a `ferrum_cuda` crate binds to replace the Rust items
+ * cited beside each declaration (paths are relative to the reference repository).
+ *
+ * Conventions
+ *  - every call returns an int status: FC_OK (0) or a negative FC_E_* code; the text of
+ *    the last error on the calling thread is returned by fc_last_error();
+ *  - no call aborts, throws or traps; bad ids, shapes and full caches are FC_E_DIM as
+ *    the reference's InferError::DimMismatch (ferrum_core/src/error.rs:6-26);
+ *  - the caller owns every host buffer it passes; the library copies at create time and
+ *    owns all device memory until the matching *_free;
+ *  - one handle is used by one host thread at a time (the reference model is !Send,
+ *    ferrum_core/src/layer/transformer.rs:82; the server keeps it on one thread,
+ *    slm_server/src/model_thread.rs:111-143);
+ *  - there is no CPU fallback: a call fails with FC_E_CUDA when no sm_100 device exists.
+ */
+#ifndef FERRUM_CUDA_H
+#define FERRUM_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FC_OK 0
+#define FC_E_SHAPE (-1)     /* InferError::ShapeMismatch / NotAMatrix */
+#define FC_E_DIM (-2)       /* InferError::DimMismatch: id >= vocab, cache full, width mismatch */
+#define FC_E_FORMAT (-3)    /* InferError::Format: K % 32 != 0, null tensor */
+#define FC_E_CUDA (-4)      /* a CUDA runtime call failed, or no sm_100 device */
+#define FC_E_TIMEOUT (-5)   /* a bounded device-side wait ran out */
+#define FC_E_CANCELLED (-6) /* the cancel flag was seen set */
+#define FC_E_ARG (-7)       /* null handle / null required pointer */
+
+/* Math modes of the prefill GEMM. Decode always runs fp32 FMA on CUDA cores. */
+#define FC_MATH_FP32 0      /* fp32 CUDA-core GEMM (exactly rounded products) */
+#define FC_MATH_BF16X3 1    /* tcgen05 kind::f16 bf16 operands, 3-term split, fp32 TMEM accumulate */
+
+/* Dimensions of a gpt2-architecture GGUF (ferrum_core/src/loader/gpt2.rs:201-215). */
+typedef struct fc_config {
+    int32_t n_layer, d_model, n_head, d_ff, ctx, vocab;
+    int32_t tied;       /* 1: no output.weight, the head is token_embd (gpt2.rs:228-233) */
+    int32_t math_mode;  /* FC_MATH_* */
+} fc_config;
+
+/* One transformer block's tensors in GGUF order (loader/gpt2.rs:236-262). A `*_q8`
+ * pointer is the raw GGML Q8_0 tensor: rows of K/32 blocks of 34 bytes
+ * [u16 f16 scale, little endian][32 x i8] (gguf_write/blocks.rs:132-140). */
+typedef struct fc_layer_weights {
+    const void* attn_qkv_q8;  const float* attn_qkv_b;   /* [3d][d] rows Q,K,V ; [3d] */
+    const void* attn_out_q8;  const float* attn_out_b;   /* [d][d] ; [d] */
+    const float *ln1_g, *ln1_b, *ln2_g, *ln2_b;          /* attn_norm, ffn_norm ; [d] each */
+    const void* ffn_up_q8;    const float* ffn_up_b;     /* [F][d] ; [F] */
+    const void* ffn_down_q8;  const float* ffn_down_b;   /* [d][F] ; [d] */
+} fc_layer_weights;
+
+typedef struct fc_weights {
+    const void* token_embd_q8;      /* [V][d] */
+    const float* position_embd;     /* [ctx][d] f32 */
+    const fc_layer_weights* layers; /* n_layer entries */
+    const float *out_norm_g, *out_norm_b;
+    const void* output_q8;          /* [V][d] or NULL when tied */
+} fc_weights;
+
+typedef struct fc_model fc_model;     /* Sequential + weights on one GPU (model.rs:51-71) */
+typedef struct fc_stream fc_stream;   /* CachedTransformer: KV caches + position (slm/cached.rs:45-64) */
+typedef struct fc_qweight fc_qweight; /* one Q8_0 matrix resident on a GPU (precedent: quant.rs:130-146 QWeight) */
+
+/* Result of scoring, as ferrum_core/src/slm/scoring.rs Score {logprob, n_tokens, greedy}. */
+typedef struct fc_score {
+    double logprob;
+    int64_t n_tokens;
+    int32_t greedy;
+} fc_score;
+
+const char* fc_last_error(void);
+/* Number of visible sm_100 devices (0 when none; never fails). */
+int fc_device_count(void);
+
+/* ---- host-side codecs (load time; not part of the forward pass) ------------------- */
+/* quant.rs:271-280 q8_0_block over n values (n % 32 == 0) -> n/32*34 bytes. */
+int fc_q8_0_quantize(const float* x, size_t n, void* out);
+/* gguf/dequant.rs:37-49 dequant_q8_0. */
+int fc_q8_0_dequantize(const void* raw, size_t n, float* out);
+uint16_t fc_f32_to_f16(float v);  /* gguf_write/blocks.rs:12-61 */
+float fc_f16_to_f32(uint16_t h);  /* gguf/dequant.rs:7-35 */
+/* rng.rs:9-48 xorshift64*: seed -> state (0 is remapped), draws advance *state. */
+uint64_t fc_rng_seed(uint64_t seed);
+void fc_rng_fill_normal(uint64_t* state, float scale, size_t n, float* out);
+void fc_rng_fill_ids(uint64_t* state, int32_t vocab, size_t n, int32_t* out);
+
+/* ---- standalone Q8_0 linear: the matmul-engine entry ------------------------------ */
+/* y[M][N] = x[M][K] · dequant(wq[N][K])ᵀ + bias — replaces ops::linear_forward
+ * (ops.rs:233-256) on a weight kept packed (the seam Linear::forward dispatches on,
+ * layer/linear.rs:191-194). Host buffers; copies in and out. M == 1 runs the decode
+ * GEMV, M >= 2 the prefill GEMM in `math_mode`. bias may be NULL. */
+int fc_q8_0_linear(int device, const float* x, const void* wq, const float* bias, float* y,
+                   int M, int K, int N, int math_mode);
+/* The same with the weight resident: upload once, multiply many times on device
+ * pointers (x_dev, bias_dev, y_dev are device memory on the weight's GPU). */
+int fc_qweight_upload(int device, const void* wq, int N, int K, fc_qweight** out);
+void fc_qweight_free(fc_qweight* w);
+int fc_q8_0_linear_dev(const fc_qweight* w, const float* x_dev, const float* bias_dev, float* y_dev,
+                       int M, int math_mode, void* cuda_stream);
+
+/* ---- model ------------------------------------------------------------------------ */
+/* Validates as loader/gpt2.rs + loader/mod.rs:147-154 (d % n_head == 0, K % 32 == 0),
+ * uploads and repacks the weights on `device`. */
+int fc_model_create(const fc_config* cfg, const fc_weights* w, int device, fc_model** out);
+void fc_model_free(fc_model* m);
+int fc_model_config(const fc_model* m, fc_config* out);
+
+/* ---- scoring: Sequential::forward + the Softmax tail, fused ------------------------ */
+/* B windows of exactly T <= ctx ids each (right-padded by the caller as scoring.rs:184-193
+ * pads with id 0). For row t of window b the target is targets[b][t] (or -1: skip).
+ * logprob = ln(max(p, 1e-12)) of the target under the model's softmax (f32 prob, f64 ln:
+ * scoring.rs:175-181, loss.rs:12-18); is_greedy = argmax_first(row) == target. Outputs are
+ * host arrays [B][T]; skipped rows get 0. */
+int fc_score_windows(fc_model* m, const int32_t* ids, const int32_t* targets, int B, int T,
+                     float* logprob, uint8_t* is_greedy);
+/* GenerativeSLM::token_logprobs (scoring.rs:151-213): window plan, <= 32 windows per
+ * forward, f64 sum. lp / is_greedy are optional host arrays of length n (entries below
+ * `from` are left untouched). */
+int fc_token_logprobs(fc_model* m, const int32_t* ids, int n, int from, fc_score* score,
+                      float* lp, uint8_t* is_greedy);
+/* n_seq independent sequences of seq_len ids each, all scored from target 1; windows of
+ * different sequences share forward batches of `batch_windows` windows. */
+int fc_score_sequences(fc_model* m, const int32_t* ids, int n_seq, int seq_len, int batch_windows,
+                       fc_score* scores, float* lp);
+/* Full-window next-token distributions, as TransformerSLMModel::predict_next
+ * (slm_wasm/src/lib.rs:217-241): probs[V] of the last of n <= ctx ids. */
+int fc_predict_next(fc_model* m, const int32_t* ids, int n, float* probs);
+
+/* ---- KV-cached decode: CachedTransformer ----------------------------------------- */
+int fc_stream_create(fc_model* m, fc_stream** out);   /* cached.rs:45-64 try_new */
+void fc_stream_free(fc_stream* s);
+int fc_stream_reset(fc_stream* s);                    /* cached.rs:93-98 */
+int fc_cached_len(const fc_stream* s);
+/* cached.rs:100-125 feed: one token; probs (host [V]) may be NULL. FC_E_DIM on id >= vocab
+ * or a full cache (transformer.rs:237-242). */
+int fc_feed(fc_stream* s, int32_t token, float* probs);
+/* cached.rs:129-136 prime: reset, then feed every id. */
+int fc_prime(fc_stream* s, const int32_t* ids, int n, float* probs);
+/* token_stream.rs:66-189 with temperature <= 0: keep the last ctx prompt ids, prime, then
+ * per step argmax_first(ln(max(p,1e-12))) (sampling.rs:96-104,147), stop before emitting
+ * `eos` (pass -1 for none), re-prime on the last ctx/2 ids when the window outgrows ctx,
+ * else feed. `cancel` (may be NULL) is polled on the host between steps
+ * (sampling.rs:69-73); when seen set the call returns FC_E_CANCELLED with *n_out tokens
+ * valid. out: host [max_new]. */
+int fc_generate_greedy(fc_stream* s, const int32_t* prompt, int n, int max_new, int32_t eos,
+                       const volatile int32_t* cancel, int32_t* out, int* n_out);
+
+/* ---- introspection used by the benchmark ----------------------------------------- */
+/* Kernel launches issued by this library on the calling thread since the last call
+ * (returns the count and resets it). */
+int64_t fc_take_launch_count(void);
+/* Device time in ms of the decode steps of the last fc_generate_greedy on this stream
+ * (CUDA events on the launching stream around the feeds after the prime). */
+float fc_last_decode_ms(const fc_stream* s);
+/* Device time in ms of the forward passes of the last scoring call on this model. */
+float fc_last_score_ms(const fc_model* m);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FERRUM_CUDA_H */

@@ -1,0 +1,197 @@
+"""ctypes wrapper of the CPU oracle (oracle/libferrum_oracle.so). Test infrastructure:
+only tests, the smoke check and the benchmark's CPU-baseline leg import this module."""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ORACLE_DIR = os.path.join(ROOT, "oracle")
+LIB_PATH = os.path.join(ORACLE_DIR, "libferrum_oracle.so")
+
+_lib = None
+
+
+def _ptr(a):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            subprocess.run(["make", "-C", ORACLE_DIR], check=True, capture_output=True)
+        L = C.CDLL(LIB_PATH)
+        L.fo_f32_to_f16.restype, L.fo_f32_to_f16.argtypes = C.c_uint16, [C.c_float]
+        L.fo_f16_to_f32.restype, L.fo_f16_to_f32.argtypes = C.c_float, [C.c_uint16]
+        L.fo_q8_0_encode.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p]
+        L.fo_q8_0_decode.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p]
+        L.fo_rng_seed.restype, L.fo_rng_seed.argtypes = C.c_uint64, [C.c_uint64]
+        L.fo_rng_next_u64.restype, L.fo_rng_next_u64.argtypes = C.c_uint64, [C.POINTER(C.c_uint64)]
+        L.fo_rng_fill_normal.argtypes = [C.POINTER(C.c_uint64), C.c_float, C.c_size_t, C.c_void_p]
+        L.fo_rng_fill_ids.argtypes = [C.POINTER(C.c_uint64), C.c_int32, C.c_size_t, C.c_void_p]
+        L.fo_linear.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int]
+        L.fo_linear_naive.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
+        L.fo_q8_0_expand_kn.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p]
+        L.fo_layernorm.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]
+        L.fo_gelu.restype, L.fo_gelu.argtypes = C.c_float, [C.c_float]
+        L.fo_softmax_rows.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p]
+        L.fo_argmax_first.restype, L.fo_argmax_first.argtypes = C.c_int, [C.c_void_p, C.c_int]
+        L.fo_model_create.restype, L.fo_model_create.argtypes = C.c_void_p, [C.c_void_p, C.c_void_p, C.c_int]
+        L.fo_model_free.argtypes = [C.c_void_p]
+        L.fo_model_set_threads.argtypes = [C.c_void_p, C.c_int]
+        L.fo_forward.restype, L.fo_forward.argtypes = C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]
+        L.fo_stream_create.restype, L.fo_stream_create.argtypes = C.c_void_p, [C.c_void_p]
+        L.fo_stream_free.argtypes = [C.c_void_p]
+        L.fo_stream_reset.argtypes = [C.c_void_p]
+        L.fo_cached_len.restype, L.fo_cached_len.argtypes = C.c_int, [C.c_void_p]
+        L.fo_feed.restype, L.fo_feed.argtypes = C.c_int, [C.c_void_p, C.c_int, C.c_void_p]
+        L.fo_prime.restype, L.fo_prime.argtypes = C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
+        L.fo_generate_greedy.restype = C.c_int
+        L.fo_generate_greedy.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+        L.fo_token_logprobs.restype = C.c_int
+        L.fo_token_logprobs.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_double),
+                                        C.POINTER(C.c_int), C.POINTER(C.c_int), C.c_void_p, C.c_void_p]
+        _lib = L
+    return _lib
+
+
+def f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def q8_0_encode(x):
+    x = f32(x).ravel()
+    out = np.empty(x.size // 32 * 34, dtype=np.uint8)
+    lib().fo_q8_0_encode(_ptr(x), x.size, _ptr(out))
+    return out
+
+
+def q8_0_decode(raw, n):
+    raw = np.ascontiguousarray(raw, dtype=np.uint8)
+    out = np.empty(n, dtype=np.float32)
+    lib().fo_q8_0_decode(_ptr(raw), n, _ptr(out))
+    return out
+
+
+def fill_normal(seed, n, scale):
+    st = C.c_uint64(lib().fo_rng_seed(seed))
+    out = np.empty(n, dtype=np.float32)
+    lib().fo_rng_fill_normal(C.byref(st), scale, n, _ptr(out))
+    return out
+
+
+def fill_ids(seed, n, vocab):
+    st = C.c_uint64(lib().fo_rng_seed(seed))
+    out = np.empty(n, dtype=np.int32)
+    lib().fo_rng_fill_ids(C.byref(st), vocab, n, _ptr(out))
+    return out
+
+
+def linear(x, w_kn, bias, threads=1, naive=False):
+    x, w_kn = f32(x), f32(w_kn)
+    m, k = x.shape
+    n = w_kn.shape[1]
+    b = None if bias is None else f32(bias)
+    y = np.empty((m, n), dtype=np.float32)
+    if naive:
+        lib().fo_linear_naive(_ptr(x), _ptr(w_kn), None if b is None else _ptr(b), m, k, n, _ptr(y))
+    else:
+        lib().fo_linear(_ptr(x), _ptr(w_kn), None if b is None else _ptr(b), m, k, n, _ptr(y), threads)
+    return y
+
+
+def expand_kn(wq, n, k):
+    """Q8_0 [n][k] -> f32 [k][n] exactly as the reference loader expands and transposes it."""
+    wq = np.ascontiguousarray(wq, dtype=np.uint8)
+    out = np.empty((k, n), dtype=np.float32)
+    lib().fo_q8_0_expand_kn(_ptr(wq), n, k, _ptr(out))
+    return out
+
+
+def layernorm(x, g, b):
+    x, g, b = f32(x), f32(g), f32(b)
+    out = np.empty_like(x)
+    lib().fo_layernorm(_ptr(x), _ptr(g), _ptr(b), x.shape[0], x.shape[1], _ptr(out))
+    return out
+
+
+def softmax_rows(x):
+    x = f32(x)
+    out = np.empty_like(x)
+    lib().fo_softmax_rows(_ptr(x), x.shape[0], x.shape[1], _ptr(out))
+    return out
+
+
+def argmax_first(x):
+    x = f32(x)
+    return lib().fo_argmax_first(_ptr(x), x.size)
+
+
+class OracleModel:
+    """The restated reference model built from the same fc_config / fc_weights structs."""
+
+    def __init__(self, synth_model, threads=1):
+        self.sm = synth_model
+        self.V = synth_model.dims[5]
+        self.T = synth_model.dims[4]
+        self._m = lib().fo_model_create(C.addressof(synth_model.config), C.addressof(synth_model.weights), threads)
+        assert self._m, "oracle rejected the model"
+        self._s = lib().fo_stream_create(self._m)
+
+    def set_threads(self, n):
+        lib().fo_model_set_threads(self._m, n)
+
+    def forward(self, ids2d):
+        ids2d = np.ascontiguousarray(ids2d, dtype=np.int32)
+        b, t = ids2d.shape
+        probs = np.empty((b * t, self.V), dtype=np.float32)
+        assert lib().fo_forward(self._m, _ptr(ids2d), b, t, _ptr(probs)) == 0
+        return probs
+
+    def prime(self, ids):
+        ids = np.ascontiguousarray(ids, dtype=np.int32)
+        probs = np.empty(self.V, dtype=np.float32)
+        assert lib().fo_prime(self._s, _ptr(ids), ids.size, _ptr(probs)) == 0
+        return probs
+
+    def feed(self, token):
+        probs = np.empty(self.V, dtype=np.float32)
+        rc = lib().fo_feed(self._s, int(token), _ptr(probs))
+        return probs if rc == 0 else None
+
+    def reset(self):
+        lib().fo_stream_reset(self._s)
+
+    def cached_len(self):
+        return lib().fo_cached_len(self._s)
+
+    def generate_greedy(self, prompt, max_new, eos=-1):
+        prompt = np.ascontiguousarray(prompt, dtype=np.int32)
+        out = np.empty(max(1, max_new), dtype=np.int32)
+        margin = np.zeros(max(1, max_new), dtype=np.float32)
+        n = lib().fo_generate_greedy(self._s, _ptr(prompt), prompt.size, max_new, eos, _ptr(out), _ptr(margin))
+        assert n >= 0
+        return out[:n].copy(), margin[:max(n, min(max_new, n + 1))].copy()
+
+    def token_logprobs(self, ids, from_=1):
+        ids = np.ascontiguousarray(ids, dtype=np.int32)
+        lp = np.zeros(ids.size, dtype=np.float32)
+        gr = np.zeros(ids.size, dtype=np.uint8)
+        total, n, g = C.c_double(), C.c_int(), C.c_int()
+        rc = lib().fo_token_logprobs(self._m, _ptr(ids), ids.size, from_, C.byref(total), C.byref(n), C.byref(g),
+                                     _ptr(lp), _ptr(gr))
+        assert rc == 0
+        return total.value, n.value, bool(g.value), lp, gr
+
+    def close(self):
+        if self._s:
+            lib().fo_stream_free(self._s)
+            self._s = None
+        if self._m:
+            lib().fo_model_free(self._m)
+            self._m = None
+
+    def __del__(self):
+        self.close()
