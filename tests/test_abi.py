@@ -1,0 +1,51 @@
+"""The C-ABI library loads on a machine without a GPU and exports every symbol the public
+header declares; device entry points fail with FC_E_CUDA instead of computing on the CPU."""
+import os
+import re
+
+import numpy as np
+import pytest
+
+import ferrum_cpu_b200 as fcb
+from ferrum_cpu_b200 import _lib, synth
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "ferrum_cuda.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(fc_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported_and_bound():
+    names = declared_symbols()
+    assert len(names) >= 25
+    L = _lib.lib()
+    for n in names:
+        assert hasattr(L, n), f"{n} is declared in ferrum_cuda.h but not exported"
+        assert n in _lib.SIGNATURES, f"{n} has no ctypes signature"
+    assert set(_lib.SIGNATURES) <= set(names)
+
+
+def test_no_cpu_fallback_without_a_device():
+    if fcb.device_count() > 0:
+        pytest.skip("a B200 is present")
+    sm = synth.SynthModel(1, 32, 1, 32, 8, 64, seed=1)
+    with pytest.raises(fcb.FerrumCudaError) as e:
+        fcb.CudaSlm(sm.config, sm.weights)
+    assert e.value.code == _lib.FC_E_CUDA
+    with pytest.raises(fcb.FerrumCudaError):
+        fcb.q8_0_linear(np.zeros((1, 32), np.float32), synth.q8_0_quantize(np.zeros(64 * 32, np.float32)), None, 64)
+
+
+def test_argument_validation_precedes_device_use():
+    sm = synth.SynthModel(1, 32, 1, 32, 8, 64, seed=1)
+    bad = _lib.FcConfig(1, 48, 5, 32, 8, 64, 1, 0)      # 48 % 5 != 0
+    with pytest.raises(fcb.FerrumCudaError) as e:
+        fcb.CudaSlm(bad, sm.weights)
+    assert e.value.code == _lib.FC_E_DIM
+    bad = _lib.FcConfig(1, 48, 3, 32, 8, 64, 1, 0)      # 48 % 32 != 0: not Q8_0 eligible
+    with pytest.raises(fcb.FerrumCudaError) as e:
+        fcb.CudaSlm(bad, sm.weights)
+    assert e.value.code == _lib.FC_E_FORMAT

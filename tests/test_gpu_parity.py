@@ -1,0 +1,227 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU oracle. Tolerances: 1e-3 max-abs
+on log-probs is the stated bound; the fp32 kernels are held to far tighter ones here."""
+import os
+
+import numpy as np
+import pytest
+
+import ferrum_cpu_b200 as fcb
+from ferrum_cpu_b200 import _lib, synth
+from tests import oracle as O
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+LOGPROB_TOL = 1e-3       # north-star bound, max-abs on log-probs
+FP32_LOGPROB_TOL = 2e-4  # what the fp32 path is held to
+
+
+def logp(p):
+    return np.log(np.maximum(p.astype(np.float64), 1e-12))
+
+
+@pytest.fixture(scope="module")
+def mini():
+    """2 blocks, d 64, 2 heads (head_dim 32), ff 128, ctx 16, vocab 96 — non-trivial biases/LN."""
+    sm = synth.SynthModel(2, 64, 2, 128, 16, 96, seed=11, perturb=True)
+    return sm, O.OracleModel(sm, threads=2), fcb.CudaSlm(sm.config, sm.weights)
+
+
+@pytest.fixture(scope="module")
+def tiny():
+    sm = synth.named("tiny", seed=0, perturb=True)
+    return sm, O.OracleModel(sm, threads=4), fcb.CudaSlm(sm.config, sm.weights)
+
+
+# ---- standalone Q8_0 linear (the matmul sweep) -----------------------------------------
+@pytest.mark.parametrize("m,k,n", [(1, 768, 2304), (1, 3072, 768), (1, 768, 50257), (1, 128, 4096), (1, 32, 7),
+                                   (2, 64, 96), (3, 96, 130), (129, 160, 257), (512, 768, 3072)])
+def test_q8_0_linear_matches_engine(m, k, n):
+    w = O.fill_normal(21, n * k, 0.02)
+    wq = synth.q8_0_quantize(w)
+    x = O.fill_normal(22, m * k, 1.0).reshape(m, k)
+    bias = O.fill_normal(23, n, 0.5)
+    want = O.linear(x, O.expand_kn(wq, n, k), bias, threads=8)
+    got = fcb.q8_0_linear(x, wq, bias, n)
+    scale = np.abs(want).max()
+    assert np.abs(got - want).max() <= 2e-5 * scale + 1e-6
+    got_nb = fcb.q8_0_linear(x, wq, None, n)
+    assert np.abs(got_nb + bias - want).max() <= 2e-5 * scale + 1e-5
+
+
+def test_q8_0_linear_is_linear_and_deterministic():
+    k, n = 768, 2304
+    wq = synth.q8_0_quantize(O.fill_normal(31, n * k, 0.02))
+    x1, x2 = O.fill_normal(32, k, 1.0).reshape(1, k), O.fill_normal(33, k, 1.0).reshape(1, k)
+    y1, y2, y12 = fcb.q8_0_linear(x1, wq, None, n), fcb.q8_0_linear(x2, wq, None, n), fcb.q8_0_linear(x1 + x2, wq, None, n)
+    assert np.abs(y1 + y2 - y12).max() < 1e-4
+    assert np.array_equal(y1, fcb.q8_0_linear(x1, wq, None, n))
+
+
+# ---- KV-cached decode ----------------------------------------------------------------------
+def test_feed_probs_match_oracle(tiny):
+    sm, om, gm = tiny
+    ids = synth.token_ids(3, 40, sm.dims[5])
+    om.reset()
+    gm.reset()
+    for t in ids:
+        po, pg = om.feed(t), gm.feed(t)
+        assert abs(pg.sum() - 1.0) < 1e-4
+        assert np.abs(logp(pg) - logp(po)).max() < FP32_LOGPROB_TOL
+    assert gm.cached_len() == om.cached_len() == 40
+    po, pg = om.prime(ids[:7]), gm.prime(ids[:7])
+    assert np.abs(logp(pg) - logp(po)).max() < FP32_LOGPROB_TOL and gm.cached_len() == 7
+
+
+def check_greedy(tokens, want, margin, tol=1e-4):
+    """Identical tokens; a mismatch is tolerated only where the oracle's top-2 margin is below tol."""
+    n = min(len(tokens), len(want))
+    for i in range(n):
+        if tokens[i] != want[i]:
+            assert margin[i] < tol, f"token {i}: got {tokens[i]}, want {want[i]}, oracle margin {margin[i]:.3e}"
+            pytest.xfail(f"greedy paths split at step {i} on an oracle margin of {margin[i]:.3e} (< {tol})")
+    assert len(tokens) == len(want)
+
+
+def test_greedy_tiny_config_matches_golden(tiny):
+    g = np.load(os.path.join(GOLD, "decode_tiny.npz"))
+    sm = synth.named("tiny", seed=0)
+    gm = fcb.CudaSlm(sm.config, sm.weights)
+    toks, cancelled = gm.generate_tokens(g["prompt"], len(g["tokens"]))
+    assert not cancelled
+    check_greedy(toks, g["tokens"], g["margin"])
+    assert gm.cached_len() == len(g["prompt"]) + len(g["tokens"])
+    # run to run determinism
+    again, _ = gm.generate_tokens(g["prompt"], len(g["tokens"]))
+    assert np.array_equal(toks, again)
+    gm.close()
+
+
+def test_greedy_reprimes_past_the_context(mini):
+    sm, om, gm = mini
+    prompt = synth.token_ids(9, 4, 96)
+    want, margin = om.generate_greedy(prompt, 45)
+    toks, _ = gm.generate_tokens(prompt, 45)
+    check_greedy(toks, want, margin)
+    # a prompt longer than the context keeps its last ctx ids (token_stream.rs:87-89)
+    long_prompt = synth.token_ids(10, 30, 96)
+    want, margin = om.generate_greedy(long_prompt, 5)
+    toks, _ = gm.generate_tokens(long_prompt, 5)
+    check_greedy(toks, want, margin)
+
+
+def test_eos_and_cancel(mini):
+    sm, om, gm = mini
+    prompt = synth.token_ids(9, 4, 96)
+    want, _ = om.generate_greedy(prompt, 12)
+    eos = int(want[5])
+    first = int(np.where(want == eos)[0][0])
+    w2, _ = om.generate_greedy(prompt, 12, eos=eos)
+    toks, _ = gm.generate_tokens(prompt, 12, eos=eos)
+    assert len(w2) == first and np.array_equal(toks, w2)
+    flag = np.ones(1, dtype=np.int32)
+    toks, cancelled = gm.generate_tokens(prompt, 12, cancel=flag)
+    assert cancelled and len(toks) <= 1
+
+
+def test_errors_are_statuses_not_faults(mini):
+    sm, om, gm = mini
+    gm.reset()
+    with pytest.raises(fcb.FerrumCudaError) as e:
+        gm.feed(96)                       # id == vocab (embedding.rs:71-76)
+    assert e.value.code == _lib.FC_E_DIM
+    with pytest.raises(fcb.FerrumCudaError):
+        gm.feed(-1)
+    gm.prime(synth.token_ids(1, 16, 96))
+    assert gm.cached_len() == 16
+    with pytest.raises(fcb.FerrumCudaError) as e:
+        gm.feed(1)                        # cache full (transformer.rs:237-242)
+    assert e.value.code == _lib.FC_E_DIM
+    with pytest.raises(fcb.FerrumCudaError) as e:
+        gm.predict_next(np.zeros(17, dtype=np.int32))
+    assert e.value.code == _lib.FC_E_DIM
+    gm.reset()
+    assert gm.feed(1).shape == (96,)      # the stream is still usable
+
+
+# ---- scoring ------------------------------------------------------------------------------
+@pytest.mark.parametrize("n", [1, 2, 15, 16, 17, 18, 32, 33, 51])
+def test_token_logprobs_windows_match_oracle(mini, n):
+    sm, om, gm = mini
+    ids = synth.token_ids(200 + n, n, 96)
+    total, cnt, greedy, lp, gr = om.token_logprobs(ids, 1)
+    score, glp, ggr = gm.token_logprobs(ids, 1, per_token=True)
+    assert score.n_tokens == cnt == max(0, n - 1)
+    assert np.abs(glp - lp).max(initial=0.0) < FP32_LOGPROB_TOL
+    assert abs(score.logprob - total) < FP32_LOGPROB_TOL * max(1, cnt)
+    assert np.array_equal(ggr, gr) and score.greedy == greedy
+
+
+def test_scoring_from_offset_and_predict_next(tiny):
+    sm, om, gm = tiny
+    V, T = sm.dims[5], sm.dims[4]
+    ids = synth.token_ids(41, 200, V)
+    total, cnt, greedy, lp, gr = om.token_logprobs(ids, 150)
+    score = gm.token_logprobs(ids, 150)
+    assert score.n_tokens == cnt == 50 and abs(score.logprob - total) < FP32_LOGPROB_TOL * cnt
+    probs = gm.predict_next(ids[:T])
+    want = om.forward(ids[:T].reshape(1, T))[-1]
+    assert np.abs(logp(probs) - logp(want)).max() < FP32_LOGPROB_TOL
+    # the cached path and the window path agree (cached.rs:152-230)
+    assert np.abs(logp(gm.prime(ids[:T])) - logp(probs)).max() < FP32_LOGPROB_TOL
+
+
+def test_score_sequences_matches_golden_tiny():
+    g = np.load(os.path.join(GOLD, "score_tiny.npz"))
+    sm = synth.named("tiny", seed=0)
+    gm = fcb.CudaSlm(sm.config, sm.weights)
+    scores, lp = gm.score_sequences(g["ids"], batch_windows=3)
+    assert np.abs(lp - g["logprob"]).max() < FP32_LOGPROB_TOL
+    for s, want in zip(scores, g["total"]):
+        assert s.n_tokens == g["ids"].shape[1] - 1 and abs(s.logprob - want) < 1e-2
+    # a checksum over the batch is independent of how windows are batched
+    scores2, lp2 = gm.score_sequences(g["ids"], batch_windows=1)
+    assert np.array_equal(lp, lp2)
+    gm.close()
+
+
+# ---- GPT-2-small-shaped configurations against committed fixtures ---------------------------
+@pytest.fixture(scope="module")
+def small():
+    sm = synth.named("small", seed=0)
+    return sm, fcb.CudaSlm(sm.config, sm.weights)
+
+
+def test_small_greedy_decode_matches_golden(small):
+    path = os.path.join(GOLD, "decode_small.npz")
+    if not os.path.exists(path):
+        pytest.skip("decode_small.npz has not been generated")
+    g = np.load(path)
+    sm, gm = small
+    toks, _ = gm.generate_tokens(g["prompt"], len(g["tokens"]))
+    check_greedy(toks, g["tokens"], g["margin"])
+
+
+def test_small_scoring_matches_golden(small):
+    path = os.path.join(GOLD, "score_small.npz")
+    if not os.path.exists(path):
+        pytest.skip("score_small.npz has not been generated")
+    g = np.load(path)
+    sm, gm = small
+    scores, lp = gm.score_sequences(g["ids"], batch_windows=4)
+    assert np.abs(lp - g["logprob"]).max() < LOGPROB_TOL
+    assert abs(scores[0].logprob - g["total"][0]) < 0.05
+
+
+def test_small_scoring_is_batch_invariant_and_causal(small):
+    """Size-independent properties at the full window length: a sequence scores the same alone
+    or inside a batch, and log-probs of a prefix do not depend on what follows it."""
+    sm, gm = small
+    V = sm.dims[5]
+    ids = synth.token_ids(1, 3 * 1024, V).reshape(3, 1024)
+    _, lp3 = gm.score_sequences(ids, batch_windows=3)
+    _, lp1 = gm.score_sequences(ids[1:2], batch_windows=1)
+    assert np.array_equal(lp3[1], lp1[0])
+    ids2 = ids.copy()
+    ids2[1, 600:] = synth.token_ids(2, 424, V)
+    _, lpb = gm.score_sequences(ids2[1:2], batch_windows=1)
+    assert np.array_equal(lpb[0, :600], lp1[0, :600]) and not np.array_equal(lpb[0, 600:], lp1[0, 600:])
