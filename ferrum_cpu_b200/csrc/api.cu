@@ -8,6 +8,7 @@
 #include <vector>
 
 #include "fc_common.cuh"
+#include "mega.cuh"
 
 namespace fc {
 
@@ -127,6 +128,11 @@ struct fc_model {
     uint8_t* gr_d = nullptr;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     float last_score_ms = 0.0f;
+    // persistent decode kernel: per-layer parameter table on the device, grid size (0: the
+    // model's shape is outside what that kernel supports)
+    MegaLayer* mega_layers = nullptr;
+    float* mega_lnf = nullptr;
+    int mega_grid = 0;
 };
 
 struct fc_stream {
@@ -142,7 +148,16 @@ struct fc_stream {
     int graph_nodes[3] = {0, 0, 0};
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     float last_decode_ms = 0.0f;
+    // persistent decode kernel: exchange buffers, grid barrier word, status word
+    float *partg = nullptr, *x1g = nullptr, *statg = nullptr;
+    unsigned* bar = nullptr;
+    int* status = nullptr;
+    int attn_splits = 1;
+    int use_mega = 0;
+    unsigned long long* trace = nullptr;   // phase timeline of the persistent kernel
+    int trace_on = 0;
 };
+static constexpr int kTraceCap = 1024;
 
 namespace fc {
 
@@ -205,6 +220,39 @@ static int run_step(fc_stream* s, int mode) {
     return FC_OK;
 }
 
+// n tokens from the queue through the persistent decode kernel in one launch. Steps before
+// head_from skip the LM head; head steps select greedily when `select`, and the last step
+// leaves its probabilities in s->probs when `probs`.
+static int run_mega(fc_stream* s, int n, int head_from, int select, int probs) {
+    fc_model* m = s->m;
+    const fc_config& c = m->cfg;
+    MegaParams p;
+    p.L = c.n_layer; p.d = c.d_model; p.H = c.n_head; p.F = c.d_ff; p.T = c.ctx; p.V = c.vocab;
+    p.tok = m->tok; p.head = m->head; p.pos = m->pos; p.lnfpack = m->mega_lnf;
+    p.layers = m->mega_layers;
+    p.kc = s->kc; p.vc = s->vc;
+    p.qg = s->q; p.partg = s->partg; p.x1g = s->x1g; p.xg = s->x; p.hidg = s->hid;
+    p.logits = s->logits; p.statg = s->statg; p.probs = probs ? s->probs : nullptr;
+    p.queue = s->queue; p.queue_cap = s->queue_cap; p.state = s->state;
+    p.bar = s->bar; p.status = s->status;
+    p.n_steps = n; p.head_from = head_from; p.select = select; p.attn_splits = s->attn_splits;
+    p.trace = s->trace_on ? s->trace : nullptr;
+    p.trace_cap = kTraceCap;
+    if (p.trace) FC_CUDA(cudaMemsetAsync(s->trace, 0, kTraceCap * sizeof(unsigned long long), m->st));
+    return launch_decode_mega(p, m->mega_grid, m->st);
+}
+
+// n steps, the last one in `last_mode`, the ones before it in `mode`.
+static int run_steps(fc_stream* s, int n, int mode, int last_mode) {
+    if (n <= 0) return FC_OK;
+    if (s->use_mega) {
+        const int head_from = mode != STEP_NOHEAD ? 0 : (last_mode != STEP_NOHEAD ? n - 1 : n);
+        return run_mega(s, n, head_from, last_mode == STEP_SELECT, last_mode == STEP_PROBS);
+    }
+    for (int i = 0; i < n; ++i) FC_TRY(run_step(s, i + 1 == n ? last_mode : mode));
+    return FC_OK;
+}
+
 __global__ void set_state_kernel(StepState* st, int pos, int fed, int tail, int done, int eos, int keep_pos) {
     if (!keep_pos) st->pos = pos;
     st->fed = fed; st->tail = tail; st->done = done; st->eos = eos; st->error = 0;
@@ -216,8 +264,14 @@ static int set_state(fc_stream* s, int pos, int fed, int tail, int eos, int keep
 }
 
 static int read_state(fc_stream* s, StepState* out) {
+    int status = 0;
     FC_CUDA(cudaMemcpyAsync(out, s->state, sizeof(StepState), cudaMemcpyDeviceToHost, s->m->st));
+    if (s->status) FC_CUDA(cudaMemcpyAsync(&status, s->status, sizeof(int), cudaMemcpyDeviceToHost, s->m->st));
     FC_CUDA(cudaStreamSynchronize(s->m->st));
+    if (status != 0) {
+        cudaMemsetAsync(s->status, 0, sizeof(int), s->m->st);
+        return fail(FC_E_TIMEOUT, "a bounded wait inside the persistent decode kernel ran out (status %d)", status);
+    }
     return FC_OK;
 }
 
@@ -413,6 +467,55 @@ static int model_build(fc_model* m, const fc_weights* w) {
         FC_TRY(upload_f32(a, s.ln1_b, d, &L.ln1b, st));
         FC_TRY(upload_f32(a, s.ln2_g, d, &L.ln2g, st));
         FC_TRY(upload_f32(a, s.ln2_b, d, &L.ln2b, st));
+    }
+    if (mega_supported(c)) {
+        int grid = 0;
+        FC_TRY(mega_max_grid(&grid));
+        // the head slice and the bias slices of one CTA must fit its shared-memory buffers
+        bool fits = (c.vocab + grid - 1) / grid + 8 <= 1024;
+        for (int cta = 0; cta < grid && fits; ++cta) {
+            int off[4];
+            fits = mega_bias_offsets(d, F, cta, grid, off) <= kMegaBiasPack;
+        }
+        if (fits) {
+            // Per block: the four LayerNorm vectors back to back, and for every CTA of the
+            // persistent kernel the slices of the four bias vectors that belong to its rows.
+            std::vector<MegaLayer> tab(c.n_layer);
+            std::vector<float> ln((size_t)4 * d), bp((size_t)grid * kMegaBiasPack);
+            for (int l = 0; l < c.n_layer; ++l) {
+                const fc_layer_weights& s = w->layers[l];
+                const LayerDev& L = m->layers[l];
+                std::copy(s.ln1_g, s.ln1_g + d, ln.begin());
+                std::copy(s.ln1_b, s.ln1_b + d, ln.begin() + d);
+                std::copy(s.ln2_g, s.ln2_g + d, ln.begin() + 2 * d);
+                std::copy(s.ln2_b, s.ln2_b + d, ln.begin() + 3 * d);
+                std::fill(bp.begin(), bp.end(), 0.0f);
+                const float* src[4] = {s.attn_qkv_b, s.attn_out_b, s.ffn_up_b, s.ffn_down_b};
+                const int N[4] = {3 * d, d, F, d}, K[4] = {d, d, d, F};
+                for (int cta = 0; cta < grid; ++cta) {
+                    int off[4];
+                    mega_bias_offsets(d, F, cta, grid, off);
+                    for (int i = 0; i < 4; ++i) {
+                        int r0, r1;
+                        mega_cta_rows(N[i], K[i], cta, grid, &r0, &r1);
+                        std::copy(src[i] + r0, src[i] + r1, bp.begin() + (size_t)cta * kMegaBiasPack + off[i]);
+                    }
+                }
+                float *lnd = nullptr, *bpd = nullptr;
+                FC_TRY(upload_f32(a, ln.data(), ln.size(), &lnd, st));
+                FC_TRY(upload_f32(a, bp.data(), bp.size(), &bpd, st));
+                FC_CUDA(cudaStreamSynchronize(st));   // ln / bp are reused by the next block
+                tab[l] = MegaLayer{L.qkv, L.out, L.up, L.down, lnd, bpd};
+            }
+            std::fill(ln.begin(), ln.end(), 0.0f);
+            std::copy(w->out_norm_g, w->out_norm_g + d, ln.begin());
+            std::copy(w->out_norm_b, w->out_norm_b + d, ln.begin() + d);
+            FC_TRY(upload_f32(a, ln.data(), ln.size(), &m->mega_lnf, st));
+            FC_TRY(a.alloc_n(&m->mega_layers, (size_t)c.n_layer));
+            FC_CUDA(cudaMemcpyAsync(m->mega_layers, tab.data(), tab.size() * sizeof(MegaLayer), cudaMemcpyHostToDevice, st));
+            FC_CUDA(cudaStreamSynchronize(st));
+            m->mega_grid = grid;
+        }
     }
     FC_CUDA(cudaStreamSynchronize(st));
     return FC_OK;
@@ -634,6 +737,18 @@ int fc_stream_create(fc_model* m, fc_stream** out) {
     if (rc == FC_OK) rc = a.alloc_n(&s->probs, (size_t)c.vocab);
     if (rc == FC_OK) rc = a.alloc_n(&s->queue, (size_t)s->queue_cap);
     if (rc == FC_OK) rc = a.alloc_n(&s->state, 1);
+    if (rc == FC_OK && m->mega_grid > 0) {
+        const int hd = c.d_model / c.n_head;
+        s->attn_splits = std::max(1, std::min(8, m->mega_grid / c.n_head));
+        rc = a.alloc_n(&s->partg, (size_t)c.n_head * s->attn_splits * (hd + 2));
+        if (rc == FC_OK) rc = a.alloc_n(&s->x1g, (size_t)c.d_model);
+        if (rc == FC_OK) rc = a.alloc_n(&s->statg, (size_t)m->mega_grid * 4);
+        if (rc == FC_OK) rc = a.alloc_n(&s->bar, 1);
+        if (rc == FC_OK) rc = a.alloc_n(&s->status, 1);
+        if (rc == FC_OK && cudaMemsetAsync(s->status, 0, sizeof(int), m->st) != cudaSuccess) rc = fail(FC_E_CUDA, "status word initialisation failed");
+        if (rc == FC_OK) rc = a.alloc_n(&s->trace, (size_t)kTraceCap);
+        s->use_mega = 1;
+    }
     if (rc == FC_OK && (cudaEventCreate(&s->ev0) != cudaSuccess || cudaEventCreate(&s->ev1) != cudaSuccess)) rc = fail(FC_E_CUDA, "event creation failed");
     if (rc == FC_OK) rc = set_state(s, 0, 0, 0, -1, 0);
     if (rc == FC_OK && cudaStreamSynchronize(m->st) != cudaSuccess) rc = fail(FC_E_CUDA, "stream initialisation failed");
@@ -661,14 +776,39 @@ int fc_stream_reset(fc_stream* s) {
 }
 
 int fc_cached_len(const fc_stream* s) { return s ? s->host_pos : 0; }
+
+int fc_stream_set_trace(fc_stream* s, int on) {
+    if (!s) return fail(FC_E_ARG, "fc_stream_set_trace: null stream");
+    if (on && !s->trace) return fail(FC_E_SHAPE, "tracing needs the persistent decode kernel");
+    s->trace_on = on != 0;
+    return FC_OK;
+}
+
+int fc_stream_read_trace(fc_stream* s, uint64_t* out, int cap) {
+    if (!s || !out || cap < 0) return fail(FC_E_ARG, "fc_stream_read_trace: bad argument");
+    if (!s->trace) return 0;
+    FC_CUDA(cudaSetDevice(s->m->device));
+    FC_CUDA(cudaStreamSynchronize(s->m->st));
+    std::vector<unsigned long long> h(kTraceCap);
+    FC_CUDA(cudaMemcpy(h.data(), s->trace, kTraceCap * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+    int n = 0;
+    while (n < kTraceCap && n < cap && h[n] != 0) { out[n] = h[n]; ++n; }
+    return n;
+}
+
+int fc_stream_set_mode(fc_stream* s, int mode) {
+    if (!s) return fail(FC_E_ARG, "fc_stream_set_mode: null stream");
+    if (mode == FC_DECODE_PERSISTENT && s->m->mega_grid <= 0)
+        return fail(FC_E_SHAPE, "the persistent decode kernel does not support this model shape");
+    if (mode != FC_DECODE_PERSISTENT && mode != FC_DECODE_PER_KERNEL) return fail(FC_E_ARG, "unknown decode mode %d", mode);
+    s->use_mega = mode == FC_DECODE_PERSISTENT;
+    return FC_OK;
+}
 float fc_last_decode_ms(const fc_stream* s) { return s ? s->last_decode_ms : 0.0f; }
 
 // Feeds queue[0..n) (already uploaded) from the current position; the last step runs in
 // `last_mode`, the ones before it skip the head (its output would be discarded).
-static int feed_queued(fc_stream* s, int n, int last_mode) {
-    for (int i = 0; i < n; ++i) FC_TRY(run_step(s, i + 1 == n ? last_mode : STEP_NOHEAD));
-    return FC_OK;
-}
+static int feed_queued(fc_stream* s, int n, int last_mode) { return run_steps(s, n, STEP_NOHEAD, last_mode); }
 
 static int feed_ids(fc_stream* s, const int32_t* ids, int n, float* probs) {
     fc_model* m = s->m;
@@ -748,25 +888,36 @@ int fc_generate_greedy(fc_stream* s, const int32_t* prompt, int n, int max_new, 
     FC_CUDA(cudaEventRecord(s->ev0, st));
     int win_start_len = (int)window.size();  // ids in the window when it was primed
     int gen_win = max_new > 0 ? 1 : 0;       // tokens selected inside this window (issued)
-    // feed i (1-based) pushes generated token i; it selects token i+1 unless it is the last
-    for (int i = 1; i <= max_new && !done; ++i) {
+    // feed i (1-based) pushes generated token i; it selects token i+1 unless it is the last.
+    // Consecutive selecting feeds are issued as one batch of at most 32 steps.
+    int i = 1;
+    while (i <= max_new && !done) {
         if (cancel && *cancel) { cancelled = true; break; }
-        const bool select = i < max_new;
         if (win_start_len + gen_win > cap) {
             // the window outgrew the context: keep the last cap/2 ids and re-prime
             // (token_stream.rs:162-165)
+            const bool select = i < max_new;
             FC_TRY(harvest());
             if (done) break;
             window.erase(window.begin(), window.end() - keep);
             FC_TRY(start_window(select));
             win_start_len = (int)window.size();
             gen_win = select ? 1 : 0;
+            i += 1;
         } else {
-            FC_TRY(run_step(s, select ? STEP_SELECT : STEP_PROBS));
-            gen_win += select ? 1 : 0;
+            // selecting feeds i..max_new-1, as many as stay inside the context
+            const int k = std::min(std::min(max_new - i, 32), cap - win_start_len - gen_win + 1);
+            if (k >= 1) {
+                FC_TRY(run_steps(s, k, STEP_SELECT, STEP_SELECT));
+                gen_win += k;
+                i += k;
+            } else {
+                FC_TRY(run_steps(s, 1, STEP_PROBS, STEP_PROBS));   // the last feed selects nothing
+                i += 1;
+            }
         }
         // eos can only be noticed on the host at a synchronisation point
-        if (eos >= 0 && (i % 32) == 0) FC_TRY(harvest());
+        if (eos >= 0) FC_TRY(harvest());
     }
     FC_CUDA(cudaEventRecord(s->ev1, st));
     FC_TRY(harvest());

@@ -1,0 +1,742 @@
+// Persistent decode kernel: whole KV-cached tokens in ONE cooperative launch.
+//
+// Replaces the per-token call chain CachedTransformer::feed (ferrum_core/src/slm/cached.rs:
+// 100-125) -> TransformerBlock::forward_with_cache (layer/transformer.rs:221-294) ->
+// Linear::forward (layer/linear.rs:177-210) and the greedy pick of token_stream.rs:134 +
+// sampling.rs:96-104, for n_steps consecutive tokens.
+//
+// Shape of the kernel (one CTA per SM, all co-resident):
+//   * a producer warp streams this CTA's share of every Q8_0 matrix, in the fixed order the
+//     token needs them, through a ring of shared-memory slots with 1-D bulk async copies
+//     (cp.async.bulk + mbarrier complete_tx), and the block's LayerNorm vectors and bias
+//     slices through a second, two-deep ring. Weights do not depend on activations, so the
+//     producer runs ahead across the grid barriers and HBM never waits for the math;
+//   * 16 consumer warps do the fp32 dot products out of shared memory (f16 scale applied per
+//     16 quants in registers, half-warp shuffles), LayerNorm, attention over the f32 KV cache
+//     (split over CTAs, combined flash-decoding style), and the softmax / greedy pick;
+//   * phases are separated by a software grid barrier (5 per block, 2 per head step); what
+//     crosses a barrier goes through small global buffers read with L1-bypassing loads.
+// Every wait (mbarrier, grid barrier) is bounded by a cycle budget; when it runs out the
+// kernel records FC_E_TIMEOUT, drains its own copies in flight and returns.
+//
+// Bound: HBM. Algorithmic bytes per token: every Q8_0 matrix once (34/32 B per weight) + the
+// f32 KV rows of positions 0..pos + small f32 vectors.
+#include "fc_common.cuh"
+#include "mega.cuh"
+
+namespace fc {
+
+namespace {
+
+constexpr int CONSUMERS = 512;                 // 16 consumer warps
+constexpr int CWARPS = CONSUMERS / 32;
+constexpr int THREADS = CONSUMERS + 32;        // + 1 producer warp
+constexpr int SLOTS = 5;
+constexpr int SLOT_Q = 24576;                  // quant bytes per slot
+constexpr int SLOT_D = SLOT_Q / 16;            // scale bytes per slot (2 B per 32 quants)
+constexpr int SLOT_BYTES = SLOT_Q + SLOT_D;
+constexpr int MAX_D = 1024, MAX_F = 4096, MAX_CTX = 1024, MAX_ROWS_HEAD = 1024;
+constexpr int PARAM_FLOATS = 4 * MAX_D + kMegaBiasPack;   // LayerNorm vectors + bias slices
+constexpr long long WAIT_CYCLES = 4000000000LL;           // ~2 s at 1.9 GHz
+
+struct Ctrl {
+    unsigned long long full[SLOTS];
+    unsigned long long empty[SLOTS];
+    unsigned long long pfull[2];
+    unsigned long long pempty[2];
+    volatile int stop;        // consumers -> producer: stop issuing copies
+    volatile int consumed;    // weight items consumed when the consumers stopped
+    volatile int pconsumed;   // parameter items consumed when the consumers stopped
+    volatile int abort;       // a bounded wait ran out in this CTA
+};
+
+// shared memory carve-up (bytes)
+constexpr int OFF_SLOTS = 0;
+constexpr int OFF_PARAM = OFF_SLOTS + SLOTS * SLOT_BYTES;        // 2 parameter buffers
+constexpr int OFF_ACT = OFF_PARAM + 2 * PARAM_FLOATS * 4;        // activation vector, swizzled float4 units
+constexpr int OFF_XS = OFF_ACT + MAX_F * 4;                      // residual stream x
+constexpr int OFF_SC = OFF_XS + MAX_D * 4;                       // attention scores / head logits slice
+constexpr int OFF_PSUM = OFF_SC + MAX_CTX * 4;                   // 2 x 256 partial sums
+constexpr int OFF_RED = OFF_PSUM + 2 * 256 * 4;                  // reductions
+constexpr int OFF_LAYERS = OFF_RED + 256 * 4;                    // copy of the layer table
+constexpr int OFF_CTRL = OFF_LAYERS + kMegaMaxLayers * (int)sizeof(MegaLayer);
+constexpr int SMEM_BYTES = OFF_CTRL + (int)sizeof(Ctrl);
+static_assert(MAX_ROWS_HEAD <= MAX_CTX, "head slice shares the score buffer");
+static_assert(sizeof(MegaLayer) % 16 == 0, "layer table entries are copied as 16-byte words");
+static_assert(OFF_PARAM % 16 == 0 && OFF_ACT % 16 == 0 && OFF_LAYERS % 16 == 0 && OFF_CTRL % 8 == 0, "alignment");
+static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
+
+// ------------------------------------------------------------------ PTX helpers
+__device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned long long* b, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s32(b)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* b, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s32(b)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long* b) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s32(b)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long* b, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(s32(b)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// 1-D bulk copy global -> shared; both addresses 16-byte aligned, bytes % 16 == 0.
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, unsigned long long* b) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(s32(dst)), "l"(src), "r"(bytes), "r"(s32(b)) : "memory");
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CONSUMERS) : "memory"); }
+__device__ __forceinline__ unsigned ld_acquire(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void red_release_add(unsigned* p, unsigned v) {
+    asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ int rows_per_item(int K) {
+    const int g = mega_row_gran(K);
+    int r = min(SLOT_Q / K, 256);      // 256 = partial-sum slots per item
+    return r - r % g;
+}
+
+template <int B>
+__device__ __forceinline__ float qbyte(uint32_t w) {
+    return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540 + B)) - 8388736.0f;
+}
+// 16 biased quants (one 16-byte chunk c of a row) times the swizzled activation.
+__device__ __forceinline__ float dot16(const uint4 w, const float4* __restrict__ act, int c) {
+    const int sw = (c >> 1) & 3, base = 4 * c;
+    const float4 x0 = act[base + (0 ^ sw)], x1 = act[base + (1 ^ sw)], x2 = act[base + (2 ^ sw)], x3 = act[base + (3 ^ sw)];
+    // four independent chains of four dependent fused multiply-adds
+    float a = x0.x * qbyte<0>(w.x), b = x1.x * qbyte<0>(w.y), c2 = x2.x * qbyte<0>(w.z), e = x3.x * qbyte<0>(w.w);
+    a = fmaf(x0.y, qbyte<1>(w.x), a); b = fmaf(x1.y, qbyte<1>(w.y), b); c2 = fmaf(x2.y, qbyte<1>(w.z), c2); e = fmaf(x3.y, qbyte<1>(w.w), e);
+    a = fmaf(x0.z, qbyte<2>(w.x), a); b = fmaf(x1.z, qbyte<2>(w.y), b); c2 = fmaf(x2.z, qbyte<2>(w.z), c2); e = fmaf(x3.z, qbyte<2>(w.w), e);
+    a = fmaf(x0.w, qbyte<3>(w.x), a); b = fmaf(x1.w, qbyte<3>(w.y), b); c2 = fmaf(x2.w, qbyte<3>(w.z), c2); e = fmaf(x3.w, qbyte<3>(w.w), e);
+    return (a + b) + (c2 + e);
+}
+// element i of the swizzled activation vector
+__device__ __forceinline__ int act_index(int i) {
+    const int u = i >> 2;
+    return ((u ^ ((u >> 3) & 3)) << 2) | (i & 3);
+}
+
+struct Cta {
+    const MegaParams& p;
+    unsigned char* smem;
+    Ctrl* ctrl;
+    const MegaLayer* layers;   // shared-memory copy of the layer table
+    float4* act4;
+    float* act;
+    float* xs;
+    float* sc;
+    float* psum;
+    float* red;
+    int c, G, tid;
+    int item;            // weight items consumed (consumers) / issued (producer)
+    int pitem;           // parameter items consumed / issued
+    unsigned bar_target;
+    int trace_n;         // next slot of the phase timeline; < 0 when this thread does not trace
+    __device__ unsigned char* slot_q(int s) const { return smem + OFF_SLOTS + s * SLOT_BYTES; }
+    __device__ const __half* slot_d(int s) const { return (const __half*)(smem + OFF_SLOTS + s * SLOT_BYTES + SLOT_Q); }
+    __device__ float* param(int b) const { return (float*)(smem + OFF_PARAM) + b * PARAM_FLOATS; }
+};
+
+__device__ __forceinline__ bool timed_out(long long t0) { return clock64() - t0 > WAIT_CYCLES; }
+
+// Phase timeline: one thread of CTA 0 stores the global timer at every phase boundary.
+__device__ __forceinline__ void mark(Cta& k) {
+    if (k.trace_n >= 0 && k.trace_n < k.p.trace_cap) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        k.p.trace[k.trace_n++] = t;
+    }
+}
+
+__device__ void raise_timeout(Cta& k) {
+    k.ctrl->abort = 1;
+    atomicExch(k.p.status, FC_E_TIMEOUT);
+}
+
+// ------------------------------------------------------------------ producer
+// Waits until `bar` completes phase `parity`; false when told to stop or out of time.
+__device__ bool producer_wait(Cta& k, unsigned long long* bar, uint32_t parity) {
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (k.ctrl->stop) return false;
+        if (timed_out(t0)) { atomicExch(k.p.status, FC_E_TIMEOUT); return false; }
+    }
+    return k.ctrl->stop == 0;
+}
+
+// Issues the bulk copies of one matrix share. Returns false when told to stop.
+__device__ bool produce_matrix(Cta& k, const QMat& w) {
+    int r0, r1;
+    mega_cta_rows(w.N, w.K, k.c, k.G, &r0, &r1);
+    const int rpi = rows_per_item(w.K), g = mega_row_gran(w.K);
+    for (int r = r0; r < r1; r += rpi) {
+        const int rows = min(rpi, r1 - r);
+        const int rows_c = (rows + g - 1) / g * g;          // padded rows exist up to N_pad
+        const int slot = k.item % SLOTS;
+        if (!producer_wait(k, &k.ctrl->empty[slot], ((k.item / SLOTS) & 1) ^ 1)) return false;
+        const uint32_t qb = (uint32_t)rows_c * w.K, db = qb >> 4;
+        mbar_expect_tx(&k.ctrl->full[slot], qb + db);
+        bulk_g2s(k.slot_q(slot), w.qu + (size_t)r * w.K, qb, &k.ctrl->full[slot]);
+        bulk_g2s((void*)k.slot_d(slot), w.d + (size_t)r * (w.K >> 5), db, &k.ctrl->full[slot]);
+        ++k.item;
+    }
+    return true;
+}
+
+// LayerNorm vectors (4d floats) and, for a block, this CTA's bias slices.
+__device__ bool produce_params(Cta& k, const float* lnpack, const float* biaspack) {
+    const int b = k.pitem & 1;
+    if (!producer_wait(k, &k.ctrl->pempty[b], ((k.pitem >> 1) & 1) ^ 1)) return false;
+    const uint32_t lb = (uint32_t)k.p.d * 16, bb = biaspack ? kMegaBiasPack * 4 : 0;
+    mbar_expect_tx(&k.ctrl->pfull[b], lb + bb);
+    bulk_g2s(k.param(b), lnpack, lb, &k.ctrl->pfull[b]);
+    if (biaspack) bulk_g2s(k.param(b) + 4 * MAX_D, biaspack + (size_t)k.c * kMegaBiasPack, bb, &k.ctrl->pfull[b]);
+    ++k.pitem;
+    return true;
+}
+
+__device__ void producer(Cta& k) {
+    const MegaParams& p = k.p;
+    for (int step = 0; step < p.n_steps; ++step) {
+        for (int l = 0; l < p.L; ++l) {
+            const MegaLayer& L = k.layers[l];
+            if (!produce_params(k, L.lnpack, L.biaspack)) return;
+            if (!produce_matrix(k, L.qkv) || !produce_matrix(k, L.out) || !produce_matrix(k, L.up) || !produce_matrix(k, L.down)) return;
+        }
+        if (step >= p.head_from) {
+            if (!produce_params(k, p.lnfpack, nullptr) || !produce_matrix(k, p.head)) return;
+        }
+    }
+}
+
+// ------------------------------------------------------------------ consumer helpers
+// Fixed-order sum / max over the 512 consumer threads.
+__device__ float csum(Cta& k, float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    consumer_sync();
+    if ((k.tid & 31) == 0) k.red[k.tid >> 5] = v;
+    consumer_sync();
+    float t = 0.0f;
+#pragma unroll
+    for (int w = 0; w < CWARPS; ++w) t += k.red[w];
+    return t;
+}
+__device__ float cmax(Cta& k, float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    consumer_sync();
+    if ((k.tid & 31) == 0) k.red[k.tid >> 5] = v;
+    consumer_sync();
+    float t = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < CWARPS; ++w) t = fmaxf(t, k.red[w]);
+    return t;
+}
+
+// layer/norm.rs:46-82 on xs[0..d) -> act (swizzled); g, b in shared memory.
+__device__ void layernorm_to_act(Cta& k, const float* g, const float* b) {
+    const int d = k.p.d;
+    const float v0 = k.tid < d ? k.xs[k.tid] : 0.0f;
+    const float v1 = k.tid + CONSUMERS < d ? k.xs[k.tid + CONSUMERS] : 0.0f;
+    const float mean = csum(k, v0 + v1) / (float)d;
+    const float t0 = v0 - mean, t1 = v1 - mean;
+    const float q = (k.tid < d ? t0 * t0 : 0.0f) + (k.tid + CONSUMERS < d ? t1 * t1 : 0.0f);
+    const float var = csum(k, q) / (float)d;
+    const float sd = sqrtf(var + 1e-5f);
+    if (k.tid < d) k.act[act_index(k.tid)] = (t0 / sd) * g[k.tid] + b[k.tid];
+    if (k.tid + CONSUMERS < d) k.act[act_index(k.tid + CONSUMERS)] = (t1 / sd) * g[k.tid + CONSUMERS] + b[k.tid + CONSUMERS];
+    consumer_sync();
+}
+
+// Waits (every consumer thread) for a full barrier; the abort flag is read after a CTA-wide
+// sync so that all consumer threads take the same branch.
+__device__ bool consumer_wait(Cta& k, unsigned long long* bar, uint32_t parity) {
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (timed_out(t0)) { raise_timeout(k); break; }
+    }
+    consumer_sync();
+    return k.ctrl->abort == 0;
+}
+
+// Grid barrier over all CTAs (consumer thread 0 arrives and polls). Returns false on timeout
+// or when another CTA reported one.
+__device__ bool grid_barrier(Cta& k) {
+    consumer_sync();                     // every thread's global writes precede the release below
+    k.bar_target += (unsigned)k.G;
+    if (k.tid == 0) {
+        red_release_add(k.p.bar, 1u);
+        const long long t0 = clock64();
+        while ((int)(ld_acquire(k.p.bar) - k.bar_target) < 0) {
+            if (*(volatile int*)k.p.status != 0) { k.ctrl->abort = 1; break; }
+            if (timed_out(t0)) { raise_timeout(k); break; }
+        }
+    }
+    consumer_sync();
+    return k.ctrl->abort == 0;
+}
+
+// Consumes this CTA's share of matrix w against the activation in act; epi(n, i, value) is
+// called once per owned output row n (i = n - first owned row) by one thread.
+template <class Epi>
+__device__ bool consume_matrix(Cta& k, const QMat& w, Epi epi) {
+    int r0, r1;
+    mega_cta_rows(w.N, w.K, k.c, k.G, &r0, &r1);
+    const int K = w.K, rpi = rows_per_item(K), chunks = K >> 4, kb_row = K >> 5;
+    const int iters = max(1, chunks >> 4);            // 16-lane sweeps per row
+    const int hw = k.tid >> 4, hl = k.tid & 15;
+    const unsigned hmask = 0xFFFFu << (k.tid & 16);
+    for (int r = r0; r < r1; r += rpi) {
+        const int rows = min(rpi, r1 - r);
+        // split K over several half warps when an item has few rows: pick the split with the
+        // fewest sweeps on the critical path (rounds over the 32 half warps x sweeps per unit)
+        int ksplit = 1, best_cost = ((rows + 31) >> 5) * iters;
+        {
+            const int cand[7] = {2, 3, 4, 6, 8, 12, 16};
+#pragma unroll
+            for (int i = 0; i < 7; ++i) {
+                const int ks = cand[i];
+                if (iters % ks == 0 && rows * ks <= 128) {
+                    const int cost = ((rows * ks + 31) >> 5) * (iters / ks);
+                    if (cost < best_cost) { best_cost = cost; ksplit = ks; }
+                }
+            }
+        }
+        const int slot = k.item % SLOTS;
+        mark(k);
+        if (!consumer_wait(k, &k.ctrl->full[slot], (k.item / SLOTS) & 1)) return false;
+        mark(k);
+        const unsigned char* q = k.slot_q(slot);
+        const __half* ds = k.slot_d(slot);
+        float* ps = k.psum + (k.item & 1) * 256;
+        const int units = rows * ksplit, per = iters / ksplit;
+        for (int u = hw; u < units; u += CONSUMERS / 16) {
+            const int row = u / ksplit, part = u - row * ksplit;
+            float acc = 0.0f;
+            for (int i = part * per; i < (part + 1) * per; ++i) {
+                const int cc = i * 16 + hl;
+                if (cc < chunks) {
+                    const uint4 wv = *(const uint4*)(q + (size_t)row * K + cc * 16);
+                    const float scale = __half2float(ds[row * kb_row + (cc >> 1)]);
+                    acc = fmaf(scale, dot16(wv, k.act4, cc), acc);
+                }
+            }
+            acc += __shfl_xor_sync(hmask, acc, 8);
+            acc += __shfl_xor_sync(hmask, acc, 4);
+            acc += __shfl_xor_sync(hmask, acc, 2);
+            acc += __shfl_xor_sync(hmask, acc, 1);
+            if (hl == 0) ps[u] = acc;
+        }
+        mark(k);
+        consumer_sync();                                   // slot fully read, partial sums visible
+        mark(k);
+        if ((k.tid & 31) == 0) mbar_arrive(&k.ctrl->empty[slot]);
+        for (int row = k.tid; row < rows; row += CONSUMERS) {
+            float v = 0.0f;
+            for (int part = 0; part < ksplit; ++part) v += ps[row * ksplit + part];
+            epi(r + row, r + row - r0, v);
+        }
+        ++k.item;
+    }
+    return true;
+}
+
+// transformer.rs:246-283 split over CTAs: CTA (h, s) handles keys [s*len/S, (s+1)*len/S) of
+// head h and writes (max, sum-exp, unnormalised out[hd]) to partg.
+__device__ void attention_partial(Cta& k, int l, int len) {
+    const MegaParams& p = k.p;
+    const int S = p.attn_splits, hd = p.d / p.H;
+    if (k.c >= p.H * S) return;
+    const int h = k.c / S, s = k.c - h * S, hs = h * hd;
+    const int j0 = (int)((long long)s * len / S), j1 = (int)((long long)(s + 1) * len / S);
+    const float* kc = p.kc + (size_t)l * p.T * p.d;
+    const float* vc = p.vc + (size_t)l * p.T * p.d;
+    float* out = p.partg + (size_t)k.c * (hd + 2);
+    const int lane = k.tid & 31, wid = k.tid >> 5;
+    // each lane owns head dimensions lane and lane + 32 (hd <= 64); a warp takes 4 keys per
+    // sweep with all of their loads (and the query's) in flight together
+    const bool has0 = lane < hd, has1 = lane + 32 < hd;
+    const float q0 = has0 ? __ldcg(p.qg + hs + lane) : 0.0f;
+    const float q1 = has1 ? __ldcg(p.qg + hs + lane + 32) : 0.0f;
+    // the values of the first 8 keys of this thread's group are requested now, so that their
+    // latency overlaps the score phase: thread (g, cc) owns keys j0 + g, j0 + g + groups, ...
+    const int groups = CONSUMERS / hd, g = k.tid / hd, cc = k.tid - g * hd;
+    float vpre[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+        const int j = j0 + g + u * groups;
+        vpre[u] = (g < groups && j < j1) ? __ldcg(vc + (size_t)j * p.d + hs + cc) : 0.0f;
+    }
+    const float scale = 1.0f / sqrtf((float)hd);
+    float mx = -INFINITY;
+    for (int jb = j0 + wid * 4; jb < j1; jb += CWARPS * 4) {
+        float a0[4], a1[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const float* kr = kc + (size_t)(jb + u) * p.d + hs;
+            const bool on = jb + u < j1;
+            a0[u] = (on && has0) ? __ldcg(kr + lane) : 0.0f;
+            a1[u] = (on && has1) ? __ldcg(kr + lane + 32) : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            float dot = fmaf(q1, a1[u], q0 * a0[u]);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+            if (jb + u < j1) {
+                const float sv = dot * scale;
+                if (lane == 0) k.sc[jb + u - j0] = sv;
+                mx = fmaxf(mx, sv);
+            }
+        }
+    }
+    mx = cmax(k, mx);
+    float e = 0.0f;
+    for (int j = j0 + k.tid; j < j1; j += CONSUMERS) {
+        const float t = expf(k.sc[j - j0] - mx);
+        k.sc[j - j0] = t;
+        e += t;
+    }
+    const float sum = csum(k, e);                 // includes the sync that publishes sc[]
+    // out[c] = sum_j e_j v[j][c], then a fixed-order combine of the groups
+    float acc = 0.0f;
+    if (g < groups) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int j = j0 + g + u * groups;
+            if (j < j1) acc = fmaf(k.sc[j - j0], vpre[u], acc);
+        }
+        for (int jb = j0 + g + 8 * groups; jb < j1; jb += groups * 8) {
+            float vv[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int j = jb + u * groups;
+                vv[u] = j < j1 ? __ldcg(vc + (size_t)j * p.d + hs + cc) : 0.0f;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int j = jb + u * groups;
+                if (j < j1) acc = fmaf(k.sc[j - j0], vv[u], acc);
+            }
+        }
+    }
+    consumer_sync();
+    float* part = k.act;                          // act is free during the attention phase
+    if (g < groups) part[g * hd + cc] = acc;
+    consumer_sync();
+    if (k.tid < hd) {
+        float t = 0.0f;
+        for (int gg = 0; gg < groups; ++gg) t += part[gg * hd + k.tid];
+        out[2 + k.tid] = t;
+    }
+    if (k.tid == 0) { out[0] = mx; out[1] = sum; }
+}
+
+// Combines the S partials of every head into the attention output, written to act.
+__device__ void attention_combine(Cta& k) {
+    const MegaParams& p = k.p;
+    const int S = p.attn_splits, hd = p.d / p.H;
+    for (int t = k.tid; t < p.d; t += CONSUMERS) {
+        const int h = t / hd, cc = t - h * hd;
+        const float* base = p.partg + (size_t)h * S * (hd + 2);
+        // all loads are issued before any use so that they overlap (S <= 8)
+        float ms[8], ls[8], os[8];
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+            const bool on = s < S;
+            ms[s] = on ? __ldcg(base + s * (hd + 2)) : -INFINITY;
+            ls[s] = on ? __ldcg(base + s * (hd + 2) + 1) : 0.0f;
+            os[s] = on ? __ldcg(base + s * (hd + 2) + 2 + cc) : 0.0f;
+        }
+        float M = -INFINITY;
+#pragma unroll
+        for (int s = 0; s < 8; ++s) M = fmaxf(M, ms[s]);
+        float Lsum = 0.0f, O = 0.0f;
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+            const float f = ms[s] > -INFINITY ? expf(ms[s] - M) : 0.0f;
+            Lsum = fmaf(ls[s], f, Lsum);
+            O = fmaf(os[s], f, O);
+        }
+        k.act[act_index(t)] = O / Lsum;
+    }
+    consumer_sync();
+}
+
+__device__ void load_vec(Cta& k, const float* g, float* dst, int n, bool swizzle) {
+    for (int i = k.tid; i < n; i += CONSUMERS) dst[swizzle ? act_index(i) : i] = __ldcg(g + i);
+    consumer_sync();
+}
+
+struct ArgBest { float v; int i; };
+__device__ __forceinline__ ArgBest better(ArgBest a, ArgBest b) {
+    return (b.v > a.v || (b.v == a.v && b.i < a.i)) ? b : a;
+}
+// Fixed-order arg-best over the consumer threads; every thread gets the result.
+__device__ ArgBest cbest(Cta& k, ArgBest best) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        ArgBest other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+        best = better(best, other);
+    }
+    consumer_sync();
+    if ((k.tid & 31) == 0) { k.red[k.tid >> 5] = best.v; k.red[32 + (k.tid >> 5)] = __int_as_float(best.i); }
+    consumer_sync();
+    ArgBest r{-INFINITY, 0x7fffffff};
+#pragma unroll
+    for (int w = 0; w < CWARPS; ++w) r = better(r, ArgBest{k.red[w], __float_as_int(k.red[32 + w])});
+    return r;
+}
+
+// ------------------------------------------------------------------ consumer
+__device__ void consumer(Cta& k) {
+    const MegaParams& p = k.p;
+    const int d = p.d, V = p.V;
+    // decode state, tracked identically by every CTA
+    int pos = p.state->pos, fed = p.state->fed, tail = p.state->tail, done = p.state->done, error = p.state->error;
+    const int eos = p.state->eos;
+    int pending_idx = -1, pending_id = 0;   // the token this launch appended last (known to every CTA)
+    int boff[4];
+    mega_bias_offsets(d, p.F, k.c, k.G, boff);
+    for (int step = 0; step < p.n_steps && !done && !error; ++step) {
+        const int id = fed == pending_idx ? pending_id : (fed < p.queue_cap ? __ldcg(p.queue + fed) : -1);
+        // embedding.rs:71-82, transformer.rs:237-242: errors, not traps
+        if (id < 0 || id >= V || pos >= p.T) { error = FC_E_DIM; break; }
+        // layer/embedding.rs:70-90: x = tok[id] + pos[pos]
+        for (int cc = k.tid; cc < d; cc += CONSUMERS) {
+            const float dq = __half2float(p.tok.d[(size_t)id * (d >> 5) + (cc >> 5)]);
+            const int q = (int)p.tok.qu[(size_t)id * d + cc] - 128;
+            k.xs[cc] = dq * (float)q + p.pos[(size_t)pos * d + cc];
+        }
+        consumer_sync();
+        // the phase timeline covers the last step of the launch
+        k.trace_n = (p.trace && k.c == 0 && k.tid == 0 && step + 1 == p.n_steps) ? 0 : -1;
+        mark(k);
+        const int len = pos + 1;
+        bool ok = true;
+        for (int l = 0; l < p.L && ok; ++l) {
+            const MegaLayer& L = k.layers[l];
+            float* kc = p.kc + ((size_t)l * p.T + pos) * d;
+            float* vc = p.vc + ((size_t)l * p.T + pos) * d;
+            const int pb = k.pitem & 1;
+            ok = consumer_wait(k, &k.ctrl->pfull[pb], (k.pitem >> 1) & 1);
+            if (!ok) break;
+            const float* prm = k.param(pb);
+            const float* bias = prm + 4 * MAX_D;
+            // LN1 -> q, k, v (k, v appended to the cache at `pos`)
+            layernorm_to_act(k, prm, prm + d);
+            mark(k);
+            ok = consume_matrix(k, L.qkv, [&](int n, int i, float v) {
+                v += bias[boff[0] + i];
+                if (n < d) p.qg[n] = v; else if (n < 2 * d) kc[n - d] = v; else vc[n - 2 * d] = v;
+            });
+            mark(k);
+            ok = ok && grid_barrier(k);
+            if (!ok) break;
+            mark(k);
+            attention_partial(k, l, len);
+            mark(k);
+            ok = grid_barrier(k);
+            if (!ok) break;
+            mark(k);
+            attention_combine(k);
+            mark(k);
+            // out-proj + residual: x1 = x + (W att + b)
+            ok = consume_matrix(k, L.out, [&](int n, int i, float v) { p.x1g[n] = k.xs[n] + (v + bias[boff[1] + i]); });
+            mark(k);
+            ok = ok && grid_barrier(k);
+            if (!ok) break;
+            mark(k);
+            load_vec(k, p.x1g, k.xs, d, false);
+            layernorm_to_act(k, prm + 2 * d, prm + 3 * d);
+            mark(k);
+            ok = consume_matrix(k, L.up, [&](int n, int i, float v) { p.hidg[n] = gelu_f(v + bias[boff[2] + i]); });
+            mark(k);
+            ok = ok && grid_barrier(k);
+            if (!ok) break;
+            mark(k);
+            load_vec(k, p.hidg, k.act, p.F, true);
+            mark(k);
+            ok = consume_matrix(k, L.down, [&](int n, int i, float v) { p.xg[n] = k.xs[n] + (v + bias[boff[3] + i]); });
+            mark(k);
+            ok = ok && grid_barrier(k);          // its first sync also ends every read of the parameters
+            if (!ok) break;
+            if ((k.tid & 31) == 0) mbar_arrive(&k.ctrl->pempty[pb]);
+            ++k.pitem;
+            mark(k);
+            load_vec(k, p.xg, k.xs, d, false);
+            mark(k);   // 15 marks per block
+        }
+        if (!ok) break;
+        if (step >= p.head_from) {
+            const int pb = k.pitem & 1;
+            if (!consumer_wait(k, &k.ctrl->pfull[pb], (k.pitem >> 1) & 1)) break;
+            layernorm_to_act(k, k.param(pb), k.param(pb) + d);   // ends with a sync
+            if ((k.tid & 31) == 0) mbar_arrive(&k.ctrl->pempty[pb]);
+            ++k.pitem;
+            int r0, r1;
+            mega_cta_rows(V, d, k.c, k.G, &r0, &r1);
+            float* lg = k.sc;                      // this CTA's logits [r1 - r0]
+            ok = consume_matrix(k, p.head, [&](int n, int i, float v) { lg[i] = v; p.logits[n] = v; });
+            if (!ok) break;
+            consumer_sync();
+            // ops.rs:478-502: max, exp(x - max), sum — per CTA, then combined across CTAs
+            float m = -INFINITY;
+            for (int i = k.tid; i < r1 - r0; i += CONSUMERS) m = fmaxf(m, lg[i]);
+            m = cmax(k, m);
+            float e = 0.0f;
+            for (int i = k.tid; i < r1 - r0; i += CONSUMERS) e += expf(lg[i] - m);
+            e = csum(k, e);
+            if (k.tid == 0) { p.statg[4 * k.c] = m; p.statg[4 * k.c + 1] = e; }
+            mark(k);
+            if (!grid_barrier(k)) break;
+            mark(k);
+            // every CTA combines the per-CTA (max, sum) pairs: one load per thread, then
+            // fixed-order block reductions (G <= 512)
+            const float mc = k.tid < k.G ? __ldcg(p.statg + 4 * k.tid) : -INFINITY;
+            const float ec = k.tid < k.G ? __ldcg(p.statg + 4 * k.tid + 1) : 0.0f;
+            const float M = cmax(k, mc);
+            const float sum = csum(k, mc > -INFINITY ? ec * expf(mc - M) : 0.0f);
+            const bool last = step + 1 == p.n_steps;
+            if (p.probs && last)
+                for (int i = k.tid; i < r1 - r0; i += CONSUMERS) p.probs[r0 + i] = expf(lg[i] - M) / sum;
+            if (p.select) {
+                // token_stream.rs:134 + sampling.rs:96-104: first index of the largest ln(max(p, 1e-12))
+                ArgBest best{-INFINITY, 0x7fffffff};
+                for (int i = k.tid; i < r1 - r0; i += CONSUMERS)
+                    best = better(best, ArgBest{logf(fmaxf(expf(lg[i] - M) / sum, 1e-12f)), r0 + i});
+                best = cbest(k, best);
+                if (k.tid == 0) {
+                    p.statg[4 * k.c + 2] = best.v;
+                    p.statg[4 * k.c + 3] = __int_as_float(best.i);
+                }
+                mark(k);
+                if (!grid_barrier(k)) break;
+                mark(k);
+                // one candidate per thread, then the same fixed-order reduction in every CTA
+                ArgBest win{-INFINITY, 0x7fffffff};
+                if (k.tid < k.G) win = ArgBest{__ldcg(p.statg + 4 * k.tid + 2), __float_as_int(__ldcg(p.statg + 4 * k.tid + 3))};
+                win = cbest(k, win);
+                mark(k);
+                if (win.i == eos) {
+                    done = 1;
+                } else if (tail < p.queue_cap) {
+                    if (k.c == 0 && k.tid == 0) p.queue[tail] = win.i;
+                    pending_idx = tail;
+                    pending_id = win.i;
+                    tail += 1;
+                } else {
+                    error = FC_E_DIM;
+                }
+            }
+        }
+        pos += 1;
+        fed += 1;
+    }
+    if (k.c == 0 && k.tid == 0) {
+        p.state->pos = pos; p.state->fed = fed; p.state->tail = tail; p.state->done = done;
+        if (error) p.state->error = error;
+    }
+}
+
+}  // namespace
+
+__global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_constant__ MegaParams p) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    Ctrl* ctrl = (Ctrl*)(smem + OFF_CTRL);
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < SLOTS; ++s) {
+            mbar_init(&ctrl->full[s], 1);
+            mbar_init(&ctrl->empty[s], CWARPS);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&ctrl->pfull[b], 1);
+            mbar_init(&ctrl->pempty[b], CWARPS);
+        }
+        ctrl->stop = 0; ctrl->consumed = 0; ctrl->pconsumed = 0; ctrl->abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // the layer table is read from shared memory: its entries sit on every phase's critical path
+    {
+        const uint4* src = (const uint4*)p.layers;
+        uint4* dst = (uint4*)(smem + OFF_LAYERS);
+        const int words = p.L * (int)(sizeof(MegaLayer) / 16);
+        for (int i = threadIdx.x; i < words; i += blockDim.x) dst[i] = src[i];
+    }
+    __syncthreads();
+    Cta k{p, smem, ctrl, (const MegaLayer*)(smem + OFF_LAYERS), (float4*)(smem + OFF_ACT), (float*)(smem + OFF_ACT),
+          (float*)(smem + OFF_XS), (float*)(smem + OFF_SC), (float*)(smem + OFF_PSUM), (float*)(smem + OFF_RED),
+          (int)blockIdx.x, (int)gridDim.x, (int)threadIdx.x, 0, 0, 0u, -1};
+    if (threadIdx.x >= CONSUMERS) {
+        if (threadIdx.x == CONSUMERS) producer(k);
+        __syncwarp();
+    } else {
+        consumer(k);
+        consumer_sync();
+        if (threadIdx.x == 0) { ctrl->consumed = k.item; ctrl->pconsumed = k.pitem; ctrl->stop = 1; }
+    }
+    __syncthreads();
+    // drain: wait for bulk copies that were issued but never consumed before the CTA exits
+    if (threadIdx.x == CONSUMERS) {
+        for (int i = ctrl->consumed; i < k.item; ++i) {
+            const long long t0 = clock64();
+            while (!mbar_try_wait(&ctrl->full[i % SLOTS], (i / SLOTS) & 1))
+                if (timed_out(t0)) { atomicExch(p.status, FC_E_TIMEOUT); break; }
+        }
+        for (int i = ctrl->pconsumed; i < k.pitem; ++i) {
+            const long long t0 = clock64();
+            while (!mbar_try_wait(&ctrl->pfull[i & 1], (i >> 1) & 1))
+                if (timed_out(t0)) { atomicExch(p.status, FC_E_TIMEOUT); break; }
+        }
+    }
+}
+
+size_t mega_smem_bytes() { return SMEM_BYTES; }
+int mega_threads() { return THREADS; }
+
+int mega_supported(const fc_config& c) {
+    const int hd = c.d_model / c.n_head;
+    return c.d_model <= MAX_D && c.d_ff <= MAX_F && c.ctx <= MAX_CTX && hd <= 64 && c.d_model <= 2 * CONSUMERS &&
+           c.n_layer <= kMegaMaxLayers;
+}
+
+int launch_decode_mega(const MegaParams& p, int grid, cudaStream_t st) {
+    static bool attr_set[64] = {};
+    int dev = 0;
+    FC_CUDA(cudaGetDevice(&dev));
+    if (dev < 64 && !attr_set[dev]) {
+        FC_CUDA(cudaFuncSetAttribute(decode_mega_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        attr_set[dev] = true;
+    }
+    FC_CUDA(cudaMemsetAsync(p.bar, 0, sizeof(unsigned), st));
+    void* args[] = {(void*)&p};
+    FC_CUDA(cudaLaunchCooperativeKernel((void*)decode_mega_kernel, dim3(grid), dim3(THREADS), args, SMEM_BYTES, st));
+    ++g_launches;
+    return FC_OK;
+}
+
+int mega_max_grid(int* grid) {
+    int dev = 0, sms = 0, per_sm = 0;
+    FC_CUDA(cudaGetDevice(&dev));
+    FC_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    FC_CUDA(cudaFuncSetAttribute(decode_mega_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    FC_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_mega_kernel, THREADS, SMEM_BYTES));
+    if (per_sm < 1) return fail(FC_E_CUDA, "the persistent decode kernel does not fit on an SM");
+    *grid = sms < CONSUMERS ? sms : CONSUMERS;
+    return FC_OK;
+}
+
+}  // namespace fc

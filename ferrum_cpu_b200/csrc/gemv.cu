@@ -63,12 +63,12 @@ __device__ __forceinline__ float dot16(const uint4& w, const float4* __restrict_
     const int sw = (c >> 1) & 3;
     const int base = 4 * c;
     const float4 x0 = xs[base + (0 ^ sw)], x1 = xs[base + (1 ^ sw)], x2 = xs[base + (2 ^ sw)], x3 = xs[base + (3 ^ sw)];
-    float a = 0.0f;
-    a = fmaf(x0.x, qbyte<0>(w.x), a); a = fmaf(x0.y, qbyte<1>(w.x), a); a = fmaf(x0.z, qbyte<2>(w.x), a); a = fmaf(x0.w, qbyte<3>(w.x), a);
-    a = fmaf(x1.x, qbyte<0>(w.y), a); a = fmaf(x1.y, qbyte<1>(w.y), a); a = fmaf(x1.z, qbyte<2>(w.y), a); a = fmaf(x1.w, qbyte<3>(w.y), a);
-    a = fmaf(x2.x, qbyte<0>(w.z), a); a = fmaf(x2.y, qbyte<1>(w.z), a); a = fmaf(x2.z, qbyte<2>(w.z), a); a = fmaf(x2.w, qbyte<3>(w.z), a);
-    a = fmaf(x3.x, qbyte<0>(w.w), a); a = fmaf(x3.y, qbyte<1>(w.w), a); a = fmaf(x3.z, qbyte<2>(w.w), a); a = fmaf(x3.w, qbyte<3>(w.w), a);
-    return a;
+    // four independent chains of four dependent fused multiply-adds
+    float a = x0.x * qbyte<0>(w.x), b = x1.x * qbyte<0>(w.y), c2 = x2.x * qbyte<0>(w.z), e = x3.x * qbyte<0>(w.w);
+    a = fmaf(x0.y, qbyte<1>(w.x), a); b = fmaf(x1.y, qbyte<1>(w.y), b); c2 = fmaf(x2.y, qbyte<1>(w.z), c2); e = fmaf(x3.y, qbyte<1>(w.w), e);
+    a = fmaf(x0.z, qbyte<2>(w.x), a); b = fmaf(x1.z, qbyte<2>(w.y), b); c2 = fmaf(x2.z, qbyte<2>(w.z), c2); e = fmaf(x3.z, qbyte<2>(w.w), e);
+    a = fmaf(x0.w, qbyte<3>(w.x), a); b = fmaf(x1.w, qbyte<3>(w.y), b); c2 = fmaf(x2.w, qbyte<3>(w.z), c2); e = fmaf(x3.w, qbyte<3>(w.w), e);
+    return (a + b) + (c2 + e);
 }
 
 struct GemvArgs {

@@ -148,6 +148,22 @@ class CudaSlm:
     def reset(self):
         check(_lib.lib().fc_stream_reset(self._stream()))
 
+    def set_trace(self, on):
+        check(_lib.lib().fc_stream_set_trace(self._stream(), int(on)))
+
+    def read_trace(self):
+        """Phase timeline (ns, relative to the token start) of the last traced token."""
+        buf = np.zeros(1024, dtype=np.uint64)
+        n = _lib.lib().fc_stream_read_trace(self._stream(), _ptr(buf), buf.size)
+        if n < 0:
+            check(n)
+        t = buf[:n].astype(np.int64)
+        return t - t[0] if n else t
+
+    def set_decode_mode(self, mode):
+        """0: persistent decode kernel (default), 1: one kernel per layer operation."""
+        check(_lib.lib().fc_stream_set_mode(self._stream(), mode))
+
     def cached_len(self):
         return _lib.lib().fc_cached_len(self._stream())
 

@@ -139,6 +139,22 @@ int fc_predict_next(fc_model* m, const int32_t* ids, int n, float* probs);
 int fc_stream_create(fc_model* m, fc_stream** out);   /* cached.rs:45-64 try_new */
 void fc_stream_free(fc_stream* s);
 int fc_stream_reset(fc_stream* s);                    /* cached.rs:93-98 */
+/* How fc_feed / fc_prime / fc_generate_greedy run a token on the GPU. Both compute the same
+ * CachedTransformer::feed; the per-kernel form exists to cross-check the persistent one.
+ *   FC_DECODE_PERSISTENT: one cooperative kernel per batch of tokens (default when the model
+ *                         shape fits it: d_model <= 1024, d_ff <= 4096, ctx <= 1024);
+ *   FC_DECODE_PER_KERNEL: one kernel per layer operation, replayed from a CUDA graph. */
+#define FC_DECODE_PERSISTENT 0
+#define FC_DECODE_PER_KERNEL 1
+int fc_stream_set_mode(fc_stream* s, int mode);
+/* Tracing (the reference's per-layer verbose log, verbose.rs:11-110, has no timing; this is
+ * its device-side counterpart). When on, the persistent decode kernel records the GPU's
+ * nanosecond timer at every phase boundary of the last token of each launch:
+ * entry 0 = token start, then 15 entries per block (LayerNorm1, QKV, barrier, attention,
+ * barrier, combine, out-proj, barrier, LayerNorm2, up, barrier, load, down, barrier, load),
+ * then the head phases. fc_stream_read_trace returns the number of entries copied (or < 0). */
+int fc_stream_set_trace(fc_stream* s, int on);
+int fc_stream_read_trace(fc_stream* s, uint64_t* out, int cap);
 int fc_cached_len(const fc_stream* s);
 /* cached.rs:100-125 feed: one token; probs (host [V]) may be NULL. FC_E_DIM on id >= vocab
  * or a full cache (transformer.rs:237-242). */

@@ -96,6 +96,27 @@ def test_greedy_tiny_config_matches_golden(tiny):
     gm.close()
 
 
+def test_per_kernel_and_persistent_decode_agree(tiny):
+    """The two ways of running a cached token compute the same feed: identical greedy tokens and
+    log-probs within fp32 reordering noise, both within tolerance of the oracle."""
+    sm, om, gm = tiny
+    V = sm.dims[5]
+    prompt = synth.token_ids(17, 9, V)
+    want, margin = om.generate_greedy(prompt, 24)
+    out = {}
+    for mode in (1, 0):
+        gm.set_decode_mode(mode)
+        toks, _ = gm.generate_tokens(prompt, 24)
+        check_greedy(toks, want, margin)
+        probs = [gm.prime(prompt[:5])] + [gm.feed(t) for t in prompt[5:]]
+        out[mode] = (toks, np.stack(probs))
+    assert np.array_equal(out[0][0], out[1][0])
+    assert np.abs(logp(out[0][1]) - logp(out[1][1])).max() < 1e-4
+    om.reset()
+    ref = np.stack([om.feed(t) for t in prompt])[4:]
+    assert np.abs(logp(out[0][1]) - logp(ref)).max() < FP32_LOGPROB_TOL
+
+
 def test_greedy_reprimes_past_the_context(mini):
     sm, om, gm = mini
     prompt = synth.token_ids(9, 4, 96)
