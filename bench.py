@@ -156,6 +156,8 @@ def main():
     ap.add_argument("--score-steps", type=int, default=2)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--score-math", choices=["bf16x3", "fp32"], default="bf16x3",
+                    help="math mode of the scoring GEMMs: tcgen05 bf16 3-term split, or fp32 CUDA cores")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -189,7 +191,8 @@ def main():
         return float(t.item())
 
     hbm_peak, tf_peak, peak_kind = peaks()
-    sm = synth.named("small", seed=0)
+    # decode always runs fp32 FMA; the prefill GEMMs of scoring run the tensor-core math mode
+    sm = synth.named("small", seed=0, math_mode=fcb.FC_MATH_FP32 if args.score_math == "fp32" else fcb.FC_MATH_BF16X3)
     dims = sm.dims
     V = dims[5]
     gm = fcb.CudaSlm(sm.config, sm.weights, device=local)
@@ -274,7 +277,10 @@ def main():
             "metric": "Q8_0 GPT-2-small log-likelihood positions/s", "value": positions / (step_ms / 1e3), "unit": "positions/s",
             "n_gpus": world, "steps": args.score_steps, "ms_per_step": step_ms, "scaling": "strong" if world > 1 else "n/a",
             "config": {"workload": "configs[2]: %d sequences x %d ids, full-window prefill, per-token log-probs, %d windows per forward"
-                       % (per * world, SEQ_LEN, bw)},
+                       % (per * world, SEQ_LEN, bw),
+                       "math": "linear layers: tcgen05 kind::f16, bf16 3-term split of f32 operands, fp32 TMEM accumulate"
+                               if args.score_math == "bf16x3" else "fp32 CUDA cores"},
+            "dtype": "bf16x3" if args.score_math == "bf16x3" else "f32",
             "e2e": {"value": positions / e2e_s, "unit": "positions/s", "h2d_bytes_per_step": per * SEQ_LEN * 4,
                     "d2h_bytes_per_step": per * SEQ_LEN * 4 + per * 24},
             "gpu_launches": int(s_launch),

@@ -108,6 +108,11 @@ struct fc_qweight {
     int device;
     Arena arena;
     QMat w;
+    // scratch of the tensor-core path: bf16 hi / lo planes of the activations, status word
+    Arena planes;
+    uint16_t *xhi = nullptr, *xlo = nullptr;
+    int* status = nullptr;
+    size_t plane_elems = 0;
 };
 
 struct fc_model {
@@ -126,6 +131,8 @@ struct fc_model {
     int *ids_d = nullptr, *targets_d = nullptr, *err_d = nullptr;
     double* lp_d = nullptr;
     uint8_t* gr_d = nullptr;
+    uint16_t *xhi = nullptr, *xlo = nullptr;   // bf16 planes of the current GEMM input
+    int* tc_status = nullptr;                  // raised by the tensor-core GEMM on a timeout
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     float last_score_ms = 0.0f;
     // persistent decode kernel: per-layer parameter table on the device, grid size (0: the
@@ -305,14 +312,26 @@ static int ensure_workspace(fc_model* m, int rows) {
     FC_TRY(a.alloc_n(&m->gr_d, R));
     FC_TRY(a.alloc_n(&m->err_d, 1));
     FC_TRY(a.alloc_n(&m->probs_d, (size_t)c.vocab));
+    if (c.math_mode == FC_MATH_BF16X3) {
+        // bf16 hi / lo planes of the widest GEMM input, and the kernel's status word
+        FC_TRY(a.alloc_n(&m->xhi, R * std::max(d, F)));
+        FC_TRY(a.alloc_n(&m->xlo, R * std::max(d, F)));
+        FC_TRY(a.alloc_n(&m->tc_status, 1));
+        FC_CUDA(cudaMemsetAsync(m->tc_status, 0, sizeof(int), m->st));
+    }
     m->ws_rows = rows;
     m->head_chunk = (int)chunk;
     return FC_OK;
 }
 
 static int gemm(fc_model* m, const QMat& w, const float* x, const float* bias, const float* res, int epi, float* y, int M, int ldy) {
-    // FC_MATH_BF16X3 is routed to the tensor-core kernel when it is built in; the fp32
-    // CUDA-core kernel serves FC_MATH_FP32.
+    // FC_MATH_BF16X3: split the activations into bf16 hi/lo planes, then the tcgen05 kernel
+    // (its k-blocks are 64 wide). FC_MATH_FP32, or a K that is not a multiple of 64: the
+    // fp32 CUDA-core kernel.
+    if (m->cfg.math_mode == FC_MATH_BF16X3 && w.K % 64 == 0) {
+        FC_TRY(launch_split_bf16(x, m->xhi, m->xlo, (size_t)M * w.K, m->st));
+        return launch_gemm_q8_bf16x3(w, m->xhi, m->xlo, bias, res, epi, y, M, ldy, m->tc_status, m->st);
+    }
     return launch_gemm_q8_fp32(w, x, bias, res, epi, y, M, ldy, m->st);
 }
 
@@ -392,7 +411,9 @@ int fc_qweight_upload(int device, const void* wq, int N, int K, fc_qweight** out
 void fc_qweight_free(fc_qweight* w) {
     if (!w) return;
     cudaSetDevice(w->device);
+    cudaDeviceSynchronize();
     w->arena.release();
+    w->planes.release();
     delete w;
 }
 
@@ -401,12 +422,29 @@ int fc_q8_0_linear_dev(const fc_qweight* w, const float* x_dev, const float* bia
     if (!w || !x_dev || !y_dev) return fail(FC_E_ARG, "fc_q8_0_linear_dev: null argument");
     if (M < 0) return fail(FC_E_SHAPE, "fc_q8_0_linear_dev: M = %d", M);
     if (M == 0) return FC_OK;
-    (void)math_mode;
+    if (math_mode != FC_MATH_FP32 && math_mode != FC_MATH_BF16X3) return fail(FC_E_ARG, "unknown math_mode %d", math_mode);
     FC_CUDA(cudaSetDevice(w->device));
     cudaStream_t st = (cudaStream_t)cuda_stream;
     if (M == 1) {
         GemvOut o; o.out[0] = y_dev;
         return launch_gemv_q8(w->w, x_dev, bias_dev, nullptr, EPI_NONE, o, nullptr, st);
+    }
+    if (math_mode == FC_MATH_BF16X3 && w->w.K % 64 == 0) {
+        // the bf16 planes of x and the status word live in the weight handle and grow on demand
+        fc_qweight* wm = const_cast<fc_qweight*>(w);
+        const size_t need = (size_t)M * w->w.K;
+        if (need > wm->plane_elems) {
+            FC_CUDA(cudaStreamSynchronize(st));
+            wm->planes.release();
+            wm->plane_elems = 0;
+            FC_TRY(wm->planes.alloc_n(&wm->xhi, need));
+            FC_TRY(wm->planes.alloc_n(&wm->xlo, need));
+            FC_TRY(wm->planes.alloc_n(&wm->status, 1));
+            FC_CUDA(cudaMemsetAsync(wm->status, 0, sizeof(int), st));
+            wm->plane_elems = need;
+        }
+        FC_TRY(launch_split_bf16(x_dev, wm->xhi, wm->xlo, need, st));
+        return launch_gemm_q8_bf16x3(w->w, wm->xhi, wm->xlo, bias_dev, nullptr, EPI_NONE, y_dev, M, w->w.N, wm->status, st);
     }
     return launch_gemm_q8_fp32(w->w, x_dev, bias_dev, nullptr, EPI_NONE, y_dev, M, w->w.N, st);
 }
@@ -431,6 +469,11 @@ int fc_q8_0_linear(int device, const float* x, const void* wq, const float* bias
         if (bias) copy(bd, bias, (size_t)N * 4, cudaMemcpyHostToDevice);
         if (rc == FC_OK) rc = fc_q8_0_linear_dev(w, xd, bd, yd, M, math_mode, nullptr);
         if (rc == FC_OK && cudaDeviceSynchronize() != cudaSuccess) rc = cuda_fail(cudaGetLastError(), "fc_q8_0_linear kernel", __FILE__, __LINE__);
+        if (rc == FC_OK && w->status) {
+            int status = 0;
+            copy(&status, w->status, sizeof(int), cudaMemcpyDeviceToHost);
+            if (rc == FC_OK && status != 0) rc = fail(FC_E_TIMEOUT, "a bounded wait inside the tensor-core GEMM ran out (status %d)", status);
+        }
         copy(y, yd, (size_t)M * N * 4, cudaMemcpyDeviceToHost);
         tmp.release();
     }
@@ -587,7 +630,13 @@ static int score_windows_impl(fc_model* m, const int32_t* ids, const int32_t* ta
     FC_CUDA(cudaEventRecord(m->ev1, st));
     FC_CUDA(cudaMemcpyAsync(lp_host, m->lp_d, (size_t)R * 8, cudaMemcpyDeviceToHost, st));
     FC_CUDA(cudaMemcpyAsync(gr_host, m->gr_d, (size_t)R, cudaMemcpyDeviceToHost, st));
+    int tc_status = 0;
+    if (m->tc_status) FC_CUDA(cudaMemcpyAsync(&tc_status, m->tc_status, sizeof(int), cudaMemcpyDeviceToHost, st));
     FC_CUDA(cudaStreamSynchronize(st));
+    if (tc_status != 0) {
+        cudaMemsetAsync(m->tc_status, 0, sizeof(int), st);
+        return fail(FC_E_TIMEOUT, "a bounded wait inside the tensor-core GEMM ran out (status %d)", tc_status);
+    }
     float ms = 0.0f;
     FC_CUDA(cudaEventElapsedTime(&ms, m->ev0, m->ev1));
     m->last_score_ms += ms;

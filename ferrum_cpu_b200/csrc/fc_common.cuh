@@ -87,6 +87,13 @@ int launch_gemv_q8(const QMat& w, const float* x, const float* bias, const float
 int launch_gemm_q8_fp32(const QMat& w, const float* x, const float* bias, const float* residual, int epi,
                         float* y, int M, int ldy, cudaStream_t st);
 
+// gemm_tc.cu — the same product on tcgen05 tensor cores (bf16 3-term split, fp32 TMEM
+// accumulate). x_hi / x_lo are bf16 planes [M][K] made by launch_split_bf16; K % 64 == 0.
+// `status` is a device int raised to FC_E_TIMEOUT when a bounded wait runs out.
+int launch_split_bf16(const float* x, void* hi, void* lo, size_t n, cudaStream_t st);
+int launch_gemm_q8_bf16x3(const QMat& w, const void* x_hi, const void* x_lo, const float* bias, const float* residual,
+                          int epi, float* y, int M, int ldy, int* status, cudaStream_t st);
+
 // rowops.cu
 int launch_embed_step(const QMat& tok, const float* pos_emb, int ctx, const int* queue, StepState* state,
                       float* x, cudaStream_t st);

@@ -1,0 +1,346 @@
+// Q8_0 GEMM on the 5th-generation tensor cores (math mode FC_MATH_BF16X3):
+//     Y[M][N] = X[M][K] · dequant(W[N][K])ᵀ + bias (+GELU) (+residual)
+//
+// Replaces ops::linear_forward (ferrum_core/src/ops.rs:233-256) for M >= 2 with the weight
+// kept packed. The reference multiplies f32 by f32; tcgen05 has no f32 operand kind, so both
+// operands are split into two bf16 terms (x = xh + xl, w = wh + wl, each exact to 2^-17
+// relative) and every 128x128x16 step issues three kind::f16 MMAs into the same fp32 TMEM
+// accumulator: xh·wh + xl·wh + xh·wl. The dropped xl·wl term is 2^-16 relative per product.
+//
+// One CTA computes a 128 x 128 tile:
+//   warp 8      TMA producer: the two bf16 planes of the X tile (128 rows x 64 k, 128-byte
+//               swizzle) into the stage's A buffers, completing on the stage's mbarrier;
+//   warps 0-7   dequantise the 128 x 64 Q8_0 weight tile: w = d * q exactly as
+//               gguf::dequant_q8_0 (ferrum_core/src/gguf/dequant.rs:37-49), split into bf16
+//               hi/lo and stored in the same swizzled K-major layout the tensor core reads;
+//   warp 9      allocates TMEM and issues tcgen05.mma from one thread; tcgen05.commit frees
+//               the stage and finally publishes the accumulator;
+//   warps 0-3   epilogue: tcgen05.ld their 32 accumulator lanes, bias / GELU / residual, store.
+// Every mbarrier wait is bounded by a cycle budget; when it runs out the kernel raises a
+// status word, releases its TMEM and returns.
+//
+// Bound: tensor pipe. 2·M·N·K algorithmic FLOP (6·M·N·K executed).
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include "fc_common.cuh"
+
+namespace fc {
+
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 64;
+constexpr int STAGES = 3;
+constexpr int TILE_BYTES = BM * BK * 2;                 // one bf16 operand tile: 16 KiB
+constexpr int STAGE_BYTES = 4 * TILE_BYTES;             // A hi, A lo, B hi, B lo
+constexpr int DQ_WARPS = 8, THREADS = (DQ_WARPS + 2) * 32;
+constexpr int TMEM_COLS = 128;
+constexpr long long WAIT_CYCLES = 4000000000LL;
+// bf16 x bf16 -> f32, M = 128, N = 128, both operands K-major
+constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+struct Bars {
+    unsigned long long full_a[STAGES];
+    unsigned long long full_b[STAGES];
+    unsigned long long empty[STAGES];
+    unsigned long long acc_full;
+    uint32_t tmem_base;
+    volatile int abort;
+};
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + (int)sizeof(Bars);
+
+__device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned long long* b, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s32(b)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* b, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s32(b)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long* b) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s32(b)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long* b, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(s32(b)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait. Returns false (after raising the status word) when the budget runs out or
+// another role of this CTA already gave up.
+__device__ bool wait_bar(Bars* bars, unsigned long long* b, uint32_t parity, int* status) {
+    const long long t0 = clock64();
+    while (!mbar_try_wait(b, parity)) {
+        if (bars->abort) return false;
+        if (clock64() - t0 > WAIT_CYCLES) {
+            bars->abort = 1;
+            atomicExch(status, FC_E_TIMEOUT);
+            return false;
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(s32(dst)), "l"(map), "r"(x), "r"(y), "r"(s32(bar)) : "memory");
+}
+// K-major, 128-byte swizzle: 8-row atoms of 1024 bytes (SBO = 64 x 16 B), descriptor version 1.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)64 << 32) | ((uint64_t)1 << 46) |
+           ((uint64_t)2 << 61);
+}
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(IDESC), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned long long* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(bar)) : "memory");
+}
+
+template <int B>
+__device__ __forceinline__ float qb(uint32_t w) {
+    return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540 + B)) - 8388736.0f;
+}
+// Two weights -> packed bf16 hi pair and lo pair (element 0 in the low half).
+__device__ __forceinline__ void split2(float w0, float w1, uint32_t* hi, uint32_t* lo) {
+    const __nv_bfloat162 h = __float22bfloat162_rn(make_float2(w0, w1));
+    const float2 hf = __bfloat1622float2(h);
+    const __nv_bfloat162 l = __float22bfloat162_rn(make_float2(w0 - hf.x, w1 - hf.y));
+    *hi = *(const uint32_t*)&h;
+    *lo = *(const uint32_t*)&l;
+}
+
+struct TcArgs {
+    const uint8_t* qu; const __half* d; int N, K;
+    const float* bias; const float* residual; int epi;
+    float* y; int M, ldy;
+    int* status;
+};
+
+}  // namespace
+
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_q8_bf16x3_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_constant__ CUtensorMap map_lo, const TcArgs a) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    Bars* bars = (Bars*)(smem + STAGES * STAGE_BYTES);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int nkb = a.K / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&bars->full_a[s], 1);
+            mbar_init(&bars->full_b[s], DQ_WARPS);
+            mbar_init(&bars->empty[s], 1);
+        }
+        mbar_init(&bars->acc_full, 1);
+        bars->abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == DQ_WARPS + 1) {   // the MMA warp owns the tensor memory allocation
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(&bars->tmem_base)), "r"((uint32_t)TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = bars->tmem_base;
+
+    if (warp == DQ_WARPS) {
+        // ---------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            for (int kb = 0; kb < nkb; ++kb) {
+                const int s = kb % STAGES;
+                if (!wait_bar(bars, &bars->empty[s], ((kb / STAGES) & 1) ^ 1, a.status)) break;
+                unsigned char* st = smem + s * STAGE_BYTES;
+                mbar_expect_tx(&bars->full_a[s], 2 * TILE_BYTES);
+                tma_load_2d(st, &map_hi, kb * BK, m0, &bars->full_a[s]);
+                tma_load_2d(st + TILE_BYTES, &map_lo, kb * BK, m0, &bars->full_a[s]);
+            }
+        }
+    } else if (warp == DQ_WARPS + 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            bool ok = true;
+            for (int kb = 0; kb < nkb && ok; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t par = (kb / STAGES) & 1;
+                ok = wait_bar(bars, &bars->full_a[s], par, a.status) && wait_bar(bars, &bars->full_b[s], par, a.status);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t base = s32(smem + s * STAGE_BYTES);
+                const uint64_t ah = smem_desc(base), al = smem_desc(base + TILE_BYTES);
+                const uint64_t bh = smem_desc(base + 2 * TILE_BYTES), bl = smem_desc(base + 3 * TILE_BYTES);
+#pragma unroll
+                for (int ks = 0; ks < BK / 16; ++ks) {
+                    const uint64_t adv = (uint64_t)(ks * 2);            // 32 bytes per k-step of 16 bf16
+                    umma(tmem, ah + adv, bh + adv, (kb | ks) != 0);
+                    umma(tmem, al + adv, bh + adv, 1);
+                    umma(tmem, ah + adv, bl + adv, 1);
+                }
+                umma_commit(&bars->empty[s]);                        // frees the stage when the MMAs retire
+            }
+            if (ok) umma_commit(&bars->acc_full);
+        }
+    } else {
+        // ---------------------------------------------------------------- weight dequantisers
+        const int t = threadIdx.x;                  // 0..255
+        const int row = t >> 1, half = t & 1;       // weight row of the tile, 32-wide half of the k-block
+        const size_t n = (size_t)(n0 + row);        // < N_pad (zero rows past N)
+        const uint8_t* qrow = a.qu + n * a.K + half * 32;
+        const __half* drow = a.d + n * (a.K >> 5) + half;
+        uint4 q0 = __ldg((const uint4*)qrow), q1 = __ldg((const uint4*)qrow + 1);
+        float sc = __half2float(__ldg(drow));
+        bool ok = true;
+        for (int kb = 0; kb < nkb; ++kb) {
+            const int s = kb % STAGES;
+            const uint4 c0 = q0, c1 = q1;
+            const float scale = sc;
+            if (kb + 1 < nkb) {                     // prefetch the next k-block's quants
+                q0 = __ldg((const uint4*)(qrow + (size_t)(kb + 1) * BK));
+                q1 = __ldg((const uint4*)(qrow + (size_t)(kb + 1) * BK) + 1);
+                sc = __half2float(__ldg(drow + (kb + 1) * 2));
+            }
+            ok = wait_bar(bars, &bars->empty[s], ((kb / STAGES) & 1) ^ 1, a.status);
+            if (!ok) break;
+            unsigned char* bhi = smem + s * STAGE_BYTES + 2 * TILE_BYTES + row * 128;
+            unsigned char* blo = bhi + TILE_BYTES;
+            const uint32_t ws[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {           // 16-byte chunk c of this half: 8 weights
+                uint4 hi, lo;
+                split2(scale * qb<0>(ws[2 * c]), scale * qb<1>(ws[2 * c]), &hi.x, &lo.x);
+                split2(scale * qb<2>(ws[2 * c]), scale * qb<3>(ws[2 * c]), &hi.y, &lo.y);
+                split2(scale * qb<0>(ws[2 * c + 1]), scale * qb<1>(ws[2 * c + 1]), &hi.z, &lo.z);
+                split2(scale * qb<2>(ws[2 * c + 1]), scale * qb<3>(ws[2 * c + 1]), &hi.w, &lo.w);
+                const int chunk = ((half * 4 + c) ^ (row & 7)) * 16;   // 128-byte swizzle
+                *(uint4*)(bhi + chunk) = hi;
+                *(uint4*)(blo + chunk) = lo;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> tensor-core reads
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->full_b[s]);
+        }
+        // ---------------------------------------------------------------- epilogue (warps 0-3)
+        if (warp < 4 && ok && wait_bar(bars, &bars->acc_full, 0, a.status)) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int m = m0 + warp * 32 + lane;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c * 32);
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                    "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                      "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                      "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                      "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                    : "r"(taddr) : "memory");
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (m < a.M) {
+                    const int nb = n0 + c * 32;
+                    float* yr = a.y + (size_t)m * a.ldy + nb;
+                    const float* rr = a.residual ? a.residual + (size_t)m * a.ldy + nb : nullptr;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        if (nb + i < a.N) {
+                            float v = __uint_as_float(r[i]);
+                            if (a.bias) v += a.bias[nb + i];
+                            if (a.epi == EPI_GELU) v = gelu_f(v);
+                            if (rr) v = rr[i] + v;
+                            yr[i] = v;
+                        }
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == DQ_WARPS + 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)TMEM_COLS) : "memory");
+    }
+}
+
+// x[n] -> bf16 hi, lo planes with x = hi + lo to 2^-17 relative.
+__global__ void split_bf16_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ hi, __nv_bfloat16* __restrict__ lo, size_t n4) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+        const float4 v = ((const float4*)x)[i];
+        uint2 h, l;
+        split2(v.x, v.y, &h.x, &l.x);
+        split2(v.z, v.w, &h.y, &l.y);
+        ((uint2*)hi)[i] = h;
+        ((uint2*)lo)[i] = l;
+    }
+}
+
+int launch_split_bf16(const float* x, void* hi, void* lo, size_t n, cudaStream_t st) {
+    if (n % 4) return fail(FC_E_SHAPE, "split_bf16: element count %zu is not a multiple of 4", n);
+    const size_t n4 = n / 4;
+    const int blocks = (int)((n4 + 255) / 256 < 148 * 8 ? (n4 + 255) / 256 : 148 * 8);
+    split_bf16_kernel<<<blocks > 0 ? blocks : 1, 256, 0, st>>>(x, (__nv_bfloat16*)hi, (__nv_bfloat16*)lo, n4);
+    FC_LAUNCHED();
+    return FC_OK;
+}
+
+namespace {
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int encode_plane(CUtensorMap* map, const void* plane, int M, int K) {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        FC_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q));
+        if (!p || q != cudaDriverEntryPointSuccess) return fail(FC_E_CUDA, "cuTensorMapEncodeTiled is not available");
+        fn = (EncodeTiledFn)p;
+    }
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
+    const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)BM};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)plane, dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(FC_E_CUDA, "cuTensorMapEncodeTiled failed (%d) for a [%d][%d] bf16 plane", (int)r, M, K);
+    return FC_OK;
+}
+}  // namespace
+
+// x_hi / x_lo: bf16 planes [M][K] (16-byte aligned). status: device int, raised on timeout.
+int launch_gemm_q8_bf16x3(const QMat& w, const void* x_hi, const void* x_lo, const float* bias, const float* residual,
+                          int epi, float* y, int M, int ldy, int* status, cudaStream_t st) {
+    if (w.K % BK) return fail(FC_E_SHAPE, "the tensor-core GEMM needs K %% 64 == 0 (K = %d)", w.K);
+    static bool attr_set[64] = {};
+    int dev = 0;
+    FC_CUDA(cudaGetDevice(&dev));
+    if (dev < 64 && !attr_set[dev]) {
+        FC_CUDA(cudaFuncSetAttribute(gemm_q8_bf16x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        attr_set[dev] = true;
+    }
+    CUtensorMap mh, ml;
+    FC_TRY(encode_plane(&mh, x_hi, M, w.K));
+    FC_TRY(encode_plane(&ml, x_lo, M, w.K));
+    TcArgs a;
+    a.qu = w.qu; a.d = w.d; a.N = w.N; a.K = w.K;
+    a.bias = bias; a.residual = residual; a.epi = epi;
+    a.y = y; a.M = M; a.ldy = ldy; a.status = status;
+    dim3 grid((w.N + BN - 1) / BN, (M + BM - 1) / BM);
+    gemm_q8_bf16x3_kernel<<<grid, THREADS, SMEM_BYTES, st>>>(mh, ml, a);
+    FC_LAUNCHED();
+    return FC_OK;
+}
+
+}  // namespace fc

@@ -246,3 +246,43 @@ def test_small_scoring_is_batch_invariant_and_causal(small):
     ids2[1, 600:] = synth.token_ids(2, 424, V)
     _, lpb = gm.score_sequences(ids2[1:2], batch_windows=1)
     assert np.array_equal(lpb[0, :600], lp1[0, :600]) and not np.array_equal(lpb[0, 600:], lp1[0, 600:])
+
+
+# ---- tensor-core math mode (bf16 3-term split on tcgen05) ----------------------------------
+@pytest.mark.parametrize("m,k,n", [(2, 64, 96), (129, 192, 257), (128, 768, 128), (512, 768, 3072), (300, 3072, 768)])
+def test_q8_0_linear_bf16x3_matches_engine(m, k, n):
+    w = O.fill_normal(21, n * k, 0.02)
+    wq = synth.q8_0_quantize(w)
+    x = O.fill_normal(22, m * k, 1.0).reshape(m, k)
+    bias = O.fill_normal(23, n, 0.5)
+    want = O.linear(x, O.expand_kn(wq, n, k), bias, threads=8)
+    got = fcb.q8_0_linear(x, wq, bias, n, math_mode=fcb.FC_MATH_BF16X3)
+    scale = np.abs(want).max()
+    err = np.abs(got - want).max()
+    assert err <= 1e-4 * scale, f"max abs err {err:.3e} vs scale {scale:.3e}"
+    # the fp32 CUDA-core kernel is the yardstick: both modes agree far inside the tolerance
+    got32 = fcb.q8_0_linear(x, wq, bias, n, math_mode=fcb.FC_MATH_FP32)
+    assert np.abs(got - got32).max() <= 1e-4 * scale
+
+
+def test_scoring_bf16x3_tiny_matches_golden():
+    g = np.load(os.path.join(GOLD, "score_tiny.npz"))
+    sm = synth.named("tiny", seed=0, math_mode=fcb.FC_MATH_BF16X3)
+    gm = fcb.CudaSlm(sm.config, sm.weights)
+    scores, lp = gm.score_sequences(g["ids"], batch_windows=4)
+    assert np.abs(lp - g["logprob"]).max() < LOGPROB_TOL
+    assert np.array_equal(lp, gm.score_sequences(g["ids"], batch_windows=4)[1]), "run-to-run determinism"
+    gm.close()
+
+
+def test_scoring_bf16x3_small_matches_golden():
+    path = os.path.join(GOLD, "score_small.npz")
+    if not os.path.exists(path):
+        pytest.skip("score_small.npz has not been generated")
+    g = np.load(path)
+    sm = synth.named("small", seed=0, math_mode=fcb.FC_MATH_BF16X3)
+    gm = fcb.CudaSlm(sm.config, sm.weights)
+    scores, lp = gm.score_sequences(g["ids"], batch_windows=4)
+    err = np.abs(lp - g["logprob"]).max()
+    assert err < LOGPROB_TOL, f"max abs log-prob error {err:.3e}"
+    gm.close()
