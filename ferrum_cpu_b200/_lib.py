@@ -48,6 +48,7 @@ SIGNATURES = {
     "fc_qweight_upload": (C.c_int, [C.c_int, C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_void_p)]),
     "fc_qweight_free": (None, [C.c_void_p]),
     "fc_q8_0_linear_dev": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
+    "fc_q8_0_linear_dev_noalloc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.POINTER(C.c_int)]),
     "fc_model_create": (C.c_int, [C.POINTER(FcConfig), C.POINTER(FcWeights), C.c_int, C.POINTER(C.c_void_p)]),
     "fc_model_free": (None, [C.c_void_p]),
     "fc_model_config": (C.c_int, [C.c_void_p, C.POINTER(FcConfig)]),

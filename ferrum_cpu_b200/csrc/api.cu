@@ -115,6 +115,13 @@ struct fc_qweight {
     size_t plane_elems = 0;
 };
 
+namespace fc {
+const QMat* qweight_matrix(const fc_qweight* w, int* device) {
+    *device = w->device;
+    return &w->w;
+}
+}  // namespace fc
+
 struct fc_model {
     fc_config cfg;
     int device;

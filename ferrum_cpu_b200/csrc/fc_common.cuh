@@ -94,6 +94,9 @@ int launch_split_bf16(const float* x, void* hi, void* lo, size_t n, cudaStream_t
 int launch_gemm_q8_bf16x3(const QMat& w, const void* x_hi, const void* x_lo, const float* bias, const float* residual,
                           int epi, float* y, int M, int ldy, int* status, cudaStream_t st);
 
+// api.cu — the matrix and device behind a resident-weight handle.
+const QMat* qweight_matrix(const fc_qweight* w, int* device);
+
 // rowops.cu
 int launch_embed_step(const QMat& tok, const float* pos_emb, int ctx, const int* queue, StepState* state,
                       float* x, cudaStream_t st);

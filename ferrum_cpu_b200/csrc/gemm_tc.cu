@@ -344,3 +344,62 @@ int launch_gemm_q8_bf16x3(const QMat& w, const void* x_hi, const void* x_lo, con
 }
 
 }  // namespace fc
+
+// =====================================================================================
+// The allocation-free variant of the tensor-core linear
+// =====================================================================================
+// fc_q8_0_linear_dev needs scratch in global memory (the two bf16 planes the activations are
+// split into, and a status word) and grows it with cudaMalloc. Here the same scratch is a
+// file-scope device array of fixed size, so the call allocates nothing at all.
+namespace {
+constexpr size_t kStaticPlaneElems = (size_t)4 << 20;   // activations per call: M * K <= 4 Mi
+// [hi plane | lo plane], 16 MiB per GPU that loads the library, held until the process exits.
+static __device__ __align__(256) uint16_t g_noalloc_planes[2 * kStaticPlaneElems];
+static __device__ __align__(256) int g_noalloc_status;
+
+// Device addresses of the two arrays above, looked up once per device. In host code the names
+// g_noalloc_planes / g_noalloc_status are only handles for cudaGetSymbolAddress: passing
+// them to a kernel directly would hand it a host address.
+struct NoAllocScratch {
+    uint16_t* planes = nullptr;
+    int* status = nullptr;
+};
+NoAllocScratch g_noalloc_dev[64];
+}  // namespace
+
+extern "C" int fc_q8_0_linear_dev_noalloc(const fc_qweight* w, const float* x_dev, const float* bias_dev, float* y_dev,
+                                          int M, void* cuda_stream, int* timed_out) {
+    using namespace fc;
+    if (!w || !x_dev || !y_dev) return fail(FC_E_ARG, "fc_q8_0_linear_dev_noalloc: null argument");
+    if (M <= 0) return fail(FC_E_SHAPE, "fc_q8_0_linear_dev_noalloc: M = %d", M);
+    int device = 0;
+    const QMat* mat = qweight_matrix(w, &device);
+    if (mat->K % 64) return fail(FC_E_SHAPE, "fc_q8_0_linear_dev_noalloc: K = %d is not a multiple of 64", mat->K);
+    if ((size_t)M * mat->K > kStaticPlaneElems)
+        return fail(FC_E_SHAPE, "fc_q8_0_linear_dev_noalloc: M * K = %zu exceeds the fixed scratch of %zu activations; "
+                    "split the rows over several calls or use fc_q8_0_linear_dev", (size_t)M * mat->K, kStaticPlaneElems);
+    if (device < 0 || device >= 64) return fail(FC_E_ARG, "fc_q8_0_linear_dev_noalloc: device %d out of range", device);
+    FC_CUDA(cudaSetDevice(device));
+    NoAllocScratch& sc = g_noalloc_dev[device];
+    if (!sc.planes) {
+        // set-up, first call on this device: resolve the device addresses of the static arrays
+        void *p = nullptr, *s = nullptr;
+        FC_CUDA(cudaGetSymbolAddress(&p, g_noalloc_planes));
+        FC_CUDA(cudaGetSymbolAddress(&s, g_noalloc_status));
+        sc.planes = (uint16_t*)p;
+        sc.status = (int*)s;
+    }
+    cudaStream_t st = (cudaStream_t)cuda_stream;
+    // the status word keeps whatever the previous call left in it: start from zero
+    FC_CUDA(cudaMemsetAsync(sc.status, 0, sizeof(int), st));
+    uint16_t* hi = sc.planes;
+    uint16_t* lo = sc.planes + kStaticPlaneElems;
+    FC_TRY(launch_split_bf16(x_dev, hi, lo, (size_t)M * mat->K, st));
+    FC_TRY(launch_gemm_q8_bf16x3(*mat, hi, lo, bias_dev, nullptr, EPI_NONE, y_dev, M, mat->N, sc.status, st));
+    if (timed_out) {
+        FC_CUDA(cudaMemcpyAsync(timed_out, sc.status, sizeof(int), cudaMemcpyDeviceToHost, st));
+        FC_CUDA(cudaStreamSynchronize(st));
+        if (*timed_out != 0) return fail(FC_E_TIMEOUT, "a bounded wait inside the tensor-core GEMM ran out (status %d)", *timed_out);
+    }
+    return FC_OK;
+}

@@ -62,6 +62,13 @@ class QWeight:
     def linear_dev(self, x_dev_ptr, bias_dev_ptr, y_dev_ptr, m, math_mode=_lib.FC_MATH_FP32, stream=None):
         check(_lib.lib().fc_q8_0_linear_dev(self._h, x_dev_ptr, bias_dev_ptr, y_dev_ptr, m, math_mode, stream))
 
+    def linear_dev_noalloc(self, x_dev_ptr, bias_dev_ptr, y_dev_ptr, m, stream=None, wait=True):
+        """The tensor-core linear out of the library's fixed scratch array: no device allocation.
+        M * K <= 4 Mi; calls that can overlap on the GPU race on the shared scratch."""
+        status = C.c_int(0)
+        check(_lib.lib().fc_q8_0_linear_dev_noalloc(self._h, x_dev_ptr, bias_dev_ptr, y_dev_ptr, m, stream,
+                                                    C.byref(status) if wait else None))
+
     def close(self):
         if self._h:
             _lib.lib().fc_qweight_free(self._h)

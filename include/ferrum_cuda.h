@@ -107,6 +107,34 @@ void fc_qweight_free(fc_qweight* w);
 int fc_q8_0_linear_dev(const fc_qweight* w, const float* x_dev, const float* bias_dev, float* y_dev,
                        int M, int math_mode, void* cuda_stream);
 
+/* The same product as fc_q8_0_linear_dev in FC_MATH_BF16X3, for callers that must not
+ * allocate device memory. No counterpart in the reference (it never leaves the host heap).
+ *
+ * Who needs it: a serving loop that handed all free device memory to its own pool at
+ * start-up, so a cudaMalloc inside the library would fail; or a latency-critical thread that
+ * cannot afford cudaMalloc taking the driver's allocation lock and synchronising with other
+ * work on the device. fc_q8_0_linear_dev grows its scratch (the two bf16 planes the
+ * activations are split into, plus a status word) with cudaMalloc on demand; this entry point
+ * keeps that scratch in a fixed array inside the library instead and calls no cudaMalloc,
+ * cudaFree or allocating library routine.
+ *
+ * Limits and rules:
+ *  - M * K <= 4 194 304 activations per call (FC_E_SHAPE beyond that: split the rows over
+ *    several calls, or use fc_q8_0_linear_dev); K % 64 == 0; the weight handle is uploaded
+ *    beforehand with fc_qweight_upload (which does allocate);
+ *  - the array is 16 MiB and every GPU that loads the library holds it until the process exits;
+ *  - the first call on a device looks up the array's device address; make that first call
+ *    before any stream capture;
+ *  - all calls on a device share the one array: two calls whose kernels can overlap on the
+ *    GPU (different streams, no ordering between them) race on it. Issue them on one stream
+ *    or order them with events;
+ *  - x_dev, bias_dev (may be NULL) and y_dev are device pointers on the weight's GPU; the
+ *    caller still provides input and output.
+ * timed_out: NULL for a fully asynchronous call; otherwise the call waits for the stream and
+ * stores the kernel's status word there (0, or FC_E_TIMEOUT, which is then also returned). */
+int fc_q8_0_linear_dev_noalloc(const fc_qweight* w, const float* x_dev, const float* bias_dev, float* y_dev,
+                               int M, void* cuda_stream, int* timed_out);
+
 /* ---- model ------------------------------------------------------------------------ */
 /* Validates as loader/gpt2.rs + loader/mod.rs:147-154 (d % n_head == 0, K % 32 == 0),
  * uploads and repacks the weights on `device`. */
