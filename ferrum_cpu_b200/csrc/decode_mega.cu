@@ -59,7 +59,8 @@ constexpr int OFF_SC = OFF_XS + MAX_D * 4;                       // attention sc
 constexpr int OFF_PSUM = OFF_SC + MAX_CTX * 4;                   // 2 x 256 partial sums
 constexpr int OFF_RED = OFF_PSUM + 2 * 256 * 4;                  // reductions
 constexpr int OFF_LAYERS = OFF_RED + 256 * 4;                    // copy of the layer table
-constexpr int OFF_CTRL = OFF_LAYERS + kMegaMaxLayers * (int)sizeof(MegaLayer);
+constexpr int OFF_WORK = OFF_LAYERS + kMegaMaxLayers * (int)sizeof(MegaLayer);   // 5 work descriptors
+constexpr int OFF_CTRL = OFF_WORK + 256;
 constexpr int SMEM_BYTES = OFF_CTRL + (int)sizeof(Ctrl);
 static_assert(MAX_ROWS_HEAD <= MAX_CTX, "head slice shares the score buffer");
 static_assert(sizeof(MegaLayer) % 16 == 0, "layer table entries are copied as 16-byte words");
@@ -77,13 +78,15 @@ __device__ __forceinline__ void mbar_expect_tx(unsigned long long* b, uint32_t b
 __device__ __forceinline__ void mbar_arrive(unsigned long long* b) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s32(b)) : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(unsigned long long* b, uint32_t parity) {
+// Tests the phase; a thread that finds it incomplete is suspended by the hardware until the
+// phase completes or `hint_ns` pass, so a waiting warp does not burn issue slots.
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long* b, uint32_t parity, uint32_t hint_ns = 2000) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(s32(b)), "r"(parity) : "memory");
+        : "=r"(ok) : "r"(s32(b)), "r"(parity), "r"(hint_ns) : "memory");
     return ok != 0;
 }
 // 1-D bulk copy global -> shared; both addresses 16-byte aligned, bytes % 16 == 0.
@@ -105,6 +108,45 @@ __device__ __forceinline__ int rows_per_item(int K) {
     const int g = mega_row_gran(K);
     int r = min(SLOT_Q / K, 256);      // 256 = partial-sum slots per item
     return r - r % g;
+}
+
+// This CTA's share of one kind of matrix (qkv, out, up, down, head), worked out once per
+// launch: the integer divisions behind it are too slow for every phase's critical path.
+struct Work {
+    int r0, r1;        // owned rows
+    int rpi;           // rows per ring item
+    int gran;          // row granularity of a bulk copy
+    int iters;         // 16-lane sweeps per row
+    int ks_full;       // K split of an item of rpi rows
+    int ks_last;       // K split of the last (shorter) item
+    int pad;
+};
+enum { W_QKV = 0, W_OUT = 1, W_UP = 2, W_DOWN = 3, W_HEAD = 4, W_KINDS = 5 };
+
+// Split K over several half warps when an item has few rows: the split with the fewest
+// sweeps on the critical path (rounds over the 32 half warps x sweeps per unit).
+__device__ int pick_ksplit(int rows, int iters) {
+    int ksplit = 1, best = ((rows + 31) >> 5) * iters;
+    const int cand[7] = {2, 3, 4, 6, 8, 12, 16};
+    for (int i = 0; i < 7; ++i) {
+        const int ks = cand[i];
+        if (iters % ks == 0 && rows * ks <= 128) {
+            const int cost = ((rows * ks + 31) >> 5) * (iters / ks);
+            if (cost < best) { best = cost; ksplit = ks; }
+        }
+    }
+    return ksplit;
+}
+__device__ void make_work(Work* w, int N, int K, int c, int G) {
+    mega_cta_rows(N, K, c, G, &w->r0, &w->r1);
+    w->rpi = rows_per_item(K);
+    w->gran = mega_row_gran(K);
+    w->iters = max(1, K >> 8);
+    const int n = w->r1 - w->r0;
+    const int last = n > 0 ? n - ((n - 1) / w->rpi) * w->rpi : 0;
+    w->ks_full = pick_ksplit(w->rpi, w->iters);
+    w->ks_last = last > 0 ? pick_ksplit(last, w->iters) : 1;
+    w->pad = 0;
 }
 
 template <int B>
@@ -133,6 +175,7 @@ struct Cta {
     unsigned char* smem;
     Ctrl* ctrl;
     const MegaLayer* layers;   // shared-memory copy of the layer table
+    const Work* work;          // shared-memory work descriptors, one per matrix kind
     float4* act4;
     float* act;
     float* xs;
@@ -177,13 +220,12 @@ __device__ bool producer_wait(Cta& k, unsigned long long* bar, uint32_t parity) 
 }
 
 // Issues the bulk copies of one matrix share. Returns false when told to stop.
-__device__ bool produce_matrix(Cta& k, const QMat& w) {
-    int r0, r1;
-    mega_cta_rows(w.N, w.K, k.c, k.G, &r0, &r1);
-    const int rpi = rows_per_item(w.K), g = mega_row_gran(w.K);
+__device__ bool produce_matrix(Cta& k, const QMat& w, int kind) {
+    const Work wk = k.work[kind];
+    const int r0 = wk.r0, r1 = wk.r1, rpi = wk.rpi, g = wk.gran;
     for (int r = r0; r < r1; r += rpi) {
         const int rows = min(rpi, r1 - r);
-        const int rows_c = (rows + g - 1) / g * g;          // padded rows exist up to N_pad
+        const int rows_c = (rows + g - 1) & ~(g - 1);       // g is a power of two; padded rows exist up to N_pad
         const int slot = k.item % SLOTS;
         if (!producer_wait(k, &k.ctrl->empty[slot], ((k.item / SLOTS) & 1) ^ 1)) return false;
         const uint32_t qb = (uint32_t)rows_c * w.K, db = qb >> 4;
@@ -213,10 +255,12 @@ __device__ void producer(Cta& k) {
         for (int l = 0; l < p.L; ++l) {
             const MegaLayer& L = k.layers[l];
             if (!produce_params(k, L.lnpack, L.biaspack)) return;
-            if (!produce_matrix(k, L.qkv) || !produce_matrix(k, L.out) || !produce_matrix(k, L.up) || !produce_matrix(k, L.down)) return;
+            if (!produce_matrix(k, L.qkv, W_QKV) || !produce_matrix(k, L.out, W_OUT) || !produce_matrix(k, L.up, W_UP) ||
+                !produce_matrix(k, L.down, W_DOWN))
+                return;
         }
         if (step >= p.head_from) {
-            if (!produce_params(k, p.lnfpack, nullptr) || !produce_matrix(k, p.head)) return;
+            if (!produce_params(k, p.lnfpack, nullptr) || !produce_matrix(k, p.head, W_HEAD)) return;
         }
     }
 }
@@ -247,17 +291,33 @@ __device__ float cmax(Cta& k, float v) {
 }
 
 // layer/norm.rs:46-82 on xs[0..d) -> act (swizzled); g, b in shared memory.
+// Two-level reductions: each thread owns elements tid and tid + 512, each warp leaves one
+// partial per statistic in shared memory, every thread adds the 16 partials in the same order.
 __device__ void layernorm_to_act(Cta& k, const float* g, const float* b) {
-    const int d = k.p.d;
-    const float v0 = k.tid < d ? k.xs[k.tid] : 0.0f;
-    const float v1 = k.tid + CONSUMERS < d ? k.xs[k.tid + CONSUMERS] : 0.0f;
-    const float mean = csum(k, v0 + v1) / (float)d;
+    const int d = k.p.d, lane = k.tid & 31, wid = k.tid >> 5;
+    const bool h0 = k.tid < d, h1 = k.tid + CONSUMERS < d;
+    const float v0 = h0 ? k.xs[k.tid] : 0.0f, v1 = h1 ? k.xs[k.tid + CONSUMERS] : 0.0f;
+    float s = v0 + v1;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) k.red[wid] = s;
+    consumer_sync();
+    float tot = 0.0f;
+#pragma unroll
+    for (int w = 0; w < CWARPS; ++w) tot += k.red[w];
+    const float mean = tot / (float)d;
     const float t0 = v0 - mean, t1 = v1 - mean;
-    const float q = (k.tid < d ? t0 * t0 : 0.0f) + (k.tid + CONSUMERS < d ? t1 * t1 : 0.0f);
-    const float var = csum(k, q) / (float)d;
-    const float sd = sqrtf(var + 1e-5f);
-    if (k.tid < d) k.act[act_index(k.tid)] = (t0 / sd) * g[k.tid] + b[k.tid];
-    if (k.tid + CONSUMERS < d) k.act[act_index(k.tid + CONSUMERS)] = (t1 / sd) * g[k.tid + CONSUMERS] + b[k.tid + CONSUMERS];
+    float q = (h0 ? t0 * t0 : 0.0f) + (h1 ? t1 * t1 : 0.0f);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) q += __shfl_xor_sync(0xffffffffu, q, o);
+    if (lane == 0) k.red[CWARPS + wid] = q;
+    consumer_sync();
+    float qt = 0.0f;
+#pragma unroll
+    for (int w = 0; w < CWARPS; ++w) qt += k.red[CWARPS + w];
+    const float sd = sqrtf(qt / (float)d + 1e-5f);
+    if (h0) k.act[act_index(k.tid)] = (t0 / sd) * g[k.tid] + b[k.tid];
+    if (h1) k.act[act_index(k.tid + CONSUMERS)] = (t1 / sd) * g[k.tid + CONSUMERS] + b[k.tid + CONSUMERS];
     consumer_sync();
 }
 
@@ -280,9 +340,13 @@ __device__ bool grid_barrier(Cta& k) {
     if (k.tid == 0) {
         red_release_add(k.p.bar, 1u);
         const long long t0 = clock64();
+        unsigned polls = 0;
         while ((int)(ld_acquire(k.p.bar) - k.bar_target) < 0) {
-            if (*(volatile int*)k.p.status != 0) { k.ctrl->abort = 1; break; }
-            if (timed_out(t0)) { raise_timeout(k); break; }
+            // the status word and the clock are only looked at every 64 polls
+            if ((++polls & 63u) == 0) {
+                if (*(volatile int*)k.p.status != 0) { k.ctrl->abort = 1; break; }
+                if (timed_out(t0)) { raise_timeout(k); break; }
+            }
         }
     }
     consumer_sync();
@@ -292,39 +356,25 @@ __device__ bool grid_barrier(Cta& k) {
 // Consumes this CTA's share of matrix w against the activation in act; epi(n, i, value) is
 // called once per owned output row n (i = n - first owned row) by one thread.
 template <class Epi>
-__device__ bool consume_matrix(Cta& k, const QMat& w, Epi epi) {
-    int r0, r1;
-    mega_cta_rows(w.N, w.K, k.c, k.G, &r0, &r1);
-    const int K = w.K, rpi = rows_per_item(K), chunks = K >> 4, kb_row = K >> 5;
-    const int iters = max(1, chunks >> 4);            // 16-lane sweeps per row
+__device__ bool consume_matrix(Cta& k, const QMat& w, int kind, Epi epi) {
+    const Work wk = k.work[kind];
+    const int r0 = wk.r0, r1 = wk.r1, rpi = wk.rpi, iters = wk.iters;
+    const int K = w.K, chunks = K >> 4, kb_row = K >> 5;
     const int hw = k.tid >> 4, hl = k.tid & 15;
     const unsigned hmask = 0xFFFFu << (k.tid & 16);
     for (int r = r0; r < r1; r += rpi) {
         const int rows = min(rpi, r1 - r);
-        // split K over several half warps when an item has few rows: pick the split with the
-        // fewest sweeps on the critical path (rounds over the 32 half warps x sweeps per unit)
-        int ksplit = 1, best_cost = ((rows + 31) >> 5) * iters;
-        {
-            const int cand[7] = {2, 3, 4, 6, 8, 12, 16};
-#pragma unroll
-            for (int i = 0; i < 7; ++i) {
-                const int ks = cand[i];
-                if (iters % ks == 0 && rows * ks <= 128) {
-                    const int cost = ((rows * ks + 31) >> 5) * (iters / ks);
-                    if (cost < best_cost) { best_cost = cost; ksplit = ks; }
-                }
-            }
-        }
+        const int ksplit = rows == rpi ? wk.ks_full : wk.ks_last;   // K split over half warps
         const int slot = k.item % SLOTS;
-        mark(k);
         if (!consumer_wait(k, &k.ctrl->full[slot], (k.item / SLOTS) & 1)) return false;
-        mark(k);
         const unsigned char* q = k.slot_q(slot);
         const __half* ds = k.slot_d(slot);
         float* ps = k.psum + (k.item & 1) * 256;
         const int units = rows * ksplit, per = iters / ksplit;
+        // unit u = (row, part); the first unit's quotient is the only division
+        int row = hw / ksplit, part = hw - row * ksplit;
+        const int drow = (CONSUMERS / 16) / ksplit, dpart = (CONSUMERS / 16) - drow * ksplit;
         for (int u = hw; u < units; u += CONSUMERS / 16) {
-            const int row = u / ksplit, part = u - row * ksplit;
             float acc = 0.0f;
             for (int i = part * per; i < (part + 1) * per; ++i) {
                 const int cc = i * 16 + hl;
@@ -339,10 +389,11 @@ __device__ bool consume_matrix(Cta& k, const QMat& w, Epi epi) {
             acc += __shfl_xor_sync(hmask, acc, 2);
             acc += __shfl_xor_sync(hmask, acc, 1);
             if (hl == 0) ps[u] = acc;
+            part += dpart;
+            row += drow;
+            if (part >= ksplit) { part -= ksplit; row += 1; }
         }
-        mark(k);
         consumer_sync();                                   // slot fully read, partial sums visible
-        mark(k);
         if ((k.tid & 31) == 0) mbar_arrive(&k.ctrl->empty[slot]);
         for (int row = k.tid; row < rows; row += CONSUMERS) {
             float v = 0.0f;
@@ -354,124 +405,123 @@ __device__ bool consume_matrix(Cta& k, const QMat& w, Epi epi) {
     return true;
 }
 
+// CTAs per head for a context of `len` keys: about 64 keys per CTA, at most attn_splits. Fewer
+// partials mean fewer loads of the same lines by every CTA in the combine phase.
+__device__ __forceinline__ int attn_splits_for(const MegaParams& p, int len) {
+    return max(1, min(p.attn_splits, (len + 63) >> 6));
+}
+
 // transformer.rs:246-283 split over CTAs: CTA (h, s) handles keys [s*len/S, (s+1)*len/S) of
-// head h and writes (max, sum-exp, unnormalised out[hd]) to partg.
+// head h and writes (max, sum-exp, unnormalised out[hd]) to partg. Inside the CTA every warp
+// runs an online softmax over its own keys (no CTA-wide synchronisation while keys are
+// processed); the 16 warp partials are combined once at the end in a fixed order.
 __device__ void attention_partial(Cta& k, int l, int len) {
     const MegaParams& p = k.p;
-    const int S = p.attn_splits, hd = p.d / p.H;
+    const int S = attn_splits_for(p, len), hd = p.d / p.H;
     if (k.c >= p.H * S) return;
     const int h = k.c / S, s = k.c - h * S, hs = h * hd;
     const int j0 = (int)((long long)s * len / S), j1 = (int)((long long)(s + 1) * len / S);
-    const float* kc = p.kc + (size_t)l * p.T * p.d;
-    const float* vc = p.vc + (size_t)l * p.T * p.d;
+    const float* kc = p.kc + (size_t)l * p.T * p.d + hs;
+    const float* vc = p.vc + (size_t)l * p.T * p.d + hs;
     float* out = p.partg + (size_t)k.c * (hd + 2);
     const int lane = k.tid & 31, wid = k.tid >> 5;
-    // each lane owns head dimensions lane and lane + 32 (hd <= 64); a warp takes 4 keys per
-    // sweep with all of their loads (and the query's) in flight together
+    // each lane owns head dimensions lane and lane + 32 (hd <= 64)
     const bool has0 = lane < hd, has1 = lane + 32 < hd;
     const float q0 = has0 ? __ldcg(p.qg + hs + lane) : 0.0f;
     const float q1 = has1 ? __ldcg(p.qg + hs + lane + 32) : 0.0f;
-    // the values of the first 8 keys of this thread's group are requested now, so that their
-    // latency overlaps the score phase: thread (g, cc) owns keys j0 + g, j0 + g + groups, ...
-    const int groups = CONSUMERS / hd, g = k.tid / hd, cc = k.tid - g * hd;
-    float vpre[8];
-#pragma unroll
-    for (int u = 0; u < 8; ++u) {
-        const int j = j0 + g + u * groups;
-        vpre[u] = (g < groups && j < j1) ? __ldcg(vc + (size_t)j * p.d + hs + cc) : 0.0f;
-    }
     const float scale = 1.0f / sqrtf((float)hd);
-    float mx = -INFINITY;
-    for (int jb = j0 + wid * 4; jb < j1; jb += CWARPS * 4) {
-        float a0[4], a1[4];
+    float m = -INFINITY, lsum = 0.0f, o0 = 0.0f, o1 = 0.0f;
+    // warp wid owns keys j0 + wid, j0 + wid + 16, ...; four keys per sweep, whose K and V rows
+    // are all requested before the first use
+    for (int jb = j0 + wid; jb < j1; jb += CWARPS * 4) {
+        float a0[4], a1[4], v0[4], v1[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-            const float* kr = kc + (size_t)(jb + u) * p.d + hs;
-            const bool on = jb + u < j1;
-            a0[u] = (on && has0) ? __ldcg(kr + lane) : 0.0f;
-            a1[u] = (on && has1) ? __ldcg(kr + lane + 32) : 0.0f;
+            const int j = jb + u * CWARPS;
+            const bool on = j < j1;
+            const size_t off = (size_t)j * p.d;
+            a0[u] = (on && has0) ? __ldcg(kc + off + lane) : 0.0f;
+            a1[u] = (on && has1) ? __ldcg(kc + off + lane + 32) : 0.0f;
+            v0[u] = (on && has0) ? __ldcg(vc + off + lane) : 0.0f;
+            v1[u] = (on && has1) ? __ldcg(vc + off + lane + 32) : 0.0f;
         }
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-            float dot = fmaf(q1, a1[u], q0 * a0[u]);
+            if (jb + u * CWARPS < j1) {                 // warp-uniform
+                float dot = fmaf(q1, a1[u], q0 * a0[u]);
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-            if (jb + u < j1) {
+                for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
                 const float sv = dot * scale;
-                if (lane == 0) k.sc[jb + u - j0] = sv;
-                mx = fmaxf(mx, sv);
+                const float mn = fmaxf(m, sv);
+                const float corr = expf(m - mn);        // m == -inf: 0
+                const float pj = expf(sv - mn);
+                lsum = fmaf(lsum, corr, pj);
+                o0 = fmaf(o0, corr, pj * v0[u]);
+                o1 = fmaf(o1, corr, pj * v1[u]);
+                m = mn;
             }
         }
     }
-    mx = cmax(k, mx);
-    float e = 0.0f;
-    for (int j = j0 + k.tid; j < j1; j += CONSUMERS) {
-        const float t = expf(k.sc[j - j0] - mx);
-        k.sc[j - j0] = t;
-        e += t;
-    }
-    const float sum = csum(k, e);                 // includes the sync that publishes sc[]
-    // out[c] = sum_j e_j v[j][c], then a fixed-order combine of the groups
-    float acc = 0.0f;
-    if (g < groups) {
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            const int j = j0 + g + u * groups;
-            if (j < j1) acc = fmaf(k.sc[j - j0], vpre[u], acc);
-        }
-        for (int jb = j0 + g + 8 * groups; jb < j1; jb += groups * 8) {
-            float vv[8];
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const int j = jb + u * groups;
-                vv[u] = j < j1 ? __ldcg(vc + (size_t)j * p.d + hs + cc) : 0.0f;
-            }
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const int j = jb + u * groups;
-                if (j < j1) acc = fmaf(k.sc[j - j0], vv[u], acc);
-            }
-        }
-    }
-    consumer_sync();
-    float* part = k.act;                          // act is free during the attention phase
-    if (g < groups) part[g * hd + cc] = acc;
+    float* part = k.act;                                // act is free during the attention phase
+    float* mine = part + wid * 66;
+    if (lane == 0) { mine[0] = m; mine[1] = lsum; }
+    mine[2 + lane] = o0;
+    mine[2 + 32 + lane] = o1;
     consumer_sync();
     if (k.tid < hd) {
-        float t = 0.0f;
-        for (int gg = 0; gg < groups; ++gg) t += part[gg * hd + k.tid];
-        out[2 + k.tid] = t;
-    }
-    if (k.tid == 0) { out[0] = mx; out[1] = sum; }
-}
-
-// Combines the S partials of every head into the attention output, written to act.
-__device__ void attention_combine(Cta& k) {
-    const MegaParams& p = k.p;
-    const int S = p.attn_splits, hd = p.d / p.H;
-    for (int t = k.tid; t < p.d; t += CONSUMERS) {
-        const int h = t / hd, cc = t - h * hd;
-        const float* base = p.partg + (size_t)h * S * (hd + 2);
-        // all loads are issued before any use so that they overlap (S <= 8)
-        float ms[8], ls[8], os[8];
-#pragma unroll
-        for (int s = 0; s < 8; ++s) {
-            const bool on = s < S;
-            ms[s] = on ? __ldcg(base + s * (hd + 2)) : -INFINITY;
-            ls[s] = on ? __ldcg(base + s * (hd + 2) + 1) : 0.0f;
-            os[s] = on ? __ldcg(base + s * (hd + 2) + 2 + cc) : 0.0f;
-        }
         float M = -INFINITY;
 #pragma unroll
-        for (int s = 0; s < 8; ++s) M = fmaxf(M, ms[s]);
+        for (int w = 0; w < CWARPS; ++w) M = fmaxf(M, part[w * 66]);
         float Lsum = 0.0f, O = 0.0f;
 #pragma unroll
-        for (int s = 0; s < 8; ++s) {
-            const float f = ms[s] > -INFINITY ? expf(ms[s] - M) : 0.0f;
-            Lsum = fmaf(ls[s], f, Lsum);
-            O = fmaf(os[s], f, O);
+        for (int w = 0; w < CWARPS; ++w) {
+            const float mw = part[w * 66];
+            const float f = mw > -INFINITY ? expf(mw - M) : 0.0f;
+            Lsum = fmaf(part[w * 66 + 1], f, Lsum);
+            O = fmaf(part[w * 66 + 2 + k.tid], f, O);
         }
-        k.act[act_index(t)] = O / Lsum;
+        out[2 + k.tid] = O;
+        if (k.tid == 0) { out[0] = M; out[1] = Lsum; }
+    }
+}
+
+// Combines the S partials of every head into the attention output, written to act. A thread
+// owns elements tid and tid + 512 of the row (d <= 1024) and requests everything it needs for
+// both before the first use, so the whole phase costs one round trip to L2.
+__device__ void attention_combine(Cta& k, int len) {
+    const MegaParams& p = k.p;
+    const int S = attn_splits_for(p, len), hd = p.d / p.H;
+    float ms[2][8], ls[2][8], os[2][8];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        const int t = k.tid + e * CONSUMERS;
+        const bool live = t < p.d;
+        const int h = live ? t / hd : 0, cc = live ? t - h * hd : 0;
+        const float* base = p.partg + (size_t)h * S * (hd + 2);
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+            const bool on = live && s < S;
+            ms[e][s] = on ? __ldcg(base + s * (hd + 2)) : -INFINITY;
+            ls[e][s] = on ? __ldcg(base + s * (hd + 2) + 1) : 0.0f;
+            os[e][s] = on ? __ldcg(base + s * (hd + 2) + 2 + cc) : 0.0f;
+        }
+    }
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        const int t = k.tid + e * CONSUMERS;
+        if (t < p.d) {
+            float M = -INFINITY;
+#pragma unroll
+            for (int s = 0; s < 8; ++s) M = fmaxf(M, ms[e][s]);
+            float Lsum = 0.0f, O = 0.0f;
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+                const float f = ms[e][s] > -INFINITY ? expf(ms[e][s] - M) : 0.0f;
+                Lsum = fmaf(ls[e][s], f, Lsum);
+                O = fmaf(os[e][s], f, O);
+            }
+            k.act[act_index(t)] = O / Lsum;
+        }
     }
     consumer_sync();
 }
@@ -539,7 +589,7 @@ __device__ void consumer(Cta& k) {
             // LN1 -> q, k, v (k, v appended to the cache at `pos`)
             layernorm_to_act(k, prm, prm + d);
             mark(k);
-            ok = consume_matrix(k, L.qkv, [&](int n, int i, float v) {
+            ok = consume_matrix(k, L.qkv, W_QKV, [&](int n, int i, float v) {
                 v += bias[boff[0] + i];
                 if (n < d) p.qg[n] = v; else if (n < 2 * d) kc[n - d] = v; else vc[n - 2 * d] = v;
             });
@@ -552,10 +602,10 @@ __device__ void consumer(Cta& k) {
             ok = grid_barrier(k);
             if (!ok) break;
             mark(k);
-            attention_combine(k);
+            attention_combine(k, len);
             mark(k);
             // out-proj + residual: x1 = x + (W att + b)
-            ok = consume_matrix(k, L.out, [&](int n, int i, float v) { p.x1g[n] = k.xs[n] + (v + bias[boff[1] + i]); });
+            ok = consume_matrix(k, L.out, W_OUT, [&](int n, int i, float v) { p.x1g[n] = k.xs[n] + (v + bias[boff[1] + i]); });
             mark(k);
             ok = ok && grid_barrier(k);
             if (!ok) break;
@@ -563,14 +613,14 @@ __device__ void consumer(Cta& k) {
             load_vec(k, p.x1g, k.xs, d, false);
             layernorm_to_act(k, prm + 2 * d, prm + 3 * d);
             mark(k);
-            ok = consume_matrix(k, L.up, [&](int n, int i, float v) { p.hidg[n] = gelu_f(v + bias[boff[2] + i]); });
+            ok = consume_matrix(k, L.up, W_UP, [&](int n, int i, float v) { p.hidg[n] = gelu_f(v + bias[boff[2] + i]); });
             mark(k);
             ok = ok && grid_barrier(k);
             if (!ok) break;
             mark(k);
             load_vec(k, p.hidg, k.act, p.F, true);
             mark(k);
-            ok = consume_matrix(k, L.down, [&](int n, int i, float v) { p.xg[n] = k.xs[n] + (v + bias[boff[3] + i]); });
+            ok = consume_matrix(k, L.down, W_DOWN, [&](int n, int i, float v) { p.xg[n] = k.xs[n] + (v + bias[boff[3] + i]); });
             mark(k);
             ok = ok && grid_barrier(k);          // its first sync also ends every read of the parameters
             if (!ok) break;
@@ -587,10 +637,9 @@ __device__ void consumer(Cta& k) {
             layernorm_to_act(k, k.param(pb), k.param(pb) + d);   // ends with a sync
             if ((k.tid & 31) == 0) mbar_arrive(&k.ctrl->pempty[pb]);
             ++k.pitem;
-            int r0, r1;
-            mega_cta_rows(V, d, k.c, k.G, &r0, &r1);
+            const int r0 = k.work[W_HEAD].r0, r1 = k.work[W_HEAD].r1;
             float* lg = k.sc;                      // this CTA's logits [r1 - r0]
-            ok = consume_matrix(k, p.head, [&](int n, int i, float v) { lg[i] = v; p.logits[n] = v; });
+            ok = consume_matrix(k, p.head, W_HEAD, [&](int n, int i, float v) { lg[i] = v; p.logits[n] = v; });
             if (!ok) break;
             consumer_sync();
             // ops.rs:478-502: max, exp(x - max), sum — per CTA, then combined across CTAs
@@ -676,8 +725,14 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_co
         const int words = p.L * (int)(sizeof(MegaLayer) / 16);
         for (int i = threadIdx.x; i < words; i += blockDim.x) dst[i] = src[i];
     }
+    if (threadIdx.x < W_KINDS) {
+        const int kind = threadIdx.x, d = p.d, F = p.F;
+        const int N = kind == W_QKV ? 3 * d : (kind == W_UP ? F : (kind == W_HEAD ? p.V : d));
+        const int K = kind == W_DOWN ? F : d;
+        make_work((Work*)(smem + OFF_WORK) + kind, N, K, (int)blockIdx.x, (int)gridDim.x);
+    }
     __syncthreads();
-    Cta k{p, smem, ctrl, (const MegaLayer*)(smem + OFF_LAYERS), (float4*)(smem + OFF_ACT), (float*)(smem + OFF_ACT),
+    Cta k{p, smem, ctrl, (const MegaLayer*)(smem + OFF_LAYERS), (const Work*)(smem + OFF_WORK), (float4*)(smem + OFF_ACT), (float*)(smem + OFF_ACT),
           (float*)(smem + OFF_XS), (float*)(smem + OFF_SC), (float*)(smem + OFF_PSUM), (float*)(smem + OFF_RED),
           (int)blockIdx.x, (int)gridDim.x, (int)threadIdx.x, 0, 0, 0u, -1};
     if (threadIdx.x >= CONSUMERS) {
