@@ -139,6 +139,9 @@ struct fc_model {
     double* lp_d = nullptr;
     uint8_t* gr_d = nullptr;
     uint16_t *xhi = nullptr, *xlo = nullptr;   // bf16 planes of the current GEMM input
+    // tensor path: bf16 hi / lo planes of LayerNorm output, qkv, attention output, GELU output
+    uint16_t *nhi = nullptr, *nlo = nullptr, *qkvhi = nullptr, *qkvlo = nullptr;
+    uint16_t *atthi = nullptr, *attlo = nullptr, *hidhi = nullptr, *hidlo = nullptr;
     int* tc_status = nullptr;                  // raised by the tensor-core GEMM on a timeout
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     float last_score_ms = 0.0f;
@@ -297,6 +300,7 @@ static int check_ids(const fc_model* m, const int32_t* ids, size_t n) {
 }
 
 // -------------------------------------------------------------------- prefill workspace
+static bool tensor_path(const fc_model* m);
 static int ensure_workspace(fc_model* m, int rows) {
     if (rows <= m->ws_rows) return FC_OK;
     m->ws_arena.release();
@@ -312,7 +316,7 @@ static int ensure_workspace(fc_model* m, int rows) {
     FC_TRY(a.alloc_n(&m->qkv, R * 3 * d));
     FC_TRY(a.alloc_n(&m->att, R * d));
     FC_TRY(a.alloc_n(&m->hid, R * F));
-    FC_TRY(a.alloc_n(&m->logits, chunk * (size_t)c.vocab));
+    FC_TRY(a.alloc_n(&m->logits, chunk * (size_t)m->head.N_pad));
     FC_TRY(a.alloc_n(&m->ids_d, R));
     FC_TRY(a.alloc_n(&m->targets_d, R));
     FC_TRY(a.alloc_n(&m->lp_d, R));
@@ -323,6 +327,12 @@ static int ensure_workspace(fc_model* m, int rows) {
         // bf16 hi / lo planes of the widest GEMM input, and the kernel's status word
         FC_TRY(a.alloc_n(&m->xhi, R * std::max(d, F)));
         FC_TRY(a.alloc_n(&m->xlo, R * std::max(d, F)));
+        if (tensor_path(m)) {
+            FC_TRY(a.alloc_n(&m->nhi, R * d));       FC_TRY(a.alloc_n(&m->nlo, R * d));
+            FC_TRY(a.alloc_n(&m->qkvhi, R * 3 * d)); FC_TRY(a.alloc_n(&m->qkvlo, R * 3 * d));
+            FC_TRY(a.alloc_n(&m->atthi, R * d));     FC_TRY(a.alloc_n(&m->attlo, R * d));
+            FC_TRY(a.alloc_n(&m->hidhi, R * F));     FC_TRY(a.alloc_n(&m->hidlo, R * F));
+        }
         FC_TRY(a.alloc_n(&m->tc_status, 1));
         FC_CUDA(cudaMemsetAsync(m->tc_status, 0, sizeof(int), m->st));
     }
@@ -342,14 +352,34 @@ static int gemm(fc_model* m, const QMat& w, const float* x, const float* bias, c
     return launch_gemm_q8_fp32(w, x, bias, res, epi, y, M, ldy, m->st);
 }
 
-// Sequential::forward (model.rs:51-71) up to the final LayerNorm, on B windows of T rows
-// whose ids are already in m->ids_d. Leaves LN_f(x) in m->n.
-static int forward_hidden(fc_model* m, int B, int T) {
+// True when the whole window forward runs on tensor cores with bf16-plane activations.
+static bool tensor_path(const fc_model* m) {
     const fc_config& c = m->cfg;
-    const int R = B * T, d = c.d_model;
+    return c.math_mode == FC_MATH_BF16X3 && c.d_model == c.n_head * 64 && c.d_model % 64 == 0 && c.d_ff % 64 == 0;
+}
+
+// Sequential::forward (model.rs:51-71) through every block, on B windows of T rows whose ids
+// are already in m->ids_d. Leaves the residual stream in m->x.
+static int forward_blocks(fc_model* m, int B, int T) {
+    const fc_config& c = m->cfg;
+    const int R = B * T, d = c.d_model, F = c.d_ff;
     cudaStream_t st = m->st;
     FC_CUDA(cudaMemsetAsync(m->err_d, 0, sizeof(int), st));
     FC_TRY(launch_embed_rows(m->tok, m->pos, m->ids_d, R, T, m->x, m->err_d, st));
+    if (tensor_path(m)) {
+        // activations between kernels are bf16 hi / lo planes; only the residual stream is f32
+        for (int l = 0; l < c.n_layer; ++l) {
+            const LayerDev& L = m->layers[l];
+            FC_TRY(launch_layernorm_planes(m->x, L.ln1g, L.ln1b, R, d, m->nhi, m->nlo, st));
+            FC_TRY(launch_gemm_q8_bf16x3_ex(L.qkv, m->nhi, m->nlo, L.qkv_b, nullptr, EPI_NONE, nullptr, m->qkvhi, m->qkvlo, R, 3 * d, m->tc_status, st));
+            FC_TRY(launch_attn_prefill_tc(m->qkvhi, m->qkvlo, B, T, d, c.n_head, m->atthi, m->attlo, m->tc_status, st));
+            FC_TRY(launch_gemm_q8_bf16x3_ex(L.out, m->atthi, m->attlo, L.out_b, m->x, EPI_NONE, m->x, nullptr, nullptr, R, d, m->tc_status, st));
+            FC_TRY(launch_layernorm_planes(m->x, L.ln2g, L.ln2b, R, d, m->nhi, m->nlo, st));
+            FC_TRY(launch_gemm_q8_bf16x3_ex(L.up, m->nhi, m->nlo, L.up_b, nullptr, EPI_GELU, nullptr, m->hidhi, m->hidlo, R, F, m->tc_status, st));
+            FC_TRY(launch_gemm_q8_bf16x3_ex(L.down, m->hidhi, m->hidlo, L.down_b, m->x, EPI_NONE, m->x, nullptr, nullptr, R, d, m->tc_status, st));
+        }
+        return FC_OK;
+    }
     for (int l = 0; l < c.n_layer; ++l) {
         const LayerDev& L = m->layers[l];
         FC_TRY(launch_layernorm(m->x, L.ln1g, L.ln1b, R, d, m->n, nullptr, st));
@@ -357,21 +387,29 @@ static int forward_hidden(fc_model* m, int B, int T) {
         FC_TRY(launch_attn_prefill(m->qkv, B, T, d, c.n_head, m->att, st));
         FC_TRY(gemm(m, L.out, m->att, L.out_b, m->x, EPI_NONE, m->x, R, d));
         FC_TRY(launch_layernorm(m->x, L.ln2g, L.ln2b, R, d, m->n, nullptr, st));
-        FC_TRY(gemm(m, L.up, m->n, L.up_b, nullptr, EPI_GELU, m->hid, R, c.d_ff));
+        FC_TRY(gemm(m, L.up, m->n, L.up_b, nullptr, EPI_GELU, m->hid, R, F));
         FC_TRY(gemm(m, L.down, m->hid, L.down_b, m->x, EPI_NONE, m->x, R, d));
     }
-    return launch_layernorm(m->x, m->lnfg, m->lnfb, R, d, m->n, nullptr, st);
+    return FC_OK;
 }
 
-// Forward + head + scoring tail for ids/targets already on the device. lp_d/gr_d filled.
+// Forward + final LayerNorm + head + scoring tail for ids/targets already on the device.
+// lp_d/gr_d filled. Logit rows are ldl floats apart (ldl % 4 == 0 for vector stores).
 static int score_device(fc_model* m, int B, int T) {
     const fc_config& c = m->cfg;
-    const int R = B * T;
-    FC_TRY(forward_hidden(m, B, T));
+    const int R = B * T, d = c.d_model, ldl = m->head.N_pad;
+    FC_TRY(forward_blocks(m, B, T));
+    const bool tc = tensor_path(m);
+    if (tc) FC_TRY(launch_layernorm_planes(m->x, m->lnfg, m->lnfb, R, d, m->nhi, m->nlo, m->st));
+    else FC_TRY(launch_layernorm(m->x, m->lnfg, m->lnfb, R, d, m->n, nullptr, m->st));
     for (int r0 = 0; r0 < R; r0 += m->head_chunk) {
         const int rows = std::min(m->head_chunk, R - r0);
-        FC_TRY(gemm(m, m->head, m->n + (size_t)r0 * c.d_model, nullptr, nullptr, EPI_NONE, m->logits, rows, c.vocab));
-        FC_TRY(launch_score_rows(m->logits, c.vocab, c.vocab, m->targets_d + r0, rows, m->lp_d + r0, m->gr_d + r0, m->st));
+        if (tc)
+            FC_TRY(launch_gemm_q8_bf16x3_ex(m->head, m->nhi + (size_t)r0 * d, m->nlo + (size_t)r0 * d, nullptr, nullptr, EPI_NONE,
+                                            m->logits, nullptr, nullptr, rows, ldl, m->tc_status, m->st));
+        else
+            FC_TRY(gemm(m, m->head, m->n + (size_t)r0 * d, nullptr, nullptr, EPI_NONE, m->logits, rows, ldl));
+        FC_TRY(launch_score_rows(m->logits, ldl, c.vocab, m->targets_d + r0, rows, m->lp_d + r0, m->gr_d + r0, m->st));
     }
     return FC_OK;
 }
@@ -762,7 +800,9 @@ int fc_predict_next(fc_model* m, const int32_t* ids, int n, float* probs) {
     FC_TRY(ensure_workspace(m, n));
     cudaStream_t st = m->st;
     FC_CUDA(cudaMemcpyAsync(m->ids_d, ids, (size_t)n * 4, cudaMemcpyHostToDevice, st));
-    FC_TRY(forward_hidden(m, 1, n));
+    FC_TRY(forward_blocks(m, 1, n));
+    FC_TRY(launch_layernorm(m->x + (size_t)(n - 1) * c.d_model, m->lnfg, m->lnfb, 1, c.d_model,
+                            m->n + (size_t)(n - 1) * c.d_model, nullptr, st));
     GemvOut o; o.out[0] = m->logits;
     FC_TRY(launch_gemv_q8(m->head, m->n + (size_t)(n - 1) * c.d_model, nullptr, nullptr, EPI_NONE, o, nullptr, st));
     FC_TRY(launch_softmax_row(m->logits, c.vocab, m->probs_d, st));

@@ -93,6 +93,9 @@ int launch_gemm_q8_fp32(const QMat& w, const float* x, const float* bias, const 
 int launch_split_bf16(const float* x, void* hi, void* lo, size_t n, cudaStream_t st);
 int launch_gemm_q8_bf16x3(const QMat& w, const void* x_hi, const void* x_lo, const float* bias, const float* residual,
                           int epi, float* y, int M, int ldy, int* status, cudaStream_t st);
+// The same with a choice of output: f32 rows y, or (y == nullptr) bf16 hi / lo planes for the next GEMM.
+int launch_gemm_q8_bf16x3_ex(const QMat& w, const void* x_hi, const void* x_lo, const float* bias, const float* residual,
+                             int epi, float* y, void* y_hi, void* y_lo, int M, int ldy, int* status, cudaStream_t st);
 
 // api.cu — the matrix and device behind a resident-weight handle.
 const QMat* qweight_matrix(const fc_qweight* w, int* device);
@@ -104,6 +107,8 @@ int launch_embed_rows(const QMat& tok, const float* pos_emb, const int* ids, int
                       int* error_flag, cudaStream_t st);
 int launch_layernorm(const float* x, const float* g, const float* b, int rows, int d, float* y,
                      const StepState* state, cudaStream_t st);
+// LayerNorm written as bf16 hi / lo planes [rows][d] for the tensor-core GEMM.
+int launch_layernorm_planes(const float* x, const float* g, const float* b, int rows, int d, void* hi, void* lo, cudaStream_t st);
 // Decode tail over logits[V]: softmax statistics, optional probs[V], optional greedy select
 // (append to queue) — and always the end-of-step bookkeeping (pos, fed).
 int launch_step_tail(const float* logits, int V, float* probs_or_null, int do_select, int* queue, int queue_cap,
@@ -120,5 +125,9 @@ int launch_attn_decode(const float* q, const float* kcache, const float* vcache,
                        const StepState* state, float* out, cudaStream_t st);
 // qkv [R][3d] (q | k | v per row), R = B·T, causal within each window of T rows.
 int launch_attn_prefill(const float* qkv, int B, int T, int d, int H, float* out, cudaStream_t st);
+// attn_tc.cu — the same on tcgen05 (head_dim 64): bf16 hi / lo planes of qkv [B*T][3d] in,
+// planes of the attention output [B*T][d] out; `status` is raised on a timeout.
+int launch_attn_prefill_tc(const void* qkv_hi, const void* qkv_lo, int B, int T, int d, int H, void* out_hi, void* out_lo,
+                           int* status, cudaStream_t st);
 
 }  // namespace fc

@@ -7,15 +7,18 @@
 // relative) and every 128x128x16 step issues three kind::f16 MMAs into the same fp32 TMEM
 // accumulator: xh·wh + xl·wh + xh·wl. The dropped xl·wl term is 2^-16 relative per product.
 //
-// One CTA computes a 128 x 128 tile:
-//   warp 8      TMA producer: the two bf16 planes of the X tile (128 rows x 64 k, 128-byte
+// Persistent kernel, one CTA per SM, 128 x 128 output tiles taken round-robin (N fastest, so
+// the CTAs running together share a few row panels of X in L2):
+//   warp 12     TMA producer: the two bf16 planes of the X tile (128 rows x 64 k, 128-byte
 //               swizzle) into the stage's A buffers, completing on the stage's mbarrier;
-//   warps 0-7   dequantise the 128 x 64 Q8_0 weight tile: w = d * q exactly as
+//   warps 4-11  dequantise the 128 x 64 Q8_0 weight tile: w = d * q exactly as
 //               gguf::dequant_q8_0 (ferrum_core/src/gguf/dequant.rs:37-49), split into bf16
 //               hi/lo and stored in the same swizzled K-major layout the tensor core reads;
-//   warp 9      allocates TMEM and issues tcgen05.mma from one thread; tcgen05.commit frees
-//               the stage and finally publishes the accumulator;
-//   warps 0-3   epilogue: tcgen05.ld their 32 accumulator lanes, bias / GELU / residual, store.
+//   warp 13     allocates 256 TMEM columns (two accumulators) and issues tcgen05.mma from one
+//               thread; tcgen05.commit frees the stage and finally publishes the accumulator;
+//   warps 0-3   epilogue of the previous tile while the next one is being multiplied:
+//               tcgen05.ld their 32 accumulator lanes, bias / GELU / residual, then either f32
+//               rows or the bf16 hi/lo planes the next GEMM consumes.
 // Every mbarrier wait is bounded by a cycle budget; when it runs out the kernel raises a
 // status word, releases its TMEM and returns.
 //
@@ -33,8 +36,10 @@ constexpr int BM = 128, BN = 128, BK = 64;
 constexpr int STAGES = 3;
 constexpr int TILE_BYTES = BM * BK * 2;                 // one bf16 operand tile: 16 KiB
 constexpr int STAGE_BYTES = 4 * TILE_BYTES;             // A hi, A lo, B hi, B lo
-constexpr int DQ_WARPS = 8, THREADS = (DQ_WARPS + 2) * 32;
-constexpr int TMEM_COLS = 128;
+constexpr int EPI_WARPS = 4, DQ_WARPS = 8;
+constexpr int TMA_WARP = EPI_WARPS + DQ_WARPS, MMA_WARP = TMA_WARP + 1;
+constexpr int THREADS = (MMA_WARP + 1) * 32;
+constexpr int TMEM_COLS = 256;                          // two 128-column accumulators
 constexpr long long WAIT_CYCLES = 4000000000LL;
 // bf16 x bf16 -> f32, M = 128, N = 128, both operands K-major
 constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
@@ -43,7 +48,8 @@ struct Bars {
     unsigned long long full_a[STAGES];
     unsigned long long full_b[STAGES];
     unsigned long long empty[STAGES];
-    unsigned long long acc_full;
+    unsigned long long acc_full[2];
+    unsigned long long acc_empty[2];
     uint32_t tmem_base;
     volatile int abort;
 };
@@ -59,13 +65,14 @@ __device__ __forceinline__ void mbar_expect_tx(unsigned long long* b, uint32_t b
 __device__ __forceinline__ void mbar_arrive(unsigned long long* b) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s32(b)) : "memory");
 }
+// A thread that finds the phase incomplete is suspended by the hardware for up to 2 us.
 __device__ __forceinline__ bool mbar_try_wait(unsigned long long* b, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(s32(b)), "r"(parity) : "memory");
+        : "=r"(ok) : "r"(s32(b)), "r"(parity), "r"(2000u) : "memory");
     return ok != 0;
 }
 // Bounded wait. Returns false (after raising the status word) when the budget runs out or
@@ -107,7 +114,7 @@ template <int B>
 __device__ __forceinline__ float qb(uint32_t w) {
     return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540 + B)) - 8388736.0f;
 }
-// Two weights -> packed bf16 hi pair and lo pair (element 0 in the low half).
+// Two values -> packed bf16 hi pair and lo pair (element 0 in the low half).
 __device__ __forceinline__ void split2(float w0, float w1, uint32_t* hi, uint32_t* lo) {
     const __nv_bfloat162 h = __float22bfloat162_rn(make_float2(w0, w1));
     const float2 hf = __bfloat1622float2(h);
@@ -119,7 +126,9 @@ __device__ __forceinline__ void split2(float w0, float w1, uint32_t* hi, uint32_
 struct TcArgs {
     const uint8_t* qu; const __half* d; int N, K;
     const float* bias; const float* residual; int epi;
-    float* y; int M, ldy;
+    float* y;                 // f32 output rows, or null when the output goes to planes
+    uint16_t *yhi, *ylo;      // bf16 hi / lo output planes [M][ldy]
+    int M, ldy;
     int* status;
 };
 
@@ -131,8 +140,9 @@ gemm_q8_bf16x3_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_c
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     Bars* bars = (Bars*)(smem + STAGES * STAGE_BYTES);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int nkb = a.K / BK;
+    const int tiles_n = (a.N + BN - 1) / BN, tiles_m = (a.M + BM - 1) / BM;
+    const int n_tiles = tiles_n * tiles_m;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -140,11 +150,14 @@ gemm_q8_bf16x3_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_c
             mbar_init(&bars->full_b[s], DQ_WARPS);
             mbar_init(&bars->empty[s], 1);
         }
-        mbar_init(&bars->acc_full, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&bars->acc_full[b], 1);
+            mbar_init(&bars->acc_empty[b], EPI_WARPS);
+        }
         bars->abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == DQ_WARPS + 1) {   // the MMA warp owns the tensor memory allocation
+    if (warp == MMA_WARP) {   // the MMA warp owns the tensor memory allocation
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(&bars->tmem_base)), "r"((uint32_t)TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -153,89 +166,119 @@ gemm_q8_bf16x3_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_c
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = bars->tmem_base;
 
-    if (warp == DQ_WARPS) {
+    if (warp == TMA_WARP) {
         // ---------------------------------------------------------------- TMA producer
         if (lane == 0) {
-            for (int kb = 0; kb < nkb; ++kb) {
-                const int s = kb % STAGES;
-                if (!wait_bar(bars, &bars->empty[s], ((kb / STAGES) & 1) ^ 1, a.status)) break;
-                unsigned char* st = smem + s * STAGE_BYTES;
-                mbar_expect_tx(&bars->full_a[s], 2 * TILE_BYTES);
-                tma_load_2d(st, &map_hi, kb * BK, m0, &bars->full_a[s]);
-                tma_load_2d(st + TILE_BYTES, &map_lo, kb * BK, m0, &bars->full_a[s]);
+            int it = 0;                                   // k-blocks issued so far, over all tiles
+            for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+                const int m0 = (tile / tiles_n) * BM;
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (!wait_bar(bars, &bars->empty[s], ((it / STAGES) & 1) ^ 1, a.status)) { tile = n_tiles; break; }
+                    unsigned char* st = smem + s * STAGE_BYTES;
+                    mbar_expect_tx(&bars->full_a[s], 2 * TILE_BYTES);
+                    tma_load_2d(st, &map_hi, kb * BK, m0, &bars->full_a[s]);
+                    tma_load_2d(st + TILE_BYTES, &map_lo, kb * BK, m0, &bars->full_a[s]);
+                }
             }
         }
-    } else if (warp == DQ_WARPS + 1) {
+    } else if (warp == MMA_WARP) {
         // ---------------------------------------------------------------- MMA issuer
         if (lane == 0) {
+            int it = 0, ti = 0;
             bool ok = true;
-            for (int kb = 0; kb < nkb && ok; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t par = (kb / STAGES) & 1;
-                ok = wait_bar(bars, &bars->full_a[s], par, a.status) && wait_bar(bars, &bars->full_b[s], par, a.status);
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++ti) {
+                const int buf = ti & 1;
+                // the epilogue must have drained this accumulator (two tiles ago)
+                ok = wait_bar(bars, &bars->acc_empty[buf], ((ti >> 1) & 1) ^ 1, a.status);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t base = s32(smem + s * STAGE_BYTES);
-                const uint64_t ah = smem_desc(base), al = smem_desc(base + TILE_BYTES);
-                const uint64_t bh = smem_desc(base + 2 * TILE_BYTES), bl = smem_desc(base + 3 * TILE_BYTES);
+                const uint32_t acc = tmem + (uint32_t)(buf * BN);
+                for (int kb = 0; kb < nkb && ok; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t par = (it / STAGES) & 1;
+                    ok = wait_bar(bars, &bars->full_a[s], par, a.status) && wait_bar(bars, &bars->full_b[s], par, a.status);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t base = s32(smem + s * STAGE_BYTES);
+                    const uint64_t ah = smem_desc(base), al = smem_desc(base + TILE_BYTES);
+                    const uint64_t bh = smem_desc(base + 2 * TILE_BYTES), bl = smem_desc(base + 3 * TILE_BYTES);
 #pragma unroll
-                for (int ks = 0; ks < BK / 16; ++ks) {
-                    const uint64_t adv = (uint64_t)(ks * 2);            // 32 bytes per k-step of 16 bf16
-                    umma(tmem, ah + adv, bh + adv, (kb | ks) != 0);
-                    umma(tmem, al + adv, bh + adv, 1);
-                    umma(tmem, ah + adv, bl + adv, 1);
+                    for (int ks = 0; ks < BK / 16; ++ks) {
+                        const uint64_t adv = (uint64_t)(ks * 2);        // 32 bytes per k-step of 16 bf16
+                        umma(acc, ah + adv, bh + adv, (kb | ks) != 0);
+                        umma(acc, al + adv, bh + adv, 1);
+                        umma(acc, ah + adv, bl + adv, 1);
+                    }
+                    umma_commit(&bars->empty[s]);                    // frees the stage when the MMAs retire
                 }
-                umma_commit(&bars->empty[s]);                        // frees the stage when the MMAs retire
+                if (ok) umma_commit(&bars->acc_full[buf]);
             }
-            if (ok) umma_commit(&bars->acc_full);
+        }
+    } else if (warp >= EPI_WARPS) {
+        // ---------------------------------------------------------------- weight dequantisers
+        const int t = threadIdx.x - EPI_WARPS * 32;  // 0..255
+        const int row = t >> 1, half = t & 1;        // weight row of the tile, 32-wide half of the k-block
+        int it = 0;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+            const int n0 = (tile % tiles_n) * BN;
+            const size_t n = (size_t)(n0 + row);     // < N_pad (zero rows past N)
+            const uint8_t* qrow = a.qu + n * a.K + half * 32;
+            const __half* drow = a.d + n * (a.K >> 5) + half;
+            // two k-blocks of quants are kept in flight ahead of the one being converted
+            uint4 qa[2], qc[2];
+            float sc[2];
+#pragma unroll
+            for (int pf = 0; pf < 2; ++pf) {
+                if (pf < nkb) {
+                    qa[pf] = __ldg((const uint4*)(qrow + (size_t)pf * BK));
+                    qc[pf] = __ldg((const uint4*)(qrow + (size_t)pf * BK) + 1);
+                    sc[pf] = __half2float(__ldg(drow + pf * 2));
+                }
+            }
+            for (int kb = 0; kb < nkb; ++kb, ++it) {
+                const int s = it % STAGES;
+                const uint4 c0 = qa[kb & 1], c1 = qc[kb & 1];
+                const float scale = sc[kb & 1];
+                if (kb + 2 < nkb) {
+                    qa[kb & 1] = __ldg((const uint4*)(qrow + (size_t)(kb + 2) * BK));
+                    qc[kb & 1] = __ldg((const uint4*)(qrow + (size_t)(kb + 2) * BK) + 1);
+                    sc[kb & 1] = __half2float(__ldg(drow + (kb + 2) * 2));
+                }
+                if (!wait_bar(bars, &bars->empty[s], ((it / STAGES) & 1) ^ 1, a.status)) { tile = n_tiles; break; }
+                unsigned char* bhi = smem + s * STAGE_BYTES + 2 * TILE_BYTES + row * 128;
+                unsigned char* blo = bhi + TILE_BYTES;
+                const uint32_t ws[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {        // 16-byte chunk c of this half: 8 weights
+                    uint4 hi, lo;
+                    split2(scale * qb<0>(ws[2 * c]), scale * qb<1>(ws[2 * c]), &hi.x, &lo.x);
+                    split2(scale * qb<2>(ws[2 * c]), scale * qb<3>(ws[2 * c]), &hi.y, &lo.y);
+                    split2(scale * qb<0>(ws[2 * c + 1]), scale * qb<1>(ws[2 * c + 1]), &hi.z, &lo.z);
+                    split2(scale * qb<2>(ws[2 * c + 1]), scale * qb<3>(ws[2 * c + 1]), &hi.w, &lo.w);
+                    const int chunk = ((half * 4 + c) ^ (row & 7)) * 16;   // 128-byte swizzle
+                    *(uint4*)(bhi + chunk) = hi;
+                    *(uint4*)(blo + chunk) = lo;
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> tensor-core reads
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars->full_b[s]);
+            }
         }
     } else {
-        // ---------------------------------------------------------------- weight dequantisers
-        const int t = threadIdx.x;                  // 0..255
-        const int row = t >> 1, half = t & 1;       // weight row of the tile, 32-wide half of the k-block
-        const size_t n = (size_t)(n0 + row);        // < N_pad (zero rows past N)
-        const uint8_t* qrow = a.qu + n * a.K + half * 32;
-        const __half* drow = a.d + n * (a.K >> 5) + half;
-        uint4 q0 = __ldg((const uint4*)qrow), q1 = __ldg((const uint4*)qrow + 1);
-        float sc = __half2float(__ldg(drow));
-        bool ok = true;
-        for (int kb = 0; kb < nkb; ++kb) {
-            const int s = kb % STAGES;
-            const uint4 c0 = q0, c1 = q1;
-            const float scale = sc;
-            if (kb + 1 < nkb) {                     // prefetch the next k-block's quants
-                q0 = __ldg((const uint4*)(qrow + (size_t)(kb + 1) * BK));
-                q1 = __ldg((const uint4*)(qrow + (size_t)(kb + 1) * BK) + 1);
-                sc = __half2float(__ldg(drow + (kb + 1) * 2));
-            }
-            ok = wait_bar(bars, &bars->empty[s], ((kb / STAGES) & 1) ^ 1, a.status);
-            if (!ok) break;
-            unsigned char* bhi = smem + s * STAGE_BYTES + 2 * TILE_BYTES + row * 128;
-            unsigned char* blo = bhi + TILE_BYTES;
-            const uint32_t ws[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {           // 16-byte chunk c of this half: 8 weights
-                uint4 hi, lo;
-                split2(scale * qb<0>(ws[2 * c]), scale * qb<1>(ws[2 * c]), &hi.x, &lo.x);
-                split2(scale * qb<2>(ws[2 * c]), scale * qb<3>(ws[2 * c]), &hi.y, &lo.y);
-                split2(scale * qb<0>(ws[2 * c + 1]), scale * qb<1>(ws[2 * c + 1]), &hi.z, &lo.z);
-                split2(scale * qb<2>(ws[2 * c + 1]), scale * qb<3>(ws[2 * c + 1]), &hi.w, &lo.w);
-                const int chunk = ((half * 4 + c) ^ (row & 7)) * 16;   // 128-byte swizzle
-                *(uint4*)(bhi + chunk) = hi;
-                *(uint4*)(blo + chunk) = lo;
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> tensor-core reads
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bars->full_b[s]);
-        }
         // ---------------------------------------------------------------- epilogue (warps 0-3)
-        if (warp < 4 && ok && wait_bar(bars, &bars->acc_full, 0, a.status)) {
+        const bool vec_ok = (a.ldy & 3) == 0;
+        int ti = 0;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++ti) {
+            const int buf = ti & 1;
+            const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+            if (!wait_bar(bars, &bars->acc_full[buf], (ti >> 1) & 1, a.status)) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int m = m0 + warp * 32 + lane;
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
                 uint32_t r[32];
-                const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c * 32);
+                const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(buf * BN + c * 32);
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                     "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -246,27 +289,67 @@ gemm_q8_bf16x3_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_c
                       "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                     : "r"(taddr) : "memory");
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (m < a.M) {
-                    const int nb = n0 + c * 32;
-                    float* yr = a.y + (size_t)m * a.ldy + nb;
-                    const float* rr = a.residual ? a.residual + (size_t)m * a.ldy + nb : nullptr;
+                if (c == BN / 32 - 1) {
+                    // the accumulator is in registers: hand the TMEM buffer back to the MMA warp
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bars->acc_empty[buf]);
+                }
+                const int nb = n0 + c * 32;
+                if (m < a.M && nb < a.N) {
+                const bool full = nb + 32 <= a.N;
+                float v[32];
+                const size_t off = (size_t)m * a.ldy + nb;
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        if (nb + i < a.N) {
-                            float v = __uint_as_float(r[i]);
-                            if (a.bias) v += a.bias[nb + i];
-                            if (a.epi == EPI_GELU) v = gelu_f(v);
-                            if (rr) v = rr[i] + v;
-                            yr[i] = v;
+                for (int i = 0; i < 32; ++i) {
+                    float t = __uint_as_float(r[i]);
+                    if (a.bias && (full || nb + i < a.N)) t += __ldg(a.bias + nb + i);
+                    if (a.epi == EPI_GELU) t = gelu_f(t);
+                    v[i] = t;
+                }
+                if (a.residual) {
+                    if (full && vec_ok) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const float4 rr = *(const float4*)(a.residual + off + 4 * i);
+                            v[4 * i] = rr.x + v[4 * i]; v[4 * i + 1] = rr.y + v[4 * i + 1];
+                            v[4 * i + 2] = rr.z + v[4 * i + 2]; v[4 * i + 3] = rr.w + v[4 * i + 3];
                         }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (nb + i < a.N) v[i] = a.residual[off + i] + v[i];
                     }
                 }
+                if (a.y) {
+                    if (full && vec_ok) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            *(float4*)(a.y + off + 4 * i) = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (nb + i < a.N) a.y[off + i] = v[i];
+                    }
+                } else {
+                    // bf16 hi / lo planes for the next GEMM (ldy % 8 == 0, N % 32 == 0 for these outputs)
+                    uint32_t hi[16], lo[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) split2(v[2 * i], v[2 * i + 1], &hi[i], &lo[i]);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        *(uint4*)(a.yhi + off + 8 * i) = make_uint4(hi[4 * i], hi[4 * i + 1], hi[4 * i + 2], hi[4 * i + 3]);
+                        *(uint4*)(a.ylo + off + 8 * i) = make_uint4(lo[4 * i], lo[4 * i + 1], lo[4 * i + 2], lo[4 * i + 3]);
+                    }
+                }
+                }
+                __syncwarp();      // the next tcgen05.ld is warp-collective
             }
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == DQ_WARPS + 1) {
+    if (warp == MMA_WARP) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)TMEM_COLS) : "memory");
     }
@@ -319,16 +402,20 @@ int encode_plane(CUtensorMap* map, const void* plane, int M, int K) {
 }
 }  // namespace
 
-// x_hi / x_lo: bf16 planes [M][K] (16-byte aligned). status: device int, raised on timeout.
-int launch_gemm_q8_bf16x3(const QMat& w, const void* x_hi, const void* x_lo, const float* bias, const float* residual,
-                          int epi, float* y, int M, int ldy, int* status, cudaStream_t st) {
+// x_hi / x_lo: bf16 planes [M][K] (16-byte aligned). Output: f32 rows y (ldy floats apart), or, when
+// y is null, bf16 planes y_hi / y_lo (N % 32 == 0, ldy % 8 == 0). status: device int, raised on timeout.
+int launch_gemm_q8_bf16x3_ex(const QMat& w, const void* x_hi, const void* x_lo, const float* bias, const float* residual,
+                             int epi, float* y, void* y_hi, void* y_lo, int M, int ldy, int* status, cudaStream_t st) {
     if (w.K % BK) return fail(FC_E_SHAPE, "the tensor-core GEMM needs K %% 64 == 0 (K = %d)", w.K);
-    static bool attr_set[64] = {};
+    if (!y && (!y_hi || !y_lo || (w.N & 31) || (ldy & 7) || residual))
+        return fail(FC_E_SHAPE, "plane output needs N %% 32 == 0, ldy %% 8 == 0 and no residual");
+    static int sms[64] = {};
     int dev = 0;
     FC_CUDA(cudaGetDevice(&dev));
-    if (dev < 64 && !attr_set[dev]) {
+    if (dev >= 64) return fail(FC_E_ARG, "device %d out of range", dev);
+    if (!sms[dev]) {
         FC_CUDA(cudaFuncSetAttribute(gemm_q8_bf16x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        attr_set[dev] = true;
+        FC_CUDA(cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev));
     }
     CUtensorMap mh, ml;
     FC_TRY(encode_plane(&mh, x_hi, M, w.K));
@@ -336,11 +423,17 @@ int launch_gemm_q8_bf16x3(const QMat& w, const void* x_hi, const void* x_lo, con
     TcArgs a;
     a.qu = w.qu; a.d = w.d; a.N = w.N; a.K = w.K;
     a.bias = bias; a.residual = residual; a.epi = epi;
-    a.y = y; a.M = M; a.ldy = ldy; a.status = status;
-    dim3 grid((w.N + BN - 1) / BN, (M + BM - 1) / BM);
+    a.y = y; a.yhi = (uint16_t*)y_hi; a.ylo = (uint16_t*)y_lo; a.M = M; a.ldy = ldy; a.status = status;
+    const int n_tiles = ((w.N + BN - 1) / BN) * ((M + BM - 1) / BM);
+    const int grid = n_tiles < sms[dev] ? n_tiles : sms[dev];
     gemm_q8_bf16x3_kernel<<<grid, THREADS, SMEM_BYTES, st>>>(mh, ml, a);
     FC_LAUNCHED();
     return FC_OK;
+}
+
+int launch_gemm_q8_bf16x3(const QMat& w, const void* x_hi, const void* x_lo, const float* bias, const float* residual,
+                          int epi, float* y, int M, int ldy, int* status, cudaStream_t st) {
+    return launch_gemm_q8_bf16x3_ex(w, x_hi, x_lo, bias, residual, epi, y, nullptr, nullptr, M, ldy, status, st);
 }
 
 }  // namespace fc

@@ -1,5 +1,7 @@
 // Row kernels of the forward path: embedding gather, LayerNorm, the decode tail
 // (softmax statistics + greedy select) and the scoring tail (per-target log-prob).
+#include <cuda_bf16.h>
+
 #include "fc_common.cuh"
 
 namespace fc {
@@ -125,6 +127,54 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const float* __res
         const int c = threadIdx.x + i * blockDim.x;
         if (c < d) y[(size_t)blockIdx.x * d + c] = ((v[i] - mean) / sd) * g[c] + b[c];
     }
+}
+
+// The same LayerNorm with the result written as the bf16 hi / lo planes (y = hi + lo to 2^-17
+// relative) that the tensor-core GEMM reads.
+template <int PER>
+__global__ void layernorm_planes_kernel(const float* __restrict__ x, const float* __restrict__ g, const float* __restrict__ b,
+                                        int d, __nv_bfloat16* __restrict__ hi, __nv_bfloat16* __restrict__ lo) {
+    __shared__ float red[33];
+    const float* xr = x + (size_t)blockIdx.x * d;
+    float v[PER];
+    float s = 0.0f;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        v[i] = c < d ? xr[c] : 0.0f;
+        s += v[i];
+    }
+    const float mean = block_sum(s, red) / (float)d;
+    float q = 0.0f;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        const float t = v[i] - mean;
+        q += c < d ? t * t : 0.0f;
+    }
+    const float var = block_sum(q, red) / (float)d;
+    const float sd = sqrtf(var + 1e-5f);
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < d) {
+            const float y = ((v[i] - mean) / sd) * g[c] + b[c];
+            const __nv_bfloat16 h = __float2bfloat16_rn(y);
+            hi[(size_t)blockIdx.x * d + c] = h;
+            lo[(size_t)blockIdx.x * d + c] = __float2bfloat16_rn(y - __bfloat162float(h));
+        }
+    }
+}
+
+int launch_layernorm_planes(const float* x, const float* g, const float* b, int rows, int d, void* hi, void* lo, cudaStream_t st) {
+    const int threads = 256;
+    const int per = (d + threads - 1) / threads;
+    if (per <= 4) layernorm_planes_kernel<4><<<rows, threads, 0, st>>>(x, g, b, d, (__nv_bfloat16*)hi, (__nv_bfloat16*)lo);
+    else if (per <= 8) layernorm_planes_kernel<8><<<rows, threads, 0, st>>>(x, g, b, d, (__nv_bfloat16*)hi, (__nv_bfloat16*)lo);
+    else if (per <= 16) layernorm_planes_kernel<16><<<rows, threads, 0, st>>>(x, g, b, d, (__nv_bfloat16*)hi, (__nv_bfloat16*)lo);
+    else return fail(FC_E_SHAPE, "LayerNorm width %d exceeds 4096", d);
+    FC_LAUNCHED();
+    return FC_OK;
 }
 
 int launch_layernorm(const float* x, const float* g, const float* b, int rows, int d, float* y,
