@@ -7,14 +7,15 @@
 // relative) and every 128x128x16 step issues three kind::f16 MMAs into the same fp32 TMEM
 // accumulator: xh·wh + xl·wh + xh·wl. The dropped xl·wl term is 2^-16 relative per product.
 //
-// Persistent kernel, one CTA per SM, 128 x 128 output tiles taken round-robin (N fastest, so
-// the CTAs running together share a few row panels of X in L2):
-//   warp 12     TMA producer: the two bf16 planes of the X tile (128 rows x 64 k, 128-byte
+// Persistent kernel, one CTA per SM, 256 x 128 output tiles (two 128-row MMA tiles that share
+// one dequantised weight tile) taken round-robin, N fastest, so that the CTAs running together
+// share a few row panels of X in L2:
+//   warp 12     TMA producer: the two bf16 planes of the X tile (256 rows x 64 k, 128-byte
 //               swizzle) into the stage's A buffers, completing on the stage's mbarrier;
 //   warps 4-11  dequantise the 128 x 64 Q8_0 weight tile: w = d * q exactly as
 //               gguf::dequant_q8_0 (ferrum_core/src/gguf/dequant.rs:37-49), split into bf16
 //               hi/lo and stored in the same swizzled K-major layout the tensor core reads;
-//   warp 13     allocates 256 TMEM columns (two accumulators) and issues tcgen05.mma from one
+//   warp 13     allocates all 512 TMEM columns (two buffers of two accumulators) and issues tcgen05.mma from one
 //               thread; tcgen05.commit frees the stage and finally publishes the accumulator;
 //   warps 0-3   epilogue of the previous tile while the next one is being multiplied:
 //               tcgen05.ld their 32 accumulator lanes, bias / GELU / residual, then either f32
@@ -32,17 +33,18 @@ namespace fc {
 
 namespace {
 
-constexpr int BM = 128, BN = 128, BK = 64;
-constexpr int STAGES = 3;
-constexpr int TILE_BYTES = BM * BK * 2;                 // one bf16 operand tile: 16 KiB
-constexpr int STAGE_BYTES = 4 * TILE_BYTES;             // A hi, A lo, B hi, B lo
+constexpr int BM = 256, BN = 128, BK = 64;            // a CTA tile is two 128-row MMA tiles sharing one weight tile
+constexpr int STAGES = 2;
+constexpr int TILE_BYTES = 128 * BK * 2;                // one 128-row bf16 operand tile: 16 KiB
+constexpr int A_BYTES = 2 * TILE_BYTES;                 // one plane of the 256-row X tile
+constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * TILE_BYTES;   // A hi, A lo (256 rows each), B hi, B lo
 constexpr int EPI_WARPS = 4, DQ_WARPS = 8;
 constexpr int TMA_WARP = EPI_WARPS + DQ_WARPS, MMA_WARP = TMA_WARP + 1;
 constexpr int THREADS = (MMA_WARP + 1) * 32;
-constexpr int TMEM_COLS = 256;                          // two 128-column accumulators
+constexpr int TMEM_COLS = 512;                          // two buffers of two 128-column accumulators
 constexpr long long WAIT_CYCLES = 4000000000LL;
 // bf16 x bf16 -> f32, M = 128, N = 128, both operands K-major
-constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 
 struct Bars {
     unsigned long long full_a[STAGES];
@@ -176,9 +178,9 @@ gemm_q8_bf16x3_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_c
                     const int s = it % STAGES;
                     if (!wait_bar(bars, &bars->empty[s], ((it / STAGES) & 1) ^ 1, a.status)) { tile = n_tiles; break; }
                     unsigned char* st = smem + s * STAGE_BYTES;
-                    mbar_expect_tx(&bars->full_a[s], 2 * TILE_BYTES);
+                    mbar_expect_tx(&bars->full_a[s], 2 * A_BYTES);
                     tma_load_2d(st, &map_hi, kb * BK, m0, &bars->full_a[s]);
-                    tma_load_2d(st + TILE_BYTES, &map_lo, kb * BK, m0, &bars->full_a[s]);
+                    tma_load_2d(st + A_BYTES, &map_lo, kb * BK, m0, &bars->full_a[s]);
                 }
             }
         }
@@ -193,7 +195,7 @@ gemm_q8_bf16x3_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_c
                 ok = wait_bar(bars, &bars->acc_empty[buf], ((ti >> 1) & 1) ^ 1, a.status);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t acc = tmem + (uint32_t)(buf * BN);
+                const uint32_t acc = tmem + (uint32_t)(buf * 2 * BN);     // rows 0..127 here, rows 128..255 at + BN
                 for (int kb = 0; kb < nkb && ok; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t par = (it / STAGES) & 1;
@@ -201,14 +203,17 @@ gemm_q8_bf16x3_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_c
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t base = s32(smem + s * STAGE_BYTES);
-                    const uint64_t ah = smem_desc(base), al = smem_desc(base + TILE_BYTES);
-                    const uint64_t bh = smem_desc(base + 2 * TILE_BYTES), bl = smem_desc(base + 3 * TILE_BYTES);
+                    const uint64_t bh = smem_desc(base + 2 * A_BYTES), bl = smem_desc(base + 2 * A_BYTES + TILE_BYTES);
 #pragma unroll
-                    for (int ks = 0; ks < BK / 16; ++ks) {
-                        const uint64_t adv = (uint64_t)(ks * 2);        // 32 bytes per k-step of 16 bf16
-                        umma(acc, ah + adv, bh + adv, (kb | ks) != 0);
-                        umma(acc, al + adv, bh + adv, 1);
-                        umma(acc, ah + adv, bl + adv, 1);
+                    for (int hm = 0; hm < 2; ++hm) {                     // the two 128-row halves of the X tile
+                        const uint64_t ah = smem_desc(base + hm * TILE_BYTES), al = smem_desc(base + A_BYTES + hm * TILE_BYTES);
+#pragma unroll
+                        for (int ks = 0; ks < BK / 16; ++ks) {
+                            const uint64_t adv = (uint64_t)(ks * 2);    // 32 bytes per k-step of 16 bf16
+                            umma(acc + hm * BN, ah + adv, bh + adv, (kb | ks) != 0);
+                            umma(acc + hm * BN, al + adv, bh + adv, 1);
+                            umma(acc + hm * BN, ah + adv, bl + adv, 1);
+                        }
                     }
                     umma_commit(&bars->empty[s]);                    // frees the stage when the MMAs retire
                 }
@@ -246,7 +251,7 @@ gemm_q8_bf16x3_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_c
                     sc[kb & 1] = __half2float(__ldg(drow + (kb + 2) * 2));
                 }
                 if (!wait_bar(bars, &bars->empty[s], ((it / STAGES) & 1) ^ 1, a.status)) { tile = n_tiles; break; }
-                unsigned char* bhi = smem + s * STAGE_BYTES + 2 * TILE_BYTES + row * 128;
+                unsigned char* bhi = smem + s * STAGE_BYTES + 2 * A_BYTES + row * 128;
                 unsigned char* blo = bhi + TILE_BYTES;
                 const uint32_t ws[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
 #pragma unroll
@@ -274,11 +279,12 @@ gemm_q8_bf16x3_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_c
             const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
             if (!wait_bar(bars, &bars->acc_full[buf], (ti >> 1) & 1, a.status)) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int m = m0 + warp * 32 + lane;
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
+            for (int cc = 0; cc < 2 * (BN / 32); ++cc) {
+                const int hm = cc / (BN / 32), c = cc % (BN / 32);       // 128-row half, 32-column chunk
+                const int m = m0 + hm * 128 + warp * 32 + lane;
                 uint32_t r[32];
-                const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(buf * BN + c * 32);
+                const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)((buf * 2 + hm) * BN + c * 32);
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                     "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -289,7 +295,7 @@ gemm_q8_bf16x3_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_c
                       "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                     : "r"(taddr) : "memory");
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (c == BN / 32 - 1) {
+                if (cc == 2 * (BN / 32) - 1) {
                     // the accumulator is in registers: hand the TMEM buffer back to the MMA warp
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     __syncwarp();
@@ -392,7 +398,7 @@ int encode_plane(CUtensorMap* map, const void* plane, int M, int K) {
     }
     const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
     const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)BM};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)BM};   // 64 x 256: two 128-row MMA tiles
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)plane, dims, strides, box, estr,
                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
