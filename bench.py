@@ -33,6 +33,8 @@ import numpy as np  # noqa: E402
 PROMPT, NEW_TOKENS = 32, 256
 N_SEQ, SEQ_LEN = 512, 1024
 METRIC = "Q8_0 GPT-2-small decode tokens/s (batch 1, KV cache, greedy)"
+# dram__bytes_read.sum + dram__bytes_write.sum of decode_mega_kernel per token (ncu, see profiles/)
+DECODE_DRAM_BYTES_PER_TOKEN = 131.0e6 + 0.75e6
 
 
 def peaks():
@@ -190,6 +192,13 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    def sum_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return float(t.item())
+
     hbm_peak, tf_peak, peak_kind = peaks()
     # decode always runs fp32 FMA; the prefill GEMMs of scoring run the tensor-core math mode
     sm = synth.named("small", seed=0, math_mode=fcb.FC_MATH_FP32 if args.score_math == "fp32" else fcb.FC_MATH_BF16X3)
@@ -240,8 +249,10 @@ def main():
                     "note": "fc_generate_greedy from pinned host buffers: prompt upload, 32-token prime, 256 feeds, token download"},
             "gpu_launches": int(launches),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
-                         "traffic": None, "peak_kind": peak_kind,
-                         "what": "one decode step (all kernels of one token): %.1f MB algorithmic per token" % (bpt / 1e6)},
+                         "traffic": DECODE_DRAM_BYTES_PER_TOKEN * 32, "peak_kind": peak_kind,
+                         "what": "decode_mega_kernel, launches of 32 tokens: %.1f MB algorithmic per token; traffic = "
+                                 "ncu dram read+write of a 7-token launch (131.0 + 0.75 MB per token, "
+                                 "profiles/decode_mega_kernel_gpt2small_7tokens.md) scaled to 32 tokens" % (bpt / 1e6)},
             "clocks": clocks,
         }
 
@@ -286,7 +297,7 @@ def main():
             "gpu_launches": int(s_launch),
             "roofline": {"bound": "tensor", "achieved": fl / (step_ms / 1e3) / 1e12, "peak": tf_peak, "unit": "TFLOP/s",
                          "frac": fl / (step_ms / 1e3) / 1e12 / tf_peak, "traffic": None, "peak_kind": peak_kind},
-            "checksum_logprob": float(sum(s.logprob for s in scores)),
+            "checksum_logprob": sum_over_ranks(float(sum(s.logprob for s in scores))),
         }
         if out:
             out["score"] = score

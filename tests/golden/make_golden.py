@@ -21,7 +21,7 @@ from tests import oracle as O  # noqa: E402
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 # name -> (prompt length, new tokens, scoring sequences kept, scoring sequence length)
-PLAN = {"tiny": (16, 64, 4, 128), "small": (32, 256, 1, 1024)}
+PLAN = {"tiny": (16, 64, 4, 128), "small": (32, 256, 1, 1024), "medium": (64, 16, 1, 256)}
 
 
 def make(name):

@@ -286,3 +286,19 @@ def test_scoring_bf16x3_small_matches_golden():
     err = np.abs(lp - g["logprob"]).max()
     assert err < LOGPROB_TOL, f"max abs log-prob error {err:.3e}"
     gm.close()
+
+
+@pytest.mark.parametrize("m,k,n", [(1100, 128, 4096), (4096, 768, 2304), (2304, 256, 3072)])
+def test_q8_0_linear_bf16x3_many_tiles_per_cta(m, k, n):
+    """More output tiles than SMs: every persistent CTA walks several tiles, reusing its stage ring
+    and both TMEM accumulators. Repeated to catch ordering races; the fp32 kernel is the yardstick."""
+    wq = synth.q8_0_quantize(synth.Rng(21).normal(n * k, 0.02))
+    x = synth.Rng(22).normal(m * k, 1.0).reshape(m, k)
+    want = fcb.q8_0_linear(x, wq, None, n, math_mode=fcb.FC_MATH_FP32)
+    scale = np.abs(want).max()
+    first = None
+    for _ in range(3):
+        got = fcb.q8_0_linear(x, wq, None, n, math_mode=fcb.FC_MATH_BF16X3)
+        assert np.abs(got - want).max() <= 1e-4 * scale
+        first = got if first is None else first
+        assert np.array_equal(got, first), "run-to-run determinism"
