@@ -66,6 +66,8 @@ SIGNATURES = {
     "fc_feed": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p]),
     "fc_prime": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "fc_generate_greedy": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int32, C.c_void_p, C.c_void_p, C.POINTER(C.c_int)]),
+    "fc_decode_batch": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int32, C.c_void_p, C.c_void_p]),
+    "fc_last_batch_ms": (C.c_float, [C.c_void_p]),
     "fc_take_launch_count": (C.c_int64, []),
     "fc_last_decode_ms": (C.c_float, [C.c_void_p]),
     "fc_last_score_ms": (C.c_float, [C.c_void_p]),

@@ -150,6 +150,9 @@ struct fc_model {
     MegaLayer* mega_layers = nullptr;
     float* mega_lnf = nullptr;
     int mega_grid = 0;
+    // streams created by fc_decode_batch, kept for the next call
+    std::vector<fc_stream*> pool;
+    float last_batch_ms = 0.0f;
 };
 
 struct fc_stream {
@@ -638,6 +641,8 @@ void fc_model_free(fc_model* m) {
     if (!m) return;
     cudaSetDevice(m->device);
     if (m->st) cudaStreamSynchronize(m->st);
+    for (fc_stream* s : m->pool) fc_stream_free(s);
+    m->pool.clear();
     m->arena.release();
     m->ws_arena.release();
     if (m->ev0) cudaEventDestroy(m->ev0);
@@ -1022,5 +1027,29 @@ int fc_generate_greedy(fc_stream* s, const int32_t* prompt, int n, int max_new, 
     if (cancelled) return fail(FC_E_CANCELLED, "generation cancelled after %d tokens", made);
     return FC_OK;
 }
+
+// Independent greedy streams on one GPU (the 64-stream workload is split over GPUs above the
+// ABI). Each stream is a CachedTransformer of its own; they run back to back on the model's
+// CUDA stream, every one through the persistent decode kernel.
+int fc_decode_batch(fc_model* m, int n_streams, const int32_t* prompts, int prompt_len, int max_new, int32_t eos,
+                    int32_t* out, int* n_out) {
+    if (!m || !prompts || !n_out || (max_new > 0 && !out)) return fail(FC_E_ARG, "fc_decode_batch: null argument");
+    if (n_streams < 0 || prompt_len <= 0 || max_new < 0) return fail(FC_E_SHAPE, "fc_decode_batch: bad sizes");
+    FC_CUDA(cudaSetDevice(m->device));
+    while ((int)m->pool.size() < n_streams) {
+        fc_stream* s = nullptr;
+        FC_TRY(fc_stream_create(m, &s));
+        m->pool.push_back(s);
+    }
+    m->last_batch_ms = 0.0f;
+    for (int i = 0; i < n_streams; ++i) {
+        FC_TRY(fc_generate_greedy(m->pool[i], prompts + (size_t)i * prompt_len, prompt_len, max_new, eos, nullptr,
+                                  out + (size_t)i * max_new, n_out + i));
+        m->last_batch_ms += m->pool[i]->last_decode_ms;
+    }
+    return FC_OK;
+}
+
+float fc_last_batch_ms(const fc_model* m) { return m ? m->last_batch_ms : 0.0f; }
 
 }  // extern "C"

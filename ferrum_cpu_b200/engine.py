@@ -186,6 +186,19 @@ class CudaSlm:
         check(rc)
         return buf[:n_out.value].copy(), False
 
+    def decode_batch(self, prompts2d, max_tokens, eos=-1):
+        """Independent greedy streams (rows of prompts2d) on this GPU; returns a list of id arrays."""
+        prompts = _ids(prompts2d)
+        n, plen = prompts.shape
+        out = np.zeros((n, max(max_tokens, 1)), dtype=np.int32)
+        n_out = np.zeros(n, dtype=np.int32)
+        check(_lib.lib().fc_decode_batch(self._m, n, _ptr(prompts), plen, max_tokens, eos, _ptr(out), _ptr(n_out)))
+        return [out[i, :n_out[i]].copy() for i in range(n)]
+
+    @property
+    def last_batch_ms(self):
+        return _lib.lib().fc_last_batch_ms(self._m)
+
     @property
     def last_decode_ms(self):
         return _lib.lib().fc_last_decode_ms(self._stream())

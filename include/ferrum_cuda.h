@@ -198,6 +198,14 @@ int fc_prime(fc_stream* s, const int32_t* ids, int n, float* probs);
 int fc_generate_greedy(fc_stream* s, const int32_t* prompt, int n, int max_new, int32_t eos,
                        const volatile int32_t* cancel, int32_t* out, int* n_out);
 
+/* n_streams independent greedy generations on one GPU: prompts [n_streams][prompt_len], out
+ * [n_streams][max_new], n_out [n_streams]. Each is token_stream.rs:66-189 with temperature <= 0
+ * on its own KV caches; the streams of a GPU currently run one after the other (weights are
+ * streamed once per stream and token). Device time of the feeds: fc_last_batch_ms. */
+int fc_decode_batch(fc_model* m, int n_streams, const int32_t* prompts, int prompt_len, int max_new, int32_t eos,
+                    int32_t* out, int* n_out);
+float fc_last_batch_ms(const fc_model* m);
+
 /* ---- introspection used by the benchmark ----------------------------------------- */
 /* Kernel launches issued by this library on the calling thread since the last call
  * (returns the count and resets it). */

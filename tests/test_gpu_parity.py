@@ -302,3 +302,37 @@ def test_q8_0_linear_bf16x3_many_tiles_per_cta(m, k, n):
         assert np.abs(got - want).max() <= 1e-4 * scale
         first = got if first is None else first
         assert np.array_equal(got, first), "run-to-run determinism"
+
+
+# ---- GPT-2-medium-shaped configuration (batched decode + scoring) ---------------------------
+@pytest.fixture(scope="module")
+def medium():
+    sm = synth.named("medium", seed=0, math_mode=fcb.FC_MATH_BF16X3)
+    return sm, fcb.CudaSlm(sm.config, sm.weights)
+
+
+def test_medium_decode_streams_match_golden_and_each_other(medium):
+    path = os.path.join(GOLD, "decode_medium.npz")
+    if not os.path.exists(path):
+        pytest.skip("decode_medium.npz has not been generated")
+    g = np.load(path)
+    sm, gm = medium
+    V = sm.dims[5]
+    # stream 0 is the fixture's prompt; the others are independent prompts of the same length
+    prompts = np.stack([g["prompt"]] + [synth.token_ids(100 + i, len(g["prompt"]), V) for i in range(3)])
+    outs = gm.decode_batch(prompts, len(g["tokens"]))
+    check_greedy(outs[0], g["tokens"], g["margin"])
+    # a stream decodes the same alone as inside a batch
+    alone, _ = gm.generate_tokens(prompts[2], len(g["tokens"]))
+    assert np.array_equal(alone, outs[2])
+
+
+def test_medium_scoring_matches_golden(medium):
+    path = os.path.join(GOLD, "score_medium.npz")
+    if not os.path.exists(path):
+        pytest.skip("score_medium.npz has not been generated")
+    g = np.load(path)
+    sm, gm = medium
+    scores, lp = gm.score_sequences(g["ids"], batch_windows=2)
+    err = np.abs(lp - g["logprob"]).max()
+    assert err < LOGPROB_TOL, f"max abs log-prob error {err:.3e}"
