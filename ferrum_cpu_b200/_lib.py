@@ -63,6 +63,7 @@ SIGNATURES = {
     "fc_stream_set_mode": (C.c_int, [C.c_void_p, C.c_int]),
     "fc_stream_set_trace": (C.c_int, [C.c_void_p, C.c_int]),
     "fc_stream_read_trace": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int]),
+    "fc_stream_read_trace_cta": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int]),
     "fc_feed": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p]),
     "fc_prime": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "fc_generate_greedy": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int32, C.c_void_p, C.c_void_p, C.POINTER(C.c_int)]),

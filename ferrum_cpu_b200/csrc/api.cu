@@ -177,7 +177,7 @@ struct fc_stream {
     unsigned long long* trace = nullptr;   // phase timeline of the persistent kernel
     int trace_on = 0;
 };
-static constexpr int kTraceCap = 1024;
+static constexpr int kTraceCap = 256;   // timeline entries per CTA
 
 namespace fc {
 
@@ -251,14 +251,14 @@ static int run_mega(fc_stream* s, int n, int head_from, int select, int probs) {
     p.tok = m->tok; p.head = m->head; p.pos = m->pos; p.lnfpack = m->mega_lnf;
     p.layers = m->mega_layers;
     p.kc = s->kc; p.vc = s->vc;
-    p.qg = s->q; p.partg = s->partg; p.x1g = s->x1g; p.xg = s->x; p.hidg = s->hid;
+    p.qg = s->q; p.attg = s->att; p.partg = s->partg; p.x1g = s->x1g; p.xg = s->x; p.hidg = s->hid;
     p.logits = s->logits; p.statg = s->statg; p.probs = probs ? s->probs : nullptr;
     p.queue = s->queue; p.queue_cap = s->queue_cap; p.state = s->state;
     p.bar = s->bar; p.status = s->status;
     p.n_steps = n; p.head_from = head_from; p.select = select; p.attn_splits = s->attn_splits;
     p.trace = s->trace_on ? s->trace : nullptr;
     p.trace_cap = kTraceCap;
-    if (p.trace) FC_CUDA(cudaMemsetAsync(s->trace, 0, kTraceCap * sizeof(unsigned long long), m->st));
+    if (p.trace) FC_CUDA(cudaMemsetAsync(s->trace, 0, (size_t)m->mega_grid * kTraceCap * sizeof(unsigned long long), m->st));
     return launch_decode_mega(p, m->mega_grid, m->st);
 }
 
@@ -847,7 +847,7 @@ int fc_stream_create(fc_model* m, fc_stream** out) {
         if (rc == FC_OK) rc = a.alloc_n(&s->bar, 1);
         if (rc == FC_OK) rc = a.alloc_n(&s->status, 1);
         if (rc == FC_OK && cudaMemsetAsync(s->status, 0, sizeof(int), m->st) != cudaSuccess) rc = fail(FC_E_CUDA, "status word initialisation failed");
-        if (rc == FC_OK) rc = a.alloc_n(&s->trace, (size_t)kTraceCap);
+        if (rc == FC_OK) rc = a.alloc_n(&s->trace, (size_t)m->mega_grid * kTraceCap);
         s->use_mega = 1;
     }
     if (rc == FC_OK && (cudaEventCreate(&s->ev0) != cudaSuccess || cudaEventCreate(&s->ev1) != cudaSuccess)) rc = fail(FC_E_CUDA, "event creation failed");
@@ -885,13 +885,16 @@ int fc_stream_set_trace(fc_stream* s, int on) {
     return FC_OK;
 }
 
-int fc_stream_read_trace(fc_stream* s, uint64_t* out, int cap) {
+int fc_stream_read_trace(fc_stream* s, uint64_t* out, int cap) { return fc_stream_read_trace_cta(s, 0, out, cap); }
+
+int fc_stream_read_trace_cta(fc_stream* s, int cta, uint64_t* out, int cap) {
     if (!s || !out || cap < 0) return fail(FC_E_ARG, "fc_stream_read_trace: bad argument");
     if (!s->trace) return 0;
+    if (cta < 0 || cta >= s->m->mega_grid) return fail(FC_E_ARG, "fc_stream_read_trace: the kernel runs %d CTAs", s->m->mega_grid);
     FC_CUDA(cudaSetDevice(s->m->device));
     FC_CUDA(cudaStreamSynchronize(s->m->st));
     std::vector<unsigned long long> h(kTraceCap);
-    FC_CUDA(cudaMemcpy(h.data(), s->trace, kTraceCap * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+    FC_CUDA(cudaMemcpy(h.data(), s->trace + (size_t)cta * kTraceCap, kTraceCap * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
     int n = 0;
     while (n < kTraceCap && n < cap && h[n] != 0) { out[n] = h[n]; ++n; }
     return n;

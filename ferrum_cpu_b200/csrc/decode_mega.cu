@@ -194,12 +194,12 @@ struct Cta {
 
 __device__ __forceinline__ bool timed_out(long long t0) { return clock64() - t0 > WAIT_CYCLES; }
 
-// Phase timeline: one thread of CTA 0 stores the global timer at every phase boundary.
+// Phase timeline: thread 0 of every CTA stores the global timer at every phase boundary.
 __device__ __forceinline__ void mark(Cta& k) {
     if (k.trace_n >= 0 && k.trace_n < k.p.trace_cap) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        k.p.trace[k.trace_n++] = t;
+        k.p.trace[(size_t)k.c * k.p.trace_cap + k.trace_n++] = t;
     }
 }
 
@@ -405,16 +405,21 @@ __device__ bool consume_matrix(Cta& k, const QMat& w, int kind, Epi epi) {
     return true;
 }
 
-// CTAs per head for a context of `len` keys: about 64 keys per CTA, at most attn_splits. Fewer
-// partials mean fewer loads of the same lines by every CTA in the combine phase.
+// CTAs per head for a context of `len` keys. Up to kWholeHead keys one CTA handles the whole
+// head and writes the finished attention output: the split into partials costs an extra grid
+// barrier and a combine phase, which only pays once a single CTA would need many sweeps.
+// Beyond that about 64 keys per CTA, at most attn_splits.
+constexpr int kWholeHead = 384;
 __device__ __forceinline__ int attn_splits_for(const MegaParams& p, int len) {
+    if (len <= kWholeHead) return 1;
     return max(1, min(p.attn_splits, (len + 63) >> 6));
 }
 
 // transformer.rs:246-283 split over CTAs: CTA (h, s) handles keys [s*len/S, (s+1)*len/S) of
-// head h and writes (max, sum-exp, unnormalised out[hd]) to partg. Inside the CTA every warp
-// runs an online softmax over its own keys (no CTA-wide synchronisation while keys are
-// processed); the 16 warp partials are combined once at the end in a fixed order.
+// head h. Inside the CTA every warp runs an online softmax over its own keys, four keys per
+// step (no CTA-wide synchronisation while keys are processed); the 16 warp partials are
+// combined once at the end in a fixed order. With S == 1 the result is the head's attention
+// output, written to attg; otherwise (max, sum-exp, unnormalised out[hd]) go to partg.
 __device__ void attention_partial(Cta& k, int l, int len) {
     const MegaParams& p = k.p;
     const int S = attn_splits_for(p, len), hd = p.d / p.H;
@@ -423,7 +428,6 @@ __device__ void attention_partial(Cta& k, int l, int len) {
     const int j0 = (int)((long long)s * len / S), j1 = (int)((long long)(s + 1) * len / S);
     const float* kc = p.kc + (size_t)l * p.T * p.d + hs;
     const float* vc = p.vc + (size_t)l * p.T * p.d + hs;
-    float* out = p.partg + (size_t)k.c * (hd + 2);
     const int lane = k.tid & 31, wid = k.tid >> 5;
     // each lane owns head dimensions lane and lane + 32 (hd <= 64)
     const bool has0 = lane < hd, has1 = lane + 32 < hd;
@@ -431,35 +435,60 @@ __device__ void attention_partial(Cta& k, int l, int len) {
     const float q1 = has1 ? __ldcg(p.qg + hs + lane + 32) : 0.0f;
     const float scale = 1.0f / sqrtf((float)hd);
     float m = -INFINITY, lsum = 0.0f, o0 = 0.0f, o1 = 0.0f;
-    // warp wid owns keys j0 + wid, j0 + wid + 16, ...; four keys per sweep, whose K and V rows
-    // are all requested before the first use
-    for (int jb = j0 + wid; jb < j1; jb += CWARPS * 4) {
-        float a0[4], a1[4], v0[4], v1[4];
+    // warp wid owns keys j0 + wid, j0 + wid + 16, ...; the K and V rows of four keys are
+    // requested together, one step ahead of the arithmetic, and their dot products reduced
+    // side by side
+    struct Rows { float a0[4], a1[4], v0[4], v1[4]; };
+    auto request = [&](Rows& r, int jb) {
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
             const int j = jb + u * CWARPS;
             const bool on = j < j1;
             const size_t off = (size_t)j * p.d;
-            a0[u] = (on && has0) ? __ldcg(kc + off + lane) : 0.0f;
-            a1[u] = (on && has1) ? __ldcg(kc + off + lane + 32) : 0.0f;
-            v0[u] = (on && has0) ? __ldcg(vc + off + lane) : 0.0f;
-            v1[u] = (on && has1) ? __ldcg(vc + off + lane + 32) : 0.0f;
+            r.a0[u] = (on && has0) ? __ldcg(kc + off + lane) : 0.0f;
+            r.a1[u] = (on && has1) ? __ldcg(kc + off + lane + 32) : 0.0f;
+            r.v0[u] = (on && has0) ? __ldcg(vc + off + lane) : 0.0f;
+            r.v1[u] = (on && has1) ? __ldcg(vc + off + lane + 32) : 0.0f;
         }
+    };
+    auto absorb = [&](const Rows& r, int jb) {
+        float dot[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) dot[u] = fmaf(q1, r.a1[u], q0 * r.a0[u]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) dot[u] += __shfl_xor_sync(0xffffffffu, dot[u], o);
+        }
+        // keys past the range score -inf and weigh 0; the first key of a step is always live
+        float mn = m;
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-            if (jb + u * CWARPS < j1) {                 // warp-uniform
-                float dot = fmaf(q1, a1[u], q0 * a0[u]);
+            dot[u] = (jb + u * CWARPS < j1) ? dot[u] * scale : -INFINITY;
+            mn = fmaxf(mn, dot[u]);
+        }
+        const float corr = expf(m - mn);                // m == -inf: 0
+        float pj[4];
 #pragma unroll
-                for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-                const float sv = dot * scale;
-                const float mn = fmaxf(m, sv);
-                const float corr = expf(m - mn);        // m == -inf: 0
-                const float pj = expf(sv - mn);
-                lsum = fmaf(lsum, corr, pj);
-                o0 = fmaf(o0, corr, pj * v0[u]);
-                o1 = fmaf(o1, corr, pj * v1[u]);
-                m = mn;
-            }
+        for (int u = 0; u < 4; ++u) pj[u] = expf(dot[u] - mn);
+        lsum = fmaf(lsum, corr, (pj[0] + pj[1]) + (pj[2] + pj[3]));
+        o0 = fmaf(o0, corr, fmaf(pj[0], r.v0[0], pj[1] * r.v0[1]) + fmaf(pj[2], r.v0[2], pj[3] * r.v0[3]));
+        o1 = fmaf(o1, corr, fmaf(pj[0], r.v1[0], pj[1] * r.v1[1]) + fmaf(pj[2], r.v1[2], pj[3] * r.v1[3]));
+        m = mn;
+    };
+    {
+        constexpr int STEP = CWARPS * 4;
+        Rows ra, rb;
+        int jb = j0 + wid;
+        if (jb < j1) request(ra, jb);
+        while (jb < j1) {
+            if (jb + STEP < j1) request(rb, jb + STEP);
+            absorb(ra, jb);
+            jb += STEP;
+            if (jb >= j1) break;
+            if (jb + STEP < j1) request(ra, jb + STEP);
+            absorb(rb, jb);
+            jb += STEP;
         }
     }
     float* part = k.act;                                // act is free during the attention phase
@@ -468,20 +497,31 @@ __device__ void attention_partial(Cta& k, int l, int len) {
     mine[2 + lane] = o0;
     mine[2 + 32 + lane] = o1;
     consumer_sync();
-    if (k.tid < hd) {
-        float M = -INFINITY;
+    if (k.tid < 64) {
+        // warps 0 and 1 each work out the 16 rescaling factors (lane w: warp w) and share them
+        // by shuffles; thread t then owns output dimension t
+        const float mw = lane < CWARPS ? part[lane * 66] : -INFINITY;
+        float M = mw;
 #pragma unroll
-        for (int w = 0; w < CWARPS; ++w) M = fmaxf(M, part[w * 66]);
+        for (int o = 8; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+        M = __shfl_sync(0xffffffffu, M, 0);
+        const float f = mw > -INFINITY ? expf(mw - M) : 0.0f;
+        const float lf = lane < CWARPS ? part[lane * 66 + 1] * f : 0.0f;
         float Lsum = 0.0f, O = 0.0f;
 #pragma unroll
         for (int w = 0; w < CWARPS; ++w) {
-            const float mw = part[w * 66];
-            const float f = mw > -INFINITY ? expf(mw - M) : 0.0f;
-            Lsum = fmaf(part[w * 66 + 1], f, Lsum);
-            O = fmaf(part[w * 66 + 2 + k.tid], f, O);
+            Lsum += __shfl_sync(0xffffffffu, lf, w);
+            O = fmaf(k.tid < hd ? part[w * 66 + 2 + k.tid] : 0.0f, __shfl_sync(0xffffffffu, f, w), O);
         }
-        out[2 + k.tid] = O;
-        if (k.tid == 0) { out[0] = M; out[1] = Lsum; }
+        if (k.tid < hd) {
+            if (S == 1) {
+                p.attg[hs + k.tid] = O / Lsum;
+            } else {
+                float* out = p.partg + (size_t)k.c * (hd + 2);
+                out[2 + k.tid] = O;
+                if (k.tid == 0) { out[0] = M; out[1] = Lsum; }
+            }
+        }
     }
 }
 
@@ -573,7 +613,7 @@ __device__ void consumer(Cta& k) {
         }
         consumer_sync();
         // the phase timeline covers the last step of the launch
-        k.trace_n = (p.trace && k.c == 0 && k.tid == 0 && step + 1 == p.n_steps) ? 0 : -1;
+        k.trace_n = (p.trace && k.tid == 0 && step + 1 == p.n_steps) ? 0 : -1;
         mark(k);
         const int len = pos + 1;
         bool ok = true;
@@ -602,7 +642,8 @@ __device__ void consumer(Cta& k) {
             ok = grid_barrier(k);
             if (!ok) break;
             mark(k);
-            attention_combine(k, len);
+            if (attn_splits_for(p, len) == 1) load_vec(k, p.attg, k.act, d, true);
+            else attention_combine(k, len);
             mark(k);
             // out-proj + residual: x1 = x + (W att + b)
             ok = consume_matrix(k, L.out, W_OUT, [&](int n, int i, float v) { p.x1g[n] = k.xs[n] + (v + bias[boff[1] + i]); });

@@ -52,6 +52,7 @@ struct MegaParams {
     float *kc, *vc;            // f32 KV caches [L][T][d]
     // exchange buffers in global memory (written by some CTAs, read by all after a barrier)
     float* qg;                 // [d] query row
+    float* attg;               // [d] attention output (contexts short enough for one CTA per head)
     float* partg;              // [H * attn_splits][hd + 2] attention partials (max, sum, out)
     float *x1g, *xg;           // [d] residual stream after attention / after the MLP
     float* hidg;               // [F] GELU output
@@ -67,8 +68,9 @@ struct MegaParams {
     int head_from;             // steps before this index skip the LM head
     int select;                // head steps pick the next token greedily and append it
     int attn_splits;           // CTAs per head in the attention phase
-    // Optional phase timeline (tracing): when non-null, CTA 0 stores the global nanosecond
-    // timer at every phase boundary of the launch's last step; entry 0 is the step start.
+    // Optional phase timeline (tracing): when non-null, every CTA stores the global nanosecond
+    // timer at every phase boundary of the launch's last step in its row [trace_cap] of the
+    // buffer; entry 0 is the step start.
     unsigned long long* trace;
     int trace_cap;
 };

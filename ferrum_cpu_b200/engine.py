@@ -158,14 +158,15 @@ class CudaSlm:
     def set_trace(self, on):
         check(_lib.lib().fc_stream_set_trace(self._stream(), int(on)))
 
-    def read_trace(self):
-        """Phase timeline (ns, relative to the token start) of the last traced token."""
-        buf = np.zeros(1024, dtype=np.uint64)
-        n = _lib.lib().fc_stream_read_trace(self._stream(), _ptr(buf), buf.size)
+    def read_trace(self, cta=0, absolute=False):
+        """Phase timeline (ns) of CTA `cta` for the last traced token: relative to that CTA's
+        token start, or the raw timer values when `absolute`."""
+        buf = np.zeros(256, dtype=np.uint64)
+        n = _lib.lib().fc_stream_read_trace_cta(self._stream(), cta, _ptr(buf), buf.size)
         if n < 0:
             check(n)
         t = buf[:n].astype(np.int64)
-        return t - t[0] if n else t
+        return t if absolute or not n else t - t[0]
 
     def set_decode_mode(self, mode):
         """0: persistent decode kernel (default), 1: one kernel per layer operation."""

@@ -180,9 +180,12 @@ int fc_stream_set_mode(fc_stream* s, int mode);
  * nanosecond timer at every phase boundary of the last token of each launch:
  * entry 0 = token start, then 15 entries per block (LayerNorm1, QKV, barrier, attention,
  * barrier, combine, out-proj, barrier, LayerNorm2, up, barrier, load, down, barrier, load),
- * then the head phases. fc_stream_read_trace returns the number of entries copied (or < 0). */
+ * then the head phases. Every CTA of the kernel keeps its own
+ * timeline (up to 256 entries): fc_stream_read_trace copies CTA 0's, fc_stream_read_trace_cta
+ * that of CTA `cta`; both return the number of entries copied (or < 0). */
 int fc_stream_set_trace(fc_stream* s, int on);
 int fc_stream_read_trace(fc_stream* s, uint64_t* out, int cap);
+int fc_stream_read_trace_cta(fc_stream* s, int cta, uint64_t* out, int cap);
 int fc_cached_len(const fc_stream* s);
 /* cached.rs:100-125 feed: one token; probs (host [V]) may be NULL. FC_E_DIM on id >= vocab
  * or a full cache (transformer.rs:237-242). */
