@@ -125,6 +125,16 @@ __device__ __forceinline__ void split2(float w0, float w1, uint32_t* hi, uint32_
     *lo = *(const uint32_t*)&l;
 }
 
+// 256-bit global accesses: one full 32-byte sector per lane and instruction.
+__device__ __forceinline__ void st256(void* p, const uint32_t* v) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]) : "memory");
+}
+__device__ __forceinline__ void ld256(const void* p, uint32_t* v) {
+    asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]) : "l"(p) : "memory");
+}
+
 struct TcArgs {
     const uint8_t* qu; const __half* d; int N, K;
     const float* bias; const float* residual; int epi;
@@ -250,20 +260,25 @@ gemm_q8_bf16x3_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_c
                     qc[kb & 1] = __ldg((const uint4*)(qrow + (size_t)(kb + 2) * BK) + 1);
                     sc[kb & 1] = __half2float(__ldg(drow + (kb + 2) * 2));
                 }
+                // the conversion runs before the stage is waited for: only the stores sit between
+                // the stage becoming free and becoming full again
+                const uint32_t ws[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+                uint4 hi[4], lo[4];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {        // 16-byte chunk c of this half: 8 weights
+                    split2(scale * qb<0>(ws[2 * c]), scale * qb<1>(ws[2 * c]), &hi[c].x, &lo[c].x);
+                    split2(scale * qb<2>(ws[2 * c]), scale * qb<3>(ws[2 * c]), &hi[c].y, &lo[c].y);
+                    split2(scale * qb<0>(ws[2 * c + 1]), scale * qb<1>(ws[2 * c + 1]), &hi[c].z, &lo[c].z);
+                    split2(scale * qb<2>(ws[2 * c + 1]), scale * qb<3>(ws[2 * c + 1]), &hi[c].w, &lo[c].w);
+                }
                 if (!wait_bar(bars, &bars->empty[s], ((it / STAGES) & 1) ^ 1, a.status)) { tile = n_tiles; break; }
                 unsigned char* bhi = smem + s * STAGE_BYTES + 2 * A_BYTES + row * 128;
                 unsigned char* blo = bhi + TILE_BYTES;
-                const uint32_t ws[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {        // 16-byte chunk c of this half: 8 weights
-                    uint4 hi, lo;
-                    split2(scale * qb<0>(ws[2 * c]), scale * qb<1>(ws[2 * c]), &hi.x, &lo.x);
-                    split2(scale * qb<2>(ws[2 * c]), scale * qb<3>(ws[2 * c]), &hi.y, &lo.y);
-                    split2(scale * qb<0>(ws[2 * c + 1]), scale * qb<1>(ws[2 * c + 1]), &hi.z, &lo.z);
-                    split2(scale * qb<2>(ws[2 * c + 1]), scale * qb<3>(ws[2 * c + 1]), &hi.w, &lo.w);
+                for (int c = 0; c < 4; ++c) {
                     const int chunk = ((half * 4 + c) ^ (row & 7)) * 16;   // 128-byte swizzle
-                    *(uint4*)(bhi + chunk) = hi;
-                    *(uint4*)(blo + chunk) = lo;
+                    *(uint4*)(bhi + chunk) = hi[c];
+                    *(uint4*)(blo + chunk) = lo[c];
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> tensor-core reads
                 __syncwarp();
@@ -273,6 +288,8 @@ gemm_q8_bf16x3_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_c
     } else {
         // ---------------------------------------------------------------- epilogue (warps 0-3)
         const bool vec_ok = (a.ldy & 3) == 0;
+        // rows of 32 columns start on 32-byte boundaries: whole-sector accesses
+        const bool vec8_ok = (a.ldy & 7) == 0 && (((uintptr_t)a.y | (uintptr_t)a.residual) & 31) == 0;
         int ti = 0;
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++ti) {
             const int buf = ti & 1;
@@ -314,7 +331,15 @@ gemm_q8_bf16x3_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_c
                     v[i] = t;
                 }
                 if (a.residual) {
-                    if (full && vec_ok) {
+                    if (full && vec8_ok) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            uint32_t rr[8];
+                            ld256(a.residual + off + 8 * i, rr);
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) v[8 * i + j] = __uint_as_float(rr[j]) + v[8 * i + j];
+                        }
+                    } else if (full && vec_ok) {
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
                             const float4 rr = *(const float4*)(a.residual + off + 4 * i);
@@ -328,7 +353,15 @@ gemm_q8_bf16x3_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_c
                     }
                 }
                 if (a.y) {
-                    if (full && vec_ok) {
+                    if (full && vec8_ok) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            uint32_t w[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) w[j] = __float_as_uint(v[8 * i + j]);
+                            st256(a.y + off + 8 * i, w);
+                        }
+                    } else if (full && vec_ok) {
 #pragma unroll
                         for (int i = 0; i < 8; ++i)
                             *(float4*)(a.y + off + 4 * i) = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
@@ -342,10 +375,18 @@ gemm_q8_bf16x3_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_c
                     uint32_t hi[16], lo[16];
 #pragma unroll
                     for (int i = 0; i < 16; ++i) split2(v[2 * i], v[2 * i + 1], &hi[i], &lo[i]);
+                    if ((((uintptr_t)a.yhi | (uintptr_t)a.ylo) & 31) == 0 && (a.ldy & 15) == 0) {
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        *(uint4*)(a.yhi + off + 8 * i) = make_uint4(hi[4 * i], hi[4 * i + 1], hi[4 * i + 2], hi[4 * i + 3]);
-                        *(uint4*)(a.ylo + off + 8 * i) = make_uint4(lo[4 * i], lo[4 * i + 1], lo[4 * i + 2], lo[4 * i + 3]);
+                        for (int i = 0; i < 2; ++i) {
+                            st256(a.yhi + off + 16 * i, hi + 8 * i);
+                            st256(a.ylo + off + 16 * i, lo + 8 * i);
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            *(uint4*)(a.yhi + off + 8 * i) = make_uint4(hi[4 * i], hi[4 * i + 1], hi[4 * i + 2], hi[4 * i + 3]);
+                            *(uint4*)(a.ylo + off + 8 * i) = make_uint4(lo[4 * i], lo[4 * i + 1], lo[4 * i + 2], lo[4 * i + 3]);
+                        }
                     }
                 }
                 }
