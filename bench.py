@@ -34,7 +34,7 @@ PROMPT, NEW_TOKENS = 32, 256
 N_SEQ, SEQ_LEN = 512, 1024
 METRIC = "Q8_0 GPT-2-small decode tokens/s (batch 1, KV cache, greedy)"
 # dram__bytes_read.sum + dram__bytes_write.sum of decode_mega_kernel per token (ncu, see profiles/)
-DECODE_DRAM_BYTES_PER_TOKEN = 131.0e6 + 0.75e6
+DECODE_DRAM_BYTES_PER_TOKEN = 128.9e6 + 3.65e6
 
 
 def peaks():
@@ -172,7 +172,7 @@ def main():
     import torch.distributed as dist
 
     import ferrum_cpu_b200 as fcb
-    from ferrum_cpu_b200 import synth
+    from ferrum_cpu_b200 import shard, synth
 
     if fcb.device_count() < 1:
         raise SystemExit("bench.py needs a B200: libferrum_cuda has no CPU fallback")
@@ -251,15 +251,16 @@ def main():
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                          "traffic": DECODE_DRAM_BYTES_PER_TOKEN * 32, "peak_kind": peak_kind,
                          "what": "decode_mega_kernel, launches of 32 tokens: %.1f MB algorithmic per token; traffic = "
-                                 "ncu dram read+write of a 7-token launch (131.0 + 0.75 MB per token, "
+                                 "ncu dram read+write of a 6-token launch (128.9 + 3.65 MB per token, "
                                  "profiles/decode_mega_kernel_gpt2small_7tokens.md) scaled to 32 tokens" % (bpt / 1e6)},
             "clocks": clocks,
         }
 
     if args.workload in ("score", "both"):
-        per = N_SEQ // world
         ids_all = synth.token_ids(1, N_SEQ * SEQ_LEN, V).reshape(N_SEQ, SEQ_LEN)
-        mine = torch.from_numpy(ids_all[rank * per:(rank + 1) * per].copy()).pin_memory()
+        first, last = shard.shard_range(N_SEQ, rank, world)      # contiguous block of sequences per rank
+        per = last - first
+        mine = torch.from_numpy(ids_all[first:last].copy()).pin_memory()
         lp = torch.empty((per, SEQ_LEN), dtype=torch.float32).pin_memory()
         bw = 64
         gm.score_sequences(mine.numpy()[:bw], batch_windows=bw, lp_out=lp.numpy()[:bw])   # warm-up (allocates the workspace)
@@ -271,10 +272,8 @@ def main():
             torch.cuda.synchronize()
             t0 = time.perf_counter()
             scores, _ = gm.score_sequences(mine.numpy(), batch_windows=bw, lp_out=lp.numpy())
-            if world > 1:   # the one collective of the path: gather the per-token log-probs
-                g = lp.cuda(non_blocking=True)
-                parts = [torch.empty_like(g) for _ in range(world)] if rank == 0 else None
-                dist.gather(g, parts, dst=0)
+            if world > 1:   # the one collective of the path: gather the per-token log-probs to rank 0
+                shard.gather_rows(lp.numpy(), N_SEQ, rank, world, device=torch.device("cuda", local))
                 torch.cuda.synchronize()
             wall.append(time.perf_counter() - t0)
             dev_ms.append(gm.last_score_ms)
@@ -282,13 +281,13 @@ def main():
         s_launch = fcb.take_launch_count()
         step_ms = max_over_ranks(sum(dev_ms) / len(dev_ms))
         e2e_s = max_over_ranks(sum(wall) / len(wall))
-        positions = per * world * SEQ_LEN
+        positions = N_SEQ * SEQ_LEN
         fl = score_flops_per_position(dims) * positions
         score = {
             "metric": "Q8_0 GPT-2-small log-likelihood positions/s", "value": positions / (step_ms / 1e3), "unit": "positions/s",
             "n_gpus": world, "steps": args.score_steps, "ms_per_step": step_ms, "scaling": "strong" if world > 1 else "n/a",
             "config": {"workload": "configs[2]: %d sequences x %d ids, full-window prefill, per-token log-probs, %d windows per forward"
-                       % (per * world, SEQ_LEN, bw),
+                       % (N_SEQ, SEQ_LEN, bw),
                        "math": "linear layers: tcgen05 kind::f16, bf16 3-term split of f32 operands, fp32 TMEM accumulate"
                                if args.score_math == "bf16x3" else "fp32 CUDA cores"},
             "dtype": "bf16x3" if args.score_math == "bf16x3" else "f32",

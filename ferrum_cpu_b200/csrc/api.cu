@@ -142,7 +142,7 @@ struct fc_model {
     // tensor path: bf16 hi / lo planes of LayerNorm output, qkv, attention output, GELU output
     uint16_t *nhi = nullptr, *nlo = nullptr, *qkvhi = nullptr, *qkvlo = nullptr;
     uint16_t *atthi = nullptr, *attlo = nullptr, *hidhi = nullptr, *hidlo = nullptr;
-    int* tc_status = nullptr;                  // raised by the tensor-core GEMM on a timeout
+    int* tc_status = nullptr;                  // raised by a scoring kernel (tensor-core GEMM, attention, row tail) on a timeout
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     float last_score_ms = 0.0f;
     // persistent decode kernel: per-layer parameter table on the device, grid size (0: the
@@ -336,9 +336,9 @@ static int ensure_workspace(fc_model* m, int rows) {
             FC_TRY(a.alloc_n(&m->atthi, R * d));     FC_TRY(a.alloc_n(&m->attlo, R * d));
             FC_TRY(a.alloc_n(&m->hidhi, R * F));     FC_TRY(a.alloc_n(&m->hidlo, R * F));
         }
-        FC_TRY(a.alloc_n(&m->tc_status, 1));
-        FC_CUDA(cudaMemsetAsync(m->tc_status, 0, sizeof(int), m->st));
     }
+    FC_TRY(a.alloc_n(&m->tc_status, 1));
+    FC_CUDA(cudaMemsetAsync(m->tc_status, 0, sizeof(int), m->st));
     m->ws_rows = rows;
     m->head_chunk = (int)chunk;
     return FC_OK;
@@ -412,7 +412,7 @@ static int score_device(fc_model* m, int B, int T) {
                                             m->logits, nullptr, nullptr, rows, ldl, m->tc_status, m->st));
         else
             FC_TRY(gemm(m, m->head, m->n + (size_t)r0 * d, nullptr, nullptr, EPI_NONE, m->logits, rows, ldl));
-        FC_TRY(launch_score_rows(m->logits, ldl, c.vocab, m->targets_d + r0, rows, m->lp_d + r0, m->gr_d + r0, m->st));
+        FC_TRY(launch_score_rows(m->logits, ldl, c.vocab, m->targets_d + r0, rows, m->lp_d + r0, m->gr_d + r0, m->tc_status, m->st));
     }
     return FC_OK;
 }
@@ -685,7 +685,7 @@ static int score_windows_impl(fc_model* m, const int32_t* ids, const int32_t* ta
     FC_CUDA(cudaStreamSynchronize(st));
     if (tc_status != 0) {
         cudaMemsetAsync(m->tc_status, 0, sizeof(int), st);
-        return fail(FC_E_TIMEOUT, "a bounded wait inside the tensor-core GEMM ran out (status %d)", tc_status);
+        return fail(FC_E_TIMEOUT, "a bounded wait inside a scoring kernel ran out (status %d)", tc_status);
     }
     float ms = 0.0f;
     FC_CUDA(cudaEventElapsedTime(&ms, m->ev0, m->ev1));
@@ -910,9 +910,72 @@ int fc_stream_set_mode(fc_stream* s, int mode) {
 }
 float fc_last_decode_ms(const fc_stream* s) { return s ? s->last_decode_ms : 0.0f; }
 
+__global__ void bump_state_kernel(StepState* st, int by) {
+    if (st->done | st->error) return;
+    st->pos += by;
+    st->fed += by;
+}
+
+// CachedTransformer::prime (slm/cached.rs:129-136) feeds the ids one at a time; on an empty
+// cache the same rows come out of ONE window forward (TransformerBlock::forward,
+// layer/transformer.rs:314-534, equals forward_with_cache row by row: transformer.rs:669-716),
+// so the n ids in queue[0..n) go through every block as an n-row batch in fp32, each block's
+// K and V rows are copied into the stream's caches, and only the last row meets the head.
+// Short prompts stay on the token-by-token path: below kPrimeBatchMin rows the 128-row GEMM
+// tiles are mostly padding and one persistent-kernel launch is as fast.
+// Returns FC_OK with *used = 0 when the shape is not covered (the caller feeds token by token).
+constexpr int kPrimeBatchMin = 48;
+static int prime_batched(fc_stream* s, int n, int last_mode, int* used) {
+    fc_model* m = s->m;
+    const fc_config& c = m->cfg;
+    const int d = c.d_model, F = c.d_ff, hd = d / c.n_head;
+    *used = 0;
+    if (n < kPrimeBatchMin || s->host_pos != 0 || (hd != 32 && hd != 64)) return FC_OK;
+    cudaStream_t st = m->st;
+    FC_TRY(ensure_workspace(m, n));
+    FC_CUDA(cudaMemcpyAsync(m->ids_d, s->queue, (size_t)n * sizeof(int), cudaMemcpyDeviceToDevice, st));
+    FC_CUDA(cudaMemsetAsync(m->err_d, 0, sizeof(int), st));
+    FC_TRY(launch_embed_rows(m->tok, m->pos, m->ids_d, n, n, m->x, m->err_d, st));
+    const size_t layer_stride = (size_t)c.ctx * d;
+    for (int l = 0; l < c.n_layer; ++l) {
+        const LayerDev& L = m->layers[l];
+        FC_TRY(launch_layernorm(m->x, L.ln1g, L.ln1b, n, d, m->n, nullptr, st));
+        FC_TRY(launch_gemm_q8_fp32(L.qkv, m->n, L.qkv_b, nullptr, EPI_NONE, m->qkv, n, 3 * d, st));
+        // rows [q | k | v] -> cache positions 0..n-1
+        FC_CUDA(cudaMemcpy2DAsync(s->kc + l * layer_stride, (size_t)d * 4, m->qkv + d, (size_t)3 * d * 4, (size_t)d * 4, n,
+                                  cudaMemcpyDeviceToDevice, st));
+        FC_CUDA(cudaMemcpy2DAsync(s->vc + l * layer_stride, (size_t)d * 4, m->qkv + 2 * d, (size_t)3 * d * 4, (size_t)d * 4, n,
+                                  cudaMemcpyDeviceToDevice, st));
+        FC_TRY(launch_attn_prefill(m->qkv, 1, n, d, c.n_head, m->att, st));
+        FC_TRY(launch_gemm_q8_fp32(L.out, m->att, L.out_b, m->x, EPI_NONE, m->x, n, d, st));
+        FC_TRY(launch_layernorm(m->x, L.ln2g, L.ln2b, n, d, m->n, nullptr, st));
+        FC_TRY(launch_gemm_q8_fp32(L.up, m->n, L.up_b, nullptr, EPI_GELU, m->hid, n, F, st));
+        FC_TRY(launch_gemm_q8_fp32(L.down, m->hid, L.down_b, m->x, EPI_NONE, m->x, n, d, st));
+    }
+    *used = 1;
+    if (last_mode == STEP_NOHEAD) {
+        bump_state_kernel<<<1, 1, 0, st>>>(s->state, n);
+        FC_LAUNCHED();
+        return FC_OK;
+    }
+    // the head sees the last row only; its tail advances the position by one
+    bump_state_kernel<<<1, 1, 0, st>>>(s->state, n - 1);
+    FC_LAUNCHED();
+    FC_TRY(launch_layernorm(m->x + (size_t)(n - 1) * d, m->lnfg, m->lnfb, 1, d, s->n, s->state, st));
+    GemvOut ol; ol.out[0] = s->logits;
+    FC_TRY(launch_gemv_q8(m->head, s->n, nullptr, nullptr, EPI_NONE, ol, s->state, st));
+    return launch_step_tail(s->logits, c.vocab, last_mode == STEP_PROBS ? s->probs : nullptr, last_mode == STEP_SELECT ? 1 : 0,
+                            s->queue, s->queue_cap, s->state, nullptr, st);
+}
+
 // Feeds queue[0..n) (already uploaded) from the current position; the last step runs in
 // `last_mode`, the ones before it skip the head (its output would be discarded).
-static int feed_queued(fc_stream* s, int n, int last_mode) { return run_steps(s, n, STEP_NOHEAD, last_mode); }
+static int feed_queued(fc_stream* s, int n, int last_mode) {
+    int used = 0;
+    FC_TRY(prime_batched(s, n, last_mode, &used));
+    if (used) return FC_OK;
+    return run_steps(s, n, STEP_NOHEAD, last_mode);
+}
 
 static int feed_ids(fc_stream* s, const int32_t* ids, int n, float* probs) {
     fc_model* m = s->m;

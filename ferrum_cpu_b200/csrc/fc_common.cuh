@@ -116,8 +116,9 @@ int launch_step_tail(const float* logits, int V, float* probs_or_null, int do_se
 // End-of-step bookkeeping alone (steps that skip the head).
 int launch_step_advance(StepState* state, cudaStream_t st);
 // Scoring tail: per row of logits[R][ldl], target id (or -1) -> logprob, is_greedy.
+// `status` (device int, may be null) is raised to FC_E_TIMEOUT when a bounded wait runs out.
 int launch_score_rows(const float* logits, int ldl, int V, const int* targets, int R, double* logprob,
-                      uint8_t* is_greedy, cudaStream_t st);
+                      uint8_t* is_greedy, int* status, cudaStream_t st);
 int launch_softmax_row(const float* logits, int V, float* probs, cudaStream_t st);
 
 // attn.cu

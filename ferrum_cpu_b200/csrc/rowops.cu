@@ -306,8 +306,97 @@ __global__ void __launch_bounds__(256) score_rows_kernel(const float* __restrict
     }
 }
 
+// The same tail with the row staged in shared memory: one CTA per SM walks rows, fetches a
+// whole row of logits with one bulk async copy (a single pass over HBM, hundreds of KB in flight
+// per SM) and makes its three passes (max, sum of exponentials + first maximal index, target)
+// out of shared memory. Same arithmetic per row as score_rows_kernel with 1024 threads.
+// Bound: HBM, 4 * ldl bytes per scored row.
+constexpr int STAGED_THREADS = 1024;
+constexpr long long STAGED_WAIT_CYCLES = 4000000000LL;
+__global__ void __launch_bounds__(STAGED_THREADS, 1)
+score_rows_staged_kernel(const float* __restrict__ logits, int ldl, int V, const int* __restrict__ targets, int R,
+                         double* __restrict__ logprob, uint8_t* __restrict__ is_greedy, int* status) {
+    extern __shared__ __align__(16) float srow[];
+    __shared__ float red[33];
+    __shared__ int ired[32];
+    __shared__ unsigned long long bar;
+    const uint32_t bar_a = (uint32_t)__cvta_generic_to_shared(&bar);
+    if (threadIdx.x == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_a) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    const uint32_t bytes = (uint32_t)ldl * 4u;
+    uint32_t copies = 0;                                   // bulk copies issued so far (phase parity)
+    for (int r = blockIdx.x; r < R; r += gridDim.x) {
+        const int target = targets[r];
+        if (target < 0 || target >= V) {
+            if (threadIdx.x == 0) { logprob[r] = 0.0; is_greedy[r] = 0; }
+            continue;
+        }
+        bool failed = false;
+        if (threadIdx.x == 0) {
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_a), "r"(bytes) : "memory");
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                         ::"r"((uint32_t)__cvta_generic_to_shared(srow)), "l"(logits + (size_t)r * ldl), "r"(bytes), "r"(bar_a) : "memory");
+            const long long t0 = clock64();
+            for (;;) {
+                uint32_t ok;
+                asm volatile(
+                    "{\n\t.reg .pred p;\n\t"
+                    "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+                    "selp.u32 %0, 1, 0, p;\n\t}"
+                    : "=r"(ok) : "r"(bar_a), "r"(copies & 1u), "r"(2000u) : "memory");
+                if (ok) break;
+                if (clock64() - t0 > STAGED_WAIT_CYCLES) { failed = true; break; }
+            }
+        }
+        ++copies;
+        if (__syncthreads_or(failed)) {                      // the row never arrived: report and stop
+            if (threadIdx.x == 0) atomicExch(status, FC_E_TIMEOUT);
+            break;
+        }
+        float mx = -INFINITY;
+        for (int i = threadIdx.x; i < V; i += STAGED_THREADS) mx = fmaxf(mx, srow[i]);
+        mx = block_max(mx, red);
+        float s = 0.0f;
+        int first = 0x7fffffff;          // first index whose probability ties the maximum's
+        for (int i = threadIdx.x; i < V; i += STAGED_THREADS) {
+            const float e = expf(srow[i] - mx);
+            s += e;
+            if (e == 1.0f && i < first) first = i;
+        }
+        const float sum = block_sum(s, red);
+        for (int o = 16; o > 0; o >>= 1) first = min(first, __shfl_xor_sync(0xffffffffu, first, o));
+        if ((threadIdx.x & 31) == 0) ired[threadIdx.x >> 5] = first;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            for (int w = 1; w < STAGED_THREADS / 32; ++w) first = min(first, ired[w]);
+            float p = expf(srow[target] - mx) / sum;
+            if (p == p) p = fmaxf(p, 1e-12f);
+            logprob[r] = log((double)p);
+            is_greedy[r] = (uint8_t)(first == target);
+        }
+        __syncthreads();                                     // the row buffer is free for the next copy
+    }
+}
+
 int launch_score_rows(const float* logits, int ldl, int V, const int* targets, int R, double* logprob,
-                      uint8_t* is_greedy, cudaStream_t st) {
+                      uint8_t* is_greedy, int* status, cudaStream_t st) {
+    static int sms[64] = {};
+    const size_t smem = (size_t)ldl * 4;
+    int dev = 0;
+    FC_CUDA(cudaGetDevice(&dev));
+    // rows staged in shared memory when a row fits and the copy is legal (16-byte multiples)
+    if (status && dev < 64 && smem <= 200 * 1024 && (ldl & 3) == 0 && (((uintptr_t)logits) & 15) == 0 && R > 0) {
+        if (!sms[dev]) {
+            FC_CUDA(cudaFuncSetAttribute(score_rows_staged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+            FC_CUDA(cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev));
+        }
+        score_rows_staged_kernel<<<R < sms[dev] ? R : sms[dev], STAGED_THREADS, smem, st>>>(logits, ldl, V, targets, R, logprob, is_greedy, status);
+        FC_LAUNCHED();
+        return FC_OK;
+    }
     score_rows_kernel<<<R, 256, 0, st>>>(logits, ldl, V, targets, logprob, is_greedy);
     FC_LAUNCHED();
     return FC_OK;

@@ -117,6 +117,30 @@ def test_per_kernel_and_persistent_decode_agree(tiny):
     assert np.abs(logp(out[0][1]) - logp(ref)).max() < FP32_LOGPROB_TOL
 
 
+def test_batched_prime_equals_token_by_token_prime(tiny):
+    """prime() on an empty cache runs the ids as one window forward; feeding them one at a time
+    (cached.rs:129-136 as written) must leave the same cache and the same next-token row."""
+    sm, om, gm = tiny
+    V = sm.dims[5]
+    ids = synth.token_ids(23, 60, V)                    # long enough for the batched path
+    p_batched = gm.prime(ids)
+    assert gm.cached_len() == len(ids)
+    nxt = [gm.feed(t) for t in (5, 9, 2)]              # continue from the batched cache
+    gm.reset()
+    for t in ids[:-1]:
+        gm.feed(t, want_probs=False)                    # one token per call: the step path
+    p_steps = gm.feed(ids[-1])
+    nxt2 = [gm.feed(t) for t in (5, 9, 2)]
+    assert np.abs(logp(p_batched) - logp(p_steps)).max() < 1e-4
+    for a, b in zip(nxt, nxt2):
+        assert np.abs(logp(a) - logp(b)).max() < 1e-4
+    om.reset()
+    po = om.prime(ids)
+    assert np.abs(logp(p_batched) - logp(po)).max() < FP32_LOGPROB_TOL
+    # short prompts stay on the step path
+    assert np.abs(logp(gm.prime(ids[:3])) - logp(om.prime(ids[:3]))).max() < FP32_LOGPROB_TOL
+
+
 def test_greedy_reprimes_past_the_context(mini):
     sm, om, gm = mini
     prompt = synth.token_ids(9, 4, 96)
