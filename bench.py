@@ -264,6 +264,9 @@ def main():
         lp = torch.empty((per, SEQ_LEN), dtype=torch.float32).pin_memory()
         bw = 64
         gm.score_sequences(mine.numpy()[:bw], batch_windows=bw, lp_out=lp.numpy()[:bw])   # warm-up (allocates the workspace)
+        if world > 1:   # warm-up of the gather too: NCCL opens its peer channels on the first send
+            shard.gather_rows(lp.numpy(), N_SEQ, rank, world, device=torch.device("cuda", local))
+            torch.cuda.synchronize()
         fcb.take_launch_count()
         dev_ms, wall = [], []
         barrier()
@@ -294,8 +297,10 @@ def main():
             "e2e": {"value": positions / e2e_s, "unit": "positions/s", "h2d_bytes_per_step": per * SEQ_LEN * 4,
                     "d2h_bytes_per_step": per * SEQ_LEN * 4 + per * 24},
             "gpu_launches": int(s_launch),
-            "roofline": {"bound": "tensor", "achieved": fl / (step_ms / 1e3) / 1e12, "peak": tf_peak, "unit": "TFLOP/s",
-                         "frac": fl / (step_ms / 1e3) / 1e12 / tf_peak, "traffic": None, "peak_kind": peak_kind},
+            # per GPU: every rank runs the same kernels on its own block of sequences
+            "roofline": {"bound": "tensor", "achieved": fl / world / (step_ms / 1e3) / 1e12, "peak": tf_peak, "unit": "TFLOP/s",
+                         "frac": fl / world / (step_ms / 1e3) / 1e12 / tf_peak, "traffic": None, "peak_kind": peak_kind,
+                         "what": "per GPU: algorithmic FLOP of the rank's sequences / its step time"},
             "checksum_logprob": sum_over_ranks(float(sum(s.logprob for s in scores))),
         }
         if out:
