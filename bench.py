@@ -154,7 +154,9 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", choices=["decode", "score", "both"], default="both")
+    ap.add_argument("--workload", choices=["decode", "score", "both", "streams-medium"], default="both",
+                    help="both: configs[1] decode (+ 8 side-by-side streams) and configs[2] scoring; streams-medium: the decode "
+                         "half of configs[4] on the GPT-2-medium shape (64 streams split over the ranks)")
     ap.add_argument("--score-steps", type=int, default=2)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -200,6 +202,31 @@ def main():
         return float(t.item())
 
     hbm_peak, tf_peak, peak_kind = peaks()
+    if args.workload == "streams-medium":
+        # configs[4], decode half: 64 streams of 64-id prompts + 128 greedy tokens, split over the ranks
+        smm = synth.named("medium", seed=0)
+        gmm = fcb.CudaSlm(smm.config, smm.weights, device=local)
+        a0, a1 = shard.shard_range(64, rank, world)
+        prompts = np.stack([synth.token_ids(200 + i, 64, smm.dims[5]) for i in range(a0, a1)])
+        gmm.decode_batch(prompts, 128)
+        ms = []
+        barrier()
+        for _ in range(args.steps):
+            gmm.decode_batch(prompts, 128)
+            ms.append(gmm.last_batch_ms)
+        barrier()
+        step_ms = max_over_ranks(sum(ms) / len(ms))
+        if rank == 0:
+            print(json.dumps({"metric": "Q8_0 GPT-2-medium decode tokens/s, 64 concurrent streams (configs[4])", "value": 64 * 128 / (step_ms / 1e3),
+                              "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "ms_per_step": step_ms, "higher_is_better": True,
+                              "scaling": "strong", "dtype": "f32", "data": "synthetic",
+                              "config": {"workload": "configs[4] decode: L24 d1024 H16 F4096 ctx1024 V50257, 64 streams x (64-id prompt + 128 greedy tokens), "
+                                                     "%d streams per GPU, up to 8 side by side; prompts primed as one batch per wave; device time "
+                                                     "includes the primes" % (a1 - a0)}}))
+        gmm.close()
+        if world > 1:
+            dist.destroy_process_group()
+        return
     # decode always runs fp32 FMA; the prefill GEMMs of scoring run the tensor-core math mode
     sm = synth.named("small", seed=0, math_mode=fcb.FC_MATH_FP32 if args.score_math == "fp32" else fcb.FC_MATH_BF16X3)
     dims = sm.dims
@@ -255,6 +282,21 @@ def main():
                                  "profiles/decode_mega_kernel_gpt2small_7tokens.md) scaled to 32 tokens" % (bpt / 1e6)},
             "clocks": clocks,
         }
+        # the per-GPU share of configs[4]'s 64 streams (8 at 8 GPUs), on this model: side-by-side persistent kernels
+        sp = np.stack([synth.token_ids(200 + 8 * rank + i, 64, V) for i in range(8)])
+        gm.decode_batch(sp, 128)
+        ms = []
+        barrier()
+        for _ in range(3):
+            gm.decode_batch(sp, 128)
+            ms.append(gm.last_batch_ms)
+        barrier()
+        sb_ms = max_over_ranks(sum(ms) / len(ms))
+        out["decode_streams"] = {"metric": "Q8_0 GPT-2-small decode tokens/s, 8 concurrent streams per GPU", "value": world * 8 * 128 / (sb_ms / 1e3),
+                                 "unit": "tokens/s", "ms_per_step": sb_ms, "n_gpus": world,
+                                 "config": {"workload": "8 streams per GPU x (64-id prompt + 128 greedy tokens), one persistent kernel per stream on "
+                                                        "an eighth of the SMs; device time includes the batched prime of the 8 prompts"},
+                                 "gpu_launches": int(fcb.take_launch_count())}
 
     if args.workload in ("score", "both"):
         ids_all = synth.token_ids(1, N_SEQ * SEQ_LEN, V).reshape(N_SEQ, SEQ_LEN)

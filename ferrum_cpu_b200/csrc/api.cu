@@ -122,6 +122,13 @@ const QMat* qweight_matrix(const fc_qweight* w, int* device) {
 }
 }  // namespace fc
 
+// Per-CTA parameter tables of the persistent decode kernel for one grid size.
+struct MegaTable {
+    int grid = 0;
+    int bias_pack = 0;
+    fc::MegaLayer* layers = nullptr;
+};
+
 struct fc_model {
     fc_config cfg;
     int device;
@@ -147,9 +154,9 @@ struct fc_model {
     float last_score_ms = 0.0f;
     // persistent decode kernel: per-layer parameter table on the device, grid size (0: the
     // model's shape is outside what that kernel supports)
-    MegaLayer* mega_layers = nullptr;
+    std::vector<MegaTable> mega_tables;  // [0]: the whole GPU; then halves, quarters, eighths
     float* mega_lnf = nullptr;
-    int mega_grid = 0;
+    int mega_grid = 0;                   // grid of mega_tables[0]
     // streams created by fc_decode_batch, kept for the next call
     std::vector<fc_stream*> pool;
     float last_batch_ms = 0.0f;
@@ -174,6 +181,11 @@ struct fc_stream {
     int* status = nullptr;
     int attn_splits = 1;
     int use_mega = 0;
+    // fc_decode_batch: index of the parameter table (grid size) this stream's launches use, and
+    // the CUDA stream they go to (null: the model's)
+    int table = 0;
+    cudaStream_t cs = nullptr;
+    cudaEvent_t cs_done = nullptr;
     unsigned long long* trace = nullptr;   // phase timeline of the persistent kernel
     int trace_on = 0;
 };
@@ -249,17 +261,21 @@ static int run_mega(fc_stream* s, int n, int head_from, int select, int probs) {
     MegaParams p;
     p.L = c.n_layer; p.d = c.d_model; p.H = c.n_head; p.F = c.d_ff; p.T = c.ctx; p.V = c.vocab;
     p.tok = m->tok; p.head = m->head; p.pos = m->pos; p.lnfpack = m->mega_lnf;
-    p.layers = m->mega_layers;
+    const MegaTable& tab = m->mega_tables[s->table];
+    p.layers = tab.layers;
+    p.bias_pack = tab.bias_pack;
     p.kc = s->kc; p.vc = s->vc;
     p.qg = s->q; p.attg = s->att; p.partg = s->partg; p.x1g = s->x1g; p.xg = s->x; p.hidg = s->hid;
     p.logits = s->logits; p.statg = s->statg; p.probs = probs ? s->probs : nullptr;
     p.queue = s->queue; p.queue_cap = s->queue_cap; p.state = s->state;
     p.bar = s->bar; p.status = s->status;
-    p.n_steps = n; p.head_from = head_from; p.select = select; p.attn_splits = s->attn_splits;
+    p.n_steps = n; p.head_from = head_from; p.select = select;
+    p.attn_splits = std::max(1, std::min(s->attn_splits, tab.grid / c.n_head));
     p.trace = s->trace_on ? s->trace : nullptr;
     p.trace_cap = kTraceCap;
-    if (p.trace) FC_CUDA(cudaMemsetAsync(s->trace, 0, (size_t)m->mega_grid * kTraceCap * sizeof(unsigned long long), m->st));
-    return launch_decode_mega(p, m->mega_grid, m->st);
+    cudaStream_t st = s->cs ? s->cs : m->st;
+    if (p.trace) FC_CUDA(cudaMemsetAsync(s->trace, 0, (size_t)m->mega_grid * kTraceCap * sizeof(unsigned long long), st));
+    return launch_decode_mega(p, tab.grid, st);
 }
 
 // n steps, the last one in `last_mode`, the ones before it in `mode`.
@@ -560,26 +576,44 @@ static int model_build(fc_model* m, const fc_weights* w) {
         FC_TRY(upload_f32(a, s.ln2_b, d, &L.ln2b, st));
     }
     if (mega_supported(c)) {
-        int grid = 0;
-        FC_TRY(mega_max_grid(&grid));
-        // the head slice and the bias slices of one CTA must fit its shared-memory buffers
-        bool fits = (c.vocab + grid - 1) / grid + 8 <= 1024;
-        for (int cta = 0; cta < grid && fits; ++cta) {
-            int off[4];
-            fits = mega_bias_offsets(d, F, cta, grid, off) <= kMegaBiasPack;
+        int full = 0;
+        FC_TRY(mega_max_grid(&full));
+        // One parameter table per grid size: the full GPU for a single stream, and halves,
+        // quarters and eighths of it for streams decoded side by side (fc_decode_batch).
+        // Per block: the four LayerNorm vectors back to back, and for every CTA of the
+        // persistent kernel the slices of the four bias vectors that belong to its rows.
+        std::vector<float*> lnpacks(c.n_layer, nullptr);
+        std::vector<float> ln((size_t)4 * d);
+        for (int l = 0; l < c.n_layer; ++l) {
+            const fc_layer_weights& s = w->layers[l];
+            std::copy(s.ln1_g, s.ln1_g + d, ln.begin());
+            std::copy(s.ln1_b, s.ln1_b + d, ln.begin() + d);
+            std::copy(s.ln2_g, s.ln2_g + d, ln.begin() + 2 * d);
+            std::copy(s.ln2_b, s.ln2_b + d, ln.begin() + 3 * d);
+            FC_TRY(upload_f32(a, ln.data(), ln.size(), &lnpacks[l], st));
+            FC_CUDA(cudaStreamSynchronize(st));   // ln is reused by the next block
         }
-        if (fits) {
-            // Per block: the four LayerNorm vectors back to back, and for every CTA of the
-            // persistent kernel the slices of the four bias vectors that belong to its rows.
+        std::fill(ln.begin(), ln.end(), 0.0f);
+        std::copy(w->out_norm_g, w->out_norm_g + d, ln.begin());
+        std::copy(w->out_norm_b, w->out_norm_b + d, ln.begin() + d);
+        FC_TRY(upload_f32(a, ln.data(), ln.size(), &m->mega_lnf, st));
+        FC_CUDA(cudaStreamSynchronize(st));
+        for (int div = 1; div <= 8; div *= 2) {
+            const int grid = full / div;
+            if (grid < c.n_head) break;
+            // the head slice and the bias slices of one CTA must fit its shared-memory buffers
+            int pack = 0;
+            for (int cta = 0; cta < grid; ++cta) {
+                int off[4];
+                pack = std::max(pack, mega_bias_offsets(d, F, cta, grid, off));
+            }
+            pack = (pack + 3) & ~3;
+            if ((c.vocab + grid - 1) / grid + 8 > mega_head_rows_max() || pack > kMegaBiasPackMax) break;
             std::vector<MegaLayer> tab(c.n_layer);
-            std::vector<float> ln((size_t)4 * d), bp((size_t)grid * kMegaBiasPack);
+            std::vector<float> bp((size_t)grid * pack);
             for (int l = 0; l < c.n_layer; ++l) {
                 const fc_layer_weights& s = w->layers[l];
                 const LayerDev& L = m->layers[l];
-                std::copy(s.ln1_g, s.ln1_g + d, ln.begin());
-                std::copy(s.ln1_b, s.ln1_b + d, ln.begin() + d);
-                std::copy(s.ln2_g, s.ln2_g + d, ln.begin() + 2 * d);
-                std::copy(s.ln2_b, s.ln2_b + d, ln.begin() + 3 * d);
                 std::fill(bp.begin(), bp.end(), 0.0f);
                 const float* src[4] = {s.attn_qkv_b, s.attn_out_b, s.ffn_up_b, s.ffn_down_b};
                 const int N[4] = {3 * d, d, F, d}, K[4] = {d, d, d, F};
@@ -589,24 +623,23 @@ static int model_build(fc_model* m, const fc_weights* w) {
                     for (int i = 0; i < 4; ++i) {
                         int r0, r1;
                         mega_cta_rows(N[i], K[i], cta, grid, &r0, &r1);
-                        std::copy(src[i] + r0, src[i] + r1, bp.begin() + (size_t)cta * kMegaBiasPack + off[i]);
+                        std::copy(src[i] + r0, src[i] + r1, bp.begin() + (size_t)cta * pack + off[i]);
                     }
                 }
-                float *lnd = nullptr, *bpd = nullptr;
-                FC_TRY(upload_f32(a, ln.data(), ln.size(), &lnd, st));
+                float* bpd = nullptr;
                 FC_TRY(upload_f32(a, bp.data(), bp.size(), &bpd, st));
-                FC_CUDA(cudaStreamSynchronize(st));   // ln / bp are reused by the next block
-                tab[l] = MegaLayer{L.qkv, L.out, L.up, L.down, lnd, bpd};
+                FC_CUDA(cudaStreamSynchronize(st));   // bp is reused by the next block
+                tab[l] = MegaLayer{L.qkv, L.out, L.up, L.down, lnpacks[l], bpd};
             }
-            std::fill(ln.begin(), ln.end(), 0.0f);
-            std::copy(w->out_norm_g, w->out_norm_g + d, ln.begin());
-            std::copy(w->out_norm_b, w->out_norm_b + d, ln.begin() + d);
-            FC_TRY(upload_f32(a, ln.data(), ln.size(), &m->mega_lnf, st));
-            FC_TRY(a.alloc_n(&m->mega_layers, (size_t)c.n_layer));
-            FC_CUDA(cudaMemcpyAsync(m->mega_layers, tab.data(), tab.size() * sizeof(MegaLayer), cudaMemcpyHostToDevice, st));
+            MegaTable t;
+            t.grid = grid;
+            t.bias_pack = pack;
+            FC_TRY(a.alloc_n(&t.layers, (size_t)c.n_layer));
+            FC_CUDA(cudaMemcpyAsync(t.layers, tab.data(), tab.size() * sizeof(MegaLayer), cudaMemcpyHostToDevice, st));
             FC_CUDA(cudaStreamSynchronize(st));
-            m->mega_grid = grid;
+            m->mega_tables.push_back(t);
         }
+        if (!m->mega_tables.empty()) m->mega_grid = m->mega_tables[0].grid;
     }
     FC_CUDA(cudaStreamSynchronize(st));
     return FC_OK;
@@ -862,6 +895,8 @@ void fc_stream_free(fc_stream* s) {
     if (!s) return;
     cudaSetDevice(s->m->device);
     cudaStreamSynchronize(s->m->st);
+    if (s->cs) { cudaStreamSynchronize(s->cs); cudaStreamDestroy(s->cs); }
+    if (s->cs_done) cudaEventDestroy(s->cs_done);
     for (int i = 0; i < 3; ++i) if (s->graph[i]) cudaGraphExecDestroy(s->graph[i]);
     if (s->ev0) cudaEventDestroy(s->ev0);
     if (s->ev1) cudaEventDestroy(s->ev1);
@@ -919,60 +954,71 @@ __global__ void bump_state_kernel(StepState* st, int by) {
 // CachedTransformer::prime (slm/cached.rs:129-136) feeds the ids one at a time; on an empty
 // cache the same rows come out of ONE window forward (TransformerBlock::forward,
 // layer/transformer.rs:314-534, equals forward_with_cache row by row: transformer.rs:669-716),
-// so the n ids in queue[0..n) go through every block as an n-row batch in fp32, each block's
-// K and V rows are copied into the stream's caches, and only the last row meets the head.
+// so the n ids in queue[0..n) of each of the S streams go through every block as S windows of
+// n rows in fp32, each block's K and V rows are copied into the streams' caches, and only the
+// last row of a window meets the head.
 // Short prompts stay on the token-by-token path: below kPrimeBatchMin rows the 128-row GEMM
 // tiles are mostly padding and one persistent-kernel launch is as fast.
 // Returns FC_OK with *used = 0 when the shape is not covered (the caller feeds token by token).
 constexpr int kPrimeBatchMin = 48;
-static int prime_batched(fc_stream* s, int n, int last_mode, int* used) {
-    fc_model* m = s->m;
+static int prime_batched(fc_stream* const* ss, int S, int n, int last_mode, int* used) {
+    fc_model* m = ss[0]->m;
     const fc_config& c = m->cfg;
-    const int d = c.d_model, F = c.d_ff, hd = d / c.n_head;
+    const int d = c.d_model, F = c.d_ff, hd = d / c.n_head, R = S * n;
     *used = 0;
-    if (n < kPrimeBatchMin || s->host_pos != 0 || (hd != 32 && hd != 64)) return FC_OK;
+    if (R < kPrimeBatchMin || n < 2 || (hd != 32 && hd != 64)) return FC_OK;
+    for (int i = 0; i < S; ++i)
+        if (ss[i]->host_pos != 0) return FC_OK;
     cudaStream_t st = m->st;
-    FC_TRY(ensure_workspace(m, n));
-    FC_CUDA(cudaMemcpyAsync(m->ids_d, s->queue, (size_t)n * sizeof(int), cudaMemcpyDeviceToDevice, st));
+    FC_TRY(ensure_workspace(m, R));
+    for (int i = 0; i < S; ++i)
+        FC_CUDA(cudaMemcpyAsync(m->ids_d + (size_t)i * n, ss[i]->queue, (size_t)n * sizeof(int), cudaMemcpyDeviceToDevice, st));
     FC_CUDA(cudaMemsetAsync(m->err_d, 0, sizeof(int), st));
-    FC_TRY(launch_embed_rows(m->tok, m->pos, m->ids_d, n, n, m->x, m->err_d, st));
+    FC_TRY(launch_embed_rows(m->tok, m->pos, m->ids_d, R, n, m->x, m->err_d, st));
     const size_t layer_stride = (size_t)c.ctx * d;
     for (int l = 0; l < c.n_layer; ++l) {
         const LayerDev& L = m->layers[l];
-        FC_TRY(launch_layernorm(m->x, L.ln1g, L.ln1b, n, d, m->n, nullptr, st));
-        FC_TRY(launch_gemm_q8_fp32(L.qkv, m->n, L.qkv_b, nullptr, EPI_NONE, m->qkv, n, 3 * d, st));
-        // rows [q | k | v] -> cache positions 0..n-1
-        FC_CUDA(cudaMemcpy2DAsync(s->kc + l * layer_stride, (size_t)d * 4, m->qkv + d, (size_t)3 * d * 4, (size_t)d * 4, n,
-                                  cudaMemcpyDeviceToDevice, st));
-        FC_CUDA(cudaMemcpy2DAsync(s->vc + l * layer_stride, (size_t)d * 4, m->qkv + 2 * d, (size_t)3 * d * 4, (size_t)d * 4, n,
-                                  cudaMemcpyDeviceToDevice, st));
-        FC_TRY(launch_attn_prefill(m->qkv, 1, n, d, c.n_head, m->att, st));
-        FC_TRY(launch_gemm_q8_fp32(L.out, m->att, L.out_b, m->x, EPI_NONE, m->x, n, d, st));
-        FC_TRY(launch_layernorm(m->x, L.ln2g, L.ln2b, n, d, m->n, nullptr, st));
-        FC_TRY(launch_gemm_q8_fp32(L.up, m->n, L.up_b, nullptr, EPI_GELU, m->hid, n, F, st));
-        FC_TRY(launch_gemm_q8_fp32(L.down, m->hid, L.down_b, m->x, EPI_NONE, m->x, n, d, st));
+        FC_TRY(launch_layernorm(m->x, L.ln1g, L.ln1b, R, d, m->n, nullptr, st));
+        FC_TRY(launch_gemm_q8_fp32(L.qkv, m->n, L.qkv_b, nullptr, EPI_NONE, m->qkv, R, 3 * d, st));
+        // rows [q | k | v] of window i -> cache positions 0..n-1 of stream i
+        for (int i = 0; i < S; ++i) {
+            const float* rows = m->qkv + (size_t)i * n * 3 * d;
+            FC_CUDA(cudaMemcpy2DAsync(ss[i]->kc + l * layer_stride, (size_t)d * 4, rows + d, (size_t)3 * d * 4, (size_t)d * 4, n,
+                                      cudaMemcpyDeviceToDevice, st));
+            FC_CUDA(cudaMemcpy2DAsync(ss[i]->vc + l * layer_stride, (size_t)d * 4, rows + 2 * d, (size_t)3 * d * 4, (size_t)d * 4, n,
+                                      cudaMemcpyDeviceToDevice, st));
+        }
+        FC_TRY(launch_attn_prefill(m->qkv, S, n, d, c.n_head, m->att, st));
+        FC_TRY(launch_gemm_q8_fp32(L.out, m->att, L.out_b, m->x, EPI_NONE, m->x, R, d, st));
+        FC_TRY(launch_layernorm(m->x, L.ln2g, L.ln2b, R, d, m->n, nullptr, st));
+        FC_TRY(launch_gemm_q8_fp32(L.up, m->n, L.up_b, nullptr, EPI_GELU, m->hid, R, F, st));
+        FC_TRY(launch_gemm_q8_fp32(L.down, m->hid, L.down_b, m->x, EPI_NONE, m->x, R, d, st));
     }
     *used = 1;
-    if (last_mode == STEP_NOHEAD) {
-        bump_state_kernel<<<1, 1, 0, st>>>(s->state, n);
+    for (int i = 0; i < S; ++i) {
+        fc_stream* s = ss[i];
+        if (last_mode == STEP_NOHEAD) {
+            bump_state_kernel<<<1, 1, 0, st>>>(s->state, n);
+            FC_LAUNCHED();
+            continue;
+        }
+        // the head sees the last row only; its tail advances the position by one
+        bump_state_kernel<<<1, 1, 0, st>>>(s->state, n - 1);
         FC_LAUNCHED();
-        return FC_OK;
+        FC_TRY(launch_layernorm(m->x + ((size_t)i * n + n - 1) * d, m->lnfg, m->lnfb, 1, d, s->n, s->state, st));
+        GemvOut ol; ol.out[0] = s->logits;
+        FC_TRY(launch_gemv_q8(m->head, s->n, nullptr, nullptr, EPI_NONE, ol, s->state, st));
+        FC_TRY(launch_step_tail(s->logits, c.vocab, last_mode == STEP_PROBS ? s->probs : nullptr, last_mode == STEP_SELECT ? 1 : 0,
+                                s->queue, s->queue_cap, s->state, nullptr, st));
     }
-    // the head sees the last row only; its tail advances the position by one
-    bump_state_kernel<<<1, 1, 0, st>>>(s->state, n - 1);
-    FC_LAUNCHED();
-    FC_TRY(launch_layernorm(m->x + (size_t)(n - 1) * d, m->lnfg, m->lnfb, 1, d, s->n, s->state, st));
-    GemvOut ol; ol.out[0] = s->logits;
-    FC_TRY(launch_gemv_q8(m->head, s->n, nullptr, nullptr, EPI_NONE, ol, s->state, st));
-    return launch_step_tail(s->logits, c.vocab, last_mode == STEP_PROBS ? s->probs : nullptr, last_mode == STEP_SELECT ? 1 : 0,
-                            s->queue, s->queue_cap, s->state, nullptr, st);
+    return FC_OK;
 }
 
 // Feeds queue[0..n) (already uploaded) from the current position; the last step runs in
 // `last_mode`, the ones before it skip the head (its output would be discarded).
 static int feed_queued(fc_stream* s, int n, int last_mode) {
     int used = 0;
-    FC_TRY(prime_batched(s, n, last_mode, &used));
+    FC_TRY(prime_batched(&s, 1, n, last_mode, &used));
     if (used) return FC_OK;
     return run_steps(s, n, STEP_NOHEAD, last_mode);
 }
@@ -1095,24 +1141,108 @@ int fc_generate_greedy(fc_stream* s, const int32_t* prompt, int n, int max_new, 
 }
 
 // Independent greedy streams on one GPU (the 64-stream workload is split over GPUs above the
-// ABI). Each stream is a CachedTransformer of its own; they run back to back on the model's
-// CUDA stream, every one through the persistent decode kernel.
+// ABI). Each stream is a CachedTransformer of its own. Up to eight of them decode side by side:
+// every stream gets its own CUDA stream and a persistent kernel that spans an eighth (quarter,
+// half) of the SMs, so the kernels of a wave are co-resident and their latency-bound phases
+// overlap. The prompts are primed one after the other on the model's stream (the prime shares
+// the model's prefill workspace). Streams that would outgrow the context, and models the
+// persistent kernel does not cover, run one after the other through fc_generate_greedy.
 int fc_decode_batch(fc_model* m, int n_streams, const int32_t* prompts, int prompt_len, int max_new, int32_t eos,
                     int32_t* out, int* n_out) {
     if (!m || !prompts || !n_out || (max_new > 0 && !out)) return fail(FC_E_ARG, "fc_decode_batch: null argument");
     if (n_streams < 0 || prompt_len <= 0 || max_new < 0) return fail(FC_E_SHAPE, "fc_decode_batch: bad sizes");
     FC_CUDA(cudaSetDevice(m->device));
+    const fc_config& c = m->cfg;
     while ((int)m->pool.size() < n_streams) {
         fc_stream* s = nullptr;
         FC_TRY(fc_stream_create(m, &s));
         m->pool.push_back(s);
     }
     m->last_batch_ms = 0.0f;
-    for (int i = 0; i < n_streams; ++i) {
-        FC_TRY(fc_generate_greedy(m->pool[i], prompts + (size_t)i * prompt_len, prompt_len, max_new, eos, nullptr,
-                                  out + (size_t)i * max_new, n_out + i));
-        m->last_batch_ms += m->pool[i]->last_decode_ms;
+    // widest wave the parameter tables allow: table t holds grids of (all SMs) / 2^t
+    int t = 0;
+    while (t + 1 < (int)m->mega_tables.size() && (2 << t) <= n_streams) ++t;
+    const int wave = 1 << t;
+    const bool side_by_side = wave > 1 && max_new > 0 && prompt_len + max_new <= c.ctx;
+    if (!side_by_side) {
+        for (int i = 0; i < n_streams; ++i) {
+            FC_TRY(fc_generate_greedy(m->pool[i], prompts + (size_t)i * prompt_len, prompt_len, max_new, eos, nullptr,
+                                      out + (size_t)i * max_new, n_out + i));
+            m->last_batch_ms += m->pool[i]->last_decode_ms;
+        }
+        return FC_OK;
     }
+    FC_TRY(check_ids(m, prompts, (size_t)n_streams * prompt_len));
+    cudaStream_t st = m->st;
+    int rc = FC_OK;
+    FC_CUDA(cudaEventRecord(m->ev0, st));
+    for (int w0 = 0; w0 < n_streams && rc == FC_OK; w0 += wave) {
+        const int nw = std::min(wave, n_streams - w0);
+        // every prompt of the wave is primed first, on the model's stream with the whole GPU:
+        // as one batch of windows when the shape allows it, else stream by stream; the last
+        // prime step selects token 1
+        std::vector<fc_stream*> wv;
+        for (int i = 0; i < nw && rc == FC_OK; ++i) {
+            fc_stream* s = m->pool[w0 + i];
+            if (!s->use_mega) { rc = fail(FC_E_SHAPE, "fc_decode_batch: a stream is not on the persistent kernel"); break; }
+            if (!s->cs && cudaStreamCreateWithFlags(&s->cs, cudaStreamNonBlocking) != cudaSuccess) { rc = fail(FC_E_CUDA, "stream creation failed"); break; }
+            if (!s->cs_done && cudaEventCreateWithFlags(&s->cs_done, cudaEventDisableTiming) != cudaSuccess) { rc = fail(FC_E_CUDA, "event creation failed"); break; }
+            s->table = 0;
+            rc = fc_stream_reset(s);
+            if (rc == FC_OK && cudaMemcpyAsync(s->queue, prompts + (size_t)(w0 + i) * prompt_len, (size_t)prompt_len * 4,
+                                               cudaMemcpyHostToDevice, st) != cudaSuccess) rc = fail(FC_E_CUDA, "prompt upload failed");
+            if (rc == FC_OK) rc = set_state(s, 0, 0, prompt_len, eos, 0);
+            wv.push_back(s);
+        }
+        int used = 0;
+        if (rc == FC_OK) rc = prime_batched(wv.data(), (int)wv.size(), prompt_len, STEP_SELECT, &used);
+        for (int i = 0; i < nw && rc == FC_OK && !used; ++i) {
+            fc_stream* s = wv[i];
+            cudaStream_t own = s->cs;
+            s->cs = nullptr;
+            rc = run_steps(s, prompt_len, STEP_NOHEAD, STEP_SELECT);
+            s->cs = own;
+        }
+        if (rc != FC_OK) break;
+        // then the decode launches of all its streams, each on its own CUDA stream and on
+        // 1/wave of the SMs, so that the wave's kernels are resident together
+        if (cudaEventRecord(m->ev1, st) != cudaSuccess) { rc = fail(FC_E_CUDA, "event record failed"); break; }
+        for (int i = 0; i < nw && rc == FC_OK; ++i) {
+            fc_stream* s = m->pool[w0 + i];
+            if (cudaStreamWaitEvent(s->cs, m->ev1, 0) != cudaSuccess) { rc = fail(FC_E_CUDA, "stream hand-over failed"); break; }
+            s->table = t;
+            for (int fed = 1; fed < max_new && rc == FC_OK; fed += 32)   // selecting feeds 1 .. max_new - 1
+                rc = run_steps(s, std::min(32, max_new - fed), STEP_SELECT, STEP_SELECT);
+            if (rc == FC_OK) rc = run_steps(s, 1, STEP_PROBS, STEP_PROBS);   // the feed of the last token selects nothing
+            s->table = 0;
+            if (rc == FC_OK && cudaEventRecord(s->cs_done, s->cs) != cudaSuccess) rc = fail(FC_E_CUDA, "event record failed");
+        }
+        // the wave is over when every one of its streams is; the model's stream waits for all
+        for (int i = 0; i < nw; ++i) {
+            fc_stream* s = m->pool[w0 + i];
+            if (s->cs && s->cs_done) cudaStreamWaitEvent(st, s->cs_done, 0);
+        }
+        for (int i = 0; i < nw && rc == FC_OK; ++i) {
+            fc_stream* s = m->pool[w0 + i];
+            StepState hs;
+            rc = read_state(s, &hs);                 // on the model's stream, which has waited for the wave
+            if (rc != FC_OK) break;
+            if (hs.error) { rc = fail(hs.error, "decode step rejected a token or position on the device"); break; }
+            const int have = std::min(hs.tail - prompt_len, max_new);
+            if (have > 0)
+                FC_CUDA(cudaMemcpy(out + (size_t)(w0 + i) * max_new, s->queue + prompt_len, (size_t)have * 4, cudaMemcpyDeviceToHost));
+            n_out[w0 + i] = std::max(have, 0);
+            s->host_pos = hs.pos;
+        }
+    }
+    if (rc != FC_OK) {   // leave nothing in flight behind an error
+        for (fc_stream* s : m->pool) if (s->cs) cudaStreamSynchronize(s->cs);
+        cudaStreamSynchronize(st);
+        return rc;
+    }
+    FC_CUDA(cudaEventRecord(m->ev1, st));
+    FC_CUDA(cudaStreamSynchronize(st));
+    FC_CUDA(cudaEventElapsedTime(&m->last_batch_ms, m->ev0, m->ev1));
     return FC_OK;
 }
 

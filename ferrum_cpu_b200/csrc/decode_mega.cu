@@ -35,8 +35,11 @@ constexpr int SLOTS = 5;
 constexpr int SLOT_Q = 24576;                  // quant bytes per slot
 constexpr int SLOT_D = SLOT_Q / 16;            // scale bytes per slot (2 B per 32 quants)
 constexpr int SLOT_BYTES = SLOT_Q + SLOT_D;
-constexpr int MAX_D = 1024, MAX_F = 4096, MAX_CTX = 1024, MAX_ROWS_HEAD = 1024;
-constexpr int PARAM_FLOATS = 4 * MAX_D + kMegaBiasPack;   // LayerNorm vectors + bias slices
+constexpr int MAX_D = 1024, MAX_F = 4096, MAX_CTX = 1024;
+// The CTA's slice of the logits lives in the activation buffer behind the (d-wide) input of the
+// head. Total shared memory stays below 196 KB: the next carve-out step would halve the L1.
+constexpr int MAX_ROWS_HEAD = MAX_F - MAX_D;
+constexpr int PARAM_FLOATS = 4 * MAX_D + kMegaBiasPackMax;   // LayerNorm vectors + bias slices
 constexpr long long WAIT_CYCLES = 4000000000LL;           // ~2 s at 1.9 GHz
 
 struct Ctrl {
@@ -55,17 +58,15 @@ constexpr int OFF_SLOTS = 0;
 constexpr int OFF_PARAM = OFF_SLOTS + SLOTS * SLOT_BYTES;        // 2 parameter buffers
 constexpr int OFF_ACT = OFF_PARAM + 2 * PARAM_FLOATS * 4;        // activation vector, swizzled float4 units
 constexpr int OFF_XS = OFF_ACT + MAX_F * 4;                      // residual stream x
-constexpr int OFF_SC = OFF_XS + MAX_D * 4;                       // attention scores / head logits slice
-constexpr int OFF_PSUM = OFF_SC + MAX_CTX * 4;                   // 2 x 256 partial sums
+constexpr int OFF_PSUM = OFF_XS + MAX_D * 4;                     // 2 x 256 partial sums
 constexpr int OFF_RED = OFF_PSUM + 2 * 256 * 4;                  // reductions
 constexpr int OFF_LAYERS = OFF_RED + 256 * 4;                    // copy of the layer table
 constexpr int OFF_WORK = OFF_LAYERS + kMegaMaxLayers * (int)sizeof(MegaLayer);   // 5 work descriptors
 constexpr int OFF_CTRL = OFF_WORK + 256;
 constexpr int SMEM_BYTES = OFF_CTRL + (int)sizeof(Ctrl);
-static_assert(MAX_ROWS_HEAD <= MAX_CTX, "head slice shares the score buffer");
 static_assert(sizeof(MegaLayer) % 16 == 0, "layer table entries are copied as 16-byte words");
 static_assert(OFF_PARAM % 16 == 0 && OFF_ACT % 16 == 0 && OFF_LAYERS % 16 == 0 && OFF_CTRL % 8 == 0, "alignment");
-static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
+static_assert(SMEM_BYTES <= 195 * 1024, "shared memory budget: 196 KB carve-out less the 1 KB the system reserves");
 
 // ------------------------------------------------------------------ PTX helpers
 __device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -179,7 +180,7 @@ struct Cta {
     float4* act4;
     float* act;
     float* xs;
-    float* sc;
+    float* sc;            // this CTA's slice of the logits: the tail of the activation buffer
     float* psum;
     float* red;
     int c, G, tid;
@@ -241,10 +242,10 @@ __device__ bool produce_matrix(Cta& k, const QMat& w, int kind) {
 __device__ bool produce_params(Cta& k, const float* lnpack, const float* biaspack) {
     const int b = k.pitem & 1;
     if (!producer_wait(k, &k.ctrl->pempty[b], ((k.pitem >> 1) & 1) ^ 1)) return false;
-    const uint32_t lb = (uint32_t)k.p.d * 16, bb = biaspack ? kMegaBiasPack * 4 : 0;
+    const uint32_t lb = (uint32_t)k.p.d * 16, bb = biaspack ? (uint32_t)k.p.bias_pack * 4 : 0;
     mbar_expect_tx(&k.ctrl->pfull[b], lb + bb);
     bulk_g2s(k.param(b), lnpack, lb, &k.ctrl->pfull[b]);
-    if (biaspack) bulk_g2s(k.param(b) + 4 * MAX_D, biaspack + (size_t)k.c * kMegaBiasPack, bb, &k.ctrl->pfull[b]);
+    if (biaspack) bulk_g2s(k.param(b) + 4 * MAX_D, biaspack + (size_t)k.c * k.p.bias_pack, bb, &k.ctrl->pfull[b]);
     ++k.pitem;
     return true;
 }
@@ -774,7 +775,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_co
     }
     __syncthreads();
     Cta k{p, smem, ctrl, (const MegaLayer*)(smem + OFF_LAYERS), (const Work*)(smem + OFF_WORK), (float4*)(smem + OFF_ACT), (float*)(smem + OFF_ACT),
-          (float*)(smem + OFF_XS), (float*)(smem + OFF_SC), (float*)(smem + OFF_PSUM), (float*)(smem + OFF_RED),
+          (float*)(smem + OFF_XS), (float*)(smem + OFF_ACT) + MAX_D, (float*)(smem + OFF_PSUM), (float*)(smem + OFF_RED),
           (int)blockIdx.x, (int)gridDim.x, (int)threadIdx.x, 0, 0, 0u, -1};
     if (threadIdx.x >= CONSUMERS) {
         if (threadIdx.x == CONSUMERS) producer(k);
@@ -801,6 +802,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_co
 }
 
 size_t mega_smem_bytes() { return SMEM_BYTES; }
+int mega_head_rows_max() { return MAX_ROWS_HEAD; }
 int mega_threads() { return THREADS; }
 
 int mega_supported(const fc_config& c) {

@@ -20,7 +20,7 @@ __host__ __device__ inline void mega_cta_rows(int N, int K, int c, int G, int* r
     *r1 = (u1 * g < N) ? u1 * g : N;
 }
 
-constexpr int kMegaBiasPack = 256;   // floats of bias per (block, CTA)
+constexpr int kMegaBiasPackMax = 640;   // most floats of bias one CTA can own in a block (smaller grids own more rows)
 constexpr int kMegaMaxLayers = 32;
 
 // Offsets (floats) of the four bias slices of one CTA inside its pack; each slice starts on a
@@ -40,7 +40,7 @@ __host__ __device__ inline int mega_bias_offsets(int d, int F, int c, int G, int
 struct MegaLayer {
     QMat qkv, out, up, down;
     const float* lnpack;     // [4d]: ln1 gain, ln1 bias, ln2 gain, ln2 bias
-    const float* biaspack;   // [G][kMegaBiasPack]: per-CTA slices of the qkv, out, up, down biases
+    const float* biaspack;   // [G][bias_pack]: per-CTA slices of the qkv, out, up, down biases
 };
 
 struct MegaParams {
@@ -48,7 +48,8 @@ struct MegaParams {
     QMat tok, head;
     const float* pos;
     const float* lnfpack;      // [4d]: final LayerNorm gain, bias (rest unused)
-    const MegaLayer* layers;   // device array [L]
+    const MegaLayer* layers;   // device array [L], built for this launch's grid size
+    int bias_pack;             // floats per CTA in the bias packs (multiple of 4, <= kMegaBiasPackMax)
     float *kc, *vc;            // f32 KV caches [L][T][d]
     // exchange buffers in global memory (written by some CTAs, read by all after a barrier)
     float* qg;                 // [d] query row
@@ -76,6 +77,7 @@ struct MegaParams {
 };
 
 size_t mega_smem_bytes();
+int mega_head_rows_max();   // most LM-head rows one CTA can own
 int mega_threads();
 int mega_supported(const fc_config& c);
 int mega_max_grid(int* grid);

@@ -141,6 +141,32 @@ def test_batched_prime_equals_token_by_token_prime(tiny):
     assert np.abs(logp(gm.prime(ids[:3])) - logp(om.prime(ids[:3]))).max() < FP32_LOGPROB_TOL
 
 
+def test_decode_batch_side_by_side_matches_oracle(tiny):
+    """Eight streams decoded side by side (one persistent kernel per stream on an eighth of the
+    SMs) give the oracle's tokens stream by stream; an EOS id ends only the stream that hits it."""
+    sm, om, gm = tiny
+    V = sm.dims[5]
+    prompts = np.stack([synth.token_ids(40 + i, 9, V) for i in range(8)])
+    outs = gm.decode_batch(prompts, 20)
+    assert gm.last_batch_ms > 0
+    wants = []
+    for i in range(8):
+        want, margin = om.generate_greedy(prompts[i], 20)
+        check_greedy(outs[i], want, margin)
+        wants.append(want)
+    # three streams: a wave of two and a wave of one
+    outs3 = gm.decode_batch(prompts[:3], 20)
+    for i in range(3):
+        assert np.array_equal(outs3[i], outs[i])
+    # EOS = the 6th token of stream 1: that stream stops after 5 tokens (token_stream.rs:140-147)
+    eos = int(wants[1][5])
+    cut = gm.decode_batch(prompts, 20, eos=eos)
+    for i in range(8):
+        stop = [j for j, t in enumerate(wants[i]) if t == eos]
+        n = stop[0] if stop else 20
+        assert np.array_equal(cut[i], wants[i][:n]), f"stream {i}"
+
+
 def test_greedy_reprimes_past_the_context(mini):
     sm, om, gm = mini
     prompt = synth.token_ids(9, 4, 96)
