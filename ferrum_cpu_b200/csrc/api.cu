@@ -957,10 +957,10 @@ __global__ void bump_state_kernel(StepState* st, int by) {
 // so the n ids in queue[0..n) of each of the S streams go through every block as S windows of
 // n rows in fp32, each block's K and V rows are copied into the streams' caches, and only the
 // last row of a window meets the head.
-// Short prompts stay on the token-by-token path: below kPrimeBatchMin rows the 128-row GEMM
-// tiles are mostly padding and one persistent-kernel launch is as fast.
+// Very short prompts stay on the token-by-token path (one persistent-kernel launch); up to 64
+// rows the GEMMs run on small tiles so that every SM gets one.
 // Returns FC_OK with *used = 0 when the shape is not covered (the caller feeds token by token).
-constexpr int kPrimeBatchMin = 48;
+constexpr int kPrimeBatchMin = 8;
 static int prime_batched(fc_stream* const* ss, int S, int n, int last_mode, int* used) {
     fc_model* m = ss[0]->m;
     const fc_config& c = m->cfg;

@@ -112,12 +112,89 @@ __global__ void __launch_bounds__(256) gemm_q8_fp32_kernel(GemmArgs a) {
     }
 }
 
+// The same product for a handful of rows (a prompt being primed): SBM x 16 output tiles, so that
+// a [32][768] x [768][2304] product still spreads over 144 CTAs instead of 18. Same arithmetic as
+// the kernel above: d * q weights, one fused multiply-add per k in ascending order.
+template <int SBM>
+__global__ void __launch_bounds__(128) gemm_q8_fp32_skinny_kernel(GemmArgs a) {
+    constexpr int SBN = 16, RM = SBM / 16, SLDA = SBM + 4, SLDB = SBN + 4;
+    __shared__ __align__(16) float As[BK * SLDA];   // [k][m]
+    __shared__ __align__(16) float Bs[BK * SLDB];   // [k][n]
+    const int t = threadIdx.x;
+    const int m0 = blockIdx.y * SBM, n0 = blockIdx.x * SBN;
+    const int K = a.K, kb_per_row = K >> 5;
+    const int tx = t & 7, ty = t >> 3;              // columns 2 tx, 2 tx + 1; rows ty * RM ...
+    float acc[RM][2];
+#pragma unroll
+    for (int i = 0; i < RM; ++i) acc[i][0] = acc[i][1] = 0.0f;
+    for (int k0 = 0; k0 < K; k0 += BK) {
+        __syncthreads();
+        // activations: SBM rows x 32 k, eight float4 per row
+#pragma unroll
+        for (int i = 0; i < SBM * 8 / 128; ++i) {
+            const int idx = t + 128 * i, row = idx >> 3, c4 = idx & 7, m = m0 + row;
+            const float4 v = m < a.M ? ((const float4*)(a.x + (size_t)m * K + k0))[c4] : make_float4(0, 0, 0, 0);
+            As[(4 * c4 + 0) * SLDA + row] = v.x; As[(4 * c4 + 1) * SLDA + row] = v.y;
+            As[(4 * c4 + 2) * SLDA + row] = v.z; As[(4 * c4 + 3) * SLDA + row] = v.w;
+        }
+        // weights: 16 rows x 32 quants of one Q8_0 block column
+        if (t < 32) {
+            const int row = t >> 1, half = t & 1;
+            const size_t n = (size_t)(n0 + row);     // < N_pad (zero rows past N)
+            const uint4 wr = __ldg((const uint4*)(a.qu + n * K + k0) + half);
+            const float wscale = __half2float(__ldg(a.d + n * kb_per_row + (k0 >> 5)));
+            const uint32_t ws[4] = {wr.x, wr.y, wr.z, wr.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                Bs[(half * 16 + 4 * j + 0) * SLDB + row] = wscale * qb<0>(ws[j]);
+                Bs[(half * 16 + 4 * j + 1) * SLDB + row] = wscale * qb<1>(ws[j]);
+                Bs[(half * 16 + 4 * j + 2) * SLDB + row] = wscale * qb<2>(ws[j]);
+                Bs[(half * 16 + 4 * j + 3) * SLDB + row] = wscale * qb<3>(ws[j]);
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < BK; ++k) {
+            const float2 b = *(const float2*)&Bs[k * SLDB + tx * 2];
+#pragma unroll
+            for (int i = 0; i < RM; ++i) {
+                const float av = As[k * SLDA + ty * RM + i];
+                acc[i][0] = fmaf(av, b.x, acc[i][0]);
+                acc[i][1] = fmaf(av, b.y, acc[i][1]);
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < RM; ++i) {
+        const int m = m0 + ty * RM + i;
+        if (m >= a.M) continue;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int n = n0 + tx * 2 + j;
+            if (n >= a.N) continue;
+            float v = acc[i][j];
+            if (a.bias) v += a.bias[n];
+            if (a.epi == EPI_GELU) v = gelu_f(v);
+            if (a.residual) v = a.residual[(size_t)m * a.ldy + n] + v;
+            a.y[(size_t)m * a.ldy + n] = v;
+        }
+    }
+}
+
 int launch_gemm_q8_fp32(const QMat& w, const float* x, const float* bias, const float* residual, int epi,
                         float* y, int M, int ldy, cudaStream_t st) {
     GemmArgs a;
     a.qu = w.qu; a.d = w.d; a.N = w.N; a.K = w.K;
     a.x = x; a.bias = bias; a.residual = residual; a.epi = epi;
     a.y = y; a.M = M; a.ldy = ldy;
+    if (M <= 64) {
+        // few rows: small tiles so that every SM gets one
+        dim3 grid((w.N + 15) / 16, 1);
+        if (M <= 32) gemm_q8_fp32_skinny_kernel<32><<<grid, 128, 0, st>>>(a);
+        else gemm_q8_fp32_skinny_kernel<64><<<grid, 128, 0, st>>>(a);
+        FC_LAUNCHED();
+        return FC_OK;
+    }
     dim3 grid((w.N + BN - 1) / BN, (M + BM - 1) / BM);
     gemm_q8_fp32_kernel<<<grid, 256, 0, st>>>(a);
     FC_LAUNCHED();
