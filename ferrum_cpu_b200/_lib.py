@@ -50,6 +50,8 @@ SIGNATURES = {
     "fc_q8_0_linear_dev": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
     "fc_q8_0_linear_dev_noalloc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.POINTER(C.c_int)]),
     "fc_model_create": (C.c_int, [C.POINTER(FcConfig), C.POINTER(FcWeights), C.c_int, C.POINTER(C.c_void_p)]),
+    "fc_model_load_gguf": (C.c_int, [C.c_char_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_void_p)]),
+    "fc_gguf_probe": (C.c_int, [C.c_char_p, C.c_void_p, C.c_int, C.POINTER(FcConfig)]),
     "fc_model_free": (None, [C.c_void_p]),
     "fc_model_config": (C.c_int, [C.c_void_p, C.POINTER(FcConfig)]),
     "fc_score_windows": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),

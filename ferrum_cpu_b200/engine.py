@@ -34,6 +34,15 @@ def device_count():
     return _lib.lib().fc_device_count()
 
 
+def gguf_probe(path, row_perm=None):
+    """Dimensions of a gpt2-architecture GGUF file; validates it without a GPU."""
+    perm = None if row_perm is None else np.ascontiguousarray(row_perm, dtype=np.int32)
+    cfg = _lib.FcConfig()
+    check(_lib.lib().fc_gguf_probe(str(path).encode(), None if perm is None else _ptr(perm), 0 if perm is None else perm.size,
+                                   C.byref(cfg)))
+    return cfg
+
+
 def take_launch_count():
     return _lib.lib().fc_take_launch_count()
 
@@ -81,14 +90,26 @@ class QWeight:
 class CudaSlm:
     """A GPT-2-architecture Q8_0 model on one GPU plus one KV-cached stream."""
 
-    def __init__(self, config, weights, device=0):
+    def __init__(self, config, weights, device=0, _handle=None):
         self._m = C.c_void_p()
         self._s = C.c_void_p()
-        check(_lib.lib().fc_model_create(C.byref(config), C.byref(weights), device, C.byref(self._m)))
+        if _handle is not None:
+            self._m = _handle
+        else:
+            check(_lib.lib().fc_model_create(C.byref(config), C.byref(weights), device, C.byref(self._m)))
         cfg = _lib.FcConfig()
         check(_lib.lib().fc_model_config(self._m, C.byref(cfg)))
         self.config = cfg
         self.device = device
+
+    @classmethod
+    def from_gguf(cls, path, row_perm=None, device=0, math_mode=_lib.FC_MATH_FP32):
+        """loader/gpt2.rs gpt2_from on a file, the tensors uploaded as stored (no f32 expansion)."""
+        perm = None if row_perm is None else np.ascontiguousarray(row_perm, dtype=np.int32)
+        h = C.c_void_p()
+        check(_lib.lib().fc_model_load_gguf(str(path).encode(), None if perm is None else _ptr(perm),
+                                            0 if perm is None else perm.size, device, math_mode, C.byref(h)))
+        return cls(None, None, device=device, _handle=h)
 
     # ---- scoring (slm/scoring.rs) ---------------------------------------------------
     def token_logprobs(self, ids, from_=1, per_token=False):

@@ -139,6 +139,20 @@ int fc_q8_0_linear_dev_noalloc(const fc_qweight* w, const float* x_dev, const fl
 /* Validates as loader/gpt2.rs + loader/mod.rs:147-154 (d % n_head == 0, K % 32 == 0),
  * uploads and repacks the weights on `device`. */
 int fc_model_create(const fc_config* cfg, const fc_weights* w, int device, fc_model** out);
+/* The same from a GGUF file, without the f32 expansion of the matrices (the direct path the
+ * reference names as future work, loader/decode.rs:99-100). Reads a gpt2-architecture GGUF
+ * (version 2 or 3, gguf/header.rs:9-66) as loader/gpt2.rs:201-262 does: gpt2.context_length /
+ * embedding_length / block_count / feed_forward_length / attention.head_count, and
+ * gpt2.attention.layer_norm_epsilon, which must be 1e-5; tensors token_embd.weight,
+ * position_embd.weight, blk.N.{attn_norm,attn_qkv,attn_output,ffn_norm,ffn_up,ffn_down}.
+ * {weight,bias}, output_norm.{weight,bias}, optional output.weight (absent: tied head).
+ * Matrices must be stored as Q8_0 (they are uploaded as stored), vectors and the position
+ * table as F32; anything else is FC_E_FORMAT. row_perm (may be NULL) is the tokenizer's row
+ * order, row_perm[model id] = row of the file (the `perm` of gpt2.rs:221-231, which stays with
+ * the tokenizer on the caller's side); n_perm becomes the vocabulary size. */
+int fc_model_load_gguf(const char* path, const int32_t* row_perm, int n_perm, int device, int math_mode, fc_model** out);
+/* Parses and validates the same file without touching a GPU; fills the dimensions. */
+int fc_gguf_probe(const char* path, const int32_t* row_perm, int n_perm, fc_config* out);
 void fc_model_free(fc_model* m);
 int fc_model_config(const fc_model* m, fc_config* out);
 
