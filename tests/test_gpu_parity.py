@@ -167,6 +167,28 @@ def test_decode_batch_side_by_side_matches_oracle(tiny):
         assert np.array_equal(cut[i], wants[i][:n]), f"stream {i}"
 
 
+def test_phase_timeline_is_recorded_per_cta(tiny):
+    """fc_stream_set_trace: every CTA of the persistent kernel leaves a rising series of timer
+    values for the last token of a launch (entry 0 = token start, 15 per block, then the head)."""
+    sm, om, gm = tiny
+    prompt = synth.token_ids(2, 6, sm.dims[5])
+    gm.set_decode_mode(0)
+    gm.set_trace(True)
+    gm.generate_tokens(prompt, 5)
+    n_layer = sm.dims[0]
+    t0 = gm.read_trace(0, absolute=True)
+    t7 = gm.read_trace(7, absolute=True)
+    gm.set_trace(False)
+    for t in (t0, t7):
+        assert len(t) >= 1 + 15 * n_layer
+        assert (np.diff(t) >= 0).all()
+    assert abs(int(t0[0]) - int(t7[0])) < 1_000_000          # both CTAs timed the same token
+    rel = gm.read_trace(0)
+    assert rel[0] == 0 and rel[-1] > 0
+    with pytest.raises(fcb.FerrumCudaError):
+        gm.read_trace(100000)
+
+
 def test_greedy_reprimes_past_the_context(mini):
     sm, om, gm = mini
     prompt = synth.token_ids(9, 4, 96)
