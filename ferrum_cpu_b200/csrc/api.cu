@@ -156,6 +156,7 @@ struct fc_model {
     // model's shape is outside what that kernel supports)
     std::vector<MegaTable> mega_tables;  // [0]: the whole GPU; then halves, quarters, eighths
     float* mega_lnf = nullptr;
+    QTile mega_head;                     // tile-major copy of the LM head for the persistent kernel
     int mega_grid = 0;                   // grid of mega_tables[0]
     // streams created by fc_decode_batch, kept for the next call
     std::vector<fc_stream*> pool;
@@ -260,7 +261,7 @@ static int run_mega(fc_stream* s, int n, int head_from, int select, int probs) {
     const fc_config& c = m->cfg;
     MegaParams p;
     p.L = c.n_layer; p.d = c.d_model; p.H = c.n_head; p.F = c.d_ff; p.T = c.ctx; p.V = c.vocab;
-    p.tok = m->tok; p.head = m->head; p.pos = m->pos; p.lnfpack = m->mega_lnf;
+    p.tok = m->tok; p.head = m->mega_head; p.pos = m->pos; p.lnfpack = m->mega_lnf;
     const MegaTable& tab = m->mega_tables[s->table];
     p.layers = tab.layers;
     p.bias_pack = tab.bias_pack;
@@ -598,6 +599,12 @@ static int model_build(fc_model* m, const fc_weights* w) {
         std::copy(w->out_norm_b, w->out_norm_b + d, ln.begin() + d);
         FC_TRY(upload_f32(a, ln.data(), ln.size(), &m->mega_lnf, st));
         FC_CUDA(cudaStreamSynchronize(st));
+        {   // the persistent kernel reads the LM head from a tile-major copy (integer tensor cores)
+            unsigned char* t = nullptr;
+            FC_TRY(a.alloc_n(&t, (size_t)(m->head.N_pad / kMegaStripRows) * mega_strip_bytes(m->head.K)));
+            FC_TRY(launch_repack_tiles(m->head, t, st));
+            m->mega_head.t = t; m->mega_head.N = m->head.N; m->mega_head.K = m->head.K;
+        }
         for (int div = 1; div <= 8; div *= 2) {
             const int grid = full / div;
             if (grid < c.n_head) break;
@@ -608,7 +615,7 @@ static int model_build(fc_model* m, const fc_weights* w) {
                 pack = std::max(pack, mega_bias_offsets(d, F, cta, grid, off));
             }
             pack = (pack + 3) & ~3;
-            if ((c.vocab + grid - 1) / grid + 8 > mega_head_rows_max() || pack > kMegaBiasPackMax) break;
+            if ((c.vocab + grid - 1) / grid + 16 > mega_head_rows_max() || pack > kMegaBiasPackMax) break;
             std::vector<MegaLayer> tab(c.n_layer);
             std::vector<float> bp((size_t)grid * pack);
             for (int l = 0; l < c.n_layer; ++l) {

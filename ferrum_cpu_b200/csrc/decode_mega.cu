@@ -14,6 +14,12 @@
 //   * 16 consumer warps do the fp32 dot products out of shared memory (f16 scale applied per
 //     16 quants in registers, half-warp shuffles), LayerNorm, attention over the f32 KV cache
 //     (split over CTAs, combined flash-decoding style), and the softmax / greedy pick;
+//   * the LM head, the one phase with enough rows per CTA to be bound by instruction issue,
+//     runs on the integer tensor cores instead: the final LayerNorm output is held as block
+//     fixed point (per 32 elements a power-of-two scale and four planes of signed base-128
+//     digits, 28 bits per element), one mma.sync m16n8k32 (s8 x s8 -> s32) multiplies the four
+//     digit rows by the 8 x 32 quants of a tile exactly, and the s32 sums are scaled by (f16
+//     block scale x activation block scale) and accumulated in fp32 per Q8_0 block;
 //   * phases are separated by a software grid barrier (5 per block, 2 per head step); what
 //     crosses a barrier goes through small global buffers read with L1-bypassing loads.
 // Every wait (mbarrier, grid barrier) is bounded by a cycle budget; when it runs out the
@@ -38,7 +44,9 @@ constexpr int SLOT_BYTES = SLOT_Q + SLOT_D;
 constexpr int MAX_D = 1024, MAX_F = 4096, MAX_CTX = 1024;
 // The CTA's slice of the logits lives in the activation buffer behind the (d-wide) input of the
 // head. Total shared memory stays below 196 KB: the next carve-out step would halve the L1.
-constexpr int MAX_ROWS_HEAD = MAX_F - MAX_D;
+constexpr int DIG_STRIDE = MAX_D + 32;          // bytes between digit planes: 32 mod 128, so the four planes hit distinct banks
+constexpr int HEAD_SC_OFF = (4 * DIG_STRIDE) / 4 + MAX_D / 32;   // floats: digit planes, then the block scales
+constexpr int MAX_ROWS_HEAD = MAX_F - HEAD_SC_OFF;
 constexpr int PARAM_FLOATS = 4 * MAX_D + kMegaBiasPackMax;   // LayerNorm vectors + bias slices
 constexpr long long WAIT_CYCLES = 4000000000LL;           // ~2 s at 1.9 GHz
 
@@ -62,7 +70,7 @@ constexpr int OFF_PSUM = OFF_XS + MAX_D * 4;                     // 2 x 256 part
 constexpr int OFF_RED = OFF_PSUM + 2 * 256 * 4;                  // reductions
 constexpr int OFF_LAYERS = OFF_RED + 256 * 4;                    // copy of the layer table
 constexpr int OFF_WORK = OFF_LAYERS + kMegaMaxLayers * (int)sizeof(MegaLayer);   // 5 work descriptors
-constexpr int OFF_CTRL = OFF_WORK + 256;
+constexpr int OFF_CTRL = OFF_WORK + 512;
 constexpr int SMEM_BYTES = OFF_CTRL + (int)sizeof(Ctrl);
 static_assert(sizeof(MegaLayer) % 16 == 0, "layer table entries are copied as 16-byte words");
 static_assert(OFF_PARAM % 16 == 0 && OFF_ACT % 16 == 0 && OFF_LAYERS % 16 == 0 && OFF_CTRL % 8 == 0, "alignment");
@@ -124,6 +132,41 @@ struct Work {
 };
 enum { W_QKV = 0, W_OUT = 1, W_UP = 2, W_DOWN = 3, W_HEAD = 4, W_KINDS = 5 };
 
+// This CTA's share of the LM head in 8-row strips. A ring item holds up to spi whole strips;
+// its 8 x 32 tiles are dealt to the consumer warps as units (strip, K part): warp w of an item
+// with ns strips handles unit w when w < ns * ks.
+struct HeadWork {
+    int s0, s1;        // owned strips
+    int spi;           // strips per ring item
+    int kb;            // tiles per strip (K / 32)
+    int strip_bytes;
+    int ks[2];         // K parts per strip: full item, last (shorter) item
+    int pad;
+    unsigned unit[2][CWARPS];   // per warp: strip | first tile << 8 | end tile << 16 (0xffffffff: idle)
+};
+static_assert(W_KINDS * 32 + sizeof(HeadWork) <= 512, "work descriptors");
+__device__ void make_head_work(HeadWork* w, int N, int K, int c, int G) {
+    mega_cta_strips(N, c, G, &w->s0, &w->s1);
+    w->kb = K >> 5;
+    w->strip_bytes = mega_strip_bytes(K);
+    w->spi = max(1, min(SLOT_BYTES / w->strip_bytes, CWARPS));
+    w->pad = 0;
+    const int n = w->s1 - w->s0;
+    const int ns_v[2] = {min(w->spi, max(n, 1)), n > 0 ? n - ((n - 1) / w->spi) * w->spi : 1};
+    for (int v = 0; v < 2; ++v) {
+        const int ns = ns_v[v], ks = max(1, min(w->kb, CWARPS / ns));
+        w->ks[v] = ks;
+        for (int u = 0; u < CWARPS; ++u) {
+            if (u < ns * ks) {
+                const int strip = u / ks, part = u - strip * ks;
+                w->unit[v][u] = (unsigned)strip | (unsigned)(part * w->kb / ks) << 8 | (unsigned)((part + 1) * w->kb / ks) << 16;
+            } else {
+                w->unit[v][u] = 0xffffffffu;
+            }
+        }
+    }
+}
+
 // Split K over several half warps when an item has few rows: the split with the fewest
 // sweeps on the critical path (rounds over the 32 half warps x sweeps per unit).
 __device__ int pick_ksplit(int rows, int iters) {
@@ -177,6 +220,7 @@ struct Cta {
     Ctrl* ctrl;
     const MegaLayer* layers;   // shared-memory copy of the layer table
     const Work* work;          // shared-memory work descriptors, one per matrix kind
+    const HeadWork* hwork;     // ... and the LM head's
     float4* act4;
     float* act;
     float* xs;
@@ -188,6 +232,8 @@ struct Cta {
     int pitem;           // parameter items consumed / issued
     unsigned bar_target;
     int trace_n;         // next slot of the phase timeline; < 0 when this thread does not trace
+    __device__ signed char* dig() const { return (signed char*)act; }                 // head phase: digit planes
+    __device__ float* xsc() const { return act + (4 * DIG_STRIDE) / 4; }             // ... and their block scales
     __device__ unsigned char* slot_q(int s) const { return smem + OFF_SLOTS + s * SLOT_BYTES; }
     __device__ const __half* slot_d(int s) const { return (const __half*)(smem + OFF_SLOTS + s * SLOT_BYTES + SLOT_Q); }
     __device__ float* param(int b) const { return (float*)(smem + OFF_PARAM) + b * PARAM_FLOATS; }
@@ -238,6 +284,21 @@ __device__ bool produce_matrix(Cta& k, const QMat& w, int kind) {
     return true;
 }
 
+// The LM head share: one bulk copy per ring item (whole strips of the tile-major copy).
+__device__ bool produce_head(Cta& k) {
+    const HeadWork& wk = *k.hwork;
+    for (int s = wk.s0; s < wk.s1; s += wk.spi) {
+        const int ns = min(wk.spi, wk.s1 - s);
+        const int slot = k.item % SLOTS;
+        if (!producer_wait(k, &k.ctrl->empty[slot], ((k.item / SLOTS) & 1) ^ 1)) return false;
+        const uint32_t bytes = (uint32_t)ns * wk.strip_bytes;
+        mbar_expect_tx(&k.ctrl->full[slot], bytes);
+        bulk_g2s(k.slot_q(slot), k.p.head.t + (size_t)s * wk.strip_bytes, bytes, &k.ctrl->full[slot]);
+        ++k.item;
+    }
+    return true;
+}
+
 // LayerNorm vectors (4d floats) and, for a block, this CTA's bias slices.
 __device__ bool produce_params(Cta& k, const float* lnpack, const float* biaspack) {
     const int b = k.pitem & 1;
@@ -261,7 +322,7 @@ __device__ void producer(Cta& k) {
                 return;
         }
         if (step >= p.head_from) {
-            if (!produce_params(k, p.lnfpack, nullptr) || !produce_matrix(k, p.head, W_HEAD)) return;
+            if (!produce_params(k, p.lnfpack, nullptr) || !produce_head(k)) return;
         }
     }
 }
@@ -291,10 +352,37 @@ __device__ float cmax(Cta& k, float v) {
     return t;
 }
 
-// layer/norm.rs:46-82 on xs[0..d) -> act (swizzled); g, b in shared memory.
+// The 32 values a warp holds (one per lane) become block kb of the activation vector: a
+// power-of-two block scale and, per value, four signed base-128 digits (most significant
+// first) of round(v / scale), |v / scale| <= 2^27.
+__device__ __forceinline__ void put_block(Cta& k, int kb, float v) {
+    float m = fabsf(v);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    // m < 2^e; e is kept where both 2^(27-e) and 2^(e-27) are normal floats
+    int e = (int)((__float_as_uint(m) >> 23) & 0xffu) - 126;
+    e = max(e, -80);
+    const float up = __uint_as_float((unsigned)(127 + 27 - e) << 23);
+    int X = __float2int_rn(v * up);
+    const int d3 = ((X + 64) & 127) - 64;
+    X = (X - d3) >> 7;
+    const int d2 = ((X + 64) & 127) - 64;
+    X = (X - d2) >> 7;
+    const int d1 = ((X + 64) & 127) - 64;
+    X = (X - d1) >> 7;                                   // the leading digit, in [-64, 64]
+    signed char* dg = k.dig() + kb * 32 + (k.tid & 31);
+    dg[0] = (signed char)X;
+    dg[DIG_STRIDE] = (signed char)d1;
+    dg[2 * DIG_STRIDE] = (signed char)d2;
+    dg[3 * DIG_STRIDE] = (signed char)d3;
+    if ((k.tid & 31) == 0) k.xsc()[kb] = __uint_as_float((unsigned)(127 - 27 + e) << 23);
+}
+
+// layer/norm.rs:46-82 on xs[0..d) -> act (swizzled floats, or digit planes for the LM head);
+// g, b in shared memory.
 // Two-level reductions: each thread owns elements tid and tid + 512, each warp leaves one
 // partial per statistic in shared memory, every thread adds the 16 partials in the same order.
-__device__ void layernorm_to_act(Cta& k, const float* g, const float* b) {
+__device__ void layernorm_to_act(Cta& k, const float* g, const float* b, bool digits = false) {
     const int d = k.p.d, lane = k.tid & 31, wid = k.tid >> 5;
     const bool h0 = k.tid < d, h1 = k.tid + CONSUMERS < d;
     const float v0 = h0 ? k.xs[k.tid] : 0.0f, v1 = h1 ? k.xs[k.tid + CONSUMERS] : 0.0f;
@@ -317,8 +405,15 @@ __device__ void layernorm_to_act(Cta& k, const float* g, const float* b) {
 #pragma unroll
     for (int w = 0; w < CWARPS; ++w) qt += k.red[CWARPS + w];
     const float sd = sqrtf(qt / (float)d + 1e-5f);
-    if (h0) k.act[act_index(k.tid)] = (t0 / sd) * g[k.tid] + b[k.tid];
-    if (h1) k.act[act_index(k.tid + CONSUMERS)] = (t1 / sd) * g[k.tid + CONSUMERS] + b[k.tid + CONSUMERS];
+    if (digits) {
+        consumer_sync();   // every read of xs and of the old activation is over before the planes are written
+        // d is a multiple of 32: a warp's 32 elements are one whole block or none
+        if (h0) put_block(k, wid, (t0 / sd) * g[k.tid] + b[k.tid]);
+        if (h1) put_block(k, CWARPS + wid, (t1 / sd) * g[k.tid + CONSUMERS] + b[k.tid + CONSUMERS]);
+    } else {
+        if (h0) k.act[act_index(k.tid)] = (t0 / sd) * g[k.tid] + b[k.tid];
+        if (h1) k.act[act_index(k.tid + CONSUMERS)] = (t1 / sd) * g[k.tid + CONSUMERS] + b[k.tid + CONSUMERS];
+    }
     consumer_sync();
 }
 
@@ -400,6 +495,77 @@ __device__ bool consume_matrix(Cta& k, const QMat& w, int kind, Epi epi) {
             float v = 0.0f;
             for (int part = 0; part < ksplit; ++part) v += ps[row * ksplit + part];
             epi(r + row, r + row - r0, v);
+        }
+        ++k.item;
+    }
+    return true;
+}
+
+// One integer MMA: D[16 x 8] = A[16 x 32] (s8, row) x B[32 x 8] (s8, col). Rows 0..3 of A are
+// the digit planes of 32 activations, B is one 8 x 32 tile of quants. With lane = 4 g + t the
+// lane supplies A[g][8t .. 8t+7] (a0, a2; rows 8.. are zero) and B[8t .. 8t+7][g] (b0, b1) and
+// receives D[g][2t], D[g][2t+1]: digit row g against weight rows 2t and 2t+1. The k index
+// inside the block is permuted the same way on both sides, which leaves the sums unchanged.
+__device__ __forceinline__ void mma_s8(int& c0, int& c1, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    int c2 __attribute__((unused)), c3 __attribute__((unused));   // rows 8..15 of D: always zero here
+    asm(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+        : "=r"(c0), "=r"(c1), "=r"(c2), "=r"(c3)
+        : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1), "r"(0), "r"(0), "r"(0), "r"(0));
+    (void)c2; (void)c3;
+}
+
+// The LM head share on the integer tensor cores: logits of the owned rows n < V go to lg[n -
+// first owned row] (shared memory) and to the global logits.
+__device__ bool consume_head(Cta& k, float* lg) {
+    const MegaParams& p = k.p;
+    const HeadWork& wk = *k.hwork;
+    const int lane = k.tid & 31, wid = k.tid >> 5, g = lane >> 2, t = lane & 3;
+    const int r0 = min(wk.s0 * kMegaStripRows, p.V);
+    // digit g carries weight 128^(3-g); lanes of the unused rows 4..7 contribute nothing
+    const float digit_w = g == 0 ? 2097152.0f : g == 1 ? 16384.0f : g == 2 ? 128.0f : g == 3 ? 1.0f : 0.0f;
+    const signed char* my_dig = k.dig() + (g & 3) * DIG_STRIDE + t * 8;
+    const float* xsc = k.xsc();
+    for (int s = wk.s0; s < wk.s1; s += wk.spi) {
+        const int ns = min(wk.spi, wk.s1 - s);
+        const int var = ns == wk.spi ? 0 : 1;
+        const int slot = k.item % SLOTS;
+        if (!consumer_wait(k, &k.ctrl->full[slot], (k.item / SLOTS) & 1)) return false;
+        float* ps = k.psum + (k.item & 1) * 256;
+        const unsigned unit = wk.unit[var][wid];
+        if (unit != 0xffffffffu) {
+            const int strip = unit & 0xff, kb0 = (unit >> 8) & 0xff, kb1 = (unit >> 16) & 0xff;
+            const unsigned char* tile = k.slot_q(slot) + strip * wk.strip_bytes + kb0 * kMegaTileBytes;
+            float acc0 = 0.0f, acc1 = 0.0f;
+#pragma unroll 2
+            for (int kb = kb0; kb < kb1; ++kb, tile += kMegaTileBytes) {
+                const uint2 b = *(const uint2*)(tile + g * 32 + t * 8);
+                const __half2 sc = *(const __half2*)(tile + 256 + t * 4);
+                uint2 a = make_uint2(0u, 0u);
+                if (g < 4) a = *(const uint2*)(my_dig + kb * 32);
+                const float xs = xsc[kb];
+                int c0, c1;
+                mma_s8(c0, c1, a.x, a.y, b.x, b.y);
+                const float2 f = __half22float2(sc);
+                acc0 = fmaf((float)c0, f.x * xs, acc0);
+                acc1 = fmaf((float)c1, f.y * xs, acc1);
+            }
+            acc0 *= digit_w;
+            acc1 *= digit_w;
+            acc0 += __shfl_xor_sync(0xffffffffu, acc0, 4);
+            acc1 += __shfl_xor_sync(0xffffffffu, acc1, 4);
+            acc0 += __shfl_xor_sync(0xffffffffu, acc0, 8);
+            acc1 += __shfl_xor_sync(0xffffffffu, acc1, 8);
+            if (lane < 4) { ps[wid * 8 + 2 * t] = acc0; ps[wid * 8 + 2 * t + 1] = acc1; }
+        }
+        consumer_sync();                                   // slot fully read, partial sums visible
+        if (lane == 0) mbar_arrive(&k.ctrl->empty[slot]);
+        if (k.tid < ns * kMegaStripRows) {
+            const int strip = k.tid >> 3, r = k.tid & 7, ks = wk.ks[var];
+            float v = 0.0f;
+            for (int part = 0; part < ks; ++part) v += ps[(strip * ks + part) * 8 + r];
+            const int n = (s + strip) * kMegaStripRows + r;
+            if (n < p.V) { lg[n - r0] = v; p.logits[n] = v; }
         }
         ++k.item;
     }
@@ -676,12 +842,12 @@ __device__ void consumer(Cta& k) {
         if (step >= p.head_from) {
             const int pb = k.pitem & 1;
             if (!consumer_wait(k, &k.ctrl->pfull[pb], (k.pitem >> 1) & 1)) break;
-            layernorm_to_act(k, k.param(pb), k.param(pb) + d);   // ends with a sync
+            layernorm_to_act(k, k.param(pb), k.param(pb) + d, /*digits=*/true);   // ends with a sync
             if ((k.tid & 31) == 0) mbar_arrive(&k.ctrl->pempty[pb]);
             ++k.pitem;
-            const int r0 = k.work[W_HEAD].r0, r1 = k.work[W_HEAD].r1;
+            const int r0 = min(k.hwork->s0 * kMegaStripRows, V), r1 = min(k.hwork->s1 * kMegaStripRows, V);
             float* lg = k.sc;                      // this CTA's logits [r1 - r0]
-            ok = consume_matrix(k, p.head, W_HEAD, [&](int n, int i, float v) { lg[i] = v; p.logits[n] = v; });
+            ok = consume_head(k, lg);
             if (!ok) break;
             consumer_sync();
             // ops.rs:478-502: max, exp(x - max), sum — per CTA, then combined across CTAs
@@ -773,9 +939,11 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_co
         const int K = kind == W_DOWN ? F : d;
         make_work((Work*)(smem + OFF_WORK) + kind, N, K, (int)blockIdx.x, (int)gridDim.x);
     }
+    if (threadIdx.x == W_KINDS) make_head_work((HeadWork*)(smem + OFF_WORK + W_KINDS * 32), p.V, p.d, (int)blockIdx.x, (int)gridDim.x);
     __syncthreads();
-    Cta k{p, smem, ctrl, (const MegaLayer*)(smem + OFF_LAYERS), (const Work*)(smem + OFF_WORK), (float4*)(smem + OFF_ACT), (float*)(smem + OFF_ACT),
-          (float*)(smem + OFF_XS), (float*)(smem + OFF_ACT) + MAX_D, (float*)(smem + OFF_PSUM), (float*)(smem + OFF_RED),
+    Cta k{p, smem, ctrl, (const MegaLayer*)(smem + OFF_LAYERS), (const Work*)(smem + OFF_WORK), (const HeadWork*)(smem + OFF_WORK + W_KINDS * 32),
+          (float4*)(smem + OFF_ACT), (float*)(smem + OFF_ACT),
+          (float*)(smem + OFF_XS), (float*)(smem + OFF_ACT) + HEAD_SC_OFF, (float*)(smem + OFF_PSUM), (float*)(smem + OFF_RED),
           (int)blockIdx.x, (int)gridDim.x, (int)threadIdx.x, 0, 0, 0u, -1};
     if (threadIdx.x >= CONSUMERS) {
         if (threadIdx.x == CONSUMERS) producer(k);
@@ -834,6 +1002,39 @@ int mega_max_grid(int* grid) {
     FC_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_mega_kernel, THREADS, SMEM_BYTES));
     if (per_sm < 1) return fail(FC_E_CUDA, "the persistent decode kernel does not fit on an SM");
     *grid = sms < CONSUMERS ? sms : CONSUMERS;
+    return FC_OK;
+}
+
+// ------------------------------------------------------------------ tile-major weight copy
+// One thread per (tile, row): 32 quants (bias of 128 removed) and the row's f16 scale.
+__global__ void repack_tiles_kernel(const uint8_t* __restrict__ qu, const __half* __restrict__ d,
+                                    unsigned char* __restrict__ out, int N_pad, int K) {
+    const int KB = K >> 5;
+    const size_t total = (size_t)(N_pad / kMegaStripRows) * KB * kMegaStripRows;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int g = (int)(i & 7);
+        const size_t tile = i >> 3, strip = tile / KB;
+        const int kb = (int)(tile - strip * KB);
+        const size_t row = strip * kMegaStripRows + g;
+        const uint4* src = (const uint4*)(qu + row * K + (size_t)kb * 32);
+        uint4 a = src[0], b = src[1];
+        a.x ^= 0x80808080u; a.y ^= 0x80808080u; a.z ^= 0x80808080u; a.w ^= 0x80808080u;
+        b.x ^= 0x80808080u; b.y ^= 0x80808080u; b.z ^= 0x80808080u; b.w ^= 0x80808080u;
+        unsigned char* t = out + tile * kMegaTileBytes;
+        ((uint4*)(t + g * 32))[0] = a;
+        ((uint4*)(t + g * 32))[1] = b;
+        ((__half*)(t + 256))[g] = d[row * KB + kb];
+    }
+}
+
+int launch_repack_tiles(const QMat& w, unsigned char* out, cudaStream_t st) {
+    if (w.N_pad % kMegaStripRows) return fail(FC_E_SHAPE, "padded row count %d is not a multiple of %d", w.N_pad, kMegaStripRows);
+    const size_t total = (size_t)w.N_pad * (w.K >> 5);
+    const int threads = 256;
+    const size_t want = (total + threads - 1) / threads;
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    repack_tiles_kernel<<<blocks, threads, 0, st>>>(w.qu, w.d, out, w.N_pad, w.K);
+    FC_LAUNCHED();
     return FC_OK;
 }
 

@@ -20,6 +20,26 @@ __host__ __device__ inline void mega_cta_rows(int N, int K, int c, int G, int* r
     *r1 = (u1 * g < N) ? u1 * g : N;
 }
 
+// The LM head is read from a second, tile-major copy made at upload: rows are grouped into
+// strips of 8, and a strip is K/32 tiles of 272 bytes, each holding the 8 x 32 signed quants of
+// one Q8_0 block column (row-major, 256 B) followed by the 8 f16 scales (16 B). A tile is
+// exactly the B operand of one m16n8k32 integer MMA plus its scales, a strip is contiguous (one
+// bulk copy), and the density is Q8_0's own 34 bytes per 32 weights.
+constexpr int kMegaStripRows = 8;
+constexpr int kMegaTileBytes = 272;
+struct QTile {
+    const unsigned char* t = nullptr;
+    int N = 0, K = 0;
+};
+__host__ __device__ inline int mega_strip_bytes(int K) { return (K >> 5) * kMegaTileBytes; }
+__host__ __device__ inline int mega_strips(int N) { return (N + kMegaStripRows - 1) / kMegaStripRows; }
+// Strips of an N-row matrix owned by CTA c of G.
+__host__ __device__ inline void mega_cta_strips(int N, int c, int G, int* s0, int* s1) {
+    const int units = mega_strips(N);
+    *s0 = (int)((long long)c * units / G);
+    *s1 = (int)((long long)(c + 1) * units / G);
+}
+
 constexpr int kMegaBiasPackMax = 640;   // most floats of bias one CTA can own in a block (smaller grids own more rows)
 constexpr int kMegaMaxLayers = 32;
 
@@ -45,7 +65,8 @@ struct MegaLayer {
 
 struct MegaParams {
     int L, d, H, F, T, V;
-    QMat tok, head;
+    QMat tok;                  // embedding rows (row-major planes)
+    QTile head;                // LM head, tile-major
     const float* pos;
     const float* lnfpack;      // [4d]: final LayerNorm gain, bias (rest unused)
     const MegaLayer* layers;   // device array [L], built for this launch's grid size
@@ -82,5 +103,8 @@ int mega_threads();
 int mega_supported(const fc_config& c);
 int mega_max_grid(int* grid);
 int launch_decode_mega(const MegaParams& p, int grid, cudaStream_t st);
+// Tile-major copy of w (rows up to w.N_pad, a multiple of 8) into out
+// [w.N_pad / 8 strips][mega_strip_bytes(K)].
+int launch_repack_tiles(const QMat& w, unsigned char* out, cudaStream_t st);
 
 }  // namespace fc
