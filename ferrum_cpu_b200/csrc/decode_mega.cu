@@ -103,6 +103,15 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(s32(dst)), "l"(src), "r"(bytes), "r"(s32(b)) : "memory");
 }
+// The same for the weight stream, marked evict-first in L2: every weight byte is used once per
+// token and the matrices are larger than the L2, so letting them age normally would push the KV
+// cache and the exchange vectors out to HBM between tokens.
+__device__ __forceinline__ void bulk_g2s_stream(void* dst, const void* src, uint32_t bytes, unsigned long long* b) {
+    unsigned long long policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+                 ::"r"(s32(dst)), "l"(src), "r"(bytes), "r"(s32(b)), "l"(policy) : "memory");
+}
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CONSUMERS) : "memory"); }
 __device__ __forceinline__ unsigned ld_acquire(const unsigned* p) {
     unsigned v;
@@ -277,8 +286,8 @@ __device__ bool produce_matrix(Cta& k, const QMat& w, int kind) {
         if (!producer_wait(k, &k.ctrl->empty[slot], ((k.item / SLOTS) & 1) ^ 1)) return false;
         const uint32_t qb = (uint32_t)rows_c * w.K, db = qb >> 4;
         mbar_expect_tx(&k.ctrl->full[slot], qb + db);
-        bulk_g2s(k.slot_q(slot), w.qu + (size_t)r * w.K, qb, &k.ctrl->full[slot]);
-        bulk_g2s((void*)k.slot_d(slot), w.d + (size_t)r * (w.K >> 5), db, &k.ctrl->full[slot]);
+        bulk_g2s_stream(k.slot_q(slot), w.qu + (size_t)r * w.K, qb, &k.ctrl->full[slot]);
+        bulk_g2s_stream((void*)k.slot_d(slot), w.d + (size_t)r * (w.K >> 5), db, &k.ctrl->full[slot]);
         ++k.item;
     }
     return true;
@@ -293,7 +302,7 @@ __device__ bool produce_head(Cta& k) {
         if (!producer_wait(k, &k.ctrl->empty[slot], ((k.item / SLOTS) & 1) ^ 1)) return false;
         const uint32_t bytes = (uint32_t)ns * wk.strip_bytes;
         mbar_expect_tx(&k.ctrl->full[slot], bytes);
-        bulk_g2s(k.slot_q(slot), k.p.head.t + (size_t)s * wk.strip_bytes, bytes, &k.ctrl->full[slot]);
+        bulk_g2s_stream(k.slot_q(slot), k.p.head.t + (size_t)s * wk.strip_bytes, bytes, &k.ctrl->full[slot]);
         ++k.item;
     }
     return true;
@@ -583,9 +592,9 @@ __device__ __forceinline__ int attn_splits_for(const MegaParams& p, int len) {
 }
 
 // transformer.rs:246-283 split over CTAs: CTA (h, s) handles keys [s*len/S, (s+1)*len/S) of
-// head h. Inside the CTA every warp runs an online softmax over its own keys, four keys per
-// step (no CTA-wide synchronisation while keys are processed); the 16 warp partials are
-// combined once at the end in a fixed order. With S == 1 the result is the head's attention
+// head h. Inside the CTA every half warp runs an online softmax over its own keys (no CTA-wide
+// synchronisation while keys are processed); the halves of a warp merge, then the 16 warp
+// partials are combined once at the end in a fixed order. With S == 1 the result is the head's attention
 // output, written to attg; otherwise (max, sum-exp, unnormalised out[hd]) go to partg.
 __device__ void attention_partial(Cta& k, int l, int len) {
     const MegaParams& p = k.p;
@@ -595,58 +604,66 @@ __device__ void attention_partial(Cta& k, int l, int len) {
     const int j0 = (int)((long long)s * len / S), j1 = (int)((long long)(s + 1) * len / S);
     const float* kc = p.kc + (size_t)l * p.T * p.d + hs;
     const float* vc = p.vc + (size_t)l * p.T * p.d + hs;
-    const int lane = k.tid & 31, wid = k.tid >> 5;
-    // each lane owns head dimensions lane and lane + 32 (hd <= 64)
-    const bool has0 = lane < hd, has1 = lane + 32 < hd;
-    const float q0 = has0 ? __ldcg(p.qg + hs + lane) : 0.0f;
-    const float q1 = has1 ? __ldcg(p.qg + hs + lane + 32) : 0.0f;
+    const int lane = k.tid & 31, wid = k.tid >> 5, hf = lane >> 4, li = lane & 15;
+    // A half warp takes one key at a time: lane li owns head dimensions 4 li .. 4 li + 3
+    // (hd <= 64), so a K or V row is one 16-byte load per lane and a dot product needs four
+    // shuffle steps. Both halves hold the query.
+    const bool has = 4 * li < hd;
+    const float4 zero4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    const float4 q = has ? __ldcg((const float4*)(p.qg + hs) + li) : zero4;
     const float scale = 1.0f / sqrtf((float)hd);
-    float m = -INFINITY, lsum = 0.0f, o0 = 0.0f, o1 = 0.0f;
-    // warp wid owns keys j0 + wid, j0 + wid + 16, ...; the K and V rows of four keys are
-    // requested together, one step ahead of the arithmetic, and their dot products reduced
-    // side by side
-    struct Rows { float a0[4], a1[4], v0[4], v1[4]; };
+    float m = -INFINITY, lsum = 0.0f;
+    float4 o = zero4;
+    // Warp wid owns the key pairs j0 + 2 wid, j0 + 2 wid + 32, ...; half hf takes key hf of a
+    // pair. Two pairs (four keys per warp) are requested together, one step ahead of the
+    // arithmetic.
+    constexpr int U = 2;
+    struct Rows { float4 kk[U], vv[U]; };
+    auto key_of = [&](int jb, int u) { return jb + u * (2 * CWARPS) + hf; };
     auto request = [&](Rows& r, int jb) {
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int j = jb + u * CWARPS;
-            const bool on = j < j1;
+        for (int u = 0; u < U; ++u) {
+            const int j = key_of(jb, u);
+            const bool on = j < j1 && has;
             const size_t off = (size_t)j * p.d;
-            r.a0[u] = (on && has0) ? __ldcg(kc + off + lane) : 0.0f;
-            r.a1[u] = (on && has1) ? __ldcg(kc + off + lane + 32) : 0.0f;
-            r.v0[u] = (on && has0) ? __ldcg(vc + off + lane) : 0.0f;
-            r.v1[u] = (on && has1) ? __ldcg(vc + off + lane + 32) : 0.0f;
+            r.kk[u] = on ? __ldcg((const float4*)(kc + off) + li) : zero4;
+            r.vv[u] = on ? __ldcg((const float4*)(vc + off) + li) : zero4;
         }
     };
     auto absorb = [&](const Rows& r, int jb) {
-        float dot[4];
+        float dot[U];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) dot[u] = fmaf(q1, r.a1[u], q0 * r.a0[u]);
+        for (int u = 0; u < U; ++u)
+            dot[u] = fmaf(q.w, r.kk[u].w, fmaf(q.z, r.kk[u].z, fmaf(q.y, r.kk[u].y, q.x * r.kk[u].x)));
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
+        for (int sh = 8; sh > 0; sh >>= 1) {
 #pragma unroll
-            for (int u = 0; u < 4; ++u) dot[u] += __shfl_xor_sync(0xffffffffu, dot[u], o);
+            for (int u = 0; u < U; ++u) dot[u] += __shfl_xor_sync(0xffffffffu, dot[u], sh);
         }
-        // keys past the range score -inf and weigh 0; the first key of a step is always live
+        // keys past the range score -inf and weigh 0
         float mn = m;
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            dot[u] = (jb + u * CWARPS < j1) ? dot[u] * scale : -INFINITY;
+        for (int u = 0; u < U; ++u) {
+            dot[u] = key_of(jb, u) < j1 ? dot[u] * scale : -INFINITY;
             mn = fmaxf(mn, dot[u]);
         }
-        const float corr = expf(m - mn);                // m == -inf: 0
-        float pj[4];
+        if (mn > -INFINITY) {                           // this half has seen a key
+            const float corr = expf(m - mn);            // m == -inf: 0
+            float pj[U];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) pj[u] = expf(dot[u] - mn);
-        lsum = fmaf(lsum, corr, (pj[0] + pj[1]) + (pj[2] + pj[3]));
-        o0 = fmaf(o0, corr, fmaf(pj[0], r.v0[0], pj[1] * r.v0[1]) + fmaf(pj[2], r.v0[2], pj[3] * r.v0[3]));
-        o1 = fmaf(o1, corr, fmaf(pj[0], r.v1[0], pj[1] * r.v1[1]) + fmaf(pj[2], r.v1[2], pj[3] * r.v1[3]));
-        m = mn;
+            for (int u = 0; u < U; ++u) pj[u] = expf(dot[u] - mn);
+            lsum = fmaf(lsum, corr, pj[0] + pj[1]);
+            o.x = fmaf(o.x, corr, fmaf(pj[0], r.vv[0].x, pj[1] * r.vv[1].x));
+            o.y = fmaf(o.y, corr, fmaf(pj[0], r.vv[0].y, pj[1] * r.vv[1].y));
+            o.z = fmaf(o.z, corr, fmaf(pj[0], r.vv[0].z, pj[1] * r.vv[1].z));
+            o.w = fmaf(o.w, corr, fmaf(pj[0], r.vv[0].w, pj[1] * r.vv[1].w));
+            m = mn;
+        }
     };
     {
-        constexpr int STEP = CWARPS * 4;
+        constexpr int STEP = U * 2 * CWARPS;            // keys per sweep of the CTA
         Rows ra, rb;
-        int jb = j0 + wid;
+        int jb = j0 + 2 * wid;
         if (jb < j1) request(ra, jb);
         while (jb < j1) {
             if (jb + STEP < j1) request(rb, jb + STEP);
@@ -658,11 +675,27 @@ __device__ void attention_partial(Cta& k, int l, int len) {
             jb += STEP;
         }
     }
+    // the two halves of the warp merge their running (max, sum, out) in a fixed order
+    {
+        const float m2 = __shfl_xor_sync(0xffffffffu, m, 16), l2 = __shfl_xor_sync(0xffffffffu, lsum, 16);
+        const float ox = __shfl_xor_sync(0xffffffffu, o.x, 16), oy = __shfl_xor_sync(0xffffffffu, o.y, 16);
+        const float oz = __shfl_xor_sync(0xffffffffu, o.z, 16), ow = __shfl_xor_sync(0xffffffffu, o.w, 16);
+        const float M = fmaxf(m, m2);
+        // half 0's terms first in both halves, so that they agree bit for bit
+        const float ma = hf ? m2 : m, mb = hf ? m : m2;
+        const float fa = ma > -INFINITY ? expf(ma - M) : 0.0f, fb = mb > -INFINITY ? expf(mb - M) : 0.0f;
+        const float la = hf ? l2 : lsum, lb = hf ? lsum : l2;
+        lsum = fmaf(la, fa, lb * fb);
+        o.x = fmaf(hf ? ox : o.x, fa, (hf ? o.x : ox) * fb);
+        o.y = fmaf(hf ? oy : o.y, fa, (hf ? o.y : oy) * fb);
+        o.z = fmaf(hf ? oz : o.z, fa, (hf ? o.z : oz) * fb);
+        o.w = fmaf(hf ? ow : o.w, fa, (hf ? o.w : ow) * fb);
+        m = M;
+    }
     float* part = k.act;                                // act is free during the attention phase
     float* mine = part + wid * 66;
     if (lane == 0) { mine[0] = m; mine[1] = lsum; }
-    mine[2 + lane] = o0;
-    mine[2 + 32 + lane] = o1;
+    if (hf == 0 && has) { mine[2 + 4 * li] = o.x; mine[3 + 4 * li] = o.y; mine[4 + 4 * li] = o.z; mine[5 + 4 * li] = o.w; }
     consumer_sync();
     if (k.tid < 64) {
         // warps 0 and 1 each work out the 16 rescaling factors (lane w: warp w) and share them
@@ -733,8 +766,20 @@ __device__ void attention_combine(Cta& k, int len) {
     consumer_sync();
 }
 
+// n <= MAX_F floats from global memory into shared memory; every thread requests all of its
+// elements before the first one is stored, so the whole vector costs one round trip to L2.
 __device__ void load_vec(Cta& k, const float* g, float* dst, int n, bool swizzle) {
-    for (int i = k.tid; i < n; i += CONSUMERS) dst[swizzle ? act_index(i) : i] = __ldcg(g + i);
+    float v[MAX_F / CONSUMERS];
+#pragma unroll
+    for (int j = 0; j < MAX_F / CONSUMERS; ++j) {
+        const int i = k.tid + j * CONSUMERS;
+        v[j] = i < n ? __ldcg(g + i) : 0.0f;
+    }
+#pragma unroll
+    for (int j = 0; j < MAX_F / CONSUMERS; ++j) {
+        const int i = k.tid + j * CONSUMERS;
+        if (i < n) dst[swizzle ? act_index(i) : i] = v[j];
+    }
     consumer_sync();
 }
 
