@@ -585,7 +585,7 @@ __device__ bool consume_head(Cta& k, float* lg) {
 // head and writes the finished attention output: the split into partials costs an extra grid
 // barrier and a combine phase, which only pays once a single CTA would need many sweeps.
 // Beyond that about 64 keys per CTA, at most attn_splits.
-constexpr int kWholeHead = 384;
+constexpr int kWholeHead = 576;
 __device__ __forceinline__ int attn_splits_for(const MegaParams& p, int len) {
     if (len <= kWholeHead) return 1;
     return max(1, min(p.attn_splits, (len + 63) >> 6));
