@@ -34,7 +34,7 @@ PROMPT, NEW_TOKENS = 32, 256
 N_SEQ, SEQ_LEN = 512, 1024
 METRIC = "Q8_0 GPT-2-small decode tokens/s (batch 1, KV cache, greedy)"
 # dram__bytes_read.sum + dram__bytes_write.sum of decode_mega_kernel per token (ncu, see profiles/)
-DECODE_DRAM_BYTES_PER_TOKEN = 128.9e6 + 3.65e6
+DECODE_DRAM_BYTES_PER_TOKEN = 134.8e6 + 4.98e6
 
 
 def peaks():
@@ -278,7 +278,7 @@ def main():
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                          "traffic": DECODE_DRAM_BYTES_PER_TOKEN * 32, "peak_kind": peak_kind,
                          "what": "decode_mega_kernel, launches of 32 tokens: %.1f MB algorithmic per token; traffic = "
-                                 "ncu dram read+write of a 6-token launch (128.9 + 3.65 MB per token, "
+                                 "ncu dram read+write of a one-token launch at position 38 (134.8 + 4.98 MB, "
                                  "profiles/decode_mega_kernel_gpt2small_7tokens.md) scaled to 32 tokens" % (bpt / 1e6)},
             "clocks": clocks,
         }

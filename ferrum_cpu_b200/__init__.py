@@ -6,4 +6,5 @@ binding and a small Python mirror of the reference interfaces used by tests and 
 """
 from . import _lib, synth  # noqa: F401
 from ._lib import (FC_MATH_BF16X3, FC_MATH_FP32, FerrumCudaError, LIB_PATH)  # noqa: F401
-from .engine import CudaSlm, QWeight, Score, device_count, q8_0_linear, take_launch_count  # noqa: F401
+from .engine import (CudaSlm, QWeight, Score, device_count, gguf_probe, q8_0_linear, sample_logits, sampling,  # noqa: F401
+                     take_launch_count)

@@ -29,6 +29,10 @@ class FcWeights(C.Structure):
                 ("out_norm_g", C.c_void_p), ("out_norm_b", C.c_void_p), ("output_q8", C.c_void_p)]
 
 
+class FcSampling(C.Structure):
+    _fields_ = [("temperature", C.c_float), ("top_k", C.c_int32), ("top_p", C.c_float), ("repetition_penalty", C.c_float)]
+
+
 class FcScore(C.Structure):
     _fields_ = [("logprob", C.c_double), ("n_tokens", C.c_int64), ("greedy", C.c_int32)]
 
@@ -69,6 +73,8 @@ SIGNATURES = {
     "fc_feed": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p]),
     "fc_prime": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "fc_generate_greedy": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int32, C.c_void_p, C.c_void_p, C.POINTER(C.c_int)]),
+    "fc_sample_logits": (C.c_int, [C.c_int, C.c_void_p, C.c_int, C.POINTER(FcSampling), C.c_void_p, C.c_int, C.POINTER(C.c_uint64), C.POINTER(C.c_int32)]),
+    "fc_generate_sampled": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int32, C.POINTER(FcSampling), C.POINTER(C.c_uint64), C.c_void_p, C.c_void_p, C.POINTER(C.c_int)]),
     "fc_decode_batch": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int32, C.c_void_p, C.c_void_p]),
     "fc_last_batch_ms": (C.c_float, [C.c_void_p]),
     "fc_take_launch_count": (C.c_int64, []),

@@ -187,6 +187,7 @@ struct fc_stream {
     int table = 0;
     cudaStream_t cs = nullptr;
     cudaEvent_t cs_done = nullptr;
+    unsigned long long* rng_d = nullptr;   // xorshift64* state of a sampled generation
     unsigned long long* trace = nullptr;   // phase timeline of the persistent kernel
     int trace_on = 0;
 };
@@ -1142,6 +1143,104 @@ int fc_generate_greedy(fc_stream* s, const int32_t* prompt, int n, int max_new, 
     FC_CUDA(cudaEventRecord(s->ev1, st));
     FC_TRY(harvest());
     FC_CUDA(cudaEventElapsedTime(&s->last_decode_ms, s->ev0, s->ev1));
+    *n_out = made;
+    if (cancelled) return fail(FC_E_CANCELLED, "generation cancelled after %d tokens", made);
+    return FC_OK;
+}
+
+int fc_sample_logits(int device, const float* logits, int n, const fc_sampling* params, const int32_t* recent, int n_recent,
+                     uint64_t* rng_state, int32_t* token) {
+    if (!logits || !params || !rng_state || !token || (n_recent > 0 && !recent)) return fail(FC_E_ARG, "fc_sample_logits: null argument");
+    if (n <= 0 || n_recent < 0) return fail(FC_E_SHAPE, "fc_sample_logits: n = %d, n_recent = %d", n, n_recent);
+    FC_TRY(select_device(device));
+    Arena a;
+    float* d_logits = nullptr;
+    int* d_recent = nullptr;
+    unsigned long long* d_rng = nullptr;
+    int* d_tok = nullptr;
+    int rc = a.alloc_n(&d_logits, (size_t)n);
+    if (rc == FC_OK) rc = a.alloc_n(&d_recent, (size_t)std::max(n_recent, 1));
+    if (rc == FC_OK) rc = a.alloc_n(&d_rng, 1);
+    if (rc == FC_OK) rc = a.alloc_n(&d_tok, 1);
+    auto copy = [&](void* dst, const void* src, size_t bytes, cudaMemcpyKind kind) {
+        if (rc == FC_OK && bytes && cudaMemcpy(dst, src, bytes, kind) != cudaSuccess) rc = fail(FC_E_CUDA, "fc_sample_logits: copy failed");
+    };
+    copy(d_logits, logits, (size_t)n * 4, cudaMemcpyHostToDevice);
+    copy(d_recent, recent, (size_t)n_recent * 4, cudaMemcpyHostToDevice);
+    copy(d_rng, rng_state, 8, cudaMemcpyHostToDevice);
+    if (rc == FC_OK) rc = launch_sample(d_logits, n, 0, *params, d_recent, n_recent, d_rng, nullptr, 0, nullptr, d_tok, nullptr);
+    if (rc == FC_OK && cudaDeviceSynchronize() != cudaSuccess) rc = fail(FC_E_CUDA, "fc_sample_logits: the sampler failed");
+    copy(token, d_tok, 4, cudaMemcpyDeviceToHost);
+    copy(rng_state, d_rng, 8, cudaMemcpyDeviceToHost);
+    a.release();
+    return rc;
+}
+
+int fc_generate_sampled(fc_stream* s, const int32_t* prompt, int n, int max_new, int32_t eos, const fc_sampling* params,
+                        uint64_t* rng_state, const volatile int32_t* cancel, int32_t* out, int* n_out) {
+    if (!s || !prompt || !n_out || !params || !rng_state || (max_new > 0 && !out)) return fail(FC_E_ARG, "fc_generate_sampled: null argument");
+    *n_out = 0;
+    if (n <= 0) return fail(FC_E_SHAPE, "fc_generate_sampled: empty prompt (pass the BOS id, token_stream.rs:84-86)");
+    if (max_new < 0) return fail(FC_E_SHAPE, "fc_generate_sampled: max_new = %d", max_new);
+    fc_model* m = s->m;
+    const fc_config& c = m->cfg;
+    FC_CUDA(cudaSetDevice(m->device));
+    FC_TRY(check_ids(m, prompt, (size_t)n));
+    cudaStream_t st = m->st;
+    const int cap = std::max(1, (int)c.ctx), keep = std::max(1, cap / 2);
+    if (!s->rng_d) FC_TRY(s->arena.alloc_n(&s->rng_d, 1));
+    FC_CUDA(cudaMemcpyAsync(s->rng_d, rng_state, 8, cudaMemcpyHostToDevice, st));
+    s->last_decode_ms = 0.0f;
+    // window = the last `cap` prompt ids (token_stream.rs:87-89); priming leaves the distribution
+    // of the next token in s->probs
+    std::vector<int32_t> window(prompt + std::max(0, n - cap), prompt + n);
+    auto start_window = [&]() -> int {
+        FC_TRY(fc_stream_reset(s));
+        FC_CUDA(cudaMemcpyAsync(s->queue, window.data(), window.size() * 4, cudaMemcpyHostToDevice, st));
+        FC_TRY(set_state(s, 0, 0, (int)window.size(), eos, 0));
+        return feed_queued(s, (int)window.size(), STEP_PROBS);
+    };
+    FC_TRY(start_window());
+    FC_CUDA(cudaEventRecord(s->ev0, st));
+    int made = 0;
+    bool cancelled = false;
+    int rc = FC_OK;
+    while (made < max_new) {
+        if (cancel && *cancel) { cancelled = true; break; }
+        // draw from the current distribution with the window as `recent`; the token is appended
+        // to the queue on the device, or `done` is raised on eos
+        rc = launch_sample(s->probs, c.vocab, 1, *params, s->queue, 0, s->rng_d, s->queue, s->queue_cap, s->state, nullptr, st);
+        if (rc != FC_OK) break;
+        StepState hs;
+        rc = read_state(s, &hs);
+        if (rc != FC_OK) break;
+        if (hs.error) { rc = fail(hs.error, "decode step rejected a token or position on the device"); break; }
+        if (hs.done) break;                                   // eos: nothing was appended
+        int32_t tok = 0;
+        if (cudaMemcpy(&tok, s->queue + hs.tail - 1, 4, cudaMemcpyDeviceToHost) != cudaSuccess) { rc = fail(FC_E_CUDA, "token download failed"); break; }
+        out[made++] = tok;
+        window.push_back(tok);
+        if ((int)window.size() > cap) {
+            // the window outgrew the context: keep the last cap/2 ids and re-prime (token_stream.rs:162-165)
+            window.erase(window.begin(), window.end() - keep);
+            rc = start_window();
+        } else {
+            rc = run_steps(s, 1, STEP_PROBS, STEP_PROBS);     // feed(next): the distribution of the token after it
+        }
+        if (rc != FC_OK) break;
+    }
+    if (rc == FC_OK) {
+        FC_CUDA(cudaEventRecord(s->ev1, st));
+        StepState hs;
+        rc = read_state(s, &hs);
+        if (rc == FC_OK && hs.error) rc = fail(hs.error, "decode step rejected a token or position on the device");
+        if (rc == FC_OK) {
+            s->host_pos = hs.pos;
+            FC_CUDA(cudaEventElapsedTime(&s->last_decode_ms, s->ev0, s->ev1));
+        }
+    }
+    FC_CUDA(cudaMemcpy(rng_state, s->rng_d, 8, cudaMemcpyDeviceToHost));
+    if (rc != FC_OK) return rc;
     *n_out = made;
     if (cancelled) return fail(FC_E_CANCELLED, "generation cancelled after %d tokens", made);
     return FC_OK;

@@ -120,6 +120,9 @@ int launch_step_advance(StepState* state, cudaStream_t st);
 int launch_score_rows(const float* logits, int ldl, int V, const int* targets, int R, double* logprob,
                       uint8_t* is_greedy, int* status, cudaStream_t st);
 int launch_softmax_row(const float* logits, int V, float* probs, cudaStream_t st);
+// sample.cu — one draw of sample_with_params on the device; see the kernel for the arguments.
+int launch_sample(const float* in, int V, int from_probs, const fc_sampling& prm, const int* recent, int n_recent,
+                  unsigned long long* rng_state, int* queue, int queue_cap, StepState* state, int* token_out, cudaStream_t st);
 
 // attn.cu
 int launch_attn_decode(const float* q, const float* kcache, const float* vcache, int d, int H, int ctx,

@@ -34,6 +34,22 @@ def device_count():
     return _lib.lib().fc_device_count()
 
 
+def sampling(temperature=1.0, top_k=0, top_p=1.0, repetition_penalty=1.0):
+    """slm/sampling.rs SamplingParams (defaults as SamplingParams::default)."""
+    return _lib.FcSampling(temperature, top_k, top_p, repetition_penalty)
+
+
+def sample_logits(logits, rng_state, params, recent=(), device=0):
+    """One draw of sample_with_params on the GPU; returns (token, advanced rng state)."""
+    logits = np.ascontiguousarray(logits, dtype=np.float32)
+    rec = np.ascontiguousarray(recent, dtype=np.int32)
+    state = C.c_uint64(rng_state)
+    tok = C.c_int32(0)
+    check(_lib.lib().fc_sample_logits(device, _ptr(logits), logits.size, C.byref(params), _ptr(rec) if rec.size else None, rec.size,
+                                      C.byref(state), C.byref(tok)))
+    return tok.value, state.value
+
+
 def gguf_probe(path, row_perm=None):
     """Dimensions of a gpt2-architecture GGUF file; validates it without a GPU."""
     perm = None if row_perm is None else np.ascontiguousarray(row_perm, dtype=np.int32)
@@ -207,6 +223,18 @@ class CudaSlm:
             return buf[:n_out.value].copy(), True
         check(rc)
         return buf[:n_out.value].copy(), False
+
+    def generate_sampled(self, prompt_ids, max_tokens, params, rng_state, eos=-1, cancel=None):
+        """generate_tokens with a sampler (token_stream.rs:66-189); returns (ids, advanced rng state)."""
+        prompt = _ids(prompt_ids)
+        buf = np.empty(max(max_tokens, 1), dtype=np.int32)
+        n_out = C.c_int(0)
+        state = C.c_uint64(rng_state)
+        rc = _lib.lib().fc_generate_sampled(self._stream(), _ptr(prompt), prompt.size, max_tokens, eos, C.byref(params),
+                                            C.byref(state), None if cancel is None else _ptr(cancel), _ptr(buf), C.byref(n_out))
+        if rc != _lib.FC_E_CANCELLED:
+            check(rc)
+        return buf[:n_out.value].copy(), state.value
 
     def decode_batch(self, prompts2d, max_tokens, eos=-1):
         """Independent greedy streams (rows of prompts2d) on this GPU; returns a list of id arrays."""

@@ -215,6 +215,30 @@ int fc_prime(fc_stream* s, const int32_t* ids, int n, float* probs);
 int fc_generate_greedy(fc_stream* s, const int32_t* prompt, int n, int max_new, int32_t eos,
                        const volatile int32_t* cancel, int32_t* out, int* n_out);
 
+/* Decoding controls of slm/sampling.rs:26-39 SamplingParams (the cancel flag is a separate
+ * argument). temperature <= 0: greedy argmax of the penalised logits, no draw. top_k 0 and
+ * top_p 1.0 disable those filters, repetition_penalty 1.0 disables the penalty. */
+typedef struct fc_sampling {
+    float temperature;
+    int32_t top_k;
+    float top_p;
+    float repetition_penalty;
+} fc_sampling;
+/* sample_with_params (slm/sampling.rs:124-210) on the device for one row of `n` logits (host
+ * buffer): penalty over `recent` (once per occurrence), temperature softmax, top-k, top-p,
+ * renormalise, one xorshift64* draw (rng.rs:29-40). *rng_state is advanced exactly as the
+ * reference advances its Rng. Sums are block reductions, so a draw can differ from the
+ * sequential reference only when r lands within rounding of a cumulative boundary; probabilities
+ * tying exactly at the top-p cut are all kept. n <= 51200. */
+int fc_sample_logits(int device, const float* logits, int n, const fc_sampling* params, const int32_t* recent, int n_recent,
+                     uint64_t* rng_state, int32_t* token);
+/* generate_tokens / stream_next (slm/token_stream.rs:66-189) with sampling: prime the last ctx
+ * prompt ids, then per token draw from ln(max(p, 1e-12)) of the current distribution with the
+ * window's ids as `recent`, stop on eos, re-prime on the last ctx/2 ids when the window
+ * outgrows the context. The sampler and the generator state stay on the device between
+ * tokens; *rng_state returns advanced. */
+int fc_generate_sampled(fc_stream* s, const int32_t* prompt, int n, int max_new, int32_t eos, const fc_sampling* params,
+                        uint64_t* rng_state, const volatile int32_t* cancel, int32_t* out, int* n_out);
 /* n_streams independent greedy generations on one GPU: prompts [n_streams][prompt_len], out
  * [n_streams][max_new], n_out [n_streams]. Each is token_stream.rs:66-189 with temperature <= 0
  * on its own KV caches; the streams of a GPU currently run one after the other (weights are

@@ -250,6 +250,75 @@ int argmax_first(const float* xs, int n) {
     return best;
 }
 
+// slm/sampling.rs:106-121 pick_by_mass: the first index whose running mass reaches r; entries
+// that top-k / top-p zeroed are never picked; falls back to the last index with any mass.
+int pick_by_mass(const float* probs, int n, float r) {
+    float cumsum = 0.0f;
+    int last = 0;
+    for (int i = 0; i < n; ++i) {
+        if (probs[i] > 0.0f) {
+            last = i;
+            cumsum += probs[i];
+            if (r <= cumsum) return i;
+        }
+    }
+    return last;
+}
+
+// rng.rs:37-40 next_f32: 24 random bits / 2^24.
+float rng_next_f32(Rng& r) { return (float)(r.next_u64() >> 40) / (float)(1ull << 24); }
+
+// slm/sampling.rs:124-210 sample_with_params: repetition penalty on the logits of `recent`
+// (once per occurrence, CTRL scheme) -> temperature <= 0: argmax_first, no draw -> temperature
+// softmax (t = max(temperature, 0.01)) -> top-k -> top-p -> renormalise -> pick_by_mass with one
+// next_f32 draw. Sums run in index order like the Rust iterators; the sorts put equal
+// probabilities in an unspecified order (sort_unstable_by), here std::sort's.
+int sample_with_params(const float* logits, int n, float temperature, int top_k, float top_p, float rep_penalty,
+                       const int32_t* recent, int n_recent, Rng& rng) {
+    std::vector<float> work(logits, logits + n);
+    if (std::fabs(rep_penalty - 1.0f) > 1.1920929e-7f && rep_penalty > 0.0f) {
+        for (int i = 0; i < n_recent; ++i) {
+            const int tok = recent[i];
+            if (tok >= 0 && tok < n) work[tok] = work[tok] > 0.0f ? work[tok] / rep_penalty : work[tok] * rep_penalty;
+        }
+    }
+    if (temperature <= 0.0f) return argmax_first(work.data(), n);
+    const float t = std::fmax(temperature, 0.01f);
+    float mx = -INFINITY;
+    for (int i = 0; i < n; ++i) mx = std::fmax(mx, work[i]);
+    std::vector<float> probs(n);
+    for (int i = 0; i < n; ++i) probs[i] = std::exp((work[i] - mx) / t);
+    float sum = 0.0f;
+    for (int i = 0; i < n; ++i) sum += probs[i];
+    if (sum != sum || sum <= 1e-10f) return (int)(rng.next_u64() % (uint64_t)n);
+    for (int i = 0; i < n; ++i) probs[i] /= sum;
+    if (top_k > 0 && top_k < n) {
+        std::vector<float> sorted(probs);
+        std::sort(sorted.begin(), sorted.end(), [](float a, float b) { return a > b; });
+        const float threshold = sorted[top_k - 1];
+        for (int i = 0; i < n; ++i)
+            if (probs[i] < threshold) probs[i] = 0.0f;
+    }
+    if (top_p < 1.0f) {
+        std::vector<int> order(n);
+        for (int i = 0; i < n; ++i) order[i] = i;
+        std::sort(order.begin(), order.end(), [&](int a, int b) { return probs[a] > probs[b]; });
+        float cum = 0.0f;
+        std::vector<char> keep(n, 0);
+        for (int i : order) {
+            keep[i] = 1;
+            cum += probs[i];
+            if (cum >= top_p) break;
+        }
+        for (int i = 0; i < n; ++i)
+            if (!keep[i]) probs[i] = 0.0f;
+    }
+    float sum2 = 0.0f;
+    for (int i = 0; i < n; ++i) sum2 += probs[i];
+    for (int i = 0; i < n; ++i) probs[i] /= sum2;
+    return pick_by_mass(probs.data(), n, rng_next_f32(rng));
+}
+
 // ---------------------------------------------------------------- model
 struct Cfg { int32_t n_layer, d_model, n_head, d_ff, ctx, vocab, tied, math_mode; };
 struct LayerW {
@@ -507,6 +576,16 @@ void fo_layernorm(const float* x, const float* g, const float* b, int rows, int 
 float fo_gelu(float x) { return gelu(x); }
 void fo_softmax_rows(const float* x, int rows, int cols, float* out) { softmax_rows(x, rows, cols, out); }
 int fo_argmax_first(const float* x, int n) { return argmax_first(x, n); }
+int fo_pick_by_mass(const float* probs, int n, float r) { return pick_by_mass(probs, n, r); }
+float fo_rng_next_f32(uint64_t* state) { Rng r(1); r.s = *state; const float v = rng_next_f32(r); *state = r.s; return v; }
+int fo_sample_with_params(const float* logits, int n, float temperature, int top_k, float top_p, float rep_penalty,
+                          const int32_t* recent, int n_recent, uint64_t* rng_state) {
+    Rng r(1);
+    r.s = *rng_state;
+    const int tok = sample_with_params(logits, n, temperature, top_k, top_p, rep_penalty, recent, n_recent, r);
+    *rng_state = r.s;
+    return tok;
+}
 
 void* fo_model_create(const void* cfg, const void* weights, int threads) {
     return model_create((const Cfg*)cfg, (const Weights*)weights, threads);

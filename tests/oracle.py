@@ -53,6 +53,11 @@ def lib():
         L.fo_token_logprobs.restype = C.c_int
         L.fo_token_logprobs.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_double),
                                         C.POINTER(C.c_int), C.POINTER(C.c_int), C.c_void_p, C.c_void_p]
+        L.fo_pick_by_mass.restype, L.fo_pick_by_mass.argtypes = C.c_int, [C.c_void_p, C.c_int, C.c_float]
+        L.fo_rng_next_f32.restype, L.fo_rng_next_f32.argtypes = C.c_float, [C.POINTER(C.c_uint64)]
+        L.fo_sample_with_params.restype = C.c_int
+        L.fo_sample_with_params.argtypes = [C.c_void_p, C.c_int, C.c_float, C.c_int, C.c_float, C.c_float, C.c_void_p, C.c_int,
+                                            C.POINTER(C.c_uint64)]
         _lib = L
     return _lib
 
@@ -122,6 +127,32 @@ def softmax_rows(x):
     out = np.empty_like(x)
     lib().fo_softmax_rows(_ptr(x), x.shape[0], x.shape[1], _ptr(out))
     return out
+
+
+class Rng:
+    """rng.rs xorshift64*: the state travels with the object, as Rng does in the reference."""
+
+    def __init__(self, seed):
+        self.state = C.c_uint64(lib().fo_rng_seed(seed))
+
+    def next_u64(self):
+        return lib().fo_rng_next_u64(C.byref(self.state))
+
+    def next_f32(self):
+        return lib().fo_rng_next_f32(C.byref(self.state))
+
+
+def pick_by_mass(probs, r):
+    probs = f32(probs)
+    return lib().fo_pick_by_mass(_ptr(probs), probs.size, r)
+
+
+def sample_with_params(logits, rng, temperature=1.0, top_k=0, top_p=1.0, repetition_penalty=1.0, recent=()):
+    """slm/sampling.rs:124-210; advances `rng` exactly as the reference would."""
+    logits = f32(logits)
+    rec = np.ascontiguousarray(recent, dtype=np.int32)
+    return lib().fo_sample_with_params(_ptr(logits), logits.size, temperature, top_k, top_p, repetition_penalty,
+                                       _ptr(rec) if rec.size else None, rec.size, C.byref(rng.state))
 
 
 def argmax_first(x):

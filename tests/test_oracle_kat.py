@@ -213,3 +213,70 @@ def test_argmax_first_ties():
 def test_softmax_rows_sum_to_one():
     p = O.softmax_rows(np.random.RandomState(0).randn(5, 999) * 3)
     assert np.allclose(p.sum(axis=1), 1.0, atol=1e-5) and (p >= 0).all()
+
+
+# ---- sampler (slm/sampling.rs tests, :215-470) ---------------------------------------------
+def test_pick_by_mass_known_answers():
+    # sampling.rs:452-468
+    assert O.pick_by_mass([0.5, 0.4, 0.0, 0.0], 0.95) == 1
+    assert O.pick_by_mass([0.0, 0.0, 0.0], 0.5) == 0
+    assert O.pick_by_mass([0.2, 0.3, 0.5], 0.0) == 0
+    assert O.pick_by_mass([0.2, 0.3, 0.5], 0.2) == 0
+    assert O.pick_by_mass([0.2, 0.3, 0.5], 0.21) == 1
+    assert O.pick_by_mass([0.2, 0.3, 0.5], 1.0) == 2
+    assert O.pick_by_mass([0.0, 1.0], 0.0) == 1
+
+
+def test_sampler_known_answers():
+    # zero / negative temperature is argmax and draws nothing (sampling.rs:397-423)
+    logits = [0.1, 2.0, 1.9, -1.0]
+    for t in (0.0, -1.0):
+        for s in range(20):
+            assert O.sample_with_params(logits, O.Rng(s), temperature=t) == 1
+    assert O.sample_with_params(logits, O.Rng(0), temperature=0.0, repetition_penalty=2.0, recent=[1]) == 2
+    r, r2 = O.Rng(3), O.Rng(3)
+    before = r.next_u64()
+    O.sample_with_params(logits, r2, temperature=0.0)
+    assert r2.next_u64() == before
+    assert O.sample_with_params([1.0, 5.0, 5.0], O.Rng(1), temperature=0.0) == 1
+    # out-of-vocabulary recent tokens are ignored (sampling.rs:219-231)
+    lg = [0.5, -1.2, 2.3]
+    assert O.sample_with_params(lg, O.Rng(1), temperature=0.0, repetition_penalty=1.5, recent=[99]) == \
+        O.sample_with_params(lg, O.Rng(1), temperature=0.0, repetition_penalty=1.5)
+    # top_p = 1 equals disabled (sampling.rs:249-264)
+    lg = [0.5, -1.2, 2.3, 0.0, 1.1]
+    a, b = O.Rng(5), O.Rng(5)
+    for _ in range(100):
+        assert O.sample_with_params(lg, a) == O.sample_with_params(lg, b, top_p=1.0)
+    # top_k restricts the support (sampling.rs:297-317); top_p keeps the minimal set (:319-335)
+    rng = O.Rng(7)
+    for _ in range(500):
+        assert O.sample_with_params([5.0, 4.0, -2.0, -3.0, -5.0], rng, top_k=2) in (0, 1)
+    rng = O.Rng(3)
+    for _ in range(500):
+        assert O.sample_with_params([10.0, 1.0, 0.5, 0.0], rng, top_p=0.5) == 0
+    # a heavy repetition penalty redirects the mass (sampling.rs:337-362)
+    rng = O.Rng(11)
+    ones = sum(O.sample_with_params([4.0, 3.0, -2.0], rng, repetition_penalty=100.0, recent=[0]) == 1 for _ in range(1000))
+    assert ones > 800
+
+
+def test_temperature_only_sampler_matches_the_legacy_formula():
+    # sampling.rs:266-295: temperature softmax + one next_f32 draw + first index reaching r
+    logits = np.array([0.5, -1.2, 2.3, 0.0, 1.1, -0.4], dtype=np.float32)
+    temp = np.float32(0.8)
+    r1, r2 = O.Rng(42), O.Rng(42)
+    for _ in range(200):
+        p = np.exp((logits - logits.max()) / temp).astype(np.float32)
+        s = np.float32(0)
+        for v in p:
+            s = np.float32(s + v)
+        p = (p / s).astype(np.float32)
+        r = r1.next_f32()
+        c, want = np.float32(0), len(p) - 1
+        for i, v in enumerate(p):
+            c = np.float32(c + v)
+            if r <= c:
+                want = i
+                break
+        assert O.sample_with_params(logits, r2, temperature=float(temp)) == want
