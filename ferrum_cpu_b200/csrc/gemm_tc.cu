@@ -240,25 +240,30 @@ gemm_q8_bf16x3_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_c
             const size_t n = (size_t)(n0 + row);     // < N_pad (zero rows past N)
             const uint8_t* qrow = a.qu + n * a.K + half * 32;
             const __half* drow = a.d + n * (a.K >> 5) + half;
-            // two k-blocks of quants are kept in flight ahead of the one being converted
-            uint4 qa[2], qc[2];
-            float sc[2];
-#pragma unroll
-            for (int pf = 0; pf < 2; ++pf) {
-                if (pf < nkb) {
-                    qa[pf] = __ldg((const uint4*)(qrow + (size_t)pf * BK));
-                    qc[pf] = __ldg((const uint4*)(qrow + (size_t)pf * BK) + 1);
-                    sc[pf] = __half2float(__ldg(drow + pf * 2));
-                }
+            // two k-blocks of quants are kept in flight ahead of the one being converted; they
+            // rotate through named registers (an array indexed by kb & 1 would live in local memory)
+            const uint4 z4 = make_uint4(0u, 0u, 0u, 0u);
+            uint4 qa0 = z4, qc0 = z4, qa1 = z4, qc1 = z4;
+            float sc0 = 0.0f, sc1 = 0.0f;
+            if (0 < nkb) {
+                qa0 = __ldg((const uint4*)qrow);
+                qc0 = __ldg((const uint4*)qrow + 1);
+                sc0 = __half2float(__ldg(drow));
+            }
+            if (1 < nkb) {
+                qa1 = __ldg((const uint4*)(qrow + (size_t)BK));
+                qc1 = __ldg((const uint4*)(qrow + (size_t)BK) + 1);
+                sc1 = __half2float(__ldg(drow + 2));
             }
             for (int kb = 0; kb < nkb; ++kb, ++it) {
                 const int s = it % STAGES;
-                const uint4 c0 = qa[kb & 1], c1 = qc[kb & 1];
-                const float scale = sc[kb & 1];
+                const uint4 c0 = qa0, c1 = qc0;
+                const float scale = sc0;
+                qa0 = qa1; qc0 = qc1; sc0 = sc1;
                 if (kb + 2 < nkb) {
-                    qa[kb & 1] = __ldg((const uint4*)(qrow + (size_t)(kb + 2) * BK));
-                    qc[kb & 1] = __ldg((const uint4*)(qrow + (size_t)(kb + 2) * BK) + 1);
-                    sc[kb & 1] = __half2float(__ldg(drow + (kb + 2) * 2));
+                    qa1 = __ldg((const uint4*)(qrow + (size_t)(kb + 2) * BK));
+                    qc1 = __ldg((const uint4*)(qrow + (size_t)(kb + 2) * BK) + 1);
+                    sc1 = __half2float(__ldg(drow + (kb + 2) * 2));
                 }
                 // the conversion runs before the stage is waited for: only the stores sit between
                 // the stage becoming free and becoming full again
