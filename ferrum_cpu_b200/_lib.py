@@ -33,6 +33,26 @@ class FcSampling(C.Structure):
     _fields_ = [("temperature", C.c_float), ("top_k", C.c_int32), ("top_p", C.c_float), ("repetition_penalty", C.c_float)]
 
 
+class FcLlamaConfig(C.Structure):
+    _fields_ = [("vocab", C.c_int32), ("d_model", C.c_int32), ("n_layer", C.c_int32), ("n_head", C.c_int32),
+                ("n_kv_head", C.c_int32), ("head_dim", C.c_int32), ("d_ff", C.c_int32), ("rope_dim", C.c_int32),
+                ("rope_base", C.c_float), ("rope_type", C.c_int32), ("rope_linear_factor", C.c_float),
+                ("norm_eps", C.c_float), ("ctx", C.c_int32), ("tied", C.c_int32), ("math_mode", C.c_int32)]
+
+
+class FcLlamaLayer(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in (
+        "attn_norm", "wq_q8", "wk_q8", "wv_q8", "wo_q8", "bq", "bk", "bv", "ffn_norm", "gate_q8", "up_q8", "down_q8")]
+
+
+class FcLlamaWeights(C.Structure):
+    _fields_ = [("token_embd_q8", C.c_void_p), ("layers", C.POINTER(FcLlamaLayer)), ("output_norm", C.c_void_p),
+                ("output_q8", C.c_void_p), ("rope_freqs", C.c_void_p)]
+
+
+FC_ROPE_NORM, FC_ROPE_NEOX = 0, 1
+
+
 class FcScore(C.Structure):
     _fields_ = [("logprob", C.c_double), ("n_tokens", C.c_int64), ("greedy", C.c_int32)]
 
@@ -77,6 +97,20 @@ SIGNATURES = {
     "fc_generate_sampled": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int32, C.POINTER(FcSampling), C.POINTER(C.c_uint64), C.c_void_p, C.c_void_p, C.POINTER(C.c_int)]),
     "fc_decode_batch": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int32, C.c_void_p, C.c_void_p]),
     "fc_last_batch_ms": (C.c_float, [C.c_void_p]),
+    "fc_llama_create": (C.c_int, [C.POINTER(FcLlamaConfig), C.POINTER(FcLlamaWeights), C.c_int, C.POINTER(C.c_void_p)]),
+    "fc_llama_free": (None, [C.c_void_p]),
+    "fc_llama_forward_tokens": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
+    "fc_llama_score_from": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.POINTER(FcScore), C.c_void_p, C.c_void_p]),
+    "fc_llama_score_sequences": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.POINTER(FcScore), C.c_void_p]),
+    "fc_llama_last_score_ms": (C.c_float, [C.c_void_p]),
+    "fc_llama_cache_create": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
+    "fc_llama_cache_free": (None, [C.c_void_p]),
+    "fc_llama_cache_clear": (C.c_int, [C.c_void_p]),
+    "fc_llama_cache_pos": (C.c_int, [C.c_void_p]),
+    "fc_llama_forward_one": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p]),
+    "fc_llama_generate": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.POINTER(FcSampling), C.c_void_p, C.c_int,
+                                    C.POINTER(C.c_uint64), C.c_void_p, C.c_void_p, C.POINTER(C.c_int)]),
+    "fc_llama_last_decode_ms": (C.c_float, [C.c_void_p]),
     "fc_take_launch_count": (C.c_int64, []),
     "fc_last_decode_ms": (C.c_float, [C.c_void_p]),
     "fc_last_score_ms": (C.c_float, [C.c_void_p]),

@@ -35,7 +35,7 @@ int cuda_fail(cudaError_t e, const char* what, const char* file, int line) {
 }
 
 // Refuses anything but a Blackwell data-centre part: there is no other code path.
-static int select_device(int device) {
+int select_device(int device) {
     int n = 0;
     if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0) {
         cudaGetLastError();
@@ -49,23 +49,7 @@ static int select_device(int device) {
     return FC_OK;
 }
 
-// Owns device allocations; frees them in the destructor.
-struct Arena {
-    std::vector<void*> ptrs;
-    int alloc(void** p, size_t bytes) {
-        FC_CUDA(cudaMalloc(p, bytes ? bytes : 16));
-        ptrs.push_back(*p);
-        return FC_OK;
-    }
-    template <class T>
-    int alloc_n(T** p, size_t n) { return alloc((void**)p, n * sizeof(T)); }
-    void release() {
-        for (void* p : ptrs) cudaFree(p);
-        ptrs.clear();
-    }
-};
-
-static int upload_f32(Arena& ar, const float* host, size_t n, float** dev, cudaStream_t st) {
+int upload_f32(Arena& ar, const float* host, size_t n, float** dev, cudaStream_t st) {
     if (!host) return fail(FC_E_FORMAT, "a required f32 tensor is null");
     FC_TRY(ar.alloc_n(dev, n));
     FC_CUDA(cudaMemcpyAsync(*dev, host, n * sizeof(float), cudaMemcpyHostToDevice, st));
@@ -73,7 +57,7 @@ static int upload_f32(Arena& ar, const float* host, size_t n, float** dev, cudaS
 }
 
 // loader/mod.rs:147-154: a matrix is Q8_0 only when its row length is a multiple of 32.
-static int upload_q8(Arena& ar, const void* host, int N, int K, QMat* out, cudaStream_t st) {
+int upload_q8(Arena& ar, const void* host, int N, int K, QMat* out, cudaStream_t st) {
     if (!host) return fail(FC_E_FORMAT, "a required Q8_0 tensor is null");
     if (N <= 0 || K <= 0 || K % 32) return fail(FC_E_FORMAT, "Q8_0 matrix [%d][%d]: row length must be a positive multiple of 32", N, K);
     if (K > 12288) return fail(FC_E_SHAPE, "row length %d exceeds the 12288 supported by the decode GEMV", K);

@@ -8,14 +8,15 @@ namespace fc {
 // --------------------------------------------------------------------------- decode form
 // layer/transformer.rs:246-283 forward_with_cache, per head h: scores[j] = (q_h · k_h(j)) *
 // 1/sqrt(hd) over the len cached rows, softmax (max, exp, sum), out_h = sum_j (e_j/sum) v_h(j).
-// One block per head. Caches are [ctx][d] f32 per layer.
+// One block per query head. Cache rows are kvd floats apart; query head h reads key/value head
+// h / group (grouped-query attention, llm.rs:305-341; group == 1 is the GPT-2 form).
 __global__ void __launch_bounds__(256) attn_decode_kernel(const float* __restrict__ q, const float* __restrict__ kc,
-                                                          const float* __restrict__ vc, int d, int hd, int ctx,
+                                                          const float* __restrict__ vc, int kvd, int group, int hd, int ctx,
                                                           const StepState* st, float* __restrict__ out) {
     extern __shared__ float sm[];   // scores[ctx] | q_h[hd] | red[64] | part[8][hd]
     if (st->done | st->error) return;
     const int len = st->pos + 1;    // the new row was appended by the QKV GEMV
-    const int h = blockIdx.x, hs = h * hd;
+    const int h = blockIdx.x, hs = h * hd, ks = (h / group) * hd;
     float* sc = sm;
     float* qh = sm + ctx;
     float* red = qh + hd;
@@ -27,7 +28,7 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(const float* __restric
     // scores: one warp per cached row, lanes across the head dimension
     float mx = -INFINITY;
     for (int j = wid; j < len; j += nw) {
-        const float* kr = kc + (size_t)j * d + hs;
+        const float* kr = kc + (size_t)j * kvd + ks;
         float dot = 0.0f;
         for (int c = lane; c < hd; c += 32) dot = fmaf(qh[c], kr[c], dot);
 #pragma unroll
@@ -59,7 +60,7 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(const float* __restric
     const int g = threadIdx.x / hd, c = threadIdx.x - g * hd;
     if (g < G) {
         float acc = 0.0f;
-        for (int j = g; j < len; j += G) acc = fmaf(sc[j] / sum, vc[(size_t)j * d + hs + c], acc);
+        for (int j = g; j < len; j += G) acc = fmaf(sc[j] / sum, vc[(size_t)j * kvd + ks + c], acc);
         part[g * hd + c] = acc;
     }
     __syncthreads();
@@ -70,15 +71,21 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(const float* __restric
     }
 }
 
-int launch_attn_decode(const float* q, const float* kcache, const float* vcache, int d, int H, int ctx,
-                       const StepState* state, float* out, cudaStream_t st) {
-    const int hd = d / H;
+int launch_attn_decode_gqa(const float* q, const float* kcache, const float* vcache, int H, int KV, int hd, int ctx,
+                           const StepState* state, float* out, cudaStream_t st) {
     if (hd > 256) return fail(FC_E_SHAPE, "head_dim %d exceeds 256", hd);
     const int threads = 256;
     const size_t smem = (size_t)(ctx + hd + 64 + (threads / hd) * hd) * sizeof(float);
-    attn_decode_kernel<<<H, threads, smem, st>>>(q, kcache, vcache, d, hd, ctx, state, out);
+    if (smem > 200 * 1024) return fail(FC_E_SHAPE, "context %d exceeds what the decode attention holds in shared memory", ctx);
+    if (smem > 48 * 1024) FC_CUDA(cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    attn_decode_kernel<<<H, threads, smem, st>>>(q, kcache, vcache, KV * hd, H / KV, hd, ctx, state, out);
     FC_LAUNCHED();
     return FC_OK;
+}
+
+int launch_attn_decode(const float* q, const float* kcache, const float* vcache, int d, int H, int ctx,
+                       const StepState* state, float* out, cudaStream_t st) {
+    return launch_attn_decode_gqa(q, kcache, vcache, H, H, d / H, ctx, state, out, st);
 }
 
 // --------------------------------------------------------------------------- window form
@@ -88,8 +95,11 @@ int launch_attn_decode(const float* q, const float* kcache, const float* vcache,
 // every 4th key of the tile for the scores and the P·V partial sums.
 constexpr int QT = 64;   // query rows per block
 constexpr int KT = 64;   // keys per tile
+// Rows of q, k and v are ld floats apart (they may be slices of one fused buffer); query head
+// h reads key/value head h / group; output rows are ldo floats apart.
 template <int HD>
-__global__ void __launch_bounds__(256) attn_prefill_kernel(const float* __restrict__ qkv, int T, int d, int H,
+__global__ void __launch_bounds__(256) attn_prefill_kernel(const float* __restrict__ q, const float* __restrict__ k,
+                                                           const float* __restrict__ v, int T, int ld, int group, int ldo,
                                                            float* __restrict__ out) {
     constexpr int LDS = HD + 4;                 // row stride in floats: 16-byte aligned, bank-shifted by 4
     extern __shared__ float4 sm4[];
@@ -99,8 +109,10 @@ __global__ void __launch_bounds__(256) attn_prefill_kernel(const float* __restri
     const int h = blockIdx.y, b = blockIdx.z;
     const int qi = threadIdx.x >> 2, part = threadIdx.x & 3;
     const int i = qt * QT + qi;                 // query row within the window
-    const size_t row3 = (size_t)3 * d;
-    const float* base = qkv + (size_t)b * T * row3 + (size_t)h * HD;
+    const size_t row3 = (size_t)ld;
+    const float* base = q + (size_t)b * T * row3 + (size_t)h * HD;
+    const float* kbase = k + (size_t)b * T * row3 + (size_t)(h / group) * HD;
+    const float* vbase = v + (size_t)b * T * row3 + (size_t)(h / group) * HD;
     const float scale = 1.0f / sqrtf((float)HD);
 
     float qreg[HD];
@@ -128,9 +140,8 @@ __global__ void __launch_bounds__(256) attn_prefill_kernel(const float* __restri
             const int r = u / (HD / 4), c4 = u - r * (HD / 4);
             float4 kv = make_float4(0, 0, 0, 0), vv = kv;
             if (k0 + r < T) {
-                const float* rp = base + (size_t)(k0 + r) * row3;
-                kv = ((const float4*)(rp + d))[c4];
-                vv = ((const float4*)(rp + 2 * d))[c4];
+                kv = ((const float4*)(kbase + (size_t)(k0 + r) * row3))[c4];
+                vv = ((const float4*)(vbase + (size_t)(k0 + r) * row3))[c4];
             }
             ((float4*)(ks + r * LDS))[c4] = kv;
             ((float4*)(vs + r * LDS))[c4] = vv;
@@ -187,7 +198,7 @@ __global__ void __launch_bounds__(256) attn_prefill_kernel(const float* __restri
         o[c] = v;
     }
     if (i < T) {
-        float* op = out + ((size_t)b * T + i) * d + (size_t)h * HD;
+        float* op = out + ((size_t)b * T + i) * ldo + (size_t)h * HD;
         // lane `part` stores its quarter of the head dimension
 #pragma unroll
         for (int c = 0; c < HD / 4; ++c)
@@ -195,20 +206,82 @@ __global__ void __launch_bounds__(256) attn_prefill_kernel(const float* __restri
     }
 }
 
-int launch_attn_prefill(const float* qkv, int B, int T, int d, int H, float* out, cudaStream_t st) {
-    const int hd = d / H;
+// Any head width (a multiple of 4, at most 256): one warp per query row, lanes across the head
+// dimension, keys read straight from global memory. Slower than the tiled kernel; used for the
+// head widths that kernel is not instantiated for.
+__global__ void __launch_bounds__(256) attn_prefill_any_kernel(const float* __restrict__ q, const float* __restrict__ k,
+                                                               const float* __restrict__ v, int T, int ld, int group, int hd,
+                                                               int ldo, float* __restrict__ out) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int i = (gridDim.x - 1 - blockIdx.x) * 8 + wid;      // late (long) rows first
+    const int h = blockIdx.y, b = blockIdx.z;
+    if (i >= T) return;
+    const float* qr = q + ((size_t)b * T + i) * ld + (size_t)h * hd;
+    const float* kb = k + (size_t)b * T * ld + (size_t)(h / group) * hd;
+    const float* vb = v + (size_t)b * T * ld + (size_t)(h / group) * hd;
+    const float scale = 1.0f / sqrtf((float)hd);
+    float qv[8], o[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+        const int c = lane + 32 * u;
+        qv[u] = c < hd ? qr[c] : 0.0f;
+        o[u] = 0.0f;
+    }
+    float m = -INFINITY, l = 0.0f;
+    for (int j = 0; j <= i; ++j) {
+        const float* kr = kb + (size_t)j * ld;
+        float dot = 0.0f;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int c = lane + 32 * u;
+            if (c < hd) dot = fmaf(qv[u], kr[c], dot);
+        }
+#pragma unroll
+        for (int s = 16; s > 0; s >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, s);
+        const float sc = dot * scale;
+        const float mnew = fmaxf(m, sc);
+        const float corr = expf(m - mnew), p = expf(sc - mnew);
+        l = l * corr + p;
+        const float* vr = vb + (size_t)j * ld;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int c = lane + 32 * u;
+            if (c < hd) o[u] = fmaf(p, vr[c], o[u] * corr);
+        }
+        m = mnew;
+    }
+    float* op = out + ((size_t)b * T + i) * ldo + (size_t)h * hd;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+        const int c = lane + 32 * u;
+        if (c < hd) op[c] = o[u] / l;
+    }
+}
+
+int launch_attn_prefill_gqa(const float* q, const float* k, const float* v, int B, int T, int ld, int H, int KV, int hd,
+                            int ldo, float* out, cudaStream_t st) {
+    if (KV <= 0 || H % KV) return fail(FC_E_DIM, "n_heads %d must be a multiple of n_kv_heads %d", H, KV);
+    const int group = H / KV;
     dim3 grid((T + QT - 1) / QT, H, B);
-    if (hd == 64) {
+    const bool aligned = ((ld | ldo) & 3) == 0 && ((((uintptr_t)q) | ((uintptr_t)k) | ((uintptr_t)v) | ((uintptr_t)out)) & 15) == 0;
+    if (hd == 64 && aligned) {
         const size_t smem = (size_t)2 * KT * (64 + 4) * sizeof(float);
-        attn_prefill_kernel<64><<<grid, 256, smem, st>>>(qkv, T, d, H, out);
-    } else if (hd == 32) {
+        attn_prefill_kernel<64><<<grid, 256, smem, st>>>(q, k, v, T, ld, group, ldo, out);
+    } else if (hd == 32 && aligned) {
         const size_t smem = (size_t)2 * KT * (32 + 4) * sizeof(float);
-        attn_prefill_kernel<32><<<grid, 256, smem, st>>>(qkv, T, d, H, out);
+        attn_prefill_kernel<32><<<grid, 256, smem, st>>>(q, k, v, T, ld, group, ldo, out);
+    } else if (hd <= 256) {
+        dim3 g2((T + 7) / 8, H, B);
+        attn_prefill_any_kernel<<<g2, 256, 0, st>>>(q, k, v, T, ld, group, hd, ldo, out);
     } else {
-        return fail(FC_E_SHAPE, "window attention supports head_dim 32 or 64, got %d", hd);
+        return fail(FC_E_SHAPE, "window attention supports head_dim up to 256, got %d", hd);
     }
     FC_LAUNCHED();
     return FC_OK;
+}
+
+int launch_attn_prefill(const float* qkv, int B, int T, int d, int H, float* out, cudaStream_t st) {
+    return launch_attn_prefill_gqa(qkv, qkv + d, qkv + 2 * d, B, T, 3 * d, H, H, d / H, d, out, st);
 }
 
 }  // namespace fc

@@ -6,6 +6,7 @@
 
 #include <cstddef>
 #include <cstdint>
+#include <vector>
 
 #include "../../include/ferrum_cuda.h"
 
@@ -33,6 +34,29 @@ extern thread_local int64_t g_launches;
         ++fc::g_launches;            \
         FC_CUDA(cudaGetLastError()); \
     } while (0)
+
+// ---- host helpers shared by the API files (defined in api.cu) ---------------------------
+// Owns device allocations until release().
+struct Arena {
+    std::vector<void*> ptrs;
+    int alloc(void** p, size_t bytes) {
+        FC_CUDA(cudaMalloc(p, bytes ? bytes : 16));
+        ptrs.push_back(*p);
+        return FC_OK;
+    }
+    template <class T>
+    int alloc_n(T** p, size_t n) { return alloc((void**)p, n * sizeof(T)); }
+    void release() {
+        for (void* p : ptrs) cudaFree(p);
+        ptrs.clear();
+    }
+};
+struct QMat;
+// Makes `device` current; refuses anything but an sm_100 part (there is no other code path).
+int select_device(int device);
+int upload_f32(Arena& ar, const float* host, size_t n, float** dev, cudaStream_t st);
+// Raw GGML Q8_0 rows [N][K/32 x 34 B] -> the device planes of QMat.
+int upload_q8(Arena& ar, const void* host, int N, int K, QMat* out, cudaStream_t st);
 
 // ---- device layout of one Q8_0 matrix [N][K] ----------------------------------------
 // The 34-byte GGML blocks are split at upload into two planes so that every row starts
@@ -129,6 +153,12 @@ int launch_attn_decode(const float* q, const float* kcache, const float* vcache,
                        const StepState* state, float* out, cudaStream_t st);
 // qkv [R][3d] (q | k | v per row), R = B·T, causal within each window of T rows.
 int launch_attn_prefill(const float* qkv, int B, int T, int d, int H, float* out, cudaStream_t st);
+// Grouped-query forms (llm.rs:305-341): H query heads share KV key/value heads of width hd.
+// Decode: q [H*hd], caches [ctx][KV*hd]. Window: q, k, v rows ld floats apart, out rows ldo apart.
+int launch_attn_decode_gqa(const float* q, const float* kcache, const float* vcache, int H, int KV, int hd, int ctx,
+                           const StepState* state, float* out, cudaStream_t st);
+int launch_attn_prefill_gqa(const float* q, const float* k, const float* v, int B, int T, int ld, int H, int KV, int hd,
+                            int ldo, float* out, cudaStream_t st);
 // attn_tc.cu — the same on tcgen05 (head_dim 64): bf16 hi / lo planes of qkv [B*T][3d] in,
 // planes of the attention output [B*T][d] out; `status` is raised on a timeout.
 int launch_attn_prefill_tc(const void* qkv_hi, const void* qkv_lo, int B, int T, int d, int H, void* out_hi, void* out_lo,

@@ -1,0 +1,626 @@
+// C ABI of the imported Llama / Qwen decoder (ferrum_core/src/llm.rs, llm_score.rs) on the
+// Q8_0 kernels of this library: upload, the full-sequence forward and exact log-softmax
+// scorer, and the KV-cached decode driver with on-device sampling.
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <vector>
+
+#include "llama_ops.cuh"
+
+using namespace fc;
+
+namespace {
+
+struct LlamaLayerDev {
+    QMat qkv, wo, gateup, down;      // wq|wk|wv rows fused, gate|up rows fused
+    float* qkv_b = nullptr;          // fused q|k|v bias, or null when the file has none
+    float *attn_norm = nullptr, *ffn_norm = nullptr;
+};
+
+}  // namespace
+
+struct fc_llama {
+    fc_llama_config cfg;
+    int device = 0;
+    cudaStream_t st = nullptr;
+    Arena arena, ws_arena;
+    QMat tok, head;
+    float* out_norm = nullptr;
+    float2* ftab = nullptr;          // per rotary pair: {frequency, frequency divisor}
+    float inv_linear = 1.0f;
+    std::vector<LlamaLayerDev> layers;
+    int q_dim = 0, kv_dim = 0, qkv_dim = 0;
+    // window-forward workspace for ws_rows rows
+    int ws_rows = 0, head_chunk = 0;
+    float *x = nullptr, *n = nullptr, *qkv = nullptr, *att = nullptr, *gu = nullptr, *hid = nullptr, *logits = nullptr;
+    int *ids_d = nullptr, *targets_d = nullptr, *err_d = nullptr, *tc_status = nullptr;
+    double* lp_d = nullptr;
+    uint8_t* gr_d = nullptr;
+    uint16_t *xhi = nullptr, *xlo = nullptr;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    float last_score_ms = 0.0f;
+};
+
+struct fc_llama_cache {
+    fc_llama* m = nullptr;
+    int device = 0;                       // kept here so that freeing does not read the model
+    Arena arena;
+    float *kc = nullptr, *vc = nullptr;   // [L][ctx][kv_dim]
+    float *x = nullptr, *n = nullptr, *qkv = nullptr, *att = nullptr, *gu = nullptr, *hid = nullptr, *logits = nullptr;
+    int* queue = nullptr;
+    int queue_cap = 0;
+    StepState* state = nullptr;
+    int host_pos = 0;
+    cudaGraphExec_t graph[2] = {nullptr, nullptr};   // [0]: step without the head, [1]: with it
+    int graph_nodes[2] = {0, 0};
+    unsigned long long* rng_d = nullptr;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    float last_decode_ms = 0.0f;
+};
+
+namespace {
+
+constexpr size_t q8_row_bytes(int K) { return (size_t)(K / 32) * 34; }
+
+// Rows of several raw Q8_0 tensors with the same row length, one after the other.
+int upload_fused(Arena& ar, std::initializer_list<std::pair<const void*, int>> parts, int K, QMat* out, cudaStream_t st) {
+    if (K <= 0 || K % 32) return fail(FC_E_FORMAT, "Q8_0 row length %d must be a positive multiple of 32", K);
+    size_t rows = 0;
+    for (auto& p : parts) {
+        if (!p.first) return fail(FC_E_FORMAT, "a required Q8_0 tensor is null");
+        rows += (size_t)p.second;
+    }
+    std::vector<uint8_t> buf(rows * q8_row_bytes(K));
+    size_t at = 0;
+    for (auto& p : parts) {
+        const size_t bytes = (size_t)p.second * q8_row_bytes(K);
+        std::memcpy(buf.data() + at, p.first, bytes);
+        at += bytes;
+    }
+    return upload_q8(ar, buf.data(), (int)rows, K, out, st);
+}
+
+int gemm(fc_llama* m, const QMat& w, const float* x, const float* bias, const float* res, float* y, int M, int ldy) {
+    if (m->cfg.math_mode == FC_MATH_BF16X3 && w.K % 64 == 0) {
+        FC_TRY(launch_split_bf16(x, m->xhi, m->xlo, (size_t)M * w.K, m->st));
+        return launch_gemm_q8_bf16x3(w, m->xhi, m->xlo, bias, res, EPI_NONE, y, M, ldy, m->tc_status, m->st);
+    }
+    return launch_gemm_q8_fp32(w, x, bias, res, EPI_NONE, y, M, ldy, m->st);
+}
+
+int ensure_workspace(fc_llama* m, int rows) {
+    if (rows <= m->ws_rows) return FC_OK;
+    m->ws_arena.release();
+    m->ws_rows = 0;
+    const fc_llama_config& c = m->cfg;
+    const size_t R = rows, d = c.d_model, F = c.d_ff;
+    size_t chunk = ((size_t)1 << 28) / (size_t)m->head.N_pad;   // logits for head_chunk rows at a time (<= 1 GiB)
+    chunk = std::max<size_t>(1, std::min<size_t>(chunk, R));
+    Arena& a = m->ws_arena;
+    FC_TRY(a.alloc_n(&m->x, R * d));
+    FC_TRY(a.alloc_n(&m->n, R * d));
+    FC_TRY(a.alloc_n(&m->qkv, R * (size_t)m->qkv_dim));
+    FC_TRY(a.alloc_n(&m->att, R * (size_t)m->q_dim));
+    FC_TRY(a.alloc_n(&m->gu, R * 2 * F));
+    FC_TRY(a.alloc_n(&m->hid, R * F));
+    FC_TRY(a.alloc_n(&m->logits, chunk * (size_t)m->head.N_pad));
+    FC_TRY(a.alloc_n(&m->ids_d, R));
+    FC_TRY(a.alloc_n(&m->targets_d, R));
+    FC_TRY(a.alloc_n(&m->lp_d, R));
+    FC_TRY(a.alloc_n(&m->gr_d, R));
+    FC_TRY(a.alloc_n(&m->err_d, 1));
+    FC_TRY(a.alloc_n(&m->tc_status, 1));
+    FC_CUDA(cudaMemsetAsync(m->tc_status, 0, sizeof(int), m->st));
+    if (c.math_mode == FC_MATH_BF16X3) {
+        const size_t widest = std::max({d, F, (size_t)m->q_dim});
+        FC_TRY(a.alloc_n(&m->xhi, R * widest));
+        FC_TRY(a.alloc_n(&m->xlo, R * widest));
+    }
+    m->ws_rows = rows;
+    m->head_chunk = (int)chunk;
+    return FC_OK;
+}
+
+// LlamaModel::forward_tokens (llm.rs:622-635) up to the final norm, for B windows of T rows
+// whose ids are in m->ids_d: every row r sits at position r % T. Leaves RMSNorm(h) in m->n.
+int forward_rows(fc_llama* m, int B, int T) {
+    const fc_llama_config& c = m->cfg;
+    const int R = B * T, d = c.d_model, F = c.d_ff;
+    cudaStream_t st = m->st;
+    FC_CUDA(cudaMemsetAsync(m->err_d, 0, sizeof(int), st));
+    FC_TRY(launch_llama_embed_rows(m->tok, m->ids_d, R, m->x, m->err_d, st));
+    for (int l = 0; l < c.n_layer; ++l) {
+        const LlamaLayerDev& L = m->layers[l];
+        // LlamaBlock::forward_full (llm.rs:464-482)
+        FC_TRY(launch_llama_rmsnorm(m->x, L.attn_norm, c.norm_eps, R, d, m->n, nullptr, st));
+        FC_TRY(gemm(m, L.qkv, m->n, L.qkv_b, nullptr, m->qkv, R, m->qkv_dim));
+        FC_TRY(launch_llama_rope_rows(m->qkv, R, m->qkv_dim, T, c.n_head, c.n_kv_head, m->q_dim, c.head_dim, c.rope_dim,
+                                      c.rope_type == FC_ROPE_NEOX, m->ftab, m->inv_linear, st));
+        FC_TRY(launch_attn_prefill_gqa(m->qkv, m->qkv + m->q_dim, m->qkv + m->q_dim + m->kv_dim, B, T, m->qkv_dim, c.n_head,
+                                       c.n_kv_head, c.head_dim, m->q_dim, m->att, st));
+        FC_TRY(gemm(m, L.wo, m->att, nullptr, m->x, m->x, R, d));
+        FC_TRY(launch_llama_rmsnorm(m->x, L.ffn_norm, c.norm_eps, R, d, m->n, nullptr, st));
+        FC_TRY(gemm(m, L.gateup, m->n, nullptr, nullptr, m->gu, R, 2 * F));
+        FC_TRY(launch_llama_swiglu(m->gu, R, F, m->hid, nullptr, st));
+        FC_TRY(gemm(m, L.down, m->hid, nullptr, m->x, m->x, R, d));
+    }
+    return launch_llama_rmsnorm(m->x, m->out_norm, c.norm_eps, R, d, m->n, nullptr, st);
+}
+
+int check_ids(const fc_llama* m, const int32_t* ids, size_t n) {
+    for (size_t i = 0; i < n; ++i)
+        if (ids[i] < 0 || ids[i] >= m->cfg.vocab) return fail(FC_E_DIM, "token %d ≥ vocab_size %d", ids[i], m->cfg.vocab);
+    return FC_OK;
+}
+
+int check_status(fc_llama* m) {
+    int err = 0, status = 0;
+    FC_CUDA(cudaMemcpyAsync(&err, m->err_d, sizeof(int), cudaMemcpyDeviceToHost, m->st));
+    FC_CUDA(cudaMemcpyAsync(&status, m->tc_status, sizeof(int), cudaMemcpyDeviceToHost, m->st));
+    FC_CUDA(cudaStreamSynchronize(m->st));
+    if (status != 0) {
+        cudaMemsetAsync(m->tc_status, 0, sizeof(int), m->st);
+        return fail(FC_E_TIMEOUT, "a bounded wait inside a tensor-core kernel ran out (status %d)", status);
+    }
+    if (err != 0) return fail(err, "a token id was rejected on the device");
+    return FC_OK;
+}
+
+// Head + scoring tail over the R rows whose normalised state is in m->n; targets in m->targets_d.
+int score_tail(fc_llama* m, int R) {
+    const int d = m->cfg.d_model, ldl = m->head.N_pad;
+    for (int r0 = 0; r0 < R; r0 += m->head_chunk) {
+        const int rows = std::min(m->head_chunk, R - r0);
+        FC_TRY(gemm(m, m->head, m->n + (size_t)r0 * d, nullptr, nullptr, m->logits, rows, ldl));
+        FC_TRY(launch_llama_score_rows(m->logits, ldl, m->cfg.vocab, m->targets_d + r0, rows, m->lp_d + r0, m->gr_d + r0, m->st));
+    }
+    return FC_OK;
+}
+
+// plan_windows (llm_score.rs:21-32).
+struct Window { int start, first, end; };
+void plan_windows(int n, int window, int from, std::vector<Window>* out) {
+    const int half = std::max(window / 2, 1);
+    int next = std::max(from, 1);
+    while (next < n) {
+        const int start = next <= window ? 0 : next - half;
+        const int end = std::min(start + window + 1, n);
+        out->push_back({start, next, end});
+        next = end;
+    }
+}
+
+int check_window(const fc_llama* m, int window) {
+    if (window < 2 || window > m->cfg.ctx)
+        return fail(FC_E_DIM, "window must be between 2 and the model's context length %d (got %d)", m->cfg.ctx, window);
+    return FC_OK;
+}
+
+// ---------------------------------------------------------------------------- decode step
+// LlamaModel::forward_one (llm.rs:610-618) -> LlamaBlock::forward_one (llm.rs:451-461) as a
+// kernel sequence; every per-step quantity is read from device state so the captured graph is
+// replayed unchanged.
+int launch_step(fc_llama_cache* s, int with_head) {
+    fc_llama* m = s->m;
+    const fc_llama_config& c = m->cfg;
+    cudaStream_t st = m->st;
+    const int d = c.d_model, F = c.d_ff;
+    const size_t layer_stride = (size_t)c.ctx * m->kv_dim;
+    FC_TRY(launch_llama_embed_step(m->tok, c.ctx, s->queue, s->state, s->x, st));
+    for (int l = 0; l < c.n_layer; ++l) {
+        const LlamaLayerDev& L = m->layers[l];
+        float* kc = s->kc + l * layer_stride;
+        float* vc = s->vc + l * layer_stride;
+        GemvOut o;
+        FC_TRY(launch_llama_rmsnorm(s->x, L.attn_norm, c.norm_eps, 1, d, s->n, s->state, st));
+        o.out[0] = s->qkv;
+        FC_TRY(launch_gemv_q8(L.qkv, s->n, L.qkv_b, nullptr, EPI_NONE, o, s->state, st));
+        FC_TRY(launch_llama_rope_store(s->qkv, c.n_head, c.n_kv_head, c.head_dim, c.rope_dim, c.rope_type == FC_ROPE_NEOX, m->ftab,
+                                       m->inv_linear, kc, vc, s->state, st));
+        FC_TRY(launch_attn_decode_gqa(s->qkv, kc, vc, c.n_head, c.n_kv_head, c.head_dim, c.ctx, s->state, s->att, st));
+        o.out[0] = s->x;
+        FC_TRY(launch_gemv_q8(L.wo, s->att, nullptr, s->x, EPI_NONE, o, s->state, st));
+        FC_TRY(launch_llama_rmsnorm(s->x, L.ffn_norm, c.norm_eps, 1, d, s->n, s->state, st));
+        o.out[0] = s->gu;
+        FC_TRY(launch_gemv_q8(L.gateup, s->n, nullptr, nullptr, EPI_NONE, o, s->state, st));
+        FC_TRY(launch_llama_swiglu(s->gu, 1, F, s->hid, s->state, st));
+        o.out[0] = s->x;
+        FC_TRY(launch_gemv_q8(L.down, s->hid, nullptr, s->x, EPI_NONE, o, s->state, st));
+    }
+    if (with_head) {
+        GemvOut o;
+        o.out[0] = s->logits;
+        FC_TRY(launch_llama_rmsnorm(s->x, m->out_norm, c.norm_eps, 1, d, s->n, s->state, st));
+        FC_TRY(launch_gemv_q8(m->head, s->n, nullptr, nullptr, EPI_NONE, o, s->state, st));
+    }
+    return launch_step_advance(s->state, st);
+}
+
+int run_step(fc_llama_cache* s, int with_head) {
+    if (!s->graph[with_head]) {
+        cudaStream_t st = s->m->st;
+        cudaGraph_t g = nullptr;
+        const int64_t before = g_launches;
+        FC_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+        const int rc = launch_step(s, with_head);
+        const cudaError_t e = cudaStreamEndCapture(st, &g);
+        s->graph_nodes[with_head] = (int)(g_launches - before);
+        g_launches = before;
+        if (rc != FC_OK) { if (g) cudaGraphDestroy(g); return rc; }
+        FC_CUDA(e);
+        const cudaError_t ei = cudaGraphInstantiate(&s->graph[with_head], g, 0);
+        cudaGraphDestroy(g);
+        FC_CUDA(ei);
+    }
+    FC_CUDA(cudaGraphLaunch(s->graph[with_head], s->m->st));
+    g_launches += s->graph_nodes[with_head];
+    return FC_OK;
+}
+
+__global__ void llama_set_state_kernel(StepState* st, int pos, int fed, int tail) {
+    st->pos = pos; st->fed = fed; st->tail = tail; st->done = 0; st->eos = -1; st->error = 0;
+}
+
+int read_state(fc_llama_cache* s, StepState* out) {
+    FC_CUDA(cudaMemcpyAsync(out, s->state, sizeof(StepState), cudaMemcpyDeviceToHost, s->m->st));
+    FC_CUDA(cudaStreamSynchronize(s->m->st));
+    return FC_OK;
+}
+
+// Queues ids behind what the queue holds and feeds them; the last one with the head when asked.
+int feed_ids(fc_llama_cache* s, const int32_t* ids, int n, int head_on_last) {
+    fc_llama* m = s->m;
+    if (s->host_pos + n > m->cfg.ctx)
+        return fail(FC_E_DIM, "%d more tokens do not fit the model's %d-token context window (position %d)", n, m->cfg.ctx, s->host_pos);
+    FC_CUDA(cudaMemcpyAsync(s->queue + s->host_pos, ids, (size_t)n * 4, cudaMemcpyHostToDevice, m->st));
+    llama_set_state_kernel<<<1, 1, 0, m->st>>>(s->state, s->host_pos, s->host_pos, s->host_pos + n);
+    FC_LAUNCHED();
+    for (int i = 0; i < n; ++i) FC_TRY(run_step(s, head_on_last && i + 1 == n));
+    s->host_pos += n;
+    return FC_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int fc_llama_create(const fc_llama_config* cfg, const fc_llama_weights* w, int device, fc_llama** out) {
+    if (!cfg || !w || !out || !w->layers) return fail(FC_E_ARG, "fc_llama_create: null argument");
+    *out = nullptr;
+    const fc_llama_config& c = *cfg;
+    if (c.vocab <= 0 || c.d_model <= 0 || c.n_layer <= 0 || c.n_head <= 0 || c.head_dim <= 0 || c.d_ff <= 0 || c.ctx <= 0)
+        return fail(FC_E_SHAPE, "fc_llama_create: non-positive dimension");
+    // Attention::new (llm.rs:243-252)
+    if (c.n_kv_head <= 0 || c.n_head % c.n_kv_head)
+        return fail(FC_E_DIM, "n_heads %d must be a multiple of n_kv_heads %d", c.n_head, c.n_kv_head);
+    if (c.rope_dim > c.head_dim || c.rope_dim < 0 || c.rope_dim % 2)
+        return fail(FC_E_DIM, "rope_dim %d must be even and ≤ head_dim %d", c.rope_dim, c.head_dim);
+    // RopeScaling::check (llm.rs:135-150)
+    auto ok = [](float v) { return std::isfinite(v) && v > 0.0f; };
+    if (!ok(c.rope_linear_factor)) return fail(FC_E_DIM, "RoPE scaling factors must be finite and > 0");
+    if (w->rope_freqs)
+        for (int i = 0; i < c.rope_dim / 2; ++i)
+            if (!ok(w->rope_freqs[i])) return fail(FC_E_DIM, "RoPE scaling factors must be finite and > 0");
+    if (c.rope_type != FC_ROPE_NORM && c.rope_type != FC_ROPE_NEOX) return fail(FC_E_ARG, "rope_type %d", c.rope_type);
+    if (c.math_mode != FC_MATH_FP32 && c.math_mode != FC_MATH_BF16X3) return fail(FC_E_ARG, "math_mode %d", c.math_mode);
+    if (c.head_dim > 256 || c.head_dim % 4) return fail(FC_E_SHAPE, "head_dim %d must be a multiple of 4, at most 256", c.head_dim);
+    if (c.d_model % 32 || c.d_ff % 32 || (c.n_head * c.head_dim) % 32)
+        return fail(FC_E_FORMAT, "d_model, d_ff and n_head * head_dim must be multiples of 32 for Q8_0 rows");
+    FC_TRY(select_device(device));
+    fc_llama* m = new fc_llama();
+    m->cfg = c;
+    m->device = device;
+    m->q_dim = c.n_head * c.head_dim;
+    m->kv_dim = c.n_kv_head * c.head_dim;
+    m->qkv_dim = m->q_dim + 2 * m->kv_dim;
+    auto build = [&]() -> int {
+        FC_CUDA(cudaStreamCreateWithFlags(&m->st, cudaStreamNonBlocking));
+        FC_CUDA(cudaEventCreate(&m->ev0));
+        FC_CUDA(cudaEventCreate(&m->ev1));
+        cudaStream_t st = m->st;
+        const int d = c.d_model, F = c.d_ff;
+        FC_TRY(upload_q8(m->arena, w->token_embd_q8, c.vocab, d, &m->tok, st));
+        if (c.tied || !w->output_q8) m->head = m->tok;
+        else FC_TRY(upload_q8(m->arena, w->output_q8, c.vocab, d, &m->head, st));
+        FC_TRY(upload_f32(m->arena, w->output_norm, d, &m->out_norm, st));
+        // apply_rope (llm.rs:172): freq_i = (base as f64).powf(-2 i / rope_dim) as f32
+        const int half = c.rope_dim / 2;
+        std::vector<float2> ftab(std::max(half, 1));
+        for (int i = 0; i < half; ++i) {
+            ftab[i].x = (float)std::pow((double)c.rope_base, -2.0 * (double)i / (double)c.rope_dim);
+            ftab[i].y = w->rope_freqs ? w->rope_freqs[i] : 1.0f;
+        }
+        FC_TRY(m->arena.alloc_n(&m->ftab, ftab.size()));
+        FC_CUDA(cudaMemcpyAsync(m->ftab, ftab.data(), ftab.size() * sizeof(float2), cudaMemcpyHostToDevice, st));
+        FC_CUDA(cudaStreamSynchronize(st));
+        m->inv_linear = 1.0f / c.rope_linear_factor;
+        m->layers.resize(c.n_layer);
+        for (int l = 0; l < c.n_layer; ++l) {
+            const fc_llama_layer& h = w->layers[l];
+            LlamaLayerDev& L = m->layers[l];
+            FC_TRY(upload_fused(m->arena, {{h.wq_q8, m->q_dim}, {h.wk_q8, m->kv_dim}, {h.wv_q8, m->kv_dim}}, d, &L.qkv, st));
+            FC_TRY(upload_q8(m->arena, h.wo_q8, d, m->q_dim, &L.wo, st));
+            FC_TRY(upload_fused(m->arena, {{h.gate_q8, F}, {h.up_q8, F}}, d, &L.gateup, st));
+            FC_TRY(upload_q8(m->arena, h.down_q8, d, F, &L.down, st));
+            FC_TRY(upload_f32(m->arena, h.attn_norm, d, &L.attn_norm, st));
+            FC_TRY(upload_f32(m->arena, h.ffn_norm, d, &L.ffn_norm, st));
+            if (h.bq || h.bk || h.bv) {
+                std::vector<float> b((size_t)m->qkv_dim, 0.0f);
+                if (h.bq) std::memcpy(b.data(), h.bq, (size_t)m->q_dim * 4);
+                if (h.bk) std::memcpy(b.data() + m->q_dim, h.bk, (size_t)m->kv_dim * 4);
+                if (h.bv) std::memcpy(b.data() + m->q_dim + m->kv_dim, h.bv, (size_t)m->kv_dim * 4);
+                FC_TRY(upload_f32(m->arena, b.data(), b.size(), &L.qkv_b, st));
+                FC_CUDA(cudaStreamSynchronize(st));
+            }
+        }
+        FC_CUDA(cudaStreamSynchronize(st));
+        return FC_OK;
+    };
+    const int rc = build();
+    if (rc != FC_OK) { fc_llama_free(m); return rc; }
+    *out = m;
+    return FC_OK;
+}
+
+void fc_llama_free(fc_llama* m) {
+    if (!m) return;
+    cudaSetDevice(m->device);
+    if (m->st) cudaStreamSynchronize(m->st);
+    m->ws_arena.release();
+    m->arena.release();
+    if (m->ev0) cudaEventDestroy(m->ev0);
+    if (m->ev1) cudaEventDestroy(m->ev1);
+    if (m->st) cudaStreamDestroy(m->st);
+    delete m;
+}
+
+int fc_llama_forward_tokens(fc_llama* m, const int32_t* ids, int n, float* logits) {
+    if (!m || !ids || !logits) return fail(FC_E_ARG, "fc_llama_forward_tokens: null argument");
+    if (n <= 0) return fail(FC_E_SHAPE, "fc_llama_forward_tokens: n = %d", n);
+    FC_CUDA(cudaSetDevice(m->device));
+    FC_TRY(check_ids(m, ids, (size_t)n));
+    FC_TRY(ensure_workspace(m, n));
+    const int d = m->cfg.d_model, V = m->cfg.vocab, ldl = m->head.N_pad;
+    FC_CUDA(cudaMemcpyAsync(m->ids_d, ids, (size_t)n * 4, cudaMemcpyHostToDevice, m->st));
+    FC_TRY(forward_rows(m, 1, n));
+    for (int r0 = 0; r0 < n; r0 += m->head_chunk) {
+        const int rows = std::min(m->head_chunk, n - r0);
+        FC_TRY(gemm(m, m->head, m->n + (size_t)r0 * d, nullptr, nullptr, m->logits, rows, ldl));
+        FC_CUDA(cudaMemcpy2DAsync(logits + (size_t)r0 * V, (size_t)V * 4, m->logits, (size_t)ldl * 4, (size_t)V * 4, rows,
+                                  cudaMemcpyDeviceToHost, m->st));
+    }
+    return check_status(m);
+}
+
+int fc_llama_score_from(fc_llama* m, const int32_t* ids, int n, int from, int window, fc_score* score, float* lp,
+                        uint8_t* is_greedy) {
+    if (!m || !ids || !score) return fail(FC_E_ARG, "fc_llama_score_from: null argument");
+    if (n < 0 || from < 0) return fail(FC_E_SHAPE, "fc_llama_score_from: n = %d, from = %d", n, from);
+    FC_CUDA(cudaSetDevice(m->device));
+    FC_TRY(check_window(m, window));
+    FC_TRY(check_ids(m, ids, (size_t)n));
+    score->logprob = 0.0; score->n_tokens = 0; score->greedy = 1;
+    if (lp) std::fill(lp, lp + std::max(n - 1, 0), 0.0f);
+    if (is_greedy) std::fill(is_greedy, is_greedy + std::max(n - 1, 0), (uint8_t)0);
+    std::vector<Window> plan;
+    plan_windows(n, window, from, &plan);
+    if (plan.empty()) return FC_OK;
+    FC_TRY(ensure_workspace(m, std::min(window, n)));
+    m->last_score_ms = 0.0f;
+    std::vector<int32_t> targets;
+    std::vector<double> lps;
+    std::vector<uint8_t> grs;
+    for (const Window& wd : plan) {
+        // the window feeds ids[start .. min(start + window, n)); row r predicts id start + r + 1
+        const int rows = std::min(wd.start + window, n) - wd.start;
+        targets.assign(rows, -1);
+        for (int t = wd.first; t < wd.end; ++t) targets[t - 1 - wd.start] = ids[t];
+        FC_CUDA(cudaMemcpyAsync(m->ids_d, ids + wd.start, (size_t)rows * 4, cudaMemcpyHostToDevice, m->st));
+        FC_CUDA(cudaMemcpyAsync(m->targets_d, targets.data(), (size_t)rows * 4, cudaMemcpyHostToDevice, m->st));
+        FC_CUDA(cudaEventRecord(m->ev0, m->st));
+        FC_TRY(forward_rows(m, 1, rows));
+        FC_TRY(score_tail(m, rows));
+        FC_CUDA(cudaEventRecord(m->ev1, m->st));
+        lps.resize(rows); grs.resize(rows);
+        FC_CUDA(cudaMemcpyAsync(lps.data(), m->lp_d, (size_t)rows * 8, cudaMemcpyDeviceToHost, m->st));
+        FC_CUDA(cudaMemcpyAsync(grs.data(), m->gr_d, (size_t)rows, cudaMemcpyDeviceToHost, m->st));
+        FC_TRY(check_status(m));
+        float ms = 0.0f;
+        FC_CUDA(cudaEventElapsedTime(&ms, m->ev0, m->ev1));
+        m->last_score_ms += ms;
+        for (int t = wd.first; t < wd.end; ++t) {           // ascending targets, f64 sum (llm_score.rs:88-93)
+            const int r = t - 1 - wd.start;
+            score->logprob += lps[r];
+            score->n_tokens += 1;
+            if (!grs[r]) score->greedy = 0;
+            if (lp) lp[t - 1] = (float)lps[r];
+            if (is_greedy) is_greedy[t - 1] = grs[r];
+        }
+    }
+    return FC_OK;
+}
+
+int fc_llama_score_sequences(fc_llama* m, const int32_t* ids, int n_seq, int seq_len, int batch_windows, fc_score* scores,
+                             float* lp) {
+    if (!m || !ids || !scores) return fail(FC_E_ARG, "fc_llama_score_sequences: null argument");
+    if (n_seq < 0 || seq_len < 2) return fail(FC_E_SHAPE, "fc_llama_score_sequences: n_seq = %d, seq_len = %d", n_seq, seq_len);
+    if (seq_len > m->cfg.ctx) return fail(FC_E_DIM, "sequences of %d ids do not fit one window of %d", seq_len, m->cfg.ctx);
+    FC_CUDA(cudaSetDevice(m->device));
+    FC_TRY(check_ids(m, ids, (size_t)n_seq * seq_len));
+    const int T = seq_len, Bmax = std::max(1, std::min(batch_windows > 0 ? batch_windows : 8, std::max(n_seq, 1)));
+    FC_TRY(ensure_workspace(m, Bmax * T));
+    m->last_score_ms = 0.0f;
+    std::vector<int32_t> targets((size_t)Bmax * T);
+    std::vector<double> lps((size_t)Bmax * T);
+    std::vector<uint8_t> grs((size_t)Bmax * T);
+    for (int s0 = 0; s0 < n_seq; s0 += Bmax) {
+        const int B = std::min(Bmax, n_seq - s0), R = B * T;
+        for (int b = 0; b < B; ++b) {
+            const int32_t* seq = ids + (size_t)(s0 + b) * T;
+            for (int t = 0; t < T; ++t) targets[(size_t)b * T + t] = t + 1 < T ? seq[t + 1] : -1;
+        }
+        FC_CUDA(cudaMemcpyAsync(m->ids_d, ids + (size_t)s0 * T, (size_t)R * 4, cudaMemcpyHostToDevice, m->st));
+        FC_CUDA(cudaMemcpyAsync(m->targets_d, targets.data(), (size_t)R * 4, cudaMemcpyHostToDevice, m->st));
+        FC_CUDA(cudaEventRecord(m->ev0, m->st));
+        FC_TRY(forward_rows(m, B, T));
+        FC_TRY(score_tail(m, R));
+        FC_CUDA(cudaEventRecord(m->ev1, m->st));
+        FC_CUDA(cudaMemcpyAsync(lps.data(), m->lp_d, (size_t)R * 8, cudaMemcpyDeviceToHost, m->st));
+        FC_CUDA(cudaMemcpyAsync(grs.data(), m->gr_d, (size_t)R, cudaMemcpyDeviceToHost, m->st));
+        FC_TRY(check_status(m));
+        float ms = 0.0f;
+        FC_CUDA(cudaEventElapsedTime(&ms, m->ev0, m->ev1));
+        m->last_score_ms += ms;
+        for (int b = 0; b < B; ++b) {
+            fc_score& sc = scores[s0 + b];
+            sc.logprob = 0.0; sc.n_tokens = 0; sc.greedy = 1;
+            for (int t = 0; t + 1 < T; ++t) {
+                const size_t r = (size_t)b * T + t;
+                sc.logprob += lps[r];
+                sc.n_tokens += 1;
+                if (!grs[r]) sc.greedy = 0;
+                if (lp) lp[(size_t)(s0 + b) * (T - 1) + t] = (float)lps[r];
+            }
+        }
+    }
+    return FC_OK;
+}
+
+float fc_llama_last_score_ms(const fc_llama* m) { return m ? m->last_score_ms : 0.0f; }
+
+int fc_llama_cache_create(fc_llama* m, fc_llama_cache** out) {
+    if (!m || !out) return fail(FC_E_ARG, "fc_llama_cache_create: null argument");
+    *out = nullptr;
+    FC_CUDA(cudaSetDevice(m->device));
+    const fc_llama_config& c = m->cfg;
+    fc_llama_cache* s = new fc_llama_cache();
+    s->m = m;
+    s->device = m->device;
+    auto build = [&]() -> int {
+        const size_t kv = (size_t)c.n_layer * c.ctx * m->kv_dim;
+        Arena& a = s->arena;
+        FC_TRY(a.alloc_n(&s->kc, kv));
+        FC_TRY(a.alloc_n(&s->vc, kv));
+        FC_TRY(a.alloc_n(&s->x, (size_t)c.d_model));
+        FC_TRY(a.alloc_n(&s->n, (size_t)c.d_model));
+        FC_TRY(a.alloc_n(&s->qkv, (size_t)m->qkv_dim));
+        FC_TRY(a.alloc_n(&s->att, (size_t)m->q_dim));
+        FC_TRY(a.alloc_n(&s->gu, (size_t)2 * c.d_ff));
+        FC_TRY(a.alloc_n(&s->hid, (size_t)c.d_ff));
+        FC_TRY(a.alloc_n(&s->logits, (size_t)m->head.N_pad));
+        s->queue_cap = c.ctx + 1;
+        FC_TRY(a.alloc_n(&s->queue, (size_t)s->queue_cap));
+        FC_TRY(a.alloc_n(&s->state, 1));
+        FC_TRY(a.alloc_n(&s->rng_d, 1));
+        FC_CUDA(cudaEventCreate(&s->ev0));
+        FC_CUDA(cudaEventCreate(&s->ev1));
+        return fc_llama_cache_clear(s);
+    };
+    const int rc = build();
+    if (rc != FC_OK) { fc_llama_cache_free(s); return rc; }
+    *out = s;
+    return FC_OK;
+}
+
+void fc_llama_cache_free(fc_llama_cache* s) {
+    if (!s) return;
+    cudaSetDevice(s->device);
+    cudaDeviceSynchronize();              // the model (and its stream) may already be gone
+    for (auto& g : s->graph) if (g) cudaGraphExecDestroy(g);
+    if (s->ev0) cudaEventDestroy(s->ev0);
+    if (s->ev1) cudaEventDestroy(s->ev1);
+    s->arena.release();
+    delete s;
+}
+
+int fc_llama_cache_clear(fc_llama_cache* s) {
+    if (!s) return fail(FC_E_ARG, "fc_llama_cache_clear: null cache");
+    FC_CUDA(cudaSetDevice(s->m->device));
+    llama_set_state_kernel<<<1, 1, 0, s->m->st>>>(s->state, 0, 0, 0);
+    FC_LAUNCHED();
+    s->host_pos = 0;
+    return FC_OK;
+}
+
+int fc_llama_cache_pos(const fc_llama_cache* s) { return s ? s->host_pos : 0; }
+
+int fc_llama_forward_one(fc_llama_cache* s, int32_t token, float* logits) {
+    if (!s) return fail(FC_E_ARG, "fc_llama_forward_one: null cache");
+    fc_llama* m = s->m;
+    FC_CUDA(cudaSetDevice(m->device));
+    FC_TRY(check_ids(m, &token, 1));
+    FC_TRY(feed_ids(s, &token, 1, logits != nullptr));
+    if (logits) FC_CUDA(cudaMemcpyAsync(logits, s->logits, (size_t)m->cfg.vocab * 4, cudaMemcpyDeviceToHost, m->st));
+    StepState hs;
+    FC_TRY(read_state(s, &hs));
+    if (hs.error) { s->host_pos -= 1; return fail(hs.error, "the decode step rejected a token or position on the device"); }
+    return FC_OK;
+}
+
+int fc_llama_generate(fc_llama_cache* s, const int32_t* prompt, int n, int max_new, const fc_sampling* params,
+                      const int32_t* stops, int n_stops, uint64_t* rng_state, const volatile int32_t* cancel,
+                      int32_t* out, int* n_out) {
+    if (!s || !prompt || !params || !rng_state || !n_out || (max_new > 0 && !out) || (n_stops > 0 && !stops))
+        return fail(FC_E_ARG, "fc_llama_generate: null argument");
+    *n_out = 0;
+    if (n <= 0) return fail(FC_E_DIM, "prompt must be non-empty");
+    if (max_new < 0 || n_stops < 0) return fail(FC_E_SHAPE, "fc_llama_generate: max_new = %d, n_stops = %d", max_new, n_stops);
+    fc_llama* m = s->m;
+    const fc_llama_config& c = m->cfg;
+    FC_CUDA(cudaSetDevice(m->device));
+    FC_TRY(check_ids(m, prompt, (size_t)n));
+    // llm.rs:723-730: the context window bounds the prompt and the generation
+    if (n >= c.ctx) return fail(FC_E_DIM, "prompt of %d tokens does not fit the model's %d-token context window", n, c.ctx);
+    max_new = std::min(max_new, c.ctx - n);
+    cudaStream_t st = m->st;
+    if (cancel && *cancel) return FC_OK;                     // cancelled while reading the prompt: nothing (llm.rs:734-736)
+    FC_TRY(fc_llama_cache_clear(s));
+    FC_CUDA(cudaMemcpyAsync(s->rng_d, rng_state, 8, cudaMemcpyHostToDevice, st));
+    FC_TRY(feed_ids(s, prompt, n, 1));
+    // greedy without a penalty needs neither the sampler's sort nor, without stop ids, the host
+    const bool plain_greedy = params->temperature <= 0.0f && params->repetition_penalty == 1.0f;
+    const bool free_run = plain_greedy && n_stops == 0 && !cancel;
+    FC_CUDA(cudaEventRecord(s->ev0, st));
+    int made = 0;
+    int rc = FC_OK;
+    bool cancelled = false;
+    while (made < max_new) {
+        if (cancel && *cancel) { cancelled = true; break; }
+        // recent = prompt + tokens so far = the queue (llm.rs:740-751)
+        rc = plain_greedy ? launch_llama_pick(s->logits, c.vocab, s->queue, s->queue_cap, s->state, st)
+                          : launch_sample(s->logits, c.vocab, 0, *params, s->queue, 0, s->rng_d, s->queue, s->queue_cap, s->state,
+                                          nullptr, st);
+        if (rc != FC_OK) break;
+        ++made;
+        bool stop = false;
+        if (!free_run) {
+            int32_t tok = 0;
+            if (cudaMemcpyAsync(&tok, s->queue + n + made - 1, 4, cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+                cudaStreamSynchronize(st) != cudaSuccess) { rc = fail(FC_E_CUDA, "token download failed"); break; }
+            out[made - 1] = tok;
+            for (int i = 0; i < n_stops; ++i) stop |= stops[i] == tok;
+        }
+        if (stop) break;                                     // a stop id is kept in out and not fed (llm.rs:747-749)
+        rc = run_step(s, 1);                                 // forward_one(next), the last token included (llm.rs:750-751)
+        if (rc != FC_OK) break;
+        s->host_pos += 1;
+    }
+    if (rc == FC_OK) {
+        FC_CUDA(cudaEventRecord(s->ev1, st));
+        if (free_run && made > 0) FC_CUDA(cudaMemcpyAsync(out, s->queue + n, (size_t)made * 4, cudaMemcpyDeviceToHost, st));
+        StepState hs;
+        rc = read_state(s, &hs);
+        if (rc == FC_OK && hs.error) rc = fail(hs.error, "the decode step rejected a token or position on the device");
+        if (rc == FC_OK) FC_CUDA(cudaEventElapsedTime(&s->last_decode_ms, s->ev0, s->ev1));
+    }
+    FC_CUDA(cudaMemcpy(rng_state, s->rng_d, 8, cudaMemcpyDeviceToHost));
+    if (rc != FC_OK) return rc;
+    *n_out = made;
+    if (cancelled) return fail(FC_E_CANCELLED, "generation cancelled after %d tokens", made);
+    return FC_OK;
+}
+
+float fc_llama_last_decode_ms(const fc_llama_cache* s) { return s ? s->last_decode_ms : 0.0f; }
+
+}  // extern "C"

@@ -1,0 +1,273 @@
+// Row kernels of the imported Llama / Qwen decoder (ferrum_core/src/llm.rs): token lookup,
+// RMSNorm, rotary positions, the SwiGLU gate, the exact log-softmax scoring tail of
+// llm_score.rs and the greedy pick. All are HBM-bound elementwise / row-reduction work: one
+// block per row, coalesced accesses, fixed-order block reductions.
+#include "llama_ops.cuh"
+
+namespace fc {
+
+namespace {
+
+__device__ __forceinline__ float warp_sum_f(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ double warp_sum_d(double v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+// Fixed-order block reductions; `red` holds 33 values.
+template <class T>
+__device__ T block_sum_t(T v, T* red) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    if constexpr (sizeof(T) == 8) v = warp_sum_d(v); else v = warp_sum_f(v);
+    __syncthreads();
+    if (lane == 0) red[wid] = v;
+    __syncthreads();
+    if (wid == 0) {
+        T t = lane < nw ? red[lane] : (T)0;
+        if constexpr (sizeof(T) == 8) t = warp_sum_d(t); else t = warp_sum_f(t);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+}
+
+// Value c of row `id` of a Q8_0 table: d * q, the single rounding of gguf::dequant_q8_0
+// (gguf/dequant.rs:37-49).
+__device__ __forceinline__ float table_value(const QMat& tok, int id, int c) {
+    const float dq = __half2float(tok.d[(size_t)id * (tok.K >> 5) + (c >> 5)]);
+    const int q = (int)tok.qu[(size_t)id * tok.K + c] - 128;
+    return dq * (float)q;
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------ embedding
+// LlamaModel::embed (llm.rs:588-597): the token's row, no position term. A bad id is an error
+// flag, never a trap.
+__global__ void llama_embed_rows_kernel(QMat tok, const int* __restrict__ ids, float* __restrict__ x, int* error_flag) {
+    const int r = blockIdx.x;
+    int id = ids[r];
+    if (id < 0 || id >= tok.N) {
+        if (threadIdx.x == 0) atomicExch(error_flag, FC_E_DIM);
+        id = 0;
+    }
+    for (int c = threadIdx.x; c < tok.K; c += blockDim.x) x[(size_t)r * tok.K + c] = table_value(tok, id, c);
+}
+int launch_llama_embed_rows(const QMat& tok, const int* ids, int R, float* x, int* error_flag, cudaStream_t st) {
+    llama_embed_rows_kernel<<<R, 256, 0, st>>>(tok, ids, x, error_flag);
+    FC_LAUNCHED();
+    return FC_OK;
+}
+
+// forward_one (llm.rs:610-618): the queued token at the cache position. A full context is
+// refused like a bad id (generation stops at the window, llm.rs:720-730).
+__global__ void llama_embed_step_kernel(QMat tok, int ctx, const int* __restrict__ queue, StepState* st, float* __restrict__ x) {
+    if (st->done | st->error) return;
+    const int pos = st->pos, id = queue[st->fed];
+    if (id < 0 || id >= tok.N || pos >= ctx) {
+        __syncthreads();
+        if (threadIdx.x == 0) st->error = FC_E_DIM;
+        return;
+    }
+    for (int c = threadIdx.x; c < tok.K; c += blockDim.x) x[c] = table_value(tok, id, c);
+}
+int launch_llama_embed_step(const QMat& tok, int ctx, const int* queue, StepState* state, float* x, cudaStream_t st) {
+    llama_embed_step_kernel<<<1, 256, 0, st>>>(tok, ctx, queue, state, x);
+    FC_LAUNCHED();
+    return FC_OK;
+}
+
+// -------------------------------------------------------------------------------- RMSNorm
+// RmsNorm::forward_row (llm.rs:57-64): ms = sum(x^2) / d, inv = 1 / sqrt(ms + eps),
+// y = (x * inv) * w. The sum is a block tree, not the reference's ascending order.
+__global__ void __launch_bounds__(256) llama_rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps,
+                                                            int d, float* __restrict__ y, const StepState* st) {
+    __shared__ float red[33];
+    if (st && (st->done | st->error)) return;
+    const float* xr = x + (size_t)blockIdx.x * d;
+    float s = 0.0f;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) { const float v = xr[c]; s = fmaf(v, v, s); }
+    const float ms = block_sum_t(s, red) / (float)d;
+    const float inv = 1.0f / sqrtf(ms + eps);
+    for (int c = threadIdx.x; c < d; c += blockDim.x) y[(size_t)blockIdx.x * d + c] = __fmul_rn(__fmul_rn(xr[c], inv), w[c]);
+}
+int launch_llama_rmsnorm(const float* x, const float* w, float eps, int rows, int d, float* y, const StepState* state,
+                         cudaStream_t st) {
+    llama_rmsnorm_kernel<<<rows, 256, 0, st>>>(x, w, eps, d, y, state);
+    FC_LAUNCHED();
+    return FC_OK;
+}
+
+// ----------------------------------------------------------------------------------- RoPE
+// apply_rope (llm.rs:158-185) with RopeScaling::angle (llm.rs:129-132): pair i of a head turns
+// by theta = ((pos * freq_i) / ff_i) * (1 / linear_factor), freq_i = (f32) base^(-2i/rope_dim)
+// computed in f64 on the host. Multiplies and adds are rounded separately, as the reference's.
+__device__ __forceinline__ void rotate_pair(float* x, int ia, int ib, float theta) {
+    float s, c;
+    sincosf(theta, &s, &c);
+    const float a = x[ia], b = x[ib];
+    x[ia] = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s));
+    x[ib] = __fadd_rn(__fmul_rn(a, s), __fmul_rn(b, c));
+}
+__device__ __forceinline__ float rope_angle(int pos, float2 f, float inv_linear) {
+    return __fmul_rn(__fdiv_rn(__fmul_rn((float)pos, f.x), f.y), inv_linear);
+}
+
+// Window form: row r of the fused [R][ld] buffer sits at position r % T; its first n_q heads
+// (queries) and the n_kv heads that follow them at `k_off` are rotated in place.
+__global__ void llama_rope_rows_kernel(float* __restrict__ qkv, int ld, int T, int n_q, int n_kv, int k_off, int hd, int half,
+                                       int neox, const float2* __restrict__ ftab, float inv_linear) {
+    const int r = blockIdx.x, pos = r % T;
+    float* row = qkv + (size_t)r * ld;
+    const int pairs = (n_q + n_kv) * half;
+    for (int u = threadIdx.x; u < pairs; u += blockDim.x) {
+        const int h = u / half, i = u - h * half;
+        const int off = h < n_q ? h * hd : k_off + (h - n_q) * hd;
+        const int ia = neox ? off + i : off + 2 * i, ib = neox ? off + i + half : off + 2 * i + 1;
+        rotate_pair(row, ia, ib, rope_angle(pos, ftab[i], inv_linear));
+    }
+}
+int launch_llama_rope_rows(float* qkv, int R, int ld, int T, int n_q, int n_kv, int k_off, int hd, int rope_dim, int neox,
+                           const float2* ftab, float inv_linear, cudaStream_t st) {
+    llama_rope_rows_kernel<<<R, 256, 0, st>>>(qkv, ld, T, n_q, n_kv, k_off, hd, rope_dim / 2, neox, ftab, inv_linear);
+    FC_LAUNCHED();
+    return FC_OK;
+}
+
+// Decode form (Attention::project + the cache append of forward_one, llm.rs:276-301,345-351):
+// rotates q in place and appends the rotated k row and the v row at the cache position.
+__global__ void llama_rope_store_kernel(float* __restrict__ qkv, int n_q, int n_kv, int hd, int half, int neox,
+                                        const float2* __restrict__ ftab, float inv_linear, float* __restrict__ kc,
+                                        float* __restrict__ vc, const StepState* st) {
+    if (st->done | st->error) return;
+    const int pos = st->pos, q_dim = n_q * hd, kv_dim = n_kv * hd;
+    const int pairs = (n_q + n_kv) * half;
+    for (int u = threadIdx.x; u < pairs; u += blockDim.x) {
+        const int h = u / half, i = u - h * half;
+        const int off = h * hd;    // k heads follow the q heads directly in the fused row
+        const int ia = neox ? off + i : off + 2 * i, ib = neox ? off + i + half : off + 2 * i + 1;
+        rotate_pair(qkv, ia, ib, rope_angle(pos, ftab[i], inv_linear));
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < kv_dim; c += blockDim.x) {
+        kc[(size_t)pos * kv_dim + c] = qkv[q_dim + c];
+        vc[(size_t)pos * kv_dim + c] = qkv[q_dim + kv_dim + c];
+    }
+}
+int launch_llama_rope_store(float* qkv, int n_q, int n_kv, int hd, int rope_dim, int neox, const float2* ftab, float inv_linear,
+                            float* kc, float* vc, const StepState* state, cudaStream_t st) {
+    llama_rope_store_kernel<<<1, 512, 0, st>>>(qkv, n_q, n_kv, hd, rope_dim / 2, neox, ftab, inv_linear, kc, vc, state);
+    FC_LAUNCHED();
+    return FC_OK;
+}
+
+// --------------------------------------------------------------------------------- SwiGLU
+// FeedForward::forward (llm.rs:417-428): h = (g / (1 + exp(-g))) * u on rows [gate | up].
+__global__ void llama_swiglu_kernel(const float* __restrict__ gu, int F, float* __restrict__ h, const StepState* st) {
+    if (st && (st->done | st->error)) return;
+    const float* row = gu + (size_t)blockIdx.y * 2 * F;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c < F) {
+        const float g = row[c], u = row[F + c];
+        h[(size_t)blockIdx.y * F + c] = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), u);
+    }
+}
+int launch_llama_swiglu(const float* gu, int rows, int F, float* h, const StepState* state, cudaStream_t st) {
+    dim3 grid((F + 255) / 256, rows);
+    llama_swiglu_kernel<<<grid, 256, 0, st>>>(gu, F, h, state);
+    FC_LAUNCHED();
+    return FC_OK;
+}
+
+// --------------------------------------------------------------------------- scoring tail
+// log_prob (llm_score.rs:35-39): ln softmax(row)[target] in f64 with no probability floor —
+// max in f32, sum of exp((f64)x - max) in f64, x[target] - max - ln(sum); and
+// argmax_first(row) == target (llm_score.rs:92). The f64 sum is a block tree.
+__global__ void __launch_bounds__(512) llama_score_rows_kernel(const float* __restrict__ logits, int ldl, int V,
+                                                               const int* __restrict__ targets, double* __restrict__ logprob,
+                                                               uint8_t* __restrict__ is_greedy) {
+    __shared__ double dred[33];
+    __shared__ float fred[32];
+    __shared__ int ired[32];
+    const int r = blockIdx.x, target = targets[r];
+    if (target < 0 || target >= V) {
+        if (threadIdx.x == 0) { logprob[r] = 0.0; is_greedy[r] = 0; }
+        return;
+    }
+    const float* row = logits + (size_t)r * ldl;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    float mx = -INFINITY;
+    int first = 0x7fffffff;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        const float v = row[i];
+        if (v > mx) { mx = v; first = i; }       // ascending i per thread: the first of a tie stays
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float om = __shfl_xor_sync(0xffffffffu, mx, o);
+        const int of = __shfl_xor_sync(0xffffffffu, first, o);
+        if (om > mx || (om == mx && of < first)) { mx = om; first = of; }
+    }
+    if (lane == 0) { fred[wid] = mx; ired[wid] = first; }
+    __syncthreads();
+    mx = fred[0]; first = ired[0];
+    for (int w = 1; w < nw; ++w)
+        if (fred[w] > mx || (fred[w] == mx && ired[w] < first)) { mx = fred[w]; first = ired[w]; }
+    const double dmax = (double)mx;
+    double s = 0.0;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) s += exp((double)row[i] - dmax);
+    const double sum = block_sum_t(s, dred);
+    if (threadIdx.x == 0) {
+        logprob[r] = (double)row[target] - dmax - log(sum);
+        is_greedy[r] = (uint8_t)(first == target);
+    }
+}
+int launch_llama_score_rows(const float* logits, int ldl, int V, const int* targets, int R, double* logprob, uint8_t* is_greedy,
+                            cudaStream_t st) {
+    llama_score_rows_kernel<<<R, 512, 0, st>>>(logits, ldl, V, targets, logprob, is_greedy);
+    FC_LAUNCHED();
+    return FC_OK;
+}
+
+// ---------------------------------------------------------------------------- greedy pick
+// sample_with_params at temperature <= 0 with no repetition penalty is argmax_first of the raw
+// logits (slm/sampling.rs:96-104,147): the id is appended to the queue for the next step.
+__global__ void __launch_bounds__(1024) llama_pick_kernel(const float* __restrict__ logits, int V, int* __restrict__ queue,
+                                                          int queue_cap, StepState* st) {
+    __shared__ float fred[32];
+    __shared__ int ired[32];
+    if (st->done | st->error) return;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    float mx = -INFINITY;
+    int first = 0x7fffffff;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        const float v = logits[i];
+        if (v > mx) { mx = v; first = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float om = __shfl_xor_sync(0xffffffffu, mx, o);
+        const int of = __shfl_xor_sync(0xffffffffu, first, o);
+        if (om > mx || (om == mx && of < first)) { mx = om; first = of; }
+    }
+    if (lane == 0) { fred[wid] = mx; ired[wid] = first; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < nw; ++w)
+            if (fred[w] > mx || (fred[w] == mx && ired[w] < first)) { mx = fred[w]; first = ired[w]; }
+        if (first == 0x7fffffff) first = 0;      // all -inf / NaN: argmax_first answers 0
+        if (st->tail < queue_cap) { queue[st->tail] = first; st->tail += 1; }
+        else st->error = FC_E_DIM;
+    }
+}
+int launch_llama_pick(const float* logits, int V, int* queue, int queue_cap, StepState* state, cudaStream_t st) {
+    llama_pick_kernel<<<1, 1024, 0, st>>>(logits, V, queue, queue_cap, state);
+    FC_LAUNCHED();
+    return FC_OK;
+}
+
+}  // namespace fc

@@ -108,6 +108,78 @@ class SynthModel:
         return (n_layer * (4 * d * d + 2 * d * F) + d * V) * 34 // 32
 
 
+# name -> (vocab, d_model, n_layer, n_head, n_kv_head, head_dim, d_ff, ctx)
+LLAMA_SHAPES = {
+    "llama-tiny": (512, 64, 2, 4, 2, 16, 128, 64),
+    "llama-mini": (4096, 256, 4, 8, 2, 32, 704, 256),
+    # the shape of a 1B-class GGUF (Llama-3.2-1B: 16 layers, 32 query / 8 key-value heads of 64)
+    "llama-1b": (32000, 2048, 16, 32, 8, 64, 8192, 2048),
+}
+
+
+class SynthLlama:
+    """Host tensors of a Llama / Qwen-shaped model (llm.rs:549-565) with the fc_llama_* structs.
+    Matrices N(0, 0.02^2) -> Q8_0; norm weights 1 (+ noise when `perturb`); optional q/k/v biases."""
+
+    def __init__(self, vocab, d_model, n_layer, n_head, n_kv_head, head_dim, d_ff, ctx, seed=0, perturb=False, math_mode=0,
+                 rope_dim=None, rope_base=10000.0, rope_type=0, rope_linear_factor=1.0, freq_factors=None, norm_eps=1e-6,
+                 tied=True, qkv_bias=False):
+        rng = Rng(seed)
+        d, F, V = d_model, d_ff, vocab
+        qd, kvd = n_head * head_dim, n_kv_head * head_dim
+        rope_dim = head_dim if rope_dim is None else rope_dim
+        self.dims = dict(vocab=V, d_model=d, n_layer=n_layer, n_head=n_head, n_kv_head=n_kv_head, head_dim=head_dim, d_ff=F, ctx=ctx)
+        self.keep = []
+
+        def mat(n, k):
+            q = q8_0_quantize(rng.normal(n * k, 0.02))
+            self.keep.append(q)
+            return q
+
+        def vec(n, base, scale, always=False):
+            v = np.full(n, base, dtype=np.float32)
+            if perturb or always:
+                v = v + rng.normal(n, scale)
+            v = np.ascontiguousarray(v, dtype=np.float32)
+            self.keep.append(v)
+            return v
+
+        self.token_embd = mat(V, d)
+        self.layers = []
+        for _ in range(n_layer):
+            L = dict(attn_norm=vec(d, 1.0, 0.1), wq_q8=mat(qd, d), wk_q8=mat(kvd, d), wv_q8=mat(kvd, d), wo_q8=mat(d, qd),
+                     ffn_norm=vec(d, 1.0, 0.1), gate_q8=mat(F, d), up_q8=mat(F, d), down_q8=mat(d, F))
+            if qkv_bias:
+                L.update(bq=vec(qd, 0.0, 0.02, True), bk=vec(kvd, 0.0, 0.02, True), bv=vec(kvd, 0.0, 0.02, True))
+            self.layers.append(L)
+        self.output_norm = vec(d, 1.0, 0.1)
+        self.output = None if tied else mat(V, d)
+        self.freq_factors = None if freq_factors is None else np.ascontiguousarray(freq_factors, dtype=np.float32)
+
+        self.config = _lib.FcLlamaConfig(V, d, n_layer, n_head, n_kv_head, head_dim, F, rope_dim, rope_base, rope_type,
+                                         rope_linear_factor, norm_eps, ctx, 1 if tied else 0, math_mode)
+        self._layer_structs = (_lib.FcLlamaLayer * n_layer)()
+        for i, L in enumerate(self.layers):
+            for k, v in L.items():
+                setattr(self._layer_structs[i], k, v.ctypes.data)
+        self.weights = _lib.FcLlamaWeights(
+            self.token_embd.ctypes.data, C.cast(self._layer_structs, C.POINTER(_lib.FcLlamaLayer)),
+            self.output_norm.ctypes.data, None if tied else self.output.ctypes.data,
+            None if self.freq_factors is None else self.freq_factors.ctypes.data)
+
+    @property
+    def q8_weight_bytes(self):
+        """Bytes of Q8_0 matrices one decoded token streams (each matrix once, the head included)."""
+        c = self.dims
+        qd, kvd, d, F = c["n_head"] * c["head_dim"], c["n_kv_head"] * c["head_dim"], c["d_model"], c["d_ff"]
+        per_layer = (qd + 2 * kvd) * d + d * qd + 3 * d * F
+        return (c["n_layer"] * per_layer + d * c["vocab"]) * 34 // 32
+
+
+def llama_named(name, **kw):
+    return SynthLlama(*LLAMA_SHAPES[name], **kw)
+
+
 def named(name, **kw):
     return SynthModel(*SHAPES[name], **kw)
 

@@ -241,11 +241,90 @@ int fc_generate_sampled(fc_stream* s, const int32_t* prompt, int n, int max_new,
                         uint64_t* rng_state, const volatile int32_t* cancel, int32_t* out, int* n_out);
 /* n_streams independent greedy generations on one GPU: prompts [n_streams][prompt_len], out
  * [n_streams][max_new], n_out [n_streams]. Each is token_stream.rs:66-189 with temperature <= 0
- * on its own KV caches; the streams of a GPU currently run one after the other (weights are
- * streamed once per stream and token). Device time of the feeds: fc_last_batch_ms. */
+ * on its own KV caches. Up to eight streams decode side by side, each on its own CUDA stream
+ * with a persistent kernel on a share of the SMs; their prompts are primed as one batched
+ * forward. Device time of the feeds: fc_last_batch_ms. */
 int fc_decode_batch(fc_model* m, int n_streams, const int32_t* prompts, int prompt_len, int max_new, int32_t eos,
                     int32_t* out, int* n_out);
 float fc_last_batch_ms(const fc_model* m);
+
+/* ---- imported Llama / Qwen models (ferrum_core/src/llm.rs, llm_score.rs) ---------- */
+/* The decoder family of llm.rs on the same Q8_0 kernels: RMSNorm (llm.rs:57-64), rotary
+ * positions in both pairings with the GGUF's frequency scaling (llm.rs:126-185), grouped-query
+ * attention over f32 KV caches (llm.rs:305-341), the SwiGLU feed-forward (llm.rs:417-428) and
+ * the exact log-softmax scorer (llm_score.rs:21-96). */
+#define FC_ROPE_NORM 0 /* rotate interleaved pairs (2i, 2i+1) — RopeType::Norm, llm.rs:97-98 */
+#define FC_ROPE_NEOX 1 /* rotate split halves (i, i + rope_dim/2) — RopeType::Neox, llm.rs:99-100 */
+
+/* LlamaConfig (llm.rs:491-519). */
+typedef struct fc_llama_config {
+    int32_t vocab, d_model, n_layer, n_head, n_kv_head, head_dim, d_ff;
+    int32_t rope_dim;          /* even, <= head_dim */
+    float rope_base;
+    int32_t rope_type;         /* FC_ROPE_* */
+    float rope_linear_factor;  /* RopeScaling::linear_factor; 1.0 = none */
+    float norm_eps;
+    int32_t ctx;
+    int32_t tied;              /* 1: the head is token_embd (llm.rs:560-564) */
+    int32_t math_mode;         /* FC_MATH_* of the window forward */
+} fc_llama_config;
+
+/* One LlamaBlock (llm.rs:438-447). Projections are raw GGML Q8_0 tensors [out][in]; the
+ * optional f32 biases of the q, k, v projections (Qwen) may be NULL. */
+typedef struct fc_llama_layer {
+    const float* attn_norm;                          /* [d] */
+    const void *wq_q8, *wk_q8, *wv_q8, *wo_q8;       /* [H*hd][d], [KV*hd][d] x2, [d][H*hd] */
+    const float *bq, *bk, *bv;                       /* NULL or [H*hd], [KV*hd], [KV*hd] */
+    const float* ffn_norm;                           /* [d] */
+    const void *gate_q8, *up_q8, *down_q8;           /* [F][d] x2, [d][F] */
+} fc_llama_layer;
+
+typedef struct fc_llama_weights {
+    const void* token_embd_q8;     /* [V][d]; rows are dequantised as they are looked up */
+    const fc_llama_layer* layers;  /* n_layer entries */
+    const float* output_norm;      /* [d] */
+    const void* output_q8;         /* [V][d] or NULL when tied */
+    const float* rope_freqs;       /* RopeScaling::freq_factors: NULL or [rope_dim/2] */
+} fc_llama_weights;
+
+typedef struct fc_llama fc_llama;             /* LlamaModel on one GPU (llm.rs:549-565) */
+typedef struct fc_llama_cache fc_llama_cache; /* LlamaCache: per-layer KV rows + position (llm.rs:522-546) */
+
+/* Validates as Attention::new (llm.rs:243-252: n_head % n_kv_head, rope_dim even and <=
+ * head_dim) and RopeScaling::check (llm.rs:135-150: factors finite and > 0): FC_E_DIM. */
+int fc_llama_create(const fc_llama_config* cfg, const fc_llama_weights* w, int device, fc_llama** out);
+void fc_llama_free(fc_llama* m);
+/* LlamaModel::forward_tokens (llm.rs:622-635): n ids -> logits [n][vocab] (host buffer). */
+int fc_llama_forward_tokens(fc_llama* m, const int32_t* ids, int n, float* logits);
+/* LlamaModel::score_from (llm_score.rs:76-96) with the windows of plan_windows
+ * (llm_score.rs:21-32): score ids[from..] given what precedes them. lp (may be NULL) receives
+ * ln softmax(logits)[target] of target i at lp[i - 1] (entries before `from` are 0);
+ * is_greedy likewise. score_rolling (llm_score.rs:61-69) is from = 1. window must lie in
+ * 2..=ctx (FC_E_DIM, llm_score.rs:42-50). */
+int fc_llama_score_from(fc_llama* m, const int32_t* ids, int n, int from, int window, fc_score* score, float* lp,
+                        uint8_t* is_greedy);
+/* The same for n_seq sequences of seq_len ids each that fit one window (seq_len <= ctx),
+ * several windows per forward: scores [n_seq], lp (may be NULL) [n_seq][seq_len - 1]. */
+int fc_llama_score_sequences(fc_llama* m, const int32_t* ids, int n_seq, int seq_len, int batch_windows, fc_score* scores,
+                             float* lp);
+float fc_llama_last_score_ms(const fc_llama* m);
+
+int fc_llama_cache_create(fc_llama* m, fc_llama_cache** out);
+void fc_llama_cache_free(fc_llama_cache* c);
+int fc_llama_cache_clear(fc_llama_cache* c);   /* LlamaCache::clear, llm.rs:536-541 */
+int fc_llama_cache_pos(const fc_llama_cache* c);
+/* LlamaModel::forward_one (llm.rs:610-618): one token at the cache position; logits (host
+ * [vocab]) may be NULL. FC_E_DIM on id >= vocab or a full context. */
+int fc_llama_forward_one(fc_llama_cache* c, int32_t token, float* logits);
+/* LlamaModel::generate_cancellable (llm.rs:658-754): prime the prompt token by token, then
+ * draw up to min(max_new, ctx - n) tokens with sample_with_params over `recent` = prompt +
+ * tokens so far, stopping after a token found in stops[n_stops] (it is kept in out). The
+ * sampler and generator state stay on the device; *rng_state returns advanced. A prompt that
+ * fills the context is FC_E_DIM (llm.rs:724-729). */
+int fc_llama_generate(fc_llama_cache* c, const int32_t* prompt, int n, int max_new, const fc_sampling* params,
+                      const int32_t* stops, int n_stops, uint64_t* rng_state, const volatile int32_t* cancel,
+                      int32_t* out, int* n_out);
+float fc_llama_last_decode_ms(const fc_llama_cache* c);
 
 /* ---- introspection used by the benchmark ----------------------------------------- */
 /* Kernel launches issued by this library on the calling thread since the last call

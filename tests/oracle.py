@@ -20,8 +20,8 @@ def _ptr(a):
 def lib():
     global _lib
     if _lib is None:
-        if not os.path.exists(LIB_PATH):
-            subprocess.run(["make", "-C", ORACLE_DIR], check=True, capture_output=True)
+        # make rebuilds when a source is newer than the library
+        subprocess.run(["make", "-C", ORACLE_DIR], check=True, capture_output=True)
         L = C.CDLL(LIB_PATH)
         L.fo_f32_to_f16.restype, L.fo_f32_to_f16.argtypes = C.c_uint16, [C.c_float]
         L.fo_f16_to_f32.restype, L.fo_f16_to_f32.argtypes = C.c_float, [C.c_uint16]
@@ -58,6 +58,27 @@ def lib():
         L.fo_sample_with_params.restype = C.c_int
         L.fo_sample_with_params.argtypes = [C.c_void_p, C.c_int, C.c_float, C.c_int, C.c_float, C.c_float, C.c_void_p, C.c_int,
                                             C.POINTER(C.c_uint64)]
+        L.fo_rmsnorm.argtypes = [C.c_void_p, C.c_void_p, C.c_float, C.c_int, C.c_int, C.c_void_p]
+        L.fo_apply_rope.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int, C.c_void_p, C.c_int, C.c_float]
+        L.fo_silu_mul.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
+        L.fo_llama_plan_windows.restype = C.c_int
+        L.fo_llama_plan_windows.argtypes = [C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int]
+        L.fo_llama_log_prob.restype, L.fo_llama_log_prob.argtypes = C.c_double, [C.c_void_p, C.c_int, C.c_int]
+        L.fo_llama_create.restype, L.fo_llama_create.argtypes = C.c_void_p, [C.c_void_p, C.c_void_p, C.c_int]
+        L.fo_llama_free.argtypes = [C.c_void_p]
+        L.fo_llama_forward_tokens.restype = C.c_int
+        L.fo_llama_forward_tokens.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
+        L.fo_llama_cache_create.restype, L.fo_llama_cache_create.argtypes = C.c_void_p, [C.c_void_p]
+        L.fo_llama_cache_free.argtypes = [C.c_void_p]
+        L.fo_llama_cache_clear.argtypes = [C.c_void_p]
+        L.fo_llama_cache_pos.restype, L.fo_llama_cache_pos.argtypes = C.c_int, [C.c_void_p]
+        L.fo_llama_forward_one.restype, L.fo_llama_forward_one.argtypes = C.c_int, [C.c_void_p, C.c_int, C.c_void_p]
+        L.fo_llama_score_from.restype = C.c_int
+        L.fo_llama_score_from.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_double),
+                                          C.POINTER(C.c_int), C.POINTER(C.c_int), C.c_void_p, C.c_void_p]
+        L.fo_llama_generate.restype = C.c_int
+        L.fo_llama_generate.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_float, C.c_int, C.c_float, C.c_float,
+                                        C.c_void_p, C.c_int, C.POINTER(C.c_uint64), C.c_void_p]
         _lib = L
     return _lib
 
@@ -222,6 +243,104 @@ class OracleModel:
             self._s = None
         if self._m:
             lib().fo_model_free(self._m)
+            self._m = None
+
+    def __del__(self):
+        self.close()
+
+
+# ------------------------------------------------------------------ Llama / Qwen (llm.rs)
+def rmsnorm(x, w, eps):
+    x = f32(x)
+    rows, d = (1, x.size) if x.ndim == 1 else x.shape
+    out = np.empty_like(x)
+    w = f32(w)
+    lib().fo_rmsnorm(_ptr(x), _ptr(w), eps, rows, d, _ptr(out))
+    return out
+
+
+def apply_rope(x, n_heads, head_dim, rope_dim, pos, base=10000.0, neox=False, freq_factors=(), linear_factor=1.0):
+    """llm.rs:158-185 on a copy of x."""
+    x = f32(x).copy()
+    ff = f32(freq_factors)
+    lib().fo_apply_rope(_ptr(x), n_heads, head_dim, rope_dim, pos, base, int(neox), _ptr(ff) if ff.size else None, ff.size,
+                        linear_factor)
+    return x
+
+
+def silu_mul(g, u):
+    g, u = f32(g), f32(u)
+    out = np.empty_like(g)
+    lib().fo_silu_mul(_ptr(g), _ptr(u), g.size, _ptr(out))
+    return out
+
+
+def llama_plan_windows(n, window, from_):
+    buf = np.zeros(3 * (n + 2), dtype=np.int32)
+    k = lib().fo_llama_plan_windows(n, window, from_, _ptr(buf), n + 2)
+    return [tuple(int(v) for v in buf[3 * i:3 * i + 3]) for i in range(k)]
+
+
+def llama_log_prob(logits, target):
+    logits = f32(logits)
+    return lib().fo_llama_log_prob(_ptr(logits), logits.size, target)
+
+
+class OracleLlama:
+    """The restated LlamaModel built from the same fc_llama_config / fc_llama_weights structs."""
+
+    def __init__(self, synth_llama, threads=1):
+        self.sm = synth_llama
+        self.V = synth_llama.dims["vocab"]
+        self._m = lib().fo_llama_create(C.addressof(synth_llama.config), C.addressof(synth_llama.weights), threads)
+        self._c = lib().fo_llama_cache_create(self._m) if self._m else None
+
+    @property
+    def ok(self):
+        return bool(self._m)
+
+    def forward_tokens(self, ids):
+        ids = np.ascontiguousarray(ids, dtype=np.int32)
+        out = np.empty((ids.size, self.V), dtype=np.float32)
+        assert lib().fo_llama_forward_tokens(self._m, _ptr(ids), ids.size, _ptr(out)) == 0
+        return out
+
+    def clear(self):
+        lib().fo_llama_cache_clear(self._c)
+
+    def pos(self):
+        return lib().fo_llama_cache_pos(self._c)
+
+    def forward_one(self, token):
+        out = np.empty(self.V, dtype=np.float32)
+        rc = lib().fo_llama_forward_one(self._c, int(token), _ptr(out))
+        return out if rc == 0 else None
+
+    def score_from(self, ids, from_, window):
+        ids = np.ascontiguousarray(ids, dtype=np.int32)
+        lp = np.zeros(max(ids.size, 1), dtype=np.float64)
+        gr = np.zeros(max(ids.size, 1), dtype=np.uint8)
+        total, n, g = C.c_double(), C.c_int(), C.c_int()
+        rc = lib().fo_llama_score_from(self._m, _ptr(ids), ids.size, from_, window, C.byref(total), C.byref(n), C.byref(g),
+                                       _ptr(lp), _ptr(gr))
+        if rc != 0:
+            return None
+        return total.value, n.value, bool(g.value), lp[:max(ids.size - 1, 0)], gr[:max(ids.size - 1, 0)].astype(bool)
+
+    def generate(self, prompt, max_new, rng, temperature=1.0, top_k=0, top_p=1.0, repetition_penalty=1.0, stops=()):
+        prompt = np.ascontiguousarray(prompt, dtype=np.int32)
+        st = np.ascontiguousarray(stops, dtype=np.int32)
+        out = np.zeros(max(max_new, 1), dtype=np.int32)
+        n = lib().fo_llama_generate(self._c, _ptr(prompt), prompt.size, max_new, temperature, top_k, top_p, repetition_penalty,
+                                    _ptr(st) if st.size else None, st.size, C.byref(rng.state), _ptr(out))
+        return None if n < 0 else out[:n].copy()
+
+    def close(self):
+        if self._c:
+            lib().fo_llama_cache_free(self._c)
+            self._c = None
+        if self._m:
+            lib().fo_llama_free(self._m)
             self._m = None
 
     def __del__(self):

@@ -49,3 +49,20 @@ def test_argument_validation_precedes_device_use():
     with pytest.raises(fcb.FerrumCudaError) as e:
         fcb.CudaSlm(bad, sm.weights)
     assert e.value.code == _lib.FC_E_FORMAT
+
+
+def test_llama_validation_precedes_device_use():
+    from ferrum_cpu_b200.llama import CudaLlama
+    shape = list(synth.LLAMA_SHAPES["llama-tiny"])
+    bad = list(shape)
+    bad[3], bad[4], bad[5] = 6, 4, 16                    # 6 query heads cannot share 4 key/value heads (llm.rs:243-247)
+    for sm in (synth.SynthLlama(*bad), synth.llama_named("llama-tiny", rope_dim=5), synth.llama_named("llama-tiny", rope_dim=32),
+               synth.llama_named("llama-tiny", rope_linear_factor=0.0),
+               synth.llama_named("llama-tiny", freq_factors=[1.0, 0.0] * 4)):
+        with pytest.raises(fcb.FerrumCudaError) as e:
+            CudaLlama.from_synth(sm)
+        assert e.value.code == _lib.FC_E_DIM
+    if fcb.device_count() == 0:
+        with pytest.raises(fcb.FerrumCudaError) as e:
+            CudaLlama.from_synth(synth.llama_named("llama-tiny"))
+        assert e.value.code == _lib.FC_E_CUDA
