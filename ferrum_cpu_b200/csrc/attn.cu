@@ -2,6 +2,7 @@
 // full-window form used by scoring/prefill. fp32 throughout; the T x T probability matrix
 // the reference stores (transformer.rs:458-478 `last_attention`) is never materialised.
 #include "fc_common.cuh"
+#include "pdl.cuh"
 
 namespace fc {
 
@@ -14,6 +15,8 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(const float* __restric
                                                           const float* __restrict__ vc, int kvd, int group, int hd, int ctx,
                                                           const StepState* st, float* __restrict__ out) {
     extern __shared__ float sm[];   // scores[ctx] | q_h[hd] | red[64] | part[8][hd]
+    pdl_trigger();
+    pdl_wait();
     if (st->done | st->error) return;
     const int len = st->pos + 1;    // the new row was appended by the QKV GEMV
     const int h = blockIdx.x, hs = h * hd, ks = (h / group) * hd;
@@ -78,14 +81,21 @@ int launch_attn_decode_gqa(const float* q, const float* kcache, const float* vca
     const size_t smem = (size_t)(ctx + hd + 64 + (threads / hd) * hd) * sizeof(float);
     if (smem > 200 * 1024) return fail(FC_E_SHAPE, "context %d exceeds what the decode attention holds in shared memory", ctx);
     if (smem > 48 * 1024) FC_CUDA(cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    attn_decode_kernel<<<H, threads, smem, st>>>(q, kcache, vcache, KV * hd, H / KV, hd, ctx, state, out);
-    FC_LAUNCHED();
+    FC_CUDA(launch_pdl(attn_decode_kernel, dim3(H), dim3(threads), smem, st, q, kcache, vcache, KV * hd, H / KV, hd, ctx, state, out));
+    ++g_launches;
     return FC_OK;
 }
 
 int launch_attn_decode(const float* q, const float* kcache, const float* vcache, int d, int H, int ctx,
                        const StepState* state, float* out, cudaStream_t st) {
-    return launch_attn_decode_gqa(q, kcache, vcache, H, H, d / H, ctx, state, out, st);
+    const int hd = d / H, threads = 256;
+    if (hd > 256) return fail(FC_E_SHAPE, "head_dim %d exceeds 256", hd);
+    const size_t smem = (size_t)(ctx + hd + 64 + (threads / hd) * hd) * sizeof(float);
+    if (smem > 200 * 1024) return fail(FC_E_SHAPE, "context %d exceeds what the decode attention holds in shared memory", ctx);
+    if (smem > 48 * 1024) FC_CUDA(cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    attn_decode_kernel<<<H, threads, smem, st>>>(q, kcache, vcache, d, 1, hd, ctx, state, out);
+    FC_LAUNCHED();
+    return FC_OK;
 }
 
 // --------------------------------------------------------------------------- window form

@@ -71,7 +71,7 @@ struct QMat {
 };
 constexpr int kRowPad = 128;
 
-enum Epilogue : int { EPI_NONE = 0, EPI_GELU = 1 };
+enum Epilogue : int { EPI_NONE = 0, EPI_GELU = 1, EPI_SWIGLU = 2 };
 
 // activation.rs:9-12 (tanh GELU), same constants and association as the reference.
 __device__ __forceinline__ float gelu_f(float x) {
@@ -107,6 +107,18 @@ struct GemvOut {
 int launch_gemv_q8(const QMat& w, const float* x, const float* bias, const float* residual, int epi,
                    const GemvOut& out, const StepState* state, cudaStream_t st);
 
+// Split-K form for wide matrices: optional RMSNorm of x (norm_w, eps) as it is staged; epi
+// EPI_SWIGLU pairs rows (2i, 2i+1) as (gate, up) and writes out[i] = silu(gate) * up. `next` (may
+// be null) is the matrix the following kernel streams: its planes are prefetched into L2.
+int launch_gemv_q8_wide(const QMat& w, const float* x, const float* norm_w, float eps, const float* bias, const float* residual,
+                        int epi, float* out, const StepState* state, const QMat* next, cudaStream_t st);
+
+// gemv_stream.cu — the same contract on a persistent kernel that streams row tiles through a
+// shared-memory ring with bulk async copies; `status` (device int) is raised to FC_E_TIMEOUT when
+// a bounded wait runs out. Shapes the ring does not cover take launch_gemv_q8_wide.
+int launch_gemv_q8_stream(const QMat& w, const float* x, const float* norm_w, float eps, const float* bias, const float* residual,
+                          int epi, float* out, const StepState* state, int* status, cudaStream_t st);
+
 // gemm_simt.cu — Y[M][N] = X[M][K]·Wᵀ + bias (+GELU) (+residual[M][N]), fp32 CUDA cores.
 int launch_gemm_q8_fp32(const QMat& w, const float* x, const float* bias, const float* residual, int epi,
                         float* y, int M, int ldy, cudaStream_t st);
@@ -139,6 +151,7 @@ int launch_step_tail(const float* logits, int V, float* probs_or_null, int do_se
                      StepState* state, float* sel_logit_or_null, cudaStream_t st);
 // End-of-step bookkeeping alone (steps that skip the head).
 int launch_step_advance(StepState* state, cudaStream_t st);
+int launch_step_advance_pdl(StepState* state, cudaStream_t st);
 // Scoring tail: per row of logits[R][ldl], target id (or -1) -> logprob, is_greedy.
 // `status` (device int, may be null) is raised to FC_E_TIMEOUT when a bounded wait runs out.
 int launch_score_rows(const float* logits, int ldl, int V, const int* targets, int R, double* logprob,

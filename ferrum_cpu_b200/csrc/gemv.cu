@@ -162,4 +162,178 @@ int launch_gemv_q8(const QMat& w, const float* x, const float* bias, const float
     return FC_OK;
 }
 
+// ------------------------------------------------------------------- split-K GEMV (Llama)
+// The same product for the wide matrices of the Llama family (K up to 12288, N from 2048 to
+// the vocabulary). A block of 16 half warps is G groups x S k-slices: a group owns RIF rows, its
+// slices take interleaved runs of 16 chunks (256 B) of those rows and their partial sums are
+// added in slice order through shared memory, so that even a [2048][8192] matrix spreads over
+// several hundred blocks with RIF independent 128-bit loads in flight per lane.
+// Prologue (optional): RMSNorm of the input row while it is staged (llm.rs:57-64).
+// Epilogue: bias, residual, or SwiGLU over interleaved (gate, up) row pairs (llm.rs:417-428).
+struct GemvWideArgs {
+    const uint8_t* qu; const __half* d; int N, K;
+    const float* x; const float* norm_w; float eps;
+    const float* bias; const float* residual; int epi;
+    float* out; int S;
+    const StepState* state;
+    // the matrix the next kernel of the step will stream (or null): prefetched into L2 from here
+    const uint8_t* next_q; const __half* next_d; unsigned long long next_q_bytes, next_d_bytes;
+};
+
+// One slice per block of `bytes` at p, as L2 prefetch hints (bulk form; 16-byte granularity).
+__device__ __forceinline__ void prefetch_slice_l2(const void* p, unsigned long long bytes) {
+    unsigned long long per = ((bytes + gridDim.x - 1) / gridDim.x + 15ull) & ~15ull;
+    const unsigned long long off = (unsigned long long)blockIdx.x * per;
+    if (off >= bytes) return;
+    if (off + per > bytes) per = (bytes - off) & ~15ull;
+    for (unsigned long long o = 0; o < per; o += 32768ull) {
+        const unsigned n = (unsigned)(per - o < 32768ull ? per - o : 32768ull);
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"((const char*)p + off + o), "r"(n) : "memory");
+    }
+}
+
+template <int RIF>
+__global__ void __launch_bounds__(256) gemv_q8_wide_kernel(GemvWideArgs a) {
+    extern __shared__ float4 xs[];
+    __shared__ float red[33];
+    __shared__ float part[16 * RIF];
+    if (a.state && (a.state->done | a.state->error)) return;
+    const int K = a.K, chunks = K >> 4, units = K >> 2;
+    const int S = a.S, G = 16 / S;
+    const int hw = threadIdx.x >> 4, hl = threadIdx.x & 15;
+    const int g = hw / S, sl = hw - g * S;
+    const int row0 = (blockIdx.x * G + g) * RIF;          // rows past N lie in the zero padding up to N_pad
+    const int kb_per_row = K >> 5;
+    // the first weights of this thread are requested before the activation is staged: they do
+    // not depend on it, and their latency hides behind the staging and the norm
+    uint4 w0[RIF];
+    float sc0[RIF];
+    const int c0 = sl * 16 + hl;
+    const bool active = row0 < a.N && c0 < chunks;
+    if (active) {
+#pragma unroll
+        for (int r = 0; r < RIF; ++r) {
+            const size_t row = (size_t)(row0 + r);
+            w0[r] = __ldg((const uint4*)(a.qu + row * K) + c0);
+            sc0[r] = __half2float(__ldg(a.d + row * kb_per_row + (c0 >> 1)));
+        }
+    }
+    if (a.next_q && threadIdx.x == 0) {
+        prefetch_slice_l2(a.next_q, a.next_q_bytes);
+        prefetch_slice_l2(a.next_d, a.next_d_bytes);
+    }
+    // stage x (swizzled 16-byte units), normalising it on the way when asked
+    float ss = 0.0f;
+    for (int u = threadIdx.x; u < units; u += blockDim.x) {
+        const float4 v = ((const float4*)a.x)[u];
+        ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+        xs[u ^ ((u >> 3) & 3)] = v;
+    }
+    if (a.norm_w) {
+        const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) red[wid] = ss;
+        __syncthreads();
+        if (wid == 0) {
+            float t = lane < 8 ? red[lane] : 0.0f;
+#pragma unroll
+            for (int o = 4; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+            if (lane == 0) red[32] = t;
+        }
+        __syncthreads();
+        const float inv = 1.0f / sqrtf(red[32] / (float)K + a.eps);
+        for (int u = threadIdx.x; u < units; u += blockDim.x) {      // the units this thread staged itself
+            float4 v = xs[u ^ ((u >> 3) & 3)];
+            const float4 w = ((const float4*)a.norm_w)[u];
+            v.x = __fmul_rn(__fmul_rn(v.x, inv), w.x); v.y = __fmul_rn(__fmul_rn(v.y, inv), w.y);
+            v.z = __fmul_rn(__fmul_rn(v.z, inv), w.z); v.w = __fmul_rn(__fmul_rn(v.w, inv), w.w);
+            xs[u ^ ((u >> 3) & 3)] = v;
+        }
+    }
+    __syncthreads();
+
+    const unsigned hmask = 0xFFFFu << (threadIdx.x & 16);
+    float acc[RIF];
+#pragma unroll
+    for (int r = 0; r < RIF; ++r) acc[r] = 0.0f;
+    if (active) {
+#pragma unroll
+        for (int r = 0; r < RIF; ++r) acc[r] = sc0[r] * dot16(w0[r], xs, c0);
+        for (int c = c0 + 16 * S; c < chunks; c += 16 * S) {
+            uint4 w[RIF];
+            float sc[RIF];
+#pragma unroll
+            for (int r = 0; r < RIF; ++r) {
+                const size_t row = (size_t)(row0 + r);
+                w[r] = __ldg((const uint4*)(a.qu + row * K) + c);
+                sc[r] = __half2float(__ldg(a.d + row * kb_per_row + (c >> 1)));
+            }
+#pragma unroll
+            for (int r = 0; r < RIF; ++r) acc[r] = fmaf(sc[r], dot16(w[r], xs, c), acc[r]);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < RIF; ++r) {
+        float v = acc[r];
+        v += __shfl_xor_sync(hmask, v, 8);
+        v += __shfl_xor_sync(hmask, v, 4);
+        v += __shfl_xor_sync(hmask, v, 2);
+        v += __shfl_xor_sync(hmask, v, 1);
+        if (hl == 0) part[hw * RIF + r] = v;
+    }
+    __syncthreads();
+    // thread t < G * RIF finishes row (t / RIF group, t % RIF): slices added in a fixed order
+    const int t = threadIdx.x;
+    float v = 0.0f;
+    int n = a.N;
+    if (t < G * RIF) {
+        const int tg = t / RIF, tr = t - tg * RIF;
+        for (int s2 = 0; s2 < S; ++s2) v += part[(tg * S + s2) * RIF + tr];
+        n = (blockIdx.x * G + tg) * RIF + tr;
+        if (n < a.N && a.bias) v += a.bias[n];
+    }
+    if (a.epi == EPI_SWIGLU) {
+        __syncthreads();
+        if (t < G * RIF) part[t] = v;
+        __syncthreads();
+        if (t < G * RIF && !(t & 1) && n < a.N) {
+            const float gte = part[t], up = part[t + 1];
+            a.out[n >> 1] = __fmul_rn(__fdiv_rn(gte, __fadd_rn(1.0f, expf(-gte))), up);
+        }
+        return;
+    }
+    if (t < G * RIF && n < a.N) {
+        if (a.residual) v = a.residual[n] + v;
+        a.out[n] = v;
+    }
+}
+
+int launch_gemv_q8_wide(const QMat& w, const float* x, const float* norm_w, float eps, const float* bias, const float* residual,
+                        int epi, float* out, const StepState* state, const QMat* next, cudaStream_t st) {
+    if (w.K % 16 || w.K > 12288) return fail(FC_E_SHAPE, "GEMV row length %d must be a multiple of 16, at most 12288", w.K);
+    if (epi == EPI_SWIGLU && ((w.N & 1) || residual)) return fail(FC_E_SHAPE, "the SwiGLU epilogue pairs rows and takes no residual");
+    GemvWideArgs a;
+    a.qu = w.qu; a.d = w.d; a.N = w.N; a.K = w.K;
+    a.x = x; a.norm_w = norm_w; a.eps = eps; a.bias = bias; a.residual = residual; a.epi = epi; a.out = out; a.state = state;
+    a.next_q = next ? next->qu : nullptr;
+    a.next_d = next ? next->d : nullptr;
+    a.next_q_bytes = next ? (unsigned long long)next->N_pad * next->K : 0;          // planes are padded to N_pad rows,
+    a.next_d_bytes = next ? (unsigned long long)next->N_pad * (next->K / 32) * 2 : 0;  // multiples of 16 bytes
+    const int chunks = w.K >> 4;
+    const bool big = (size_t)w.N * w.K >= (size_t)8 << 20;
+    const int rif = big ? 4 : 2;
+    // more k-slices (fewer rows per block) until the grid fills the SMs four times over
+    int S = 1;
+    while (S < 16 && (w.N + (16 / S) * rif - 1) / ((16 / S) * rif) < 592 && chunks / (16 * S * 2) >= 1) S *= 2;
+    a.S = S;
+    const int rows_per_block = (16 / S) * rif;
+    const int blocks = (w.N + rows_per_block - 1) / rows_per_block;
+    const size_t smem = (size_t)w.K * sizeof(float);
+    if (big) gemv_q8_wide_kernel<4><<<blocks, 256, smem, st>>>(a);
+    else gemv_q8_wide_kernel<2><<<blocks, 256, smem, st>>>(a);
+    FC_LAUNCHED();
+    return FC_OK;
+}
+
 }  // namespace fc

@@ -13,7 +13,7 @@ using namespace fc;
 namespace {
 
 struct LlamaLayerDev {
-    QMat qkv, wo, gateup, down;      // wq|wk|wv rows fused, gate|up rows fused
+    QMat qkv, wo, gateup, down;      // wq|wk|wv rows fused; gate and up rows interleaved (g0, u0, g1, u1, ...)
     float* qkv_b = nullptr;          // fused q|k|v bias, or null when the file has none
     float *attn_norm = nullptr, *ffn_norm = nullptr;
 };
@@ -51,6 +51,7 @@ struct fc_llama_cache {
     int* queue = nullptr;
     int queue_cap = 0;
     StepState* state = nullptr;
+    int* status = nullptr;                // raised by a kernel whose bounded wait ran out
     int host_pos = 0;
     cudaGraphExec_t graph[2] = {nullptr, nullptr};   // [0]: step without the head, [1]: with it
     int graph_nodes[2] = {0, 0};
@@ -79,6 +80,19 @@ int upload_fused(Arena& ar, std::initializer_list<std::pair<const void*, int>> p
         at += bytes;
     }
     return upload_q8(ar, buf.data(), (int)rows, K, out, st);
+}
+
+// Rows of two raw Q8_0 tensors [rows][K] interleaved: a0, b0, a1, b1, ...
+int upload_interleaved(Arena& ar, const void* a, const void* b, int rows, int K, QMat* out, cudaStream_t st) {
+    if (!a || !b) return fail(FC_E_FORMAT, "a required Q8_0 tensor is null");
+    if (K <= 0 || K % 32) return fail(FC_E_FORMAT, "Q8_0 row length %d must be a positive multiple of 32", K);
+    const size_t rb = q8_row_bytes(K);
+    std::vector<uint8_t> buf((size_t)2 * rows * rb);
+    for (int r = 0; r < rows; ++r) {
+        std::memcpy(buf.data() + (size_t)(2 * r) * rb, (const uint8_t*)a + (size_t)r * rb, rb);
+        std::memcpy(buf.data() + (size_t)(2 * r + 1) * rb, (const uint8_t*)b + (size_t)r * rb, rb);
+    }
+    return upload_q8(ar, buf.data(), 2 * rows, K, out, st);
 }
 
 int gemm(fc_llama* m, const QMat& w, const float* x, const float* bias, const float* res, float* y, int M, int ldy) {
@@ -205,36 +219,24 @@ int launch_step(fc_llama_cache* s, int with_head) {
     fc_llama* m = s->m;
     const fc_llama_config& c = m->cfg;
     cudaStream_t st = m->st;
-    const int d = c.d_model, F = c.d_ff;
     const size_t layer_stride = (size_t)c.ctx * m->kv_dim;
     FC_TRY(launch_llama_embed_step(m->tok, c.ctx, s->queue, s->state, s->x, st));
     for (int l = 0; l < c.n_layer; ++l) {
         const LlamaLayerDev& L = m->layers[l];
         float* kc = s->kc + l * layer_stride;
         float* vc = s->vc + l * layer_stride;
-        GemvOut o;
-        FC_TRY(launch_llama_rmsnorm(s->x, L.attn_norm, c.norm_eps, 1, d, s->n, s->state, st));
-        o.out[0] = s->qkv;
-        FC_TRY(launch_gemv_q8(L.qkv, s->n, L.qkv_b, nullptr, EPI_NONE, o, s->state, st));
+        // RMSNorm rides in the prologue of the projection that reads it, SwiGLU in the epilogue of gate/up
+        FC_TRY(launch_gemv_q8_stream(L.qkv, s->x, L.attn_norm, c.norm_eps, L.qkv_b, nullptr, EPI_NONE, s->qkv, s->state, s->status, st));
         FC_TRY(launch_llama_rope_store(s->qkv, c.n_head, c.n_kv_head, c.head_dim, c.rope_dim, c.rope_type == FC_ROPE_NEOX, m->ftab,
                                        m->inv_linear, kc, vc, s->state, st));
         FC_TRY(launch_attn_decode_gqa(s->qkv, kc, vc, c.n_head, c.n_kv_head, c.head_dim, c.ctx, s->state, s->att, st));
-        o.out[0] = s->x;
-        FC_TRY(launch_gemv_q8(L.wo, s->att, nullptr, s->x, EPI_NONE, o, s->state, st));
-        FC_TRY(launch_llama_rmsnorm(s->x, L.ffn_norm, c.norm_eps, 1, d, s->n, s->state, st));
-        o.out[0] = s->gu;
-        FC_TRY(launch_gemv_q8(L.gateup, s->n, nullptr, nullptr, EPI_NONE, o, s->state, st));
-        FC_TRY(launch_llama_swiglu(s->gu, 1, F, s->hid, s->state, st));
-        o.out[0] = s->x;
-        FC_TRY(launch_gemv_q8(L.down, s->hid, nullptr, s->x, EPI_NONE, o, s->state, st));
+        FC_TRY(launch_gemv_q8_stream(L.wo, s->att, nullptr, 0.0f, nullptr, s->x, EPI_NONE, s->x, s->state, s->status, st));
+        FC_TRY(launch_gemv_q8_stream(L.gateup, s->x, L.ffn_norm, c.norm_eps, nullptr, nullptr, EPI_SWIGLU, s->hid, s->state, s->status, st));
+        FC_TRY(launch_gemv_q8_stream(L.down, s->hid, nullptr, 0.0f, nullptr, s->x, EPI_NONE, s->x, s->state, s->status, st));
     }
-    if (with_head) {
-        GemvOut o;
-        o.out[0] = s->logits;
-        FC_TRY(launch_llama_rmsnorm(s->x, m->out_norm, c.norm_eps, 1, d, s->n, s->state, st));
-        FC_TRY(launch_gemv_q8(m->head, s->n, nullptr, nullptr, EPI_NONE, o, s->state, st));
-    }
-    return launch_step_advance(s->state, st);
+    if (with_head)
+        FC_TRY(launch_gemv_q8_stream(m->head, s->x, m->out_norm, c.norm_eps, nullptr, nullptr, EPI_NONE, s->logits, s->state, s->status, st));
+    return launch_step_advance_pdl(s->state, st);
 }
 
 int run_step(fc_llama_cache* s, int with_head) {
@@ -263,8 +265,14 @@ __global__ void llama_set_state_kernel(StepState* st, int pos, int fed, int tail
 }
 
 int read_state(fc_llama_cache* s, StepState* out) {
+    int status = 0;
     FC_CUDA(cudaMemcpyAsync(out, s->state, sizeof(StepState), cudaMemcpyDeviceToHost, s->m->st));
+    FC_CUDA(cudaMemcpyAsync(&status, s->status, sizeof(int), cudaMemcpyDeviceToHost, s->m->st));
     FC_CUDA(cudaStreamSynchronize(s->m->st));
+    if (status != 0) {
+        cudaMemsetAsync(s->status, 0, sizeof(int), s->m->st);
+        return fail(FC_E_TIMEOUT, "a bounded wait inside the streaming GEMV ran out (status %d)", status);
+    }
     return FC_OK;
 }
 
@@ -341,7 +349,7 @@ int fc_llama_create(const fc_llama_config* cfg, const fc_llama_weights* w, int d
             LlamaLayerDev& L = m->layers[l];
             FC_TRY(upload_fused(m->arena, {{h.wq_q8, m->q_dim}, {h.wk_q8, m->kv_dim}, {h.wv_q8, m->kv_dim}}, d, &L.qkv, st));
             FC_TRY(upload_q8(m->arena, h.wo_q8, d, m->q_dim, &L.wo, st));
-            FC_TRY(upload_fused(m->arena, {{h.gate_q8, F}, {h.up_q8, F}}, d, &L.gateup, st));
+            FC_TRY(upload_interleaved(m->arena, h.gate_q8, h.up_q8, F, d, &L.gateup, st));
             FC_TRY(upload_q8(m->arena, h.down_q8, d, F, &L.down, st));
             FC_TRY(upload_f32(m->arena, h.attn_norm, d, &L.attn_norm, st));
             FC_TRY(upload_f32(m->arena, h.ffn_norm, d, &L.ffn_norm, st));
@@ -512,6 +520,8 @@ int fc_llama_cache_create(fc_llama* m, fc_llama_cache** out) {
         s->queue_cap = c.ctx + 1;
         FC_TRY(a.alloc_n(&s->queue, (size_t)s->queue_cap));
         FC_TRY(a.alloc_n(&s->state, 1));
+        FC_TRY(a.alloc_n(&s->status, 1));
+        FC_CUDA(cudaMemsetAsync(s->status, 0, sizeof(int), m->st));
         FC_TRY(a.alloc_n(&s->rng_d, 1));
         FC_CUDA(cudaEventCreate(&s->ev0));
         FC_CUDA(cudaEventCreate(&s->ev1));

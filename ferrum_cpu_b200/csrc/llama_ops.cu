@@ -3,6 +3,7 @@
 // llm_score.rs and the greedy pick. All are HBM-bound elementwise / row-reduction work: one
 // block per row, coalesced accesses, fixed-order block reductions.
 #include "llama_ops.cuh"
+#include "pdl.cuh"
 
 namespace fc {
 
@@ -66,6 +67,8 @@ int launch_llama_embed_rows(const QMat& tok, const int* ids, int R, float* x, in
 // forward_one (llm.rs:610-618): the queued token at the cache position. A full context is
 // refused like a bad id (generation stops at the window, llm.rs:720-730).
 __global__ void llama_embed_step_kernel(QMat tok, int ctx, const int* __restrict__ queue, StepState* st, float* __restrict__ x) {
+    pdl_trigger();
+    pdl_wait();
     if (st->done | st->error) return;
     const int pos = st->pos, id = queue[st->fed];
     if (id < 0 || id >= tok.N || pos >= ctx) {
@@ -76,8 +79,8 @@ __global__ void llama_embed_step_kernel(QMat tok, int ctx, const int* __restrict
     for (int c = threadIdx.x; c < tok.K; c += blockDim.x) x[c] = table_value(tok, id, c);
 }
 int launch_llama_embed_step(const QMat& tok, int ctx, const int* queue, StepState* state, float* x, cudaStream_t st) {
-    llama_embed_step_kernel<<<1, 256, 0, st>>>(tok, ctx, queue, state, x);
-    FC_LAUNCHED();
+    FC_CUDA(launch_pdl(llama_embed_step_kernel, dim3(1), dim3(256), 0, st, tok, ctx, queue, state, x));
+    ++g_launches;
     return FC_OK;
 }
 
@@ -139,40 +142,49 @@ int launch_llama_rope_rows(float* qkv, int R, int ld, int T, int n_q, int n_kv, 
 }
 
 // Decode form (Attention::project + the cache append of forward_one, llm.rs:276-301,345-351):
-// rotates q in place and appends the rotated k row and the v row at the cache position.
+// one block per head of the fused q | k | v row. Query heads are rotated in place, key heads are
+// rotated into the cache row of the current position, value heads are copied there.
 __global__ void llama_rope_store_kernel(float* __restrict__ qkv, int n_q, int n_kv, int hd, int half, int neox,
                                         const float2* __restrict__ ftab, float inv_linear, float* __restrict__ kc,
                                         float* __restrict__ vc, const StepState* st) {
+    pdl_trigger();
+    pdl_wait();
     if (st->done | st->error) return;
-    const int pos = st->pos, q_dim = n_q * hd, kv_dim = n_kv * hd;
-    const int pairs = (n_q + n_kv) * half;
-    for (int u = threadIdx.x; u < pairs; u += blockDim.x) {
-        const int h = u / half, i = u - h * half;
-        const int off = h * hd;    // k heads follow the q heads directly in the fused row
-        const int ia = neox ? off + i : off + 2 * i, ib = neox ? off + i + half : off + 2 * i + 1;
-        rotate_pair(qkv, ia, ib, rope_angle(pos, ftab[i], inv_linear));
+    const int pos = st->pos, kv_dim = n_kv * hd;
+    const int h = blockIdx.x, t = threadIdx.x;
+    float* src = qkv + (size_t)h * hd;
+    if (h >= n_q + n_kv) {                                   // a value head
+        if (t < hd) vc[(size_t)pos * kv_dim + (h - n_q - n_kv) * hd + t] = src[t];
+        return;
     }
-    __syncthreads();
-    for (int c = threadIdx.x; c < kv_dim; c += blockDim.x) {
-        kc[(size_t)pos * kv_dim + c] = qkv[q_dim + c];
-        vc[(size_t)pos * kv_dim + c] = qkv[q_dim + kv_dim + c];
+    float* dst = h < n_q ? src : kc + (size_t)pos * kv_dim + (h - n_q) * hd;
+    if (t < half) {
+        const int ia = neox ? t : 2 * t, ib = neox ? t + half : 2 * t + 1;
+        float s, c;
+        sincosf(rope_angle(pos, ftab[t], inv_linear), &s, &c);
+        const float a = src[ia], b = src[ib];
+        dst[ia] = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s));
+        dst[ib] = __fadd_rn(__fmul_rn(a, s), __fmul_rn(b, c));
     }
+    if (dst != src && t >= 2 * half && t < hd) dst[t] = src[t];   // the unrotated tail of a key head
 }
 int launch_llama_rope_store(float* qkv, int n_q, int n_kv, int hd, int rope_dim, int neox, const float2* ftab, float inv_linear,
                             float* kc, float* vc, const StepState* state, cudaStream_t st) {
-    llama_rope_store_kernel<<<1, 512, 0, st>>>(qkv, n_q, n_kv, hd, rope_dim / 2, neox, ftab, inv_linear, kc, vc, state);
-    FC_LAUNCHED();
+    FC_CUDA(launch_pdl(llama_rope_store_kernel, dim3(n_q + 2 * n_kv), dim3(hd), 0, st, qkv, n_q, n_kv, hd, rope_dim / 2, neox, ftab,
+                       inv_linear, kc, vc, state));
+    ++g_launches;
     return FC_OK;
 }
 
 // --------------------------------------------------------------------------------- SwiGLU
-// FeedForward::forward (llm.rs:417-428): h = (g / (1 + exp(-g))) * u on rows [gate | up].
+// FeedForward::forward (llm.rs:417-428): h = (g / (1 + exp(-g))) * u on rows of interleaved
+// (gate_i, up_i) pairs, the row order of the fused gate/up matrix.
 __global__ void llama_swiglu_kernel(const float* __restrict__ gu, int F, float* __restrict__ h, const StepState* st) {
     if (st && (st->done | st->error)) return;
     const float* row = gu + (size_t)blockIdx.y * 2 * F;
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c < F) {
-        const float g = row[c], u = row[F + c];
+        const float g = row[2 * c], u = row[2 * c + 1];
         h[(size_t)blockIdx.y * F + c] = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), u);
     }
 }
@@ -240,6 +252,8 @@ __global__ void __launch_bounds__(1024) llama_pick_kernel(const float* __restric
                                                           int queue_cap, StepState* st) {
     __shared__ float fred[32];
     __shared__ int ired[32];
+    pdl_trigger();
+    pdl_wait();
     if (st->done | st->error) return;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
     float mx = -INFINITY;

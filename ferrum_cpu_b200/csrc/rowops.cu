@@ -3,6 +3,7 @@
 #include <cuda_bf16.h>
 
 #include "fc_common.cuh"
+#include "pdl.cuh"
 
 namespace fc {
 
@@ -258,6 +259,8 @@ int launch_step_tail(const float* logits, int V, float* probs_or_null, int do_se
 }
 
 __global__ void step_advance_kernel(StepState* st) {
+    pdl_trigger();
+    pdl_wait();
     if (st->done | st->error) return;
     st->pos += 1;
     st->fed += 1;
@@ -265,6 +268,12 @@ __global__ void step_advance_kernel(StepState* st) {
 int launch_step_advance(StepState* state, cudaStream_t st) {
     step_advance_kernel<<<1, 1, 0, st>>>(state);
     FC_LAUNCHED();
+    return FC_OK;
+}
+// The same as a programmatic dependent of the kernel ahead (steps whose kernels all wait first).
+int launch_step_advance_pdl(StepState* state, cudaStream_t st) {
+    FC_CUDA(launch_pdl(step_advance_kernel, dim3(1), dim3(1), 0, st, state));
+    ++g_launches;
     return FC_OK;
 }
 

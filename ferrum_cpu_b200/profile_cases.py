@@ -3,6 +3,8 @@
     python -m ferrum_cpu_b200.profile_cases decode [--tokens 8] [--model small]
     python -m ferrum_cpu_b200.profile_cases score  [--windows 4] [--model small]
     python -m ferrum_cpu_b200.profile_cases linear --m 1 --k 768 --n 50257 [--reps 3]
+    python -m ferrum_cpu_b200.profile_cases llama-decode [--model llama-1b] [--tokens 64]
+    python -m ferrum_cpu_b200.profile_cases llama-score  [--model llama-1b] [--windows 2] [--math 1]
 
 Each case runs the same kernels as the benchmark on the same seeded synthetic model, but on a
 few tokens / windows so that a multi-pass capture ends by itself. Prints CUDA-event times.
@@ -19,7 +21,7 @@ from ferrum_cpu_b200 import synth
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["decode", "score", "linear"])
+    ap.add_argument("case", choices=["decode", "score", "linear", "llama-decode", "llama-score"])
     ap.add_argument("--model", default="small")
     ap.add_argument("--tokens", type=int, default=8)
     ap.add_argument("--prompt", type=int, default=32)
@@ -52,6 +54,8 @@ def main():
             print(f"linear M={a.m} K={a.k} N={a.n}: {ms * 1e3:.1f} us, {byts / ms / 1e6:.1f} GB/s, "
                   f"{2 * a.m * a.k * a.n / ms / 1e9:.2f} TFLOP/s")
         return
+    if a.case.startswith("llama"):
+        return llama_case(a)
     sm = synth.named(a.model, seed=0, math_mode=a.math)
     V, T = sm.dims[5], sm.dims[4]
     gm = fcb.CudaSlm(sm.config, sm.weights)
@@ -86,6 +90,37 @@ def main():
             scores, _ = gm.score_sequences(ids, batch_windows=a.windows)
             print(f"score {a.windows} x {T}: device {gm.last_score_ms:.2f} ms, "
                   f"{a.windows * T / gm.last_score_ms * 1e3:.0f} positions/s, launches {fcb.take_launch_count()}")
+    gm.close()
+
+
+def llama_case(a):
+    from ferrum_cpu_b200.engine import sampling
+    from ferrum_cpu_b200.llama import CudaLlama
+    name = a.model if a.model.startswith("llama") else "llama-1b"
+    sm = synth.llama_named(name, seed=0, math_mode=a.math)
+    c = sm.dims
+    gm = CudaLlama.from_synth(sm)
+    if a.case == "llama-decode":
+        prompt = synth.token_ids(0, a.prompt, c["vocab"])
+        cache = gm.new_cache()
+        kvd = c["n_kv_head"] * c["head_dim"]
+        for i in range(a.reps):
+            toks, _ = gm.generate(prompt, a.tokens, sampling(temperature=0.0), cache=cache)
+            us = cache.last_decode_ms / a.tokens * 1e3
+            # bytes one token streams: Q8_0 matrices once + the f32 KV rows of the mean position
+            kv = c["n_layer"] * 2 * (a.prompt + a.tokens / 2) * kvd * 4
+            print(f"{name} decode {a.tokens} tokens: device {us:.1f} us/token, {1e6 / us:.0f} tokens/s, "
+                  f"{(sm.q8_weight_bytes + kv) / us / 1e3:.0f} GB/s algorithmic, launches {fcb.take_launch_count()}")
+    else:
+        T = min(c["ctx"], 1024)
+        ids = synth.token_ids(1, a.windows * T, c["vocab"]).reshape(a.windows, T)
+        qd = c["n_head"] * c["head_dim"]
+        flop = 2 * sm.q8_weight_bytes * 32 / 34 + c["n_layer"] * 4 * qd * (T + 1) / 2
+        for i in range(a.reps):
+            gm.score_sequences(ids, batch_windows=a.windows)
+            ms = gm.last_score_ms
+            print(f"{name} score {a.windows} x {T}: device {ms:.2f} ms, {a.windows * T / ms * 1e3:.0f} positions/s, "
+                  f"{flop * a.windows * T / ms / 1e9:.1f} TFLOP/s algorithmic, launches {fcb.take_launch_count()}")
     gm.close()
 
 

@@ -114,6 +114,8 @@ LLAMA_SHAPES = {
     "llama-mini": (4096, 256, 4, 8, 2, 32, 704, 256),
     # the shape of a 1B-class GGUF (Llama-3.2-1B: 16 layers, 32 query / 8 key-value heads of 64)
     "llama-1b": (32000, 2048, 16, 32, 8, 64, 8192, 2048),
+    # the same depth and head layout at a quarter of the width: what a step costs when the weights are small
+    "llama-narrow": (32000, 512, 16, 8, 2, 64, 2048, 2048),
 }
 
 
