@@ -227,9 +227,8 @@ int launch_step(fc_llama_cache* s, int with_head) {
         float* vc = s->vc + l * layer_stride;
         // RMSNorm rides in the prologue of the projection that reads it, SwiGLU in the epilogue of gate/up
         FC_TRY(launch_gemv_q8_stream(L.qkv, s->x, L.attn_norm, c.norm_eps, L.qkv_b, nullptr, EPI_NONE, s->qkv, s->state, s->status, st));
-        FC_TRY(launch_llama_rope_store(s->qkv, c.n_head, c.n_kv_head, c.head_dim, c.rope_dim, c.rope_type == FC_ROPE_NEOX, m->ftab,
-                                       m->inv_linear, kc, vc, s->state, st));
-        FC_TRY(launch_attn_decode_gqa(s->qkv, kc, vc, c.n_head, c.n_kv_head, c.head_dim, c.ctx, s->state, s->att, st));
+        FC_TRY(launch_llama_attn_decode(s->qkv, c.n_head, c.n_kv_head, c.head_dim, c.rope_dim, c.rope_type == FC_ROPE_NEOX, m->ftab,
+                                        m->inv_linear, kc, vc, c.ctx, s->state, s->att, st));
         FC_TRY(launch_gemv_q8_stream(L.wo, s->att, nullptr, 0.0f, nullptr, s->x, EPI_NONE, s->x, s->state, s->status, st));
         FC_TRY(launch_gemv_q8_stream(L.gateup, s->x, L.ffn_norm, c.norm_eps, nullptr, nullptr, EPI_SWIGLU, s->hid, s->state, s->status, st));
         FC_TRY(launch_gemv_q8_stream(L.down, s->hid, nullptr, 0.0f, nullptr, s->x, EPI_NONE, s->x, s->state, s->status, st));

@@ -176,6 +176,123 @@ int launch_llama_rope_store(float* qkv, int n_q, int n_kv, int hd, int rope_dim,
     return FC_OK;
 }
 
+// Decode attention with the rotation folded in (Attention::project + forward_one + attend,
+// llm.rs:276-358): one block per query head. The block rotates its query head and the key head
+// of its group for the current position into shared memory, the first head of a group appends
+// the rotated key and the value row to the caches, and the scores run over the cached rows plus
+// that new row — so no other block's write is ever read.
+__global__ void __launch_bounds__(256) llama_attn_decode_kernel(const float* __restrict__ qkv, int n_q, int n_kv, int hd, int half,
+                                                                int neox, const float2* __restrict__ ftab, float inv_linear,
+                                                                float* __restrict__ kc, float* __restrict__ vc, int ctx,
+                                                                const StepState* st, float* __restrict__ out) {
+    extern __shared__ float sm[];   // scores[ctx] | q[hd] | k[hd] | v[hd] | red[64] | part[(256 / hd) * hd]
+    pdl_trigger();
+    pdl_wait();
+    if (st->done | st->error) return;
+    const int pos = st->pos, len = pos + 1, kv_dim = n_kv * hd, q_dim = n_q * hd;
+    const int h = blockIdx.x, group = n_q / n_kv, kvh = h / group;
+    float* sc = sm;
+    float* qh = sm + ((ctx + 3) & ~3);      // 16-byte aligned: read as float4
+    float* kh = qh + hd;
+    float* vh = kh + hd;
+    float* red = vh + hd;
+    float* part = red + 64;
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5, nw = blockDim.x >> 5;
+    const float* qsrc = qkv + (size_t)h * hd;
+    const float* ksrc = qkv + q_dim + (size_t)kvh * hd;
+    const float* vsrc = qkv + q_dim + kv_dim + (size_t)kvh * hd;
+    // threads 0..hd-1 build q, hd..2hd-1 build k (rotated pairs, then the unrotated tail)
+    for (int u = tid; u < 2 * hd; u += blockDim.x) {
+        const bool is_k = u >= hd;
+        const int t = is_k ? u - hd : u;
+        const float* src = is_k ? ksrc : qsrc;
+        float* dst = is_k ? kh : qh;
+        if (t < half) {
+            const int ia = neox ? t : 2 * t, ib = neox ? t + half : 2 * t + 1;
+            float s, c;
+            sincosf(rope_angle(pos, ftab[t], inv_linear), &s, &c);
+            const float a = src[ia], b = src[ib];
+            dst[ia] = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s));
+            dst[ib] = __fadd_rn(__fmul_rn(a, s), __fmul_rn(b, c));
+        } else if (t >= 2 * half) {
+            dst[t] = src[t];
+        }
+    }
+    for (int c = tid; c < hd; c += blockDim.x) vh[c] = vsrc[c];
+    __syncthreads();
+    float* krow = kc + (size_t)pos * kv_dim + (size_t)kvh * hd;
+    float* vrow = vc + (size_t)pos * kv_dim + (size_t)kvh * hd;
+    if (h == kvh * group)
+        for (int c = tid; c < hd; c += blockDim.x) { krow[c] = kh[c]; vrow[c] = vh[c]; }
+    const float scale = 1.0f / sqrtf((float)hd);
+    // scores: one half warp per row, float4 per lane
+    const int hw = tid >> 4, hl = tid & 15, nhw = blockDim.x >> 4;
+    const unsigned hmask = 0xFFFFu << (tid & 16);
+    float mx = -INFINITY;
+    for (int j = hw; j < len; j += nhw) {
+        const float4* kr = j == pos ? (const float4*)kh : (const float4*)(kc + (size_t)j * kv_dim + (size_t)kvh * hd);
+        float dot = 0.0f;
+        for (int c4 = hl; c4 < (hd >> 2); c4 += 16) {
+            const float4 kv = kr[c4], qv = ((const float4*)qh)[c4];
+            dot = fmaf(qv.x, kv.x, dot); dot = fmaf(qv.y, kv.y, dot); dot = fmaf(qv.z, kv.z, dot); dot = fmaf(qv.w, kv.w, dot);
+        }
+        dot += __shfl_xor_sync(hmask, dot, 8);
+        dot += __shfl_xor_sync(hmask, dot, 4);
+        dot += __shfl_xor_sync(hmask, dot, 2);
+        dot += __shfl_xor_sync(hmask, dot, 1);
+        const float s = dot * scale;
+        if (hl == 0) sc[j] = s;
+        mx = fmaxf(mx, s);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) red[wid] = mx;
+    __syncthreads();
+    mx = red[0];
+    for (int w = 1; w < nw; ++w) mx = fmaxf(mx, red[w]);
+    float s = 0.0f;
+    for (int j = tid; j < len; j += blockDim.x) {
+        const float e = expf(sc[j] - mx);
+        sc[j] = e;
+        s += e;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) red[32 + wid] = s;
+    __syncthreads();
+    float sum = 0.0f;
+    for (int w = 0; w < nw; ++w) sum += red[32 + w];
+    // out: thread (g, c) accumulates rows j = g, g + G, ... for dimension c; partials added in order
+    const int G = blockDim.x / hd;
+    const int g = tid / hd, c = tid - g * hd;
+    if (g < G) {
+        float acc = 0.0f;
+        for (int j = g; j < len; j += G) {
+            const float v = j == pos ? vh[c] : vc[(size_t)j * kv_dim + (size_t)kvh * hd + c];
+            acc = fmaf(sc[j] / sum, v, acc);
+        }
+        part[g * hd + c] = acc;
+    }
+    __syncthreads();
+    if (tid < hd) {
+        float acc = 0.0f;
+        for (int gg = 0; gg < G; ++gg) acc += part[gg * hd + tid];
+        out[(size_t)h * hd + tid] = acc;
+    }
+}
+int launch_llama_attn_decode(const float* qkv, int n_q, int n_kv, int hd, int rope_dim, int neox, const float2* ftab, float inv_linear,
+                             float* kc, float* vc, int ctx, const StepState* state, float* out, cudaStream_t st) {
+    if (hd > 256 || hd % 4) return fail(FC_E_SHAPE, "head_dim %d must be a multiple of 4, at most 256", hd);
+    const int threads = 256;
+    const size_t smem = (size_t)(((ctx + 3) & ~3) + 3 * hd + 64 + (threads / hd) * hd) * sizeof(float);
+    if (smem > 200 * 1024) return fail(FC_E_SHAPE, "context %d exceeds what the decode attention holds in shared memory", ctx);
+    if (smem > 48 * 1024) FC_CUDA(cudaFuncSetAttribute(llama_attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    FC_CUDA(launch_pdl(llama_attn_decode_kernel, dim3(n_q), dim3(threads), smem, st, qkv, n_q, n_kv, hd, rope_dim / 2, neox, ftab,
+                       inv_linear, kc, vc, ctx, state, out));
+    ++g_launches;
+    return FC_OK;
+}
+
 // --------------------------------------------------------------------------------- SwiGLU
 // FeedForward::forward (llm.rs:417-428): h = (g / (1 + exp(-g))) * u on rows of interleaved
 // (gate_i, up_i) pairs, the row order of the fused gate/up matrix.

@@ -13,6 +13,10 @@ int launch_llama_rope_rows(float* qkv, int R, int ld, int T, int n_q, int n_kv, 
                            const float2* ftab, float inv_linear, cudaStream_t st);
 int launch_llama_rope_store(float* qkv, int n_q, int n_kv, int hd, int rope_dim, int neox, const float2* ftab, float inv_linear,
                             float* kc, float* vc, const StepState* state, cudaStream_t st);
+// Rotation, cache append and single-query grouped attention in one kernel: q | k | v fused row
+// in, attention output [n_q * hd] out.
+int launch_llama_attn_decode(const float* qkv, int n_q, int n_kv, int hd, int rope_dim, int neox, const float2* ftab, float inv_linear,
+                             float* kc, float* vc, int ctx, const StepState* state, float* out, cudaStream_t st);
 int launch_llama_swiglu(const float* gu, int rows, int F, float* h, const StepState* state, cudaStream_t st);
 int launch_llama_score_rows(const float* logits, int ldl, int V, const int* targets, int R, double* logprob, uint8_t* is_greedy,
                             cudaStream_t st);
