@@ -154,9 +154,10 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", choices=["decode", "score", "both", "streams-medium"], default="both",
+    ap.add_argument("--workload", choices=["decode", "score", "both", "streams-medium", "llama-1b"], default="both",
                     help="both: configs[1] decode (+ 8 side-by-side streams) and configs[2] scoring; streams-medium: the decode "
-                         "half of configs[4] on the GPT-2-medium shape (64 streams split over the ranks)")
+                         "half of configs[4] on the GPT-2-medium shape (64 streams split over the ranks); llama-1b: greedy decode and "
+                         "one-window scoring of a Llama-3.2-1B-shaped Q8_0 model (the imported-model path, replicas per rank)")
     ap.add_argument("--score-steps", type=int, default=2)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -224,6 +225,63 @@ def main():
                                                      "%d streams per GPU, up to 8 side by side; prompts primed as one batch per wave; device time "
                                                      "includes the primes" % (a1 - a0)}}))
         gmm.close()
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    if args.workload == "llama-1b":
+        # The imported Llama / Qwen path (llm.rs) on a 1B-class shape: batch-1 greedy decode and window scoring.
+        from ferrum_cpu_b200.engine import sampling
+        from ferrum_cpu_b200.llama import CudaLlama
+        sml = synth.llama_named("llama-1b", seed=0, math_mode=fcb.FC_MATH_BF16X3)
+        c = sml.dims
+        gml = CudaLlama.from_synth(sml, device=local)
+        cache = gml.new_cache()
+        prompt = synth.token_ids(rank, PROMPT, c["vocab"])
+        greedy = sampling(temperature=0.0)
+        for _ in range(args.warmup):
+            gml.generate(prompt, NEW_TOKENS, greedy, cache=cache)
+        fcb.take_launch_count()
+        ms, wall = [], []
+        barrier()
+        for _ in range(args.steps):
+            t0 = time.perf_counter()
+            gml.generate(prompt, NEW_TOKENS, greedy, cache=cache)     # host ids in, host ids out
+            wall.append(time.perf_counter() - t0)
+            ms.append(cache.last_decode_ms)
+        barrier()
+        launches = fcb.take_launch_count()
+        step_ms = max_over_ranks(sum(ms) / len(ms))
+        wall_s = max_over_ranks(sum(wall) / len(wall))
+        kvd = c["n_kv_head"] * c["head_dim"]
+        kv_bytes = c["n_layer"] * 2 * (PROMPT + NEW_TOKENS / 2) * kvd * 4
+        per_token = sml.q8_weight_bytes + kv_bytes + c["n_layer"] * 2 * c["d_model"] * 4
+        T = 1024
+        ids = synth.token_ids(100 + rank, 4 * T, c["vocab"]).reshape(4, T)
+        gml.score_sequences(ids, batch_windows=4)
+        sms_ = []
+        for _ in range(max(1, args.score_steps)):
+            gml.score_sequences(ids, batch_windows=4)
+            sms_.append(gml.last_score_ms)
+        score_ms = max_over_ranks(sum(sms_) / len(sms_))
+        qd = c["n_head"] * c["head_dim"]
+        flop_pos = 2 * sml.q8_weight_bytes * 32 / 34 + c["n_layer"] * 4 * qd * (T + 1) / 2
+        if rank == 0:
+            gbs = per_token * NEW_TOKENS / (step_ms / 1e3) / 1e9
+            print(json.dumps({
+                "metric": "Q8_0 Llama-1B-shaped batch-1 greedy decode tokens/s", "value": world * NEW_TOKENS / (step_ms / 1e3),
+                "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms,
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": "Llama-3.2-1B shape: L16 d2048 H32 KV8 hd64 F8192 ctx2048 V32000, Q8_0, %d-token prompt, %d greedy "
+                                       "tokens, one replica per GPU; weights (1.1 GB) exceed the L2" % (PROMPT, NEW_TOKENS)},
+                "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s", "frac": gbs / hbm_peak, "traffic": None,
+                             "peak_kind": peak_kind, "algorithmic_bytes_per_token": per_token},
+                "e2e": {"value": world * NEW_TOKENS / wall_s, "unit": "tokens/s", "h2d_bytes_per_step": PROMPT * 4 + 8,
+                        "d2h_bytes_per_step": NEW_TOKENS * 4 + 8 + 32, "note": "includes priming the prompt token by token"},
+                "gpu_launches": int(launches),
+                "scoring": {"value": world * 4 * T / (score_ms / 1e3), "unit": "positions/s", "ms_per_step": score_ms,
+                            "tflops_algorithmic": flop_pos * 4 * T / (score_ms / 1e3) / 1e12,
+                            "workload": "4 windows x 1024 ids, tcgen05 bf16x3 projections, exact log-softmax tail"}}))
+        gml.close()
         if world > 1:
             dist.destroy_process_group()
         return
