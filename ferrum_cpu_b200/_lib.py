@@ -51,6 +51,7 @@ class FcLlamaWeights(C.Structure):
 
 
 FC_ROPE_NORM, FC_ROPE_NEOX = 0, 1
+FC_Q_INT8, FC_Q_INT4 = 0, 1
 
 
 class FcScore(C.Structure):
@@ -111,6 +112,13 @@ SIGNATURES = {
     "fc_llama_generate": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.POINTER(FcSampling), C.c_void_p, C.c_int,
                                     C.POINTER(C.c_uint64), C.c_void_p, C.c_void_p, C.POINTER(C.c_int)]),
     "fc_llama_last_decode_ms": (C.c_float, [C.c_void_p]),
+    "fc_rowq_packed_len": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
+    "fc_rowq_from_f32": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
+    "fc_rowq_to_f32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "fc_rowq_upload": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_void_p)]),
+    "fc_rowq_free": (None, [C.c_void_p]),
+    "fc_rowq_linear": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int]),
+    "fc_rowq_linear_dev": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "fc_take_launch_count": (C.c_int64, []),
     "fc_last_decode_ms": (C.c_float, [C.c_void_p]),
     "fc_last_score_ms": (C.c_float, [C.c_void_p]),

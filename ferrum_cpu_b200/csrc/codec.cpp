@@ -123,4 +123,61 @@ void fc_rng_fill_ids(uint64_t* state, int32_t vocab, size_t n, int32_t* out) {
     *state = s;
 }
 
+
+// ---- per-row-scale int8 / int4 (quant.rs:122-263) -------------------------------------------
+size_t fc_rowq_packed_len(int rows, int cols, int kind) {
+    if (rows <= 0 || cols <= 0) return 0;
+    return (size_t)rows * (size_t)(kind == FC_Q_INT4 ? (cols + 1) / 2 : cols);
+}
+
+// QWeight::from_f32: scale = max|v| / 127 (int8_scale, quant.rs:17-19) or / 7 (quant.rs:189-190);
+// level = round_half_away(v / scale) clamped to the symmetric range; a zero row has scale 0.
+int fc_rowq_from_f32(const float* data, int rows, int cols, int kind, float* scales, uint8_t* q) {
+    if (!data || !scales || !q) return FC_E_ARG;
+    if (rows <= 0 || cols <= 0 || (kind != FC_Q_INT8 && kind != FC_Q_INT4)) return FC_E_SHAPE;
+    const float qmax = kind == FC_Q_INT8 ? 127.0f : 7.0f;
+    const int half = (cols + 1) / 2;
+    const size_t rb = kind == FC_Q_INT8 ? (size_t)cols : (size_t)half;
+    std::memset(q, 0, (size_t)rows * rb);
+    for (int r = 0; r < rows; ++r) {
+        const float* row = data + (size_t)r * cols;
+        float amax = 0.0f;
+        for (int c = 0; c < cols; ++c) amax = std::fmax(amax, std::fabs(row[c]));
+        const float scale = amax / qmax;
+        scales[r] = scale;
+        const float inv = scale > 0.0f ? 1.0f / scale : 0.0f;
+        uint8_t* dst = q + (size_t)r * rb;
+        for (int c = 0; c < cols; ++c) {
+            float lv = std::round(row[c] * inv);
+            lv = lv < -qmax ? -qmax : (lv > qmax ? qmax : lv);
+            if (!(lv == lv)) lv = 0.0f;                         // `NaN as i8` is 0 in Rust
+            const int qi = (int)lv;
+            if (kind == FC_Q_INT8) dst[c] = (uint8_t)(int8_t)qi;
+            else if (c < half) dst[c] = (uint8_t)((dst[c] & 0xF0) | (qi & 0x0F));
+            else dst[c - half] = (uint8_t)((dst[c - half] & 0x0F) | ((qi & 0x0F) << 4));
+        }
+    }
+    return FC_OK;
+}
+
+int fc_rowq_to_f32(const uint8_t* q, const float* scales, int rows, int cols, int kind, float* out) {
+    if (!q || !scales || !out) return FC_E_ARG;
+    if (rows <= 0 || cols <= 0 || (kind != FC_Q_INT8 && kind != FC_Q_INT4)) return FC_E_SHAPE;
+    const int half = (cols + 1) / 2;
+    const size_t rb = kind == FC_Q_INT8 ? (size_t)cols : (size_t)half;
+    for (int r = 0; r < rows; ++r) {
+        const uint8_t* src = q + (size_t)r * rb;
+        for (int c = 0; c < cols; ++c) {
+            int lv;
+            if (kind == FC_Q_INT8) lv = (int8_t)src[c];
+            else {
+                const uint8_t nib = c < half ? (src[c] & 0x0F) : (src[c - half] >> 4);
+                lv = (int8_t)(nib << 4) >> 4;                   // nibble_to_i8, quant.rs:221-223
+            }
+            out[(size_t)r * cols + c] = (float)lv * scales[r];
+        }
+    }
+    return FC_OK;
+}
+
 }  // extern "C"

@@ -75,6 +75,67 @@ def q8_0_linear(x, wq, bias, n_out, device=0, math_mode=_lib.FC_MATH_FP32):
     return y
 
 
+def rowq_from_f32(data, kind):
+    """QWeight::from_f32 (quant.rs:164-212) on the host: (packed bytes, scales) of a [rows][cols] matrix."""
+    data = np.ascontiguousarray(data, dtype=np.float32)
+    rows, cols = data.shape
+    q = np.zeros(_lib.lib().fc_rowq_packed_len(rows, cols, kind), dtype=np.uint8)
+    scales = np.zeros(rows, dtype=np.float32)
+    check(_lib.lib().fc_rowq_from_f32(_ptr(data), rows, cols, kind, _ptr(scales), _ptr(q)))
+    return q, scales
+
+
+def rowq_to_f32(q, scales, rows, cols, kind):
+    """QWeight::to_f32 (quant.rs:255-263)."""
+    q = np.ascontiguousarray(q, dtype=np.uint8)
+    scales = np.ascontiguousarray(scales, dtype=np.float32)
+    out = np.empty((rows, cols), dtype=np.float32)
+    check(_lib.lib().fc_rowq_to_f32(_ptr(q), _ptr(scales), rows, cols, kind, _ptr(out)))
+    return out
+
+
+class RowQWeight:
+    """A per-row-scale int8 / int4 QWeight resident on a GPU (quant.rs:122-146); `linear` is ops::qlinear."""
+
+    def __init__(self, q, scales, rows, cols, kind, device=0):
+        self.rows, self.cols, self.kind = rows, cols, kind
+        self._h = C.c_void_p()
+        q = np.ascontiguousarray(q, dtype=np.uint8)
+        scales = np.ascontiguousarray(scales, dtype=np.float32)
+        check(_lib.lib().fc_rowq_upload(device, _ptr(q), _ptr(scales), rows, cols, kind, C.byref(self._h)))
+
+    @classmethod
+    def from_f32(cls, data, kind, device=0):
+        data = np.ascontiguousarray(data, dtype=np.float32)
+        q, scales = rowq_from_f32(data, kind)
+        return cls(q, scales, data.shape[0], data.shape[1], kind, device)
+
+    def linear(self, x, bias):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        if x.ndim != 2 or x.shape[1] != self.rows:
+            raise FerrumCudaError(_lib.FC_E_DIM, f"qlinear: input width {x.shape[-1]} ≠ weight rows {self.rows}")
+        bias = np.ascontiguousarray(bias, dtype=np.float32)
+        if bias.size != self.cols:
+            raise FerrumCudaError(_lib.FC_E_DIM, f"qlinear: bias length {bias.size} ≠ out_features {self.cols}")
+        y = np.empty((x.shape[0], self.cols), dtype=np.float32)
+        check(_lib.lib().fc_rowq_linear(self._h, _ptr(x), _ptr(bias), _ptr(y), x.shape[0]))
+        return y
+
+    def linear_dev(self, x_ptr, bias_ptr, y_ptr, m, stream=None):
+        check(_lib.lib().fc_rowq_linear_dev(self._h, C.c_void_p(x_ptr), C.c_void_p(bias_ptr), C.c_void_p(y_ptr), m, stream))
+
+    def close(self):
+        if self._h:
+            _lib.lib().fc_rowq_free(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 class QWeight:
     """One Q8_0 matrix resident on a GPU (the packed-weight seam of layer/linear.rs:21-35)."""
 

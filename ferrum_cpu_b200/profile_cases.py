@@ -3,6 +3,7 @@
     python -m ferrum_cpu_b200.profile_cases decode [--tokens 8] [--model small]
     python -m ferrum_cpu_b200.profile_cases score  [--windows 4] [--model small]
     python -m ferrum_cpu_b200.profile_cases linear --m 1 --k 768 --n 50257 [--reps 3]
+    python -m ferrum_cpu_b200.profile_cases rowq --m 1 --k 2048 --n 8192 --kind 1 [--reps 3]
     python -m ferrum_cpu_b200.profile_cases llama-decode [--model llama-1b] [--tokens 64]
     python -m ferrum_cpu_b200.profile_cases llama-score  [--model llama-1b] [--windows 2] [--math 1]
 
@@ -21,7 +22,7 @@ from ferrum_cpu_b200 import synth
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["decode", "score", "linear", "llama-decode", "llama-score"])
+    ap.add_argument("case", choices=["decode", "score", "linear", "rowq", "llama-decode", "llama-score"])
     ap.add_argument("--model", default="small")
     ap.add_argument("--tokens", type=int, default=8)
     ap.add_argument("--prompt", type=int, default=32)
@@ -31,6 +32,7 @@ def main():
     ap.add_argument("--n", type=int, default=50257)
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--math", type=int, default=0)
+    ap.add_argument("--kind", type=int, default=0, help="rowq: 0 int8, 1 int4")
     ap.add_argument("--trace", action="store_true", help="decode: print the phase timeline of one token")
     ap.add_argument("--mode", type=int, default=0, help="decode: 0 persistent kernel, 1 one kernel per operation")
     a = ap.parse_args()
@@ -52,6 +54,28 @@ def main():
             ms = e0.elapsed_time(e1)
             byts = a.n * a.k * 34 / 32 + 4 * a.m * a.k + 4 * a.m * a.n
             print(f"linear M={a.m} K={a.k} N={a.n}: {ms * 1e3:.1f} us, {byts / ms / 1e6:.1f} GB/s, "
+                  f"{2 * a.m * a.k * a.n / ms / 1e9:.2f} TFLOP/s")
+        return
+    if a.case == "rowq":
+        import torch
+        from ferrum_cpu_b200.engine import RowQWeight
+        w = synth.Rng(21).normal(a.k * a.n, 0.02).reshape(a.k, a.n)
+        qw = RowQWeight.from_f32(w, a.kind)
+        x = torch.randn(a.m, a.k, device="cuda")
+        bias = torch.zeros(a.n, device="cuda")
+        y = torch.empty(a.m, a.n, device="cuda")
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+        st = torch.cuda.current_stream().cuda_stream
+        for i in range(a.reps):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            qw.linear_dev(x.data_ptr(), bias.data_ptr(), y.data_ptr(), a.m, C.c_void_p(st))
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1)
+            byts = a.k * a.n / (2 if a.kind else 1) + 4 * a.k + 4 * a.m * (a.k + a.n)
+            print(f"rowq {'int4' if a.kind else 'int8'} M={a.m} K={a.k} N={a.n}: {ms * 1e3:.1f} us, {byts / ms / 1e6:.1f} GB/s, "
                   f"{2 * a.m * a.k * a.n / ms / 1e9:.2f} TFLOP/s")
         return
     if a.case.startswith("llama"):

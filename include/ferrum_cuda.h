@@ -326,6 +326,30 @@ int fc_llama_generate(fc_llama_cache* c, const int32_t* prompt, int n, int max_n
                       int32_t* out, int* n_out);
 float fc_llama_last_decode_ms(const fc_llama_cache* c);
 
+/* ---- per-row-scale int8 / int4 weights (quant.rs:122-263 QWeight, ops.rs:268-377 qlinear) ---- */
+/* The in-memory quantised weight of the reference: [rows = in_features][cols = out_features]
+ * row-major, one f32 scale per row. Int8: one i8 per weight. Int4: ceil(cols/2) bytes per row in
+ * the split-half layout — byte b holds column b in its low nibble and column half + b in its
+ * high nibble (quant.rs:137-144). */
+#define FC_Q_INT8 0
+#define FC_Q_INT4 1
+/* Bytes of the packed matrix (QKind::packed_len). */
+size_t fc_rowq_packed_len(int rows, int cols, int kind);
+/* QWeight::from_f32 (quant.rs:164-212) on the host: scales [rows], q [fc_rowq_packed_len]. */
+int fc_rowq_from_f32(const float* data, int rows, int cols, int kind, float* scales, uint8_t* q);
+/* QWeight::to_f32 (quant.rs:226-263): out [rows][cols]. */
+int fc_rowq_to_f32(const uint8_t* q, const float* scales, int rows, int cols, int kind, float* out);
+typedef struct fc_rowq fc_rowq;   /* one QWeight resident on a GPU */
+int fc_rowq_upload(int device, const uint8_t* q, const float* scales, int rows, int cols, int kind, fc_rowq** out);
+void fc_rowq_free(fc_rowq* w);
+/* ops::qlinear (ops.rs:316-377): y[M][cols] = bias + (x[M][rows] * scale) · levels, the scale
+ * folded into the activations, never expanding the weights. Host buffers; bias [cols] is
+ * required as in the reference. FC_E_DIM on a width mismatch is the caller's check (rows and
+ * cols are the handle's). */
+int fc_rowq_linear(const fc_rowq* w, const float* x, const float* bias, float* y, int M);
+/* The same on device pointers, asynchronous on `stream` (a cudaStream_t, or NULL). */
+int fc_rowq_linear_dev(const fc_rowq* w, const float* x_dev, const float* bias_dev, float* y_dev, int M, void* stream);
+
 /* ---- introspection used by the benchmark ----------------------------------------- */
 /* Kernel launches issued by this library on the calling thread since the last call
  * (returns the count and resets it). */

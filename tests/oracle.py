@@ -79,6 +79,11 @@ def lib():
         L.fo_llama_generate.restype = C.c_int
         L.fo_llama_generate.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_float, C.c_int, C.c_float, C.c_float,
                                         C.c_void_p, C.c_int, C.POINTER(C.c_uint64), C.c_void_p]
+        L.fo_nibble_to_i8.restype, L.fo_nibble_to_i8.argtypes = C.c_int, [C.c_int]
+        L.fo_rowq_packed_len.restype, L.fo_rowq_packed_len.argtypes = C.c_size_t, [C.c_int, C.c_int, C.c_int]
+        L.fo_rowq_from_f32.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+        L.fo_rowq_to_f32.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
+        L.fo_rowq_linear.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
         _lib = L
     return _lib
 
@@ -345,3 +350,28 @@ class OracleLlama:
 
     def __del__(self):
         self.close()
+
+
+# ------------------------------------------------- per-row-scale QWeight (quant.rs, ops.rs)
+def rowq_from_f32(data, kind):
+    data = f32(data)
+    rows, cols = data.shape
+    q = np.zeros(lib().fo_rowq_packed_len(rows, cols, kind), dtype=np.uint8)
+    scales = np.zeros(rows, dtype=np.float32)
+    lib().fo_rowq_from_f32(_ptr(data), rows, cols, kind, _ptr(scales), _ptr(q))
+    return q, scales
+
+
+def rowq_to_f32(q, scales, rows, cols, kind):
+    out = np.empty((rows, cols), dtype=np.float32)
+    lib().fo_rowq_to_f32(_ptr(q), _ptr(scales), rows, cols, kind, _ptr(out))
+    return out
+
+
+def rowq_linear(x, q, scales, kind, bias, n):
+    x = f32(x)
+    m, k = x.shape
+    bias = f32(bias)
+    y = np.empty((m, n), dtype=np.float32)
+    lib().fo_rowq_linear(_ptr(x), _ptr(q), _ptr(scales), kind, _ptr(bias), m, k, n, _ptr(y))
+    return y
