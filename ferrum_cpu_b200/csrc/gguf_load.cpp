@@ -38,11 +38,12 @@ struct Meta {
     uint32_t type = 0;
     uint64_t u = 0;
     double f = 0.0;
+    std::string s;                // VT_STRING values shorter than 256 bytes (names, not vocabularies)
 };
 
 struct File {
     std::vector<uint8_t> bytes;
-    std::map<std::string, Meta> meta;        // scalar metadata only (strings and arrays are skipped)
+    std::map<std::string, Meta> meta;        // scalars and short strings (arrays are skipped)
     std::map<std::string, Tensor> tensors;
     uint64_t data = 0;                        // absolute offset of the data section
 };
@@ -95,7 +96,7 @@ bool read_value(Cursor& c, uint32_t type, Meta* out) {
         case VT_U64: out->u = c.get<uint64_t>(); break;
         case VT_I64: out->u = (uint64_t)c.get<int64_t>(); break;
         case VT_F64: out->f = c.get<double>(); break;
-        case VT_STRING: c.str(); break;
+        case VT_STRING: out->s = c.str(); if (out->s.size() >= 256) out->s.clear(); break;
         case VT_ARRAY: {
             const uint32_t et = c.get<uint32_t>();
             const uint64_t count = c.get<uint64_t>();
@@ -147,7 +148,7 @@ int read_file(const char* path, File* f) {
         const uint32_t type = c.get<uint32_t>();
         Meta m;
         if (!read_value(c, type, &m)) return fail(FC_E_FORMAT, "GGUF metadata entry %llu (%s) is malformed", (unsigned long long)i, key.c_str());
-        if (type != VT_STRING && type != VT_ARRAY) f->meta[key] = m;
+        if (type != VT_ARRAY) f->meta[key] = m;
     }
     for (uint64_t i = 0; i < n_tensors; ++i) {
         const std::string name = c.str();
@@ -178,7 +179,7 @@ int meta_int(const File& f, const char* key, int* out) {
     auto it = f.meta.find(key);
     if (it == f.meta.end()) return fail(FC_E_FORMAT, "GGUF metadata key %s is missing", key);
     const Meta& m = it->second;
-    if (m.type == VT_F32 || m.type == VT_F64 || m.type == VT_BOOL || m.u > (1u << 30)) return fail(FC_E_FORMAT, "GGUF metadata key %s is not a small integer", key);
+    if (m.type == VT_F32 || m.type == VT_F64 || m.type == VT_BOOL || m.type == VT_STRING || m.u > (1u << 30)) return fail(FC_E_FORMAT, "GGUF metadata key %s is not a small integer", key);
     *out = (int)m.u;
     return FC_OK;
 }
@@ -295,6 +296,148 @@ int parse_model(const File& f, const int32_t* row_perm, int n_perm, int math_mod
     return FC_OK;
 }
 
+
+// ---------------------------------------------------------------- llama / qwen2 files
+// Gguf::load_llama_prec (gguf/llama.rs:171-339): metadata keys, defaults and refusals as there;
+// the projections must be Q8_0 and stay packed, the norms F32.
+struct ParsedLlama {
+    fc_llama_config cfg{};
+    std::vector<fc_llama_layer> layers;
+    fc_llama_weights w{};
+    std::vector<std::vector<float>> owned_f32;
+};
+
+bool has_tensor(const File& f, const std::string& name) { return f.tensors.find(name) != f.tensors.end(); }
+
+int opt_int(const File& f, const std::string& key, int fallback, int* out) {
+    if (f.meta.find(key) == f.meta.end()) { *out = fallback; return FC_OK; }
+    return meta_int(f, key.c_str(), out);
+}
+
+double meta_f32_or(const File& f, const std::string& key, double fallback) {
+    auto it = f.meta.find(key);
+    if (it == f.meta.end()) return fallback;
+    const Meta& m = it->second;
+    if (m.type == VT_F32 || m.type == VT_F64) return m.f;
+    if (m.type == VT_STRING || m.type == VT_BOOL) return fallback;
+    return (double)(int64_t)m.u;
+}
+
+int f32_owned(const File& f, ParsedLlama* p, const std::string& name, uint64_t n, const float** out) {
+    const uint8_t* b = nullptr;
+    const int rc = tensor(f, name, T_F32, n, 1, &b);
+    if (rc != FC_OK) return rc;
+    p->owned_f32.emplace_back((size_t)n);
+    memcpy(p->owned_f32.back().data(), b, (size_t)n * 4);
+    *out = p->owned_f32.back().data();
+    return FC_OK;
+}
+
+int parse_llama(const File& f, int math_mode, int ctx_cap, ParsedLlama* p) {
+    auto at = f.meta.find("general.architecture");
+    if (at == f.meta.end() || at->second.type != VT_STRING) return fail(FC_E_FORMAT, "GGUF missing general.architecture");
+    const std::string arch = at->second.s;
+    if (arch != "llama" && arch != "qwen2")
+        return fail(FC_E_FORMAT, "architecture '%s' is not supported by load_llama (llama / qwen2 only)", arch.c_str());
+    auto key = [&](const char* k) { return arch + "." + k; };
+    int d = 0, L = 0, H = 0, KV = 0, F = 0, hd = 0, rope_dim = 0, ctx = 0;
+    int rc;
+    if ((rc = meta_int(f, key("embedding_length").c_str(), &d)) != FC_OK) return rc;
+    if ((rc = meta_int(f, key("block_count").c_str(), &L)) != FC_OK) return rc;
+    if ((rc = meta_int(f, key("attention.head_count").c_str(), &H)) != FC_OK) return rc;
+    if ((rc = opt_int(f, key("attention.head_count_kv"), H, &KV)) != FC_OK) return rc;
+    if ((rc = meta_int(f, key("feed_forward_length").c_str(), &F)) != FC_OK) return rc;
+    if (d <= 0 || L <= 0 || H <= 0 || F <= 0) return fail(FC_E_FORMAT, "%s.* dimensions must be positive", arch.c_str());
+    if ((size_t)L > f.tensors.size()) return fail(FC_E_FORMAT, "block_count %d exceeds the %zu tensors of the file", L, f.tensors.size());
+    if ((rc = opt_int(f, key("attention.key_length"), d / H, &hd)) != FC_OK) return rc;
+    if ((rc = opt_int(f, key("rope.dimension_count"), hd, &rope_dim)) != FC_OK) return rc;
+    if ((rc = opt_int(f, key("context_length"), 2048, &ctx)) != FC_OK) return rc;
+    const double rope_base = meta_f32_or(f, key("rope.freq_base"), 10000.0);
+    const double eps = meta_f32_or(f, key("attention.layer_norm_rms_epsilon"), 1e-5);
+    // rope_scaling (gguf/llama.rs:51-103): linear (also when no type is given) and
+    // rope_freqs.weight; yarn, longrope and a non-1 attn_factor are refused
+    double factor = 1.0;
+    {
+        auto it = f.meta.find(key("rope.scaling.factor"));
+        if (it == f.meta.end()) it = f.meta.find(key("rope.scale_linear"));
+        if (it != f.meta.end()) factor = meta_f32_or(f, it->first, 1.0);
+        if (factor == 0.0) factor = 1.0;
+        std::string ty = "linear";
+        auto tt = f.meta.find(key("rope.scaling.type"));
+        if (tt != f.meta.end()) {
+            if (tt->second.type != VT_STRING) return fail(FC_E_FORMAT, "'%s' is not a string", key("rope.scaling.type").c_str());
+            ty = tt->second.s;
+        }
+        if (ty == "none") {
+            if (factor != 1.0) return fail(FC_E_FORMAT, "'%s' is \"none\" but the scaling factor is %g", key("rope.scaling.type").c_str(), factor);
+        } else if (ty != "linear") {
+            return fail(FC_E_FORMAT, "RoPE scaling type '%s' is not supported: none, linear and rope_freqs.weight are (yarn and longrope are refused)", ty.c_str());
+        }
+        const double attn = meta_f32_or(f, key("rope.scaling.attn_factor"), 1.0);
+        if (attn != 1.0) return fail(FC_E_FORMAT, "RoPE scaling attn_factor %g is not supported (only 1.0)", attn);
+    }
+    if (has_tensor(f, "rope_freqs.weight")) {
+        if (rope_dim < 2) return fail(FC_E_FORMAT, "rope_freqs.weight without a rotary dimension");
+        if ((rc = f32_owned(f, p, "rope_freqs.weight", (uint64_t)rope_dim / 2, &p->w.rope_freqs)) != FC_OK) return rc;
+    }
+    auto te = f.tensors.find("token_embd.weight");
+    if (te == f.tensors.end()) return fail(FC_E_FORMAT, "GGUF missing token_embd.weight");
+    if (te->second.dims.size() != 2 || te->second.dims[0] != (uint64_t)d) return fail(FC_E_FORMAT, "token_embd.weight size does not match vocab x dim");
+    const uint64_t V = te->second.dims[1];
+    if (V == 0 || V > (1u << 30)) return fail(FC_E_FORMAT, "token_embd.weight size does not match vocab x dim");
+    if (d % 32 || F % 32 || ((long long)H * hd) % 32)
+        return fail(FC_E_FORMAT, "embedding_length, feed_forward_length and head_count x key_length must be multiples of 32 for Q8_0 rows");
+    const uint64_t q_dim = (uint64_t)H * hd, kv_dim = (uint64_t)KV * hd;
+    const uint8_t* b = nullptr;
+    if ((rc = tensor(f, "token_embd.weight", T_Q8_0, d, V, &b)) != FC_OK) return rc;
+    p->w.token_embd_q8 = b;
+    p->layers.resize(L);
+    for (int i = 0; i < L; ++i) {
+        fc_llama_layer& lw = p->layers[i];
+        const std::string n = "blk." + std::to_string(i) + ".";
+        // biases other than q / k / v are refused, not dropped (gguf/llama.rs:252-263)
+        for (const char* stem : {"attn_output", "ffn_gate", "ffn_up", "ffn_down"})
+            if (has_tensor(f, n + stem + ".bias"))
+                return fail(FC_E_FORMAT, "GGUF tensor '%s%s.bias' is not supported: biases are loaded only for attn_q/attn_k/attn_v", n.c_str(), stem);
+        if ((rc = f32_owned(f, p, n + "attn_norm.weight", d, &lw.attn_norm)) != FC_OK) return rc;
+        if ((rc = tensor(f, n + "attn_q.weight", T_Q8_0, d, q_dim, &b)) != FC_OK) return rc;
+        lw.wq_q8 = b;
+        if ((rc = tensor(f, n + "attn_k.weight", T_Q8_0, d, kv_dim, &b)) != FC_OK) return rc;
+        lw.wk_q8 = b;
+        if ((rc = tensor(f, n + "attn_v.weight", T_Q8_0, d, kv_dim, &b)) != FC_OK) return rc;
+        lw.wv_q8 = b;
+        if ((rc = tensor(f, n + "attn_output.weight", T_Q8_0, q_dim, d, &b)) != FC_OK) return rc;
+        lw.wo_q8 = b;
+        if (has_tensor(f, n + "attn_q.bias") && (rc = f32_owned(f, p, n + "attn_q.bias", q_dim, &lw.bq)) != FC_OK) return rc;
+        if (has_tensor(f, n + "attn_k.bias") && (rc = f32_owned(f, p, n + "attn_k.bias", kv_dim, &lw.bk)) != FC_OK) return rc;
+        if (has_tensor(f, n + "attn_v.bias") && (rc = f32_owned(f, p, n + "attn_v.bias", kv_dim, &lw.bv)) != FC_OK) return rc;
+        if ((rc = f32_owned(f, p, n + "ffn_norm.weight", d, &lw.ffn_norm)) != FC_OK) return rc;
+        if ((rc = tensor(f, n + "ffn_gate.weight", T_Q8_0, d, F, &b)) != FC_OK) return rc;
+        lw.gate_q8 = b;
+        if ((rc = tensor(f, n + "ffn_up.weight", T_Q8_0, d, F, &b)) != FC_OK) return rc;
+        lw.up_q8 = b;
+        if ((rc = tensor(f, n + "ffn_down.weight", T_Q8_0, F, d, &b)) != FC_OK) return rc;
+        lw.down_q8 = b;
+    }
+    if ((rc = f32_owned(f, p, "output_norm.weight", d, &p->w.output_norm)) != FC_OK) return rc;
+    if (has_tensor(f, "output.bias"))
+        return fail(FC_E_FORMAT, "GGUF tensor 'output.bias' is not supported: biases are loaded only for attn_q/attn_k/attn_v");
+    const bool tied = !has_tensor(f, "output.weight");
+    if (!tied) {
+        if ((rc = tensor(f, "output.weight", T_Q8_0, d, V, &b)) != FC_OK) return rc;
+        p->w.output_q8 = b;
+    }
+    p->w.layers = p->layers.data();
+    fc_llama_config& c = p->cfg;
+    c.vocab = (int)V; c.d_model = d; c.n_layer = L; c.n_head = H; c.n_kv_head = KV; c.head_dim = hd; c.d_ff = F;
+    c.rope_dim = rope_dim; c.rope_base = (float)rope_base;
+    c.rope_type = arch == "qwen2" ? FC_ROPE_NEOX : FC_ROPE_NORM;   // gguf/llama.rs:181-186
+    c.rope_linear_factor = (float)factor; c.norm_eps = (float)eps;
+    c.ctx = ctx_cap > 0 && ctx_cap < ctx ? ctx_cap : ctx;
+    c.tied = tied ? 1 : 0; c.math_mode = math_mode;
+    return FC_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -321,6 +464,30 @@ int fc_model_load_gguf(const char* path, const int32_t* row_perm, int n_perm, in
     rc = parse_model(f, row_perm, n_perm, math_mode, &p);
     if (rc != FC_OK) return rc;
     return fc_model_create(&p.cfg, &p.w, device, out);   // copies everything it needs
+}
+
+int fc_llama_gguf_probe(const char* path, fc_llama_config* out) {
+    if (!path || !out) return fail(FC_E_ARG, "fc_llama_gguf_probe: bad argument");
+    File f;
+    int rc = read_file(path, &f);
+    if (rc != FC_OK) return rc;
+    ParsedLlama p;
+    rc = parse_llama(f, FC_MATH_FP32, 0, &p);
+    if (rc != FC_OK) return rc;
+    *out = p.cfg;
+    return FC_OK;
+}
+
+int fc_llama_load_gguf(const char* path, int device, int math_mode, int ctx_cap, fc_llama** out) {
+    if (!path || !out) return fail(FC_E_ARG, "fc_llama_load_gguf: bad argument");
+    *out = nullptr;
+    File f;
+    int rc = read_file(path, &f);
+    if (rc != FC_OK) return rc;
+    ParsedLlama p;
+    rc = parse_llama(f, math_mode, ctx_cap, &p);
+    if (rc != FC_OK) return rc;
+    return fc_llama_create(&p.cfg, &p.w, device, out);   // copies everything it needs
 }
 
 }  // extern "C"

@@ -1,4 +1,4 @@
-"""Writes a synthetic model as a gpt2-architecture GGUF file (version 3).
+"""Writes a synthetic model as a gpt2-, llama- or qwen2-architecture GGUF file (version 3).
 
 The container follows the reference's builder (ferrum_core/src/gguf_write/builder.rs and
 gguf/header.rs:9-66): magic, version, tensor count, metadata count, metadata key/value pairs,
@@ -67,6 +67,10 @@ def write_gpt2_gguf(path, sm, alignment=32, eps=1e-5, version=3, untied_head=Non
     if untied_head is not None:
         q8("output.weight", untied_head, V, d)
 
+    return _emit(path, meta, tensors, alignment, version)
+
+
+def _emit(path, meta, tensors, alignment, version):
     out = bytearray()
     out += struct.pack("<IIQQ", 0x46554747, version, len(tensors), len(meta))
     for key, vt, val in meta:
@@ -92,3 +96,60 @@ def write_gpt2_gguf(path, sm, alignment=32, eps=1e-5, version=3, untied_head=Non
     with open(path, "wb") as fh:
         fh.write(out)
     return path
+
+
+def write_llama_gguf(path, sm, arch="llama", alignment=32, version=3, extra_meta=(), extra_tensors=(), drop_meta=()):
+    """sm: synth.SynthLlama. Keys and tensor names as gguf/llama.rs:164-339 reads them. The file's
+    architecture decides the rotation (qwen2: split halves), so write `arch` to match sm's rope_type."""
+    c = sm.dims
+    V, d, L, H, KV, hd, F, ctx = (c[k] for k in ("vocab", "d_model", "n_layer", "n_head", "n_kv_head", "head_dim", "d_ff", "ctx"))
+    cfg = sm.config
+    meta = [
+        ("general.architecture", VT_STRING, arch),
+        ("general.alignment", VT_U32, alignment),
+        (f"{arch}.context_length", VT_U32, ctx),
+        (f"{arch}.embedding_length", VT_U32, d),
+        (f"{arch}.block_count", VT_U32, L),
+        (f"{arch}.feed_forward_length", VT_U32, F),
+        (f"{arch}.attention.head_count", VT_U32, H),
+        (f"{arch}.attention.head_count_kv", VT_U32, KV),
+        (f"{arch}.attention.key_length", VT_U32, hd),
+        (f"{arch}.rope.dimension_count", VT_U32, cfg.rope_dim),
+        (f"{arch}.rope.freq_base", VT_F32, cfg.rope_base),
+        (f"{arch}.attention.layer_norm_rms_epsilon", VT_F32, cfg.norm_eps),
+    ]
+    if cfg.rope_linear_factor != 1.0:
+        meta += [(f"{arch}.rope.scaling.type", VT_STRING, "linear"), (f"{arch}.rope.scaling.factor", VT_F32, cfg.rope_linear_factor)]
+    meta = [m for m in meta if m[0] not in drop_meta] + list(extra_meta)
+    tensors = []
+
+    def q8(name, raw, n, k):
+        tensors.append((name, (k, n), GGML_Q8_0, np.ascontiguousarray(raw, dtype=np.uint8).tobytes()))
+
+    def f32(name, v, dims):
+        tensors.append((name, dims, GGML_F32, np.ascontiguousarray(v, dtype=np.float32).tobytes()))
+
+    q8("token_embd.weight", sm.token_embd, V, d)
+    if sm.freq_factors is not None:
+        f32("rope_freqs.weight", sm.freq_factors, (cfg.rope_dim // 2,))
+    qd, kvd = H * hd, KV * hd
+    for i, lw in enumerate(sm.layers):
+        n = f"blk.{i}."
+        f32(n + "attn_norm.weight", lw["attn_norm"], (d,))
+        q8(n + "attn_q.weight", lw["wq_q8"], qd, d)
+        q8(n + "attn_k.weight", lw["wk_q8"], kvd, d)
+        q8(n + "attn_v.weight", lw["wv_q8"], kvd, d)
+        q8(n + "attn_output.weight", lw["wo_q8"], d, qd)
+        for s_, w_ in (("q", qd), ("k", kvd), ("v", kvd)):
+            if "b" + s_ in lw:
+                f32(n + f"attn_{s_}.bias", lw["b" + s_], (w_,))
+        f32(n + "ffn_norm.weight", lw["ffn_norm"], (d,))
+        q8(n + "ffn_gate.weight", lw["gate_q8"], F, d)
+        q8(n + "ffn_up.weight", lw["up_q8"], F, d)
+        q8(n + "ffn_down.weight", lw["down_q8"], d, F)
+    f32("output_norm.weight", sm.output_norm, (d,))
+    if sm.output is not None:
+        q8("output.weight", sm.output, V, d)
+    for name, v, dims in extra_tensors:
+        f32(name, v, dims)
+    return _emit(path, meta, tensors, alignment, version)

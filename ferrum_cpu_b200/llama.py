@@ -12,6 +12,13 @@ from ._lib import check
 from .engine import Score, _ids, _ptr
 
 
+def gguf_probe(path):
+    """Configuration of a llama / qwen2 GGUF file; validates it without a GPU."""
+    cfg = _lib.FcLlamaConfig()
+    check(_lib.lib().fc_llama_gguf_probe(str(path).encode(), C.byref(cfg)))
+    return cfg
+
+
 class CudaLlamaCache:
     """LlamaCache (llm.rs:522-546): per-layer KV rows and the position of the next token."""
 
@@ -55,6 +62,19 @@ class CudaLlama:
     @classmethod
     def from_synth(cls, synth, device=0):
         return cls(synth.config, synth.weights, device)
+
+    @classmethod
+    def from_gguf(cls, path, device=0, math_mode=_lib.FC_MATH_FP32, ctx_cap=0):
+        """Gguf::load_llama (gguf/llama.rs:164-339) for llama / qwen2 files with Q8_0 projections."""
+        self = cls.__new__(cls)
+        self._h = C.c_void_p()
+        self._caches = []
+        self.config = gguf_probe(path)
+        if 0 < ctx_cap < self.config.ctx:
+            self.config.ctx = ctx_cap
+        self.config.math_mode = math_mode
+        check(_lib.lib().fc_llama_load_gguf(str(path).encode(), device, math_mode, ctx_cap, C.byref(self._h)))
+        return self
 
     def close(self):
         for ref in self._caches:                 # caches go first: they hold device memory of this model's context

@@ -294,6 +294,13 @@ typedef struct fc_llama_cache fc_llama_cache; /* LlamaCache: per-layer KV rows +
  * head_dim) and RopeScaling::check (llm.rs:135-150: factors finite and > 0): FC_E_DIM. */
 int fc_llama_create(const fc_llama_config* cfg, const fc_llama_weights* w, int device, fc_llama** out);
 void fc_llama_free(fc_llama* m);
+/* Gguf::load_llama (gguf/llama.rs:164-339) for `llama` and `qwen2` files whose projections are
+ * Q8_0 (they stay packed) and whose norms are F32: the same metadata keys, defaults and refusals
+ * (yarn / longrope scaling, attn_factor != 1, biases other than q/k/v, FC_E_FORMAT). qwen2 rotates
+ * split halves, llama interleaved pairs. ctx_cap > 0 lowers the context (and with it the KV
+ * caches) below the file's context_length. fc_llama_gguf_probe validates without a GPU. */
+int fc_llama_load_gguf(const char* path, int device, int math_mode, int ctx_cap, fc_llama** out);
+int fc_llama_gguf_probe(const char* path, fc_llama_config* out);
 /* LlamaModel::forward_tokens (llm.rs:622-635): n ids -> logits [n][vocab] (host buffer). */
 int fc_llama_forward_tokens(fc_llama* m, const int32_t* ids, int n, float* logits);
 /* LlamaModel::score_from (llm_score.rs:76-96) with the windows of plan_windows
