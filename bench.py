@@ -276,7 +276,7 @@ def main():
                 "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s", "frac": gbs / hbm_peak, "traffic": None,
                              "peak_kind": peak_kind, "algorithmic_bytes_per_token": per_token},
                 "e2e": {"value": world * NEW_TOKENS / wall_s, "unit": "tokens/s", "h2d_bytes_per_step": PROMPT * 4 + 8,
-                        "d2h_bytes_per_step": NEW_TOKENS * 4 + 8 + 32, "note": "includes priming the prompt token by token"},
+                        "d2h_bytes_per_step": NEW_TOKENS * 4 + 8 + 32, "note": "includes priming the prompt (one window forward)"},
                 "gpu_launches": int(launches),
                 "scoring": {"value": world * 4 * T / (score_ms / 1e3), "unit": "positions/s", "ms_per_step": score_ms,
                             "tflops_algorithmic": flop_pos * 4 * T / (score_ms / 1e3) / 1e12,

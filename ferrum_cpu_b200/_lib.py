@@ -111,6 +111,7 @@ SIGNATURES = {
     "fc_llama_cache_clear": (C.c_int, [C.c_void_p]),
     "fc_llama_cache_pos": (C.c_int, [C.c_void_p]),
     "fc_llama_forward_one": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p]),
+    "fc_llama_prime": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "fc_llama_generate": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.POINTER(FcSampling), C.c_void_p, C.c_int,
                                     C.POINTER(C.c_uint64), C.c_void_p, C.c_void_p, C.POINTER(C.c_int)]),
     "fc_llama_last_decode_ms": (C.c_float, [C.c_void_p]),

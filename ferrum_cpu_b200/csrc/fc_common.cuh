@@ -108,10 +108,9 @@ int launch_gemv_q8(const QMat& w, const float* x, const float* bias, const float
                    const GemvOut& out, const StepState* state, cudaStream_t st);
 
 // Split-K form for wide matrices: optional RMSNorm of x (norm_w, eps) as it is staged; epi
-// EPI_SWIGLU pairs rows (2i, 2i+1) as (gate, up) and writes out[i] = silu(gate) * up. `next` (may
-// be null) is the matrix the following kernel streams: its planes are prefetched into L2.
+// EPI_SWIGLU pairs rows (2i, 2i+1) as (gate, up) and writes out[i] = silu(gate) * up.
 int launch_gemv_q8_wide(const QMat& w, const float* x, const float* norm_w, float eps, const float* bias, const float* residual,
-                        int epi, float* out, const StepState* state, const QMat* next, cudaStream_t st);
+                        int epi, float* out, const StepState* state, cudaStream_t st);
 
 // gemv_stream.cu — the same contract on a persistent kernel that streams row tiles through a
 // shared-memory ring with bulk async copies; `status` (device int) is raised to FC_E_TIMEOUT when

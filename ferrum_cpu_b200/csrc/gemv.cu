@@ -176,21 +176,7 @@ struct GemvWideArgs {
     const float* bias; const float* residual; int epi;
     float* out; int S;
     const StepState* state;
-    // the matrix the next kernel of the step will stream (or null): prefetched into L2 from here
-    const uint8_t* next_q; const __half* next_d; unsigned long long next_q_bytes, next_d_bytes;
 };
-
-// One slice per block of `bytes` at p, as L2 prefetch hints (bulk form; 16-byte granularity).
-__device__ __forceinline__ void prefetch_slice_l2(const void* p, unsigned long long bytes) {
-    unsigned long long per = ((bytes + gridDim.x - 1) / gridDim.x + 15ull) & ~15ull;
-    const unsigned long long off = (unsigned long long)blockIdx.x * per;
-    if (off >= bytes) return;
-    if (off + per > bytes) per = (bytes - off) & ~15ull;
-    for (unsigned long long o = 0; o < per; o += 32768ull) {
-        const unsigned n = (unsigned)(per - o < 32768ull ? per - o : 32768ull);
-        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"((const char*)p + off + o), "r"(n) : "memory");
-    }
-}
 
 template <int RIF>
 __global__ void __launch_bounds__(256) gemv_q8_wide_kernel(GemvWideArgs a) {
@@ -217,10 +203,6 @@ __global__ void __launch_bounds__(256) gemv_q8_wide_kernel(GemvWideArgs a) {
             w0[r] = __ldg((const uint4*)(a.qu + row * K) + c0);
             sc0[r] = __half2float(__ldg(a.d + row * kb_per_row + (c0 >> 1)));
         }
-    }
-    if (a.next_q && threadIdx.x == 0) {
-        prefetch_slice_l2(a.next_q, a.next_q_bytes);
-        prefetch_slice_l2(a.next_d, a.next_d_bytes);
     }
     // stage x (swizzled 16-byte units), normalising it on the way when asked
     float ss = 0.0f;
@@ -310,16 +292,12 @@ __global__ void __launch_bounds__(256) gemv_q8_wide_kernel(GemvWideArgs a) {
 }
 
 int launch_gemv_q8_wide(const QMat& w, const float* x, const float* norm_w, float eps, const float* bias, const float* residual,
-                        int epi, float* out, const StepState* state, const QMat* next, cudaStream_t st) {
+                        int epi, float* out, const StepState* state, cudaStream_t st) {
     if (w.K % 16 || w.K > 12288) return fail(FC_E_SHAPE, "GEMV row length %d must be a multiple of 16, at most 12288", w.K);
     if (epi == EPI_SWIGLU && ((w.N & 1) || residual)) return fail(FC_E_SHAPE, "the SwiGLU epilogue pairs rows and takes no residual");
     GemvWideArgs a;
     a.qu = w.qu; a.d = w.d; a.N = w.N; a.K = w.K;
     a.x = x; a.norm_w = norm_w; a.eps = eps; a.bias = bias; a.residual = residual; a.epi = epi; a.out = out; a.state = state;
-    a.next_q = next ? next->qu : nullptr;
-    a.next_d = next ? next->d : nullptr;
-    a.next_q_bytes = next ? (unsigned long long)next->N_pad * next->K : 0;          // planes are padded to N_pad rows,
-    a.next_d_bytes = next ? (unsigned long long)next->N_pad * (next->K / 32) * 2 : 0;  // multiples of 16 bytes
     const int chunks = w.K >> 4;
     const bool big = (size_t)w.N * w.K >= (size_t)8 << 20;
     const int rif = big ? 4 : 2;

@@ -268,7 +268,7 @@ int launch_gemv_q8_stream(const QMat& w, const float* x, const float* norm_w, fl
     }
     int RT = 0, slots = 0, slot_bytes = 0;
     if (!status || !stream_shape(w, &RT, &slots, &slot_bytes, sms[dev]))
-        return launch_gemv_q8_wide(w, x, norm_w, eps, bias, residual, epi, out, state, nullptr, st);
+        return launch_gemv_q8_wide(w, x, norm_w, eps, bias, residual, epi, out, state, st);
     if (epi == EPI_SWIGLU && ((w.N & 1) || residual)) return fail(FC_E_SHAPE, "the SwiGLU epilogue pairs rows and takes no residual");
     StreamArgs a;
     a.qu = w.qu; a.d = w.d; a.N = w.N; a.N_pad = w.N_pad; a.K = w.K;

@@ -40,6 +40,7 @@ struct fc_llama {
     uint16_t *xhi = nullptr, *xlo = nullptr;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     float last_score_ms = 0.0f;
+    bool force_fp32 = false;         // the batched prime keeps the cache rows at fp32 rounding
 };
 
 struct fc_llama_cache {
@@ -96,7 +97,7 @@ int upload_interleaved(Arena& ar, const void* a, const void* b, int rows, int K,
 }
 
 int gemm(fc_llama* m, const QMat& w, const float* x, const float* bias, const float* res, float* y, int M, int ldy) {
-    if (m->cfg.math_mode == FC_MATH_BF16X3 && w.K % 64 == 0) {
+    if (m->cfg.math_mode == FC_MATH_BF16X3 && !m->force_fp32 && w.K % 64 == 0) {
         FC_TRY(launch_split_bf16(x, m->xhi, m->xlo, (size_t)M * w.K, m->st));
         return launch_gemm_q8_bf16x3(w, m->xhi, m->xlo, bias, res, EPI_NONE, y, M, ldy, m->tc_status, m->st);
     }
@@ -138,7 +139,8 @@ int ensure_workspace(fc_llama* m, int rows) {
 
 // LlamaModel::forward_tokens (llm.rs:622-635) up to the final norm, for B windows of T rows
 // whose ids are in m->ids_d: every row r sits at position r % T. Leaves RMSNorm(h) in m->n.
-int forward_rows(fc_llama* m, int B, int T) {
+// With `fill` (B == 1) the rotated keys and the values of every block become the cache's rows 0..T-1.
+int forward_rows(fc_llama* m, int B, int T, fc_llama_cache* fill = nullptr) {
     const fc_llama_config& c = m->cfg;
     const int R = B * T, d = c.d_model, F = c.d_ff;
     cudaStream_t st = m->st;
@@ -151,6 +153,11 @@ int forward_rows(fc_llama* m, int B, int T) {
         FC_TRY(gemm(m, L.qkv, m->n, L.qkv_b, nullptr, m->qkv, R, m->qkv_dim));
         FC_TRY(launch_llama_rope_rows(m->qkv, R, m->qkv_dim, T, c.n_head, c.n_kv_head, m->q_dim, c.head_dim, c.rope_dim,
                                       c.rope_type == FC_ROPE_NEOX, m->ftab, m->inv_linear, st));
+        if (fill) {
+            const size_t layer_stride = (size_t)c.ctx * m->kv_dim;
+            FC_TRY(launch_llama_store_kv_rows(m->qkv, R, m->qkv_dim, m->q_dim, m->kv_dim, fill->kc + l * layer_stride,
+                                              fill->vc + l * layer_stride, st));
+        }
         FC_TRY(launch_attn_prefill_gqa(m->qkv, m->qkv + m->q_dim, m->qkv + m->q_dim + m->kv_dim, B, T, m->qkv_dim, c.n_head,
                                        c.n_kv_head, c.head_dim, m->q_dim, m->att, st));
         FC_TRY(gemm(m, L.wo, m->att, nullptr, m->x, m->x, R, d));
@@ -285,6 +292,32 @@ int feed_ids(fc_llama_cache* s, const int32_t* ids, int n, int head_on_last) {
     FC_LAUNCHED();
     for (int i = 0; i < n; ++i) FC_TRY(run_step(s, head_on_last && i + 1 == n));
     s->host_pos += n;
+    return FC_OK;
+}
+
+// The prompt of an empty cache as one fp32 window forward instead of n decode steps: the same
+// cache rows and last-row logits to fp32 rounding (the order of the sums differs), at a fraction of
+// the launches. Short prompts keep the step path.
+constexpr int kPrimeBatchMin = 8;
+int prime_window(fc_llama_cache* s, const int32_t* ids, int n) {
+    fc_llama* m = s->m;
+    const fc_llama_config& c = m->cfg;
+    if (n > c.ctx) return fail(FC_E_DIM, "%d tokens do not fit the model's %d-token context window", n, c.ctx);
+    FC_TRY(ensure_workspace(m, n));
+    cudaStream_t st = m->st;
+    FC_CUDA(cudaMemcpyAsync(m->ids_d, ids, (size_t)n * 4, cudaMemcpyHostToDevice, st));
+    FC_CUDA(cudaMemcpyAsync(s->queue, ids, (size_t)n * 4, cudaMemcpyHostToDevice, st));
+    m->force_fp32 = true;
+    const int rc = forward_rows(m, 1, n, s);
+    m->force_fp32 = false;
+    FC_TRY(rc);
+    llama_set_state_kernel<<<1, 1, 0, st>>>(s->state, n, n, n);
+    FC_LAUNCHED();
+    // logits of the last row: the final norm was applied by forward_rows
+    FC_TRY(launch_gemv_q8_stream(m->head, m->n + (size_t)(n - 1) * c.d_model, nullptr, 0.0f, nullptr, nullptr, EPI_NONE, s->logits,
+                                 s->state, s->status, st));
+    FC_TRY(check_status(m));
+    s->host_pos = n;
     return FC_OK;
 }
 
@@ -567,6 +600,22 @@ int fc_llama_forward_one(fc_llama_cache* s, int32_t token, float* logits) {
     return FC_OK;
 }
 
+int fc_llama_prime(fc_llama_cache* s, const int32_t* ids, int n, float* logits) {
+    if (!s || !ids) return fail(FC_E_ARG, "fc_llama_prime: null argument");
+    if (n <= 0) return fail(FC_E_DIM, "prompt must be non-empty");
+    fc_llama* m = s->m;
+    FC_CUDA(cudaSetDevice(m->device));
+    FC_TRY(check_ids(m, ids, (size_t)n));
+    FC_TRY(fc_llama_cache_clear(s));
+    if (n >= kPrimeBatchMin) FC_TRY(prime_window(s, ids, n));
+    else FC_TRY(feed_ids(s, ids, n, 1));
+    if (logits) FC_CUDA(cudaMemcpyAsync(logits, s->logits, (size_t)m->cfg.vocab * 4, cudaMemcpyDeviceToHost, m->st));
+    StepState hs;
+    FC_TRY(read_state(s, &hs));
+    if (hs.error) return fail(hs.error, "the decode step rejected a token or position on the device");
+    return FC_OK;
+}
+
 int fc_llama_generate(fc_llama_cache* s, const int32_t* prompt, int n, int max_new, const fc_sampling* params,
                       const int32_t* stops, int n_stops, uint64_t* rng_state, const volatile int32_t* cancel,
                       int32_t* out, int* n_out) {
@@ -586,7 +635,8 @@ int fc_llama_generate(fc_llama_cache* s, const int32_t* prompt, int n, int max_n
     if (cancel && *cancel) return FC_OK;                     // cancelled while reading the prompt: nothing (llm.rs:734-736)
     FC_TRY(fc_llama_cache_clear(s));
     FC_CUDA(cudaMemcpyAsync(s->rng_d, rng_state, 8, cudaMemcpyHostToDevice, st));
-    FC_TRY(feed_ids(s, prompt, n, 1));
+    if (n >= kPrimeBatchMin) FC_TRY(prime_window(s, prompt, n));
+    else FC_TRY(feed_ids(s, prompt, n, 1));
     // greedy without a penalty needs neither the sampler's sort nor, without stop ids, the host
     const bool plain_greedy = params->temperature <= 0.0f && params->repetition_penalty == 1.0f;
     const bool free_run = plain_greedy && n_stops == 0 && !cancel;

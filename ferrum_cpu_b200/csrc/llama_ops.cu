@@ -141,38 +141,19 @@ int launch_llama_rope_rows(float* qkv, int R, int ld, int T, int n_q, int n_kv, 
     return FC_OK;
 }
 
-// Decode form (Attention::project + the cache append of forward_one, llm.rs:276-301,345-351):
-// one block per head of the fused q | k | v row. Query heads are rotated in place, key heads are
-// rotated into the cache row of the current position, value heads are copied there.
-__global__ void llama_rope_store_kernel(float* __restrict__ qkv, int n_q, int n_kv, int hd, int half, int neox,
-                                        const float2* __restrict__ ftab, float inv_linear, float* __restrict__ kc,
-                                        float* __restrict__ vc, const StepState* st) {
-    pdl_trigger();
-    pdl_wait();
-    if (st->done | st->error) return;
-    const int pos = st->pos, kv_dim = n_kv * hd;
-    const int h = blockIdx.x, t = threadIdx.x;
-    float* src = qkv + (size_t)h * hd;
-    if (h >= n_q + n_kv) {                                   // a value head
-        if (t < hd) vc[(size_t)pos * kv_dim + (h - n_q - n_kv) * hd + t] = src[t];
-        return;
+// Batched prime: the rotated key rows and the value rows of a window forward become the first R
+// cache rows of a layer (what R calls of forward_one would have appended, llm.rs:349-350).
+__global__ void llama_store_kv_rows_kernel(const float* __restrict__ qkv, int ld, int q_dim, int kv_dim, float* __restrict__ kc,
+                                           float* __restrict__ vc) {
+    const float* row = qkv + (size_t)blockIdx.x * ld + q_dim;
+    for (int c = threadIdx.x; c < kv_dim; c += blockDim.x) {
+        kc[(size_t)blockIdx.x * kv_dim + c] = row[c];
+        vc[(size_t)blockIdx.x * kv_dim + c] = row[kv_dim + c];
     }
-    float* dst = h < n_q ? src : kc + (size_t)pos * kv_dim + (h - n_q) * hd;
-    if (t < half) {
-        const int ia = neox ? t : 2 * t, ib = neox ? t + half : 2 * t + 1;
-        float s, c;
-        sincosf(rope_angle(pos, ftab[t], inv_linear), &s, &c);
-        const float a = src[ia], b = src[ib];
-        dst[ia] = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s));
-        dst[ib] = __fadd_rn(__fmul_rn(a, s), __fmul_rn(b, c));
-    }
-    if (dst != src && t >= 2 * half && t < hd) dst[t] = src[t];   // the unrotated tail of a key head
 }
-int launch_llama_rope_store(float* qkv, int n_q, int n_kv, int hd, int rope_dim, int neox, const float2* ftab, float inv_linear,
-                            float* kc, float* vc, const StepState* state, cudaStream_t st) {
-    FC_CUDA(launch_pdl(llama_rope_store_kernel, dim3(n_q + 2 * n_kv), dim3(hd), 0, st, qkv, n_q, n_kv, hd, rope_dim / 2, neox, ftab,
-                       inv_linear, kc, vc, state));
-    ++g_launches;
+int launch_llama_store_kv_rows(const float* qkv, int R, int ld, int q_dim, int kv_dim, float* kc, float* vc, cudaStream_t st) {
+    llama_store_kv_rows_kernel<<<R, 256, 0, st>>>(qkv, ld, q_dim, kv_dim, kc, vc);
+    FC_LAUNCHED();
     return FC_OK;
 }
 

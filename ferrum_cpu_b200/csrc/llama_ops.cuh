@@ -11,8 +11,8 @@ int launch_llama_rmsnorm(const float* x, const float* w, float eps, int rows, in
 // ftab[i] = {base^(-2i/rope_dim) as f32, freq_factor_i or 1}; inv_linear = 1 / linear_factor.
 int launch_llama_rope_rows(float* qkv, int R, int ld, int T, int n_q, int n_kv, int k_off, int hd, int rope_dim, int neox,
                            const float2* ftab, float inv_linear, cudaStream_t st);
-int launch_llama_rope_store(float* qkv, int n_q, int n_kv, int hd, int rope_dim, int neox, const float2* ftab, float inv_linear,
-                            float* kc, float* vc, const StepState* state, cudaStream_t st);
+// Rows [R] of a fused, rotated q | k | v buffer -> the first R rows of a layer's caches.
+int launch_llama_store_kv_rows(const float* qkv, int R, int ld, int q_dim, int kv_dim, float* kc, float* vc, cudaStream_t st);
 // Rotation, cache append and single-query grouped attention in one kernel: q | k | v fused row
 // in, attention output [n_q * hd] out.
 int launch_llama_attn_decode(const float* qkv, int n_q, int n_kv, int hd, int rope_dim, int neox, const float2* ftab, float inv_linear,

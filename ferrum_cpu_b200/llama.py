@@ -143,6 +143,13 @@ class CudaLlama:
         check(_lib.lib().fc_llama_forward_one(cache._h, int(token), None if out is None else _ptr(out)))
         return out
 
+    def prime(self, ids, cache, want_logits=True):
+        """Clear the cache and feed a prompt (llm.rs:733-738); logits after its last token."""
+        ids = _ids(ids)
+        out = np.empty(self.config.vocab, dtype=np.float32) if want_logits else None
+        check(_lib.lib().fc_llama_prime(cache._h, _ptr(ids), ids.size, None if out is None else _ptr(out)))
+        return out
+
     def generate(self, prompt, max_new, params, stops=(), rng_state=1, cache=None, cancel=None):
         """llm.rs:643-754: (new token ids, advanced generator state)."""
         prompt = _ids(prompt)

@@ -323,6 +323,10 @@ int fc_llama_cache_pos(const fc_llama_cache* c);
 /* LlamaModel::forward_one (llm.rs:610-618): one token at the cache position; logits (host
  * [vocab]) may be NULL. FC_E_DIM on id >= vocab or a full context. */
 int fc_llama_forward_one(fc_llama_cache* c, int32_t token, float* logits);
+/* The prompt loop of generate_inner (llm.rs:733-738) on its own: clears the cache, feeds ids[n]
+ * and returns the logits after the last one (host [vocab], may be NULL). Prompts of 8 ids or
+ * more run as one fp32 window forward that fills the caches (same values to fp32 rounding). */
+int fc_llama_prime(fc_llama_cache* c, const int32_t* ids, int n, float* logits);
 /* LlamaModel::generate_cancellable (llm.rs:658-754): prime the prompt token by token, then
  * draw up to min(max_new, ctx - n) tokens with sample_with_params over `recent` = prompt +
  * tokens so far, stopping after a token found in stops[n_stops] (it is kept in out). The

@@ -99,6 +99,48 @@ def test_mini_model_forward_and_decode(mini):
         assert np.abs(gm.forward_one(tok, cache) - want[t]).max() < FP32_TOL
 
 
+def test_batched_prime_equals_token_by_token(tiny, mini):
+    for sm, om, gm in (tiny, mini):
+        ids = synth.token_ids(13, 40, sm.dims["vocab"])
+        a, b = gm.new_cache(), gm.new_cache()
+        step = None
+        for t in ids[:32]:
+            step = gm.forward_one(t, a)
+        batched = gm.prime(ids[:32], b)
+        assert b.pos() == a.pos() == 32
+        assert np.abs(batched - step).max() < 1e-4
+        om.clear()
+        want = None
+        for t in ids[:32]:
+            want = om.forward_one(t)
+        assert np.abs(batched - want).max() < FP32_TOL
+        for t in ids[32:]:                                   # the filled caches carry the decode on
+            assert np.abs(gm.forward_one(t, a) - gm.forward_one(t, b)).max() < 1e-4
+        short = gm.prime(ids[:5], b)                          # below the threshold: the step path
+        om.clear()
+        for t in ids[:5]:
+            want = om.forward_one(t)
+        assert b.pos() == 5 and np.abs(short - want).max() < FP32_TOL
+
+
+def test_narrow_deep_model_decode_matches_forward_and_oracle():
+    # 16 blocks, vocabulary 32000, d 512 / F 2048: the ring GEMV's tile shapes for wide rows, a long chain of steps
+    sm = synth.llama_named("llama-narrow", seed=3)
+    gm = CudaLlama.from_synth(sm)
+    ids = synth.token_ids(14, 24, sm.dims["vocab"])
+    full = gm.forward_tokens(ids)
+    cache = gm.new_cache()
+    for t, tok in enumerate(ids):
+        assert np.abs(gm.forward_one(tok, cache) - full[t]).max() < FP32_TOL, t
+    om = O.OracleLlama(sm, threads=8)
+    want = om.forward_tokens(ids[:6])
+    assert np.abs(full[:6] - want).max() < FP32_TOL
+    out1, _ = gm.generate(ids[:12], 16, sampling(temperature=0.0))
+    out2, _ = gm.generate(ids[:12], 16, sampling(temperature=0.0))
+    assert np.array_equal(out1, out2)                         # bitwise repeatable
+    gm.close()
+
+
 def test_tensor_core_window_forward_stays_within_tolerance():
     sm, om, gm = build("llama-mini", math_mode=_lib.FC_MATH_BF16X3, seed=5)
     ids = synth.token_ids(6, 200, sm.dims["vocab"])
