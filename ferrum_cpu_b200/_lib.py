@@ -82,6 +82,7 @@ SIGNATURES = {
     "fc_score_windows": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
     "fc_token_logprobs": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.POINTER(FcScore), C.c_void_p, C.c_void_p]),
     "fc_score_sequences": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.POINTER(FcScore), C.c_void_p]),
+    "fc_score_requests": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.POINTER(FcScore)]),
     "fc_predict_next": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "fc_stream_create": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
     "fc_stream_free": (None, [C.c_void_p]),

@@ -746,10 +746,10 @@ void plan_windows(int seq, int n, int from, int T, std::vector<Window>* out) {
     }
 }
 
-// Scores every window of `plan` in batches; seq_ids(s) gives the ids of sequence s, n its
-// length. For each scored target calls add(seq, target, logprob, greedy).
-template <class Ids, class Add>
-int run_plan(fc_model* m, const std::vector<Window>& plan, int batch, Ids seq_ids, int n, Add add) {
+// Scores every window of `plan` in batches; seq_ids(s) gives the ids of sequence s, seq_len(s)
+// its length. For each scored target calls add(seq, target, logprob, greedy).
+template <class Ids, class Len, class Add>
+int run_plan_ragged(fc_model* m, const std::vector<Window>& plan, int batch, Ids seq_ids, Len seq_len, Add add) {
     const int T = m->cfg.ctx;
     std::vector<int32_t> ids, targets;
     std::vector<double> lp;
@@ -758,13 +758,13 @@ int run_plan(fc_model* m, const std::vector<Window>& plan, int batch, Ids seq_id
         const int B = (int)std::min<size_t>(batch, plan.size() - w0);
         // rows past the longest window of the batch are never read under the causal mask
         int Tb = 1;
-        for (int b = 0; b < B; ++b) Tb = std::max(Tb, std::min(plan[w0 + b].start + T, n) - plan[w0 + b].start);
+        for (int b = 0; b < B; ++b) Tb = std::max(Tb, std::min(plan[w0 + b].start + T, seq_len(plan[w0 + b].seq)) - plan[w0 + b].start);
         ids.assign((size_t)B * Tb, 0);          // right padding with id 0 (scoring.rs:188-190)
         targets.assign((size_t)B * Tb, -1);
         for (int b = 0; b < B; ++b) {
             const Window& w = plan[w0 + b];
             const int32_t* src = seq_ids(w.seq);
-            const int wl = std::min(w.start + T, n) - w.start;
+            const int wl = std::min(w.start + T, seq_len(w.seq)) - w.start;
             std::copy(src + w.start, src + w.start + wl, ids.begin() + (size_t)b * Tb);
             for (int t = w.first; t < w.end; ++t) targets[(size_t)b * Tb + (t - 1 - w.start)] = src[t];
         }
@@ -781,9 +781,36 @@ int run_plan(fc_model* m, const std::vector<Window>& plan, int batch, Ids seq_id
     }
     return FC_OK;
 }
+template <class Ids, class Add>
+int run_plan(fc_model* m, const std::vector<Window>& plan, int batch, Ids seq_ids, int n, Add add) {
+    return run_plan_ragged(m, plan, batch, seq_ids, [n](int) { return n; }, add);
+}
 }  // namespace
 
 extern "C" {
+
+int fc_score_requests(fc_model* m, const int32_t* ids, const int64_t* offsets, const int32_t* from, int n_req, int batch_windows,
+                      fc_score* scores) {
+    if (!m || !scores || (n_req > 0 && (!ids || !offsets || !from))) return fail(FC_E_ARG, "fc_score_requests: null argument");
+    if (n_req < 0) return fail(FC_E_SHAPE, "fc_score_requests: n_req = %d", n_req);
+    m->last_score_ms = 0.0f;
+    std::vector<Window> plan;
+    for (int r = 0; r < n_req; ++r) {
+        scores[r].logprob = 0.0; scores[r].n_tokens = 0; scores[r].greedy = 1;
+        const int64_t n = offsets[r + 1] - offsets[r];
+        if (n < 0 || n > (1 << 30) || from[r] < 0) return fail(FC_E_SHAPE, "fc_score_requests: request %d has length %lld, from %d", r, (long long)n, from[r]);
+        FC_TRY(check_ids(m, ids + offsets[r], (size_t)n));
+        plan_windows(r, (int)n, from[r], m->cfg.ctx, &plan);
+    }
+    if (plan.empty()) return FC_OK;
+    // windows of similar length share a forward: the rows a batch pads are wasted work
+    auto wlen = [&](const Window& w) { return std::min<int64_t>(w.start + m->cfg.ctx, offsets[w.seq + 1] - offsets[w.seq]) - w.start; };
+    std::stable_sort(plan.begin(), plan.end(), [&](const Window& a, const Window& b) { return wlen(a) > wlen(b); });
+    if (batch_windows <= 0) batch_windows = 32;
+    return run_plan_ragged(m, plan, batch_windows, [&](int r) { return ids + offsets[r]; },
+                           [&](int r) { return (int)(offsets[r + 1] - offsets[r]); },
+                           [&](int r, int, double l, uint8_t g) { scores[r].logprob += l; scores[r].n_tokens += 1; scores[r].greedy &= (int32_t)g; });
+}
 
 int fc_token_logprobs(fc_model* m, const int32_t* ids, int n, int from, fc_score* score, float* lp, uint8_t* is_greedy) {
     if (!m || !score || (n > 0 && !ids)) return fail(FC_E_ARG, "fc_token_logprobs: null argument");

@@ -211,6 +211,19 @@ class CudaSlm:
         check(_lib.lib().fc_score_sequences(self._m, _ptr(ids2d), n_seq, seq_len, batch_windows, scores, _ptr(lp)))
         return [Score(s.logprob, s.n_tokens, bool(s.greedy)) for s in scores], lp
 
+    def score_requests(self, requests, batch_windows=32):
+        """Many (ids, first scored target) requests in shared forward passes: one Score per request.
+        GenerativeSLM::score(ctx, cont) is (ctx + cont, len(ctx)); score_rolling is (ids, 1)."""
+        seqs = [_ids(r[0]) for r in requests]
+        offsets = np.zeros(len(seqs) + 1, dtype=np.int64)
+        offsets[1:] = np.cumsum([s.size for s in seqs])
+        flat = np.concatenate(seqs) if seqs else np.zeros(0, dtype=np.int32)
+        start = np.ascontiguousarray([r[1] for r in requests], dtype=np.int32)
+        scores = (_lib.FcScore * max(len(seqs), 1))()
+        check(_lib.lib().fc_score_requests(self._m, _ptr(flat) if flat.size else None, _ptr(offsets), _ptr(start) if start.size else None,
+                                           len(seqs), batch_windows, scores))
+        return [Score(s.logprob, s.n_tokens, bool(s.greedy)) for s in scores[:len(seqs)]]
+
     def score_windows(self, ids2d, targets2d):
         ids2d, targets2d = _ids(ids2d), _ids(targets2d)
         b, t = ids2d.shape

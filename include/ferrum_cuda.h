@@ -173,6 +173,13 @@ int fc_token_logprobs(fc_model* m, const int32_t* ids, int n, int from, fc_score
  * different sequences share forward batches of `batch_windows` windows. */
 int fc_score_sequences(fc_model* m, const int32_t* ids, int n_seq, int seq_len, int batch_windows,
                        fc_score* scores, float* lp);
+/* Many scoring requests in shared forward passes (the reference's server scores them one by one,
+ * slm_server/src/model_thread.rs:29-38): request r is ids[offsets[r] .. offsets[r+1]) scored from
+ * target from[r] (GenerativeSLM::score(ctx, cont) is from = len(ctx), score_rolling from = 1;
+ * slm/scoring.rs:95-140). Each request keeps its own window plan; the windows of all requests are
+ * sorted by length and run batch_windows (0: 32) at a time. scores [n_req]. */
+int fc_score_requests(fc_model* m, const int32_t* ids, const int64_t* offsets, const int32_t* from, int n_req, int batch_windows,
+                      fc_score* scores);
 /* Full-window next-token distributions, as TransformerSLMModel::predict_next
  * (slm_wasm/src/lib.rs:217-241): probs[V] of the last of n <= ctx ids. */
 int fc_predict_next(fc_model* m, const int32_t* ids, int n, float* probs);
