@@ -237,3 +237,29 @@ def test_errors_are_statuses_not_traps(tiny):
         assert e.value.code == _lib.FC_E_DIM
     with pytest.raises(FerrumCudaError):
         gm.score_rolling([1], 8)
+
+
+def test_1b_shape_matches_the_golden_fixture():
+    """Llama-3.2-1B shape, synthetic weights: per-token log-probs and greedy tokens against
+    tests/golden/llama_1b.npz (made by tests/golden/make_golden_llama.py from the oracle)."""
+    import os
+    gold = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "llama_1b.npz"))
+    sm = synth.llama_named("llama-1b", seed=0)
+    ids = gold["ids"]
+    for mode, tol in ((_lib.FC_MATH_FP32, FP32_TOL), (_lib.FC_MATH_BF16X3, TOL)):
+        sm.config.math_mode = mode
+        gm = CudaLlama.from_synth(sm)
+        sc, lp, gr = gm.score_from(ids, 1, 2048, per_token=True)
+        assert sc.n_tokens == ids.size - 1
+        assert np.abs(lp - gold["logprob"]).max() < tol
+        assert abs(sc.logprob - float(gold["total"])) < tol * sc.n_tokens
+        assert np.array_equal(gr, gold["is_greedy"])
+        if mode == _lib.FC_MATH_FP32:
+            toks, _ = gm.generate(gold["prompt"], gold["tokens"].size, sampling(temperature=0.0))
+            assert gold["margin"].min() > TOL and np.array_equal(toks, gold["tokens"])
+            # size-independent property at the full shape: the cached path reproduces the window forward
+            full = gm.forward_tokens(ids[:12])
+            cache = gm.new_cache()
+            for t, tok in enumerate(ids[:12]):
+                assert np.abs(gm.forward_one(tok, cache) - full[t]).max() < FP32_TOL
+        gm.close()
