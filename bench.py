@@ -120,14 +120,41 @@ def cpu_baseline_score(sm, ids_row, threads):
     return (len(ids_row) - 1) / dt
 
 
+def cpu_baseline_llama(sml, prompt, n_tokens):
+    """The restated LlamaModel::forward_one (llm.rs:610-618) on one host core: n_tokens cached steps
+    after the prompt. Building the f32 model (1.04 G weights) is not timed."""
+    from tests import oracle as O
+    om = O.OracleLlama(sml, threads=1)
+    logits = None
+    for t in prompt:
+        logits = om.forward_one(int(t))
+    t0 = time.perf_counter()
+    for _ in range(n_tokens):
+        logits = om.forward_one(int(np.argmax(logits)))
+    dt = time.perf_counter() - t0
+    om.close()
+    return n_tokens / dt
+
+
 def run_reference(args, rank):
     """--impl reference: the CPU restatement of the reference path, bounded samples."""
     if rank != 0:
         return
     from ferrum_cpu_b200 import synth
-    sm = synth.named("small", seed=0)
     cores = os.cpu_count() or 1
-    if args.workload == "score":
+    if args.workload == "llama-1b":
+        sml = synth.llama_named("llama-1b", seed=0)
+        n = 4
+        v = cpu_baseline_llama(sml, synth.token_ids(0, 8, sml.dims["vocab"]), n)
+        unit, metric = "tokens/s", "Q8_0 Llama-1B-shaped batch-1 greedy decode tokens/s"
+        sample, used = f"{n} KV-cached steps after an 8-token prompt, 1 thread (f32 Linear with one row is serial in the reference)", 1
+        cfg = {"workload": "Llama-3.2-1B shape: L16 d2048 H32 KV8 hd64 F8192 ctx2048 V32000, Q8_0", "sample": f"{n} tokens"}
+        sm = None
+    else:
+        sm = synth.named("small", seed=0)
+    if sm is None:
+        pass
+    elif args.workload == "score":
         ids = synth.token_ids(1, SEQ_LEN, sm.dims[5])
         vals = [cpu_baseline_score(sm, ids, cores) for _ in range(max(1, min(args.steps, 2)))]
         v, unit, metric = statistics.median(vals), "positions/s", "Q8_0 GPT-2-small log-likelihood positions/s"
@@ -278,6 +305,9 @@ def main():
                 "e2e": {"value": world * NEW_TOKENS / wall_s, "unit": "tokens/s", "h2d_bytes_per_step": PROMPT * 4 + 8,
                         "d2h_bytes_per_step": NEW_TOKENS * 4 + 8 + 32, "note": "includes priming the prompt (one window forward)"},
                 "gpu_launches": int(launches),
+                "cpu_baseline": (None if args.no_cpu_baseline else
+                                 {"value": cpu_baseline_llama(sml, synth.token_ids(0, 8, c["vocab"]), 4), "unit": "tokens/s", "cores": 1,
+                                  "kind": "port", "sample": "4 KV-cached steps after an 8-token prompt, 1 thread"}),
                 "scoring": {"value": world * 4 * T / (score_ms / 1e3), "unit": "positions/s", "ms_per_step": score_ms,
                             "tflops_algorithmic": flop_pos * 4 * T / (score_ms / 1e3) / 1e12,
                             "workload": "4 windows x 1024 ids, tcgen05 bf16x3 projections, exact log-softmax tail"}}))
