@@ -310,7 +310,7 @@ def main():
                                   "kind": "port", "sample": "4 KV-cached steps after an 8-token prompt, 1 thread"}),
                 "scoring": {"value": world * 4 * T / (score_ms / 1e3), "unit": "positions/s", "ms_per_step": score_ms,
                             "tflops_algorithmic": flop_pos * 4 * T / (score_ms / 1e3) / 1e12,
-                            "workload": "4 windows x 1024 ids, tcgen05 bf16x3 projections, exact log-softmax tail"}}))
+                            "workload": "4 windows x 1024 ids, tcgen05 bf16x3 projections and grouped-query attention, exact log-softmax tail"}}))
         gml.close()
         if world > 1:
             dist.destroy_process_group()

@@ -127,8 +127,11 @@ __device__ __forceinline__ void split2(float w0, float w1, uint32_t* hi, uint32_
 }
 
 struct AttnArgs {
-    int T, d, H;
-    uint16_t *out_hi, *out_lo;   // [R][d] bf16 planes
+    int T;
+    int k_col, v_col;            // first column of the key / value heads in the fused q | k | v planes
+    int group;                   // query heads per key / value head (1: multi-head attention)
+    int ldo;                     // row stride of the output planes (= query heads x 64)
+    uint16_t *out_hi, *out_lo;   // [R][ldo] bf16 planes
     int* status;
 };
 
@@ -176,12 +179,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_hi, const __grid_co
                 const uint32_t par = (kt & 1) ^ 1;
                 if (!wait_bar(bars, &bars->k_empty, par, a.status)) break;
                 mbar_expect_tx(&bars->k_full, 2 * KV_BYTES);
-                tma_load_2d(smem + OFF_K, &kv_hi, a.d + h * HD, row0 + kt * KT, &bars->k_full);
-                tma_load_2d(smem + OFF_K + KV_BYTES, &kv_lo, a.d + h * HD, row0 + kt * KT, &bars->k_full);
+                tma_load_2d(smem + OFF_K, &kv_hi, a.k_col + (h / a.group) * HD, row0 + kt * KT, &bars->k_full);
+                tma_load_2d(smem + OFF_K + KV_BYTES, &kv_lo, a.k_col + (h / a.group) * HD, row0 + kt * KT, &bars->k_full);
                 if (!wait_bar(bars, &bars->v_empty, par, a.status)) break;
                 mbar_expect_tx(&bars->v_full, 2 * KV_BYTES);
-                tma_load_2d(smem + OFF_V, &kv_hi, 2 * a.d + h * HD, row0 + kt * KT, &bars->v_full);
-                tma_load_2d(smem + OFF_V + KV_BYTES, &kv_lo, 2 * a.d + h * HD, row0 + kt * KT, &bars->v_full);
+                tma_load_2d(smem + OFF_V, &kv_hi, a.v_col + (h / a.group) * HD, row0 + kt * KT, &bars->v_full);
+                tma_load_2d(smem + OFF_V + KV_BYTES, &kv_lo, a.v_col + (h / a.group) * HD, row0 + kt * KT, &bars->v_full);
             }
         }
     } else if (warp == MMA_WARP) {
@@ -296,7 +299,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_hi, const __grid_co
         }
         if (ok && qi < a.T) {
             const float inv = 1.0f / l;
-            const size_t off = (size_t)(row0 + qi) * a.d + (size_t)h * HD;
+            const size_t off = (size_t)(row0 + qi) * a.ldo + (size_t)h * HD;
 #pragma unroll
             for (int c = 0; c < HD / 8; ++c) {
                 uint4 hi, lo;
@@ -344,10 +347,11 @@ int encode(CUtensorMap* map, const void* plane, size_t rows, size_t cols, int bo
 }
 }  // namespace
 
-// qkv_hi / qkv_lo: bf16 planes [B*T][3d] (q | k | v per row); out_hi / out_lo: planes [B*T][d].
-int launch_attn_prefill_tc(const void* qkv_hi, const void* qkv_lo, int B, int T, int d, int H, void* out_hi, void* out_lo,
-                           int* status, cudaStream_t st) {
-    if (d != H * HD) return fail(FC_E_SHAPE, "tensor-core attention needs head_dim 64 (d = %d, H = %d)", d, H);
+// qkv_hi / qkv_lo: bf16 planes [B*T][H*64 + 2*KV*64] (q heads | k heads | v heads per row);
+// out_hi / out_lo: planes [B*T][H*64]. Query head h reads key / value head h / (H / KV).
+int launch_attn_prefill_tc_gqa(const void* qkv_hi, const void* qkv_lo, int B, int T, int H, int KV, void* out_hi, void* out_lo,
+                               int* status, cudaStream_t st) {
+    if (KV <= 0 || H % KV) return fail(FC_E_DIM, "n_heads %d must be a multiple of n_kv_heads %d", H, KV);
     static bool attr_set[64] = {};
     int dev = 0;
     FC_CUDA(cudaGetDevice(&dev));
@@ -355,19 +359,26 @@ int launch_attn_prefill_tc(const void* qkv_hi, const void* qkv_lo, int B, int T,
         FC_CUDA(cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         attr_set[dev] = true;
     }
-    const size_t R = (size_t)B * T;
+    const size_t R = (size_t)B * T, ld = (size_t)(H + 2 * KV) * HD;
     CUtensorMap qh, ql, kh, kl;
-    FC_TRY(encode(&qh, qkv_hi, R, (size_t)3 * d, QT));
-    FC_TRY(encode(&ql, qkv_lo, R, (size_t)3 * d, QT));
-    FC_TRY(encode(&kh, qkv_hi, R, (size_t)3 * d, KT));
-    FC_TRY(encode(&kl, qkv_lo, R, (size_t)3 * d, KT));
+    FC_TRY(encode(&qh, qkv_hi, R, ld, QT));
+    FC_TRY(encode(&ql, qkv_lo, R, ld, QT));
+    FC_TRY(encode(&kh, qkv_hi, R, ld, KT));
+    FC_TRY(encode(&kl, qkv_lo, R, ld, KT));
     AttnArgs a;
-    a.T = T; a.d = d; a.H = H;
+    a.T = T; a.k_col = H * HD; a.v_col = (H + KV) * HD; a.group = H / KV; a.ldo = H * HD;
     a.out_hi = (uint16_t*)out_hi; a.out_lo = (uint16_t*)out_lo; a.status = status;
     dim3 grid((T + QT - 1) / QT, H, B);
     attn_prefill_tc_kernel<<<grid, THREADS, SMEM_BYTES, st>>>(qh, ql, kh, kl, a);
     FC_LAUNCHED();
     return FC_OK;
+}
+
+// The multi-head form: planes [B*T][3d] in, [B*T][d] out.
+int launch_attn_prefill_tc(const void* qkv_hi, const void* qkv_lo, int B, int T, int d, int H, void* out_hi, void* out_lo,
+                           int* status, cudaStream_t st) {
+    if (d != H * HD) return fail(FC_E_SHAPE, "tensor-core attention needs head_dim 64 (d = %d, H = %d)", d, H);
+    return launch_attn_prefill_tc_gqa(qkv_hi, qkv_lo, B, T, H, H, out_hi, out_lo, status, st);
 }
 
 }  // namespace fc

@@ -175,5 +175,8 @@ int launch_attn_prefill_gqa(const float* q, const float* k, const float* v, int 
 // planes of the attention output [B*T][d] out; `status` is raised on a timeout.
 int launch_attn_prefill_tc(const void* qkv_hi, const void* qkv_lo, int B, int T, int d, int H, void* out_hi, void* out_lo,
                            int* status, cudaStream_t st);
+// Grouped-query form: planes [B*T][(H + 2 KV) * 64] in (q heads | k heads | v heads), [B*T][H * 64] out.
+int launch_attn_prefill_tc_gqa(const void* qkv_hi, const void* qkv_lo, int B, int T, int H, int KV, void* out_hi, void* out_lo,
+                               int* status, cudaStream_t st);
 
 }  // namespace fc

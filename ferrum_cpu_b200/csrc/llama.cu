@@ -38,6 +38,7 @@ struct fc_llama {
     double* lp_d = nullptr;
     uint8_t* gr_d = nullptr;
     uint16_t *xhi = nullptr, *xlo = nullptr;
+    uint16_t *qkvhi = nullptr, *qkvlo = nullptr, *atthi = nullptr, *attlo = nullptr;   // planes around the tensor-core attention
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     float last_score_ms = 0.0f;
     bool force_fp32 = false;         // the batched prime keeps the cache rows at fp32 rounding
@@ -104,6 +105,12 @@ int gemm(fc_llama* m, const QMat& w, const float* x, const float* bias, const fl
     return launch_gemm_q8_fp32(w, x, bias, res, EPI_NONE, y, M, ldy, m->st);
 }
 
+// The window attention runs on tcgen05 when the math mode allows it and heads are 64 wide (the
+// rotated q | k | v rows are split into bf16 planes for it; its output planes feed the wo GEMM).
+bool tensor_attention(const fc_llama* m) {
+    return m->cfg.math_mode == FC_MATH_BF16X3 && m->cfg.head_dim == 64 && m->cfg.d_model % 64 == 0;
+}
+
 int ensure_workspace(fc_llama* m, int rows) {
     if (rows <= m->ws_rows) return FC_OK;
     m->ws_arena.release();
@@ -131,6 +138,10 @@ int ensure_workspace(fc_llama* m, int rows) {
         const size_t widest = std::max({d, F, (size_t)m->q_dim});
         FC_TRY(a.alloc_n(&m->xhi, R * widest));
         FC_TRY(a.alloc_n(&m->xlo, R * widest));
+        if (tensor_attention(m)) {
+            FC_TRY(a.alloc_n(&m->qkvhi, R * (size_t)m->qkv_dim)); FC_TRY(a.alloc_n(&m->qkvlo, R * (size_t)m->qkv_dim));
+            FC_TRY(a.alloc_n(&m->atthi, R * (size_t)m->q_dim));   FC_TRY(a.alloc_n(&m->attlo, R * (size_t)m->q_dim));
+        }
     }
     m->ws_rows = rows;
     m->head_chunk = (int)chunk;
@@ -149,8 +160,15 @@ int forward_rows(fc_llama* m, int B, int T, fc_llama_cache* fill = nullptr) {
     for (int l = 0; l < c.n_layer; ++l) {
         const LlamaLayerDev& L = m->layers[l];
         // LlamaBlock::forward_full (llm.rs:464-482)
-        FC_TRY(launch_llama_rmsnorm(m->x, L.attn_norm, c.norm_eps, R, d, m->n, nullptr, st));
-        FC_TRY(gemm(m, L.qkv, m->n, L.qkv_b, nullptr, m->qkv, R, m->qkv_dim));
+        const bool planes = m->cfg.math_mode == FC_MATH_BF16X3 && !m->force_fp32 && d % 64 == 0 && F % 64 == 0;
+        if (planes) {
+            // norms and the gate write the planes the next GEMM reads: no f32 copy of them, no split pass
+            FC_TRY(launch_llama_rmsnorm_planes(m->x, L.attn_norm, c.norm_eps, R, d, m->xhi, m->xlo, st));
+            FC_TRY(launch_gemm_q8_bf16x3(L.qkv, m->xhi, m->xlo, L.qkv_b, nullptr, EPI_NONE, m->qkv, R, m->qkv_dim, m->tc_status, st));
+        } else {
+            FC_TRY(launch_llama_rmsnorm(m->x, L.attn_norm, c.norm_eps, R, d, m->n, nullptr, st));
+            FC_TRY(gemm(m, L.qkv, m->n, L.qkv_b, nullptr, m->qkv, R, m->qkv_dim));
+        }
         FC_TRY(launch_llama_rope_rows(m->qkv, R, m->qkv_dim, T, c.n_head, c.n_kv_head, m->q_dim, c.head_dim, c.rope_dim,
                                       c.rope_type == FC_ROPE_NEOX, m->ftab, m->inv_linear, st));
         if (fill) {
@@ -158,13 +176,26 @@ int forward_rows(fc_llama* m, int B, int T, fc_llama_cache* fill = nullptr) {
             FC_TRY(launch_llama_store_kv_rows(m->qkv, R, m->qkv_dim, m->q_dim, m->kv_dim, fill->kc + l * layer_stride,
                                               fill->vc + l * layer_stride, st));
         }
-        FC_TRY(launch_attn_prefill_gqa(m->qkv, m->qkv + m->q_dim, m->qkv + m->q_dim + m->kv_dim, B, T, m->qkv_dim, c.n_head,
-                                       c.n_kv_head, c.head_dim, m->q_dim, m->att, st));
-        FC_TRY(gemm(m, L.wo, m->att, nullptr, m->x, m->x, R, d));
-        FC_TRY(launch_llama_rmsnorm(m->x, L.ffn_norm, c.norm_eps, R, d, m->n, nullptr, st));
-        FC_TRY(gemm(m, L.gateup, m->n, nullptr, nullptr, m->gu, R, 2 * F));
-        FC_TRY(launch_llama_swiglu(m->gu, R, F, m->hid, nullptr, st));
-        FC_TRY(gemm(m, L.down, m->hid, nullptr, m->x, m->x, R, d));
+        if (tensor_attention(m) && !m->force_fp32) {
+            FC_TRY(launch_split_bf16(m->qkv, m->qkvhi, m->qkvlo, (size_t)R * m->qkv_dim, st));
+            FC_TRY(launch_attn_prefill_tc_gqa(m->qkvhi, m->qkvlo, B, T, c.n_head, c.n_kv_head, m->atthi, m->attlo, m->tc_status, st));
+            FC_TRY(launch_gemm_q8_bf16x3(L.wo, m->atthi, m->attlo, nullptr, m->x, EPI_NONE, m->x, R, d, m->tc_status, st));
+        } else {
+            FC_TRY(launch_attn_prefill_gqa(m->qkv, m->qkv + m->q_dim, m->qkv + m->q_dim + m->kv_dim, B, T, m->qkv_dim, c.n_head,
+                                           c.n_kv_head, c.head_dim, m->q_dim, m->att, st));
+            FC_TRY(gemm(m, L.wo, m->att, nullptr, m->x, m->x, R, d));
+        }
+        if (planes) {
+            FC_TRY(launch_llama_rmsnorm_planes(m->x, L.ffn_norm, c.norm_eps, R, d, m->xhi, m->xlo, st));
+            FC_TRY(launch_gemm_q8_bf16x3(L.gateup, m->xhi, m->xlo, nullptr, nullptr, EPI_NONE, m->gu, R, 2 * F, m->tc_status, st));
+            FC_TRY(launch_llama_swiglu_planes(m->gu, R, F, m->xhi, m->xlo, st));
+            FC_TRY(launch_gemm_q8_bf16x3(L.down, m->xhi, m->xlo, nullptr, m->x, EPI_NONE, m->x, R, d, m->tc_status, st));
+        } else {
+            FC_TRY(launch_llama_rmsnorm(m->x, L.ffn_norm, c.norm_eps, R, d, m->n, nullptr, st));
+            FC_TRY(gemm(m, L.gateup, m->n, nullptr, nullptr, m->gu, R, 2 * F));
+            FC_TRY(launch_llama_swiglu(m->gu, R, F, m->hid, nullptr, st));
+            FC_TRY(gemm(m, L.down, m->hid, nullptr, m->x, m->x, R, d));
+        }
     }
     return launch_llama_rmsnorm(m->x, m->out_norm, c.norm_eps, R, d, m->n, nullptr, st);
 }

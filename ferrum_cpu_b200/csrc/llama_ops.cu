@@ -2,6 +2,8 @@
 // RMSNorm, rotary positions, the SwiGLU gate, the exact log-softmax scoring tail of
 // llm_score.rs and the greedy pick. All are HBM-bound elementwise / row-reduction work: one
 // block per row, coalesced accesses, fixed-order block reductions.
+#include <cuda_bf16.h>
+
 #include "llama_ops.cuh"
 #include "pdl.cuh"
 
@@ -98,6 +100,29 @@ __global__ void __launch_bounds__(256) llama_rmsnorm_kernel(const float* __restr
     const float inv = 1.0f / sqrtf(ms + eps);
     for (int c = threadIdx.x; c < d; c += blockDim.x) y[(size_t)blockIdx.x * d + c] = __fmul_rn(__fmul_rn(xr[c], inv), w[c]);
 }
+// The same with the result written as the bf16 hi / lo planes (y = hi + lo to 2^-17 relative)
+// that the tensor-core GEMM reads.
+__device__ __forceinline__ void store_planes(float y, __nv_bfloat16* hi, __nv_bfloat16* lo, size_t i) {
+    const __nv_bfloat16 h = __float2bfloat16_rn(y);
+    hi[i] = h;
+    lo[i] = __float2bfloat16_rn(y - __bfloat162float(h));
+}
+__global__ void __launch_bounds__(256) llama_rmsnorm_planes_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps,
+                                                                   int d, __nv_bfloat16* __restrict__ hi, __nv_bfloat16* __restrict__ lo) {
+    __shared__ float red[33];
+    const float* xr = x + (size_t)blockIdx.x * d;
+    float s = 0.0f;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) { const float v = xr[c]; s = fmaf(v, v, s); }
+    const float ms = block_sum_t(s, red) / (float)d;
+    const float inv = 1.0f / sqrtf(ms + eps);
+    for (int c = threadIdx.x; c < d; c += blockDim.x) store_planes(__fmul_rn(__fmul_rn(xr[c], inv), w[c]), hi, lo, (size_t)blockIdx.x * d + c);
+}
+int launch_llama_rmsnorm_planes(const float* x, const float* w, float eps, int rows, int d, void* hi, void* lo, cudaStream_t st) {
+    llama_rmsnorm_planes_kernel<<<rows, 256, 0, st>>>(x, w, eps, d, (__nv_bfloat16*)hi, (__nv_bfloat16*)lo);
+    FC_LAUNCHED();
+    return FC_OK;
+}
+
 int launch_llama_rmsnorm(const float* x, const float* w, float eps, int rows, int d, float* y, const StepState* state,
                          cudaStream_t st) {
     llama_rmsnorm_kernel<<<rows, 256, 0, st>>>(x, w, eps, d, y, state);
@@ -286,6 +311,21 @@ __global__ void llama_swiglu_kernel(const float* __restrict__ gu, int F, float* 
         h[(size_t)blockIdx.y * F + c] = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), u);
     }
 }
+__global__ void llama_swiglu_planes_kernel(const float* __restrict__ gu, int F, __nv_bfloat16* __restrict__ hi, __nv_bfloat16* __restrict__ lo) {
+    const float* row = gu + (size_t)blockIdx.y * 2 * F;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c < F) {
+        const float g = row[2 * c], u = row[2 * c + 1];
+        store_planes(__fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), u), hi, lo, (size_t)blockIdx.y * F + c);
+    }
+}
+int launch_llama_swiglu_planes(const float* gu, int rows, int F, void* hi, void* lo, cudaStream_t st) {
+    dim3 grid((F + 255) / 256, rows);
+    llama_swiglu_planes_kernel<<<grid, 256, 0, st>>>(gu, F, (__nv_bfloat16*)hi, (__nv_bfloat16*)lo);
+    FC_LAUNCHED();
+    return FC_OK;
+}
+
 int launch_llama_swiglu(const float* gu, int rows, int F, float* h, const StepState* state, cudaStream_t st) {
     dim3 grid((F + 255) / 256, rows);
     llama_swiglu_kernel<<<grid, 256, 0, st>>>(gu, F, h, state);

@@ -112,6 +112,8 @@ class SynthModel:
 LLAMA_SHAPES = {
     "llama-tiny": (512, 64, 2, 4, 2, 16, 128, 64),
     "llama-mini": (4096, 256, 4, 8, 2, 32, 704, 256),
+    # heads of 64 (the width the tensor-core window attention takes), two query heads per key/value head
+    "llama-hd64": (1024, 256, 2, 4, 2, 64, 512, 320),
     # the shape of a 1B-class GGUF (Llama-3.2-1B: 16 layers, 32 query / 8 key-value heads of 64)
     "llama-1b": (32000, 2048, 16, 32, 8, 64, 8192, 2048),
     # the same depth and head layout at a quarter of the width: what a step costs when the weights are small

@@ -151,6 +151,25 @@ def test_tensor_core_window_forward_stays_within_tolerance():
     assert sc.n_tokens == n and np.abs(glp - lp).max() < TOL
 
 
+def test_tensor_core_attention_with_grouped_heads():
+    # head_dim 64 in the bf16x3 mode: rotated q | k | v planes -> tcgen05 attention -> wo GEMM from planes
+    sm, om, gm = build("llama-hd64", math_mode=_lib.FC_MATH_BF16X3, seed=9, rope_type=1, qkv_bias=True)
+    V = sm.dims["vocab"]
+    ids = synth.token_ids(21, 300, V)
+    want, got = om.forward_tokens(ids), gm.forward_tokens(ids)
+    assert np.abs(got - want).max() < TOL
+    seqs = synth.token_ids(22, 3 * 100, V).reshape(3, 100)          # windows that are no multiple of the 128-row tile
+    scores, lp = gm.score_sequences(seqs, batch_windows=3, per_token=True)
+    for i in range(3):
+        total, n, greedy, wlp, _ = om.score_from(seqs[i], 1, 128)
+        assert scores[i].n_tokens == n and np.abs(lp[i] - wlp).max() < TOL
+    # the fp32 mode of the same model (SIMT attention) agrees with the tensor-core mode
+    sm.config.math_mode = _lib.FC_MATH_FP32
+    g32 = CudaLlama.from_synth(sm)
+    assert np.abs(g32.forward_tokens(ids) - got).max() < TOL
+    g32.close()
+
+
 def margins(om, prompt, tokens):
     """Top-two logit gap of the oracle at every generated position."""
     om.clear()
