@@ -396,9 +396,17 @@ __global__ void __launch_bounds__(1024) llama_pick_kernel(const float* __restric
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
     float mx = -INFINITY;
     int first = 0x7fffffff;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-        const float v = logits[i];
-        if (v > mx) { mx = v; first = i; }
+    // eight loads in flight per thread: the row is 128 KB read by one block
+    for (int i0 = threadIdx.x; i0 < V; i0 += 8 * blockDim.x) {
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int i = i0 + u * blockDim.x;
+            v[u] = i < V ? logits[i] : -INFINITY;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            if (v[u] > mx) { mx = v[u]; first = i0 + u * blockDim.x; }     // ascending i per thread: the first of a tie stays
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
