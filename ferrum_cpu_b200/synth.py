@@ -114,6 +114,8 @@ LLAMA_SHAPES = {
     "llama-mini": (4096, 256, 4, 8, 2, 32, 704, 256),
     # heads of 64 (the width the tensor-core window attention takes), two query heads per key/value head
     "llama-hd64": (1024, 256, 2, 4, 2, 64, 512, 320),
+    # widths that are no powers of two, seven query heads on one key/value head (the proportions of a small Qwen2)
+    "qwen-odd": (1536, 448, 2, 7, 1, 64, 1216, 160),
     # the shape of a 1B-class GGUF (Llama-3.2-1B: 16 layers, 32 query / 8 key-value heads of 64)
     "llama-1b": (32000, 2048, 16, 32, 8, 64, 8192, 2048),
     # the same depth and head layout at a quarter of the width: what a step costs when the weights are small

@@ -170,6 +170,23 @@ def test_tensor_core_attention_with_grouped_heads():
     g32.close()
 
 
+@pytest.mark.parametrize("mode,tol", [(_lib.FC_MATH_FP32, FP32_TOL), (_lib.FC_MATH_BF16X3, TOL)])
+def test_widths_that_are_no_powers_of_two(mode, tol):
+    sm, om, gm = build("qwen-odd", math_mode=mode, seed=4, rope_type=1, qkv_bias=True, tied=False, rope_base=1000000.0)
+    V = sm.dims["vocab"]
+    ids = synth.token_ids(31, 150, V)
+    want = om.forward_tokens(ids)
+    assert np.abs(gm.forward_tokens(ids) - want).max() < tol
+    cache = gm.new_cache()
+    for t, tok in enumerate(ids[:20]):                       # the ring GEMV with 28 and 76 chunks per row
+        assert np.abs(gm.forward_one(tok, cache) - want[t]).max() < FP32_TOL, t
+    primed = gm.prime(ids[:40], cache)
+    assert np.abs(primed - want[39]).max() < FP32_TOL
+    total, n, greedy, lp, gr = om.score_from(ids, 1, 64)
+    sc, glp, _ = gm.score_from(ids, 1, 64, per_token=True)
+    assert sc.n_tokens == n and np.abs(glp - lp).max() < tol
+
+
 def margins(om, prompt, tokens):
     """Top-two logit gap of the oracle at every generated position."""
     om.clear()
