@@ -180,4 +180,47 @@ int fc_rowq_to_f32(const uint8_t* q, const float* scales, int rows, int cols, in
     return FC_OK;
 }
 
+
+// ---- exact re-blocking of integer-level GGML formats to Q8_0 ---------------------------------
+size_t fc_ggml_block_bytes(int ggml_type) {
+    switch (ggml_type) {
+        case FC_GGML_Q4_0: return 18;   // f16 d + 16 bytes of nibbles (gguf/format.rs:116)
+        case FC_GGML_Q5_0: return 22;   // f16 d + 4 bytes of high bits + 16 bytes of nibbles (gguf/format.rs:118)
+        case FC_GGML_Q8_0: return 34;
+        default: return 0;
+    }
+}
+
+int fc_ggml_to_q8_0(int ggml_type, const void* raw, size_t n, void* out) {
+    if (!raw || !out) return FC_E_ARG;
+    const size_t bb = fc_ggml_block_bytes(ggml_type);
+    if (!bb || n % 32) return FC_E_FORMAT;
+    const uint8_t* src = (const uint8_t*)raw;
+    uint8_t* dst = (uint8_t*)out;
+    for (size_t b = 0; b < n / 32; ++b, src += bb, dst += 34) {
+        dst[0] = src[0]; dst[1] = src[1];                       // the f16 scale, untouched
+        int8_t* q = (int8_t*)(dst + 2);
+        if (ggml_type == FC_GGML_Q8_0) {
+            std::memcpy(q, src + 2, 32);
+        } else if (ggml_type == FC_GGML_Q4_0) {
+            // low nibble -> element j, high nibble -> element j + 16, centred at 8 (dequant.rs:73-80)
+            for (int j = 0; j < 16; ++j) {
+                q[j] = (int8_t)((src[2 + j] & 0x0F) - 8);
+                q[j + 16] = (int8_t)((src[2 + j] >> 4) - 8);
+            }
+        } else {
+            // the fifth bit of element j is bit j of qh, of element j + 16 bit j + 16 (dequant.rs:112-126)
+            uint32_t qh;
+            std::memcpy(&qh, src + 2, 4);
+            for (int j = 0; j < 16; ++j) {
+                const int x0 = (src[6 + j] & 0x0F) | (int)(((qh >> j) & 1u) << 4);
+                const int x1 = (src[6 + j] >> 4) | (int)(((qh >> (j + 16)) & 1u) << 4);
+                q[j] = (int8_t)(x0 - 16);
+                q[j + 16] = (int8_t)(x1 - 16);
+            }
+        }
+    }
+    return FC_OK;
+}
+
 }  // extern "C"

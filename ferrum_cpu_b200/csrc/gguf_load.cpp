@@ -24,7 +24,7 @@ using fc::fail;
 namespace {
 
 constexpr uint32_t kMagic = 0x46554747u;   // "GGUF"
-constexpr uint32_t T_F32 = 0, T_F16 = 1, T_Q8_0 = 8;
+constexpr uint32_t T_F32 = 0, T_F16 = 1, T_Q4_0 = 2, T_Q5_0 = 6, T_Q8_0 = 8;
 enum : uint32_t { VT_U8, VT_I8, VT_U16, VT_I16, VT_U32, VT_I32, VT_F32, VT_BOOL, VT_STRING, VT_ARRAY, VT_U64, VT_I64, VT_F64 };
 
 struct Tensor {
@@ -42,6 +42,8 @@ struct Meta {
 };
 
 struct File {
+    // Q4_0 / Q5_0 matrices re-blocked to Q8_0 (exactly: same scale, integer levels) on first use
+    mutable std::map<std::string, std::vector<uint8_t>> reblocked;
     std::vector<uint8_t> bytes;
     std::map<std::string, Meta> meta;        // scalars and short strings (arrays are skipped)
     std::map<std::string, Tensor> tensors;
@@ -121,6 +123,8 @@ uint64_t type_nbytes(uint32_t type, uint64_t n) {
         case T_F32: return n * 4;
         case T_F16: return n * 2;
         case T_Q8_0: return n % 32 ? 0 : n / 32 * 34;
+        case T_Q4_0: return n % 32 ? 0 : n / 32 * 18;
+        case T_Q5_0: return n % 32 ? 0 : n / 32 * 22;
         default: return 0;
     }
 }
@@ -189,9 +193,10 @@ int tensor(const File& f, const std::string& name, uint32_t type, uint64_t ne0, 
     auto it = f.tensors.find(name);
     if (it == f.tensors.end()) return fail(FC_E_FORMAT, "GGUF tensor %s is missing", name.c_str());
     const Tensor& t = it->second;
-    if (t.type != type)
+    const bool reblock = type == T_Q8_0 && (t.type == T_Q4_0 || t.type == T_Q5_0);
+    if (t.type != type && !reblock)
         return fail(FC_E_FORMAT, "GGUF tensor %s has ggml type %u, this engine needs %u (%s)", name.c_str(), t.type, type,
-                    type == T_Q8_0 ? "matrices stay packed as Q8_0" : "vectors are F32");
+                    type == T_Q8_0 ? "matrices stay packed: Q8_0, or Q4_0 / Q5_0 re-blocked to it" : "vectors are F32");
     const uint64_t d0 = t.dims[0], d1 = t.dims.size() > 1 ? t.dims[1] : 1;
     for (size_t k = 2; k < t.dims.size(); ++k)
         if (t.dims[k] != 1) return fail(FC_E_FORMAT, "GGUF tensor %s has more than two dimensions", name.c_str());
@@ -201,6 +206,16 @@ int tensor(const File& f, const std::string& name, uint32_t type, uint64_t ne0, 
     if (t.nbytes == 0 || f.data + t.offset > f.bytes.size() || t.nbytes > f.bytes.size() - f.data - t.offset)
         return fail(FC_E_FORMAT, "GGUF tensor %s runs past the end of the file", name.c_str());
     *out = f.bytes.data() + f.data + t.offset;
+    if (reblock) {
+        std::vector<uint8_t>& store = f.reblocked[name];
+        if (store.empty()) {
+            const uint64_t n = d0 * d1;
+            store.resize((size_t)(n / 32 * 34));
+            if (fc_ggml_to_q8_0((int)t.type, *out, (size_t)n, store.data()) != FC_OK)
+                return fail(FC_E_FORMAT, "GGUF tensor %s could not be re-blocked to Q8_0", name.c_str());
+        }
+        *out = store.data();
+    }
     return FC_OK;
 }
 

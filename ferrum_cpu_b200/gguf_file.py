@@ -11,7 +11,7 @@ import struct
 
 import numpy as np
 
-GGML_F32, GGML_Q8_0 = 0, 8
+GGML_F32, GGML_Q4_0, GGML_Q5_0, GGML_Q8_0 = 0, 2, 6, 8
 VT_U32, VT_F32, VT_STRING = 4, 6, 8
 
 
@@ -98,9 +98,12 @@ def _emit(path, meta, tensors, alignment, version):
     return path
 
 
-def write_llama_gguf(path, sm, arch="llama", alignment=32, version=3, extra_meta=(), extra_tensors=(), drop_meta=()):
+def write_llama_gguf(path, sm, arch="llama", alignment=32, version=3, extra_meta=(), extra_tensors=(), drop_meta=(), raw=None):
     """sm: synth.SynthLlama. Keys and tensor names as gguf/llama.rs:164-339 reads them. The file's
-    architecture decides the rotation (qwen2: split halves), so write `arch` to match sm's rope_type."""
+    architecture decides the rotation (qwen2: split halves), so write `arch` to match sm's rope_type.
+    raw: {tensor name: (ggml type, bytes)} stores a matrix in another block format (Q4_0, Q5_0) instead
+    of sm's Q8_0 bytes."""
+    raw = raw or {}
     c = sm.dims
     V, d, L, H, KV, hd, F, ctx = (c[k] for k in ("vocab", "d_model", "n_layer", "n_head", "n_kv_head", "head_dim", "d_ff", "ctx"))
     cfg = sm.config
@@ -123,8 +126,9 @@ def write_llama_gguf(path, sm, arch="llama", alignment=32, version=3, extra_meta
     meta = [m for m in meta if m[0] not in drop_meta] + list(extra_meta)
     tensors = []
 
-    def q8(name, raw, n, k):
-        tensors.append((name, (k, n), GGML_Q8_0, np.ascontiguousarray(raw, dtype=np.uint8).tobytes()))
+    def q8(name, data, n, k):
+        typ, data = raw.get(name, (GGML_Q8_0, data))
+        tensors.append((name, (k, n), typ, np.ascontiguousarray(data, dtype=np.uint8).tobytes()))
 
     def f32(name, v, dims):
         tensors.append((name, dims, GGML_F32, np.ascontiguousarray(v, dtype=np.float32).tobytes()))

@@ -86,6 +86,17 @@ int fc_device_count(void);
 int fc_q8_0_quantize(const float* x, size_t n, void* out);
 /* gguf/dequant.rs:37-49 dequant_q8_0. */
 int fc_q8_0_dequantize(const void* raw, size_t n, float* out);
+/* GGML block formats whose values are an f16 scale times a small integer re-blocked, exactly, to
+ * Q8_0 (same scale, the integer as the int8 level): type 8 Q8_0 (copied), 2 Q4_0 (level = nibble
+ * - 8, gguf/dequant.rs:66-83), 6 Q5_0 (level = 5-bit value - 16, gguf/dequant.rs:105-130). n
+ * values (n % 32 == 0) -> n/32*34 bytes. d * level is then the very product the reference's
+ * dequantiser forms, so every kernel here serves these files unchanged (at Q8_0's footprint).
+ * Formats with a minimum or sub-block scales (Q4_1, Q5_1, K-quants) are FC_E_FORMAT. */
+#define FC_GGML_Q4_0 2
+#define FC_GGML_Q5_0 6
+#define FC_GGML_Q8_0 8
+size_t fc_ggml_block_bytes(int ggml_type);   /* bytes of one 32-value block, 0 if not covered */
+int fc_ggml_to_q8_0(int ggml_type, const void* raw, size_t n, void* out);
 uint16_t fc_f32_to_f16(float v);  /* gguf_write/blocks.rs:12-61 */
 float fc_f16_to_f32(uint16_t h);  /* gguf/dequant.rs:7-35 */
 /* rng.rs:9-48 xorshift64*: seed -> state (0 is remapped), draws advance *state. */

@@ -7,7 +7,8 @@
 // Parity status: pinned on the reference's own unit tests — round trips bounded by half a step
 // (quant.rs:597-637), packed sizes (quant.rs:639-648,680-685), nibble sign extension
 // (quant.rs:650-656), qlinear against the dequantised serial sum (ops.rs:877-949) and against
-// the f32 linear within the reference's drift bounds (ops.rs:836-930).
+// the f32 linear within the reference's drift bounds (ops.rs:836-930); the Q4_0 / Q5_0 block
+// decoders on the reference's Q5 known-answer block (gguf/dequant.rs:371-393).
 #include <algorithm>
 #include <cmath>
 #include <cstdint>
@@ -56,6 +57,34 @@ int level_at(const uint8_t* q, int cols, int kind, int r, int c) {
 }  // namespace
 
 extern "C" {
+
+float fo_f16_to_f32(uint16_t h);   // ferrum_oracle.cpp
+
+// gguf/dequant.rs:66-83 dequant_q4_0: blocks of [f16 d][16 bytes]; low nibble -> element j, high
+// nibble -> element j + 16, value d * (nibble - 8).
+void fo_dequant_q4_0(const uint8_t* raw, size_t n, float* out) {
+    for (size_t b = 0; b < n / 32; ++b, raw += 18) {
+        const float d = fo_f16_to_f32((uint16_t)(raw[0] | (raw[1] << 8)));
+        for (int j = 0; j < 16; ++j) {
+            out[b * 32 + j] = d * (float)((int)(raw[2 + j] & 0x0F) - 8);
+            out[b * 32 + j + 16] = d * (float)((int)(raw[2 + j] >> 4) - 8);
+        }
+    }
+}
+// gguf/dequant.rs:105-130 dequant_q5 without a minimum (Q5_0): [f16 d][u32 qh][16 bytes];
+// value d * ((nibble | fifth bit << 4) - 16).
+void fo_dequant_q5_0(const uint8_t* raw, size_t n, float* out) {
+    for (size_t b = 0; b < n / 32; ++b, raw += 22) {
+        const float d = fo_f16_to_f32((uint16_t)(raw[0] | (raw[1] << 8)));
+        const uint32_t qh = (uint32_t)raw[2] | ((uint32_t)raw[3] << 8) | ((uint32_t)raw[4] << 16) | ((uint32_t)raw[5] << 24);
+        for (int j = 0; j < 16; ++j) {
+            const int x0 = (int)((raw[6 + j] & 0x0F) | (((qh >> j) & 1u) << 4));
+            const int x1 = (int)((raw[6 + j] >> 4) | (((qh >> (j + 16)) & 1u) << 4));
+            out[b * 32 + j] = d * (float)(x0 - 16);
+            out[b * 32 + j + 16] = d * (float)(x1 - 16);
+        }
+    }
+}
 
 int fo_nibble_to_i8(int nib) { return nibble_to_i8((uint8_t)nib); }
 size_t fo_rowq_packed_len(int rows, int cols, int kind) { return (size_t)rows * row_bytes(cols, kind); }

@@ -79,6 +79,8 @@ def lib():
         L.fo_llama_generate.restype = C.c_int
         L.fo_llama_generate.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_float, C.c_int, C.c_float, C.c_float,
                                         C.c_void_p, C.c_int, C.POINTER(C.c_uint64), C.c_void_p]
+        L.fo_dequant_q4_0.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p]
+        L.fo_dequant_q5_0.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p]
         L.fo_nibble_to_i8.restype, L.fo_nibble_to_i8.argtypes = C.c_int, [C.c_int]
         L.fo_rowq_packed_len.restype, L.fo_rowq_packed_len.argtypes = C.c_size_t, [C.c_int, C.c_int, C.c_int]
         L.fo_rowq_from_f32.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
@@ -375,3 +377,11 @@ def rowq_linear(x, q, scales, kind, bias, n):
     y = np.empty((m, n), dtype=np.float32)
     lib().fo_rowq_linear(_ptr(x), _ptr(q), _ptr(scales), kind, _ptr(bias), m, k, n, _ptr(y))
     return y
+
+
+def dequant_ggml(ggml_type, raw, n):
+    """gguf/dequant.rs dequant_q4_0 (type 2) / dequant_q5 without a minimum (type 6)."""
+    raw = np.ascontiguousarray(raw, dtype=np.uint8)
+    out = np.empty(n, dtype=np.float32)
+    {2: lib().fo_dequant_q4_0, 6: lib().fo_dequant_q5_0}[ggml_type](_ptr(raw), n, _ptr(out))
+    return out
