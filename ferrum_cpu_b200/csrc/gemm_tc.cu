@@ -376,6 +376,28 @@ gemm_q8_bf16x3_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_c
                             if (nb + i < a.N) a.y[off + i] = v[i];
                     }
                 } else {
+                    if (a.epi == EPI_SWIGLU) {
+                        // columns (2j, 2j + 1) are (gate_j, up_j) (llm.rs:417-428): 16 gated values, planes [M][N / 2]
+                        uint32_t hi8[8], lo8[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const float g0 = v[4 * i], g1 = v[4 * i + 2];
+                            const float h0 = __fmul_rn(__fdiv_rn(g0, __fadd_rn(1.0f, expf(-g0))), v[4 * i + 1]);
+                            const float h1 = __fmul_rn(__fdiv_rn(g1, __fadd_rn(1.0f, expf(-g1))), v[4 * i + 3]);
+                            split2(h0, h1, &hi8[i], &lo8[i]);
+                        }
+                        const size_t o2 = (size_t)m * a.ldy + (nb >> 1);
+                        if ((((uintptr_t)a.yhi | (uintptr_t)a.ylo) & 31) == 0 && (a.ldy & 15) == 0) {
+                            st256(a.yhi + o2, hi8);
+                            st256(a.ylo + o2, lo8);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 2; ++i) {
+                                *(uint4*)(a.yhi + o2 + 8 * i) = make_uint4(hi8[4 * i], hi8[4 * i + 1], hi8[4 * i + 2], hi8[4 * i + 3]);
+                                *(uint4*)(a.ylo + o2 + 8 * i) = make_uint4(lo8[4 * i], lo8[4 * i + 1], lo8[4 * i + 2], lo8[4 * i + 3]);
+                            }
+                        }
+                    } else {
                     // bf16 hi / lo planes for the next GEMM (ldy % 8 == 0, N % 32 == 0 for these outputs)
                     uint32_t hi[16], lo[16];
 #pragma unroll
@@ -392,6 +414,7 @@ gemm_q8_bf16x3_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_c
                             *(uint4*)(a.yhi + off + 8 * i) = make_uint4(hi[4 * i], hi[4 * i + 1], hi[4 * i + 2], hi[4 * i + 3]);
                             *(uint4*)(a.ylo + off + 8 * i) = make_uint4(lo[4 * i], lo[4 * i + 1], lo[4 * i + 2], lo[4 * i + 3]);
                         }
+                    }
                     }
                 }
                 }
@@ -461,6 +484,7 @@ int launch_gemm_q8_bf16x3_ex(const QMat& w, const void* x_hi, const void* x_lo, 
     if (w.K % BK) return fail(FC_E_SHAPE, "the tensor-core GEMM needs K %% 64 == 0 (K = %d)", w.K);
     if (!y && (!y_hi || !y_lo || (w.N & 31) || (ldy & 7) || residual))
         return fail(FC_E_SHAPE, "plane output needs N %% 32 == 0, ldy %% 8 == 0 and no residual");
+    if (epi == EPI_SWIGLU && (y || ldy < w.N / 2)) return fail(FC_E_SHAPE, "the SwiGLU epilogue writes planes [M][N / 2]");
     static int sms[64] = {};
     int dev = 0;
     FC_CUDA(cudaGetDevice(&dev));

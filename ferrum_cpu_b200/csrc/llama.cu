@@ -39,6 +39,7 @@ struct fc_llama {
     uint8_t* gr_d = nullptr;
     uint16_t *xhi = nullptr, *xlo = nullptr;
     uint16_t *qkvhi = nullptr, *qkvlo = nullptr, *atthi = nullptr, *attlo = nullptr;   // planes around the tensor-core attention
+    uint16_t *hidhi = nullptr, *hidlo = nullptr;                                       // gated hidden state, written by the gate/up GEMM
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     float last_score_ms = 0.0f;
     bool force_fp32 = false;         // the batched prime keeps the cache rows at fp32 rounding
@@ -138,6 +139,10 @@ int ensure_workspace(fc_llama* m, int rows) {
         const size_t widest = std::max({d, F, (size_t)m->q_dim});
         FC_TRY(a.alloc_n(&m->xhi, R * widest));
         FC_TRY(a.alloc_n(&m->xlo, R * widest));
+        if (d % 64 == 0 && F % 64 == 0) {
+            FC_TRY(a.alloc_n(&m->hidhi, R * F));
+            FC_TRY(a.alloc_n(&m->hidlo, R * F));
+        }
         if (tensor_attention(m)) {
             FC_TRY(a.alloc_n(&m->qkvhi, R * (size_t)m->qkv_dim)); FC_TRY(a.alloc_n(&m->qkvlo, R * (size_t)m->qkv_dim));
             FC_TRY(a.alloc_n(&m->atthi, R * (size_t)m->q_dim));   FC_TRY(a.alloc_n(&m->attlo, R * (size_t)m->q_dim));
@@ -187,9 +192,10 @@ int forward_rows(fc_llama* m, int B, int T, fc_llama_cache* fill = nullptr) {
         }
         if (planes) {
             FC_TRY(launch_llama_rmsnorm_planes(m->x, L.ffn_norm, c.norm_eps, R, d, m->xhi, m->xlo, st));
-            FC_TRY(launch_gemm_q8_bf16x3(L.gateup, m->xhi, m->xlo, nullptr, nullptr, EPI_NONE, m->gu, R, 2 * F, m->tc_status, st));
-            FC_TRY(launch_llama_swiglu_planes(m->gu, R, F, m->xhi, m->xlo, st));
-            FC_TRY(launch_gemm_q8_bf16x3(L.down, m->xhi, m->xlo, nullptr, m->x, EPI_NONE, m->x, R, d, m->tc_status, st));
+            // the gate is the GEMM's epilogue: interleaved (gate, up) columns -> planes of the gated hidden state
+            FC_TRY(launch_gemm_q8_bf16x3_ex(L.gateup, m->xhi, m->xlo, nullptr, nullptr, EPI_SWIGLU, nullptr, m->hidhi, m->hidlo, R, F,
+                                            m->tc_status, st));
+            FC_TRY(launch_gemm_q8_bf16x3(L.down, m->hidhi, m->hidlo, nullptr, m->x, EPI_NONE, m->x, R, d, m->tc_status, st));
         } else {
             FC_TRY(launch_llama_rmsnorm(m->x, L.ffn_norm, c.norm_eps, R, d, m->n, nullptr, st));
             FC_TRY(gemm(m, L.gateup, m->n, nullptr, nullptr, m->gu, R, 2 * F));

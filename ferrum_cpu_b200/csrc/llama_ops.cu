@@ -311,21 +311,6 @@ __global__ void llama_swiglu_kernel(const float* __restrict__ gu, int F, float* 
         h[(size_t)blockIdx.y * F + c] = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), u);
     }
 }
-__global__ void llama_swiglu_planes_kernel(const float* __restrict__ gu, int F, __nv_bfloat16* __restrict__ hi, __nv_bfloat16* __restrict__ lo) {
-    const float* row = gu + (size_t)blockIdx.y * 2 * F;
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c < F) {
-        const float g = row[2 * c], u = row[2 * c + 1];
-        store_planes(__fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), u), hi, lo, (size_t)blockIdx.y * F + c);
-    }
-}
-int launch_llama_swiglu_planes(const float* gu, int rows, int F, void* hi, void* lo, cudaStream_t st) {
-    dim3 grid((F + 255) / 256, rows);
-    llama_swiglu_planes_kernel<<<grid, 256, 0, st>>>(gu, F, (__nv_bfloat16*)hi, (__nv_bfloat16*)lo);
-    FC_LAUNCHED();
-    return FC_OK;
-}
-
 int launch_llama_swiglu(const float* gu, int rows, int F, float* h, const StepState* state, cudaStream_t st) {
     dim3 grid((F + 255) / 256, rows);
     llama_swiglu_kernel<<<grid, 256, 0, st>>>(gu, F, h, state);

@@ -17,9 +17,8 @@ int launch_llama_store_kv_rows(const float* qkv, int R, int ld, int q_dim, int k
 // in, attention output [n_q * hd] out.
 int launch_llama_attn_decode(const float* qkv, int n_q, int n_kv, int hd, int rope_dim, int neox, const float2* ftab, float inv_linear,
                              float* kc, float* vc, int ctx, const StepState* state, float* out, cudaStream_t st);
-// RMSNorm and SwiGLU written as the bf16 hi / lo planes [rows][d] / [rows][F] of the tensor-core GEMM.
+// RMSNorm written as the bf16 hi / lo planes [rows][d] of the tensor-core GEMM.
 int launch_llama_rmsnorm_planes(const float* x, const float* w, float eps, int rows, int d, void* hi, void* lo, cudaStream_t st);
-int launch_llama_swiglu_planes(const float* gu, int rows, int F, void* hi, void* lo, cudaStream_t st);
 int launch_llama_swiglu(const float* gu, int rows, int F, float* h, const StepState* state, cudaStream_t st);
 int launch_llama_score_rows(const float* logits, int ldl, int V, const int* targets, int R, double* logprob, uint8_t* is_greedy,
                             cudaStream_t st);
