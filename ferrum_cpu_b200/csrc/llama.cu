@@ -174,15 +174,21 @@ int forward_rows(fc_llama* m, int B, int T, fc_llama_cache* fill = nullptr) {
             FC_TRY(launch_llama_rmsnorm(m->x, L.attn_norm, c.norm_eps, R, d, m->n, nullptr, st));
             FC_TRY(gemm(m, L.qkv, m->n, L.qkv_b, nullptr, m->qkv, R, m->qkv_dim));
         }
-        FC_TRY(launch_llama_rope_rows(m->qkv, R, m->qkv_dim, T, c.n_head, c.n_kv_head, m->q_dim, c.head_dim, c.rope_dim,
-                                      c.rope_type == FC_ROPE_NEOX, m->ftab, m->inv_linear, st));
+        const bool tc_attn = tensor_attention(m) && !m->force_fp32 && !fill && (size_t)m->qkv_dim * 4 <= 48 * 1024;
+        if (tc_attn) {
+            // rotate and split in one pass: the attention reads planes, nothing reads the rotated f32 rows
+            FC_TRY(launch_llama_rope_planes(m->qkv, R, m->qkv_dim, T, c.n_head, c.n_kv_head, m->q_dim, c.head_dim, c.rope_dim,
+                                            c.rope_type == FC_ROPE_NEOX, m->ftab, m->inv_linear, m->qkvhi, m->qkvlo, st));
+        } else {
+            FC_TRY(launch_llama_rope_rows(m->qkv, R, m->qkv_dim, T, c.n_head, c.n_kv_head, m->q_dim, c.head_dim, c.rope_dim,
+                                          c.rope_type == FC_ROPE_NEOX, m->ftab, m->inv_linear, st));
+        }
         if (fill) {
             const size_t layer_stride = (size_t)c.ctx * m->kv_dim;
             FC_TRY(launch_llama_store_kv_rows(m->qkv, R, m->qkv_dim, m->q_dim, m->kv_dim, fill->kc + l * layer_stride,
                                               fill->vc + l * layer_stride, st));
         }
-        if (tensor_attention(m) && !m->force_fp32) {
-            FC_TRY(launch_split_bf16(m->qkv, m->qkvhi, m->qkvlo, (size_t)R * m->qkv_dim, st));
+        if (tc_attn) {
             FC_TRY(launch_attn_prefill_tc_gqa(m->qkvhi, m->qkvlo, B, T, c.n_head, c.n_kv_head, m->atthi, m->attlo, m->tc_status, st));
             FC_TRY(launch_gemm_q8_bf16x3(L.wo, m->atthi, m->attlo, nullptr, m->x, EPI_NONE, m->x, R, d, m->tc_status, st));
         } else {

@@ -159,6 +159,36 @@ __global__ void llama_rope_rows_kernel(float* __restrict__ qkv, int ld, int T, i
         rotate_pair(row, ia, ib, rope_angle(pos, ftab[i], inv_linear));
     }
 }
+// The same rotation with the row handed on as bf16 hi / lo planes (the input of the tensor-core
+// attention): the f32 row is staged in shared memory, rotated there and written once.
+__global__ void llama_rope_planes_kernel(const float* __restrict__ qkv, int ld, int T, int n_q, int n_kv, int k_off, int hd, int half,
+                                         int neox, const float2* __restrict__ ftab, float inv_linear,
+                                         __nv_bfloat16* __restrict__ hi, __nv_bfloat16* __restrict__ lo) {
+    extern __shared__ float srow[];
+    const int r = blockIdx.x, pos = r % T;
+    const float* row = qkv + (size_t)r * ld;
+    for (int c = threadIdx.x; c < ld; c += blockDim.x) srow[c] = row[c];
+    __syncthreads();
+    const int pairs = (n_q + n_kv) * half;
+    for (int u = threadIdx.x; u < pairs; u += blockDim.x) {
+        const int h = u / half, i = u - h * half;
+        const int off = h < n_q ? h * hd : k_off + (h - n_q) * hd;
+        const int ia = neox ? off + i : off + 2 * i, ib = neox ? off + i + half : off + 2 * i + 1;
+        rotate_pair(srow, ia, ib, rope_angle(pos, ftab[i], inv_linear));
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < ld; c += blockDim.x) store_planes(srow[c], hi, lo, (size_t)r * ld + c);
+}
+int launch_llama_rope_planes(const float* qkv, int R, int ld, int T, int n_q, int n_kv, int k_off, int hd, int rope_dim, int neox,
+                             const float2* ftab, float inv_linear, void* hi, void* lo, cudaStream_t st) {
+    const size_t smem = (size_t)ld * sizeof(float);
+    if (smem > 48 * 1024) return fail(FC_E_SHAPE, "fused q | k | v rows of %d floats exceed the rotation kernel's staging", ld);
+    llama_rope_planes_kernel<<<R, 256, smem, st>>>(qkv, ld, T, n_q, n_kv, k_off, hd, rope_dim / 2, neox, ftab, inv_linear,
+                                                   (__nv_bfloat16*)hi, (__nv_bfloat16*)lo);
+    FC_LAUNCHED();
+    return FC_OK;
+}
+
 int launch_llama_rope_rows(float* qkv, int R, int ld, int T, int n_q, int n_kv, int k_off, int hd, int rope_dim, int neox,
                            const float2* ftab, float inv_linear, cudaStream_t st) {
     llama_rope_rows_kernel<<<R, 256, 0, st>>>(qkv, ld, T, n_q, n_kv, k_off, hd, rope_dim / 2, neox, ftab, inv_linear);

@@ -5,6 +5,9 @@
 namespace fc {
 
 int launch_llama_embed_rows(const QMat& tok, const int* ids, int R, float* x, int* error_flag, cudaStream_t st);
+// Rotation of window rows with the result written as bf16 hi / lo planes [R][ld] (the f32 rows stay as they were).
+int launch_llama_rope_planes(const float* qkv, int R, int ld, int T, int n_q, int n_kv, int k_off, int hd, int rope_dim, int neox,
+                             const float2* ftab, float inv_linear, void* hi, void* lo, cudaStream_t st);
 int launch_llama_embed_step(const QMat& tok, int ctx, const int* queue, StepState* state, float* x, cudaStream_t st);
 int launch_llama_rmsnorm(const float* x, const float* w, float eps, int rows, int d, float* y, const StepState* state,
                          cudaStream_t st);
