@@ -217,11 +217,11 @@ int launch_llama_store_kv_rows(const float* qkv, int R, int ld, int q_dim, int k
 // of its group for the current position into shared memory, the first head of a group appends
 // the rotated key and the value row to the caches, and the scores run over the cached rows plus
 // that new row — so no other block's write is ever read.
-__global__ void __launch_bounds__(256) llama_attn_decode_kernel(const float* __restrict__ qkv, int n_q, int n_kv, int hd, int half,
+__global__ void __launch_bounds__(512) llama_attn_decode_kernel(const float* __restrict__ qkv, int n_q, int n_kv, int hd, int half,
                                                                 int neox, const float2* __restrict__ ftab, float inv_linear,
                                                                 float* __restrict__ kc, float* __restrict__ vc, int ctx,
                                                                 const StepState* st, float* __restrict__ out) {
-    extern __shared__ float sm[];   // scores[ctx] | q[hd] | k[hd] | v[hd] | red[64] | part[(256 / hd) * hd]
+    extern __shared__ float sm[];   // scores[ctx] | q[hd] | k[hd] | v[hd] | red[64] | part[(threads / hd) * hd]
     pdl_trigger();
     pdl_wait();
     if (st->done | st->error) return;
@@ -265,20 +265,27 @@ __global__ void __launch_bounds__(256) llama_attn_decode_kernel(const float* __r
     const int hw = tid >> 4, hl = tid & 15, nhw = blockDim.x >> 4;
     const unsigned hmask = 0xFFFFu << (tid & 16);
     float mx = -INFINITY;
-    for (int j = hw; j < len; j += nhw) {
+    // two rows per half warp and sweep: their loads are requested together
+    for (int j = hw; j < len; j += 2 * nhw) {
+        const int j2 = j + nhw;
+        const bool has2 = j2 < len;
         const float4* kr = j == pos ? (const float4*)kh : (const float4*)(kc + (size_t)j * kv_dim + (size_t)kvh * hd);
-        float dot = 0.0f;
+        const float4* kr2 = !has2 ? kr : (j2 == pos ? (const float4*)kh : (const float4*)(kc + (size_t)j2 * kv_dim + (size_t)kvh * hd));
+        float dot = 0.0f, dot2 = 0.0f;
         for (int c4 = hl; c4 < (hd >> 2); c4 += 16) {
-            const float4 kv = kr[c4], qv = ((const float4*)qh)[c4];
+            const float4 kv = kr[c4], kv2 = kr2[c4], qv = ((const float4*)qh)[c4];
             dot = fmaf(qv.x, kv.x, dot); dot = fmaf(qv.y, kv.y, dot); dot = fmaf(qv.z, kv.z, dot); dot = fmaf(qv.w, kv.w, dot);
+            dot2 = fmaf(qv.x, kv2.x, dot2); dot2 = fmaf(qv.y, kv2.y, dot2); dot2 = fmaf(qv.z, kv2.z, dot2); dot2 = fmaf(qv.w, kv2.w, dot2);
         }
-        dot += __shfl_xor_sync(hmask, dot, 8);
-        dot += __shfl_xor_sync(hmask, dot, 4);
-        dot += __shfl_xor_sync(hmask, dot, 2);
-        dot += __shfl_xor_sync(hmask, dot, 1);
-        const float s = dot * scale;
-        if (hl == 0) sc[j] = s;
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) {
+            dot += __shfl_xor_sync(hmask, dot, o);
+            dot2 += __shfl_xor_sync(hmask, dot2, o);
+        }
+        const float s = dot * scale, s2 = dot2 * scale;
+        if (hl == 0) { sc[j] = s; if (has2) sc[j2] = s2; }
         mx = fmaxf(mx, s);
+        if (has2) mx = fmaxf(mx, s2);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
@@ -302,12 +309,19 @@ __global__ void __launch_bounds__(256) llama_attn_decode_kernel(const float* __r
     const int G = blockDim.x / hd;
     const int g = tid / hd, c = tid - g * hd;
     if (g < G) {
-        float acc = 0.0f;
-        for (int j = g; j < len; j += G) {
-            const float v = j == pos ? vh[c] : vc[(size_t)j * kv_dim + (size_t)kvh * hd + c];
-            acc = fmaf(sc[j] / sum, v, acc);
+        // four rows in flight per thread; the four partial sums are added in a fixed order
+        float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+        const float* vbase = vc + (size_t)kvh * hd + c;
+        int j = g;
+        for (; j + 3 * G < len; j += 4 * G) {
+            const int j1 = j + G, j2 = j + 2 * G, j3 = j + 3 * G;
+            const float v0 = j == pos ? vh[c] : vbase[(size_t)j * kv_dim], v1 = j1 == pos ? vh[c] : vbase[(size_t)j1 * kv_dim];
+            const float v2 = j2 == pos ? vh[c] : vbase[(size_t)j2 * kv_dim], v3 = j3 == pos ? vh[c] : vbase[(size_t)j3 * kv_dim];
+            a0 = fmaf(sc[j] / sum, v0, a0); a1 = fmaf(sc[j1] / sum, v1, a1);
+            a2 = fmaf(sc[j2] / sum, v2, a2); a3 = fmaf(sc[j3] / sum, v3, a3);
         }
-        part[g * hd + c] = acc;
+        for (; j < len; j += G) a0 = fmaf(sc[j] / sum, j == pos ? vh[c] : vbase[(size_t)j * kv_dim], a0);
+        part[g * hd + c] = (a0 + a1) + (a2 + a3);
     }
     __syncthreads();
     if (tid < hd) {
@@ -319,7 +333,7 @@ __global__ void __launch_bounds__(256) llama_attn_decode_kernel(const float* __r
 int launch_llama_attn_decode(const float* qkv, int n_q, int n_kv, int hd, int rope_dim, int neox, const float2* ftab, float inv_linear,
                              float* kc, float* vc, int ctx, const StepState* state, float* out, cudaStream_t st) {
     if (hd > 256 || hd % 4) return fail(FC_E_SHAPE, "head_dim %d must be a multiple of 4, at most 256", hd);
-    const int threads = 256;
+    const int threads = 512;
     const size_t smem = (size_t)(((ctx + 3) & ~3) + 3 * hd + 64 + (threads / hd) * hd) * sizeof(float);
     if (smem > 200 * 1024) return fail(FC_E_SHAPE, "context %d exceeds what the decode attention holds in shared memory", ctx);
     if (smem > 48 * 1024) FC_CUDA(cudaFuncSetAttribute(llama_attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
