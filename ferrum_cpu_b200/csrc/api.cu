@@ -113,6 +113,24 @@ struct MegaTable {
     fc::MegaLayer* layers = nullptr;
 };
 
+// Buffers of the lock-step decode of many streams (fc_decode_batch), for up to `cap` streams.
+struct BatchCtx {
+    Arena arena;                       // step buffers
+    Arena frag_arena;                  // fragment-major weight copies, made on first use
+    bool frags = false;
+    std::vector<fc::QFrag> qkv, out, up, down;
+    fc::QFrag head;
+    int cap = 0, out_cap = 0;
+    float *x = nullptr, *qkv_f = nullptr, *logits = nullptr;
+    void *xp = nullptr, *ap = nullptr, *hp = nullptr;      // f16 hi / lo rows of LayerNorm output, attention output, GELU output
+    int *cur = nullptr, *done = nullptr, *n_out = nullptr, *out_tok = nullptr, *pos = nullptr;
+    float **kcs = nullptr, **vcs = nullptr;
+    int** queues = nullptr;
+    fc::StepState** states = nullptr;
+    cudaGraphExec_t graph = nullptr;   // one step, captured for (graph_S, graph_eos, out_cap)
+    int graph_S = 0, graph_eos = 0, graph_cap = 0, graph_nodes = 0;
+};
+
 struct fc_model {
     fc_config cfg;
     int device;
@@ -145,6 +163,7 @@ struct fc_model {
     // streams created by fc_decode_batch, kept for the next call
     std::vector<fc_stream*> pool;
     float last_batch_ms = 0.0f;
+    BatchCtx batch;
 };
 
 struct fc_stream {
@@ -470,6 +489,8 @@ void fc_qweight_free(fc_qweight* w) {
 int fc_q8_0_linear_dev(const fc_qweight* w, const float* x_dev, const float* bias_dev, float* y_dev,
                        int M, int math_mode, void* cuda_stream) {
     if (!w || !x_dev || !y_dev) return fail(FC_E_ARG, "fc_q8_0_linear_dev: null argument");
+    if (!aligned16(x_dev) || !aligned16(y_dev) || !aligned16(bias_dev))
+        return fail(FC_E_ARG, "fc_q8_0_linear_dev: x_dev, y_dev and bias_dev must be 16-byte aligned");
     if (M < 0) return fail(FC_E_SHAPE, "fc_q8_0_linear_dev: M = %d", M);
     if (M == 0) return FC_OK;
     if (math_mode != FC_MATH_FP32 && math_mode != FC_MATH_BF16X3) return fail(FC_E_ARG, "unknown math_mode %d", math_mode);
@@ -670,6 +691,9 @@ void fc_model_free(fc_model* m) {
     m->pool.clear();
     m->arena.release();
     m->ws_arena.release();
+    if (m->batch.graph) cudaGraphExecDestroy(m->batch.graph);
+    m->batch.arena.release();
+    m->batch.frag_arena.release();
     if (m->ev0) cudaEventDestroy(m->ev0);
     if (m->ev1) cudaEventDestroy(m->ev1);
     if (m->st) cudaStreamDestroy(m->st);
@@ -980,7 +1004,8 @@ __global__ void bump_state_kernel(StepState* st, int by) {
 // rows the GEMMs run on small tiles so that every SM gets one.
 // Returns FC_OK with *used = 0 when the shape is not covered (the caller feeds token by token).
 constexpr int kPrimeBatchMin = 8;
-static int prime_batched(fc_stream* const* ss, int S, int n, int last_mode, int* used) {
+static int prime_batched(fc_stream* const* ss, int S, int n, int last_mode, int* used, float* const* kcs_dev = nullptr,
+                         float* const* vcs_dev = nullptr) {
     fc_model* m = ss[0]->m;
     const fc_config& c = m->cfg;
     const int d = c.d_model, F = c.d_ff, hd = d / c.n_head, R = S * n;
@@ -995,11 +1020,9 @@ static int prime_batched(fc_stream* const* ss, int S, int n, int last_mode, int*
     FC_CUDA(cudaMemsetAsync(m->err_d, 0, sizeof(int), st));
     FC_TRY(launch_embed_rows(m->tok, m->pos, m->ids_d, R, n, m->x, m->err_d, st));
     const size_t layer_stride = (size_t)c.ctx * d;
-    for (int l = 0; l < c.n_layer; ++l) {
-        const LayerDev& L = m->layers[l];
-        FC_TRY(launch_layernorm(m->x, L.ln1g, L.ln1b, R, d, m->n, nullptr, st));
-        FC_TRY(launch_gemm_q8_fp32(L.qkv, m->n, L.qkv_b, nullptr, EPI_NONE, m->qkv, R, 3 * d, st));
-        // rows [q | k | v] of window i -> cache positions 0..n-1 of stream i
+    // rows [q | k | v] of window i -> cache positions 0..n-1 of stream i
+    auto to_caches = [&](int l) -> int {
+        if (kcs_dev && vcs_dev) return launch_scatter_kv(m->qkv, kcs_dev, vcs_dev, l * layer_stride, S, n, d, st);
         for (int i = 0; i < S; ++i) {
             const float* rows = m->qkv + (size_t)i * n * 3 * d;
             FC_CUDA(cudaMemcpy2DAsync(ss[i]->kc + l * layer_stride, (size_t)d * 4, rows + d, (size_t)3 * d * 4, (size_t)d * 4, n,
@@ -1007,11 +1030,35 @@ static int prime_batched(fc_stream* const* ss, int S, int n, int last_mode, int*
             FC_CUDA(cudaMemcpy2DAsync(ss[i]->vc + l * layer_stride, (size_t)d * 4, rows + 2 * d, (size_t)3 * d * 4, (size_t)d * 4, n,
                                       cudaMemcpyDeviceToDevice, st));
         }
-        FC_TRY(launch_attn_prefill(m->qkv, S, n, d, c.n_head, m->att, st));
-        FC_TRY(launch_gemm_q8_fp32(L.out, m->att, L.out_b, m->x, EPI_NONE, m->x, R, d, st));
-        FC_TRY(launch_layernorm(m->x, L.ln2g, L.ln2b, R, d, m->n, nullptr, st));
-        FC_TRY(launch_gemm_q8_fp32(L.up, m->n, L.up_b, nullptr, EPI_GELU, m->hid, R, F, st));
-        FC_TRY(launch_gemm_q8_fp32(L.down, m->hid, L.down_b, m->x, EPI_NONE, m->x, R, d, st));
+        return FC_OK;
+    };
+    if (tensor_path(m) && R >= 256) {
+        // many rows: the window forward of the scoring path (tcgen05 GEMMs and attention on bf16 hi / lo
+        // planes); the QKV product also leaves f32 rows, which feed the caches
+        for (int l = 0; l < c.n_layer; ++l) {
+            const LayerDev& L = m->layers[l];
+            FC_TRY(launch_layernorm_planes(m->x, L.ln1g, L.ln1b, R, d, m->nhi, m->nlo, st));
+            FC_TRY(launch_gemm_q8_bf16x3_ex(L.qkv, m->nhi, m->nlo, L.qkv_b, nullptr, EPI_NONE, m->qkv, nullptr, nullptr, R, 3 * d, m->tc_status, st));
+            FC_TRY(to_caches(l));
+            FC_TRY(launch_split_bf16(m->qkv, m->qkvhi, m->qkvlo, (size_t)R * 3 * d, st));
+            FC_TRY(launch_attn_prefill_tc(m->qkvhi, m->qkvlo, S, n, d, c.n_head, m->atthi, m->attlo, m->tc_status, st));
+            FC_TRY(launch_gemm_q8_bf16x3_ex(L.out, m->atthi, m->attlo, L.out_b, m->x, EPI_NONE, m->x, nullptr, nullptr, R, d, m->tc_status, st));
+            FC_TRY(launch_layernorm_planes(m->x, L.ln2g, L.ln2b, R, d, m->nhi, m->nlo, st));
+            FC_TRY(launch_gemm_q8_bf16x3_ex(L.up, m->nhi, m->nlo, L.up_b, nullptr, EPI_GELU, nullptr, m->hidhi, m->hidlo, R, F, m->tc_status, st));
+            FC_TRY(launch_gemm_q8_bf16x3_ex(L.down, m->hidhi, m->hidlo, L.down_b, m->x, EPI_NONE, m->x, nullptr, nullptr, R, d, m->tc_status, st));
+        }
+    } else {
+        for (int l = 0; l < c.n_layer; ++l) {
+            const LayerDev& L = m->layers[l];
+            FC_TRY(launch_layernorm(m->x, L.ln1g, L.ln1b, R, d, m->n, nullptr, st));
+            FC_TRY(launch_gemm_q8_fp32(L.qkv, m->n, L.qkv_b, nullptr, EPI_NONE, m->qkv, R, 3 * d, st));
+            FC_TRY(to_caches(l));
+            FC_TRY(launch_attn_prefill(m->qkv, S, n, d, c.n_head, m->att, st));
+            FC_TRY(launch_gemm_q8_fp32(L.out, m->att, L.out_b, m->x, EPI_NONE, m->x, R, d, st));
+            FC_TRY(launch_layernorm(m->x, L.ln2g, L.ln2b, R, d, m->n, nullptr, st));
+            FC_TRY(launch_gemm_q8_fp32(L.up, m->n, L.up_b, nullptr, EPI_GELU, m->hid, R, F, st));
+            FC_TRY(launch_gemm_q8_fp32(L.down, m->hid, L.down_b, m->x, EPI_NONE, m->x, R, d, st));
+        }
     }
     *used = 1;
     for (int i = 0; i < S; ++i) {
@@ -1257,13 +1304,129 @@ int fc_generate_sampled(fc_stream* s, const int32_t* prompt, int n, int max_new,
     return FC_OK;
 }
 
+// ------------------------------------------------------------------- lock-step decode
+// Fragment-major copies of every matrix, made once per model on the first batched decode.
+static int batch_make_frags(fc_model* m) {
+    BatchCtx& b = m->batch;
+    if (b.frags) return FC_OK;
+    cudaStream_t st = m->st;
+    auto make = [&](const QMat& w, QFrag* out) -> int {
+        void *q = nullptr, *d = nullptr;
+        FC_TRY(b.frag_arena.alloc(&q, frag_quant_bytes(w)));
+        FC_TRY(b.frag_arena.alloc(&d, frag_scale_bytes(w)));
+        FC_TRY(launch_repack_frag(w, q, d, st));
+        out->q = q; out->d = d; out->N = w.N; out->K = w.K; out->N_pad = w.N_pad;
+        return FC_OK;
+    };
+    const int L = m->cfg.n_layer;
+    b.qkv.resize(L); b.out.resize(L); b.up.resize(L); b.down.resize(L);
+    int rc = FC_OK;
+    for (int l = 0; l < L && rc == FC_OK; ++l) {
+        rc = make(m->layers[l].qkv, &b.qkv[l]);
+        if (rc == FC_OK) rc = make(m->layers[l].out, &b.out[l]);
+        if (rc == FC_OK) rc = make(m->layers[l].up, &b.up[l]);
+        if (rc == FC_OK) rc = make(m->layers[l].down, &b.down[l]);
+    }
+    if (rc == FC_OK) rc = make(m->head, &b.head);
+    if (rc == FC_OK && cudaStreamSynchronize(st) != cudaSuccess) rc = fail(FC_E_CUDA, "fragment-major weight copy failed");
+    if (rc != FC_OK) { b.frag_arena.release(); return rc; }
+    b.frags = true;
+    return FC_OK;
+}
+
+static int batch_ensure(fc_model* m, int S, int out_cap) {
+    BatchCtx& b = m->batch;
+    if (S <= b.cap && out_cap <= b.out_cap) return FC_OK;
+    FC_CUDA(cudaStreamSynchronize(m->st));
+    if (b.graph) { cudaGraphExecDestroy(b.graph); b.graph = nullptr; }
+    b.arena.release();
+    b.cap = b.out_cap = 0;
+    const fc_config& c = m->cfg;
+    const size_t cap = std::max(S, b.cap), oc = std::max(out_cap, b.out_cap), C = kBatchMaxStreams * 2;
+    const size_t d = c.d_model, F = c.d_ff;
+    Arena& a = b.arena;
+    FC_TRY(a.alloc_n(&b.x, cap * d));
+    FC_TRY(a.alloc_n(&b.qkv_f, cap * 3 * d));
+    FC_TRY(a.alloc_n(&b.logits, cap * (size_t)m->head.N_pad));
+    FC_TRY(a.alloc(&b.xp, C * d * 2));
+    FC_TRY(a.alloc(&b.ap, C * d * 2));
+    FC_TRY(a.alloc(&b.hp, C * F * 2));
+    // rows past the live streams are read by the MMA tiles: they stay zero
+    FC_CUDA(cudaMemsetAsync(b.xp, 0, C * d * 2, m->st));
+    FC_CUDA(cudaMemsetAsync(b.ap, 0, C * d * 2, m->st));
+    FC_CUDA(cudaMemsetAsync(b.hp, 0, C * F * 2, m->st));
+    FC_TRY(a.alloc_n(&b.cur, cap));
+    FC_TRY(a.alloc_n(&b.done, cap));
+    FC_TRY(a.alloc_n(&b.n_out, cap));
+    FC_TRY(a.alloc_n(&b.out_tok, cap * std::max<size_t>(oc, 1)));
+    FC_TRY(a.alloc_n(&b.pos, 1));
+    FC_TRY(a.alloc_n(&b.kcs, cap));
+    FC_TRY(a.alloc_n(&b.vcs, cap));
+    FC_TRY(a.alloc_n(&b.queues, cap));
+    FC_TRY(a.alloc_n(&b.states, cap));
+    b.cap = (int)cap;
+    b.out_cap = (int)oc;
+    return FC_OK;
+}
+
+// One step for S streams: CachedTransformer::feed (cached.rs:100-125) on every stream's current
+// token at the shared position, then the greedy pick per stream.
+static int batch_launch_step(fc_model* m, int S, int eos) {
+    const fc_config& c = m->cfg;
+    BatchCtx& b = m->batch;
+    cudaStream_t st = m->st;
+    const int d = c.d_model, F = c.d_ff;
+    const size_t layer_stride = (size_t)c.ctx * d;
+    FC_TRY(launch_embed_batch(m->tok, m->pos, b.cur, b.pos, S, b.x, st));
+    for (int l = 0; l < c.n_layer; ++l) {
+        const LayerDev& L = m->layers[l];
+        FC_TRY(launch_ln_rows_f16(b.x, L.ln1g, L.ln1b, S, d, b.xp, st));
+        FC_TRY(launch_skinny_q8(b.qkv[l], b.xp, S, L.qkv_b, nullptr, 0, EPI_NONE, b.qkv_f, 3 * d, nullptr, 0, st));
+        FC_TRY(launch_attn_decode_batch(b.qkv_f, b.kcs, b.vcs, l * layer_stride, d, c.n_head, c.ctx, b.pos, S, b.ap, st));
+        FC_TRY(launch_skinny_q8(b.out[l], b.ap, S, L.out_b, b.x, d, EPI_NONE, b.x, d, nullptr, 0, st));
+        FC_TRY(launch_ln_rows_f16(b.x, L.ln2g, L.ln2b, S, d, b.xp, st));
+        FC_TRY(launch_skinny_q8(b.up[l], b.xp, S, L.up_b, nullptr, 0, EPI_GELU, nullptr, 0, b.hp, F, st));
+        FC_TRY(launch_skinny_q8(b.down[l], b.hp, S, L.down_b, b.x, d, EPI_NONE, b.x, d, nullptr, 0, st));
+    }
+    FC_TRY(launch_ln_rows_f16(b.x, m->lnfg, m->lnfb, S, d, b.xp, st));
+    FC_TRY(launch_skinny_q8(b.head, b.xp, S, nullptr, nullptr, 0, EPI_NONE, b.logits, m->head.N_pad, nullptr, 0, st));
+    return launch_pick_batch(b.logits, m->head.N_pad, c.vocab, S, eos, b.cur, b.done, b.n_out, b.out_tok, b.out_cap, b.pos, 1, st);
+}
+
+// The step is launch-bound (7 small kernels per block): it is captured once into a CUDA graph and
+// replayed; position and tokens are read from device memory, so no node changes between steps.
+static int batch_run_step(fc_model* m, int S, int eos) {
+    BatchCtx& b = m->batch;
+    if (!b.graph || b.graph_S != S || b.graph_eos != eos || b.graph_cap != b.out_cap) {
+        if (b.graph) { cudaGraphExecDestroy(b.graph); b.graph = nullptr; }
+        cudaGraph_t g = nullptr;
+        const int64_t before = g_launches;
+        FC_CUDA(cudaStreamBeginCapture(m->st, cudaStreamCaptureModeThreadLocal));
+        const int rc = batch_launch_step(m, S, eos);
+        const cudaError_t e = cudaStreamEndCapture(m->st, &g);
+        b.graph_nodes = (int)(g_launches - before);
+        g_launches = before;
+        if (rc != FC_OK) { if (g) cudaGraphDestroy(g); return rc; }
+        FC_CUDA(e);
+        const cudaError_t ei = cudaGraphInstantiate(&b.graph, g, 0);
+        cudaGraphDestroy(g);
+        FC_CUDA(ei);
+        b.graph_S = S; b.graph_eos = eos; b.graph_cap = b.out_cap;
+    }
+    FC_CUDA(cudaGraphLaunch(b.graph, m->st));
+    g_launches += b.graph_nodes;
+    return FC_OK;
+}
+
 // Independent greedy streams on one GPU (the 64-stream workload is split over GPUs above the
-// ABI). Each stream is a CachedTransformer of its own. Up to eight of them decode side by side:
-// every stream gets its own CUDA stream and a persistent kernel that spans an eighth (quarter,
-// half) of the SMs, so the kernels of a wave are co-resident and their latency-bound phases
-// overlap. The prompts are primed one after the other on the model's stream (the prime shares
-// the model's prefill workspace). Streams that would outgrow the context, and models the
-// persistent kernel does not cover, run one after the other through fc_generate_greedy.
+// ABI). Each stream is a CachedTransformer of its own (its own KV caches and window); the
+// streams advance in lock step, up to 64 at a time: the prompts are primed as one batch of
+// windows, then every step runs all streams through each Q8_0 matrix at once, so the weights
+// are read once per step whatever the number of streams. A stream that picks `eos` stops
+// emitting; the others go on. The reference's extra feed after the last sampled token
+// (token_stream.rs:181-186) is not run: its distribution is never used.
+// Streams that would outgrow the context (they need the re-prime of token_stream.rs:162-165)
+// and single streams run one after the other through fc_generate_greedy.
 int fc_decode_batch(fc_model* m, int n_streams, const int32_t* prompts, int prompt_len, int max_new, int32_t eos,
                     int32_t* out, int* n_out) {
     if (!m || !prompts || !n_out || (max_new > 0 && !out)) return fail(FC_E_ARG, "fc_decode_batch: null argument");
@@ -1276,12 +1439,10 @@ int fc_decode_batch(fc_model* m, int n_streams, const int32_t* prompts, int prom
         m->pool.push_back(s);
     }
     m->last_batch_ms = 0.0f;
-    // widest wave the parameter tables allow: table t holds grids of (all SMs) / 2^t
-    int t = 0;
-    while (t + 1 < (int)m->mega_tables.size() && (2 << t) <= n_streams) ++t;
-    const int wave = 1 << t;
-    const bool side_by_side = wave > 1 && max_new > 0 && prompt_len + max_new <= c.ctx;
-    if (!side_by_side) {
+    const int hd = c.d_model / c.n_head;
+    const bool lock_step = n_streams >= 2 && max_new > 0 && prompt_len + max_new <= c.ctx && hd <= 64 && hd % 4 == 0 &&
+                           (size_t)(c.ctx + 4 + 64 + 1024) * sizeof(float) <= 48 * 1024;
+    if (!lock_step) {
         for (int i = 0; i < n_streams; ++i) {
             FC_TRY(fc_generate_greedy(m->pool[i], prompts + (size_t)i * prompt_len, prompt_len, max_new, eos, nullptr,
                                       out + (size_t)i * max_new, n_out + i));
@@ -1290,72 +1451,70 @@ int fc_decode_batch(fc_model* m, int n_streams, const int32_t* prompts, int prom
         return FC_OK;
     }
     FC_TRY(check_ids(m, prompts, (size_t)n_streams * prompt_len));
+    FC_TRY(batch_make_frags(m));
+    FC_TRY(batch_ensure(m, std::min(n_streams, kBatchMaxStreams), max_new));
+    BatchCtx& b = m->batch;
     cudaStream_t st = m->st;
-    int rc = FC_OK;
     FC_CUDA(cudaEventRecord(m->ev0, st));
-    for (int w0 = 0; w0 < n_streams && rc == FC_OK; w0 += wave) {
-        const int nw = std::min(wave, n_streams - w0);
-        // every prompt of the wave is primed first, on the model's stream with the whole GPU:
-        // as one batch of windows when the shape allows it, else stream by stream; the last
-        // prime step selects token 1
+    for (int w0 = 0; w0 < n_streams; w0 += kBatchMaxStreams) {
+        const int S = std::min(kBatchMaxStreams, n_streams - w0);
+        // prime: all prompts of the wave as one batch of windows; the last row of each selects token 1
         std::vector<fc_stream*> wv;
-        for (int i = 0; i < nw && rc == FC_OK; ++i) {
+        for (int i = 0; i < S; ++i) {
             fc_stream* s = m->pool[w0 + i];
-            if (!s->use_mega) { rc = fail(FC_E_SHAPE, "fc_decode_batch: a stream is not on the persistent kernel"); break; }
-            if (!s->cs && cudaStreamCreateWithFlags(&s->cs, cudaStreamNonBlocking) != cudaSuccess) { rc = fail(FC_E_CUDA, "stream creation failed"); break; }
-            if (!s->cs_done && cudaEventCreateWithFlags(&s->cs_done, cudaEventDisableTiming) != cudaSuccess) { rc = fail(FC_E_CUDA, "event creation failed"); break; }
             s->table = 0;
-            rc = fc_stream_reset(s);
-            if (rc == FC_OK && cudaMemcpyAsync(s->queue, prompts + (size_t)(w0 + i) * prompt_len, (size_t)prompt_len * 4,
-                                               cudaMemcpyHostToDevice, st) != cudaSuccess) rc = fail(FC_E_CUDA, "prompt upload failed");
-            if (rc == FC_OK) rc = set_state(s, 0, 0, prompt_len, eos, 0);
+            FC_TRY(fc_stream_reset(s));
+            FC_CUDA(cudaMemcpyAsync(s->queue, prompts + (size_t)(w0 + i) * prompt_len, (size_t)prompt_len * 4, cudaMemcpyHostToDevice, st));
+            FC_TRY(set_state(s, 0, 0, prompt_len, eos, 0));
             wv.push_back(s);
         }
+        // per-stream pointers for the step kernels
+        std::vector<float*> kcs(S), vcs(S);
+        std::vector<int*> queues(S);
+        std::vector<StepState*> states(S);
+        for (int i = 0; i < S; ++i) { kcs[i] = wv[i]->kc; vcs[i] = wv[i]->vc; queues[i] = wv[i]->queue; states[i] = wv[i]->state; }
+        FC_CUDA(cudaMemcpyAsync(b.kcs, kcs.data(), S * sizeof(float*), cudaMemcpyHostToDevice, st));
+        FC_CUDA(cudaMemcpyAsync(b.vcs, vcs.data(), S * sizeof(float*), cudaMemcpyHostToDevice, st));
+        FC_CUDA(cudaMemcpyAsync(b.queues, queues.data(), S * sizeof(int*), cudaMemcpyHostToDevice, st));
+        FC_CUDA(cudaMemcpyAsync(b.states, states.data(), S * sizeof(StepState*), cudaMemcpyHostToDevice, st));
+        FC_CUDA(cudaStreamSynchronize(st));   // the host vectors above go out of use
         int used = 0;
-        if (rc == FC_OK) rc = prime_batched(wv.data(), (int)wv.size(), prompt_len, STEP_SELECT, &used);
-        for (int i = 0; i < nw && rc == FC_OK && !used; ++i) {
-            fc_stream* s = wv[i];
-            cudaStream_t own = s->cs;
-            s->cs = nullptr;
-            rc = run_steps(s, prompt_len, STEP_NOHEAD, STEP_SELECT);
-            s->cs = own;
+        FC_TRY(prime_batched(wv.data(), S, prompt_len, STEP_NOHEAD, &used, b.kcs, b.vcs));
+        if (used) {
+            // the head sees the last row of every window: final LayerNorm, one product for all streams, pick of token 1
+            const int d = c.d_model;
+            FC_TRY(launch_gather_last_rows(m->x, S, prompt_len, d, b.x, st));
+            FC_TRY(launch_batch_init(S, prompt_len, b.done, b.n_out, b.cur, b.pos, st));
+            FC_TRY(launch_ln_rows_f16(b.x, m->lnfg, m->lnfb, S, d, b.xp, st));
+            FC_TRY(launch_skinny_q8(b.head, b.xp, S, nullptr, nullptr, 0, EPI_NONE, b.logits, m->head.N_pad, nullptr, 0, st));
+            FC_TRY(launch_pick_batch(b.logits, m->head.N_pad, c.vocab, S, eos, b.cur, b.done, b.n_out, b.out_tok, b.out_cap, b.pos, 0, st));
+        } else {
+            // prompts too short for a window forward: token by token per stream; the last step selects token 1
+            for (int i = 0; i < S; ++i) FC_TRY(run_steps(wv[i], prompt_len, STEP_NOHEAD, STEP_SELECT));
+            FC_TRY(launch_gather_first(b.queues, b.states, prompt_len, S, b.cur, b.done, b.n_out, b.out_tok, b.out_cap, b.pos, st));
         }
-        if (rc != FC_OK) break;
-        // then the decode launches of all its streams, each on its own CUDA stream and on
-        // 1/wave of the SMs, so that the wave's kernels are resident together
-        if (cudaEventRecord(m->ev1, st) != cudaSuccess) { rc = fail(FC_E_CUDA, "event record failed"); break; }
-        for (int i = 0; i < nw && rc == FC_OK; ++i) {
-            fc_stream* s = m->pool[w0 + i];
-            if (cudaStreamWaitEvent(s->cs, m->ev1, 0) != cudaSuccess) { rc = fail(FC_E_CUDA, "stream hand-over failed"); break; }
-            s->table = t;
-            for (int fed = 1; fed < max_new && rc == FC_OK; fed += 32)   // selecting feeds 1 .. max_new - 1
-                rc = run_steps(s, std::min(32, max_new - fed), STEP_SELECT, STEP_SELECT);
-            if (rc == FC_OK) rc = run_steps(s, 1, STEP_PROBS, STEP_PROBS);   // the feed of the last token selects nothing
-            s->table = 0;
-            if (rc == FC_OK && cudaEventRecord(s->cs_done, s->cs) != cudaSuccess) rc = fail(FC_E_CUDA, "event record failed");
+        std::vector<int> done(S, 0);
+        for (int i = 1; i < max_new; ++i) {        // step i feeds token i and picks token i + 1
+            FC_TRY(batch_run_step(m, S, eos));
+            if (eos >= 0 && (i % 16 == 0)) {          // eos can only be noticed on the host at a synchronisation point
+                FC_CUDA(cudaMemcpyAsync(done.data(), b.done, S * sizeof(int), cudaMemcpyDeviceToHost, st));
+                FC_CUDA(cudaStreamSynchronize(st));
+                if (std::all_of(done.begin(), done.end(), [](int v) { return v != 0; })) break;
+            }
         }
-        // the wave is over when every one of its streams is; the model's stream waits for all
-        for (int i = 0; i < nw; ++i) {
-            fc_stream* s = m->pool[w0 + i];
-            if (s->cs && s->cs_done) cudaStreamWaitEvent(st, s->cs_done, 0);
+        std::vector<int> cnt(S);
+        std::vector<int32_t> toks((size_t)S * b.out_cap);
+        int pos_h = 0;
+        FC_CUDA(cudaMemcpyAsync(cnt.data(), b.n_out, S * sizeof(int), cudaMemcpyDeviceToHost, st));
+        FC_CUDA(cudaMemcpyAsync(toks.data(), b.out_tok, toks.size() * 4, cudaMemcpyDeviceToHost, st));
+        FC_CUDA(cudaMemcpyAsync(&pos_h, b.pos, sizeof(int), cudaMemcpyDeviceToHost, st));
+        FC_CUDA(cudaStreamSynchronize(st));
+        for (int i = 0; i < S; ++i) {
+            const int have = std::min(cnt[i], max_new);
+            std::copy(toks.begin() + (size_t)i * b.out_cap, toks.begin() + (size_t)i * b.out_cap + have, out + (size_t)(w0 + i) * max_new);
+            n_out[w0 + i] = have;
+            wv[i]->host_pos = pos_h;
         }
-        for (int i = 0; i < nw && rc == FC_OK; ++i) {
-            fc_stream* s = m->pool[w0 + i];
-            StepState hs;
-            rc = read_state(s, &hs);                 // on the model's stream, which has waited for the wave
-            if (rc != FC_OK) break;
-            if (hs.error) { rc = fail(hs.error, "decode step rejected a token or position on the device"); break; }
-            const int have = std::min(hs.tail - prompt_len, max_new);
-            if (have > 0)
-                FC_CUDA(cudaMemcpy(out + (size_t)(w0 + i) * max_new, s->queue + prompt_len, (size_t)have * 4, cudaMemcpyDeviceToHost));
-            n_out[w0 + i] = std::max(have, 0);
-            s->host_pos = hs.pos;
-        }
-    }
-    if (rc != FC_OK) {   // leave nothing in flight behind an error
-        for (fc_stream* s : m->pool) if (s->cs) cudaStreamSynchronize(s->cs);
-        cudaStreamSynchronize(st);
-        return rc;
     }
     FC_CUDA(cudaEventRecord(m->ev1, st));
     FC_CUDA(cudaStreamSynchronize(st));

@@ -35,6 +35,10 @@ extern thread_local int64_t g_launches;
         FC_CUDA(cudaGetLastError()); \
     } while (0)
 
+// Device pointers a caller hands to the *_dev entry points are read and written with 16-byte
+// vector accesses: anything else is refused on the host before a kernel is launched.
+inline bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
+
 // ---- host helpers shared by the API files (defined in api.cu) ---------------------------
 // Owns device allocations until release().
 struct Arena {
@@ -178,5 +182,36 @@ int launch_attn_prefill_tc(const void* qkv_hi, const void* qkv_lo, int B, int T,
 // Grouped-query form: planes [B*T][(H + 2 KV) * 64] in (q heads | k heads | v heads), [B*T][H * 64] out.
 int launch_attn_prefill_tc_gqa(const void* qkv_hi, const void* qkv_lo, int B, int T, int H, int KV, void* out_hi, void* out_lo,
                                int* status, cudaStream_t st);
+
+// decode_batch.cu — one lock-step decode step for S <= kBatchMaxStreams streams.
+// Fragment-major copy of a Q8_0 matrix for the warp-level tensor-core product: per (16 rows,
+// 32-wide block) 512 bytes of biased quants in lane order (q) and 8 pairs of f16 scales (d).
+struct QFrag {
+    const void* q = nullptr;
+    const void* d = nullptr;
+    int N = 0, K = 0, N_pad = 0;
+};
+constexpr int kBatchMaxStreams = 64;
+size_t frag_quant_bytes(const QMat& w);
+size_t frag_scale_bytes(const QMat& w);
+int launch_repack_frag(const QMat& w, void* fq, void* fd, cudaStream_t st);
+// Columns of the activation planes for S streams (two f16 rows per stream, padded to the MMA tiling).
+int batch_cols(int S);
+// Y = X · Wᵀ (+bias, +GELU, +residual[S][ldr]) for S streams. xp: f16 planes [batch_cols(S)][K], row 2s = hi and
+// row 2s + 1 = lo of stream s (rows past 2S zero). Output: f32 rows y [S][ldy] and / or f16 planes yp [..][ldp].
+int launch_skinny_q8(const QFrag& w, const void* xp, int S, const float* bias, const float* residual, int ldr, int epi,
+                     float* y, int ldy, void* yp, int ldp, cudaStream_t st);
+int launch_embed_batch(const QMat& tok, const float* pos_emb, const int* cur, const int* pos, int S, float* x, cudaStream_t st);
+int launch_ln_rows_f16(const float* x, const float* g, const float* b, int S, int d, void* xp, cudaStream_t st);
+// qkv [S][3d] of this step; kcs / vcs: per-stream cache base pointers (device array), layer_off floats into each.
+int launch_attn_decode_batch(const float* qkv, float* const* kcs, float* const* vcs, size_t layer_off, int d, int H, int ctx,
+                             const int* pos, int S, void* ap, cudaStream_t st);
+int launch_pick_batch(const float* logits, int ldl, int V, int S, int eos, int* cur, int* done, int* n_out, int* out, int out_cap,
+                      int* pos, int advance, cudaStream_t st);
+int launch_scatter_kv(const float* qkv, float* const* kcs, float* const* vcs, size_t layer_off, int S, int n, int d, cudaStream_t st);
+int launch_gather_last_rows(const float* x, int S, int n, int d, float* out, cudaStream_t st);
+int launch_batch_init(int S, int pos0, int* done, int* n_out, int* cur, int* pos, cudaStream_t st);
+int launch_gather_first(int* const* queues, StepState* const* states, int prompt_len, int S, int* cur, int* done, int* n_out,
+                        int* out, int out_cap, int* pos, cudaStream_t st);
 
 }  // namespace fc

@@ -292,7 +292,7 @@ gemm_q8_bf16x3_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_c
         }
     } else {
         // ---------------------------------------------------------------- epilogue (warps 0-3)
-        const bool vec_ok = (a.ldy & 3) == 0;
+        const bool vec_ok = (a.ldy & 3) == 0 && (((uintptr_t)a.y | (uintptr_t)a.residual) & 15) == 0;
         // rows of 32 columns start on 32-byte boundaries: whole-sector accesses
         const bool vec8_ok = (a.ldy & 7) == 0 && (((uintptr_t)a.y | (uintptr_t)a.residual) & 31) == 0;
         int ti = 0;
@@ -540,6 +540,8 @@ extern "C" int fc_q8_0_linear_dev_noalloc(const fc_qweight* w, const float* x_de
                                           int M, void* cuda_stream, int* timed_out) {
     using namespace fc;
     if (!w || !x_dev || !y_dev) return fail(FC_E_ARG, "fc_q8_0_linear_dev_noalloc: null argument");
+    if (!aligned16(x_dev) || !aligned16(y_dev) || !aligned16(bias_dev))
+        return fail(FC_E_ARG, "fc_q8_0_linear_dev_noalloc: x_dev, y_dev and bias_dev must be 16-byte aligned");
     if (M <= 0) return fail(FC_E_SHAPE, "fc_q8_0_linear_dev_noalloc: M = %d", M);
     int device = 0;
     const QMat* mat = qweight_matrix(w, &device);

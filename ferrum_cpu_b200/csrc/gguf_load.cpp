@@ -48,6 +48,7 @@ struct File {
     std::map<std::string, Meta> meta;        // scalars and short strings (arrays are skipped)
     std::map<std::string, Tensor> tensors;
     uint64_t data = 0;                        // absolute offset of the data section
+    uint64_t align = 32;                      // general.alignment: every tensor offset is a multiple of it
 };
 
 struct Cursor {
@@ -169,13 +170,14 @@ int read_file(const char* path, File* f) {
         t.offset = c.get<uint64_t>();
         if (!c.ok) return fail(FC_E_FORMAT, "GGUF tensor directory is truncated at %s", name.c_str());
         t.nbytes = type_nbytes(t.type, n);
-        f->tensors[name] = t;
+        if (!f->tensors.emplace(name, t).second) return fail(FC_E_FORMAT, "GGUF tensor %s appears twice in the directory", name.c_str());
     }
     uint64_t align = 32;
     auto it = f->meta.find("general.alignment");
     if (it != f->meta.end()) align = it->second.u;
     if (align == 0 || (align & (align - 1))) return fail(FC_E_FORMAT, "general.alignment %llu is not a power of two", (unsigned long long)align);
     f->data = (c.pos + align - 1) / align * align;
+    f->align = align;
     return FC_OK;
 }
 
@@ -203,8 +205,13 @@ int tensor(const File& f, const std::string& name, uint32_t type, uint64_t ne0, 
     if (d0 != ne0 || d1 != ne1)
         return fail(FC_E_FORMAT, "GGUF tensor %s is [%llu][%llu], expected [%llu][%llu]", name.c_str(), (unsigned long long)d1,
                     (unsigned long long)d0, (unsigned long long)ne1, (unsigned long long)ne0);
-    if (t.nbytes == 0 || f.data + t.offset > f.bytes.size() || t.nbytes > f.bytes.size() - f.data - t.offset)
+    // compared without additions, so that a crafted offset near 2^64 cannot wrap
+    const uint64_t size = f.bytes.size();
+    if (t.nbytes == 0 || f.data > size || t.offset > size - f.data || t.nbytes > size - f.data - t.offset)
         return fail(FC_E_FORMAT, "GGUF tensor %s runs past the end of the file", name.c_str());
+    if (t.offset % f.align)
+        return fail(FC_E_FORMAT, "GGUF tensor %s starts at offset %llu, not a multiple of general.alignment %llu", name.c_str(),
+                    (unsigned long long)t.offset, (unsigned long long)f.align);
     *out = f.bytes.data() + f.data + t.offset;
     if (reblock) {
         std::vector<uint8_t>& store = f.reblocked[name];

@@ -236,6 +236,8 @@ void fc_rowq_free(fc_rowq* w) {
 
 int fc_rowq_linear_dev(const fc_rowq* w, const float* x_dev, const float* bias_dev, float* y_dev, int M, void* stream) {
     if (!w || !x_dev || !bias_dev || !y_dev) return fail(FC_E_ARG, "fc_rowq_linear_dev: null argument");
+    if (!aligned16(x_dev) || !aligned16(y_dev) || !aligned16(bias_dev))
+        return fail(FC_E_ARG, "fc_rowq_linear_dev: x_dev, y_dev and bias_dev must be 16-byte aligned");
     if (M <= 0) return fail(FC_E_SHAPE, "fc_rowq_linear_dev: M = %d", M);
     FC_CUDA(cudaSetDevice(w->device));
     return rowq_launch(const_cast<fc_rowq*>(w), x_dev, bias_dev, y_dev, M, (cudaStream_t)stream);

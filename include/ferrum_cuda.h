@@ -112,7 +112,11 @@ void fc_rng_fill_ids(uint64_t* state, int32_t vocab, size_t n, int32_t* out);
 int fc_q8_0_linear(int device, const float* x, const void* wq, const float* bias, float* y,
                    int M, int K, int N, int math_mode);
 /* The same with the weight resident: upload once, multiply many times on device
- * pointers (x_dev, bias_dev, y_dev are device memory on the weight's GPU). */
+ * pointers (x_dev, bias_dev, y_dev are device memory on the weight's GPU). The kernels read and
+ * write them with 16-byte vector accesses: a pointer that is not 16-byte aligned (a sub-view at an
+ * odd element offset, say) is refused with FC_E_ARG before anything is launched. This entry cannot
+ * report a device-side timeout (it returns before the kernel ends); an fc_qweight handle is used
+ * by one host thread at a time, like every other handle. */
 int fc_qweight_upload(int device, const void* wq, int N, int K, fc_qweight** out);
 void fc_qweight_free(fc_qweight* w);
 int fc_q8_0_linear_dev(const fc_qweight* w, const float* x_dev, const float* bias_dev, float* y_dev,
@@ -133,9 +137,13 @@ int fc_q8_0_linear_dev(const fc_qweight* w, const float* x_dev, const float* bia
  *  - M * K <= 4 194 304 activations per call (FC_E_SHAPE beyond that: split the rows over
  *    several calls, or use fc_q8_0_linear_dev); K % 64 == 0; the weight handle is uploaded
  *    beforehand with fc_qweight_upload (which does allocate);
- *  - the array is 16 MiB and every GPU that loads the library holds it until the process exits;
- *  - the first call on a device looks up the array's device address; make that first call
- *    before any stream capture;
+ *  - the array is 16 MiB per GPU. The CUDA runtime loads the library's device code lazily, so the
+ *    array (and the kernel images) are allocated by the driver at the FIRST call on a device, not
+ *    when the library is loaded, and then held until the process exits: make one warm-up call per
+ *    device before the host reserves the remaining device memory for its own pool (or run with
+ *    CUDA_MODULE_LOADING=EAGER). From the second call on nothing is allocated;
+ *  - that first call also looks up the array's device address; make it before any stream capture;
+ *  - x_dev, y_dev and bias_dev must be 16-byte aligned (FC_E_ARG otherwise);
  *  - all calls on a device share the one array: two calls whose kernels can overlap on the
  *    GPU (different streams, no ordering between them) race on it. Issue them on one stream
  *    or order them with events;
@@ -376,7 +384,8 @@ void fc_rowq_free(fc_rowq* w);
  * required as in the reference. FC_E_DIM on a width mismatch is the caller's check (rows and
  * cols are the handle's). */
 int fc_rowq_linear(const fc_rowq* w, const float* x, const float* bias, float* y, int M);
-/* The same on device pointers, asynchronous on `stream` (a cudaStream_t, or NULL). */
+/* The same on device pointers, asynchronous on `stream` (a cudaStream_t, or NULL). x_dev, bias_dev and
+ * y_dev must be 16-byte aligned (FC_E_ARG otherwise). */
 int fc_rowq_linear_dev(const fc_rowq* w, const float* x_dev, const float* bias_dev, float* y_dev, int M, void* stream);
 
 /* ---- introspection used by the benchmark ----------------------------------------- */

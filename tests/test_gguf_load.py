@@ -79,6 +79,25 @@ def test_probe_rejects_what_the_reference_rejects(model_and_file, tmp_path):
     struct.pack_into("<I", b, at, 0)
     open(p, "wb").write(bytes(b))
     assert "ffn_up" in _expect(FC_E_FORMAT, lambda: gguf_probe(p))
+    # crafted directory entries: an offset near 2^64 (must not wrap the bounds check), an offset off
+    # the file's alignment, and a tensor name that appears twice
+    gguf_file.write_gpt2_gguf(p, sm2)
+    good = bytearray(open(p, "rb").read())
+    name = b"blk.0.ffn_up.weight"
+    at = good.index(name) + len(name) + 4 + 16 + 4      # name, n_dims, two u64 dims, type -> the offset field
+    real = struct.unpack_from("<Q", good, at)[0]
+    for off, word in ((0xFFFFFFFFFFFFFFE0, "past the end"), (real + 16, "alignment")):
+        b = bytearray(good)
+        struct.pack_into("<Q", b, at, off)
+        open(p, "wb").write(bytes(b))
+        assert word in _expect(FC_E_FORMAT, lambda: gguf_probe(p))
+    b = bytearray(good)
+    old, dup = b"blk.0.ffn_down.bias", b"blk.0.attn_qkv.bias"
+    assert len(old) == len(dup)
+    k = b.index(old)
+    b[k:k + len(old)] = dup
+    open(p, "wb").write(bytes(b))
+    assert "twice" in _expect(FC_E_FORMAT, lambda: gguf_probe(p))
 
 
 @pytest.mark.gpu

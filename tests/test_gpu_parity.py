@@ -34,7 +34,7 @@ def tiny():
 
 # ---- standalone Q8_0 linear (the matmul sweep) -----------------------------------------
 @pytest.mark.parametrize("m,k,n", [(1, 768, 2304), (1, 3072, 768), (1, 768, 50257), (1, 128, 4096), (1, 32, 7),
-                                   (2, 64, 96), (3, 96, 130), (129, 160, 257), (512, 768, 3072)])
+                                   (2, 64, 96), (3, 96, 130), (129, 160, 257), (512, 768, 3072), (4096, 1024, 4096)])
 def test_q8_0_linear_matches_engine(m, k, n):
     w = O.fill_normal(21, n * k, 0.02)
     wq = synth.q8_0_quantize(w)
@@ -72,14 +72,21 @@ def test_feed_probs_match_oracle(tiny):
     assert np.abs(logp(pg) - logp(po)).max() < FP32_LOGPROB_TOL and gm.cached_len() == 7
 
 
-def check_greedy(tokens, want, margin, tol=1e-4):
-    """Identical tokens; a mismatch is tolerated only where the oracle's top-2 margin is below tol."""
+def check_greedy(tokens, want, margin, tol=1e-4, what=""):
+    """Identical tokens. A mismatch is tolerated only at a step where the oracle's own top-2 margin is
+    below tol (two candidates closer than fp32 reordering noise); the tokens after such a split belong to
+    a different continuation and are not compared. Every tolerated split is recorded and listed in the
+    terminal summary of the run (tests/conftest.py), so it cannot pass unnoticed. Returns the number of
+    tokens that were compared."""
     n = min(len(tokens), len(want))
     for i in range(n):
         if tokens[i] != want[i]:
-            assert margin[i] < tol, f"token {i}: got {tokens[i]}, want {want[i]}, oracle margin {margin[i]:.3e}"
-            pytest.xfail(f"greedy paths split at step {i} on an oracle margin of {margin[i]:.3e} (< {tol})")
-    assert len(tokens) == len(want)
+            assert margin[i] < tol, f"{what} token {i}: got {tokens[i]}, want {want[i]}, oracle margin {margin[i]:.3e}"
+            from tests import conftest
+            conftest.record_split(what or "greedy", i, float(margin[i]), tol)
+            return i
+    assert len(tokens) == len(want), f"{what}: {len(tokens)} tokens, expected {len(want)}"
+    return n
 
 
 def test_greedy_tiny_config_matches_golden(tiny):
@@ -141,9 +148,9 @@ def test_batched_prime_equals_token_by_token_prime(tiny):
     assert np.abs(logp(gm.prime(ids[:3])) - logp(om.prime(ids[:3]))).max() < FP32_LOGPROB_TOL
 
 
-def test_decode_batch_side_by_side_matches_oracle(tiny):
-    """Eight streams decoded side by side (one persistent kernel per stream on an eighth of the
-    SMs) give the oracle's tokens stream by stream; an EOS id ends only the stream that hits it."""
+def test_decode_batch_lock_step_matches_oracle(tiny):
+    """Eight streams decoded in lock step (every Q8_0 matrix read once per step for all of them) give
+    the oracle's tokens stream by stream; an EOS id ends only the stream that hits it."""
     sm, om, gm = tiny
     V = sm.dims[5]
     prompts = np.stack([synth.token_ids(40 + i, 9, V) for i in range(8)])
@@ -154,7 +161,7 @@ def test_decode_batch_side_by_side_matches_oracle(tiny):
         want, margin = om.generate_greedy(prompts[i], 20)
         check_greedy(outs[i], want, margin)
         wants.append(want)
-    # three streams: a wave of two and a wave of one
+    # three streams: the MMA tiles are padded with zero columns
     outs3 = gm.decode_batch(prompts[:3], 20)
     for i in range(3):
         assert np.array_equal(outs3[i], outs[i])
@@ -321,7 +328,8 @@ def test_small_scoring_is_batch_invariant_and_causal(small):
 
 
 # ---- tensor-core math mode (bf16 3-term split on tcgen05) ----------------------------------
-@pytest.mark.parametrize("m,k,n", [(2, 64, 96), (129, 192, 257), (128, 768, 128), (512, 768, 3072), (300, 3072, 768)])
+@pytest.mark.parametrize("m,k,n", [(2, 64, 96), (129, 192, 257), (128, 768, 128), (512, 768, 3072), (300, 3072, 768),
+                                   (4096, 1024, 4096)])
 def test_q8_0_linear_bf16x3_matches_engine(m, k, n):
     w = O.fill_normal(21, n * k, 0.02)
     wq = synth.q8_0_quantize(w)
@@ -360,6 +368,22 @@ def test_scoring_bf16x3_small_matches_golden():
     gm.close()
 
 
+def test_scoring_bf16x3_small_spread_of_the_512_sequences():
+    """Eight of the 512 sequences of the GPT-2-small scoring workload (first, last, six between), scored
+    inside one batch, against oracle fixtures."""
+    g = np.load(os.path.join(GOLD, "score_spread_small.npz"))
+    sm = synth.named("small", seed=0, math_mode=fcb.FC_MATH_BF16X3)
+    gm = fcb.CudaSlm(sm.config, sm.weights)
+    ids_all = synth.token_ids(1, 512 * 1024, sm.dims[5]).reshape(512, 1024)
+    assert np.array_equal(ids_all[g["index"]], g["ids"])
+    scores, lp = gm.score_sequences(g["ids"], batch_windows=8)
+    err = np.abs(lp - g["logprob"]).max()
+    assert err < LOGPROB_TOL, f"max abs log-prob error {err:.3e}"
+    for sc, want in zip(scores, g["total"]):
+        assert abs(sc.logprob - want) < 0.05
+    gm.close()
+
+
 @pytest.mark.parametrize("m,k,n", [(1100, 128, 4096), (4096, 768, 2304), (2304, 256, 3072)])
 def test_q8_0_linear_bf16x3_many_tiles_per_cta(m, k, n):
     """More output tiles than SMs: every persistent CTA walks several tiles, reusing its stage ring
@@ -383,20 +407,55 @@ def medium():
     return sm, fcb.CudaSlm(sm.config, sm.weights)
 
 
-def test_medium_decode_streams_match_golden_and_each_other(medium):
-    path = os.path.join(GOLD, "decode_medium.npz")
-    if not os.path.exists(path):
-        pytest.skip("decode_medium.npz has not been generated")
-    g = np.load(path)
+def stream_prompts(n, plen, V, base=200):
+    """Prompts of the concurrent-stream workload: stream i is token_ids(base + i, plen, V)."""
+    return np.stack([synth.token_ids(base + i, plen, V) for i in range(n)])
+
+
+def test_medium_decode_64_streams_match_goldens(medium):
+    """The decode half of the medium-shaped workload at full size: 64 streams x (64-id prompt + 128 greedy
+    tokens) in lock step; eight of the streams are checked against per-stream oracle fixtures, and one
+    stream must decode the same alone (persistent single-stream kernel) as inside the batch."""
+    g = np.load(os.path.join(GOLD, "streams_medium.npz"))
     sm, gm = medium
     V = sm.dims[5]
-    # stream 0 is the fixture's prompt; the others are independent prompts of the same length
-    prompts = np.stack([g["prompt"]] + [synth.token_ids(100 + i, len(g["prompt"]), V) for i in range(3)])
-    outs = gm.decode_batch(prompts, len(g["tokens"]))
-    check_greedy(outs[0], g["tokens"], g["margin"])
-    # a stream decodes the same alone as inside a batch
-    alone, _ = gm.generate_tokens(prompts[2], len(g["tokens"]))
-    assert np.array_equal(alone, outs[2])
+    n_new = g["tokens"].shape[1]
+    prompts = stream_prompts(64, int(g["prompt_len"]), V, int(g["seed_base"]))
+    outs = gm.decode_batch(prompts, n_new)
+    assert gm.last_batch_ms > 0
+    compared = 0
+    for j, idx in enumerate(g["index"]):
+        compared += check_greedy(outs[idx], g["tokens"][j], g["margin"][j], what=f"medium stream {idx}")
+    assert compared >= 4 * n_new, "most of the checked tokens must lie before any sub-margin split"
+    alone, _ = gm.generate_tokens(prompts[5], n_new)
+    first_diff = next((i for i in range(n_new) if alone[i] != outs[5][i]), n_new)
+    assert first_diff >= 16, f"single-stream and lock-step decode split at token {first_diff}"
+    # run-to-run determinism of the lock-step path
+    again = gm.decode_batch(prompts, n_new)
+    for a, b in zip(outs, again):
+        assert np.array_equal(a, b)
+
+
+def test_medium_single_stream_decode_matches_golden(medium):
+    g = np.load(os.path.join(GOLD, "decode_medium.npz"))
+    sm, gm = medium
+    toks, _ = gm.generate_tokens(g["prompt"], len(g["tokens"]))
+    check_greedy(toks, g["tokens"], g["margin"], what="medium single stream")
+
+
+def test_small_decode_8_streams_match_goldens(small):
+    """Eight lock-step streams on the GPT-2-small shape (one GPU's share of 64 streams over 8 GPUs)."""
+    g = np.load(os.path.join(GOLD, "streams_small.npz"))
+    sm, gm = small
+    n_new = g["tokens"].shape[1]
+    prompts = stream_prompts(8, int(g["prompt_len"]), sm.dims[5], int(g["seed_base"]))
+    outs = gm.decode_batch(prompts, n_new)
+    for j, idx in enumerate(g["index"]):
+        check_greedy(outs[idx], g["tokens"][j], g["margin"][j], what=f"small stream {idx}")
+    # odd stream counts pad the MMA tiles with zero columns
+    outs5 = gm.decode_batch(prompts[:5], 24)
+    for i in range(5):
+        assert np.array_equal(outs5[i], outs[i][:24])
 
 
 def test_medium_scoring_matches_golden(medium):
@@ -405,6 +464,7 @@ def test_medium_scoring_matches_golden(medium):
         pytest.skip("score_medium.npz has not been generated")
     g = np.load(path)
     sm, gm = medium
+    assert g["ids"].shape[1] == 1024, "the fixture is a full 1024-id window"
     scores, lp = gm.score_sequences(g["ids"], batch_windows=2)
     err = np.abs(lp - g["logprob"]).max()
     assert err < LOGPROB_TOL, f"max abs log-prob error {err:.3e}"

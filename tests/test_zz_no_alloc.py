@@ -60,3 +60,47 @@ def test_noalloc_linear_rejects_sizes_beyond_its_array():
     torch.cuda.synchronize()
     assert float(y.abs().max()) == 0.0
     qw.close()
+
+
+def test_noalloc_linear_takes_no_device_memory_after_its_first_call():
+    """The claim the entry point exists for: once the first call on a device has made the driver load the
+    library's device code (which is when the fixed array comes into being), a call changes the amount of
+    free device memory by nothing."""
+    import torch
+
+    n, k, m = 512, 768, 200
+    qw = fcb.QWeight(synth.q8_0_quantize(synth.Rng(15).normal(n * k, 0.02)), n, k)
+    x = torch.from_numpy(synth.Rng(16).normal(m * k, 1.0).reshape(m, k)).cuda()
+    y = torch.zeros(m, n, device="cuda")
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    qw.linear_dev_noalloc(x.data_ptr(), None, y.data_ptr(), m, stream)      # warm-up: loads the module
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    for _ in range(3):
+        qw.linear_dev_noalloc(x.data_ptr(), None, y.data_ptr(), m, stream)
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before
+    qw.close()
+
+
+def test_device_pointer_entries_refuse_misaligned_pointers_on_the_host():
+    """x_dev / y_dev / bias_dev are accessed with 16-byte vector loads and stores: a pointer off that
+    alignment is an FC_E_ARG from the host-side check, and nothing is launched."""
+    import torch
+
+    n, k, m = 128, 64, 4
+    qw = fcb.QWeight(synth.q8_0_quantize(synth.Rng(17).normal(n * k, 0.02)), n, k)
+    x = torch.zeros(m * k + 4, device="cuda")
+    y = torch.zeros(m * n + 4, device="cuda")
+    for xp, yp in ((x.data_ptr() + 4, y.data_ptr()), (x.data_ptr(), y.data_ptr() + 4)):
+        with pytest.raises(fcb.FerrumCudaError) as e:
+            qw.linear_dev_noalloc(xp, None, yp, m, None)
+        assert e.value.code == _lib.FC_E_ARG
+        with pytest.raises(fcb.FerrumCudaError) as e:
+            qw.linear_dev(xp, None, yp, m, fcb.FC_MATH_BF16X3, None)
+        assert e.value.code == _lib.FC_E_ARG
+    fcb.take_launch_count()
+    with pytest.raises(fcb.FerrumCudaError):
+        qw.linear_dev(x.data_ptr() + 4, None, y.data_ptr(), 1, fcb.FC_MATH_FP32, None)
+    assert fcb.take_launch_count() == 0
+    qw.close()
