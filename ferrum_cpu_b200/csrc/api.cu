@@ -121,7 +121,8 @@ struct BatchCtx {
     std::vector<fc::QFrag> qkv, out, up, down;
     fc::QFrag head;
     int cap = 0, out_cap = 0;
-    float *x = nullptr, *qkv_f = nullptr, *logits = nullptr;
+    float *x = nullptr, *x2 = nullptr, *qkv_f = nullptr, *logits = nullptr;   // the residual stream alternates between x and x2
+    float* part = nullptr;             // K-split partial sums of the out- and down-projections [splits][S][d]
     void *xp = nullptr, *ap = nullptr, *hp = nullptr;      // f16 hi / lo rows of LayerNorm output, attention output, GELU output
     int *cur = nullptr, *done = nullptr, *n_out = nullptr, *out_tok = nullptr, *pos = nullptr;
     float **kcs = nullptr, **vcs = nullptr;
@@ -1346,6 +1347,8 @@ static int batch_ensure(fc_model* m, int S, int out_cap) {
     const size_t d = c.d_model, F = c.d_ff;
     Arena& a = b.arena;
     FC_TRY(a.alloc_n(&b.x, cap * d));
+    FC_TRY(a.alloc_n(&b.x2, cap * d));
+    FC_TRY(a.alloc_n(&b.part, (size_t)skinny_max_splits() * cap * d));
     FC_TRY(a.alloc_n(&b.qkv_f, cap * 3 * d));
     FC_TRY(a.alloc_n(&b.logits, cap * (size_t)m->head.N_pad));
     FC_TRY(a.alloc(&b.xp, C * d * 2));
@@ -1369,28 +1372,73 @@ static int batch_ensure(fc_model* m, int S, int out_cap) {
     return FC_OK;
 }
 
+// The tail of a step: final LayerNorm (model.rs:51-71 layer list: ..., LayerNorm, Linear, Softmax), head,
+// greedy pick. With `part` the last down-projection is still in partial sums, which the LayerNorm adds.
+static int batch_head_and_pick(fc_model* m, int S, int eos, const float* x, const float* part, int n_part, const float* part_bias,
+                               float* x_other, int advance) {
+    const fc_config& c = m->cfg;
+    BatchCtx& b = m->batch;
+    cudaStream_t st = m->st;
+    FC_TRY(launch_ln_rows_f16(x, part, n_part, part_bias, x_other, m->lnfg, m->lnfb, S, c.d_model, b.xp, st));
+    SkinnyOut out;
+    out.y = b.logits; out.ldy = m->head.N_pad;
+    FC_TRY(launch_skinny_q8(b.head, S, b.xp, nullptr, EPI_NONE, out, nullptr, st));
+    return launch_pick_batch(b.logits, m->head.N_pad, c.vocab, S, eos, b.cur, b.done, b.n_out, b.out_tok, b.out_cap, b.pos, advance, st);
+}
+
 // One step for S streams: CachedTransformer::feed (cached.rs:100-125) on every stream's current
-// token at the shared position, then the greedy pick per stream.
+// token at the shared position, then the greedy pick per stream. Seven kernels per block.
+//  * Up to 16 streams every kernel is a chain of a few memory round trips and nothing else: the
+//    out- and down-projections add bias and residual in their own epilogue (in place).
+//  * Beyond that the out- and down-projections split K over CTAs (their 1024-odd output rows
+//    alone would leave most SMs idle) and leave partial sums; the LayerNorm kernel that reads the
+//    residual stream next adds them, the bias and the residual in a fixed order
+//    (transformer.rs:272,293).
 static int batch_launch_step(fc_model* m, int S, int eos) {
     const fc_config& c = m->cfg;
     BatchCtx& b = m->batch;
     cudaStream_t st = m->st;
     const int d = c.d_model, F = c.d_ff;
     const size_t layer_stride = (size_t)c.ctx * d;
+    const bool split_k = S > 16;
     FC_TRY(launch_embed_batch(m->tok, m->pos, b.cur, b.pos, S, b.x, st));
+    float *x = b.x, *x_other = b.x2;       // the stream as of the last completed residual add, and the other buffer
+    const float* part_bias = nullptr;      // bias of the product whose partial sums are pending
+    int n_part = 0;
+    // LayerNorm of the residual stream, completed first when partial sums are pending
+    auto normed = [&](const float* g, const float* be) -> int {
+        FC_TRY(launch_ln_rows_f16(x, n_part > 0 ? b.part : nullptr, n_part, part_bias, x_other, g, be, S, d, b.xp, st));
+        if (n_part > 0) std::swap(x, x_other);   // the completed stream now lives in the other buffer
+        n_part = 0;
+        part_bias = nullptr;
+        return FC_OK;
+    };
+    // x <- x + (W in + bias): as partial sums for the next LayerNorm, or finished in the epilogue
+    auto project_add = [&](const QFrag& w, const void* in, const float* bias) -> int {
+        SkinnyOut o;
+        if (split_k) {
+            o.part = b.part;
+            FC_TRY(launch_skinny_q8(w, S, in, nullptr, EPI_NONE, o, &n_part, st));
+            part_bias = bias;
+            return FC_OK;
+        }
+        o.y = x; o.ldy = d; o.residual = x;
+        return launch_skinny_q8(w, S, in, bias, EPI_NONE, o, nullptr, st);
+    };
+    SkinnyOut oq, oh;
+    oq.y = b.qkv_f; oq.ldy = 3 * d;
+    oh.planes = b.hp; oh.ldp = F;
     for (int l = 0; l < c.n_layer; ++l) {
         const LayerDev& L = m->layers[l];
-        FC_TRY(launch_ln_rows_f16(b.x, L.ln1g, L.ln1b, S, d, b.xp, st));
-        FC_TRY(launch_skinny_q8(b.qkv[l], b.xp, S, L.qkv_b, nullptr, 0, EPI_NONE, b.qkv_f, 3 * d, nullptr, 0, st));
+        FC_TRY(normed(L.ln1g, L.ln1b));
+        FC_TRY(launch_skinny_q8(b.qkv[l], S, b.xp, L.qkv_b, EPI_NONE, oq, nullptr, st));
         FC_TRY(launch_attn_decode_batch(b.qkv_f, b.kcs, b.vcs, l * layer_stride, d, c.n_head, c.ctx, b.pos, S, b.ap, st));
-        FC_TRY(launch_skinny_q8(b.out[l], b.ap, S, L.out_b, b.x, d, EPI_NONE, b.x, d, nullptr, 0, st));
-        FC_TRY(launch_ln_rows_f16(b.x, L.ln2g, L.ln2b, S, d, b.xp, st));
-        FC_TRY(launch_skinny_q8(b.up[l], b.xp, S, L.up_b, nullptr, 0, EPI_GELU, nullptr, 0, b.hp, F, st));
-        FC_TRY(launch_skinny_q8(b.down[l], b.hp, S, L.down_b, b.x, d, EPI_NONE, b.x, d, nullptr, 0, st));
+        FC_TRY(project_add(b.out[l], b.ap, L.out_b));
+        FC_TRY(normed(L.ln2g, L.ln2b));
+        FC_TRY(launch_skinny_q8(b.up[l], S, b.xp, L.up_b, EPI_GELU, oh, nullptr, st));
+        FC_TRY(project_add(b.down[l], b.hp, L.down_b));
     }
-    FC_TRY(launch_ln_rows_f16(b.x, m->lnfg, m->lnfb, S, d, b.xp, st));
-    FC_TRY(launch_skinny_q8(b.head, b.xp, S, nullptr, nullptr, 0, EPI_NONE, b.logits, m->head.N_pad, nullptr, 0, st));
-    return launch_pick_batch(b.logits, m->head.N_pad, c.vocab, S, eos, b.cur, b.done, b.n_out, b.out_tok, b.out_cap, b.pos, 1, st);
+    return batch_head_and_pick(m, S, eos, x, b.part, n_part, part_bias, x_other, 1);
 }
 
 // The step is launch-bound (7 small kernels per block): it is captured once into a CUDA graph and
@@ -1485,9 +1533,7 @@ int fc_decode_batch(fc_model* m, int n_streams, const int32_t* prompts, int prom
             const int d = c.d_model;
             FC_TRY(launch_gather_last_rows(m->x, S, prompt_len, d, b.x, st));
             FC_TRY(launch_batch_init(S, prompt_len, b.done, b.n_out, b.cur, b.pos, st));
-            FC_TRY(launch_ln_rows_f16(b.x, m->lnfg, m->lnfb, S, d, b.xp, st));
-            FC_TRY(launch_skinny_q8(b.head, b.xp, S, nullptr, nullptr, 0, EPI_NONE, b.logits, m->head.N_pad, nullptr, 0, st));
-            FC_TRY(launch_pick_batch(b.logits, m->head.N_pad, c.vocab, S, eos, b.cur, b.done, b.n_out, b.out_tok, b.out_cap, b.pos, 0, st));
+            FC_TRY(batch_head_and_pick(m, S, eos, b.x, nullptr, 0, nullptr, nullptr, 0));
         } else {
             // prompts too short for a window forward: token by token per stream; the last step selects token 1
             for (int i = 0; i < S; ++i) FC_TRY(run_steps(wv[i], prompt_len, STEP_NOHEAD, STEP_SELECT));
@@ -1503,12 +1549,15 @@ int fc_decode_batch(fc_model* m, int n_streams, const int32_t* prompts, int prom
             }
         }
         std::vector<int> cnt(S);
+        FC_CUDA(cudaMemcpyAsync(done.data(), b.done, S * sizeof(int), cudaMemcpyDeviceToHost, st));
         std::vector<int32_t> toks((size_t)S * b.out_cap);
         int pos_h = 0;
         FC_CUDA(cudaMemcpyAsync(cnt.data(), b.n_out, S * sizeof(int), cudaMemcpyDeviceToHost, st));
         FC_CUDA(cudaMemcpyAsync(toks.data(), b.out_tok, toks.size() * 4, cudaMemcpyDeviceToHost, st));
         FC_CUDA(cudaMemcpyAsync(&pos_h, b.pos, sizeof(int), cudaMemcpyDeviceToHost, st));
         FC_CUDA(cudaStreamSynchronize(st));
+        for (int i = 0; i < S; ++i)
+            if (done[i] == 2) return fail(FC_E_CUDA, "fc_decode_batch: stream %d produced no finite logit", w0 + i);
         for (int i = 0; i < S; ++i) {
             const int have = std::min(cnt[i], max_new);
             std::copy(toks.begin() + (size_t)i * b.out_cap, toks.begin() + (size_t)i * b.out_cap + have, out + (size_t)(w0 + i) * max_new);

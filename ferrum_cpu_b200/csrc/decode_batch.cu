@@ -25,6 +25,8 @@
 // Bound: HBM. Per step: every Q8_0 matrix once + per stream the f32 K/V rows of positions 0..pos.
 #include <cuda_fp16.h>
 
+#include <algorithm>
+
 #include "fc_common.cuh"
 
 namespace fc {
@@ -60,19 +62,33 @@ __device__ __forceinline__ void mma16816(float* d, uint32_t a0, uint32_t a1, uin
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
 struct SkArgs {
     const uint4* wq;        // fragment-major quants: [row group][k-block][32 lanes] x 16 B
     const __half2* wd;      // scales: [row group][k-block][8] pairs (row g, row g + 8)
-    const uint4* xp;        // activation planes [C_pad][K] f16: row 2s = hi, 2s + 1 = lo of stream s
     int N, K, S;
+    int depth;              // ring slots per warp (k-blocks in flight), <= SK_DEPTH
+    // ---- input: f16 hi / lo rows [cols][K] (row 2s = hi, 2s + 1 = lo of stream s)
+    const uint4* xp;
+    // ---- output
     const float* bias;      // [N] or null
-    const float* residual;  // [S][ldr] or null
-    int ldr;
     int epi;                // EPI_NONE / EPI_GELU
+    const float* residual;  // [S][ldy] or null: y = residual + (product + bias); may be y itself
     float* y;               // f32 rows [S][ldy], or null
     int ldy;
-    __half* yp;             // f16 planes [C_pad][ldp] (row 2s = hi, 2s + 1 = lo), or null
+    __half* yp;             // f16 hi / lo rows [cols][ldp], or null
     int ldp;
+    float* part_out;        // raw sums of this CTA's K range [gridDim.z][S][N] (no bias), or null
 };
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
@@ -82,58 +98,88 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-constexpr int SK_DEPTH = 16;   // k-blocks of weights a warp keeps in flight
+// Waits until at most n (< 16) of this thread's cp.async groups are still in flight.
+__device__ __forceinline__ void cp_async_wait_n(int n) {
+    switch (n) {
+        case 0: cp_async_wait<0>(); break;
+        case 1: cp_async_wait<1>(); break;
+        case 2: cp_async_wait<2>(); break;
+        case 3: cp_async_wait<3>(); break;
+        case 4: cp_async_wait<4>(); break;
+        case 5: cp_async_wait<5>(); break;
+        case 6: cp_async_wait<6>(); break;
+        case 7: cp_async_wait<7>(); break;
+        case 8: cp_async_wait<8>(); break;
+        case 9: cp_async_wait<9>(); break;
+        case 10: cp_async_wait<10>(); break;
+        case 11: cp_async_wait<11>(); break;
+        case 12: cp_async_wait<12>(); break;
+        case 13: cp_async_wait<13>(); break;
+        case 14: cp_async_wait<14>(); break;
+        default: cp_async_wait<15>(); break;
+    }
+}
 
-// NT: 8-column MMA tiles (4 streams each) per warp; RG: 16-row groups per warp. blockIdx.x picks the
-// rows, blockIdx.y the group of 8 * NT activation columns.
+constexpr int SK_DEPTH = 16;       // most k-blocks of weights a warp keeps in flight
+constexpr int SK_MAX_SPLITS = 8;
+
+// NT: 8-column MMA tiles (4 streams each) per warp; RG: 16-row groups per warp. blockIdx.x picks the rows,
+// blockIdx.y the group of 8 * NT activation columns, blockIdx.z the K range (products whose K ranges are split over
+// CTAs leave partial sums that the consumer adds in range order).
 //
-// Weights never depend on the kernel ahead, so every warp requests the first SK_DEPTH blocks of its K
-// slice (its own ring in shared memory, cp.async) before it waits for that kernel (programmatic
-// dependent launch): the weight stream of one product overlaps the tail of the kernel before it, and
-// HBM sees RG * 544 B * SK_DEPTH per warp in flight instead of one block at a time.
+// Weights never depend on the kernel ahead, so every warp requests the first blocks of its K slice
+// (its own ring in shared memory, cp.async) before it waits for that kernel (programmatic dependent
+// launch): the weight stream of one product overlaps the tail of the kernel before it, and HBM sees
+// RG * 544 B * depth per warp in flight instead of one block at a time.
 template <int NT, int RG>
 __global__ void __launch_bounds__(256) skinny_q8_kernel(const SkArgs a) {
     extern __shared__ __align__(16) unsigned char sk_smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int nwarps = blockDim.x >> 5;
-    // [warps][SK_DEPTH][RG] x (512 B quants + 32 B scales), then the reduction buffer
-    constexpr int SLOT = RG * 544;
-    unsigned char* ring = sk_smem + (size_t)warp * SK_DEPTH * SLOT;
-    float* red = (float*)(sk_smem + (size_t)nwarps * SK_DEPTH * SLOT);   // [warps][4 * NT streams][RED_LD]
+    constexpr int SLOT = RG * 544;                     // per 16-row group: 512 B quants + 32 B scales
+    const int depth = a.depth;
+    unsigned char* ring = sk_smem + (size_t)warp * depth * SLOT;
+    float* red = (float*)(sk_smem + (size_t)nwarps * depth * SLOT);   // [warps][4 * NT streams][RED_LD]
     const int nkb = a.K >> 5, k8 = a.K >> 3;
-    const int kb0 = (int)((long long)warp * nkb / nwarps), kb1 = (int)((long long)(warp + 1) * nkb / nwarps);
+    const int kbA = (int)((long long)blockIdx.z * nkb / gridDim.z), kbB = (int)((long long)(blockIdx.z + 1) * nkb / gridDim.z);
+    const int kb0 = kbA + (int)((long long)warp * (kbB - kbA) / nwarps), kb1 = kbA + (int)((long long)(warp + 1) * (kbB - kbA) / nwarps);
     const int rg0 = blockIdx.x * RG;
     const int col0 = blockIdx.y * (8 * NT);           // first activation column of this CTA
     const uint4* wq = a.wq + ((size_t)rg0 * nkb) * 32 + lane;
     const uint4* wd4 = (const uint4*)(a.wd + ((size_t)rg0 * nkb) * 8);   // 32 B of scales per (row group, k-block)
+    int slot_w = 0;                                    // ring slot the next request fills
     auto request = [&](int kb) {
-        unsigned char* slot = ring + (size_t)((kb - kb0) % SK_DEPTH) * SLOT;
+        unsigned char* slot = ring + (size_t)slot_w * SLOT;
 #pragma unroll
         for (int r = 0; r < RG; ++r) {
             cp_async16(slot + r * 544 + lane * 16, wq + ((size_t)r * nkb + kb) * 32);
             if (lane < 2) cp_async16(slot + r * 544 + 512 + lane * 16, wd4 + ((size_t)r * nkb + kb) * 2 + lane);
         }
+        slot_w = slot_w + 1 == depth ? 0 : slot_w + 1;
     };
 #pragma unroll 1
-    for (int i = 0; i < SK_DEPTH; ++i) {
+    for (int i = 0; i < depth; ++i) {                  // one group per block, empty ones included: block i is group i
         if (kb0 + i < kb1) request(kb0 + i);
         cp_async_commit();
     }
     pdl_wait_prior();                                  // the activations come from the kernel ahead
     pdl_launch_next();                                 // the kernel behind may start fetching its own weights
+
     float acc[RG][NT][2];
 #pragma unroll
     for (int r = 0; r < RG; ++r)
 #pragma unroll
         for (int j = 0; j < NT; ++j) acc[r][j][0] = acc[r][j][1] = 0.0f;
     const uint4* xb = a.xp + (size_t)(col0 + g) * k8 + t;
+    int slot_r = 0;
     for (int kb = kb0; kb < kb1; ++kb) {
         uint4 xv[NT];
 #pragma unroll
         for (int j = 0; j < NT; ++j) xv[j] = __ldg(xb + (size_t)(8 * j) * k8 + 4 * kb);
-        cp_async_wait<SK_DEPTH - 1>();                 // block kb has landed (one group per block, in order)
+        cp_async_wait_n(depth - 1);                    // block kb has landed: depth + i groups committed, the first i + 1 complete
         __syncwarp();
-        const unsigned char* slot = ring + (size_t)((kb - kb0) % SK_DEPTH) * SLOT;
+        const unsigned char* slot = ring + (size_t)slot_r * SLOT;
+        slot_r = slot_r + 1 == depth ? 0 : slot_r + 1;
         uint4 w[RG];
         float2 sc[RG];
 #pragma unroll
@@ -142,7 +188,7 @@ __global__ void __launch_bounds__(256) skinny_q8_kernel(const SkArgs a) {
             sc[r] = __half22float2(*(const __half2*)(slot + r * 544 + 512 + g * 4));
         }
         __syncwarp();                                  // every lane has read the slot before it is refilled
-        if (kb + SK_DEPTH < kb1) request(kb + SK_DEPTH);
+        if (kb + depth < kb1) request(kb + depth);
         cp_async_commit();
         // lane (g, t) holds k = 8t .. 8t+7 of rows g (x, y) and g + 8 (z, w): k-step 0 takes the
         // first four, k-step 1 the last four, on both operands alike
@@ -167,6 +213,8 @@ __global__ void __launch_bounds__(256) skinny_q8_kernel(const SkArgs a) {
     cp_async_wait<0>();
     // partial sums of this warp's K slice: red[warp][stream][row]
     float* mine = red + (size_t)warp * (4 * NT) * RED_LD;
+    constexpr int ROWS = 16 * RG;
+    static_assert(ROWS <= RED_LD, "reduction rows");
 #pragma unroll
     for (int j = 0; j < NT; ++j) {
         float* col = mine + (4 * j + t) * RED_LD;
@@ -174,7 +222,6 @@ __global__ void __launch_bounds__(256) skinny_q8_kernel(const SkArgs a) {
         for (int r = 0; r < RG; ++r) { col[16 * r + g] = acc[r][j][0]; col[16 * r + g + 8] = acc[r][j][1]; }
     }
     __syncthreads();
-    constexpr int ROWS = 16 * RG;
     const int n_base = blockIdx.x * ROWS, s_base = col0 >> 1;
     const int s_here = min(4 * NT, a.S - s_base);
     for (int idx = threadIdx.x; idx < s_here * ROWS; idx += blockDim.x) {
@@ -182,9 +229,13 @@ __global__ void __launch_bounds__(256) skinny_q8_kernel(const SkArgs a) {
         if (n >= a.N) continue;
         float v = 0.0f;
         for (int w = 0; w < nwarps; ++w) v += red[((size_t)w * (4 * NT) + sl) * RED_LD + r];   // K slices in order
+        if (a.part_out) {
+            a.part_out[((size_t)blockIdx.z * a.S + s) * a.N + n] = v;
+            continue;
+        }
         if (a.bias) v += a.bias[n];
         if (a.epi == EPI_GELU) v = gelu_f(v);
-        if (a.residual) v = a.residual[(size_t)s * a.ldr + n] + v;
+        if (a.residual) v = a.residual[(size_t)s * a.ldy + n] + v;
         if (a.y) a.y[(size_t)s * a.ldy + n] = v;
         if (a.yp) {
             const __half h = __float2half_rn(v);
@@ -211,16 +262,6 @@ __global__ void repack_frag_kernel(const uint8_t* __restrict__ qu, const __half*
     }
 }
 
-__device__ __forceinline__ float warp_sum(float v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    return v;
-}
-__device__ __forceinline__ float warp_max(float v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-    return v;
-}
 // Fixed-order block reductions; `red` has >= 33 floats.
 __device__ float block_sum(float v, float* red) {
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
@@ -256,7 +297,8 @@ __global__ void embed_batch_kernel(QMat tok, const float* __restrict__ pos_emb, 
                                    float* __restrict__ x) {
     pdl_wait_prior();
     pdl_launch_next();
-    const int s = blockIdx.x, id = cur[s], p = *pos;
+    const int s = blockIdx.x, p = *pos;
+    const int id = min(max(cur[s], 0), tok.N - 1);   // the pick only hands on ids below the vocabulary size; never index outside the table
     const int d = tok.K;
     for (int c = threadIdx.x; c < d; c += blockDim.x) {
         const float dq = __half2float(tok.d[(size_t)id * (d >> 5) + (c >> 5)]);
@@ -265,10 +307,13 @@ __global__ void embed_batch_kernel(QMat tok, const float* __restrict__ pos_emb, 
     }
 }
 
-// layer/norm.rs:46-82 per stream row, written as the f16 hi / lo rows the skinny product reads.
+// layer/norm.rs:46-82 per stream row, written as the f16 hi / lo rows the skinny product reads. When
+// the product ahead left K-split partial sums, the row is first completed: x_new = x + (sum of the
+// n_part partials in order + part_bias), stored to x_out (the residual add of transformer.rs:272,293).
 template <int PER>
-__global__ void ln_rows_f16_kernel(const float* __restrict__ x, const float* __restrict__ g, const float* __restrict__ b, int d,
-                                   __half* __restrict__ xp) {
+__global__ void ln_rows_f16_kernel(const float* __restrict__ x, const float* __restrict__ part, int n_part, int S,
+                                   const float* __restrict__ part_bias, float* __restrict__ x_out, const float* __restrict__ g,
+                                   const float* __restrict__ b, int d, __half* __restrict__ xp) {
     __shared__ float red[33];
     pdl_wait_prior();
     pdl_launch_next();
@@ -279,8 +324,24 @@ __global__ void ln_rows_f16_kernel(const float* __restrict__ x, const float* __r
 #pragma unroll
     for (int i = 0; i < PER; ++i) {
         const int c = threadIdx.x + i * blockDim.x;
-        v[i] = c < d ? xr[c] : 0.0f;
-        sum += v[i];
+        float xv = 0.0f;
+        if (c < d) {
+            xv = xr[c];
+            if (n_part > 0) {
+                // all partials are requested before the first add (n_part <= SK_MAX_SPLITS), then added in order
+                float pp[SK_MAX_SPLITS];
+#pragma unroll
+                for (int p = 0; p < SK_MAX_SPLITS; ++p) pp[p] = p < n_part ? part[((size_t)p * S + s) * d + c] : 0.0f;
+                float pv = pp[0];
+#pragma unroll
+                for (int p = 1; p < SK_MAX_SPLITS; ++p) pv = p < n_part ? pv + pp[p] : pv;
+                if (part_bias) pv += part_bias[c];
+                xv = xv + pv;
+                if (x_out) x_out[(size_t)s * d + c] = xv;
+            }
+        }
+        v[i] = xv;
+        sum += xv;
     }
     const float mean = block_sum(sum, red) / (float)d;
     float q = 0.0f;
@@ -450,7 +511,9 @@ __global__ void __launch_bounds__(1024) pick_batch_kernel(const float* __restric
         for (int o = 16; o > 0; o >>= 1) best = better(best, ArgPair{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)});
         if (lane == 0) {
             if (!done[s]) {
-                if (best.i == eos) {
+                if (best.i < 0 || best.i >= V) {
+                    done[s] = 2;                       // no finite logit: reported as an error by the host, nothing is emitted
+                } else if (best.i == eos) {
                     done[s] = 1;
                 } else {
                     if (n_out[s] < out_cap) out[(size_t)s * out_cap + n_out[s]] = best.i;
@@ -520,17 +583,23 @@ __global__ void batch_init_kernel(int S, int pos0, int* done, int* n_out, int* c
 }
 
 template <int NT, int RG>
-int launch_skinny_nt(const SkArgs& a, int warps, int col_groups, cudaStream_t st) {
-    const size_t smem = (size_t)warps * (SK_DEPTH * RG * 544 + 4 * NT * RED_LD * sizeof(float));
+int launch_skinny_nt(const SkArgs& a, int warps, int col_groups, int splits, cudaStream_t st) {
+    auto bytes = [](int w, int depth) {
+        return (size_t)w * (depth * RG * 544 + 4 * NT * RED_LD * sizeof(float));
+    };
+    constexpr size_t kSmemCap = 200 * 1024;
     static bool attr[64] = {};
     int dev = 0;
     FC_CUDA(cudaGetDevice(&dev));
     if (dev < 64 && !attr[dev]) {
-        FC_CUDA(cudaFuncSetAttribute(skinny_q8_kernel<NT, RG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     8 * (SK_DEPTH * RG * 544 + 4 * NT * RED_LD * (int)sizeof(float))));
+        FC_CUDA(cudaFuncSetAttribute(skinny_q8_kernel<NT, RG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemCap));
         attr[dev] = true;
     }
-    FC_CUDA(launch_dep(skinny_q8_kernel<NT, RG>, dim3((a.N + 16 * RG - 1) / (16 * RG), col_groups), dim3(warps * 32), smem, st, a));
+    SkArgs b = a;
+    while (b.depth > 1 && bytes(warps, b.depth) > kSmemCap) --b.depth;   // a shallower ring when the slots are large
+    if (bytes(warps, b.depth) > kSmemCap) return fail(FC_E_SHAPE, "the lock-step product does not fit shared memory");
+    FC_CUDA(launch_dep(skinny_q8_kernel<NT, RG>, dim3((a.N + 16 * RG - 1) / (16 * RG), col_groups, splits), dim3(warps * 32),
+                       bytes(warps, b.depth), st, b));
     ++g_launches;
     return FC_OK;
 }
@@ -551,24 +620,33 @@ int launch_repack_frag(const QMat& w, void* fq, void* fd, cudaStream_t st) {
 
 int batch_cols(int S) { return S <= 8 ? 16 : S <= 16 ? 32 : S <= 32 ? 64 : 128; }
 
-int launch_skinny_q8(const QFrag& w, const void* xp, int S, const float* bias, const float* residual, int ldr, int epi,
-                     float* y, int ldy, void* yp, int ldp, cudaStream_t st) {
+int skinny_max_splits() { return SK_MAX_SPLITS; }
+
+int launch_skinny_q8(const QFrag& w, int S, const void* xp, const float* bias, int epi, const SkinnyOut& out, int* splits_used,
+                     cudaStream_t st) {
     if (S < 1 || S > kBatchMaxStreams) return fail(FC_E_SHAPE, "the lock-step product takes 1..%d streams (got %d)", kBatchMaxStreams, S);
     SkArgs a;
     a.wq = (const uint4*)w.q; a.wd = (const __half2*)w.d; a.xp = (const uint4*)xp;
     a.N = w.N; a.K = w.K; a.S = S;
-    a.bias = bias; a.residual = residual; a.ldr = ldr; a.epi = epi;
-    a.y = y; a.ldy = ldy; a.yp = (__half*)yp; a.ldp = ldp;
-    // warps split K: at least two 32-wide blocks each, at most 8 warps
-    const int nkb = w.K >> 5;
-    const int warps = nkb >= 16 ? 8 : nkb >= 8 ? 4 : nkb >= 4 ? 2 : 1;
-    // matrices with many rows give every SM several CTAs even at 32 rows per CTA; the others take 16
-    const bool wide = (w.N + 31) / 32 >= 2 * 148;
-    const int cols = batch_cols(S);
-    if (cols == 16) return wide ? launch_skinny_nt<2, 2>(a, warps, 1, st) : launch_skinny_nt<2, 1>(a, warps, 1, st);
-    if (cols == 32) return wide ? launch_skinny_nt<4, 2>(a, warps, 1, st) : launch_skinny_nt<4, 1>(a, warps, 1, st);
-    // 64 or 128 columns: CTAs of 64 columns, one or two per row range
-    return wide ? launch_skinny_nt<8, 2>(a, warps, cols / 64, st) : launch_skinny_nt<8, 1>(a, warps, cols / 64, st);
+    a.bias = bias; a.epi = epi; a.residual = out.residual;
+    a.y = out.y; a.ldy = out.ldy; a.yp = (__half*)out.planes; a.ldp = out.ldp; a.part_out = out.part;
+    const int nkb = w.K >> 5, cols = batch_cols(S);
+    // products that leave partial sums split K over CTAs as well: ranges of at least 8 blocks
+    int splits = 1;
+    if (out.part) splits = std::max(1, std::min(SK_MAX_SPLITS, nkb / 8));
+    if (splits_used) *splits_used = splits;
+    const int kb_cta = (nkb + splits - 1) / splits;
+    // warps split a CTA's K range: at least two 32-wide blocks each, at most 8 warps
+    const int warps = kb_cta >= 16 ? 8 : kb_cta >= 8 ? 4 : kb_cta >= 4 ? 2 : 1;
+    a.depth = std::max(1, std::min(SK_DEPTH, (kb_cta + warps - 1) / warps));
+    if (cols <= 32) {
+        // few streams: bound by the weight stream; 32 rows per CTA only when that still leaves every SM several CTAs
+        const bool wide = (w.N + 31) / 32 * splits >= 2 * 148;
+        if (cols == 16) return wide ? launch_skinny_nt<2, 2>(a, warps, 1, splits, st) : launch_skinny_nt<2, 1>(a, warps, 1, splits, st);
+        return wide ? launch_skinny_nt<4, 2>(a, warps, 1, splits, st) : launch_skinny_nt<4, 1>(a, warps, 1, splits, st);
+    }
+    // 17..64 streams: CTAs of 64 columns (one or two per row range), 32 rows each
+    return launch_skinny_nt<8, 2>(a, warps, cols / 64, splits, st);
 }
 
 int launch_embed_batch(const QMat& tok, const float* pos_emb, const int* cur, const int* pos, int S, float* x, cudaStream_t st) {
@@ -577,10 +655,12 @@ int launch_embed_batch(const QMat& tok, const float* pos_emb, const int* cur, co
     return FC_OK;
 }
 
-int launch_ln_rows_f16(const float* x, const float* g, const float* b, int S, int d, void* xp, cudaStream_t st) {
+int launch_ln_rows_f16(const float* x, const float* part, int n_part, const float* part_bias, float* x_out, const float* g,
+                       const float* b, int S, int d, void* xp, cudaStream_t st) {
     const int threads = 256, per = (d + threads - 1) / threads;
-    if (per <= 4) FC_CUDA(launch_dep(ln_rows_f16_kernel<4>, dim3(S), dim3(threads), 0, st, x, g, b, d, (__half*)xp));
-    else if (per <= 16) FC_CUDA(launch_dep(ln_rows_f16_kernel<16>, dim3(S), dim3(threads), 0, st, x, g, b, d, (__half*)xp));
+    if (!part) n_part = 0;
+    if (per <= 4) FC_CUDA(launch_dep(ln_rows_f16_kernel<4>, dim3(S), dim3(threads), 0, st, x, part, n_part, S, part_bias, x_out, g, b, d, (__half*)xp));
+    else if (per <= 16) FC_CUDA(launch_dep(ln_rows_f16_kernel<16>, dim3(S), dim3(threads), 0, st, x, part, n_part, S, part_bias, x_out, g, b, d, (__half*)xp));
     else return fail(FC_E_SHAPE, "LayerNorm width %d exceeds 4096", d);
     ++g_launches;
     return FC_OK;

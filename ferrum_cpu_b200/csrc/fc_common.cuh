@@ -197,12 +197,27 @@ size_t frag_scale_bytes(const QMat& w);
 int launch_repack_frag(const QMat& w, void* fq, void* fd, cudaStream_t st);
 // Columns of the activation planes for S streams (two f16 rows per stream, padded to the MMA tiling).
 int batch_cols(int S);
-// Y = X · Wᵀ (+bias, +GELU, +residual[S][ldr]) for S streams. xp: f16 planes [batch_cols(S)][K], row 2s = hi and
-// row 2s + 1 = lo of stream s (rows past 2S zero). Output: f32 rows y [S][ldy] and / or f16 planes yp [..][ldp].
-int launch_skinny_q8(const QFrag& w, const void* xp, int S, const float* bias, const float* residual, int ldr, int epi,
-                     float* y, int ldy, void* yp, int ldp, cudaStream_t st);
+// Y = X · Wᵀ for S streams. xp: f16 rows [batch_cols(S)][K], row 2s = hi and row 2s + 1 = lo of stream s (rows past
+// 2S zero).
+// Where the result goes: f32 rows (optionally residual + result; residual may be y) and / or f16 hi / lo rows (after
+// bias and epilogue), or raw partial sums part[splits][S][N] of K ranges (no bias; the consumer adds them in order,
+// then the bias and the residual).
+struct SkinnyOut {
+    float* y = nullptr;
+    int ldy = 0;
+    const float* residual = nullptr;
+    void* planes = nullptr;
+    int ldp = 0;
+    float* part = nullptr;
+};
+int skinny_max_splits();
+int launch_skinny_q8(const QFrag& w, int S, const void* xp, const float* bias, int epi, const SkinnyOut& out, int* splits_used,
+                     cudaStream_t st);
 int launch_embed_batch(const QMat& tok, const float* pos_emb, const int* cur, const int* pos, int S, float* x, cudaStream_t st);
-int launch_ln_rows_f16(const float* x, const float* g, const float* b, int S, int d, void* xp, cudaStream_t st);
+// LayerNorm rows as f16 hi / lo rows; with partials (part != null) the row is first completed, x_new = x + (sum of the
+// n_part partial products part[n_part][S][d] + part_bias), and stored to x_out.
+int launch_ln_rows_f16(const float* x, const float* part, int n_part, const float* part_bias, float* x_out, const float* g,
+                       const float* b, int S, int d, void* xp, cudaStream_t st);
 // qkv [S][3d] of this step; kcs / vcs: per-stream cache base pointers (device array), layer_off floats into each.
 int launch_attn_decode_batch(const float* qkv, float* const* kcs, float* const* vcs, size_t layer_off, int d, int H, int ctx,
                              const int* pos, int S, void* ap, cudaStream_t st);
