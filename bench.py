@@ -1,15 +1,28 @@
 #!/usr/bin/env python
 """Benchmark of the Q8_0 GPT-2 forward path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload decode|score|both]
-                    [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload ...] [--impl ours|reference]
+    python bench.py --case decode|score|linear|rowq|streams|llama-decode|llama-score [...]
 
 Workloads (synthetic, seeded; shapes of the reference's configurations):
-  decode : GPT-2-small-shaped Q8_0 model, batch 1, 32-token prompt, 256 greedy tokens with a
-           KV cache. One step = one such generation. metric: decode tokens/s. At N GPUs every
-           rank decodes its own stream (replicas only; the path does not shard).
-  score  : the same model, 512 sequences x 1024 ids scored per step (per-token log-probs),
-           sharded by sequence over the ranks with one gather of the results.
+  decode        : GPT-2-small-shaped Q8_0 model, batch 1, 32-token prompt, 256 greedy tokens with a
+                  KV cache. One step = one such generation. metric: decode tokens/s. At N GPUs every
+                  rank decodes its own stream (replicas only; the path does not shard).
+  score         : the same model, 512 sequences x 1024 ids scored per step (per-token log-probs),
+                  sharded by sequence over the ranks with one gather of the results.
+  both (default): decode + score, plus the concurrent-stream decodes (8 streams on the small shape,
+                  64 streams on the GPT-2-medium shape, split over the ranks); a short `summary`
+                  object closes the line.
+  streams-medium: the decode half of the medium-shaped configuration alone.
+  score-medium  : its scoring half, 1024 sequences x 1024 ids split over the ranks.
+  sweep         : the five (M, K, N) shapes of the standalone Q8_0 matmul sweep, each against the
+                  oracle's matmul engine.
+  tiny          : the 4-block CPU-sized configuration (16-token prompt, 64 greedy tokens).
+  llama-1b      : the imported Llama-shaped decoder.
+
+--case runs one small, self-terminating piece of the same kernels (a few tokens / windows / one
+product) and prints CUDA-event times: these are the command lines the profiler notes under
+profiles/ were captured with.
 
 `value` is device time of the hot path with inputs resident (CUDA events on the launching
 stream, max over ranks); `e2e` is the same metric through the C ABI with pinned host buffers,
@@ -33,8 +46,16 @@ import numpy as np  # noqa: E402
 PROMPT, NEW_TOKENS = 32, 256
 N_SEQ, SEQ_LEN = 512, 1024
 METRIC = "Q8_0 GPT-2-small decode tokens/s (batch 1, KV cache, greedy)"
-# dram__bytes_read.sum + dram__bytes_write.sum of decode_mega_kernel per token (ncu, see profiles/)
-DECODE_DRAM_BYTES_PER_TOKEN = 134.8e6 + 4.98e6
+
+
+def decode_dram_bytes_per_token():
+    """dram__bytes_read.sum + dram__bytes_write.sum of the persistent decode kernel per token, from the
+    tracked capture record (which names the kernel revision it was taken at); None when absent."""
+    path = os.path.join(ROOT, "profiles", "decode_mega_kernel_traffic.json")
+    if not os.path.exists(path):
+        return None
+    rec = json.load(open(path))
+    return float(rec["dram_bytes_read_per_token"]) + float(rec["dram_bytes_write_per_token"])
 
 
 def peaks():
@@ -136,6 +157,207 @@ def cpu_baseline_llama(sml, prompt, n_tokens):
     return n_tokens / dt
 
 
+SWEEP_SHAPES = [(1, 768, 2304), (1, 3072, 768), (1, 768, 50257), (512, 768, 3072), (4096, 1024, 4096)]
+STREAM_PROMPT, STREAM_NEW, STREAM_SEED = 64, 128, 200
+
+
+def stream_bytes_per_step(dims, S, p_first, n_steps):
+    """Algorithmic HBM bytes of one lock-step decode step for S streams, averaged over the cache positions
+    p_first .. p_first + n_steps - 1: every Q8_0 matrix once, the f32 vectors once, and per stream one
+    position row, one token row and the f32 K / V rows of positions 0..p (read) and p (written)."""
+    L, d, H, F, T, V = dims
+    q8 = (L * (4 * d * d + 2 * d * F) + d * V) * 34 // 32
+    small = (L * (9 * d + F) + 2 * d) * 4
+    per_stream = d * 4 + d * 34 // 32
+    kv = sum(L * 2 * (p + 1) * d * 4 + L * 2 * d * 4 for p in range(p_first, p_first + n_steps)) / max(n_steps, 1)
+    return q8 + small + S * (per_stream + kv)
+
+
+def run_streams(fcb, synth, shard, name, n_streams, local, rank, world, steps, barrier, max_over_ranks, hbm_peak, peak_kind):
+    """The concurrent-stream decode workload on model `name`: n_streams streams (split over the ranks in
+    contiguous blocks) x (64-id prompt + 128 greedy tokens), lock step. Returns the result object."""
+    sm = synth.named(name, seed=0, math_mode=fcb.FC_MATH_BF16X3)
+    gm = fcb.CudaSlm(sm.config, sm.weights, device=local)
+    a0, a1 = shard.shard_range(n_streams, rank, world)
+    S = a1 - a0
+    prompts = np.stack([synth.token_ids(STREAM_SEED + i, STREAM_PROMPT, sm.dims[5]) for i in range(a0, a1)])
+    outs = gm.decode_batch(prompts, STREAM_NEW)                # warm-up: builds the weight copies, caches and the step graph
+    fcb.take_launch_count()
+    ms, prime, wall = [], [], []
+    barrier()
+    for _ in range(max(1, steps)):
+        t0 = time.perf_counter()
+        outs = gm.decode_batch(prompts, STREAM_NEW)            # host prompts in, host tokens out
+        wall.append(time.perf_counter() - t0)
+        ms.append(gm.last_batch_ms)
+        prime.append(gm.last_batch_prime_ms)
+    barrier()
+    launches = fcb.take_launch_count()
+    step_ms = max_over_ranks(sum(ms) / len(ms))
+    prime_ms = max_over_ranks(sum(prime) / len(prime))
+    wall_s = max_over_ranks(sum(wall) / len(wall))
+    n_steps = STREAM_NEW - 1                                    # token 1 comes out of the prime
+    per_step_s = (step_ms - prime_ms) / 1e3 / n_steps
+    byts = stream_bytes_per_step(sm.dims, S, STREAM_PROMPT, n_steps)
+    gbs = byts / per_step_s / 1e9
+    checksum = int(sum(int(o.sum()) for o in outs))
+    gm.close()
+    return {
+        "metric": "Q8_0 GPT-2-%s decode tokens/s, %d concurrent streams" % (name, n_streams),
+        "value": n_streams * STREAM_NEW / (step_ms / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": max(1, steps),
+        "ms_per_step": step_ms, "prime_ms": prime_ms, "us_per_decode_step": per_step_s * 1e6,
+        "higher_is_better": True, "scaling": "strong" if world > 1 else "n/a", "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "%d streams x (%d-id prompt + %d greedy tokens) on the GPT-2-%s shape, %d streams per GPU in lock "
+                               "step: one tensor-core window forward primes all prompts, then every step reads each Q8_0 matrix "
+                               "once for all streams; device time includes the primes" % (n_streams, STREAM_PROMPT, STREAM_NEW, name, S)},
+        "e2e": {"value": n_streams * STREAM_NEW / wall_s, "unit": "tokens/s", "h2d_bytes_per_step": S * STREAM_PROMPT * 4,
+                "d2h_bytes_per_step": S * STREAM_NEW * 4 + S * 4},
+        "gpu_launches": int(launches),
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s", "frac": gbs / hbm_peak, "traffic": None,
+                     "peak_kind": peak_kind,
+                     "what": "per GPU, decode steps only (prime excluded): %.1f MB algorithmic per step for %d streams "
+                             "(weights once + f32 K/V rows per stream)" % (byts / 1e6, S)},
+        "token_checksum": checksum,
+    }
+
+
+def run_sweep(fcb, synth, torch, shapes, reps, with_oracle):
+    """The standalone Q8_0 matmul sweep: device time of one product with the weight resident (CUDA events on
+    the launching stream, L2 flushed between repetitions), and the error against the oracle's matmul engine."""
+    import ctypes as C
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    rows = []
+    for (m, k, n) in shapes:
+        w = synth.Rng(21).normal(n * k, 0.02)
+        wq = synth.q8_0_quantize(w)
+        x_h = synth.Rng(22).normal(m * k, 1.0).reshape(m, k)
+        qw = fcb.QWeight(wq, n, k)
+        x = torch.from_numpy(x_h).cuda()
+        y = torch.empty(m, n, device="cuda")
+        want = None
+        if with_oracle:
+            from tests import oracle as O
+            want = O.linear(x_h, O.expand_kn(wq, n, k), None, threads=os.cpu_count() or 1)
+        byts = n * k * 34 / 32 + 4 * m * k + 4 * m * n
+        row = {"M": m, "K": k, "N": n, "algorithmic_bytes": byts, "flop": 2.0 * m * k * n}
+        for mode, label in ((fcb.FC_MATH_FP32, "fp32"), (fcb.FC_MATH_BF16X3, "bf16x3")):
+            if m == 1 and mode != fcb.FC_MATH_FP32:
+                continue                                   # one row is the decode GEMV whatever the mode
+            best = None
+            for _ in range(max(3, reps)):
+                flush.zero_()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                qw.linear_dev(x.data_ptr(), None, y.data_ptr(), m, mode, st)
+                e1.record()
+                torch.cuda.synchronize()
+                t = e0.elapsed_time(e1)
+                best = t if best is None else min(best, t)
+            r = {"us": best * 1e3, "GBps": byts / best / 1e6, "TFLOPs": 2.0 * m * k * n / best / 1e9}
+            if want is not None:
+                got = y.cpu().numpy()
+                r["max_abs_err"] = float(np.abs(got - want).max())
+                r["max_err_rel_to_scale"] = float(np.abs(got - want).max() / np.abs(want).max())
+            row["gemv" if m == 1 else label] = r
+        qw.close()
+        rows.append(row)
+    return rows
+
+
+def run_case(a):
+    """Small self-terminating cases for profiler captures (same kernels as the workloads)."""
+    import ctypes as C
+
+    import torch
+
+    import ferrum_cpu_b200 as fcb
+    from ferrum_cpu_b200 import synth
+    if a.case == "linear":
+        for row in run_sweep(fcb, synth, torch, [(a.m, a.k, a.n)], a.reps, False):
+            print(json.dumps(row))
+        return
+    if a.case == "rowq":
+        from ferrum_cpu_b200.engine import RowQWeight
+        w = synth.Rng(21).normal(a.k * a.n, 0.02).reshape(a.k, a.n)
+        qw = RowQWeight.from_f32(w, a.kind)
+        x = torch.randn(a.m, a.k, device="cuda")
+        bias = torch.zeros(a.n, device="cuda")
+        y = torch.empty(a.m, a.n, device="cuda")
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+        st = torch.cuda.current_stream().cuda_stream
+        for _ in range(a.reps):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            qw.linear_dev(x.data_ptr(), bias.data_ptr(), y.data_ptr(), a.m, C.c_void_p(st))
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1)
+            byts = a.k * a.n / (2 if a.kind else 1) + 4 * a.k + 4 * a.m * (a.k + a.n)
+            print(f"rowq {'int4' if a.kind else 'int8'} M={a.m} K={a.k} N={a.n}: {ms * 1e3:.1f} us, {byts / ms / 1e6:.1f} GB/s")
+        return
+    if a.case.startswith("llama"):
+        from ferrum_cpu_b200.engine import sampling
+        from ferrum_cpu_b200.llama import CudaLlama
+        name = a.model if a.model.startswith("llama") else "llama-1b"
+        sm = synth.llama_named(name, seed=0, math_mode=a.math)
+        c = sm.dims
+        gm = CudaLlama.from_synth(sm)
+        if a.case == "llama-decode":
+            prompt = synth.token_ids(0, a.prompt, c["vocab"])
+            cache = gm.new_cache()
+            kvd = c["n_kv_head"] * c["head_dim"]
+            for _ in range(a.reps):
+                gm.generate(prompt, a.tokens, sampling(temperature=0.0), cache=cache)
+                us = cache.last_decode_ms / a.tokens * 1e3
+                kv = c["n_layer"] * 2 * (a.prompt + a.tokens / 2) * kvd * 4
+                print(f"{name} decode {a.tokens} tokens: device {us:.1f} us/token, {(sm.q8_weight_bytes + kv) / us / 1e3:.0f} GB/s "
+                      f"algorithmic, launches {fcb.take_launch_count()}")
+        else:
+            T = min(c["ctx"], 1024)
+            ids = synth.token_ids(1, a.windows * T, c["vocab"]).reshape(a.windows, T)
+            for _ in range(a.reps):
+                gm.score_sequences(ids, batch_windows=a.windows)
+                print(f"{name} score {a.windows} x {T}: device {gm.last_score_ms:.2f} ms, launches {fcb.take_launch_count()}")
+        gm.close()
+        return
+    sm = synth.named(a.model, seed=0, math_mode=a.math)
+    V, T = sm.dims[5], sm.dims[4]
+    gm = fcb.CudaSlm(sm.config, sm.weights)
+    if a.case == "decode":
+        prompt = synth.token_ids(0, a.prompt, V)
+        gm.set_decode_mode(a.mode)
+        for _ in range(a.reps):
+            gm.generate_tokens(prompt, a.tokens)
+            print(f"decode {a.tokens} tokens: device {gm.last_decode_ms / a.tokens * 1e3:.1f} us/token, launches {fcb.take_launch_count()}")
+        if a.trace and a.mode == 0:
+            # phase timeline of one token of the persistent kernel (CTA 0), mean over blocks
+            gm.set_trace(True)
+            gm.generate_tokens(prompt, a.tokens)
+            t = gm.read_trace()
+            gm.set_trace(False)
+            L = sm.dims[0]
+            names = ["ln1", "qkv", "barrier", "attn", "barrier", "combine", "out", "barrier", "load+ln2", "up", "barrier", "load",
+                     "down", "barrier", "load"]
+            if len(t) >= 1 + 15 * L:
+                per = np.diff(t[:1 + 15 * L]).reshape(L, 15)
+                print("phase timeline of CTA 0 (ns, mean over blocks): " + ", ".join(f"{n} {per[:, i].mean():.0f}" for i, n in enumerate(names)))
+                print(f"blocks {per.sum():.0f} ns; head + select {t[-1] - t[15 * L]:.0f} ns; token {t[-1]:.0f} ns")
+    elif a.case == "streams":
+        prompts = np.stack([synth.token_ids(STREAM_SEED + i, a.prompt, V) for i in range(a.streams)])
+        for _ in range(a.reps):
+            gm.decode_batch(prompts, a.tokens)
+            print(f"{a.streams} streams x {a.tokens} tokens: device {gm.last_batch_ms:.3f} ms (prime {gm.last_batch_prime_ms:.3f} ms), "
+                  f"launches {fcb.take_launch_count()}")
+    else:
+        ids = synth.token_ids(1, a.windows * T, V).reshape(a.windows, T)
+        for _ in range(a.reps):
+            gm.score_sequences(ids, batch_windows=a.windows)
+            print(f"score {a.windows} x {T}: device {gm.last_score_ms:.2f} ms, launches {fcb.take_launch_count()}")
+    gm.close()
+
+
 def run_reference(args, rank):
     """--impl reference: the CPU restatement of the reference path, bounded samples."""
     if rank != 0:
@@ -181,10 +403,23 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", choices=["decode", "score", "both", "streams-medium", "llama-1b"], default="both",
-                    help="both: configs[1] decode (+ 8 side-by-side streams) and configs[2] scoring; streams-medium: the decode "
-                         "half of configs[4] on the GPT-2-medium shape (64 streams split over the ranks); llama-1b: greedy decode and "
-                         "one-window scoring of a Llama-3.2-1B-shaped Q8_0 model (the imported-model path, replicas per rank)")
+    ap.add_argument("--workload", choices=["decode", "score", "both", "streams-medium", "score-medium", "sweep", "tiny", "llama-1b"],
+                    default="both", help="see the module docstring")
+    ap.add_argument("--case", choices=["decode", "score", "linear", "rowq", "streams", "llama-decode", "llama-score"], default=None,
+                    help="run one small self-terminating case (for profiler captures) instead of a workload")
+    ap.add_argument("--model", default="small")
+    ap.add_argument("--tokens", type=int, default=8)
+    ap.add_argument("--prompt", type=int, default=32)
+    ap.add_argument("--windows", type=int, default=4)
+    ap.add_argument("--streams", type=int, default=8)
+    ap.add_argument("--m", type=int, default=1)
+    ap.add_argument("--k", type=int, default=768)
+    ap.add_argument("--n", type=int, default=50257)
+    ap.add_argument("--reps", type=int, default=3)
+    ap.add_argument("--math", type=int, default=0, help="--case: 0 fp32 CUDA cores, 1 tcgen05 bf16x3")
+    ap.add_argument("--kind", type=int, default=0, help="--case rowq: 0 int8, 1 int4")
+    ap.add_argument("--mode", type=int, default=0, help="--case decode: 0 persistent kernel, 1 one kernel per operation")
+    ap.add_argument("--trace", action="store_true", help="--case decode: print the phase timeline of one token")
     ap.add_argument("--score-steps", type=int, default=2)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -196,6 +431,9 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.case:
+        run_case(args)
         return
 
     import torch
@@ -231,27 +469,94 @@ def main():
 
     hbm_peak, tf_peak, peak_kind = peaks()
     if args.workload == "streams-medium":
-        # configs[4], decode half: 64 streams of 64-id prompts + 128 greedy tokens, split over the ranks
-        smm = synth.named("medium", seed=0)
+        # the decode half of the medium-shaped configuration: 64 streams split over the ranks
+        res = run_streams(fcb, synth, shard, "medium", 64, local, rank, world, args.steps, barrier, max_over_ranks, hbm_peak, peak_kind)
+        if rank == 0:
+            print(json.dumps(dict(res, warmup=1, vs_baseline=None)))
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    if args.workload == "score-medium":
+        # its scoring half: 1024 sequences x 1024 ids, split over the ranks in contiguous blocks
+        smm = synth.named("medium", seed=0, math_mode=fcb.FC_MATH_BF16X3)
         gmm = fcb.CudaSlm(smm.config, smm.weights, device=local)
-        a0, a1 = shard.shard_range(64, rank, world)
-        prompts = np.stack([synth.token_ids(200 + i, 64, smm.dims[5]) for i in range(a0, a1)])
-        gmm.decode_batch(prompts, 128)
-        ms = []
+        n_seq = 1024
+        a0, a1 = shard.shard_range(n_seq, rank, world)
+        ids = synth.token_ids(1, n_seq * SEQ_LEN, smm.dims[5]).reshape(n_seq, SEQ_LEN)[a0:a1]
+        gmm.score_sequences(ids[:32], batch_windows=32)
+        ms, wall = [], []
         barrier()
-        for _ in range(args.steps):
-            gmm.decode_batch(prompts, 128)
-            ms.append(gmm.last_batch_ms)
+        for _ in range(max(1, args.score_steps)):
+            t0 = time.perf_counter()
+            scores, _ = gmm.score_sequences(ids, batch_windows=32)
+            wall.append(time.perf_counter() - t0)
+            ms.append(gmm.last_score_ms)
         barrier()
         step_ms = max_over_ranks(sum(ms) / len(ms))
+        wall_s = max_over_ranks(sum(wall) / len(wall))
+        fl = score_flops_per_position(smm.dims) * n_seq * SEQ_LEN
+        tf = fl / world / (step_ms / 1e3) / 1e12
         if rank == 0:
-            print(json.dumps({"metric": "Q8_0 GPT-2-medium decode tokens/s, 64 concurrent streams (configs[4])", "value": 64 * 128 / (step_ms / 1e3),
-                              "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "ms_per_step": step_ms, "higher_is_better": True,
-                              "scaling": "strong", "dtype": "f32", "data": "synthetic",
-                              "config": {"workload": "configs[4] decode: L24 d1024 H16 F4096 ctx1024 V50257, 64 streams x (64-id prompt + 128 greedy tokens), "
-                                                     "%d streams per GPU, up to 8 side by side; prompts primed as one batch per wave; device time "
-                                                     "includes the primes" % (a1 - a0)}}))
+            print(json.dumps({
+                "metric": "Q8_0 GPT-2-medium log-likelihood positions/s", "value": n_seq * SEQ_LEN / (step_ms / 1e3), "unit": "positions/s",
+                "n_gpus": world, "steps": max(1, args.score_steps), "warmup": 1, "ms_per_step": step_ms, "higher_is_better": True,
+                "scaling": "strong" if world > 1 else "n/a", "vs_baseline": None, "dtype": "bf16x3", "data": "synthetic",
+                "config": {"workload": "GPT-2-medium shape L24 d1024 H16 F4096 ctx1024 V50257: %d sequences x %d ids, full-window "
+                                       "prefill, per-token log-probs, 32 windows per forward, %d sequences per GPU" % (n_seq, SEQ_LEN, a1 - a0)},
+                "e2e": {"value": n_seq * SEQ_LEN / wall_s, "unit": "positions/s", "h2d_bytes_per_step": (a1 - a0) * SEQ_LEN * 4,
+                        "d2h_bytes_per_step": (a1 - a0) * SEQ_LEN * 4},
+                "roofline": {"bound": "tensor", "achieved": tf, "peak": tf_peak, "unit": "TFLOP/s", "frac": tf / tf_peak, "traffic": None,
+                             "peak_kind": peak_kind, "what": "per GPU: algorithmic FLOP of the rank's sequences / its step time"},
+                "checksum_logprob": sum_over_ranks(float(sum(sc.logprob for sc in scores)))}))
         gmm.close()
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    if args.workload == "sweep":
+        rows = run_sweep(fcb, synth, torch, SWEEP_SHAPES, args.steps, rank == 0 and not args.no_cpu_baseline) if rank == 0 else []
+        if rank == 0:
+            big = rows[-1]
+            print(json.dumps({
+                "metric": "Q8_0 matmul sweep, (4096, 1024, 4096) TFLOP/s (bf16x3)", "value": big["bf16x3"]["TFLOPs"], "unit": "TFLOP/s",
+                "n_gpus": 1, "steps": max(3, args.steps), "warmup": 0, "ms_per_step": big["bf16x3"]["us"] / 1e3, "higher_is_better": True,
+                "scaling": "n/a", "vs_baseline": None, "dtype": "bf16x3 / f32", "data": "synthetic",
+                "config": {"workload": "standalone Q8_0 linear, weight resident, five (M, K, N) shapes; M = 1 is the decode GEMV "
+                                       "(GB/s of algorithmic bytes), M >= 512 the prefill GEMM in both math modes (TFLOP/s); 256 MiB "
+                                       "written between repetitions; best of the repetitions; errors against the oracle's matmul engine"},
+                "peaks": {"hbm_gbs": hbm_peak, "bf16_tflops": tf_peak, "kind": peak_kind},
+                "shapes": rows}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    if args.workload == "tiny":
+        # the 4-block configuration the reference itself runs on a CPU: 16-token prompt, 64 greedy tokens
+        smt = synth.named("tiny", seed=0)
+        gmt = fcb.CudaSlm(smt.config, smt.weights, device=local)
+        prompt = synth.token_ids(0, 16, smt.dims[5])
+        for _ in range(max(3, args.warmup)):
+            gmt.generate_tokens(prompt, 64)
+        ms, wall = [], []
+        barrier()
+        for _ in range(args.steps):
+            t0 = time.perf_counter()
+            gmt.generate_tokens(prompt, 64)
+            wall.append(time.perf_counter() - t0)
+            ms.append(gmt.last_decode_ms)
+        barrier()
+        step_ms = max_over_ranks(sum(ms) / len(ms))
+        wall_s = max_over_ranks(sum(wall) / len(wall))
+        if rank == 0:
+            res = {"metric": "Q8_0 tiny GPT-2 decode tokens/s (batch 1, KV cache, greedy)", "value": world * 64 / (step_ms / 1e3),
+                   "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": step_ms,
+                   "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                   "config": {"workload": "L4 d128 H4 F512 ctx128 V4096, 16-token prompt, 64 greedy tokens, one stream per GPU; the "
+                                          "model (1.4 MB of Q8_0) lives in L2: latency-bound, no roofline"},
+                   "e2e": {"value": world * 64 / wall_s, "unit": "tokens/s", "h2d_bytes_per_step": 64, "d2h_bytes_per_step": 64 * 4 + 32}}
+            if not args.no_cpu_baseline and world == 1:
+                res["cpu_baseline"] = {"value": cpu_baseline_decode(smt, prompt, 48), "unit": "tokens/s", "cores": 1, "kind": "port",
+                                       "sample": "48 KV-cached feeds after the 16-token prompt, 1 thread"}
+            print(json.dumps(res))
+        gmt.close()
         if world > 1:
             dist.destroy_process_group()
         return
@@ -364,27 +669,21 @@ def main():
                     "note": "fc_generate_greedy from pinned host buffers: prompt upload, 32-token prime, 256 feeds, token download"},
             "gpu_launches": int(launches),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
-                         "traffic": DECODE_DRAM_BYTES_PER_TOKEN * 32, "peak_kind": peak_kind,
-                         "what": "decode_mega_kernel, launches of 32 tokens: %.1f MB algorithmic per token; traffic = "
-                                 "ncu dram read+write of a one-token launch at position 38 (134.8 + 4.98 MB, "
-                                 "profiles/decode_mega_kernel_gpt2small_7tokens.md) scaled to 32 tokens" % (bpt / 1e6)},
+                         "traffic": None if decode_dram_bytes_per_token() is None else decode_dram_bytes_per_token() * 32,
+                         "peak_kind": peak_kind,
+                         "what": "decode_mega_kernel, launches of 32 tokens: %.1f MB algorithmic per token; traffic = ncu dram "
+                                 "read + write of a one-token launch at position 38, scaled to 32 tokens" % (bpt / 1e6)},
             "clocks": clocks,
         }
-        # the per-GPU share of configs[4]'s 64 streams (8 at 8 GPUs), on this model: side-by-side persistent kernels
-        sp = np.stack([synth.token_ids(200 + 8 * rank + i, 64, V) for i in range(8)])
-        gm.decode_batch(sp, 128)
-        ms = []
-        barrier()
-        for _ in range(3):
-            gm.decode_batch(sp, 128)
-            ms.append(gm.last_batch_ms)
-        barrier()
-        sb_ms = max_over_ranks(sum(ms) / len(ms))
-        out["decode_streams"] = {"metric": "Q8_0 GPT-2-small decode tokens/s, 8 concurrent streams per GPU", "value": world * 8 * 128 / (sb_ms / 1e3),
-                                 "unit": "tokens/s", "ms_per_step": sb_ms, "n_gpus": world,
-                                 "config": {"workload": "8 streams per GPU x (64-id prompt + 128 greedy tokens), one persistent kernel per stream on "
-                                                        "an eighth of the SMs; device time includes the batched prime of the 8 prompts"},
-                                 "gpu_launches": int(fcb.take_launch_count())}
+        if args.workload == "both":
+            # concurrent streams: 8 per GPU on this shape, and the medium-shaped 64-stream workload split over the ranks
+            gm.close()
+            gm = None
+            out["decode_streams"] = run_streams(fcb, synth, shard, "small", 8 * world, local, rank, world, 3, barrier, max_over_ranks,
+                                                hbm_peak, peak_kind)
+            out["streams_medium"] = run_streams(fcb, synth, shard, "medium", 64, local, rank, world, 2, barrier, max_over_ranks,
+                                                hbm_peak, peak_kind)
+            gm = fcb.CudaSlm(sm.config, sm.weights, device=local)
 
     if args.workload in ("score", "both"):
         ids_all = synth.token_ids(1, N_SEQ * SEQ_LEN, V).reshape(N_SEQ, SEQ_LEN)
@@ -452,8 +751,29 @@ def main():
                 tgt = out["score"] if "score" in out else out
                 tgt["cpu_baseline"] = {"value": v, "unit": "positions/s", "cores": cores, "kind": "port",
                                        "sample": f"one {SEQ_LEN}-id window of configs[2], {cores} threads"}
+        # the figures every reader needs, short and last (a log tail keeps them); at N > 1 the long descriptions go
+        subs = [k for k in ("decode_streams", "streams_medium", "score") if k in out]
+        if world > 1:
+            for k in subs:
+                out[k].pop("config", None)
+                out[k].get("roofline", {}).pop("what", None)
+        summary = {"n_gpus": world}
+        if out.get("unit") == "tokens/s":
+            summary.update(decode_tok_s=round(out["value"], 1), decode_e2e_tok_s=round(out["e2e"]["value"], 1),
+                           decode_hbm_frac=round(out["roofline"]["frac"], 4))
+        for k, short in (("decode_streams", "streams_small"), ("streams_medium", "streams_medium")):
+            if k in out:
+                summary[short + "_tok_s"] = round(out[k]["value"], 1)
+                summary[short + "_e2e_tok_s"] = round(out[k]["e2e"]["value"], 1)
+                summary[short + "_step_hbm_frac"] = round(out[k]["roofline"]["frac"], 4)
+        sc = out.get("score", out if out.get("unit") == "positions/s" else None)
+        if sc:
+            summary.update(score_pos_s=round(sc["value"], 1), score_e2e_pos_s=round(sc["e2e"]["value"], 1), score_ms=round(sc["ms_per_step"], 2),
+                           score_tensor_frac=round(sc["roofline"]["frac"], 4))
+        out["summary"] = summary
         print(json.dumps(out))
-    gm.close()
+    if gm is not None:
+        gm.close()
     if world > 1:
         dist.destroy_process_group()
 

@@ -101,6 +101,8 @@ SIGNATURES = {
     "fc_generate_sampled": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int32, C.POINTER(FcSampling), C.POINTER(C.c_uint64), C.c_void_p, C.c_void_p, C.POINTER(C.c_int)]),
     "fc_decode_batch": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int32, C.c_void_p, C.c_void_p]),
     "fc_last_batch_ms": (C.c_float, [C.c_void_p]),
+    "fc_last_batch_prime_ms": (C.c_float, [C.c_void_p]),
+    "fc_debug_set_wait_budget": (C.c_int, [C.c_longlong, C.c_int]),
     "fc_llama_create": (C.c_int, [C.POINTER(FcLlamaConfig), C.POINTER(FcLlamaWeights), C.c_int, C.POINTER(C.c_void_p)]),
     "fc_llama_free": (None, [C.c_void_p]),
     "fc_llama_load_gguf": (C.c_int, [C.c_char_p, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_void_p)]),

@@ -15,6 +15,7 @@ namespace fc {
 // ------------------------------------------------------------------------------- errors
 static thread_local char g_err[512] = "";
 thread_local int64_t g_launches = 0;
+DebugKnobs g_debug;
 
 void set_error(const char* fmt, ...) {
     va_list ap;
@@ -163,7 +164,8 @@ struct fc_model {
     int mega_grid = 0;                   // grid of mega_tables[0]
     // streams created by fc_decode_batch, kept for the next call
     std::vector<fc_stream*> pool;
-    float last_batch_ms = 0.0f;
+    float last_batch_ms = 0.0f, last_batch_prime_ms = 0.0f;
+    cudaEvent_t ev_prime = nullptr;
     BatchCtx batch;
 };
 
@@ -279,6 +281,7 @@ static int run_mega(fc_stream* s, int n, int head_from, int select, int probs) {
     p.attn_splits = std::max(1, std::min(s->attn_splits, tab.grid / c.n_head));
     p.trace = s->trace_on ? s->trace : nullptr;
     p.trace_cap = kTraceCap;
+    p.wait_cycles = g_debug.wait_cycles; p.withhold = g_debug.withhold;
     cudaStream_t st = s->cs ? s->cs : m->st;
     if (p.trace) FC_CUDA(cudaMemsetAsync(s->trace, 0, (size_t)m->mega_grid * kTraceCap * sizeof(unsigned long long), st));
     return launch_decode_mega(p, tab.grid, st);
@@ -697,6 +700,7 @@ void fc_model_free(fc_model* m) {
     m->batch.frag_arena.release();
     if (m->ev0) cudaEventDestroy(m->ev0);
     if (m->ev1) cudaEventDestroy(m->ev1);
+    if (m->ev_prime) cudaEventDestroy(m->ev_prime);
     if (m->st) cudaStreamDestroy(m->st);
     delete m;
 }
@@ -1487,6 +1491,8 @@ int fc_decode_batch(fc_model* m, int n_streams, const int32_t* prompts, int prom
         m->pool.push_back(s);
     }
     m->last_batch_ms = 0.0f;
+    m->last_batch_prime_ms = 0.0f;
+    if (!m->ev_prime) FC_CUDA(cudaEventCreate(&m->ev_prime));
     const int hd = c.d_model / c.n_head;
     const bool lock_step = n_streams >= 2 && max_new > 0 && prompt_len + max_new <= c.ctx && hd <= 64 && hd % 4 == 0 &&
                            (size_t)(c.ctx + 4 + 64 + 1024) * sizeof(float) <= 48 * 1024;
@@ -1506,6 +1512,7 @@ int fc_decode_batch(fc_model* m, int n_streams, const int32_t* prompts, int prom
     FC_CUDA(cudaEventRecord(m->ev0, st));
     for (int w0 = 0; w0 < n_streams; w0 += kBatchMaxStreams) {
         const int S = std::min(kBatchMaxStreams, n_streams - w0);
+        if (w0 > 0) FC_CUDA(cudaEventRecord(m->ev1, st));   // start of this wave's prime (the first wave starts at ev0)
         // prime: all prompts of the wave as one batch of windows; the last row of each selects token 1
         std::vector<fc_stream*> wv;
         for (int i = 0; i < S; ++i) {
@@ -1539,6 +1546,7 @@ int fc_decode_batch(fc_model* m, int n_streams, const int32_t* prompts, int prom
             for (int i = 0; i < S; ++i) FC_TRY(run_steps(wv[i], prompt_len, STEP_NOHEAD, STEP_SELECT));
             FC_TRY(launch_gather_first(b.queues, b.states, prompt_len, S, b.cur, b.done, b.n_out, b.out_tok, b.out_cap, b.pos, st));
         }
+        FC_CUDA(cudaEventRecord(m->ev_prime, st));
         std::vector<int> done(S, 0);
         for (int i = 1; i < max_new; ++i) {        // step i feeds token i and picks token i + 1
             FC_TRY(batch_run_step(m, S, eos));
@@ -1556,6 +1564,11 @@ int fc_decode_batch(fc_model* m, int n_streams, const int32_t* prompts, int prom
         FC_CUDA(cudaMemcpyAsync(toks.data(), b.out_tok, toks.size() * 4, cudaMemcpyDeviceToHost, st));
         FC_CUDA(cudaMemcpyAsync(&pos_h, b.pos, sizeof(int), cudaMemcpyDeviceToHost, st));
         FC_CUDA(cudaStreamSynchronize(st));
+        {
+            float pm = 0.0f;
+            FC_CUDA(cudaEventElapsedTime(&pm, w0 > 0 ? m->ev1 : m->ev0, m->ev_prime));
+            m->last_batch_prime_ms += pm;
+        }
         for (int i = 0; i < S; ++i)
             if (done[i] == 2) return fail(FC_E_CUDA, "fc_decode_batch: stream %d produced no finite logit", w0 + i);
         for (int i = 0; i < S; ++i) {
@@ -1572,5 +1585,13 @@ int fc_decode_batch(fc_model* m, int n_streams, const int32_t* prompts, int prom
 }
 
 float fc_last_batch_ms(const fc_model* m) { return m ? m->last_batch_ms : 0.0f; }
+float fc_last_batch_prime_ms(const fc_model* m) { return m ? m->last_batch_prime_ms : 0.0f; }
+
+int fc_debug_set_wait_budget(long long cycles, int withhold_producers) {
+    if (cycles <= 0) return fail(FC_E_ARG, "fc_debug_set_wait_budget: cycles = %lld", cycles);
+    g_debug.wait_cycles = cycles;
+    g_debug.withhold = withhold_producers != 0;
+    return FC_OK;
+}
 
 }  // extern "C"

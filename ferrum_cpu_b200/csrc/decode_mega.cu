@@ -48,7 +48,6 @@ constexpr int DIG_STRIDE = MAX_D + 32;          // bytes between digit planes: 3
 constexpr int HEAD_SC_OFF = (4 * DIG_STRIDE) / 4 + MAX_D / 32;   // floats: digit planes, then the block scales
 constexpr int MAX_ROWS_HEAD = MAX_F - HEAD_SC_OFF;
 constexpr int PARAM_FLOATS = 4 * MAX_D + kMegaBiasPackMax;   // LayerNorm vectors + bias slices
-constexpr long long WAIT_CYCLES = 4000000000LL;           // ~2 s at 1.9 GHz
 
 struct Ctrl {
     unsigned long long full[SLOTS];
@@ -248,7 +247,7 @@ struct Cta {
     __device__ float* param(int b) const { return (float*)(smem + OFF_PARAM) + b * PARAM_FLOATS; }
 };
 
-__device__ __forceinline__ bool timed_out(long long t0) { return clock64() - t0 > WAIT_CYCLES; }
+__device__ __forceinline__ bool timed_out(const Cta& k, long long t0) { return clock64() - t0 > k.p.wait_cycles; }
 
 // Phase timeline: thread 0 of every CTA stores the global timer at every phase boundary.
 __device__ __forceinline__ void mark(Cta& k) {
@@ -270,7 +269,7 @@ __device__ bool producer_wait(Cta& k, unsigned long long* bar, uint32_t parity) 
     const long long t0 = clock64();
     while (!mbar_try_wait(bar, parity)) {
         if (k.ctrl->stop) return false;
-        if (timed_out(t0)) { atomicExch(k.p.status, FC_E_TIMEOUT); return false; }
+        if (timed_out(k, t0)) { atomicExch(k.p.status, FC_E_TIMEOUT); return false; }
     }
     return k.ctrl->stop == 0;
 }
@@ -322,6 +321,7 @@ __device__ bool produce_params(Cta& k, const float* lnpack, const float* biaspac
 
 __device__ void producer(Cta& k) {
     const MegaParams& p = k.p;
+    if (p.withhold) return;   // test hook: nothing is copied, the consumers' first wait runs out
     for (int step = 0; step < p.n_steps; ++step) {
         for (int l = 0; l < p.L; ++l) {
             const MegaLayer& L = k.layers[l];
@@ -431,7 +431,7 @@ __device__ void layernorm_to_act(Cta& k, const float* g, const float* b, bool di
 __device__ bool consumer_wait(Cta& k, unsigned long long* bar, uint32_t parity) {
     const long long t0 = clock64();
     while (!mbar_try_wait(bar, parity)) {
-        if (timed_out(t0)) { raise_timeout(k); break; }
+        if (timed_out(k, t0)) { raise_timeout(k); break; }
     }
     consumer_sync();
     return k.ctrl->abort == 0;
@@ -450,7 +450,7 @@ __device__ bool grid_barrier(Cta& k) {
             // the status word and the clock are only looked at every 64 polls
             if ((++polls & 63u) == 0) {
                 if (*(volatile int*)k.p.status != 0) { k.ctrl->abort = 1; break; }
-                if (timed_out(t0)) { raise_timeout(k); break; }
+                if (timed_out(k, t0)) { raise_timeout(k); break; }
             }
         }
     }
@@ -1004,12 +1004,12 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_co
         for (int i = ctrl->consumed; i < k.item; ++i) {
             const long long t0 = clock64();
             while (!mbar_try_wait(&ctrl->full[i % SLOTS], (i / SLOTS) & 1))
-                if (timed_out(t0)) { atomicExch(p.status, FC_E_TIMEOUT); break; }
+                if (clock64() - t0 > p.wait_cycles) { atomicExch(p.status, FC_E_TIMEOUT); break; }
         }
         for (int i = ctrl->pconsumed; i < k.pitem; ++i) {
             const long long t0 = clock64();
             while (!mbar_try_wait(&ctrl->pfull[i & 1], (i >> 1) & 1))
-                if (timed_out(t0)) { atomicExch(p.status, FC_E_TIMEOUT); break; }
+                if (clock64() - t0 > p.wait_cycles) { atomicExch(p.status, FC_E_TIMEOUT); break; }
         }
     }
 }

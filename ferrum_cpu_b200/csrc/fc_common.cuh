@@ -39,6 +39,15 @@ extern thread_local int64_t g_launches;
 // vector accesses: anything else is refused on the host before a kernel is launched.
 inline bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
 
+// Test hooks (fc_debug_set_wait_budget): the cycle budget of every bounded device-side wait, and a
+// switch that makes the producers of the pipelined kernels withhold their copies, so that a test can
+// make a wait run out without faulting, trapping or hanging anything.
+struct DebugKnobs {
+    long long wait_cycles = 4000000000LL;   // ~2 s at 1.9 GHz
+    int withhold = 0;
+};
+extern DebugKnobs g_debug;
+
 // ---- host helpers shared by the API files (defined in api.cu) ---------------------------
 // Owns device allocations until release().
 struct Arena {

@@ -42,7 +42,6 @@ constexpr int EPI_WARPS = 4, DQ_WARPS = 8;
 constexpr int TMA_WARP = EPI_WARPS + DQ_WARPS, MMA_WARP = TMA_WARP + 1;
 constexpr int THREADS = (MMA_WARP + 1) * 32;
 constexpr int TMEM_COLS = 512;                          // two buffers of two 128-column accumulators
-constexpr long long WAIT_CYCLES = 4000000000LL;
 // bf16 x bf16 -> f32, M = 128, N = 128, both operands K-major
 constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 
@@ -79,11 +78,11 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned long long* b, uint32_t pa
 }
 // Bounded wait. Returns false (after raising the status word) when the budget runs out or
 // another role of this CTA already gave up.
-__device__ bool wait_bar(Bars* bars, unsigned long long* b, uint32_t parity, int* status) {
+__device__ bool wait_bar(Bars* bars, unsigned long long* b, uint32_t parity, int* status, long long budget) {
     const long long t0 = clock64();
     while (!mbar_try_wait(b, parity)) {
         if (bars->abort) return false;
-        if (clock64() - t0 > WAIT_CYCLES) {
+        if (clock64() - t0 > budget) {
             bars->abort = 1;
             atomicExch(status, FC_E_TIMEOUT);
             return false;
@@ -142,6 +141,8 @@ struct TcArgs {
     uint16_t *yhi, *ylo;      // bf16 hi / lo output planes [M][ldy]
     int M, ldy;
     int* status;
+    long long wait_cycles;    // budget of every mbarrier wait
+    int withhold;             // test hook: the TMA producer issues nothing, so the waits on its stages run out
 };
 
 }  // namespace
@@ -180,13 +181,13 @@ gemm_q8_bf16x3_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_c
 
     if (warp == TMA_WARP) {
         // ---------------------------------------------------------------- TMA producer
-        if (lane == 0) {
+        if (lane == 0 && !a.withhold) {
             int it = 0;                                   // k-blocks issued so far, over all tiles
             for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
                 const int m0 = (tile / tiles_n) * BM;
                 for (int kb = 0; kb < nkb; ++kb, ++it) {
                     const int s = it % STAGES;
-                    if (!wait_bar(bars, &bars->empty[s], ((it / STAGES) & 1) ^ 1, a.status)) { tile = n_tiles; break; }
+                    if (!wait_bar(bars, &bars->empty[s], ((it / STAGES) & 1) ^ 1, a.status, a.wait_cycles)) { tile = n_tiles; break; }
                     unsigned char* st = smem + s * STAGE_BYTES;
                     mbar_expect_tx(&bars->full_a[s], 2 * A_BYTES);
                     tma_load_2d(st, &map_hi, kb * BK, m0, &bars->full_a[s]);
@@ -202,14 +203,14 @@ gemm_q8_bf16x3_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_c
             for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++ti) {
                 const int buf = ti & 1;
                 // the epilogue must have drained this accumulator (two tiles ago)
-                ok = wait_bar(bars, &bars->acc_empty[buf], ((ti >> 1) & 1) ^ 1, a.status);
+                ok = wait_bar(bars, &bars->acc_empty[buf], ((ti >> 1) & 1) ^ 1, a.status, a.wait_cycles);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t acc = tmem + (uint32_t)(buf * 2 * BN);     // rows 0..127 here, rows 128..255 at + BN
                 for (int kb = 0; kb < nkb && ok; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t par = (it / STAGES) & 1;
-                    ok = wait_bar(bars, &bars->full_a[s], par, a.status) && wait_bar(bars, &bars->full_b[s], par, a.status);
+                    ok = wait_bar(bars, &bars->full_a[s], par, a.status, a.wait_cycles) && wait_bar(bars, &bars->full_b[s], par, a.status, a.wait_cycles);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t base = s32(smem + s * STAGE_BYTES);
@@ -276,7 +277,7 @@ gemm_q8_bf16x3_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_c
                     split2(scale * qb<0>(ws[2 * c + 1]), scale * qb<1>(ws[2 * c + 1]), &hi[c].z, &lo[c].z);
                     split2(scale * qb<2>(ws[2 * c + 1]), scale * qb<3>(ws[2 * c + 1]), &hi[c].w, &lo[c].w);
                 }
-                if (!wait_bar(bars, &bars->empty[s], ((it / STAGES) & 1) ^ 1, a.status)) { tile = n_tiles; break; }
+                if (!wait_bar(bars, &bars->empty[s], ((it / STAGES) & 1) ^ 1, a.status, a.wait_cycles)) { tile = n_tiles; break; }
                 unsigned char* bhi = smem + s * STAGE_BYTES + 2 * A_BYTES + row * 128;
                 unsigned char* blo = bhi + TILE_BYTES;
 #pragma unroll
@@ -299,7 +300,7 @@ gemm_q8_bf16x3_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_c
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++ti) {
             const int buf = ti & 1;
             const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
-            if (!wait_bar(bars, &bars->acc_full[buf], (ti >> 1) & 1, a.status)) break;
+            if (!wait_bar(bars, &bars->acc_full[buf], (ti >> 1) & 1, a.status, a.wait_cycles)) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
             for (int cc = 0; cc < 2 * (BN / 32); ++cc) {
@@ -500,6 +501,7 @@ int launch_gemm_q8_bf16x3_ex(const QMat& w, const void* x_hi, const void* x_lo, 
     a.qu = w.qu; a.d = w.d; a.N = w.N; a.K = w.K;
     a.bias = bias; a.residual = residual; a.epi = epi;
     a.y = y; a.yhi = (uint16_t*)y_hi; a.ylo = (uint16_t*)y_lo; a.M = M; a.ldy = ldy; a.status = status;
+    a.wait_cycles = g_debug.wait_cycles; a.withhold = g_debug.withhold;
     const int n_tiles = ((w.N + BN - 1) / BN) * ((M + BM - 1) / BM);
     const int grid = n_tiles < sms[dev] ? n_tiles : sms[dev];
     gemm_q8_bf16x3_kernel<<<grid, THREADS, SMEM_BYTES, st>>>(mh, ml, a);

@@ -95,6 +95,8 @@ struct MegaParams {
     // buffer; entry 0 is the step start.
     unsigned long long* trace;
     int trace_cap;
+    long long wait_cycles;     // budget of every bounded wait (mbarrier, grid barrier)
+    int withhold;              // test hook: the producer warps copy nothing
 };
 
 size_t mega_smem_bytes();

@@ -324,6 +324,11 @@ class CudaSlm:
         return _lib.lib().fc_last_batch_ms(self._m)
 
     @property
+    def last_batch_prime_ms(self):
+        """Device time of the primes inside the last decode_batch call."""
+        return _lib.lib().fc_last_batch_prime_ms(self._m)
+
+    @property
     def last_decode_ms(self):
         return _lib.lib().fc_last_decode_ms(self._stream())
 

@@ -28,20 +28,22 @@ def gather_rows(local, n_items, rank, world, device=None):
     import torch
     import torch.distributed as dist
     longest = max(shard_range(n_items, r, world)[1] - shard_range(n_items, r, world)[0] for r in range(world))
-    padded = np.zeros((longest,) + local.shape[1:], dtype=local.dtype)
-    padded[:local.shape[0]] = local
-    t = torch.from_numpy(padded)
-    if device is not None:
-        t = t.to(device)
+    on_gpu = device is not None and torch.device(device).type == "cuda"
+    # one staging buffer in pinned host memory, so that the copies to and from the device are single DMA transfers
+    stage = torch.zeros((longest,) + local.shape[1:], dtype=torch.from_numpy(local[:0]).dtype, pin_memory=on_gpu)
+    stage[:local.shape[0]] = torch.from_numpy(local)
+    t = stage.to(device, non_blocking=True) if device is not None else stage
     parts = [torch.empty_like(t) for _ in range(world)] if rank == 0 else None
     dist.gather(t, parts, dst=0)
     if rank != 0:
         return None
-    out = []
+    full = torch.empty((n_items,) + local.shape[1:], dtype=t.dtype, pin_memory=on_gpu)
     for r, part in enumerate(parts):
         a, b = shard_range(n_items, r, world)
-        out.append(part[:b - a].cpu().numpy())
-    return np.concatenate(out, axis=0)
+        full[a:b].copy_(part[:b - a], non_blocking=True)
+    if on_gpu:
+        torch.cuda.synchronize(device)
+    return full.numpy()
 
 
 def score_sharded(score_fn, ids2d, rank, world, device=None):
@@ -58,12 +60,18 @@ def score_sharded(score_fn, ids2d, rank, world, device=None):
         scores, lp = score_fn(ids2d[a:b])
     else:
         scores, lp = [], np.zeros((0, ids2d.shape[1]), dtype=np.float32)
-    # one record per sequence: [logprob, n_tokens, greedy] as f64, then the f32 rows
+    # one record per sequence in one byte buffer, so that the path has ONE collective: [logprob, n_tokens, greedy]
+    # as three f64, then the row of f32 log-probs
+    T = ids2d.shape[1]
     head = np.array([[s.logprob, float(s.n_tokens), float(s.greedy)] for s in scores], dtype=np.float64).reshape(-1, 3)
-    head_all = gather_rows(head, n, rank, world, device)
-    lp_all = gather_rows(np.asarray(lp, dtype=np.float32), n, rank, world, device)
+    rec = np.zeros((b - a, 24 + 4 * T), dtype=np.uint8)
+    rec[:, :24] = head.view(np.uint8).reshape(-1, 24)
+    rec[:, 24:] = np.ascontiguousarray(lp, dtype=np.float32).view(np.uint8).reshape(-1, 4 * T)
+    full = gather_rows(rec, n, rank, world, device)
     if rank != 0:
         return None
+    head_all = np.ascontiguousarray(full[:, :24]).view(np.float64).reshape(-1, 3)
+    lp_all = np.ascontiguousarray(full[:, 24:]).view(np.float32).reshape(-1, T)
     return head_all[:, 0], head_all[:, 1].astype(np.int64), head_all[:, 2].astype(np.uint8), lp_all
 
 

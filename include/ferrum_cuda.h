@@ -267,12 +267,18 @@ int fc_generate_sampled(fc_stream* s, const int32_t* prompt, int n, int max_new,
                         uint64_t* rng_state, const volatile int32_t* cancel, int32_t* out, int* n_out);
 /* n_streams independent greedy generations on one GPU: prompts [n_streams][prompt_len], out
  * [n_streams][max_new], n_out [n_streams]. Each is token_stream.rs:66-189 with temperature <= 0
- * on its own KV caches. Up to eight streams decode side by side, each on its own CUDA stream
- * with a persistent kernel on a share of the SMs; their prompts are primed as one batched
- * forward. Device time of the feeds: fc_last_batch_ms. */
+ * on its own KV caches (a CachedTransformer per stream, slm/cached.rs:45-64). The streams advance
+ * in lock step, up to 64 at a time: the prompts are primed as one batch of windows, then every
+ * step takes all streams through each Q8_0 matrix at once, so the weights are read once per step
+ * whatever the number of streams. A stream that picks `eos` (-1: none) stops emitting; the others
+ * go on. The extra feed after the last sampled token (token_stream.rs:181-186) is not run. Streams
+ * that would outgrow the context (prompt_len + max_new > ctx: they need the re-prime of
+ * token_stream.rs:162-165) and single streams run one after the other as fc_generate_greedy.
+ * Device time of the whole call: fc_last_batch_ms; of its primes alone: fc_last_batch_prime_ms. */
 int fc_decode_batch(fc_model* m, int n_streams, const int32_t* prompts, int prompt_len, int max_new, int32_t eos,
                     int32_t* out, int* n_out);
 float fc_last_batch_ms(const fc_model* m);
+float fc_last_batch_prime_ms(const fc_model* m);
 
 /* ---- imported Llama / Qwen models (ferrum_core/src/llm.rs, llm_score.rs) ---------- */
 /* The decoder family of llm.rs on the same Q8_0 kernels: RMSNorm (llm.rs:57-64), rotary
@@ -397,6 +403,18 @@ int64_t fc_take_launch_count(void);
 float fc_last_decode_ms(const fc_stream* s);
 /* Device time in ms of the forward passes of the last scoring call on this model. */
 float fc_last_score_ms(const fc_model* m);
+
+/* ---- test hook ------------------------------------------------------------------------ */
+/* Every device-side wait of the pipelined kernels (mbarriers of the tensor-core GEMM and of the
+ * persistent decode kernel, its grid barrier) is bounded by a cycle budget (default 4e9, about two
+ * seconds); when it runs out the kernel raises a status word, drains what it has in flight and
+ * returns, and the call reports FC_E_TIMEOUT (the device-side counterpart of the reference's
+ * request timeout, slm_server/src/model_thread.rs:48-56). This hook sets that budget for launches
+ * made afterwards by this process and, with withhold_producers != 0, makes the producer warps of
+ * those kernels copy nothing, so that a test can watch a wait run out and the handle stay usable.
+ * Nothing faults, traps or waits without a limit. Not for production use: restore
+ * (4000000000, 0) afterwards. */
+int fc_debug_set_wait_budget(long long cycles, int withhold_producers);
 
 #ifdef __cplusplus
 }
