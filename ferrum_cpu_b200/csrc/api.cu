@@ -153,6 +153,8 @@ struct fc_model {
     // tensor path: bf16 hi / lo planes of LayerNorm output, qkv, attention output, GELU output
     uint16_t *nhi = nullptr, *nlo = nullptr, *qkvhi = nullptr, *qkvlo = nullptr;
     uint16_t *atthi = nullptr, *attlo = nullptr, *hidhi = nullptr, *hidlo = nullptr;
+    void* head_stats = nullptr;                // fused head: per (row, 128-column tile) softmax records, 16 B each
+    float* head_tlogit = nullptr;              // ... and the logit of each row's target
     int* tc_status = nullptr;                  // raised by a scoring kernel (tensor-core GEMM, attention, row tail) on a timeout
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     float last_score_ms = 0.0f;
@@ -335,9 +337,11 @@ static int ensure_workspace(fc_model* m, int rows) {
     m->ws_rows = 0;
     const fc_config& c = m->cfg;
     const size_t R = rows, d = c.d_model, F = c.d_ff;
-    // head logits are produced for head_chunk rows at a time (<= 1 GiB of f32)
+    // fp32 mode: head logits are produced for head_chunk rows at a time (<= 1 GiB of f32). On the tensor-core
+    // path the head never writes logits (its epilogue leaves softmax records): one row is kept for predict_next.
     size_t chunk = ((size_t)1 << 28) / (size_t)c.vocab;
     chunk = std::max<size_t>(1, std::min<size_t>(chunk, R));
+    if (tensor_path(m)) chunk = 1;
     Arena& a = m->ws_arena;
     FC_TRY(a.alloc_n(&m->x, R * d));
     FC_TRY(a.alloc_n(&m->n, R * d));
@@ -360,6 +364,8 @@ static int ensure_workspace(fc_model* m, int rows) {
             FC_TRY(a.alloc_n(&m->qkvhi, R * 3 * d)); FC_TRY(a.alloc_n(&m->qkvlo, R * 3 * d));
             FC_TRY(a.alloc_n(&m->atthi, R * d));     FC_TRY(a.alloc_n(&m->attlo, R * d));
             FC_TRY(a.alloc_n(&m->hidhi, R * F));     FC_TRY(a.alloc_n(&m->hidlo, R * F));
+            FC_TRY(a.alloc(&m->head_stats, R * (size_t)((c.vocab + 127) / 128) * 16));
+            FC_TRY(a.alloc_n(&m->head_tlogit, R));
         }
     }
     FC_TRY(a.alloc_n(&m->tc_status, 1));
@@ -427,16 +433,17 @@ static int score_device(fc_model* m, int B, int T) {
     const fc_config& c = m->cfg;
     const int R = B * T, d = c.d_model, ldl = m->head.N_pad;
     FC_TRY(forward_blocks(m, B, T));
-    const bool tc = tensor_path(m);
-    if (tc) FC_TRY(launch_layernorm_planes(m->x, m->lnfg, m->lnfb, R, d, m->nhi, m->nlo, m->st));
-    else FC_TRY(launch_layernorm(m->x, m->lnfg, m->lnfb, R, d, m->n, nullptr, m->st));
+    if (tensor_path(m)) {
+        // the head's epilogue keeps (max, sum of exponentials, first argmax) per row and 128-column tile and the
+        // target's logit: [rows][V] logits never reach memory (scoring.rs:175-181 needs one number per row)
+        FC_TRY(launch_layernorm_planes(m->x, m->lnfg, m->lnfb, R, d, m->nhi, m->nlo, m->st));
+        FC_TRY(launch_gemm_q8_bf16x3_score(m->head, m->nhi, m->nlo, m->targets_d, m->head_stats, m->head_tlogit, R, m->tc_status, m->st));
+        return launch_score_combine(m->head_stats, m->head_tlogit, m->targets_d, R, (c.vocab + 127) / 128, c.vocab, m->lp_d, m->gr_d, m->st);
+    }
+    FC_TRY(launch_layernorm(m->x, m->lnfg, m->lnfb, R, d, m->n, nullptr, m->st));
     for (int r0 = 0; r0 < R; r0 += m->head_chunk) {
         const int rows = std::min(m->head_chunk, R - r0);
-        if (tc)
-            FC_TRY(launch_gemm_q8_bf16x3_ex(m->head, m->nhi + (size_t)r0 * d, m->nlo + (size_t)r0 * d, nullptr, nullptr, EPI_NONE,
-                                            m->logits, nullptr, nullptr, rows, ldl, m->tc_status, m->st));
-        else
-            FC_TRY(gemm(m, m->head, m->n + (size_t)r0 * d, nullptr, nullptr, EPI_NONE, m->logits, rows, ldl));
+        FC_TRY(gemm(m, m->head, m->n + (size_t)r0 * d, nullptr, nullptr, EPI_NONE, m->logits, rows, ldl));
         FC_TRY(launch_score_rows(m->logits, ldl, c.vocab, m->targets_d + r0, rows, m->lp_d + r0, m->gr_d + r0, m->tc_status, m->st));
     }
     return FC_OK;

@@ -84,7 +84,7 @@ struct QMat {
 };
 constexpr int kRowPad = 128;
 
-enum Epilogue : int { EPI_NONE = 0, EPI_GELU = 1, EPI_SWIGLU = 2 };
+enum Epilogue : int { EPI_NONE = 0, EPI_GELU = 1, EPI_SWIGLU = 2, EPI_SCORE = 3 };
 
 // activation.rs:9-12 (tanh GELU), same constants and association as the reference.
 __device__ __forceinline__ float gelu_f(float x) {
@@ -144,6 +144,16 @@ int launch_gemm_q8_bf16x3(const QMat& w, const void* x_hi, const void* x_lo, con
 // The same with a choice of output: f32 rows y, or (y == nullptr) bf16 hi / lo planes for the next GEMM.
 int launch_gemm_q8_bf16x3_ex(const QMat& w, const void* x_hi, const void* x_lo, const float* bias, const float* residual,
                              int epi, float* y, void* y_hi, void* y_lo, int M, int ldy, int* status, cudaStream_t st);
+
+// The LM head fused with the statistics of the softmax tail (math mode FC_MATH_BF16X3): instead of logits the
+// epilogue leaves, per (row, 128-column tile), the tile's largest logit, the sum of exp(logit - that) and the first
+// column that attains it in stats [M][ceil(N / 128)] (16-byte records), and the logit of the row's target
+// (targets[M], -1: none) in tlogit [M]. launch_score_combine folds the records of a row in tile order into
+// ln(max(softmax(row)[target], 1e-12)) (f32 probability, f64 logarithm) and argmax_first(row) == target.
+int launch_gemm_q8_bf16x3_score(const QMat& w, const void* x_hi, const void* x_lo, const int* targets, void* stats, float* tlogit,
+                                int M, int* status, cudaStream_t st);
+int launch_score_combine(const void* stats, const float* tlogit, const int* targets, int M, int n_tiles, int V, double* logprob,
+                         uint8_t* is_greedy, cudaStream_t st);
 
 // api.cu — the matrix and device behind a resident-weight handle.
 const QMat* qweight_matrix(const fc_qweight* w, int* device);

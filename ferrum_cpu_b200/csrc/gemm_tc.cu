@@ -141,6 +141,10 @@ struct TcArgs {
     uint16_t *yhi, *ylo;      // bf16 hi / lo output planes [M][ldy]
     int M, ldy;
     int* status;
+    // EPI_SCORE: per (row, N tile) softmax statistics instead of the product (see launch_gemm_q8_bf16x3_score)
+    const int* targets;
+    float4* stats;
+    float* tlogit;
     long long wait_cycles;    // budget of every mbarrier wait
     int withhold;             // test hook: the TMA producer issues nothing, so the waits on its stages run out
 };
@@ -297,6 +301,10 @@ gemm_q8_bf16x3_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_c
         // rows of 32 columns start on 32-byte boundaries: whole-sector accesses
         const bool vec8_ok = (a.ldy & 7) == 0 && (((uintptr_t)a.y | (uintptr_t)a.residual) & 31) == 0;
         int ti = 0;
+        // EPI_SCORE: running (largest logit, sum of exponentials relative to it, its first column) of this lane's row
+        // over the four 32-column chunks of a tile, and the row's target
+        float run_m = -INFINITY, run_s = 0.0f;
+        int run_i = 0x7fffffff, tgt = -1;
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++ti) {
             const int buf = ti & 1;
             const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
@@ -325,6 +333,41 @@ gemm_q8_bf16x3_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_c
                     if (lane == 0) mbar_arrive(&bars->acc_empty[buf]);
                 }
                 const int nb = n0 + c * 32;
+                if (a.epi == EPI_SCORE) {
+                    if (c == 0) {
+                        run_m = -INFINITY; run_s = 0.0f; run_i = 0x7fffffff;
+                        tgt = m < a.M ? __ldg(a.targets + m) : -1;
+                    }
+                    if (m < a.M && nb < a.N) {
+                        // this chunk's largest logit and its first column (columns past N do not exist)
+                        float cm = -INFINITY;
+                        int ci = 0x7fffffff;
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const float t = __uint_as_float(r[i]);
+                            if (nb + i < a.N && t > cm) { cm = t; ci = nb + i; }
+                        }
+                        if (cm > run_m) {                      // strictly larger: an equal later column never replaces an earlier one
+                            run_s *= expf(run_m - cm);          // run_m == -inf: run_s is 0 and stays 0
+                            run_m = cm;
+                            run_i = ci;
+                        }
+                        float e = 0.0f;
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (nb + i < a.N) e += expf(__uint_as_float(r[i]) - run_m);
+                        run_s += e;
+                        if (tgt >= nb && tgt < nb + 32) {
+                            float tl = 0.0f;
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                if (nb + i == tgt) tl = __uint_as_float(r[i]);
+                            a.tlogit[m] = tl;
+                        }
+                    }
+                    if (c == BN / 32 - 1 && m < a.M)
+                        a.stats[(size_t)m * tiles_n + (tile % tiles_n)] = make_float4(run_m, run_s, __int_as_float(run_i), 0.0f);
+                } else
                 if (m < a.M && nb < a.N) {
                 const bool full = nb + 32 <= a.N;
                 float v[32];
@@ -480,12 +523,7 @@ int encode_plane(CUtensorMap* map, const void* plane, int M, int K) {
 
 // x_hi / x_lo: bf16 planes [M][K] (16-byte aligned). Output: f32 rows y (ldy floats apart), or, when
 // y is null, bf16 planes y_hi / y_lo (N % 32 == 0, ldy % 8 == 0). status: device int, raised on timeout.
-int launch_gemm_q8_bf16x3_ex(const QMat& w, const void* x_hi, const void* x_lo, const float* bias, const float* residual,
-                             int epi, float* y, void* y_hi, void* y_lo, int M, int ldy, int* status, cudaStream_t st) {
-    if (w.K % BK) return fail(FC_E_SHAPE, "the tensor-core GEMM needs K %% 64 == 0 (K = %d)", w.K);
-    if (!y && (!y_hi || !y_lo || (w.N & 31) || (ldy & 7) || residual))
-        return fail(FC_E_SHAPE, "plane output needs N %% 32 == 0, ldy %% 8 == 0 and no residual");
-    if (epi == EPI_SWIGLU && (y || ldy < w.N / 2)) return fail(FC_E_SHAPE, "the SwiGLU epilogue writes planes [M][N / 2]");
+static int launch_tc(const QMat& w, const void* x_hi, const void* x_lo, TcArgs a, int M, cudaStream_t st) {
     static int sms[64] = {};
     int dev = 0;
     FC_CUDA(cudaGetDevice(&dev));
@@ -497,10 +535,7 @@ int launch_gemm_q8_bf16x3_ex(const QMat& w, const void* x_hi, const void* x_lo, 
     CUtensorMap mh, ml;
     FC_TRY(encode_plane(&mh, x_hi, M, w.K));
     FC_TRY(encode_plane(&ml, x_lo, M, w.K));
-    TcArgs a;
-    a.qu = w.qu; a.d = w.d; a.N = w.N; a.K = w.K;
-    a.bias = bias; a.residual = residual; a.epi = epi;
-    a.y = y; a.yhi = (uint16_t*)y_hi; a.ylo = (uint16_t*)y_lo; a.M = M; a.ldy = ldy; a.status = status;
+    a.qu = w.qu; a.d = w.d; a.N = w.N; a.K = w.K; a.M = M;
     a.wait_cycles = g_debug.wait_cycles; a.withhold = g_debug.withhold;
     const int n_tiles = ((w.N + BN - 1) / BN) * ((M + BM - 1) / BM);
     const int grid = n_tiles < sms[dev] ? n_tiles : sms[dev];
@@ -509,9 +544,88 @@ int launch_gemm_q8_bf16x3_ex(const QMat& w, const void* x_hi, const void* x_lo, 
     return FC_OK;
 }
 
+int launch_gemm_q8_bf16x3_ex(const QMat& w, const void* x_hi, const void* x_lo, const float* bias, const float* residual,
+                             int epi, float* y, void* y_hi, void* y_lo, int M, int ldy, int* status, cudaStream_t st) {
+    if (w.K % BK) return fail(FC_E_SHAPE, "the tensor-core GEMM needs K %% 64 == 0 (K = %d)", w.K);
+    if (!y && (!y_hi || !y_lo || (w.N & 31) || (ldy & 7) || residual))
+        return fail(FC_E_SHAPE, "plane output needs N %% 32 == 0, ldy %% 8 == 0 and no residual");
+    if (epi == EPI_SWIGLU && (y || ldy < w.N / 2)) return fail(FC_E_SHAPE, "the SwiGLU epilogue writes planes [M][N / 2]");
+    if (epi == EPI_SCORE) return fail(FC_E_ARG, "the scoring epilogue has its own entry");
+    TcArgs a = {};
+    a.bias = bias; a.residual = residual; a.epi = epi;
+    a.y = y; a.yhi = (uint16_t*)y_hi; a.ylo = (uint16_t*)y_lo; a.ldy = ldy; a.status = status;
+    return launch_tc(w, x_hi, x_lo, a, M, st);
+}
+
+int launch_gemm_q8_bf16x3_score(const QMat& w, const void* x_hi, const void* x_lo, const int* targets, void* stats, float* tlogit,
+                                int M, int* status, cudaStream_t st) {
+    if (w.K % BK) return fail(FC_E_SHAPE, "the tensor-core GEMM needs K %% 64 == 0 (K = %d)", w.K);
+    if (!targets || !stats || !tlogit) return fail(FC_E_ARG, "the scoring epilogue needs targets, stats and tlogit");
+    TcArgs a = {};
+    a.epi = EPI_SCORE; a.targets = targets; a.stats = (float4*)stats; a.tlogit = tlogit; a.status = status;
+    return launch_tc(w, x_hi, x_lo, a, M, st);
+}
+
 int launch_gemm_q8_bf16x3(const QMat& w, const void* x_hi, const void* x_lo, const float* bias, const float* residual,
                           int epi, float* y, int M, int ldy, int* status, cudaStream_t st) {
     return launch_gemm_q8_bf16x3_ex(w, x_hi, x_lo, bias, residual, epi, y, nullptr, nullptr, M, ldy, status, st);
+}
+
+// scoring.rs:175-181 from the per-tile records of the fused head: a warp per row folds the records in tile
+// order (lane l takes tiles l, l + 32, ...; the lanes are then merged pairwise in a fixed pattern), p =
+// exp(target logit - max) / sum in f32, clamp_prob (loss.rs:12-18), ln in f64; greedy = the first column of the
+// largest logit is the target.
+__global__ void __launch_bounds__(256) score_combine_kernel(const float4* __restrict__ stats, const float* __restrict__ tlogit,
+                                                            const int* __restrict__ targets, int M, int n_tiles, int V,
+                                                            double* __restrict__ logprob, uint8_t* __restrict__ is_greedy) {
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= M) return;
+    const int target = targets[row];
+    if (target < 0 || target >= V) {
+        if (lane == 0) { logprob[row] = 0.0; is_greedy[row] = 0; }
+        return;
+    }
+    float m = -INFINITY, s = 0.0f;
+    int idx = 0x7fffffff;
+    auto merge = [&](float m2, float s2, int i2) {
+        const float M2 = fmaxf(m, m2);
+        const float f1 = m > -INFINITY ? expf(m - M2) : 0.0f, f2 = m2 > -INFINITY ? expf(m2 - M2) : 0.0f;
+        s = s * f1 + s2 * f2;
+        idx = m2 > m ? i2 : (m > m2 ? idx : min(idx, i2));
+        m = M2;
+    };
+    const float4* rec = stats + (size_t)row * n_tiles;
+    for (int t = lane; t < n_tiles; t += 32) {
+        const float4 r = rec[t];
+        merge(r.x, r.y, __float_as_int(r.z));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float m2 = __shfl_xor_sync(0xffffffffu, m, o), s2 = __shfl_xor_sync(0xffffffffu, s, o);
+        const int i2 = __shfl_xor_sync(0xffffffffu, idx, o);
+        // both lanes of a pair fold (lower lane, upper lane) in that order, so that they agree bit for bit
+        if (lane & o) {
+            const float m1 = m, s1 = s;
+            const int i1 = idx;
+            m = m2; s = s2; idx = i2;
+            merge(m1, s1, i1);
+        } else {
+            merge(m2, s2, i2);
+        }
+    }
+    if (lane == 0) {
+        float p = expf(tlogit[row] - m) / s;
+        if (p == p) p = fmaxf(p, 1e-12f);
+        logprob[row] = log((double)p);
+        is_greedy[row] = (uint8_t)(idx == target);
+    }
+}
+
+int launch_score_combine(const void* stats, const float* tlogit, const int* targets, int M, int n_tiles, int V, double* logprob,
+                         uint8_t* is_greedy, cudaStream_t st) {
+    score_combine_kernel<<<(M + 7) / 8, 256, 0, st>>>((const float4*)stats, tlogit, targets, M, n_tiles, V, logprob, is_greedy);
+    FC_LAUNCHED();
+    return FC_OK;
 }
 
 }  // namespace fc

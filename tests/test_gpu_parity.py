@@ -368,6 +368,27 @@ def test_scoring_bf16x3_small_matches_golden():
     gm.close()
 
 
+def test_scoring_bf16x3_flags_the_oracles_greedy_tokens():
+    """The fused head keeps the first argmax per row: scoring the oracle's own greedy continuation (prompt + 256
+    tokens of the decode fixture, every oracle margin above 3e-3) must flag every target greedy and reproduce
+    the log-prob each token had when it was picked."""
+    g = np.load(os.path.join(GOLD, "decode_small.npz"))
+    sm = synth.named("small", seed=0, math_mode=fcb.FC_MATH_BF16X3)
+    gm = fcb.CudaSlm(sm.config, sm.weights)
+    ids = np.concatenate([g["prompt"], g["tokens"]]).astype(np.int32)
+    n0 = len(g["prompt"])
+    score, lp, gr = gm.token_logprobs(ids, n0, per_token=True)
+    assert score.n_tokens == len(g["tokens"])
+    assert g["margin"].min() > 1e-3
+    assert gr[n0:].all() and score.greedy
+    assert np.abs(lp[n0:] - g["token_logprob"]).max() < LOGPROB_TOL
+    # a sequence of random ids is (almost) never greedy, and the flags say so
+    rnd = synth.token_ids(5, 300, sm.dims[5])
+    score2, _, gr2 = gm.token_logprobs(rnd, 1, per_token=True)
+    assert not score2.greedy and gr2[1:].sum() <= 2
+    gm.close()
+
+
 def test_scoring_bf16x3_small_spread_of_the_512_sequences():
     """Eight of the 512 sequences of the GPT-2-small scoring workload (first, last, six between), scored
     inside one batch, against oracle fixtures."""
