@@ -58,6 +58,11 @@ class FcScore(C.Structure):
     _fields_ = [("logprob", C.c_double), ("n_tokens", C.c_int64), ("greedy", C.c_int32)]
 
 
+class FcLayerStats(C.Structure):
+    _fields_ = [("min", C.c_float), ("max", C.c_float), ("mean", C.c_float), ("nan_count", C.c_int64), ("inf_count", C.c_int64),
+                ("n_elements", C.c_int64)]
+
+
 # name -> (restype, argtypes); every symbol include/ferrum_cuda.h declares
 SIGNATURES = {
     "fc_last_error": (C.c_char_p, []),
@@ -103,6 +108,10 @@ SIGNATURES = {
     "fc_last_batch_ms": (C.c_float, [C.c_void_p]),
     "fc_last_batch_prime_ms": (C.c_float, [C.c_void_p]),
     "fc_debug_set_wait_budget": (C.c_int, [C.c_longlong, C.c_int]),
+    "fc_score_sequences_multi": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
+    "fc_decode_batch_multi": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int32, C.c_void_p, C.c_void_p]),
+    "fc_model_set_layer_stats": (C.c_int, [C.c_void_p, C.c_int]),
+    "fc_model_read_layer_stats": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int]),
     "fc_llama_create": (C.c_int, [C.POINTER(FcLlamaConfig), C.POINTER(FcLlamaWeights), C.c_int, C.POINTER(C.c_void_p)]),
     "fc_llama_free": (None, [C.c_void_p]),
     "fc_llama_load_gguf": (C.c_int, [C.c_char_p, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_void_p)]),

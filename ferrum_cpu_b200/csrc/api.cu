@@ -4,7 +4,10 @@
 #include <algorithm>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
+#include <string>
+#include <thread>
 #include <vector>
 
 #include "fc_common.cuh"
@@ -23,6 +26,7 @@ void set_error(const char* fmt, ...) {
     vsnprintf(g_err, sizeof g_err, fmt, ap);
     va_end(ap);
 }
+const char* g_err_text() { return g_err; }
 int fail(int code, const char* fmt, ...) {
     va_list ap;
     va_start(ap, fmt);
@@ -167,6 +171,10 @@ struct fc_model {
     // streams created by fc_decode_batch, kept for the next call
     std::vector<fc_stream*> pool;
     float last_batch_ms = 0.0f, last_batch_prime_ms = 0.0f;
+    // per-layer statistics of the last window forward (fc_model_set_layer_stats)
+    int stats_on = 0, stats_n = 0;
+    LayerStatsDev* stats_d = nullptr;   // [n_layer + 2]: embedding, every block, final LayerNorm
+    void* stats_scratch = nullptr;
     cudaEvent_t ev_prime = nullptr;
     BatchCtx batch;
 };
@@ -400,6 +408,13 @@ static int forward_blocks(fc_model* m, int B, int T) {
     cudaStream_t st = m->st;
     FC_CUDA(cudaMemsetAsync(m->err_d, 0, sizeof(int), st));
     FC_TRY(launch_embed_rows(m->tok, m->pos, m->ids_d, R, T, m->x, m->err_d, st));
+    // model.rs:58-68: with the statistics switched on, every layer's output is summarised as it appears
+    m->stats_n = 0;
+    auto layer_stats = [&]() -> int {
+        if (!m->stats_on) return FC_OK;
+        return launch_layer_stats(m->x, nullptr, nullptr, (size_t)R * d, m->stats_scratch, m->stats_d + m->stats_n++, st);
+    };
+    FC_TRY(layer_stats());
     if (tensor_path(m)) {
         // activations between kernels are bf16 hi / lo planes; only the residual stream is f32
         for (int l = 0; l < c.n_layer; ++l) {
@@ -411,6 +426,7 @@ static int forward_blocks(fc_model* m, int B, int T) {
             FC_TRY(launch_layernorm_planes(m->x, L.ln2g, L.ln2b, R, d, m->nhi, m->nlo, st));
             FC_TRY(launch_gemm_q8_bf16x3_ex(L.up, m->nhi, m->nlo, L.up_b, nullptr, EPI_GELU, nullptr, m->hidhi, m->hidlo, R, F, m->tc_status, st));
             FC_TRY(launch_gemm_q8_bf16x3_ex(L.down, m->hidhi, m->hidlo, L.down_b, m->x, EPI_NONE, m->x, nullptr, nullptr, R, d, m->tc_status, st));
+            FC_TRY(layer_stats());
         }
         return FC_OK;
     }
@@ -423,6 +439,7 @@ static int forward_blocks(fc_model* m, int B, int T) {
         FC_TRY(launch_layernorm(m->x, L.ln2g, L.ln2b, R, d, m->n, nullptr, st));
         FC_TRY(gemm(m, L.up, m->n, L.up_b, nullptr, EPI_GELU, m->hid, R, F));
         FC_TRY(gemm(m, L.down, m->hid, L.down_b, m->x, EPI_NONE, m->x, R, d));
+        FC_TRY(layer_stats());
     }
     return FC_OK;
 }
@@ -437,10 +454,12 @@ static int score_device(fc_model* m, int B, int T) {
         // the head's epilogue keeps (max, sum of exponentials, first argmax) per row and 128-column tile and the
         // target's logit: [rows][V] logits never reach memory (scoring.rs:175-181 needs one number per row)
         FC_TRY(launch_layernorm_planes(m->x, m->lnfg, m->lnfb, R, d, m->nhi, m->nlo, m->st));
+        if (m->stats_on) FC_TRY(launch_layer_stats(nullptr, m->nhi, m->nlo, (size_t)R * d, m->stats_scratch, m->stats_d + m->stats_n++, m->st));
         FC_TRY(launch_gemm_q8_bf16x3_score(m->head, m->nhi, m->nlo, m->targets_d, m->head_stats, m->head_tlogit, R, m->tc_status, m->st));
         return launch_score_combine(m->head_stats, m->head_tlogit, m->targets_d, R, (c.vocab + 127) / 128, c.vocab, m->lp_d, m->gr_d, m->st);
     }
     FC_TRY(launch_layernorm(m->x, m->lnfg, m->lnfb, R, d, m->n, nullptr, m->st));
+    if (m->stats_on) FC_TRY(launch_layer_stats(m->n, nullptr, nullptr, (size_t)R * d, m->stats_scratch, m->stats_d + m->stats_n++, m->st));
     for (int r0 = 0; r0 < R; r0 += m->head_chunk) {
         const int rows = std::min(m->head_chunk, R - r0);
         FC_TRY(gemm(m, m->head, m->n + (size_t)r0 * d, nullptr, nullptr, EPI_NONE, m->logits, rows, ldl));
@@ -689,6 +708,10 @@ int fc_model_create(const fc_config* cfg, const fc_weights* w, int device, fc_mo
     if (cudaStreamCreateWithFlags(&m->st, cudaStreamNonBlocking) != cudaSuccess) rc = fail(FC_E_CUDA, "stream creation failed");
     if (rc == FC_OK && (cudaEventCreate(&m->ev0) != cudaSuccess || cudaEventCreate(&m->ev1) != cudaSuccess)) rc = fail(FC_E_CUDA, "event creation failed");
     if (rc == FC_OK) rc = model_build(m, w);
+    if (rc == FC_OK) {
+        const char* tr = getenv("FERRUM_CUDA_TRACE");
+        if (tr && tr[0] == '1') rc = fc_model_set_layer_stats(m, 1);
+    }
     if (rc != FC_OK) { fc_model_free(m); return rc; }
     *out = m;
     return FC_OK;
@@ -719,6 +742,33 @@ int fc_model_config(const fc_model* m, fc_config* out) {
 }
 
 float fc_last_score_ms(const fc_model* m) { return m ? m->last_score_ms : 0.0f; }
+
+int fc_model_set_layer_stats(fc_model* m, int on) {
+    if (!m) return fail(FC_E_ARG, "fc_model_set_layer_stats: null model");
+    FC_CUDA(cudaSetDevice(m->device));
+    if (on && !m->stats_d) {
+        FC_TRY(m->arena.alloc_n(&m->stats_d, (size_t)m->cfg.n_layer + 2));
+        FC_TRY(m->arena.alloc(&m->stats_scratch, layer_stats_scratch_bytes()));
+    }
+    m->stats_on = on != 0;
+    m->stats_n = 0;
+    return FC_OK;
+}
+
+int fc_model_read_layer_stats(fc_model* m, fc_layer_stats* out, int cap) {
+    if (!m || (cap > 0 && !out) || cap < 0) return fail(FC_E_ARG, "fc_model_read_layer_stats: bad argument");
+    if (!m->stats_d || m->stats_n == 0) return 0;
+    FC_CUDA(cudaSetDevice(m->device));
+    FC_CUDA(cudaStreamSynchronize(m->st));
+    std::vector<LayerStatsDev> h(m->stats_n);
+    FC_CUDA(cudaMemcpy(h.data(), m->stats_d, h.size() * sizeof(LayerStatsDev), cudaMemcpyDeviceToHost));
+    const int n = std::min(cap, m->stats_n);
+    for (int i = 0; i < n; ++i) {
+        out[i].min = h[i].min; out[i].max = h[i].max; out[i].mean = h[i].mean;
+        out[i].nan_count = h[i].nan_count; out[i].inf_count = h[i].inf_count; out[i].n_elements = h[i].n;
+    }
+    return n;
+}
 
 // ---------------------------------------------------------------------------- scoring
 // Runs B windows x T rows through the model; double log-probs / flags stay on the device
@@ -1593,6 +1643,60 @@ int fc_decode_batch(fc_model* m, int n_streams, const int32_t* prompts, int prom
 
 float fc_last_batch_ms(const fc_model* m) { return m ? m->last_batch_ms : 0.0f; }
 float fc_last_batch_prime_ms(const fc_model* m) { return m ? m->last_batch_prime_ms : 0.0f; }
+
+}  // extern "C"
+
+// ---------------------------------------------------------------- several devices, one call
+namespace {
+// Runs fn(i, first, last) for every model on a host thread of its own (one handle = one GPU = one host thread
+// at a time, as everywhere in this ABI), item i * n / n_models .. (i + 1) * n / n_models each. The first
+// failure (in model order) is returned with its message; kernel launches are credited to the caller.
+template <class Fn>
+int run_on_models(int n_models, int n_items, Fn fn) {
+    std::vector<int> rc(n_models, FC_OK);
+    std::vector<std::string> msg(n_models);
+    std::vector<int64_t> launches(n_models, 0);
+    std::vector<std::thread> workers;
+    for (int i = 0; i < n_models; ++i) {
+        const int first = (int)((long long)i * n_items / n_models), last = (int)((long long)(i + 1) * n_items / n_models);
+        workers.emplace_back([&, i, first, last] {
+            if (last > first) rc[i] = fn(i, first, last);
+            if (rc[i] != FC_OK) msg[i] = fc::g_err_text();
+            launches[i] = fc::g_launches;
+        });
+    }
+    for (auto& w : workers) w.join();
+    for (int i = 0; i < n_models; ++i) fc::g_launches += launches[i];
+    for (int i = 0; i < n_models; ++i)
+        if (rc[i] != FC_OK) return fail(rc[i], "model %d of %d: %s", i, n_models, msg[i].c_str());
+    return FC_OK;
+}
+}  // namespace
+
+extern "C" {
+
+int fc_score_sequences_multi(fc_model* const* models, int n_models, const int32_t* ids, int n_seq, int seq_len, int batch_windows,
+                             fc_score* scores, float* lp) {
+    if (!models || n_models <= 0 || !ids || !scores) return fail(FC_E_ARG, "fc_score_sequences_multi: null argument");
+    for (int i = 0; i < n_models; ++i)
+        if (!models[i]) return fail(FC_E_ARG, "fc_score_sequences_multi: model %d is null", i);
+    if (n_seq < 0 || seq_len < 0) return fail(FC_E_SHAPE, "fc_score_sequences_multi: negative size");
+    return run_on_models(n_models, n_seq, [&](int i, int a, int b) {
+        return fc_score_sequences(models[i], ids + (size_t)a * seq_len, b - a, seq_len, batch_windows, scores + a,
+                                  lp ? lp + (size_t)a * seq_len : nullptr);
+    });
+}
+
+int fc_decode_batch_multi(fc_model* const* models, int n_models, int n_streams, const int32_t* prompts, int prompt_len, int max_new,
+                          int32_t eos, int32_t* out, int* n_out) {
+    if (!models || n_models <= 0 || !prompts || !n_out || (max_new > 0 && !out)) return fail(FC_E_ARG, "fc_decode_batch_multi: null argument");
+    for (int i = 0; i < n_models; ++i)
+        if (!models[i]) return fail(FC_E_ARG, "fc_decode_batch_multi: model %d is null", i);
+    if (n_streams < 0 || prompt_len <= 0 || max_new < 0) return fail(FC_E_SHAPE, "fc_decode_batch_multi: bad sizes");
+    return run_on_models(n_models, n_streams, [&](int i, int a, int b) {
+        return fc_decode_batch(models[i], b - a, prompts + (size_t)a * prompt_len, prompt_len, max_new, eos, out + (size_t)a * max_new, n_out + a);
+    });
+}
 
 int fc_debug_set_wait_budget(long long cycles, int withhold_producers) {
     if (cycles <= 0) return fail(FC_E_ARG, "fc_debug_set_wait_budget: cycles = %lld", cycles);

@@ -16,6 +16,7 @@ namespace fc {
 void set_error(const char* fmt, ...);
 int cuda_fail(cudaError_t e, const char* what, const char* file, int line);
 int fail(int code, const char* fmt, ...);
+const char* g_err_text();   // the calling thread's last error text
 extern thread_local int64_t g_launches;
 
 #define FC_CUDA(expr)                                                               \
@@ -182,6 +183,15 @@ int launch_softmax_row(const float* logits, int V, float* probs, cudaStream_t st
 // sample.cu — one draw of sample_with_params on the device; see the kernel for the arguments.
 int launch_sample(const float* in, int V, int from_probs, const fc_sampling& prm, const int* recent, int n_recent,
                   unsigned long long* rng_state, int* queue, int queue_cap, StepState* state, int* token_out, cudaStream_t st);
+
+// Per-layer statistics of a window forward (the device-side counterpart of verbose.rs:85-110): one record per layer.
+struct LayerStatsDev {
+    float min, max, mean, pad;
+    long long nan_count, inf_count, n;
+};
+size_t layer_stats_scratch_bytes();
+// x (f32), or (x == nullptr) bf16 hi / lo planes whose sum is the value; n elements; scratch: layer_stats_scratch_bytes().
+int launch_layer_stats(const float* x, const void* hi, const void* lo, size_t n, void* scratch, LayerStatsDev* out, cudaStream_t st);
 
 // attn.cu
 int launch_attn_decode(const float* q, const float* kcache, const float* vcache, int d, int H, int ctx,

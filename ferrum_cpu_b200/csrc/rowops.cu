@@ -2,6 +2,8 @@
 // (softmax statistics + greedy select) and the scoring tail (per-target log-prob).
 #include <cuda_bf16.h>
 
+#include <algorithm>
+
 #include "fc_common.cuh"
 #include "pdl.cuh"
 
@@ -423,6 +425,59 @@ __global__ void __launch_bounds__(1024) softmax_row_kernel(const float* __restri
 }
 int launch_softmax_row(const float* logits, int V, float* probs, cudaStream_t st) {
     softmax_row_kernel<<<1, 1024, 0, st>>>(logits, V, probs);
+    FC_LAUNCHED();
+    return FC_OK;
+}
+
+// ------------------------------------------------------------------------------ layer statistics
+// verbose::stats + verbose::check_nan_inf (verbose.rs:85-110) of one layer output: min, max, f64 sum, and the
+// counts of NaN and Inf. Two stages with a fixed order (per-block partials, then one block), so the figures are
+// the same from run to run. planes_lo != null: the tensor is held as bf16 hi / lo planes, value = hi + lo.
+struct StatPart { float mn, mx; double sum; unsigned long long nan, inf; };
+
+__global__ void __launch_bounds__(256) layer_stats_partial_kernel(const float* __restrict__ x, const __nv_bfloat16* __restrict__ hi,
+                                                                  const __nv_bfloat16* __restrict__ lo, size_t n, StatPart* part) {
+    __shared__ StatPart sh[256];
+    StatPart p{INFINITY, -INFINITY, 0.0, 0ull, 0ull};
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const float v = x ? x[i] : __bfloat162float(hi[i]) + __bfloat162float(lo[i]);
+        if (v != v) { p.nan += 1; continue; }      // as the reference's comparisons, NaN never becomes min or max
+        if (isinf(v)) p.inf += 1;
+        p.mn = fminf(p.mn, v);
+        p.mx = fmaxf(p.mx, v);
+        p.sum += (double)v;
+    }
+    sh[threadIdx.x] = p;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        StatPart t = sh[0];
+        for (int i = 1; i < (int)blockDim.x; ++i) {
+            t.mn = fminf(t.mn, sh[i].mn); t.mx = fmaxf(t.mx, sh[i].mx); t.sum += sh[i].sum; t.nan += sh[i].nan; t.inf += sh[i].inf;
+        }
+        part[blockIdx.x] = t;
+    }
+}
+
+__global__ void layer_stats_final_kernel(const StatPart* part, int n_part, size_t n, LayerStatsDev* out) {
+    StatPart t = part[0];
+    for (int i = 1; i < n_part; ++i) {
+        t.mn = fminf(t.mn, part[i].mn); t.mx = fmaxf(t.mx, part[i].mx); t.sum += part[i].sum; t.nan += part[i].nan; t.inf += part[i].inf;
+    }
+    out->min = n ? t.mn : 0.0f;
+    out->max = n ? t.mx : 0.0f;
+    out->mean = n ? (float)(t.sum / (double)n) : 0.0f;
+    out->nan_count = (long long)t.nan;
+    out->inf_count = (long long)t.inf;
+    out->n = (long long)n;
+}
+
+size_t layer_stats_scratch_bytes() { return 148 * sizeof(StatPart); }
+
+int launch_layer_stats(const float* x, const void* hi, const void* lo, size_t n, void* scratch, LayerStatsDev* out, cudaStream_t st) {
+    const int blocks = (int)std::min<size_t>(148, std::max<size_t>(1, (n + 255) / 256));
+    layer_stats_partial_kernel<<<blocks, 256, 0, st>>>(x, (const __nv_bfloat16*)hi, (const __nv_bfloat16*)lo, n, (StatPart*)scratch);
+    FC_LAUNCHED();
+    layer_stats_final_kernel<<<1, 1, 0, st>>>((const StatPart*)scratch, blocks, n, out);
     FC_LAUNCHED();
     return FC_OK;
 }

@@ -319,6 +319,19 @@ class CudaSlm:
         check(_lib.lib().fc_decode_batch(self._m, n, _ptr(prompts), plen, max_tokens, eos, _ptr(out), _ptr(n_out)))
         return [out[i, :n_out[i]].copy() for i in range(n)]
 
+    def set_layer_stats(self, on=True):
+        """Per-layer min / max / mean / NaN / Inf records of the window forwards (verbose.rs:85-110)."""
+        check(_lib.lib().fc_model_set_layer_stats(self._m, 1 if on else 0))
+
+    def layer_stats(self):
+        """Records of the last forward pass: embedding, every block, final LayerNorm."""
+        n = self.config.n_layer + 2
+        buf = (_lib.FcLayerStats * n)()
+        got = _lib.lib().fc_model_read_layer_stats(self._m, buf, n)
+        if got < 0:
+            check(got)
+        return [dict(min=b.min, max=b.max, mean=b.mean, nan_count=b.nan_count, inf_count=b.inf_count, n_elements=b.n_elements) for b in buf[:got]]
+
     @property
     def last_batch_ms(self):
         return _lib.lib().fc_last_batch_ms(self._m)
@@ -345,3 +358,29 @@ class CudaSlm:
             self.close()
         except Exception:
             pass
+
+
+def _handles(models):
+    arr = (C.c_void_p * len(models))(*[m._m for m in models])
+    return arr
+
+
+def score_sequences_multi(models, ids2d, batch_windows=32):
+    """fc_score_sequences_multi: the sequences split in contiguous blocks over several CudaSlm (one per GPU),
+    each driven by its own host thread inside the call. Returns (scores, lp) as CudaSlm.score_sequences."""
+    ids2d = _ids(ids2d)
+    n_seq, seq_len = ids2d.shape
+    scores = (_lib.FcScore * n_seq)()
+    lp = np.zeros((n_seq, seq_len), dtype=np.float32)
+    check(_lib.lib().fc_score_sequences_multi(_handles(models), len(models), _ptr(ids2d), n_seq, seq_len, batch_windows, scores, _ptr(lp)))
+    return [Score(s.logprob, s.n_tokens, bool(s.greedy)) for s in scores], lp
+
+
+def decode_batch_multi(models, prompts2d, max_tokens, eos=-1):
+    """fc_decode_batch_multi: the streams split in contiguous blocks over several CudaSlm."""
+    prompts = _ids(prompts2d)
+    n, plen = prompts.shape
+    out = np.zeros((n, max(max_tokens, 1)), dtype=np.int32)
+    n_out = np.zeros(n, dtype=np.int32)
+    check(_lib.lib().fc_decode_batch_multi(_handles(models), len(models), n, _ptr(prompts), plen, max_tokens, eos, _ptr(out), _ptr(n_out)))
+    return [out[i, :n_out[i]].copy() for i in range(n)]

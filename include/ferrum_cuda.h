@@ -175,6 +175,21 @@ int fc_gguf_probe(const char* path, const int32_t* row_perm, int n_perm, fc_conf
 void fc_model_free(fc_model* m);
 int fc_model_config(const fc_model* m, fc_config* out);
 
+/* Per-layer statistics of a window forward: the device-side counterpart of the reference's verbose log
+ * (model.rs:58-68 prints verbose::stats and check_nan_inf of every layer's output, verbose.rs:85-110).
+ * When switched on (also by the environment variable FERRUM_CUDA_TRACE=1 at fc_model_create), every
+ * scoring / predict_next forward leaves one record per layer output - the embedding, each transformer
+ * block, the final LayerNorm - of the LAST forward pass the call ran: min, max, mean (f64 sum), and the
+ * counts of NaN and Inf (NaN never enters min / max, as in the reference's comparisons). The head's logits
+ * and the softmax are not materialised on this path and have no record. fc_model_read_layer_stats
+ * copies up to cap records and returns how many (n_layer + 2 at most), or a negative status. */
+typedef struct fc_layer_stats {
+    float min, max, mean;
+    int64_t nan_count, inf_count, n_elements;
+} fc_layer_stats;
+int fc_model_set_layer_stats(fc_model* m, int on);
+int fc_model_read_layer_stats(fc_model* m, fc_layer_stats* out, int cap);
+
 /* ---- scoring: Sequential::forward + the Softmax tail, fused ------------------------ */
 /* B windows of exactly T <= ctx ids each (right-padded by the caller as scoring.rs:184-193
  * pads with id 0). For row t of window b the target is targets[b][t] (or -1: skip).
@@ -279,6 +294,19 @@ int fc_decode_batch(fc_model* m, int n_streams, const int32_t* prompts, int prom
                     int32_t* out, int* n_out);
 float fc_last_batch_ms(const fc_model* m);
 float fc_last_batch_prime_ms(const fc_model* m);
+
+/* ---- several GPUs behind one call ---------------------------------------------------- */
+/* The reference's server owns ONE model on one thread and serialises jobs (slm_server/src/model_thread.rs:
+ * 111-143); scoring sequences and decode streams are independent, so a box of N GPUs serves them N at a
+ * time with the weights replicated. These calls take N model handles (normally fc_model_create with the
+ * same weights on devices 0..N-1), give each a contiguous block of the items - item i goes to model
+ * i * N / n_items - on a host thread of its own, and write every block's results straight into the
+ * caller's arrays: there is nothing to gather and no collective. Results are identical to the single-
+ * model calls on the same items. The first failing model's status and message are returned. */
+int fc_score_sequences_multi(fc_model* const* models, int n_models, const int32_t* ids, int n_seq, int seq_len, int batch_windows,
+                             fc_score* scores, float* lp);
+int fc_decode_batch_multi(fc_model* const* models, int n_models, int n_streams, const int32_t* prompts, int prompt_len, int max_new,
+                          int32_t eos, int32_t* out, int* n_out);
 
 /* ---- imported Llama / Qwen models (ferrum_core/src/llm.rs, llm_score.rs) ---------- */
 /* The decoder family of llm.rs on the same Q8_0 kernels: RMSNorm (llm.rs:57-64), rotary
