@@ -66,3 +66,20 @@ def test_llama_validation_precedes_device_use():
         with pytest.raises(fcb.FerrumCudaError) as e:
             CudaLlama.from_synth(synth.llama_named("llama-tiny"))
         assert e.value.code == _lib.FC_E_CUDA
+
+
+def test_rust_binding_declares_every_symbol_of_the_header():
+    """ferrum_cuda/src/ffi.rs (the binding a Ferrum maintainer adds; it cannot be compiled here) names every
+    function include/ferrum_cuda.h declares, with the same number of arguments."""
+    import re
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    header = re.sub(r"/\*.*?\*/", "", open(os.path.join(root, "include", "ferrum_cuda.h")).read(), flags=re.S)
+    rust = open(os.path.join(root, "ferrum_cuda", "src", "ffi.rs")).read()
+    decls = re.findall(r"\b(fc_[a-z0-9_]+)\s*\(([^;{]*?)\)\s*;", header)
+    assert len(decls) >= 70
+    for name, args in decls:
+        m = re.search(r"pub fn %s\(([^)]*)\)" % name, rust)
+        assert m, f"{name} is missing from ffi.rs"
+        n_c = 0 if args.strip() in ("", "void") else args.count(",") + 1
+        n_rs = 0 if not m.group(1).strip() else m.group(1).count(",") + 1
+        assert n_c == n_rs, f"{name}: {n_c} arguments in the header, {n_rs} in ffi.rs"
