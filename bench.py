@@ -496,6 +496,7 @@ def main():
         wall_s = max_over_ranks(sum(wall) / len(wall))
         fl = score_flops_per_position(smm.dims) * n_seq * SEQ_LEN
         tf = fl / world / (step_ms / 1e3) / 1e12
+        checksum = sum_over_ranks(float(sum(sc.logprob for sc in scores)))   # a collective: every rank takes part
         if rank == 0:
             print(json.dumps({
                 "metric": "Q8_0 GPT-2-medium log-likelihood positions/s", "value": n_seq * SEQ_LEN / (step_ms / 1e3), "unit": "positions/s",
@@ -507,7 +508,7 @@ def main():
                         "d2h_bytes_per_step": (a1 - a0) * SEQ_LEN * 4},
                 "roofline": {"bound": "tensor", "achieved": tf, "peak": tf_peak, "unit": "TFLOP/s", "frac": tf / tf_peak, "traffic": None,
                              "peak_kind": peak_kind, "what": "per GPU: algorithmic FLOP of the rank's sequences / its step time"},
-                "checksum_logprob": sum_over_ranks(float(sum(sc.logprob for sc in scores)))}))
+                "checksum_logprob": checksum}))
         gmm.close()
         if world > 1:
             dist.destroy_process_group()

@@ -198,16 +198,31 @@ __global__ void __launch_bounds__(256) skinny_q8_kernel(const SkArgs a) {
             A[r][0][0] = q2h<0>(w[r].x); A[r][0][2] = q2h<1>(w[r].x); A[r][0][1] = q2h<0>(w[r].z); A[r][0][3] = q2h<1>(w[r].z);
             A[r][1][0] = q2h<0>(w[r].y); A[r][1][2] = q2h<1>(w[r].y); A[r][1][1] = q2h<0>(w[r].w); A[r][1][3] = q2h<1>(w[r].w);
         }
+        // the MMAs of up to four column tiles are issued back to back (independent accumulators), and only then are
+        // their block sums scaled and added: the tensor pipe's latency is covered by the MMAs behind, not waited for
+        constexpr int JB = NT < 4 ? NT : 4;
 #pragma unroll
-        for (int j = 0; j < NT; ++j) {
+        for (int j0 = 0; j0 < NT; j0 += JB) {
+            float d[JB][RG][4];
 #pragma unroll
-            for (int r = 0; r < RG; ++r) {
-                float d[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                mma16816(d, A[r][0][0], A[r][0][1], A[r][0][2], A[r][0][3], xv[j].x, xv[j].y);
-                mma16816(d, A[r][1][0], A[r][1][1], A[r][1][2], A[r][1][3], xv[j].z, xv[j].w);
-                acc[r][j][0] = fmaf(sc[r].x, d[0] + d[1], acc[r][j][0]);
-                acc[r][j][1] = fmaf(sc[r].y, d[2] + d[3], acc[r][j][1]);
-            }
+            for (int jj = 0; jj < JB; ++jj)
+#pragma unroll
+                for (int r = 0; r < RG; ++r) {
+                    d[jj][r][0] = d[jj][r][1] = d[jj][r][2] = d[jj][r][3] = 0.0f;
+                    mma16816(d[jj][r], A[r][0][0], A[r][0][1], A[r][0][2], A[r][0][3], xv[j0 + jj].x, xv[j0 + jj].y);
+                }
+#pragma unroll
+            for (int jj = 0; jj < JB; ++jj)
+#pragma unroll
+                for (int r = 0; r < RG; ++r)
+                    mma16816(d[jj][r], A[r][1][0], A[r][1][1], A[r][1][2], A[r][1][3], xv[j0 + jj].z, xv[j0 + jj].w);
+#pragma unroll
+            for (int jj = 0; jj < JB; ++jj)
+#pragma unroll
+                for (int r = 0; r < RG; ++r) {
+                    acc[r][j0 + jj][0] = fmaf(sc[r].x, d[jj][r][0] + d[jj][r][1], acc[r][j0 + jj][0]);
+                    acc[r][j0 + jj][1] = fmaf(sc[r].y, d[jj][r][2] + d[jj][r][3], acc[r][j0 + jj][1]);
+                }
         }
     }
     cp_async_wait<0>();
