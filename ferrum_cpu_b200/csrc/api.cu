@@ -133,8 +133,12 @@ struct BatchCtx {
     float **kcs = nullptr, **vcs = nullptr;
     int** queues = nullptr;
     fc::StepState** states = nullptr;
-    cudaGraphExec_t graph = nullptr;   // one step, captured for (graph_S, graph_eos, out_cap)
-    int graph_S = 0, graph_eos = 0, graph_cap = 0, graph_nodes = 0;
+    cudaGraphExec_t graph = nullptr;   // one step, captured for (graph_S, graph_eos, out_cap, graph_group)
+    int graph_S = 0, graph_eos = 0, graph_cap = 0, graph_nodes = 0, graph_group = 0;
+    // the step graph runs groups of streams as parallel branches: branch g > 0 is captured on side[g - 1]
+    std::vector<cudaStream_t> side;
+    std::vector<cudaEvent_t> side_done;
+    cudaEvent_t fork = nullptr;
 };
 
 struct fc_model {
@@ -726,6 +730,9 @@ void fc_model_free(fc_model* m) {
     m->arena.release();
     m->ws_arena.release();
     if (m->batch.graph) cudaGraphExecDestroy(m->batch.graph);
+    for (cudaStream_t t : m->batch.side) cudaStreamDestroy(t);
+    for (cudaEvent_t e : m->batch.side_done) cudaEventDestroy(e);
+    if (m->batch.fork) cudaEventDestroy(m->batch.fork);
     m->batch.arena.release();
     m->batch.frag_arena.release();
     if (m->ev0) cudaEventDestroy(m->ev0);
@@ -1404,7 +1411,8 @@ static int batch_ensure(fc_model* m, int S, int out_cap) {
     b.arena.release();
     b.cap = b.out_cap = 0;
     const fc_config& c = m->cfg;
-    const size_t cap = std::max(S, b.cap), oc = std::max(out_cap, b.out_cap), C = kBatchMaxStreams * 2;
+    // two f16 columns per stream; a ragged last group reads (never uses) up to 128 columns past its own
+    const size_t cap = std::max(S, b.cap), oc = std::max(out_cap, b.out_cap), C = kBatchMaxStreams * 2 + 128;
     const size_t d = c.d_model, F = c.d_ff;
     Arena& a = b.arena;
     FC_TRY(a.alloc_n(&b.x, cap * d));
@@ -1423,7 +1431,7 @@ static int batch_ensure(fc_model* m, int S, int out_cap) {
     FC_TRY(a.alloc_n(&b.done, cap));
     FC_TRY(a.alloc_n(&b.n_out, cap));
     FC_TRY(a.alloc_n(&b.out_tok, cap * std::max<size_t>(oc, 1)));
-    FC_TRY(a.alloc_n(&b.pos, 1));
+    FC_TRY(a.alloc_n(&b.pos, kBatchMaxStreams));   // one position word per group of the step graph, all equal
     FC_TRY(a.alloc_n(&b.kcs, cap));
     FC_TRY(a.alloc_n(&b.vcs, cap));
     FC_TRY(a.alloc_n(&b.queues, cap));
@@ -1433,21 +1441,54 @@ static int batch_ensure(fc_model* m, int S, int out_cap) {
     return FC_OK;
 }
 
-// The tail of a step: final LayerNorm (model.rs:51-71 layer list: ..., LayerNorm, Linear, Softmax), head,
-// greedy pick. With `part` the last down-projection is still in partial sums, which the LayerNorm adds.
-static int batch_head_and_pick(fc_model* m, int S, int eos, const float* x, const float* part, int n_part, const float* part_bias,
-                               float* x_other, int advance) {
+// The buffers of one group of streams (streams s0 .. s0 + S of a wave). Every per-stream array is indexed by the
+// stream, so a group is a set of offsets into the wave's buffers, its own position word and the CUDA stream its
+// kernels are issued on.
+struct BatchView {
+    int S;
+    float *x, *x2, *part, *qkv_f, *logits;
+    void *xp, *ap, *hp;
+    int *cur, *done, *n_out, *out_tok, *pos;
+    float **kcs, **vcs;
+    cudaStream_t st;
+};
+
+static BatchView batch_view(fc_model* m, int s0, int S, int group_index, cudaStream_t st) {
     const fc_config& c = m->cfg;
     BatchCtx& b = m->batch;
-    cudaStream_t st = m->st;
-    FC_TRY(launch_ln_rows_f16(x, part, n_part, part_bias, x_other, m->lnfg, m->lnfb, S, c.d_model, b.xp, st));
-    SkinnyOut out;
-    out.y = b.logits; out.ldy = m->head.N_pad;
-    FC_TRY(launch_skinny_q8(b.head, S, b.xp, nullptr, EPI_NONE, out, nullptr, st));
-    return launch_pick_batch(b.logits, m->head.N_pad, c.vocab, S, eos, b.cur, b.done, b.n_out, b.out_tok, b.out_cap, b.pos, advance, st);
+    const size_t d = c.d_model, F = c.d_ff, o = (size_t)s0;
+    BatchView v;
+    v.S = S;
+    v.x = b.x + o * d;
+    v.x2 = b.x2 + o * d;
+    v.part = b.part + (size_t)skinny_max_splits() * o * d;        // [splits][S][d] of the group
+    v.qkv_f = b.qkv_f + o * 3 * d;
+    v.logits = b.logits + o * (size_t)m->head.N_pad;
+    v.xp = (char*)b.xp + 2 * o * d * 2;                           // two f16 columns per stream
+    v.ap = (char*)b.ap + 2 * o * d * 2;
+    v.hp = (char*)b.hp + 2 * o * F * 2;
+    v.cur = b.cur + o; v.done = b.done + o; v.n_out = b.n_out + o;
+    v.out_tok = b.out_tok + o * (size_t)b.out_cap;
+    v.pos = b.pos + group_index;
+    v.kcs = b.kcs + o; v.vcs = b.vcs + o;
+    v.st = st;
+    return v;
 }
 
-// One step for S streams: CachedTransformer::feed (cached.rs:100-125) on every stream's current
+// The tail of a step: final LayerNorm (model.rs:51-71 layer list: ..., LayerNorm, Linear, Softmax), head,
+// greedy pick. With `part` the last down-projection is still in partial sums, which the LayerNorm adds.
+static int batch_head_and_pick(fc_model* m, const BatchView& v, int eos, const float* x, const float* part, int n_part,
+                               const float* part_bias, float* x_other, int advance) {
+    const fc_config& c = m->cfg;
+    BatchCtx& b = m->batch;
+    FC_TRY(launch_ln_rows_f16(x, part, n_part, part_bias, x_other, m->lnfg, m->lnfb, v.S, c.d_model, v.xp, v.st));
+    SkinnyOut out;
+    out.y = v.logits; out.ldy = m->head.N_pad;
+    FC_TRY(launch_skinny_q8(b.head, v.S, v.xp, nullptr, EPI_NONE, out, nullptr, v.st));
+    return launch_pick_batch(v.logits, m->head.N_pad, c.vocab, v.S, eos, v.cur, v.done, v.n_out, v.out_tok, b.out_cap, v.pos, advance, v.st);
+}
+
+// One step for the S streams of a group: CachedTransformer::feed (cached.rs:100-125) on every stream's current
 // token at the shared position, then the greedy pick per stream. Seven kernels per block.
 //  * Up to 16 streams every kernel is a chain of a few memory round trips and nothing else: the
 //    out- and down-projections add bias and residual in their own epilogue (in place).
@@ -1455,20 +1496,20 @@ static int batch_head_and_pick(fc_model* m, int S, int eos, const float* x, cons
 //    alone would leave most SMs idle) and leave partial sums; the LayerNorm kernel that reads the
 //    residual stream next adds them, the bias and the residual in a fixed order
 //    (transformer.rs:272,293).
-static int batch_launch_step(fc_model* m, int S, int eos) {
+static int batch_launch_step(fc_model* m, const BatchView& v, int eos) {
     const fc_config& c = m->cfg;
     BatchCtx& b = m->batch;
-    cudaStream_t st = m->st;
-    const int d = c.d_model, F = c.d_ff;
+    cudaStream_t st = v.st;
+    const int S = v.S, d = c.d_model, F = c.d_ff;
     const size_t layer_stride = (size_t)c.ctx * d;
     const bool split_k = S > 16;
-    FC_TRY(launch_embed_batch(m->tok, m->pos, b.cur, b.pos, S, b.x, st));
-    float *x = b.x, *x_other = b.x2;       // the stream as of the last completed residual add, and the other buffer
+    FC_TRY(launch_embed_batch(m->tok, m->pos, v.cur, v.pos, S, v.x, st));
+    float *x = v.x, *x_other = v.x2;       // the stream as of the last completed residual add, and the other buffer
     const float* part_bias = nullptr;      // bias of the product whose partial sums are pending
     int n_part = 0;
     // LayerNorm of the residual stream, completed first when partial sums are pending
     auto normed = [&](const float* g, const float* be) -> int {
-        FC_TRY(launch_ln_rows_f16(x, n_part > 0 ? b.part : nullptr, n_part, part_bias, x_other, g, be, S, d, b.xp, st));
+        FC_TRY(launch_ln_rows_f16(x, n_part > 0 ? v.part : nullptr, n_part, part_bias, x_other, g, be, S, d, v.xp, st));
         if (n_part > 0) std::swap(x, x_other);   // the completed stream now lives in the other buffer
         n_part = 0;
         part_bias = nullptr;
@@ -1478,7 +1519,7 @@ static int batch_launch_step(fc_model* m, int S, int eos) {
     auto project_add = [&](const QFrag& w, const void* in, const float* bias) -> int {
         SkinnyOut o;
         if (split_k) {
-            o.part = b.part;
+            o.part = v.part;
             FC_TRY(launch_skinny_q8(w, S, in, nullptr, EPI_NONE, o, &n_part, st));
             part_bias = bias;
             return FC_OK;
@@ -1487,31 +1528,72 @@ static int batch_launch_step(fc_model* m, int S, int eos) {
         return launch_skinny_q8(w, S, in, bias, EPI_NONE, o, nullptr, st);
     };
     SkinnyOut oq, oh;
-    oq.y = b.qkv_f; oq.ldy = 3 * d;
-    oh.planes = b.hp; oh.ldp = F;
+    oq.y = v.qkv_f; oq.ldy = 3 * d;
+    oh.planes = v.hp; oh.ldp = F;
     for (int l = 0; l < c.n_layer; ++l) {
         const LayerDev& L = m->layers[l];
         FC_TRY(normed(L.ln1g, L.ln1b));
-        FC_TRY(launch_skinny_q8(b.qkv[l], S, b.xp, L.qkv_b, EPI_NONE, oq, nullptr, st));
-        FC_TRY(launch_attn_decode_batch(b.qkv_f, b.kcs, b.vcs, l * layer_stride, d, c.n_head, c.ctx, b.pos, S, b.ap, st));
-        FC_TRY(project_add(b.out[l], b.ap, L.out_b));
+        FC_TRY(launch_skinny_q8(b.qkv[l], S, v.xp, L.qkv_b, EPI_NONE, oq, nullptr, st));
+        FC_TRY(launch_attn_decode_batch(v.qkv_f, v.kcs, v.vcs, l * layer_stride, d, c.n_head, c.ctx, v.pos, S, v.ap, st));
+        FC_TRY(project_add(b.out[l], v.ap, L.out_b));
         FC_TRY(normed(L.ln2g, L.ln2b));
-        FC_TRY(launch_skinny_q8(b.up[l], S, b.xp, L.up_b, EPI_GELU, oh, nullptr, st));
-        FC_TRY(project_add(b.down[l], b.hp, L.down_b));
+        FC_TRY(launch_skinny_q8(b.up[l], S, v.xp, L.up_b, EPI_GELU, oh, nullptr, st));
+        FC_TRY(project_add(b.down[l], v.hp, L.down_b));
     }
-    return batch_head_and_pick(m, S, eos, x, b.part, n_part, part_bias, x_other, 1);
+    return batch_head_and_pick(m, v, eos, x, v.part, n_part, part_bias, x_other, 1);
+}
+
+// Streams per group of the step graph. Every step kernel is a chain of memory round trips that leaves most of the
+// GPU idle, and its duration hardly falls with fewer streams, so groups run as parallel branches of the graph and
+// their chains overlap. The weights are then read once per group, the re-reads coming from L2 (a block's matrices
+// are a few MB and the branches stay within a block or two of each other). Measured on the 24-block, 1024-wide
+// shape with 64 streams: one group 1.63 ms per step, groups of 32 1.47 ms, of 16 1.37 ms, of 8 1.55 ms.
+// FERRUM_LOCKSTEP_GROUP=<n> overrides the choice (a tuning aid; results do not depend on it beyond the
+// summation order of the kernels that n selects).
+static int batch_group_size(int S) {
+    if (const char* e = getenv("FERRUM_LOCKSTEP_GROUP")) {
+        const int forced = atoi(e);
+        if (forced > 0) return std::min(forced, kBatchMaxStreams);
+    }
+    return S > 16 ? 16 : S;
+}
+
+// All groups of one step on the capture: group 0 on the model's stream, the others on side streams forked from
+// it and joined back.
+static int batch_launch_groups(fc_model* m, int S, int eos, int group) {
+    BatchCtx& b = m->batch;
+    const int n_groups = (S + group - 1) / group;
+    while ((int)b.side.size() < n_groups - 1) {
+        cudaStream_t s = nullptr;
+        cudaEvent_t e = nullptr;
+        FC_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+        b.side.push_back(s);
+        FC_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        b.side_done.push_back(e);
+    }
+    if (!b.fork) FC_CUDA(cudaEventCreateWithFlags(&b.fork, cudaEventDisableTiming));
+    if (n_groups > 1) FC_CUDA(cudaEventRecord(b.fork, m->st));
+    for (int g = 1; g < n_groups; ++g) {
+        FC_CUDA(cudaStreamWaitEvent(b.side[g - 1], b.fork, 0));
+        FC_TRY(batch_launch_step(m, batch_view(m, g * group, std::min(group, S - g * group), g, b.side[g - 1]), eos));
+        FC_CUDA(cudaEventRecord(b.side_done[g - 1], b.side[g - 1]));
+    }
+    FC_TRY(batch_launch_step(m, batch_view(m, 0, std::min(group, S), 0, m->st), eos));
+    for (int g = 1; g < n_groups; ++g) FC_CUDA(cudaStreamWaitEvent(m->st, b.side_done[g - 1], 0));
+    return FC_OK;
 }
 
 // The step is launch-bound (7 small kernels per block): it is captured once into a CUDA graph and
 // replayed; position and tokens are read from device memory, so no node changes between steps.
 static int batch_run_step(fc_model* m, int S, int eos) {
     BatchCtx& b = m->batch;
-    if (!b.graph || b.graph_S != S || b.graph_eos != eos || b.graph_cap != b.out_cap) {
+    const int group = batch_group_size(S);
+    if (!b.graph || b.graph_S != S || b.graph_eos != eos || b.graph_cap != b.out_cap || b.graph_group != group) {
         if (b.graph) { cudaGraphExecDestroy(b.graph); b.graph = nullptr; }
         cudaGraph_t g = nullptr;
         const int64_t before = g_launches;
         FC_CUDA(cudaStreamBeginCapture(m->st, cudaStreamCaptureModeThreadLocal));
-        const int rc = batch_launch_step(m, S, eos);
+        const int rc = batch_launch_groups(m, S, eos, group);
         const cudaError_t e = cudaStreamEndCapture(m->st, &g);
         b.graph_nodes = (int)(g_launches - before);
         g_launches = before;
@@ -1520,7 +1602,7 @@ static int batch_run_step(fc_model* m, int S, int eos) {
         const cudaError_t ei = cudaGraphInstantiate(&b.graph, g, 0);
         cudaGraphDestroy(g);
         FC_CUDA(ei);
-        b.graph_S = S; b.graph_eos = eos; b.graph_cap = b.out_cap;
+        b.graph_S = S; b.graph_eos = eos; b.graph_cap = b.out_cap; b.graph_group = group;
     }
     FC_CUDA(cudaGraphLaunch(b.graph, m->st));
     g_launches += b.graph_nodes;
@@ -1597,7 +1679,7 @@ int fc_decode_batch(fc_model* m, int n_streams, const int32_t* prompts, int prom
             const int d = c.d_model;
             FC_TRY(launch_gather_last_rows(m->x, S, prompt_len, d, b.x, st));
             FC_TRY(launch_batch_init(S, prompt_len, b.done, b.n_out, b.cur, b.pos, st));
-            FC_TRY(batch_head_and_pick(m, S, eos, b.x, nullptr, 0, nullptr, nullptr, 0));
+            FC_TRY(batch_head_and_pick(m, batch_view(m, 0, S, 0, st), eos, b.x, nullptr, 0, nullptr, nullptr, 0));
         } else {
             // prompts too short for a window forward: token by token per stream; the last step selects token 1
             for (int i = 0; i < S; ++i) FC_TRY(run_steps(wv[i], prompt_len, STEP_NOHEAD, STEP_SELECT));

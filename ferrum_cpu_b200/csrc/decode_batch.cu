@@ -546,7 +546,7 @@ __global__ void __launch_bounds__(1024) pick_batch_kernel(const float* __restric
 __global__ void gather_first_kernel(int* const* __restrict__ queues, StepState* const* __restrict__ states, int prompt_len, int S,
                                     int* cur, int* done, int* n_out, int* out, int out_cap, int* pos) {
     const int s = blockIdx.x * blockDim.x + threadIdx.x;
-    if (s == 0) *pos = prompt_len;
+    if (s < kBatchMaxStreams) pos[s] = prompt_len;       // one position word per group of the step
     if (s >= S) return;
     const StepState* st = states[s];
     const bool fin = st->done != 0 || st->tail <= prompt_len;
@@ -593,7 +593,7 @@ __global__ void gather_last_rows_kernel(const float* __restrict__ x, int n, int 
 
 __global__ void batch_init_kernel(int S, int pos0, int* done, int* n_out, int* cur, int* pos) {
     const int s = blockIdx.x * blockDim.x + threadIdx.x;
-    if (s == 0) *pos = pos0;
+    if (s < kBatchMaxStreams) pos[s] = pos0;             // one position word per group of the step
     if (s < S) { done[s] = 0; n_out[s] = 0; cur[s] = 0; }
 }
 

@@ -174,6 +174,24 @@ def test_decode_batch_lock_step_matches_oracle(tiny):
         assert np.array_equal(cut[i], wants[i][:n]), f"stream {i}"
 
 
+def test_decode_batch_groups_of_streams_match_oracle(tiny, monkeypatch):
+    """The step graph runs groups of streams as parallel branches. 40 streams under the default grouping (16, 16, 8),
+    as one group (the K-split kernels) and as groups of 8 (a ragged last group of MMA columns is never used) all give
+    the oracle's tokens."""
+    sm, om, gm = tiny
+    V = sm.dims[5]
+    prompts = np.stack([synth.token_ids(300 + i, 7, V) for i in range(40)])
+    wants = [om.generate_greedy(prompts[i], 12) for i in range(40)]
+    for group in (None, "64", "8", "12"):
+        if group is None:
+            monkeypatch.delenv("FERRUM_LOCKSTEP_GROUP", raising=False)
+        else:
+            monkeypatch.setenv("FERRUM_LOCKSTEP_GROUP", group)
+        outs = gm.decode_batch(prompts, 12)
+        for i in range(40):
+            check_greedy(outs[i], wants[i][0], wants[i][1])
+
+
 def test_phase_timeline_is_recorded_per_cta(tiny):
     """fc_stream_set_trace: every CTA of the persistent kernel leaves a rising series of timer
     values for the last token of a launch (entry 0 = token start, 15 per block, then the head)."""
