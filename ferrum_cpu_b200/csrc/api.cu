@@ -1451,9 +1451,10 @@ struct BatchView {
     int *cur, *done, *n_out, *out_tok, *pos;
     float **kcs, **vcs;
     cudaStream_t st;
+    int max_warps;                     // per CTA of the products: fewer when several groups run side by side
 };
 
-static BatchView batch_view(fc_model* m, int s0, int S, int group_index, cudaStream_t st) {
+static BatchView batch_view(fc_model* m, int s0, int S, int group_index, cudaStream_t st, int n_groups = 1) {
     const fc_config& c = m->cfg;
     BatchCtx& b = m->batch;
     const size_t d = c.d_model, F = c.d_ff, o = (size_t)s0;
@@ -1472,6 +1473,7 @@ static BatchView batch_view(fc_model* m, int s0, int S, int group_index, cudaStr
     v.pos = b.pos + group_index;
     v.kcs = b.kcs + o; v.vcs = b.vcs + o;
     v.st = st;
+    v.max_warps = n_groups > 1 ? 8 : 16;
     return v;
 }
 
@@ -1483,6 +1485,7 @@ static int batch_head_and_pick(fc_model* m, const BatchView& v, int eos, const f
     BatchCtx& b = m->batch;
     FC_TRY(launch_ln_rows_f16(x, part, n_part, part_bias, x_other, m->lnfg, m->lnfb, v.S, c.d_model, v.xp, v.st));
     SkinnyOut out;
+    out.max_warps = v.max_warps;
     out.y = v.logits; out.ldy = m->head.N_pad;
     FC_TRY(launch_skinny_q8(b.head, v.S, v.xp, nullptr, EPI_NONE, out, nullptr, v.st));
     return launch_pick_batch(v.logits, m->head.N_pad, c.vocab, v.S, eos, v.cur, v.done, v.n_out, v.out_tok, b.out_cap, v.pos, advance, v.st);
@@ -1518,6 +1521,7 @@ static int batch_launch_step(fc_model* m, const BatchView& v, int eos) {
     // x <- x + (W in + bias): as partial sums for the next LayerNorm, or finished in the epilogue
     auto project_add = [&](const QFrag& w, const void* in, const float* bias) -> int {
         SkinnyOut o;
+        o.max_warps = v.max_warps;
         if (split_k) {
             o.part = v.part;
             FC_TRY(launch_skinny_q8(w, S, in, nullptr, EPI_NONE, o, &n_part, st));
@@ -1528,6 +1532,7 @@ static int batch_launch_step(fc_model* m, const BatchView& v, int eos) {
         return launch_skinny_q8(w, S, in, bias, EPI_NONE, o, nullptr, st);
     };
     SkinnyOut oq, oh;
+    oq.max_warps = oh.max_warps = v.max_warps;
     oq.y = v.qkv_f; oq.ldy = 3 * d;
     oh.planes = v.hp; oh.ldp = F;
     for (int l = 0; l < c.n_layer; ++l) {
@@ -1575,10 +1580,10 @@ static int batch_launch_groups(fc_model* m, int S, int eos, int group) {
     if (n_groups > 1) FC_CUDA(cudaEventRecord(b.fork, m->st));
     for (int g = 1; g < n_groups; ++g) {
         FC_CUDA(cudaStreamWaitEvent(b.side[g - 1], b.fork, 0));
-        FC_TRY(batch_launch_step(m, batch_view(m, g * group, std::min(group, S - g * group), g, b.side[g - 1]), eos));
+        FC_TRY(batch_launch_step(m, batch_view(m, g * group, std::min(group, S - g * group), g, b.side[g - 1], n_groups), eos));
         FC_CUDA(cudaEventRecord(b.side_done[g - 1], b.side[g - 1]));
     }
-    FC_TRY(batch_launch_step(m, batch_view(m, 0, std::min(group, S), 0, m->st), eos));
+    FC_TRY(batch_launch_step(m, batch_view(m, 0, std::min(group, S), 0, m->st, n_groups), eos));
     for (int g = 1; g < n_groups; ++g) FC_CUDA(cudaStreamWaitEvent(m->st, b.side_done[g - 1], 0));
     return FC_OK;
 }

@@ -132,7 +132,7 @@ constexpr int SK_MAX_SPLITS = 8;
 // launch): the weight stream of one product overlaps the tail of the kernel before it, and HBM sees
 // RG * 544 B * depth per warp in flight instead of one block at a time.
 template <int NT, int RG>
-__global__ void __launch_bounds__(256) skinny_q8_kernel(const SkArgs a) {
+__global__ void __launch_bounds__(512) skinny_q8_kernel(const SkArgs a) {
     extern __shared__ __align__(16) unsigned char sk_smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int nwarps = blockDim.x >> 5;
@@ -165,6 +165,19 @@ __global__ void __launch_bounds__(256) skinny_q8_kernel(const SkArgs a) {
     pdl_wait_prior();                                  // the activations come from the kernel ahead
     pdl_launch_next();                                 // the kernel behind may start fetching its own weights
 
+    // bias and residual of the output this thread finishes first are requested now, so that they have arrived when
+    // the K loop ends
+    constexpr int ROWS = 16 * RG;
+    const int n_base = blockIdx.x * ROWS, s_base = col0 >> 1;
+    const int s_here = min(4 * NT, a.S - s_base);
+    float bias0 = 0.0f, res0 = 0.0f;
+    {
+        const int sl = threadIdx.x / ROWS, n = n_base + (threadIdx.x - sl * ROWS);
+        if (sl < s_here && n < a.N && !a.part_out) {
+            if (a.bias) bias0 = __ldg(a.bias + n);
+            if (a.residual) res0 = a.residual[(size_t)(s_base + sl) * a.ldy + n];
+        }
+    }
     float acc[RG][NT][2];
 #pragma unroll
     for (int r = 0; r < RG; ++r)
@@ -228,7 +241,6 @@ __global__ void __launch_bounds__(256) skinny_q8_kernel(const SkArgs a) {
     cp_async_wait<0>();
     // partial sums of this warp's K slice: red[warp][stream][row]
     float* mine = red + (size_t)warp * (4 * NT) * RED_LD;
-    constexpr int ROWS = 16 * RG;
     static_assert(ROWS <= RED_LD, "reduction rows");
 #pragma unroll
     for (int j = 0; j < NT; ++j) {
@@ -237,8 +249,6 @@ __global__ void __launch_bounds__(256) skinny_q8_kernel(const SkArgs a) {
         for (int r = 0; r < RG; ++r) { col[16 * r + g] = acc[r][j][0]; col[16 * r + g + 8] = acc[r][j][1]; }
     }
     __syncthreads();
-    const int n_base = blockIdx.x * ROWS, s_base = col0 >> 1;
-    const int s_here = min(4 * NT, a.S - s_base);
     for (int idx = threadIdx.x; idx < s_here * ROWS; idx += blockDim.x) {
         const int sl = idx / ROWS, r = idx - sl * ROWS, n = n_base + r, s = s_base + sl;
         if (n >= a.N) continue;
@@ -248,9 +258,10 @@ __global__ void __launch_bounds__(256) skinny_q8_kernel(const SkArgs a) {
             a.part_out[((size_t)blockIdx.z * a.S + s) * a.N + n] = v;
             continue;
         }
-        if (a.bias) v += a.bias[n];
+        const bool first = idx == (int)threadIdx.x;
+        if (a.bias) v += first ? bias0 : a.bias[n];
         if (a.epi == EPI_GELU) v = gelu_f(v);
-        if (a.residual) v = a.residual[(size_t)s * a.ldy + n] + v;
+        if (a.residual) v = (first ? res0 : a.residual[(size_t)s * a.ldy + n]) + v;
         if (a.y) a.y[(size_t)s * a.ldy + n] = v;
         if (a.yp) {
             const __half h = __float2half_rn(v);
@@ -330,6 +341,16 @@ __global__ void ln_rows_f16_kernel(const float* __restrict__ x, const float* __r
                                    const float* __restrict__ part_bias, float* __restrict__ x_out, const float* __restrict__ g,
                                    const float* __restrict__ b, int d, __half* __restrict__ xp) {
     __shared__ float red[33];
+    // gain, bias and the pending product's bias do not depend on the kernel ahead: they are on their way while this
+    // kernel waits for it
+    float gv[PER], bv[PER], pbv[PER];
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        gv[i] = c < d ? __ldg(g + c) : 0.0f;
+        bv[i] = c < d ? __ldg(b + c) : 0.0f;
+        pbv[i] = (c < d && n_part > 0 && part_bias) ? __ldg(part_bias + c) : 0.0f;
+    }
     pdl_wait_prior();
     pdl_launch_next();
     const int s = blockIdx.x;
@@ -350,7 +371,7 @@ __global__ void ln_rows_f16_kernel(const float* __restrict__ x, const float* __r
                 float pv = pp[0];
 #pragma unroll
                 for (int p = 1; p < SK_MAX_SPLITS; ++p) pv = p < n_part ? pv + pp[p] : pv;
-                if (part_bias) pv += part_bias[c];
+                if (part_bias) pv += pbv[i];
                 xv = xv + pv;
                 if (x_out) x_out[(size_t)s * d + c] = xv;
             }
@@ -371,7 +392,7 @@ __global__ void ln_rows_f16_kernel(const float* __restrict__ x, const float* __r
     for (int i = 0; i < PER; ++i) {
         const int c = threadIdx.x + i * blockDim.x;
         if (c < d) {
-            const float y = ((v[i] - mean) / sd) * g[c] + b[c];
+            const float y = ((v[i] - mean) / sd) * gv[i] + bv[i];
             const __half h = __float2half_rn(y);
             xp[(size_t)(2 * s) * d + c] = h;
             xp[(size_t)(2 * s + 1) * d + c] = __float2half_rn(y - __half2float(h));
@@ -652,7 +673,9 @@ int launch_skinny_q8(const QFrag& w, int S, const void* xp, const float* bias, i
     if (splits_used) *splits_used = splits;
     const int kb_cta = (nkb + splits - 1) / splits;
     // warps split a CTA's K range: at least two 32-wide blocks each, at most 8 warps
-    const int warps = kb_cta >= 16 ? 8 : kb_cta >= 8 ? 4 : kb_cta >= 4 ? 2 : 1;
+    // A warp's K slice is a chain of dependent steps (block landed -> fragments -> MMAs -> scaled add), about 0.3 us
+    // per k-block whatever the width: the slices are kept to two or three blocks by using up to 16 warps.
+    const int warps = std::min(out.max_warps, kb_cta >= 32 ? 16 : kb_cta >= 16 ? 8 : kb_cta >= 8 ? 4 : kb_cta >= 4 ? 2 : 1);
     a.depth = std::max(1, std::min(SK_DEPTH, (kb_cta + warps - 1) / warps));
     if (cols <= 32) {
         // few streams: bound by the weight stream; 32 rows per CTA only when that still leaves every SM several CTAs

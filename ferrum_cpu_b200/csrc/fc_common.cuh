@@ -238,6 +238,7 @@ struct SkinnyOut {
     void* planes = nullptr;
     int ldp = 0;
     float* part = nullptr;
+    int max_warps = 16;   // warps per CTA; 8 when several chains of step kernels share the GPU (two or three CTAs per SM then)
 };
 int skinny_max_splits();
 int launch_skinny_q8(const QFrag& w, int S, const void* xp, const float* bias, int epi, const SkinnyOut& out, int* splits_used,
