@@ -184,25 +184,19 @@ __global__ void __launch_bounds__(512) skinny_q8_kernel(const SkArgs a) {
 #pragma unroll
         for (int j = 0; j < NT; ++j) acc[r][j][0] = acc[r][j][1] = 0.0f;
     const uint4* xb = a.xp + (size_t)(col0 + g) * k8 + t;
-    int slot_r = 0;
-    for (int kb = kb0; kb < kb1; ++kb) {
-        uint4 xv[NT];
+    auto fetch_x = [&](uint4 (&xv)[NT], int kb) {
 #pragma unroll
         for (int j = 0; j < NT; ++j) xv[j] = __ldg(xb + (size_t)(8 * j) * k8 + 4 * kb);
-        cp_async_wait_n(depth - 1);                    // block kb has landed: depth + i groups committed, the first i + 1 complete
-        __syncwarp();
-        const unsigned char* slot = ring + (size_t)slot_r * SLOT;
-        slot_r = slot_r + 1 == depth ? 0 : slot_r + 1;
-        uint4 w[RG];
-        float2 sc[RG];
+    };
+    auto fetch_w = [&](uint4 (&w)[RG], float2 (&sc)[RG], const unsigned char* slot) {
 #pragma unroll
         for (int r = 0; r < RG; ++r) {
             w[r] = *(const uint4*)(slot + r * 544 + lane * 16);
             sc[r] = __half22float2(*(const __half2*)(slot + r * 544 + 512 + g * 4));
         }
-        __syncwarp();                                  // every lane has read the slot before it is refilled
-        if (kb + depth < kb1) request(kb + depth);
-        cp_async_commit();
+    };
+    // one k-block: 32 k of RG * 16 rows against 4 * NT streams
+    auto block_math = [&](const uint4 (&xv)[NT], const uint4 (&w)[RG], const float2 (&sc)[RG]) {
         // lane (g, t) holds k = 8t .. 8t+7 of rows g (x, y) and g + 8 (z, w): k-step 0 takes the
         // first four, k-step 1 the last four, on both operands alike
         uint32_t A[RG][2][4];
@@ -236,6 +230,37 @@ __global__ void __launch_bounds__(512) skinny_q8_kernel(const SkArgs a) {
                     acc[r][j0 + jj][0] = fmaf(sc[r].x, d[jj][r][0] + d[jj][r][1], acc[r][j0 + jj][0]);
                     acc[r][j0 + jj][1] = fmaf(sc[r].y, d[jj][r][2] + d[jj][r][3], acc[r][j0 + jj][1]);
                 }
+        }
+    };
+    if (kb1 - kb0 <= depth) {
+        // The whole K slice of the warp is in its ring (every shape of the models here): one wait for all of it, and
+        // then a loop without waits or refills, which the compiler is free to overlap across k-blocks. (A wait on
+        // the copy groups also holds back until the loads issued before it have returned, activation fragments
+        // included: per k-block it costs an L2 round trip.)
+        cp_async_wait<0>();
+        __syncwarp();
+#pragma unroll 2
+        for (int i = 0; i < kb1 - kb0; ++i) {
+            uint4 xv[NT], w[RG];
+            float2 sc[RG];
+            fetch_x(xv, kb0 + i);
+            fetch_w(w, sc, ring + (size_t)i * SLOT);
+            block_math(xv, w, sc);
+        }
+    } else {
+        int slot_r = 0;
+        for (int kb = kb0; kb < kb1; ++kb) {
+            uint4 xv[NT], w[RG];
+            float2 sc[RG];
+            fetch_x(xv, kb);
+            cp_async_wait_n(depth - 1);                // block kb has landed: depth + i groups committed, the first i + 1 complete
+            __syncwarp();
+            fetch_w(w, sc, ring + (size_t)slot_r * SLOT);
+            slot_r = slot_r + 1 == depth ? 0 : slot_r + 1;
+            __syncwarp();                              // every lane has read the slot before it is refilled
+            if (kb + depth < kb1) request(kb + depth);
+            cp_async_commit();
+            block_math(xv, w, sc);
         }
     }
     cp_async_wait<0>();
