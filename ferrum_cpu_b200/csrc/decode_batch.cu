@@ -433,44 +433,54 @@ __global__ void __launch_bounds__(256) attn_decode_batch_kernel(const float* __r
                                                                 float* const* __restrict__ vcs, size_t layer_off, int d, int hd,
                                                                 const int* __restrict__ pos, __half* __restrict__ ap) {
     extern __shared__ float sm[];   // scores[len] | red[64] | part[16][64]
-    pdl_wait_prior();
-    pdl_launch_next();
+    // The position and the cached rows of earlier steps were written at least two kernels ago (a kernel is only
+    // launched once the one ahead of it has passed its own dependency wait), so they can be touched before this
+    // kernel's wait: the head's slices of the cached k and v rows are asked into L2 while the QKV product runs.
     const int h = blockIdx.x, s = blockIdx.y, hs = h * hd;
     const int p = *pos, len = p + 1;
+    float* kc = kcs[s] + layer_off;
+    float* vc = vcs[s] + layer_off;
+    for (int i = threadIdx.x; i < 4 * p; i += blockDim.x) {   // 128 B lines: two per row slice of up to 64 floats, k and v
+        const int j = i >> 2, part_i = i & 3;
+        const float* base = (part_i & 2 ? vc : kc) + (size_t)j * d + hs + (part_i & 1) * 32;
+        if ((part_i & 1) * 32 < hd) asm volatile("prefetch.global.L2 [%0];" ::"l"(base));
+    }
+    pdl_wait_prior();
+    pdl_launch_next();
     float* sc = sm;
     float* red = sm + ((len + 3) & ~3);
     float* part = red + 64;
-    float* kc = kcs[s] + layer_off;
-    float* vc = vcs[s] + layer_off;
     const float* row = qkv + (size_t)s * 3 * d;
+    // the step's own k and v rows go to the cache; this kernel reads them from the QKV product's output instead
     if (threadIdx.x < hd) {
         kc[(size_t)p * d + hs + threadIdx.x] = row[d + hs + threadIdx.x];
         vc[(size_t)p * d + hs + threadIdx.x] = row[2 * d + hs + threadIdx.x];
     }
-    __syncthreads();
     const int hw = threadIdx.x >> 4, li = threadIdx.x & 15;
     const bool has = 4 * li < hd;
     const float4 z4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     const float4 q = has ? *(const float4*)(row + hs + 4 * li) : z4;
     const float scale = 1.0f / sqrtf((float)hd);
     float mx = -INFINITY;
-    // a half warp per cached row: lane li owns dimensions 4 li .. 4 li + 3. The two halves of a warp
-    // may run different numbers of rows, so the shuffles name only the lanes of their own half.
+    // a half warp per cached row: lane li owns dimensions 4 li .. 4 li + 3, eight rows in flight. The two halves of
+    // a warp may run different numbers of rows, so the shuffles name only the lanes of their own half.
     const unsigned hmask = 0xFFFFu << (threadIdx.x & 16);
-    for (int j0 = hw; j0 < len; j0 += 64) {
-        float dot[4];
+    constexpr int UK = 8;
+    for (int j0 = hw; j0 < len; j0 += 16 * UK) {
+        float dot[UK];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < UK; ++u) {
             const int j = j0 + 16 * u;
-            const float4 kk = (j < len && has) ? *(const float4*)(kc + (size_t)j * d + hs + 4 * li) : z4;
+            const float* kr = j == p ? row + d : kc + (size_t)j * d;
+            const float4 kk = (j < len && has) ? *(const float4*)(kr + hs + 4 * li) : z4;
             dot[u] = fmaf(q.w, kk.w, fmaf(q.z, kk.z, fmaf(q.y, kk.y, q.x * kk.x)));
         }
 #pragma unroll
         for (int sh = 8; sh > 0; sh >>= 1)
 #pragma unroll
-            for (int u = 0; u < 4; ++u) dot[u] += __shfl_xor_sync(hmask, dot[u], sh);
+            for (int u = 0; u < UK; ++u) dot[u] += __shfl_xor_sync(hmask, dot[u], sh);
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < UK; ++u) {
             const int j = j0 + 16 * u;
             if (j < len) {
                 const float v = dot[u] * scale;
@@ -497,7 +507,8 @@ __global__ void __launch_bounds__(256) attn_decode_batch_kernel(const float* __r
         for (int u = 0; u < 4; ++u) {
             const int j = j0 + 16 * u;
             const bool on = j < len && has;
-            vv[u] = on ? *(const float4*)(vc + (size_t)j * d + hs + 4 * li) : z4;
+            const float* vr = j == p ? row + 2 * d : vc + (size_t)j * d;
+            vv[u] = on ? *(const float4*)(vr + hs + 4 * li) : z4;
             pj[u] = j < len ? sc[j] / sum : 0.0f;
         }
 #pragma unroll
