@@ -714,8 +714,10 @@ int launch_skinny_q8(const QFrag& w, int S, const void* xp, const float* bias, i
     const int warps = std::min(out.max_warps, kb_cta >= 32 ? 16 : kb_cta >= 16 ? 8 : kb_cta >= 8 ? 4 : kb_cta >= 4 ? 2 : 1);
     a.depth = std::max(1, std::min(SK_DEPTH, (kb_cta + warps - 1) / warps));
     if (cols <= 32) {
-        // few streams: bound by the weight stream; 32 rows per CTA only when that still leaves every SM several CTAs
-        const bool wide = (w.N + 31) / 32 * splits >= 2 * 148;
+        // few streams: a chain on its own is bound by latency and takes 32 rows per CTA only when that still leaves
+        // every SM several CTAs; chains that share the GPU are bound by throughput, and 32 rows halve the activation
+        // fragments read from L2 per weight
+        const bool wide = (w.N + 31) / 32 * splits >= 2 * 148 || out.max_warps < 16;
         if (cols == 16) return wide ? launch_skinny_nt<2, 2>(a, warps, 1, splits, st) : launch_skinny_nt<2, 1>(a, warps, 1, splits, st);
         return wide ? launch_skinny_nt<4, 2>(a, warps, 1, splits, st) : launch_skinny_nt<4, 1>(a, warps, 1, splits, st);
     }
