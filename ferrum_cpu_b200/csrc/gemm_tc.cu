@@ -38,7 +38,7 @@ constexpr int STAGES = 2;
 constexpr int TILE_BYTES = 128 * BK * 2;                // one 128-row bf16 operand tile: 16 KiB
 constexpr int A_BYTES = 2 * TILE_BYTES;                 // one plane of the 256-row X tile
 constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * TILE_BYTES;   // A hi, A lo (256 rows each), B hi, B lo
-constexpr int EPI_WARPS = 4, DQ_WARPS = 8;
+constexpr int EPI_WARPS = 8, DQ_WARPS = 8;   // epilogue: four warps (one per 32 TMEM lanes) for each 128-row half of the tile
 constexpr int TMA_WARP = EPI_WARPS + DQ_WARPS, MMA_WARP = TMA_WARP + 1;
 constexpr int THREADS = (MMA_WARP + 1) * 32;
 constexpr int TMEM_COLS = 512;                          // two buffers of two 128-column accumulators
@@ -296,7 +296,7 @@ gemm_q8_bf16x3_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_c
             }
         }
     } else {
-        // ---------------------------------------------------------------- epilogue (warps 0-3)
+        // ---------------------------------------------------------------- epilogue (warps 0-7)
         const bool vec_ok = (a.ldy & 3) == 0 && (((uintptr_t)a.y | (uintptr_t)a.residual) & 15) == 0;
         // rows of 32 columns start on 32-byte boundaries: whole-sector accesses
         const bool vec8_ok = (a.ldy & 7) == 0 && (((uintptr_t)a.y | (uintptr_t)a.residual) & 31) == 0;
@@ -310,12 +310,12 @@ gemm_q8_bf16x3_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_c
             const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
             if (!wait_bar(bars, &bars->acc_full[buf], (ti >> 1) & 1, a.status, a.wait_cycles)) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int hm = warp >> 2, quarter = warp & 3;                // 128-row half of the tile, 32-lane quarter of TMEM
 #pragma unroll 1
-            for (int cc = 0; cc < 2 * (BN / 32); ++cc) {
-                const int hm = cc / (BN / 32), c = cc % (BN / 32);       // 128-row half, 32-column chunk
-                const int m = m0 + hm * 128 + warp * 32 + lane;
+            for (int c = 0; c < BN / 32; ++c) {                          // 32-column chunk
+                const int m = m0 + hm * 128 + quarter * 32 + lane;
                 uint32_t r[32];
-                const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)((buf * 2 + hm) * BN + c * 32);
+                const uint32_t taddr = tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)((buf * 2 + hm) * BN + c * 32);
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                     "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -326,8 +326,8 @@ gemm_q8_bf16x3_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_c
                       "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                     : "r"(taddr) : "memory");
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (cc == 2 * (BN / 32) - 1) {
-                    // the accumulator is in registers: hand the TMEM buffer back to the MMA warp
+                if (c == BN / 32 - 1) {
+                    // this warp's part of the accumulator is in registers: hand the TMEM buffer back to the MMA warp
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&bars->acc_empty[buf]);
