@@ -195,11 +195,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_hi, const __grid_co
             const uint64_t vh = smem_desc(sb + OFF_V), vl = smem_desc(sb + OFF_V + KV_BYTES);
             const uint64_t ph = smem_desc(sb + OFF_P), pl = smem_desc(sb + OFF_P + P_BYTES);
             bool ok = wait_bar(bars, &bars->q_full, 0, a.status);
-            for (int kt = 0; kt < n_kt && ok; ++kt) {
+            // score tile kt: its keys have landed and the softmax warps have read the previous one out of TMEM
+            auto issue_scores = [&](int kt) -> bool {
                 const uint32_t par = kt & 1;
-                // score tile: the softmax warps must have read the previous one out of TMEM
-                ok = wait_bar(bars, &bars->k_full, par, a.status) && wait_bar(bars, &bars->s_empty, par ^ 1, a.status);
-                if (!ok) break;
+                if (!(wait_bar(bars, &bars->k_full, par, a.status) && wait_bar(bars, &bars->s_empty, par ^ 1, a.status))) return false;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ++ks) {
@@ -210,6 +209,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_hi, const __grid_co
                 }
                 umma_commit(&bars->s_full);
                 umma_commit(&bars->k_empty);
+                return true;
+            };
+            ok = ok && issue_scores(0);
+            for (int kt = 0; kt < n_kt && ok; ++kt) {
+                const uint32_t par = kt & 1;
+                // the next score tile is issued ahead of this tile's P·V: its MMAs run while the softmax warps are
+                // still turning this tile's scores into P, and its scores are ready when they come back
+                if (kt + 1 < n_kt) {
+                    ok = issue_scores(kt + 1);
+                    if (!ok) break;
+                }
                 // P·V tile: P is in shared memory, the previous P·V tile has been folded in
                 ok = wait_bar(bars, &bars->v_full, par, a.status) && wait_bar(bars, &bars->p_full, par, a.status) &&
                      wait_bar(bars, &bars->o_empty, par ^ 1, a.status);
