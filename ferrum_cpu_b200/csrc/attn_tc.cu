@@ -55,6 +55,12 @@ struct Bars {
 constexpr int SMEM_BYTES = OFF_BARS + 1024 /* alignment slack */ + (int)sizeof(Bars);
 
 __device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+// 2^x on the special-function unit (2 ulp); 2^-inf = 0
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ void mbar_init(unsigned long long* b, int count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s32(b)), "r"(count) : "memory");
 }
@@ -241,7 +247,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_hi, const __grid_co
         // ------------------------------------------------------------------ softmax warps
         const int r = warp * 32 + lane;               // query row inside the tile
         const int qi = q0 + r;                        // query index inside the window
-        const float scale = 0.125f;                   // 1 / sqrt(64)
+        const float c2 = 0.125f * 1.4426950408889634f;   // 1 / sqrt(64) times log2(e)
         float o[HD];
 #pragma unroll
         for (int c = 0; c < HD; ++c) o[c] = 0.0f;
@@ -261,25 +267,27 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_hi, const __grid_co
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars->s_empty);
-            // scale, causal mask (key j > query i has weight exactly 0), running max
+            // causal mask (key j > query i has weight exactly 0) and running max on the raw scores; the scale
+            // 1 / sqrt(hd) and log2(e) go into one constant of the exponent: p = 2^((s - max) * scale * log2 e)
             const int k0 = kt * KT;
             float sv[KT];
             float tmax = -INFINITY;
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-                sv[j] = (k0 + j <= qi) ? __uint_as_float(s0[j]) * scale : -INFINITY;
-                sv[32 + j] = (k0 + 32 + j <= qi) ? __uint_as_float(s1[j]) * scale : -INFINITY;
+                sv[j] = (k0 + j <= qi) ? __uint_as_float(s0[j]) : -INFINITY;
+                sv[32 + j] = (k0 + 32 + j <= qi) ? __uint_as_float(s1[j]) : -INFINITY;
                 tmax = fmaxf(tmax, fmaxf(sv[j], sv[32 + j]));
             }
             const float mn = fmaxf(m, tmax);          // finite from the first tile on (key 0 <= every query)
-            const float corr = expf(m - mn);
+            const float corr = exp2f((m - mn) * c2);
+            const float off2 = -mn * c2;
             float psum = 0.0f;
 #pragma unroll
             for (int c = 0; c < KT / 8; ++c) {        // 16-byte chunk c of the P row: 8 keys
                 uint4 hi, lo;
                 float p[8];
 #pragma unroll
-                for (int e = 0; e < 8; ++e) { p[e] = expf(sv[8 * c + e] - mn); psum += p[e]; }
+                for (int e = 0; e < 8; ++e) { p[e] = ex2_approx(fmaf(sv[8 * c + e], c2, off2)); psum += p[e]; }
                 split2(p[0], p[1], &hi.x, &lo.x);
                 split2(p[2], p[3], &hi.y, &lo.y);
                 split2(p[4], p[5], &hi.z, &lo.z);
@@ -293,8 +301,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_hi, const __grid_co
             if (lane == 0) mbar_arrive(&bars->p_full);
             l = fmaf(l, corr, psum);
             m = mn;
+            if (__any_sync(0xffffffffu, corr != 1.0f)) {   // the running max moves in the first tiles and rarely after
 #pragma unroll
-            for (int c = 0; c < HD; ++c) o[c] *= corr;
+                for (int c = 0; c < HD; ++c) o[c] *= corr;
+            }
             // fold in this tile's P·V
             ok = wait_bar(bars, &bars->o_full, par, a.status);
             if (!ok) break;
