@@ -289,6 +289,9 @@ int fc_generate_sampled(fc_stream* s, const int32_t* prompt, int n, int max_new,
  * go on. The extra feed after the last sampled token (token_stream.rs:181-186) is not run. Streams
  * that would outgrow the context (prompt_len + max_new > ctx: they need the re-prime of
  * token_stream.rs:162-165) and single streams run one after the other as fc_generate_greedy.
+ * More than 16 streams of a wave run as groups of 16 on parallel branches of the step's CUDA graph (each group
+ * reads the weights once); the environment variable FERRUM_LOCKSTEP_GROUP=<n> sets another group size (a
+ * tuning aid: tokens do not depend on it beyond the summation order of the kernels it selects).
  * Device time of the whole call: fc_last_batch_ms; of its primes alone: fc_last_batch_prime_ms. */
 int fc_decode_batch(fc_model* m, int n_streams, const int32_t* prompts, int prompt_len, int max_new, int32_t eos,
                     int32_t* out, int* n_out);
