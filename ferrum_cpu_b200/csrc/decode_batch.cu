@@ -372,37 +372,51 @@ __global__ void ln_rows_f16_kernel(const float* __restrict__ x, const float* __r
 #pragma unroll
     for (int i = 0; i < PER; ++i) {
         const int c = threadIdx.x + i * blockDim.x;
-        gv[i] = c < d ? __ldg(g + c) : 0.0f;
-        bv[i] = c < d ? __ldg(b + c) : 0.0f;
-        pbv[i] = (c < d && n_part > 0 && part_bias) ? __ldg(part_bias + c) : 0.0f;
+        gv[i] = __ldg(g + min(c, d - 1));
+        bv[i] = __ldg(b + min(c, d - 1));
+        pbv[i] = (n_part > 0 && part_bias) ? __ldg(part_bias + min(c, d - 1)) : 0.0f;
     }
     pdl_wait_prior();
     pdl_launch_next();
     const int s = blockIdx.x;
     const float* xr = x + (size_t)s * d;
+    // Loads are clamped, not guarded: a guarded load per iteration puts a branch between the loads and they go out one
+    // L2 round trip at a time; unguarded they are all in flight together.
     float v[PER];
     float sum = 0.0f;
+    if (n_part > 0) {
+        constexpr int CH = PER < 4 ? PER : 4;      // columns per thread whose loads are in flight together
 #pragma unroll
-    for (int i = 0; i < PER; ++i) {
-        const int c = threadIdx.x + i * blockDim.x;
-        float xv = 0.0f;
-        if (c < d) {
-            xv = xr[c];
-            if (n_part > 0) {
-                // all partials are requested before the first add (n_part <= SK_MAX_SPLITS), then added in order
-                float pp[SK_MAX_SPLITS];
+        for (int i0 = 0; i0 < PER; i0 += CH) {
+            float pp[CH][SK_MAX_SPLITS];
 #pragma unroll
-                for (int p = 0; p < SK_MAX_SPLITS; ++p) pp[p] = p < n_part ? part[((size_t)p * S + s) * d + c] : 0.0f;
-                float pv = pp[0];
+            for (int k = 0; k < CH; ++k) {
+                const int c = min((int)(threadIdx.x + (i0 + k) * blockDim.x), d - 1);
+                v[i0 + k] = xr[c];
 #pragma unroll
-                for (int p = 1; p < SK_MAX_SPLITS; ++p) pv = p < n_part ? pv + pp[p] : pv;
+                for (int p = 0; p < SK_MAX_SPLITS; ++p) pp[k][p] = part[((size_t)min(p, n_part - 1) * S + s) * d + c];
+            }
+#pragma unroll
+            for (int k = 0; k < CH; ++k) {
+                const int i = i0 + k, c = threadIdx.x + i * blockDim.x;
+                float pv = pp[k][0];               // the partials are added in order
+#pragma unroll
+                for (int p = 1; p < SK_MAX_SPLITS; ++p) pv = p < n_part ? pv + pp[k][p] : pv;
                 if (part_bias) pv += pbv[i];
-                xv = xv + pv;
-                if (x_out) x_out[(size_t)s * d + c] = xv;
+                const float xv = c < d ? v[i] + pv : 0.0f;
+                if (c < d && x_out) x_out[(size_t)s * d + c] = xv;
+                v[i] = xv;
+                sum += xv;
             }
         }
-        v[i] = xv;
-        sum += xv;
+    } else {
+#pragma unroll
+        for (int i = 0; i < PER; ++i) v[i] = xr[min((int)(threadIdx.x + i * blockDim.x), d - 1)];
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            if ((int)(threadIdx.x + i * blockDim.x) >= d) v[i] = 0.0f;
+            sum += v[i];
+        }
     }
     const float mean = block_sum(sum, red) / (float)d;
     float q = 0.0f;
@@ -458,6 +472,7 @@ __global__ void __launch_bounds__(256) attn_decode_batch_kernel(const float* __r
     }
     const int hw = threadIdx.x >> 4, li = threadIdx.x & 15;
     const bool has = 4 * li < hd;
+    const int lic = has ? li : 0;                  // a lane past the head width reads lane 0's columns and drops them
     const float4 z4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     const float4 q = has ? *(const float4*)(row + hs + 4 * li) : z4;
     const float scale = 1.0f / sqrtf((float)hd);
@@ -468,11 +483,17 @@ __global__ void __launch_bounds__(256) attn_decode_batch_kernel(const float* __r
     constexpr int UK = 8;
     for (int j0 = hw; j0 < len; j0 += 16 * UK) {
         float dot[UK];
+        float4 kq[UK];
 #pragma unroll
         for (int u = 0; u < UK; ++u) {
             const int j = j0 + 16 * u;
-            const float* kr = j == p ? row + d : kc + (size_t)j * d;
-            const float4 kk = (j < len && has) ? *(const float4*)(kr + hs + 4 * li) : z4;
+            const int jc = min(j, len - 1);            // clamped, not guarded: all eight loads are in flight together
+            const float* kr = jc == p ? row + d : kc + (size_t)jc * d;
+            kq[u] = *(const float4*)(kr + hs + 4 * lic);
+        }
+#pragma unroll
+        for (int u = 0; u < UK; ++u) {
+            const float4 kk = (j0 + 16 * u < len && has) ? kq[u] : z4;
             dot[u] = fmaf(q.w, kk.w, fmaf(q.z, kk.z, fmaf(q.y, kk.y, q.x * kk.x)));
         }
 #pragma unroll
@@ -506,10 +527,10 @@ __global__ void __launch_bounds__(256) attn_decode_batch_kernel(const float* __r
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
             const int j = j0 + 16 * u;
-            const bool on = j < len && has;
-            const float* vr = j == p ? row + 2 * d : vc + (size_t)j * d;
-            vv[u] = on ? *(const float4*)(vr + hs + 4 * li) : z4;
-            pj[u] = j < len ? sc[j] / sum : 0.0f;
+            const int jc = min(j, len - 1);
+            const float* vr = jc == p ? row + 2 * d : vc + (size_t)jc * d;
+            vv[u] = *(const float4*)(vr + hs + 4 * lic);
+            pj[u] = (j < len && has) ? sc[jc] / sum : 0.0f;   // rows past the end and lanes past the head weigh 0
         }
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
