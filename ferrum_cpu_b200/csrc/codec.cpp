@@ -223,4 +223,196 @@ int fc_ggml_to_q8_0(int ggml_type, const void* raw, size_t n, void* out) {
     return FC_OK;
 }
 
+
+// ---- every GGML block format the reference's importer reads (gguf/dequant.rs:37-315), to f32 ---------------
+// Sizes of gguf/format.rs:107-130: values per block and bytes per block.
+static bool ggml_block(int t, size_t* vals, size_t* bytes) {
+    switch (t) {
+        case FC_GGML_F32: *vals = 1; *bytes = 4; return true;
+        case FC_GGML_F16: *vals = 1; *bytes = 2; return true;
+        case FC_GGML_Q4_0: *vals = 32; *bytes = 18; return true;
+        case FC_GGML_Q4_1: *vals = 32; *bytes = 20; return true;
+        case FC_GGML_Q5_0: *vals = 32; *bytes = 22; return true;
+        case FC_GGML_Q5_1: *vals = 32; *bytes = 24; return true;
+        case FC_GGML_Q8_0: *vals = 32; *bytes = 34; return true;
+        case FC_GGML_Q8_1: *vals = 32; *bytes = 36; return true;
+        case FC_GGML_Q2_K: *vals = 256; *bytes = 84; return true;
+        case FC_GGML_Q3_K: *vals = 256; *bytes = 110; return true;
+        case FC_GGML_Q4_K: *vals = 256; *bytes = 144; return true;
+        case FC_GGML_Q5_K: *vals = 256; *bytes = 176; return true;
+        case FC_GGML_Q6_K: *vals = 256; *bytes = 210; return true;
+        default: return false;
+    }
+}
+
+size_t fc_ggml_type_bytes(int ggml_type, size_t n) {
+    size_t vals = 0, bytes = 0;
+    if (!ggml_block(ggml_type, &vals, &bytes) || n % vals) return 0;
+    return n / vals * bytes;
+}
+
+}  // extern "C"
+
+namespace {
+inline float half_at(const uint8_t* p) { return fc_f16_to_f32((uint16_t)(p[0] | (p[1] << 8))); }
+
+// The 6-bit (scale, min) pair of sub-block j of a Q4_K / Q5_K super-block (gguf/dequant.rs:133-141): the first
+// four pairs sit in the low six bits of bytes j and j + 4; the last four keep their low nibbles in byte j + 4
+// and their top two bits in the spare bits of bytes j - 4 and j.
+inline void k4_scale_min(int j, const uint8_t* q, int* sc, int* mn) {
+    if (j < 4) { *sc = q[j] & 63; *mn = q[j + 4] & 63; }
+    else { *sc = (q[j + 4] & 0x0F) | ((q[j - 4] >> 6) << 4); *mn = (q[j + 4] >> 4) | ((q[j] >> 6) << 4); }
+}
+
+// One block of `t` at `b` into out[0 .. values per block). Products are formed exactly as the reference forms them
+// (which factor is rounded first), so the f32 results agree bit for bit.
+void dequant_block(int t, const uint8_t* b, float* out) {
+    switch (t) {
+        case FC_GGML_F32: std::memcpy(out, b, 4); break;
+        case FC_GGML_F16: out[0] = half_at(b); break;
+        case FC_GGML_Q8_0: case FC_GGML_Q8_1: {           // dequant.rs:37-64 (Q8_1 carries an unused block sum)
+            const float d = half_at(b);
+            const int8_t* q = (const int8_t*)(b + (t == FC_GGML_Q8_0 ? 2 : 4));
+            for (int j = 0; j < 32; ++j) out[j] = d * (float)q[j];
+            break;
+        }
+        case FC_GGML_Q4_0: {                               // dequant.rs:66-83
+            const float d = half_at(b);
+            for (int j = 0; j < 16; ++j) {
+                out[j] = d * (float)((int)(b[2 + j] & 0x0F) - 8);
+                out[j + 16] = d * (float)((int)(b[2 + j] >> 4) - 8);
+            }
+            break;
+        }
+        case FC_GGML_Q4_1: {                               // dequant.rs:85-101: d * nibble + m
+            const float d = half_at(b), m = half_at(b + 2);
+            for (int j = 0; j < 16; ++j) {
+                out[j] = d * (float)(b[4 + j] & 0x0F) + m;
+                out[j + 16] = d * (float)(b[4 + j] >> 4) + m;
+            }
+            break;
+        }
+        case FC_GGML_Q5_0: case FC_GGML_Q5_1: {           // dequant.rs:105-130
+            const bool with_min = t == FC_GGML_Q5_1;
+            const float d = half_at(b), m = with_min ? half_at(b + 2) : 0.0f;
+            const uint8_t* hb = b + (with_min ? 4 : 2);
+            const uint32_t qh = (uint32_t)hb[0] | ((uint32_t)hb[1] << 8) | ((uint32_t)hb[2] << 16) | ((uint32_t)hb[3] << 24);
+            const uint8_t* qs = hb + 4;
+            for (int j = 0; j < 16; ++j) {
+                const int x0 = (qs[j] & 0x0F) | (int)(((qh >> j) & 1u) << 4);
+                const int x1 = (qs[j] >> 4) | (int)(((qh >> (j + 16)) & 1u) << 4);
+                out[j] = with_min ? d * (float)x0 + m : d * (float)(x0 - 16);
+                out[j + 16] = with_min ? d * (float)x1 + m : d * (float)(x1 - 16);
+            }
+            break;
+        }
+        case FC_GGML_Q4_K: case FC_GGML_Q5_K: {           // dequant.rs:143-206: (d * sc) * q - (dmin * m)
+            const bool five = t == FC_GGML_Q5_K;
+            const float d = half_at(b), dmin = half_at(b + 2);
+            const uint8_t* scales = b + 4;
+            const uint8_t* qh = b + 16;                     // Q5_K only: 32 bytes, bit 2g / 2g + 1 of byte l for pair g
+            const uint8_t* qs = b + (five ? 48 : 16);
+            for (int g = 0; g < 4; ++g) {                  // 64 values: low nibbles, then high nibbles, of 32 bytes
+                int s1, m1, s2, m2;
+                k4_scale_min(2 * g, scales, &s1, &m1);
+                k4_scale_min(2 * g + 1, scales, &s2, &m2);
+                const float d1 = d * (float)s1, n1 = dmin * (float)m1, d2 = d * (float)s2, n2 = dmin * (float)m2;
+                for (int l = 0; l < 32; ++l) {
+                    const int h1 = five && (qh[l] & (1u << (2 * g))) ? 16 : 0;
+                    const int h2 = five && (qh[l] & (2u << (2 * g))) ? 16 : 0;
+                    out[64 * g + l] = d1 * (float)((qs[32 * g + l] & 0x0F) + h1) - n1;
+                    out[64 * g + 32 + l] = d2 * (float)((qs[32 * g + l] >> 4) + h2) - n2;
+                }
+            }
+            break;
+        }
+        case FC_GGML_Q6_K: {                               // dequant.rs:208-241: (d * scale) * (6-bit value - 32)
+            const uint8_t *ql = b, *qh = b + 128;
+            const int8_t* sc = (const int8_t*)(b + 192);
+            const float d = half_at(b + 208);
+            for (int half = 0; half < 2; ++half)
+                for (int l = 0; l < 32; ++l) {
+                    const int is = l / 16;
+                    const uint8_t h = qh[32 * half + l];
+                    const int q1 = ((ql[64 * half + l] & 0x0F) | ((h & 3) << 4)) - 32;
+                    const int q2 = ((ql[64 * half + l + 32] & 0x0F) | (((h >> 2) & 3) << 4)) - 32;
+                    const int q3 = ((ql[64 * half + l] >> 4) | (((h >> 4) & 3) << 4)) - 32;
+                    const int q4 = ((ql[64 * half + l + 32] >> 4) | (((h >> 6) & 3) << 4)) - 32;
+                    float* o = out + 128 * half + l;
+                    o[0] = d * (float)sc[8 * half + is] * (float)q1;
+                    o[32] = d * (float)sc[8 * half + is + 2] * (float)q2;
+                    o[64] = d * (float)sc[8 * half + is + 4] * (float)q3;
+                    o[96] = d * (float)sc[8 * half + is + 6] * (float)q4;
+                }
+            break;
+        }
+        case FC_GGML_Q2_K: {                               // dequant.rs:243-276: (d * sc) * q - (dmin * m), 16 runs of 16
+            const uint8_t *scales = b, *qs = b + 16;
+            const float d = half_at(b + 80), dmin = half_at(b + 82);
+            int run = 0;
+            for (int half = 0; half < 2; ++half)
+                for (int shift = 0; shift < 8; shift += 2)
+                    for (int r = 0; r < 2; ++r, ++run) {
+                        const float dl = d * (float)(scales[run] & 0x0F), ml = dmin * (float)(scales[run] >> 4);
+                        for (int l = 0; l < 16; ++l) out[16 * run + l] = dl * (float)((qs[32 * half + 16 * r + l] >> shift) & 3) - ml;
+                    }
+            break;
+        }
+        case FC_GGML_Q3_K: {                               // dequant.rs:278-324: d * (scale - 32) * (low2 - (high bit ? 0 : 4))
+            const uint8_t *hmask = b, *qs = b + 32, *sc = b + 96;
+            const float d = half_at(b + 108);
+            int scales[16];
+            for (int j = 0; j < 8; ++j) { scales[j] = sc[j] & 0x0F; scales[j + 8] = sc[j] >> 4; }
+            for (int j = 0; j < 16; ++j) scales[j] |= ((sc[8 + j / 4] >> (2 * (j % 4))) & 3) << 4;
+            int run = 0;
+            unsigned m = 1;
+            for (int half = 0; half < 2; ++half)
+                for (int shift = 0; shift < 8; shift += 2, m <<= 1)
+                    for (int r = 0; r < 2; ++r, ++run) {
+                        const float dl = d * (float)((int)(int8_t)scales[run] - 32);
+                        for (int l = 16 * r; l < 16 * r + 16; ++l) {
+                            const int low = (qs[32 * half + l] >> shift) & 3;
+                            out[16 * run + (l - 16 * r)] = dl * (float)(low - ((hmask[l] & m) ? 0 : 4));
+                        }
+                    }
+            break;
+        }
+    }
+}
+}  // namespace
+
+extern "C" {
+
+int fc_ggml_dequantize(int ggml_type, const void* raw, size_t nbytes, size_t n, float* out) {
+    if (!raw || !out) return FC_E_ARG;
+    size_t vals = 0, bytes = 0;
+    if (!ggml_block(ggml_type, &vals, &bytes) || n % vals) return FC_E_FORMAT;
+    if (nbytes < n / vals * bytes) return FC_E_FORMAT;       // data shorter than the element count (dequant.rs:541-547)
+    const uint8_t* src = (const uint8_t*)raw;
+    for (size_t i = 0; i < n / vals; ++i) dequant_block(ggml_type, src + i * bytes, out + i * vals);
+    return FC_OK;
+}
+
+int fc_ggml_requantize_q8_0(int ggml_type, const void* raw, size_t nbytes, size_t n, void* out) {
+    if (!raw || !out) return FC_E_ARG;
+    if (n % 32) return FC_E_FORMAT;
+    if (fc_ggml_block_bytes(ggml_type)) {                      // integer levels under one f16 scale: exact
+        if (nbytes < n / 32 * fc_ggml_block_bytes(ggml_type)) return FC_E_FORMAT;
+        return fc_ggml_to_q8_0(ggml_type, raw, n, out);
+    }
+    size_t vals = 0, bytes = 0;
+    if (!ggml_block(ggml_type, &vals, &bytes) || n % vals || nbytes < n / vals * bytes) return FC_E_FORMAT;
+    // formats with minima or sub-block scales: to f32 and through the Q8_0 encoder, 256 values at a time
+    const uint8_t* src = (const uint8_t*)raw;
+    uint8_t* dst = (uint8_t*)out;
+    float buf[256];
+    const size_t step = vals < 32 ? 32 : vals;                 // f32 / f16 values go 32 at a time
+    for (size_t i = 0; i < n; i += step) {
+        for (size_t k = 0; k < step / vals; ++k) dequant_block(ggml_type, src + (i / vals + k) * bytes, buf + k * vals);
+        const int rc = fc_q8_0_quantize(buf, step, dst + i / 32 * 34);
+        if (rc != FC_OK) return rc;
+    }
+    return FC_OK;
+}
+
 }  // extern "C"

@@ -24,7 +24,7 @@ using fc::fail;
 namespace {
 
 constexpr uint32_t kMagic = 0x46554747u;   // "GGUF"
-constexpr uint32_t T_F32 = 0, T_F16 = 1, T_Q4_0 = 2, T_Q5_0 = 6, T_Q8_0 = 8;
+constexpr uint32_t T_F32 = 0, T_Q8_0 = 8;   // the types this engine computes on; the others are converted at load
 enum : uint32_t { VT_U8, VT_I8, VT_U16, VT_I16, VT_U32, VT_I32, VT_F32, VT_BOOL, VT_STRING, VT_ARRAY, VT_U64, VT_I64, VT_F64 };
 
 struct Tensor {
@@ -42,7 +42,9 @@ struct Meta {
 };
 
 struct File {
-    // Q4_0 / Q5_0 matrices re-blocked to Q8_0 (exactly: same scale, integer levels) on first use
+    // matrices stored in another block format, brought to Q8_0 on first use: Q4_0 / Q5_0 re-blocked exactly (same scale,
+    // integer levels), the formats with minima or sub-block scales (Q4_1, Q5_1, Q8_1, the K-quants) and f16 / f32
+    // matrices decoded and re-encoded with the Q8_0 block encoder
     mutable std::map<std::string, std::vector<uint8_t>> reblocked;
     std::vector<uint8_t> bytes;
     std::map<std::string, Meta> meta;        // scalars and short strings (arrays are skipped)
@@ -119,16 +121,8 @@ bool read_value(Cursor& c, uint32_t type, Meta* out) {
     return c.ok;
 }
 
-uint64_t type_nbytes(uint32_t type, uint64_t n) {
-    switch (type) {
-        case T_F32: return n * 4;
-        case T_F16: return n * 2;
-        case T_Q8_0: return n % 32 ? 0 : n / 32 * 34;
-        case T_Q4_0: return n % 32 ? 0 : n / 32 * 18;
-        case T_Q5_0: return n % 32 ? 0 : n / 32 * 22;
-        default: return 0;
-    }
-}
+// gguf/format.rs:107-130: every tensor type the reference's importer reads; 0 for the others
+uint64_t type_nbytes(uint32_t type, uint64_t n) { return (uint64_t)fc_ggml_type_bytes((int)type, (size_t)n); }
 
 int read_file(const char* path, File* f) {
     FILE* fp = fopen(path, "rb");
@@ -195,10 +189,10 @@ int tensor(const File& f, const std::string& name, uint32_t type, uint64_t ne0, 
     auto it = f.tensors.find(name);
     if (it == f.tensors.end()) return fail(FC_E_FORMAT, "GGUF tensor %s is missing", name.c_str());
     const Tensor& t = it->second;
-    const bool reblock = type == T_Q8_0 && (t.type == T_Q4_0 || t.type == T_Q5_0);
+    const bool reblock = type == T_Q8_0 && t.type != T_Q8_0 && type_nbytes(t.type, 256) != 0;
     if (t.type != type && !reblock)
         return fail(FC_E_FORMAT, "GGUF tensor %s has ggml type %u, this engine needs %u (%s)", name.c_str(), t.type, type,
-                    type == T_Q8_0 ? "matrices stay packed: Q8_0, or Q4_0 / Q5_0 re-blocked to it" : "vectors are F32");
+                    type == T_Q8_0 ? "matrices are Q8_0, or one of the block formats of gguf/dequant.rs brought to it" : "vectors are F32");
     const uint64_t d0 = t.dims[0], d1 = t.dims.size() > 1 ? t.dims[1] : 1;
     for (size_t k = 2; k < t.dims.size(); ++k)
         if (t.dims[k] != 1) return fail(FC_E_FORMAT, "GGUF tensor %s has more than two dimensions", name.c_str());
@@ -218,8 +212,8 @@ int tensor(const File& f, const std::string& name, uint32_t type, uint64_t ne0, 
         if (store.empty()) {
             const uint64_t n = d0 * d1;
             store.resize((size_t)(n / 32 * 34));
-            if (fc_ggml_to_q8_0((int)t.type, *out, (size_t)n, store.data()) != FC_OK)
-                return fail(FC_E_FORMAT, "GGUF tensor %s could not be re-blocked to Q8_0", name.c_str());
+            if (n % 32 || fc_ggml_requantize_q8_0((int)t.type, *out, (size_t)t.nbytes, (size_t)n, store.data()) != FC_OK)
+                return fail(FC_E_FORMAT, "GGUF tensor %s (ggml type %u) could not be brought to Q8_0", name.c_str(), t.type);
         }
         *out = store.data();
     }

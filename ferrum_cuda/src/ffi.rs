@@ -25,6 +25,16 @@ pub const FC_ROPE_NEOX: c_int = 1;
 pub const FC_GGML_Q4_0: c_int = 2;
 pub const FC_GGML_Q5_0: c_int = 6;
 pub const FC_GGML_Q8_0: c_int = 8;
+pub const FC_GGML_F32: c_int = 0;
+pub const FC_GGML_F16: c_int = 1;
+pub const FC_GGML_Q4_1: c_int = 3;
+pub const FC_GGML_Q5_1: c_int = 7;
+pub const FC_GGML_Q8_1: c_int = 9;
+pub const FC_GGML_Q2_K: c_int = 10;
+pub const FC_GGML_Q3_K: c_int = 11;
+pub const FC_GGML_Q4_K: c_int = 12;
+pub const FC_GGML_Q5_K: c_int = 13;
+pub const FC_GGML_Q6_K: c_int = 14;
 pub const FC_Q_INT8: c_int = 0;
 pub const FC_Q_INT4: c_int = 1;
 
@@ -93,6 +103,9 @@ extern "C" {
     pub fn fc_q8_0_dequantize(raw: *const c_void, n: usize, out: *mut f32) -> c_int;
     pub fn fc_ggml_block_bytes(ggml_type: c_int) -> usize;
     pub fn fc_ggml_to_q8_0(ggml_type: c_int, raw: *const c_void, n: usize, out: *mut c_void) -> c_int;
+    pub fn fc_ggml_type_bytes(ggml_type: c_int, n: usize) -> usize;
+    pub fn fc_ggml_dequantize(ggml_type: c_int, raw: *const c_void, nbytes: usize, n: usize, out: *mut f32) -> c_int;
+    pub fn fc_ggml_requantize_q8_0(ggml_type: c_int, raw: *const c_void, nbytes: usize, n: usize, out: *mut c_void) -> c_int;
     pub fn fc_f32_to_f16(v: f32) -> u16;
     pub fn fc_f16_to_f32(h: u16) -> f32;
     pub fn fc_rng_seed(seed: u64) -> u64;

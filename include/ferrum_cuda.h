@@ -91,12 +91,34 @@ int fc_q8_0_dequantize(const void* raw, size_t n, float* out);
  * - 8, gguf/dequant.rs:66-83), 6 Q5_0 (level = 5-bit value - 16, gguf/dequant.rs:105-130). n
  * values (n % 32 == 0) -> n/32*34 bytes. d * level is then the very product the reference's
  * dequantiser forms, so every kernel here serves these files unchanged (at Q8_0's footprint).
- * Formats with a minimum or sub-block scales (Q4_1, Q5_1, K-quants) are FC_E_FORMAT. */
+ * Formats with a minimum or sub-block scales (Q4_1, Q5_1, K-quants) are FC_E_FORMAT here; they go through
+ * fc_ggml_requantize_q8_0 below. */
 #define FC_GGML_Q4_0 2
 #define FC_GGML_Q5_0 6
 #define FC_GGML_Q8_0 8
 size_t fc_ggml_block_bytes(int ggml_type);   /* bytes of one 32-value block, 0 if not covered */
 int fc_ggml_to_q8_0(int ggml_type, const void* raw, size_t n, void* out);
+/* Every tensor type the reference's importer reads (gguf/format.rs:10-42, gguf/dequant.rs:37-315), decoded to
+ * f32 with the reference's own order of operations (bit-identical): F32, F16, Q4_0, Q4_1, Q5_0, Q5_1, Q8_0, Q8_1
+ * and the K-quants Q2_K .. Q6_K (super-blocks of 256). fc_ggml_type_bytes: storage of n values, 0 for an unknown
+ * type or an n that is not a whole number of blocks (gguf/format.rs:107-130). fc_ggml_dequantize refuses data
+ * shorter than n values (FC_E_FORMAT). fc_ggml_requantize_q8_0 is the import route for matrices: the exact
+ * re-blocking above where it exists, else decode and re-encode with the Q8_0 block encoder along the row
+ * (quant.rs:271-280) - what a wrapper beside the untouched loader does with the f32 layers it is handed, and the
+ * counterpart of the reference re-packing every imported matrix to int8 / int4 (gguf/llama.rs:13-27). */
+#define FC_GGML_F32 0
+#define FC_GGML_F16 1
+#define FC_GGML_Q4_1 3
+#define FC_GGML_Q5_1 7
+#define FC_GGML_Q8_1 9
+#define FC_GGML_Q2_K 10
+#define FC_GGML_Q3_K 11
+#define FC_GGML_Q4_K 12
+#define FC_GGML_Q5_K 13
+#define FC_GGML_Q6_K 14
+size_t fc_ggml_type_bytes(int ggml_type, size_t n);
+int fc_ggml_dequantize(int ggml_type, const void* raw, size_t nbytes, size_t n, float* out);
+int fc_ggml_requantize_q8_0(int ggml_type, const void* raw, size_t nbytes, size_t n, void* out);
 uint16_t fc_f32_to_f16(float v);  /* gguf_write/blocks.rs:12-61 */
 float fc_f16_to_f32(uint16_t h);  /* gguf/dequant.rs:7-35 */
 /* rng.rs:9-48 xorshift64*: seed -> state (0 is remapped), draws advance *state. */
