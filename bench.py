@@ -303,7 +303,9 @@ def run_case(a):
         name = a.model if a.model.startswith("llama") else "llama-1b"
         sm = synth.llama_named(name, seed=0, math_mode=a.math)
         c = sm.dims
-        gm = CudaLlama.from_synth(sm)
+        gm = CudaLlama.from_synth(sm, prec=None if a.packed < 0 else a.packed)
+        if a.packed >= 0:
+            name += " packed int4" if a.packed else " packed int8"
         if a.case == "llama-decode":
             prompt = synth.token_ids(0, a.prompt, c["vocab"])
             cache = gm.new_cache()
@@ -418,6 +420,7 @@ def main():
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--math", type=int, default=0, help="--case: 0 fp32 CUDA cores, 1 tcgen05 bf16x3")
     ap.add_argument("--kind", type=int, default=0, help="--case rowq: 0 int8, 1 int4")
+    ap.add_argument("--packed", type=int, default=-1, help="--case llama-*: every Linear packed to per-row int8 (0) / int4 (1), as the reference's importer does")
     ap.add_argument("--mode", type=int, default=0, help="--case decode: 0 persistent kernel, 1 one kernel per operation")
     ap.add_argument("--trace", action="store_true", help="--case decode: print the phase timeline of one token")
     ap.add_argument("--score-steps", type=int, default=2)

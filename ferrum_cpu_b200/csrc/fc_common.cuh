@@ -185,6 +185,12 @@ int launch_sample(const float* in, int V, int from_probs, const fc_sampling& prm
                   unsigned long long* rng_state, int* queue, int queue_cap, StepState* state, int* token_out, cudaStream_t st);
 
 // Per-layer statistics of a window forward (the device-side counterpart of verbose.rs:85-110): one record per layer.
+// Per-row-scale int8 / int4 linear on a packed matrix (rowq.cu): y[M][ldy] = [residual +] bias + x · W; bias and residual may
+// be null, residual may be y itself.
+int launch_rowq_linear(fc_rowq* w, const float* x, const float* bias, const float* residual, float* y, int ldy, int M, cudaStream_t st);
+int rowq_in(const fc_rowq* w);
+int rowq_out(const fc_rowq* w);
+
 struct LayerStatsDev {
     float min, max, mean, pad;
     long long nan_count, inf_count, n;

@@ -494,7 +494,7 @@ int fc_llama_gguf_probe(const char* path, fc_llama_config* out) {
     return FC_OK;
 }
 
-int fc_llama_load_gguf(const char* path, int device, int math_mode, int ctx_cap, fc_llama** out) {
+static int load_llama_file(const char* path, int device, int math_mode, int ctx_cap, int kind, fc_llama** out) {
     if (!path || !out) return fail(FC_E_ARG, "fc_llama_load_gguf: bad argument");
     *out = nullptr;
     File f;
@@ -503,7 +503,17 @@ int fc_llama_load_gguf(const char* path, int device, int math_mode, int ctx_cap,
     ParsedLlama p;
     rc = parse_llama(f, math_mode, ctx_cap, &p);
     if (rc != FC_OK) return rc;
-    return fc_llama_create(&p.cfg, &p.w, device, out);   // copies everything it needs
+    // copies everything it needs
+    return kind < 0 ? fc_llama_create(&p.cfg, &p.w, device, out) : fc_llama_create_packed(&p.cfg, &p.w, device, kind, out);
+}
+
+int fc_llama_load_gguf(const char* path, int device, int math_mode, int ctx_cap, fc_llama** out) {
+    return load_llama_file(path, device, math_mode, ctx_cap, -1, out);
+}
+
+int fc_llama_load_gguf_packed(const char* path, int device, int ctx_cap, int kind, fc_llama** out) {
+    if (kind != FC_Q_INT8 && kind != FC_Q_INT4) return fail(FC_E_ARG, "fc_llama_load_gguf_packed: kind %d", kind);
+    return load_llama_file(path, device, FC_MATH_FP32, ctx_cap, kind, out);
 }
 
 }  // extern "C"

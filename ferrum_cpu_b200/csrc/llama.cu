@@ -43,6 +43,12 @@ struct fc_llama {
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     float last_score_ms = 0.0f;
     bool force_fp32 = false;         // the batched prime keeps the cache rows at fp32 rounding
+    // Every Linear packed as the reference's importer packs it (Gguf::load_llama(kind), gguf/llama.rs:13-27,164-171):
+    // per-input-row int8 / int4 QWeights, run by ops::qlinear. prec < 0: the Q8_0 matrices above are what runs.
+    int prec = -1;
+    struct PackedLayer { fc_rowq *wq = nullptr, *wk = nullptr, *wv = nullptr, *wo = nullptr, *gate = nullptr, *up = nullptr, *down = nullptr; };
+    std::vector<PackedLayer> packed;
+    fc_rowq* packed_head = nullptr;
 };
 
 struct fc_llama_cache {
@@ -156,7 +162,9 @@ int ensure_workspace(fc_llama* m, int rows) {
 // LlamaModel::forward_tokens (llm.rs:622-635) up to the final norm, for B windows of T rows
 // whose ids are in m->ids_d: every row r sits at position r % T. Leaves RMSNorm(h) in m->n.
 // With `fill` (B == 1) the rotated keys and the values of every block become the cache's rows 0..T-1.
+int forward_rows_packed(fc_llama* m, int B, int T, fc_llama_cache* fill);
 int forward_rows(fc_llama* m, int B, int T, fc_llama_cache* fill = nullptr) {
+    if (m->prec >= 0) return forward_rows_packed(m, B, T, fill);
     const fc_llama_config& c = m->cfg;
     const int R = B * T, d = c.d_model, F = c.d_ff;
     cudaStream_t st = m->st;
@@ -212,6 +220,67 @@ int forward_rows(fc_llama* m, int B, int T, fc_llama_cache* fill = nullptr) {
     return launch_llama_rmsnorm(m->x, m->out_norm, c.norm_eps, R, d, m->n, nullptr, st);
 }
 
+// FeedForward::forward (llm.rs:417-428) on separate gate and up rows: h = silu(gate) * up.
+__global__ void silu_mul_kernel(const float* __restrict__ g, const float* __restrict__ u, size_t n, float* __restrict__ h) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const float a = g[i];
+        h[i] = __fmul_rn(__fdiv_rn(a, __fadd_rn(1.0f, expf(-a))), u[i]);
+    }
+}
+int launch_silu_mul(const float* g, const float* u, size_t n, float* h, cudaStream_t st) {
+    const size_t want = (n + 255) / 256;
+    silu_mul_kernel<<<(unsigned)std::min<size_t>(std::max<size_t>(want, 1), 148 * 8), 256, 0, st>>>(g, u, n, h);
+    FC_LAUNCHED();
+    return FC_OK;
+}
+
+// One block of the packed model on R rows: LlamaBlock::forward_full / forward_one (llm.rs:451-482) with every
+// Linear an ops::qlinear (ops.rs:316-377). x: residual stream [R][d]; n: scratch [R][d]; qkv: [R][qkv_dim]; att:
+// [R][q_dim]; gu: [R][2 F] (gate rows, then up rows); hid: [R][F]. `attend` runs between the projections and wo.
+template <class Attend>
+int packed_block(fc_llama* m, int l, int R, float* x, float* n, float* qkv, float* att, float* gu, float* hid,
+                 const StepState* state, Attend attend) {
+    const fc_llama_config& c = m->cfg;
+    const LlamaLayerDev& L = m->layers[l];
+    const fc_llama::PackedLayer& P = m->packed[l];
+    const int d = c.d_model, F = c.d_ff;
+    cudaStream_t st = m->st;
+    FC_TRY(launch_llama_rmsnorm(x, L.attn_norm, c.norm_eps, R, d, n, state, st));
+    const float* b = L.qkv_b;
+    FC_TRY(launch_rowq_linear(P.wq, n, b, nullptr, qkv, m->qkv_dim, R, st));
+    FC_TRY(launch_rowq_linear(P.wk, n, b ? b + m->q_dim : nullptr, nullptr, qkv + m->q_dim, m->qkv_dim, R, st));
+    FC_TRY(launch_rowq_linear(P.wv, n, b ? b + m->q_dim + m->kv_dim : nullptr, nullptr, qkv + m->q_dim + m->kv_dim, m->qkv_dim, R, st));
+    FC_TRY(attend());
+    FC_TRY(launch_rowq_linear(P.wo, att, nullptr, x, x, d, R, st));
+    FC_TRY(launch_llama_rmsnorm(x, L.ffn_norm, c.norm_eps, R, d, n, state, st));
+    FC_TRY(launch_rowq_linear(P.gate, n, nullptr, nullptr, gu, F, R, st));
+    FC_TRY(launch_rowq_linear(P.up, n, nullptr, nullptr, gu + (size_t)R * F, F, R, st));
+    FC_TRY(launch_silu_mul(gu, gu + (size_t)R * F, (size_t)R * F, hid, st));
+    return launch_rowq_linear(P.down, hid, nullptr, x, x, d, R, st);
+}
+
+int forward_rows_packed(fc_llama* m, int B, int T, fc_llama_cache* fill) {
+    const fc_llama_config& c = m->cfg;
+    const int R = B * T, d = c.d_model;
+    cudaStream_t st = m->st;
+    FC_CUDA(cudaMemsetAsync(m->err_d, 0, sizeof(int), st));
+    FC_TRY(launch_llama_embed_rows(m->tok, m->ids_d, R, m->x, m->err_d, st));
+    for (int l = 0; l < c.n_layer; ++l) {
+        FC_TRY(packed_block(m, l, R, m->x, m->n, m->qkv, m->att, m->gu, m->hid, nullptr, [&]() -> int {
+            FC_TRY(launch_llama_rope_rows(m->qkv, R, m->qkv_dim, T, c.n_head, c.n_kv_head, m->q_dim, c.head_dim, c.rope_dim,
+                                          c.rope_type == FC_ROPE_NEOX, m->ftab, m->inv_linear, st));
+            if (fill) {
+                const size_t layer_stride = (size_t)c.ctx * m->kv_dim;
+                FC_TRY(launch_llama_store_kv_rows(m->qkv, R, m->qkv_dim, m->q_dim, m->kv_dim, fill->kc + l * layer_stride,
+                                                  fill->vc + l * layer_stride, st));
+            }
+            return launch_attn_prefill_gqa(m->qkv, m->qkv + m->q_dim, m->qkv + m->q_dim + m->kv_dim, B, T, m->qkv_dim, c.n_head,
+                                           c.n_kv_head, c.head_dim, m->q_dim, m->att, st);
+        }));
+    }
+    return launch_llama_rmsnorm(m->x, m->out_norm, c.norm_eps, R, d, m->n, nullptr, st);
+}
+
 int check_ids(const fc_llama* m, const int32_t* ids, size_t n) {
     for (size_t i = 0; i < n; ++i)
         if (ids[i] < 0 || ids[i] >= m->cfg.vocab) return fail(FC_E_DIM, "token %d ≥ vocab_size %d", ids[i], m->cfg.vocab);
@@ -236,7 +305,8 @@ int score_tail(fc_llama* m, int R) {
     const int d = m->cfg.d_model, ldl = m->head.N_pad;
     for (int r0 = 0; r0 < R; r0 += m->head_chunk) {
         const int rows = std::min(m->head_chunk, R - r0);
-        FC_TRY(gemm(m, m->head, m->n + (size_t)r0 * d, nullptr, nullptr, m->logits, rows, ldl));
+        if (m->prec >= 0) FC_TRY(launch_rowq_linear(m->packed_head, m->n + (size_t)r0 * d, nullptr, nullptr, m->logits, ldl, rows, m->st));
+        else FC_TRY(gemm(m, m->head, m->n + (size_t)r0 * d, nullptr, nullptr, m->logits, rows, ldl));
         FC_TRY(launch_llama_score_rows(m->logits, ldl, m->cfg.vocab, m->targets_d + r0, rows, m->lp_d + r0, m->gr_d + r0, m->st));
     }
     return FC_OK;
@@ -288,7 +358,31 @@ int launch_step(fc_llama_cache* s, int with_head) {
     return launch_step_advance_pdl(s->state, st);
 }
 
+// The same step on the packed model, one kernel per operation (not captured: the packed linears keep scratch that grows
+// on demand). The norms read the position word only to stay no-ops once the stream is done.
+int launch_step_packed(fc_llama_cache* s, int with_head) {
+    fc_llama* m = s->m;
+    const fc_llama_config& c = m->cfg;
+    cudaStream_t st = m->st;
+    const size_t layer_stride = (size_t)c.ctx * m->kv_dim;
+    FC_TRY(launch_llama_embed_step(m->tok, c.ctx, s->queue, s->state, s->x, st));
+    for (int l = 0; l < c.n_layer; ++l) {
+        float* kc = s->kc + l * layer_stride;
+        float* vc = s->vc + l * layer_stride;
+        FC_TRY(packed_block(m, l, 1, s->x, s->n, s->qkv, s->att, s->gu, s->hid, nullptr, [&]() -> int {
+            return launch_llama_attn_decode(s->qkv, c.n_head, c.n_kv_head, c.head_dim, c.rope_dim, c.rope_type == FC_ROPE_NEOX, m->ftab,
+                                            m->inv_linear, kc, vc, c.ctx, s->state, s->att, st);
+        }));
+    }
+    if (with_head) {
+        FC_TRY(launch_llama_rmsnorm(s->x, m->out_norm, c.norm_eps, 1, c.d_model, s->n, nullptr, st));
+        FC_TRY(launch_rowq_linear(m->packed_head, s->n, nullptr, nullptr, s->logits, m->head.N_pad, 1, st));
+    }
+    return launch_step_advance_pdl(s->state, st);
+}
+
 int run_step(fc_llama_cache* s, int with_head) {
+    if (s->m->prec >= 0) return launch_step_packed(s, with_head);
     if (!s->graph[with_head]) {
         cudaStream_t st = s->m->st;
         cudaGraph_t g = nullptr;
@@ -357,8 +451,11 @@ int prime_window(fc_llama_cache* s, const int32_t* ids, int n) {
     llama_set_state_kernel<<<1, 1, 0, st>>>(s->state, n, n, n);
     FC_LAUNCHED();
     // logits of the last row: the final norm was applied by forward_rows
-    FC_TRY(launch_gemv_q8_stream(m->head, m->n + (size_t)(n - 1) * c.d_model, nullptr, 0.0f, nullptr, nullptr, EPI_NONE, s->logits,
-                                 s->state, s->status, st));
+    if (m->prec >= 0)
+        FC_TRY(launch_rowq_linear(m->packed_head, m->n + (size_t)(n - 1) * c.d_model, nullptr, nullptr, s->logits, m->head.N_pad, 1, st));
+    else
+        FC_TRY(launch_gemv_q8_stream(m->head, m->n + (size_t)(n - 1) * c.d_model, nullptr, 0.0f, nullptr, nullptr, EPI_NONE, s->logits,
+                                     s->state, s->status, st));
     FC_TRY(check_status(m));
     s->host_pos = n;
     return FC_OK;
@@ -446,10 +543,55 @@ int fc_llama_create(const fc_llama_config* cfg, const fc_llama_weights* w, int d
     return FC_OK;
 }
 
+// A Q8_0 tensor [n_out][n_in] as the reference's importer packs it: decoded (gguf/dequant.rs:37-49), transposed to
+// Ferrum's [n_in][n_out] (gguf/llama.rs:143-144) and packed by QWeight::from_f32 (quant.rs:164-212), then uploaded.
+static int pack_linear(int device, const void* q8, int n_out, int n_in, int kind, fc_rowq** out) {
+    if (!q8) return fail(FC_E_FORMAT, "a required Q8_0 tensor is null");
+    std::vector<float> w((size_t)n_out * n_in), t((size_t)n_out * n_in);
+    FC_TRY(fc_q8_0_dequantize(q8, w.size(), w.data()));
+    for (int o = 0; o < n_out; ++o)
+        for (int i = 0; i < n_in; ++i) t[(size_t)i * n_out + o] = w[(size_t)o * n_in + i];
+    std::vector<float> scales((size_t)n_in);
+    std::vector<uint8_t> q(fc_rowq_packed_len(n_in, n_out, kind));
+    FC_TRY(fc_rowq_from_f32(t.data(), n_in, n_out, kind, scales.data(), q.data()));
+    return fc_rowq_upload(device, q.data(), scales.data(), n_in, n_out, kind, out);
+}
+
+int fc_llama_create_packed(const fc_llama_config* cfg, const fc_llama_weights* w, int device, int kind, fc_llama** out) {
+    if (kind != FC_Q_INT8 && kind != FC_Q_INT4) return fail(FC_E_ARG, "fc_llama_create_packed: kind %d", kind);
+    FC_TRY(fc_llama_create(cfg, w, device, out));
+    fc_llama* m = *out;
+    const fc_llama_config& c = m->cfg;
+    auto build = [&]() -> int {
+        m->packed.resize(c.n_layer);
+        for (int l = 0; l < c.n_layer; ++l) {
+            const fc_llama_layer& h = w->layers[l];
+            fc_llama::PackedLayer& P = m->packed[l];
+            FC_TRY(pack_linear(device, h.wq_q8, m->q_dim, c.d_model, kind, &P.wq));
+            FC_TRY(pack_linear(device, h.wk_q8, m->kv_dim, c.d_model, kind, &P.wk));
+            FC_TRY(pack_linear(device, h.wv_q8, m->kv_dim, c.d_model, kind, &P.wv));
+            FC_TRY(pack_linear(device, h.wo_q8, c.d_model, m->q_dim, kind, &P.wo));
+            FC_TRY(pack_linear(device, h.gate_q8, c.d_ff, c.d_model, kind, &P.gate));
+            FC_TRY(pack_linear(device, h.up_q8, c.d_ff, c.d_model, kind, &P.up));
+            FC_TRY(pack_linear(device, h.down_q8, c.d_model, c.d_ff, kind, &P.down));
+        }
+        // the LM head: `output.weight`, or the token embedding transposed when tied (gguf/llama.rs:304-311)
+        FC_TRY(pack_linear(device, (c.tied || !w->output_q8) ? w->token_embd_q8 : w->output_q8, c.vocab, c.d_model, kind, &m->packed_head));
+        m->prec = kind;
+        return FC_OK;
+    };
+    const int rc = build();
+    if (rc != FC_OK) { fc_llama_free(m); *out = nullptr; }
+    return rc;
+}
+
 void fc_llama_free(fc_llama* m) {
     if (!m) return;
     cudaSetDevice(m->device);
     if (m->st) cudaStreamSynchronize(m->st);
+    for (auto& P : m->packed)
+        for (fc_rowq* q : {P.wq, P.wk, P.wv, P.wo, P.gate, P.up, P.down}) fc_rowq_free(q);
+    fc_rowq_free(m->packed_head);
     m->ws_arena.release();
     m->arena.release();
     if (m->ev0) cudaEventDestroy(m->ev0);
@@ -469,7 +611,8 @@ int fc_llama_forward_tokens(fc_llama* m, const int32_t* ids, int n, float* logit
     FC_TRY(forward_rows(m, 1, n));
     for (int r0 = 0; r0 < n; r0 += m->head_chunk) {
         const int rows = std::min(m->head_chunk, n - r0);
-        FC_TRY(gemm(m, m->head, m->n + (size_t)r0 * d, nullptr, nullptr, m->logits, rows, ldl));
+        if (m->prec >= 0) FC_TRY(launch_rowq_linear(m->packed_head, m->n + (size_t)r0 * d, nullptr, nullptr, m->logits, ldl, rows, m->st));
+        else FC_TRY(gemm(m, m->head, m->n + (size_t)r0 * d, nullptr, nullptr, m->logits, rows, ldl));
         FC_CUDA(cudaMemcpy2DAsync(logits + (size_t)r0 * V, (size_t)V * 4, m->logits, (size_t)ldl * 4, (size_t)V * 4, rows,
                                   cudaMemcpyDeviceToHost, m->st));
     }

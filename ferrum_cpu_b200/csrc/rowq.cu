@@ -46,6 +46,8 @@ struct RowqArgs {
     const uint8_t* q; const float* scales; int K, N, ld, half;
     const float* x; const float* bias; float* y; float* partial;
     int M, kper, KS;
+    int ldy;                       // floats between output rows
+    const float* residual;         // [M][ldy] or null: y = residual + (bias + sum); may be y itself
 };
 
 template <int W> struct Words;
@@ -132,23 +134,29 @@ __global__ void __launch_bounds__(TPB) rowq_linear_kernel(RowqArgs a) {
             const int j = c < NB ? b0 + c : a.half + b0 + (c - NB);
             const bool live = INT4 ? (c < NB ? j < a.half : j < a.N) : j < a.N;
             if (!live) continue;
-            if (a.KS == 1) a.y[(size_t)(m0 + m) * a.N + j] = a.bias[j] + acc[m][c];
+            if (a.KS == 1) {
+                const float v = (a.bias ? a.bias[j] : 0.0f) + acc[m][c];
+                const size_t at = (size_t)(m0 + m) * a.ldy + j;
+                a.y[at] = a.residual ? a.residual[at] + v : v;
+            }
             else a.partial[((size_t)blockIdx.y * a.M + m0 + m) * a.N + j] = acc[m][c];
         }
     }
 }
 
 // y = bias + partial[0] + partial[1] + ... in slice order.
-__global__ void rowq_reduce_kernel(const float* __restrict__ partial, const float* __restrict__ bias, float* __restrict__ y,
-                                   int M, int N, int KS) {
+__global__ void rowq_reduce_kernel(const float* __restrict__ partial, const float* __restrict__ bias, const float* residual, float* y,
+                                   int M, int N, int KS, int ldy) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (size_t)M * N) return;
-    float v = bias[i % N];
+    const size_t m = i / N, j = i - m * N;
+    float v = bias ? bias[j] : 0.0f;
     for (int s = 0; s < KS; ++s) v += partial[(size_t)s * M * N + i];
-    y[i] = v;
+    const size_t at = m * ldy + j;
+    y[at] = residual ? residual[at] + v : v;
 }
 
-int rowq_launch(fc_rowq* w, const float* x, const float* bias, float* y, int M, cudaStream_t st) {
+int rowq_launch(fc_rowq* w, const float* x, const float* bias, const float* residual, float* y, int ldy, int M, cudaStream_t st) {
     static int sms[64] = {};
     int dev = 0;
     FC_CUDA(cudaGetDevice(&dev));
@@ -179,6 +187,7 @@ int rowq_launch(fc_rowq* w, const float* x, const float* bias, float* y, int M, 
     RowqArgs a;
     a.q = w->q; a.scales = w->scales; a.K = w->rows; a.N = w->cols; a.ld = w->ld; a.half = (w->cols + 1) / 2;
     a.x = x; a.bias = bias; a.y = y; a.partial = w->partial; a.M = M; a.kper = kper; a.KS = KS;
+    a.ldy = ldy; a.residual = residual;
     const dim3 grid(bx, KS, mz);
     const bool i4 = w->kind == FC_Q_INT4;
     const size_t smem = ((size_t)std::min(M, mtt) * kper + (KL > 1 ? (size_t)TPB * (i4 ? 32 : 16) : 0)) * sizeof(float);
@@ -188,13 +197,21 @@ int rowq_launch(fc_rowq* w, const float* x, const float* bias, float* y, int M, 
     FC_LAUNCHED();
     if (KS > 1) {
         const size_t n = (size_t)M * w->cols;
-        rowq_reduce_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(w->partial, bias, y, M, w->cols, KS);
+        rowq_reduce_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(w->partial, bias, residual, y, M, w->cols, KS, ldy);
         FC_LAUNCHED();
     }
     return FC_OK;
 }
 
 }  // namespace
+
+// y[M][ldy] (columns 0 .. cols-1) = [residual +] bias + x · W for a packed matrix; bias and residual may be null.
+int launch_rowq_linear(fc_rowq* w, const float* x, const float* bias, const float* residual, float* y, int ldy, int M, cudaStream_t st) {
+    if (ldy < w->cols) return fail(FC_E_SHAPE, "rowq linear: row stride %d below %d columns", ldy, w->cols);
+    return rowq_launch(w, x, bias, residual, y, ldy, M, st);
+}
+int rowq_in(const fc_rowq* w) { return w->rows; }
+int rowq_out(const fc_rowq* w) { return w->cols; }
 }  // namespace fc
 
 using namespace fc;
@@ -240,7 +257,7 @@ int fc_rowq_linear_dev(const fc_rowq* w, const float* x_dev, const float* bias_d
         return fail(FC_E_ARG, "fc_rowq_linear_dev: x_dev, y_dev and bias_dev must be 16-byte aligned");
     if (M <= 0) return fail(FC_E_SHAPE, "fc_rowq_linear_dev: M = %d", M);
     FC_CUDA(cudaSetDevice(w->device));
-    return rowq_launch(const_cast<fc_rowq*>(w), x_dev, bias_dev, y_dev, M, (cudaStream_t)stream);
+    return rowq_launch(const_cast<fc_rowq*>(w), x_dev, bias_dev, nullptr, y_dev, w->cols, M, (cudaStream_t)stream);
 }
 
 int fc_rowq_linear(const fc_rowq* w, const float* x, const float* bias, float* y, int M) {
@@ -257,7 +274,7 @@ int fc_rowq_linear(const fc_rowq* w, const float* x, const float* bias, float* y
     };
     copy(xd, x, (size_t)M * w->rows * 4, cudaMemcpyHostToDevice);
     copy(bd, bias, (size_t)w->cols * 4, cudaMemcpyHostToDevice);
-    if (rc == FC_OK) rc = rowq_launch(const_cast<fc_rowq*>(w), xd, bd, yd, M, nullptr);
+    if (rc == FC_OK) rc = rowq_launch(const_cast<fc_rowq*>(w), xd, bd, nullptr, yd, w->cols, M, nullptr);
     if (rc == FC_OK && cudaDeviceSynchronize() != cudaSuccess) rc = fail(FC_E_CUDA, "fc_rowq_linear: the kernel failed");
     copy(y, yd, (size_t)M * w->cols * 4, cudaMemcpyDeviceToHost);
     a.release();

@@ -53,19 +53,24 @@ class CudaLlamaCache:
 class CudaLlama:
     """LlamaModel on one GPU."""
 
-    def __init__(self, config, weights, device=0):
+    def __init__(self, config, weights, device=0, prec=None):
         self._h = C.c_void_p()
         self._caches = []
         self.config = config
-        check(_lib.lib().fc_llama_create(C.byref(config), C.byref(weights), device, C.byref(self._h)))
+        if prec is None:
+            check(_lib.lib().fc_llama_create(C.byref(config), C.byref(weights), device, C.byref(self._h)))
+        else:
+            check(_lib.lib().fc_llama_create_packed(C.byref(config), C.byref(weights), device, int(prec), C.byref(self._h)))
 
     @classmethod
-    def from_synth(cls, synth, device=0):
-        return cls(synth.config, synth.weights, device)
+    def from_synth(cls, synth, device=0, prec=None):
+        """prec: None runs the Q8_0 matrices as stored; 0 / 1 packs every Linear to per-row int8 / int4 as the
+        reference's importer does (Gguf::load_llama(kind), gguf/llama.rs:164-171)."""
+        return cls(synth.config, synth.weights, device, prec=prec)
 
     @classmethod
-    def from_gguf(cls, path, device=0, math_mode=_lib.FC_MATH_FP32, ctx_cap=0):
-        """Gguf::load_llama (gguf/llama.rs:164-339) for llama / qwen2 files with Q8_0 projections."""
+    def from_gguf(cls, path, device=0, math_mode=_lib.FC_MATH_FP32, ctx_cap=0, prec=None):
+        """Gguf::load_llama (gguf/llama.rs:164-339) for llama / qwen2 files."""
         self = cls.__new__(cls)
         self._h = C.c_void_p()
         self._caches = []
@@ -73,7 +78,10 @@ class CudaLlama:
         if 0 < ctx_cap < self.config.ctx:
             self.config.ctx = ctx_cap
         self.config.math_mode = math_mode
-        check(_lib.lib().fc_llama_load_gguf(str(path).encode(), device, math_mode, ctx_cap, C.byref(self._h)))
+        if prec is None:
+            check(_lib.lib().fc_llama_load_gguf(str(path).encode(), device, math_mode, ctx_cap, C.byref(self._h)))
+        else:
+            check(_lib.lib().fc_llama_load_gguf_packed(str(path).encode(), device, ctx_cap, int(prec), C.byref(self._h)))
         return self
 
     def close(self):

@@ -378,6 +378,13 @@ typedef struct fc_llama_cache fc_llama_cache; /* LlamaCache: per-layer KV rows +
 /* Validates as Attention::new (llm.rs:243-252: n_head % n_kv_head, rope_dim even and <=
  * head_dim) and RopeScaling::check (llm.rs:135-150: factors finite and > 0): FC_E_DIM. */
 int fc_llama_create(const fc_llama_config* cfg, const fc_llama_weights* w, int device, fc_llama** out);
+/* The same model with every Linear packed the way the reference's importer packs it (Gguf::load_llama(kind),
+ * gguf/llama.rs:13-27,164-171): each Q8_0 matrix is decoded, transposed to [in][out] and packed by
+ * QWeight::from_f32 (quant.rs:164-212) to per-input-row int8 (FC_Q_INT8) or int4 (FC_Q_INT4) - the LM head too, the
+ * tied one from the transposed embedding (gguf/llama.rs:304-311) - and every forward runs ops::qlinear
+ * (ops.rs:316-377) on them; the embedding table stays as stored. All fc_llama_* calls work on the result; the decode
+ * step runs one kernel per operation. */
+int fc_llama_create_packed(const fc_llama_config* cfg, const fc_llama_weights* w, int device, int kind, fc_llama** out);
 void fc_llama_free(fc_llama* m);
 /* Gguf::load_llama (gguf/llama.rs:164-339) for `llama` and `qwen2` files whose projections are
  * Q8_0 (they stay packed) and whose norms are F32: the same metadata keys, defaults and refusals
@@ -385,6 +392,9 @@ void fc_llama_free(fc_llama* m);
  * split halves, llama interleaved pairs. ctx_cap > 0 lowers the context (and with it the KV
  * caches) below the file's context_length. fc_llama_gguf_probe validates without a GPU. */
 int fc_llama_load_gguf(const char* path, int device, int math_mode, int ctx_cap, fc_llama** out);
+/* Gguf::load_llama(kind) (gguf/llama.rs:164-171) from the file: fc_llama_load_gguf followed by the packing of
+ * fc_llama_create_packed. */
+int fc_llama_load_gguf_packed(const char* path, int device, int ctx_cap, int kind, fc_llama** out);
 int fc_llama_gguf_probe(const char* path, fc_llama_config* out);
 /* LlamaModel::forward_tokens (llm.rs:622-635): n ids -> logits [n][vocab] (host buffer). */
 int fc_llama_forward_tokens(fc_llama* m, const int32_t* ids, int n, float* logits);

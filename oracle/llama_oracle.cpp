@@ -27,6 +27,9 @@ void fo_linear(const float* x, const float* w_kn, const float* bias, int m, int 
 void fo_q8_0_expand_kn(const void* wq, int n, int k, float* w_kn);
 void fo_q8_0_decode(const uint8_t* raw, size_t n, float* out);
 int fo_argmax_first(const float* x, int n);
+size_t fo_rowq_packed_len(int rows, int cols, int kind);
+void fo_rowq_from_f32(const float* data, int rows, int cols, int kind, float* scales, uint8_t* q);
+void fo_rowq_linear(const float* x, const uint8_t* q, const float* scales, int kind, const float* bias, int m, int k, int n, float* y);
 int fo_sample_with_params(const float* logits, int n, float temperature, int top_k, float top_p, float rep_penalty,
                           const int32_t* recent, int n_recent, uint64_t* state);
 }
@@ -67,7 +70,21 @@ struct Lin {                     // Linear (layer/linear.rs): weight [in][out], 
         b.assign(out, 0.0f);
         if (bias) std::memcpy(b.data(), bias, (size_t)out * 4);
     }
-    void forward(const float* x, int rows, float* y, int threads) const { fo_linear(x, w.data(), b.data(), rows, in, out, y, threads); }
+    // Linear::quantized (layer/linear.rs:98-130) as gguf/llama.rs:13-27 builds it: the weight packed by
+    // QWeight::from_f32 (quant.rs:164-212), forward = ops::qlinear (layer/linear.rs:191-194, ops.rs:316-377)
+    int kind = -1;
+    std::vector<uint8_t> q;
+    std::vector<float> scales;
+    void pack(int k) {
+        kind = k;
+        q.assign(fo_rowq_packed_len(in, out, k), 0);
+        scales.assign(in, 0.0f);
+        fo_rowq_from_f32(w.data(), in, out, k, scales.data(), q.data());
+    }
+    void forward(const float* x, int rows, float* y, int threads) const {
+        if (kind >= 0) fo_rowq_linear(x, q.data(), scales.data(), kind, b.data(), rows, in, out, y);
+        else fo_linear(x, w.data(), b.data(), rows, in, out, y, threads);
+    }
 };
 
 // llm.rs:57-64 RmsNorm::forward_row.
@@ -320,6 +337,14 @@ void* fo_llama_create(const void* cfg, const void* weights, int threads) {
     // a tied head is the transpose of the embedding (llm.rs:580-585)
     m->head.load(c.tied || !w.output ? w.token_embd : w.output, nullptr, c.vocab, d);
     return m;
+}
+// Gguf::load_llama(kind) (gguf/llama.rs:164-171): every Linear of the model, the LM head included, packed to int8 (0)
+// or int4 (1); the embedding table stays f32.
+void fo_llama_pack(void* mp, int kind) {
+    Model& m = *(Model*)mp;
+    for (Layer& L : m.layers)
+        for (Lin* l : {&L.wq, &L.wk, &L.wv, &L.wo, &L.gate, &L.up, &L.down}) l->pack(kind);
+    m.head.pack(kind);
 }
 void fo_llama_free(void* m) { delete (Model*)m; }
 

@@ -66,6 +66,8 @@ def lib():
         L.fo_llama_log_prob.restype, L.fo_llama_log_prob.argtypes = C.c_double, [C.c_void_p, C.c_int, C.c_int]
         L.fo_llama_create.restype, L.fo_llama_create.argtypes = C.c_void_p, [C.c_void_p, C.c_void_p, C.c_int]
         L.fo_llama_free.argtypes = [C.c_void_p]
+        L.fo_llama_pack.argtypes = [C.c_void_p, C.c_int]
+        L.fo_llama_pack.restype = None
         L.fo_llama_forward_tokens.restype = C.c_int
         L.fo_llama_forward_tokens.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
         L.fo_llama_cache_create.restype, L.fo_llama_cache_create.argtypes = C.c_void_p, [C.c_void_p]
@@ -296,10 +298,13 @@ def llama_log_prob(logits, target):
 class OracleLlama:
     """The restated LlamaModel built from the same fc_llama_config / fc_llama_weights structs."""
 
-    def __init__(self, synth_llama, threads=1):
+    def __init__(self, synth_llama, threads=1, prec=None):
+        """prec 0 / 1: every Linear packed to per-row int8 / int4 (Gguf::load_llama(kind), gguf/llama.rs:164-171)."""
         self.sm = synth_llama
         self.V = synth_llama.dims["vocab"]
         self._m = lib().fo_llama_create(C.addressof(synth_llama.config), C.addressof(synth_llama.weights), threads)
+        if self._m and prec is not None:
+            lib().fo_llama_pack(self._m, int(prec))
         self._c = lib().fo_llama_cache_create(self._m) if self._m else None
 
     @property
