@@ -64,6 +64,7 @@ struct fc_llama_cache {
     int host_pos = 0;
     cudaGraphExec_t graph[2] = {nullptr, nullptr};   // [0]: step without the head, [1]: with it
     int graph_nodes[2] = {0, 0};
+    bool packed_warm[2] = {false, false};   // packed model: the uncaptured first step of each kind has run
     unsigned long long* rng_d = nullptr;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     float last_decode_ms = 0.0f;
@@ -358,8 +359,8 @@ int launch_step(fc_llama_cache* s, int with_head) {
     return launch_step_advance_pdl(s->state, st);
 }
 
-// The same step on the packed model, one kernel per operation (not captured: the packed linears keep scratch that grows
-// on demand). The norms read the position word only to stay no-ops once the stream is done.
+// The same step on the packed model, one kernel per operation. The first step of a cache runs uncaptured, so that the
+// packed linears' single-row scratch exists before the step is captured.
 int launch_step_packed(fc_llama_cache* s, int with_head) {
     fc_llama* m = s->m;
     const fc_llama_config& c = m->cfg;
@@ -382,13 +383,17 @@ int launch_step_packed(fc_llama_cache* s, int with_head) {
 }
 
 int run_step(fc_llama_cache* s, int with_head) {
-    if (s->m->prec >= 0) return launch_step_packed(s, with_head);
+    const bool packed = s->m->prec >= 0;
+    if (packed && !s->packed_warm[with_head]) {
+        s->packed_warm[with_head] = true;
+        return launch_step_packed(s, with_head);
+    }
     if (!s->graph[with_head]) {
         cudaStream_t st = s->m->st;
         cudaGraph_t g = nullptr;
         const int64_t before = g_launches;
         FC_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
-        const int rc = launch_step(s, with_head);
+        const int rc = packed ? launch_step_packed(s, with_head) : launch_step(s, with_head);
         const cudaError_t e = cudaStreamEndCapture(st, &g);
         s->graph_nodes[with_head] = (int)(g_launches - before);
         g_launches = before;

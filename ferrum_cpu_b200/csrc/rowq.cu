@@ -22,10 +22,13 @@ struct fc_rowq {
     fc::Arena arena;
     uint8_t* q = nullptr;
     float* scales = nullptr;
-    // scratch: slice partials, grown on demand
-    fc::Arena ws;
+    // scratch: slice partials, grown on demand. A single activation row has a buffer of its own, whose size never
+    // changes once it exists: a captured decode step keeps pointing at it whatever the batched calls do to the other.
+    fc::Arena ws, ws1;
     float* partial = nullptr;
     size_t partial_floats = 0;
+    float* partial1 = nullptr;
+    size_t partial1_floats = 0;
 };
 
 namespace fc {
@@ -174,19 +177,27 @@ int rowq_launch(fc_rowq* w, const float* x, const float* bias, const float* resi
     const int kper_max = 32768 / (4 * std::min(M, mtt));
     if (kper > kper_max) kper = kper_max;
     KS = (w->rows + kper - 1) / kper;
+    float* scratch = nullptr;
     if (KS > 1) {
         const size_t need = (size_t)KS * M * w->cols;
-        if (need > w->partial_floats) {
+        fc::Arena& arena = M == 1 ? w->ws1 : w->ws;
+        float*& buf = M == 1 ? w->partial1 : w->partial;
+        size_t& have = M == 1 ? w->partial1_floats : w->partial_floats;
+        if (need > have) {
+            cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+            FC_CUDA(cudaStreamIsCapturing(st, &cap));
+            if (cap != cudaStreamCaptureStatusNone) return fail(FC_E_CUDA, "rowq linear: scratch must exist before a stream capture");
             FC_CUDA(cudaStreamSynchronize(st));
-            w->ws.release();
-            w->partial = nullptr; w->partial_floats = 0;
-            FC_TRY(w->ws.alloc_n(&w->partial, need));
-            w->partial_floats = need;
+            arena.release();
+            buf = nullptr; have = 0;
+            FC_TRY(arena.alloc_n(&buf, need));
+            have = need;
         }
+        scratch = buf;
     }
     RowqArgs a;
     a.q = w->q; a.scales = w->scales; a.K = w->rows; a.N = w->cols; a.ld = w->ld; a.half = (w->cols + 1) / 2;
-    a.x = x; a.bias = bias; a.y = y; a.partial = w->partial; a.M = M; a.kper = kper; a.KS = KS;
+    a.x = x; a.bias = bias; a.y = y; a.partial = scratch; a.M = M; a.kper = kper; a.KS = KS;
     a.ldy = ldy; a.residual = residual;
     const dim3 grid(bx, KS, mz);
     const bool i4 = w->kind == FC_Q_INT4;
@@ -197,7 +208,7 @@ int rowq_launch(fc_rowq* w, const float* x, const float* bias, const float* resi
     FC_LAUNCHED();
     if (KS > 1) {
         const size_t n = (size_t)M * w->cols;
-        rowq_reduce_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(w->partial, bias, residual, y, M, w->cols, KS, ldy);
+        rowq_reduce_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(scratch, bias, residual, y, M, w->cols, KS, ldy);
         FC_LAUNCHED();
     }
     return FC_OK;
@@ -247,6 +258,7 @@ void fc_rowq_free(fc_rowq* w) {
     cudaSetDevice(w->device);
     cudaDeviceSynchronize();
     w->ws.release();
+    w->ws1.release();
     w->arena.release();
     delete w;
 }
