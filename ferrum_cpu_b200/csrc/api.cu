@@ -133,8 +133,10 @@ struct BatchCtx {
     float **kcs = nullptr, **vcs = nullptr;
     int** queues = nullptr;
     fc::StepState** states = nullptr;
-    cudaGraphExec_t graph = nullptr;   // one step, captured for (graph_S, graph_eos, out_cap, graph_group)
-    int graph_S = 0, graph_eos = 0, graph_cap = 0, graph_nodes = 0, graph_group = 0;
+    // one step, and four steps in a row (no gap between graph launches inside them), captured for
+    // (graph_S, graph_eos, out_cap, graph_group)
+    cudaGraphExec_t graph = nullptr, graph4 = nullptr;
+    int graph_S = 0, graph_eos = 0, graph_cap = 0, graph_nodes = 0, graph4_nodes = 0, graph_group = 0;
     // the step graph runs groups of streams as parallel branches: branch g > 0 is captured on side[g - 1]
     std::vector<cudaStream_t> side;
     std::vector<cudaEvent_t> side_done;
@@ -730,6 +732,7 @@ void fc_model_free(fc_model* m) {
     m->arena.release();
     m->ws_arena.release();
     if (m->batch.graph) cudaGraphExecDestroy(m->batch.graph);
+    if (m->batch.graph4) cudaGraphExecDestroy(m->batch.graph4);
     for (cudaStream_t t : m->batch.side) cudaStreamDestroy(t);
     for (cudaEvent_t e : m->batch.side_done) cudaEventDestroy(e);
     if (m->batch.fork) cudaEventDestroy(m->batch.fork);
@@ -1411,6 +1414,8 @@ static int batch_ensure(fc_model* m, int S, int out_cap) {
     if (S <= b.cap && out_cap <= b.out_cap) return FC_OK;
     FC_CUDA(cudaStreamSynchronize(m->st));
     if (b.graph) { cudaGraphExecDestroy(b.graph); b.graph = nullptr; }
+    if (b.graph4) { cudaGraphExecDestroy(b.graph4); b.graph4 = nullptr; }
+    b.graph_S = 0;
     b.arena.release();
     b.cap = b.out_cap = 0;
     const fc_config& c = m->cfg;
@@ -1593,27 +1598,34 @@ static int batch_launch_groups(fc_model* m, int S, int eos, int group) {
 
 // The step is launch-bound (7 small kernels per block): it is captured once into a CUDA graph and
 // replayed; position and tokens are read from device memory, so no node changes between steps.
-static int batch_run_step(fc_model* m, int S, int eos) {
+// n_steps: 1 or 4 consecutive steps in one launch.
+static int batch_run_steps(fc_model* m, int S, int eos, int n_steps) {
     BatchCtx& b = m->batch;
     const int group = batch_group_size(S);
-    if (!b.graph || b.graph_S != S || b.graph_eos != eos || b.graph_cap != b.out_cap || b.graph_group != group) {
+    if (b.graph_S != S || b.graph_eos != eos || b.graph_cap != b.out_cap || b.graph_group != group) {
         if (b.graph) { cudaGraphExecDestroy(b.graph); b.graph = nullptr; }
+        if (b.graph4) { cudaGraphExecDestroy(b.graph4); b.graph4 = nullptr; }
+        b.graph_S = S; b.graph_eos = eos; b.graph_cap = b.out_cap; b.graph_group = group;
+    }
+    cudaGraphExec_t& exec = n_steps == 4 ? b.graph4 : b.graph;
+    int& nodes = n_steps == 4 ? b.graph4_nodes : b.graph_nodes;
+    if (!exec) {
         cudaGraph_t g = nullptr;
         const int64_t before = g_launches;
         FC_CUDA(cudaStreamBeginCapture(m->st, cudaStreamCaptureModeThreadLocal));
-        const int rc = batch_launch_groups(m, S, eos, group);
+        int rc = FC_OK;
+        for (int k = 0; k < n_steps && rc == FC_OK; ++k) rc = batch_launch_groups(m, S, eos, group);
         const cudaError_t e = cudaStreamEndCapture(m->st, &g);
-        b.graph_nodes = (int)(g_launches - before);
+        nodes = (int)(g_launches - before);
         g_launches = before;
         if (rc != FC_OK) { if (g) cudaGraphDestroy(g); return rc; }
         FC_CUDA(e);
-        const cudaError_t ei = cudaGraphInstantiate(&b.graph, g, 0);
+        const cudaError_t ei = cudaGraphInstantiate(&exec, g, 0);
         cudaGraphDestroy(g);
         FC_CUDA(ei);
-        b.graph_S = S; b.graph_eos = eos; b.graph_cap = b.out_cap; b.graph_group = group;
     }
-    FC_CUDA(cudaGraphLaunch(b.graph, m->st));
-    g_launches += b.graph_nodes;
+    FC_CUDA(cudaGraphLaunch(exec, m->st));
+    g_launches += nodes;
     return FC_OK;
 }
 
@@ -1696,7 +1708,10 @@ int fc_decode_batch(fc_model* m, int n_streams, const int32_t* prompts, int prom
         FC_CUDA(cudaEventRecord(m->ev_prime, st));
         std::vector<int> done(S, 0);
         for (int i = 1; i < max_new; ++i) {        // step i feeds token i and picks token i + 1
-            FC_TRY(batch_run_step(m, S, eos));
+            // four steps per launch while they fit (steps 1-4, 5-8, ...: a chunk ends where the eos check falls)
+            const int n_steps = (i % 4 == 1 && i + 3 < max_new) ? 4 : 1;
+            FC_TRY(batch_run_steps(m, S, eos, n_steps));
+            i += n_steps - 1;
             if (eos >= 0 && (i % 16 == 0)) {          // eos can only be noticed on the host at a synchronisation point
                 FC_CUDA(cudaMemcpyAsync(done.data(), b.done, S * sizeof(int), cudaMemcpyDeviceToHost, st));
                 FC_CUDA(cudaStreamSynchronize(st));

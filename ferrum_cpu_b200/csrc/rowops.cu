@@ -169,7 +169,66 @@ __global__ void layernorm_planes_kernel(const float* __restrict__ x, const float
     }
 }
 
+// The same for rows of up to 1024 columns (a multiple of 128): a warp per row, the row in registers as 16-byte loads,
+// the two sums by shuffles (no block-wide synchronisation), the planes written 8 bytes per lane. Eight rows per CTA.
+template <int NV>
+__global__ void __launch_bounds__(256) layernorm_planes_warp_kernel(const float* __restrict__ x, const float* __restrict__ g,
+                                                                    const float* __restrict__ b, int rows, int d,
+                                                                    __nv_bfloat16* __restrict__ hi, __nv_bfloat16* __restrict__ lo) {
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int nv = d >> 7;                                  // 16-byte chunks per lane
+    const float4* xr = (const float4*)(x + (size_t)row * d);
+    float4 v[NV];
+    float s = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        v[i] = i < nv ? xr[lane + 32 * i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    const float mean = s / (float)d;
+    float q = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+        if (i < nv) {
+            const float a = v[i].x - mean, c = v[i].y - mean, e = v[i].z - mean, f = v[i].w - mean;
+            q += (a * a + c * c) + (e * e + f * f);
+        }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) q += __shfl_xor_sync(0xffffffffu, q, o);
+    const float sd = sqrtf(q / (float)d + 1e-5f);
+    const float4* g4 = (const float4*)g;
+    const float4* b4 = (const float4*)b;
+    uint2* h2 = (uint2*)(hi + (size_t)row * d);
+    uint2* l2 = (uint2*)(lo + (size_t)row * d);
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+        if (i < nv) {
+            const float4 gg = __ldg(g4 + lane + 32 * i), bb = __ldg(b4 + lane + 32 * i);
+            const float y[4] = {((v[i].x - mean) / sd) * gg.x + bb.x, ((v[i].y - mean) / sd) * gg.y + bb.y,
+                                ((v[i].z - mean) / sd) * gg.z + bb.z, ((v[i].w - mean) / sd) * gg.w + bb.w};
+            __nv_bfloat16 hh[4], ll[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                hh[k] = __float2bfloat16_rn(y[k]);
+                ll[k] = __float2bfloat16_rn(y[k] - __bfloat162float(hh[k]));
+            }
+            h2[lane + 32 * i] = *(const uint2*)hh;
+            l2[lane + 32 * i] = *(const uint2*)ll;
+        }
+}
+
 int launch_layernorm_planes(const float* x, const float* g, const float* b, int rows, int d, void* hi, void* lo, cudaStream_t st) {
+    if (d % 128 == 0 && d <= 1024 && aligned16(x) && aligned16(g) && aligned16(b) && aligned16(hi) && aligned16(lo)) {
+        const int blocks = (rows + 7) / 8;
+        if (d <= 512) layernorm_planes_warp_kernel<4><<<blocks, 256, 0, st>>>(x, g, b, rows, d, (__nv_bfloat16*)hi, (__nv_bfloat16*)lo);
+        else layernorm_planes_warp_kernel<8><<<blocks, 256, 0, st>>>(x, g, b, rows, d, (__nv_bfloat16*)hi, (__nv_bfloat16*)lo);
+        FC_LAUNCHED();
+        return FC_OK;
+    }
     const int threads = 256;
     const int per = (d + threads - 1) / threads;
     if (per <= 4) layernorm_planes_kernel<4><<<rows, threads, 0, st>>>(x, g, b, d, (__nv_bfloat16*)hi, (__nv_bfloat16*)lo);
