@@ -18,9 +18,10 @@
 //   * the weights are read from a fragment-major copy made at upload: per (16 rows, 32-wide block)
 //     512 contiguous bytes in lane order plus 32 bytes of scales — Q8_0's own 34 B per 32 weights,
 //     every warp load a full 512-byte line.
-// A CTA owns 32 output rows; its warps split K and add their partial sums through shared memory
+// A CTA owns 16 or 32 output rows; its warps split K and add their partial sums through shared memory
 // in warp order (deterministic). Attention reads each stream's f32 cache rows once; the greedy
-// pick is token_stream.rs:134 + sampling.rs:96-104 per stream.
+// pick is token_stream.rs:134 + sampling.rs:96-104 per stream. More than 16 streams run as groups of 16
+// whose kernel chains are parallel branches of the step's CUDA graph (the caller's side).
 //
 // Bound: HBM. Per step: every Q8_0 matrix once + per stream the f32 K/V rows of positions 0..pos.
 #include <cuda_fp16.h>

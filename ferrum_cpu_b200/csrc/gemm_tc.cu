@@ -10,16 +10,17 @@
 // Persistent kernel, one CTA per SM, 256 x 128 output tiles (two 128-row MMA tiles that share
 // one dequantised weight tile) taken round-robin, N fastest, so that the CTAs running together
 // share a few row panels of X in L2:
-//   warp 12     TMA producer: the two bf16 planes of the X tile (256 rows x 64 k, 128-byte
+//   warp 16     TMA producer: the two bf16 planes of the X tile (256 rows x 64 k, 128-byte
 //               swizzle) into the stage's A buffers, completing on the stage's mbarrier;
-//   warps 4-11  dequantise the 128 x 64 Q8_0 weight tile: w = d * q exactly as
+//   warps 8-15  dequantise the 128 x 64 Q8_0 weight tile: w = d * q exactly as
 //               gguf::dequant_q8_0 (ferrum_core/src/gguf/dequant.rs:37-49), split into bf16
 //               hi/lo and stored in the same swizzled K-major layout the tensor core reads;
-//   warp 13     allocates all 512 TMEM columns (two buffers of two accumulators) and issues tcgen05.mma from one
+//   warp 17     allocates all 512 TMEM columns (two buffers of two accumulators) and issues tcgen05.mma from one
 //               thread; tcgen05.commit frees the stage and finally publishes the accumulator;
-//   warps 0-3   epilogue of the previous tile while the next one is being multiplied:
-//               tcgen05.ld their 32 accumulator lanes, bias / GELU / residual, then either f32
-//               rows or the bf16 hi/lo planes the next GEMM consumes.
+//   warps 0-7   epilogue of the previous tile while the next one is being multiplied, four warps (one per 32
+//               TMEM lanes) for each 128-row half: tcgen05.ld their accumulator lanes, bias / GELU /
+//               residual, then either f32 rows or the bf16 hi/lo planes the next GEMM consumes. (With four
+//               warps for the whole tile the epilogue outlasted the MMAs of the next tile and held its buffer.)
 // Every mbarrier wait is bounded by a cycle budget; when it runs out the kernel raises a
 // status word, releases its TMEM and returns.
 //
