@@ -228,6 +228,64 @@ impl Drop for MirrorFlag {
     }
 }
 
+/// Weight precision of an imported decoder, as `Gguf::load_llama(kind)` / `load_llama_prec(None)` choose it
+/// (gguf/llama.rs:164-176): the file's own blocks brought to Q8_0 (the fast path of this crate), or every Linear
+/// re-packed to a per-input-row int8 / int4 `QWeight` and run by `ops::qlinear`, which is what `ferrum_core` computes.
+#[derive(Clone, Copy, Debug, PartialEq, Eq)]
+pub enum LlamaWeights { AsStored, PackedInt8, PackedInt4 }
+
+/// A llama / qwen2 architecture model resident on one GPU: `LlamaModel` of llm.rs:549-565.
+pub struct CudaLlama {
+    raw: *mut ffi::fc_llama,
+    vocab: usize,
+    _not_send: PhantomData<*mut ()>,
+}
+
+impl CudaLlama {
+    /// `Gguf::open(path)?.load_llama(..)` (gguf/llama.rs:164-339) straight from the file to the device.
+    pub fn from_gguf(path: &str, device: usize, math: MathMode, ctx_cap: usize, weights: LlamaWeights) -> Result<Self> {
+        let c_path = CString::new(path).map_err(|_| InferError::Format("path holds a NUL byte".into()))?;
+        let mut cfg: ffi::fc_llama_config = unsafe { std::mem::zeroed() };
+        status(unsafe { ffi::fc_llama_gguf_probe(c_path.as_ptr(), &mut cfg) })?;
+        let mut raw = ptr::null_mut();
+        let (dev, cap) = (device as c_int, ctx_cap as c_int);
+        status(match weights {
+            LlamaWeights::AsStored => unsafe { ffi::fc_llama_load_gguf(c_path.as_ptr(), dev, math as c_int, cap, &mut raw) },
+            LlamaWeights::PackedInt8 => unsafe { ffi::fc_llama_load_gguf_packed(c_path.as_ptr(), dev, cap, ffi::FC_Q_INT8, &mut raw) },
+            LlamaWeights::PackedInt4 => unsafe { ffi::fc_llama_load_gguf_packed(c_path.as_ptr(), dev, cap, ffi::FC_Q_INT4, &mut raw) },
+        })?;
+        Ok(Self { raw, vocab: cfg.vocab as usize, _not_send: PhantomData })
+    }
+
+    /// `LlamaModel::forward_tokens` (llm.rs:622-635): logits `[ids.len()][vocab]`, row-major.
+    pub fn forward_tokens(&self, ids: &[usize]) -> Result<Vec<f32>> {
+        let ids = ids32(ids);
+        let mut logits = vec![0f32; ids.len() * self.vocab];
+        status(unsafe { ffi::fc_llama_forward_tokens(self.raw, ids.as_ptr(), ids.len() as c_int, logits.as_mut_ptr()) })?;
+        Ok(logits)
+    }
+
+    /// `LlamaModel::score_from` (llm_score.rs:76-96): the log-probability of `ids[from..]` given what precedes it,
+    /// in windows of `window` tokens.
+    pub fn score_from(&self, ids: &[usize], from: usize, window: usize) -> Result<Score> {
+        let ids = ids32(ids);
+        let mut sc: ffi::fc_score = unsafe { std::mem::zeroed() };
+        status(unsafe {
+            ffi::fc_llama_score_from(self.raw, ids.as_ptr(), ids.len() as c_int, from as c_int, window as c_int, &mut sc,
+                                     ptr::null_mut(), ptr::null_mut())
+        })?;
+        Ok(Score { logprob: sc.logprob, n_tokens: sc.n_tokens as usize, greedy: sc.greedy != 0 })
+    }
+
+    /// `LlamaModel::score_rolling` (llm_score.rs:61-69).
+    pub fn score_rolling(&self, ids: &[usize], window: usize) -> Result<Score> { self.score_from(ids, 1, window) }
+}
+
+impl Drop for CudaLlama {
+    fn drop(&mut self) { unsafe { ffi::fc_llama_free(self.raw) } }
+}
+
+
 /// One model per GPU behind a single call: sequences (or decode streams) are split in contiguous blocks and
 /// each block runs on its own host thread inside the library; results land in order, nothing is gathered.
 pub struct CudaModelSet { models: Vec<CudaModel> }
