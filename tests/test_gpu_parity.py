@@ -192,6 +192,27 @@ def test_decode_batch_groups_of_streams_match_oracle(tiny, monkeypatch):
             check_greedy(outs[i], wants[i][0], wants[i][1])
 
 
+def test_decode_batch_in_two_waves(tiny):
+    """More than 64 streams run as waves of 64: 70 streams give what the first 64 and the last 6 give as calls of their
+    own, and the streams of both waves follow the oracle."""
+    sm, om, gm = tiny
+    V = sm.dims[5]
+    prompts = np.stack([synth.token_ids(500 + i, 8, V) for i in range(70)])
+    outs = gm.decode_batch(prompts, 10)
+    first, last = gm.decode_batch(prompts[:64], 10), gm.decode_batch(prompts[64:], 10)
+    for i in range(64):
+        assert np.array_equal(outs[i], first[i]), i
+    for i in range(6):
+        assert np.array_equal(outs[64 + i], last[i]), i
+    for i in (0, 17, 63, 64, 69):
+        want, margin = om.generate_greedy(prompts[i], 10)
+        check_greedy(outs[i], want, margin)
+    # a single stream takes the one-stream generator and gives the same tokens as the oracle
+    one = gm.decode_batch(prompts[:1], 10)
+    want, margin = om.generate_greedy(prompts[0], 10)
+    check_greedy(one[0], want, margin)
+
+
 def test_phase_timeline_is_recorded_per_cta(tiny):
     """fc_stream_set_trace: every CTA of the persistent kernel leaves a rising series of timer
     values for the last token of a launch (entry 0 = token start, 15 per block, then the head)."""
