@@ -74,6 +74,10 @@ SIGNATURES = {
     "fc_ggml_type_bytes": (C.c_size_t, [C.c_int, C.c_size_t]),
     "fc_ggml_dequantize": (C.c_int, [C.c_int, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p]),
     "fc_ggml_requantize_q8_0": (C.c_int, [C.c_int, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p]),
+    "fc_ggml_weight_upload": (C.c_int, [C.c_int, C.c_int, C.c_void_p, C.c_size_t, C.c_int, C.c_int, C.POINTER(C.c_void_p)]),
+    "fc_ggml_weight_free": (None, [C.c_void_p]),
+    "fc_ggml_linear": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int]),
+    "fc_ggml_linear_dev": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "fc_f32_to_f16": (C.c_uint16, [C.c_float]),
     "fc_f16_to_f32": (C.c_float, [C.c_uint16]),
     "fc_rng_seed": (C.c_uint64, [C.c_uint64]),

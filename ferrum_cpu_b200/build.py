@@ -11,7 +11,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libferrum_cuda.so")
-SOURCES = ["codec.cpp", "gguf_load.cpp", "gemv.cu", "gemv_stream.cu", "rowops.cu", "attn.cu", "gemm_simt.cu", "gemm_tc.cu", "attn_tc.cu", "decode_mega.cu", "decode_batch.cu", "sample.cu", "llama_ops.cu", "llama.cu", "rowq.cu", "api.cu"]
+SOURCES = ["codec.cpp", "gguf_load.cpp", "gemv.cu", "gemv_stream.cu", "rowops.cu", "attn.cu", "gemm_simt.cu", "gemm_tc.cu", "attn_tc.cu", "decode_mega.cu", "decode_batch.cu", "sample.cu", "llama_ops.cu", "llama.cu", "rowq.cu", "ggml_linear.cu", "api.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall",

@@ -185,6 +185,15 @@ int launch_sample(const float* in, int V, int from_probs, const fc_sampling& prm
                   unsigned long long* rng_state, int* queue, int queue_cap, StepState* state, int* token_out, cudaStream_t st);
 
 // Per-layer statistics of a window forward (the device-side counterpart of verbose.rs:85-110): one record per layer.
+// Linear on a matrix kept in its GGML block format, decoded in the kernel (ggml_linear.cu): y[M][ldy] = [residual +] bias +
+// x · dequant(W)ᵀ; rows of the same kind of table decoded by id (ids, or the queue entry at state->fed when ids is null).
+int launch_ggml_linear(const fc_ggml_weight* w, const float* x, const float* bias, const float* residual, float* y, int ldy, int M,
+                       cudaStream_t st);
+int launch_ggml_rows(const fc_ggml_weight* w, const int* ids, const StepState* state, const int* queue, int R, float* x, int* error_flag,
+                     cudaStream_t st);
+int ggml_weight_rows(const fc_ggml_weight* w);
+int ggml_weight_cols(const fc_ggml_weight* w);
+
 // Per-row-scale int8 / int4 linear on a packed matrix (rowq.cu): y[M][ldy] = [residual +] bias + x · W; bias and residual may
 // be null, residual may be y itself.
 int launch_rowq_linear(fc_rowq* w, const float* x, const float* bias, const float* residual, float* y, int ldy, int M, cudaStream_t st);

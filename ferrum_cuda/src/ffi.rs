@@ -91,6 +91,7 @@ pub struct fc_llama_weights {
 pub enum fc_model {}
 pub enum fc_stream {}
 pub enum fc_qweight {}
+pub enum fc_ggml_weight {}
 pub enum fc_llama {}
 pub enum fc_llama_cache {}
 pub enum fc_rowq {}
@@ -106,6 +107,10 @@ extern "C" {
     pub fn fc_ggml_type_bytes(ggml_type: c_int, n: usize) -> usize;
     pub fn fc_ggml_dequantize(ggml_type: c_int, raw: *const c_void, nbytes: usize, n: usize, out: *mut f32) -> c_int;
     pub fn fc_ggml_requantize_q8_0(ggml_type: c_int, raw: *const c_void, nbytes: usize, n: usize, out: *mut c_void) -> c_int;
+    pub fn fc_ggml_weight_upload(device: c_int, ggml_type: c_int, raw: *const c_void, nbytes: usize, n: c_int, k: c_int, out: *mut *mut fc_ggml_weight) -> c_int;
+    pub fn fc_ggml_weight_free(w: *mut fc_ggml_weight);
+    pub fn fc_ggml_linear(w: *const fc_ggml_weight, x: *const f32, bias: *const f32, y: *mut f32, m: c_int) -> c_int;
+    pub fn fc_ggml_linear_dev(w: *const fc_ggml_weight, x_dev: *const f32, bias_dev: *const f32, y_dev: *mut f32, m: c_int, cuda_stream: *mut c_void) -> c_int;
     pub fn fc_f32_to_f16(v: f32) -> u16;
     pub fn fc_f16_to_f32(h: u16) -> f32;
     pub fn fc_rng_seed(seed: u64) -> u64;

@@ -119,6 +119,19 @@ int fc_ggml_to_q8_0(int ggml_type, const void* raw, size_t n, void* out);
 size_t fc_ggml_type_bytes(int ggml_type, size_t n);
 int fc_ggml_dequantize(int ggml_type, const void* raw, size_t nbytes, size_t n, float* out);
 int fc_ggml_requantize_q8_0(int ggml_type, const void* raw, size_t nbytes, size_t n, void* out);
+/* A matrix [N = out][K = in] kept on the device in its GGML block format (its file footprint: 4.5 bits per weight for
+ * Q4_0 / Q4_K, 5.5 for Q5_0 / Q5_K, 6.56 for Q6_K, ...) and multiplied with the blocks decoded inside the kernel:
+ * y[M][N] = x[M][K] · dequant(W)ᵀ + bias. The decoded weights are bit-identical to gguf/dequant.rs (each value is
+ * formed in the reference's order of operations), so this is Linear::forward on the f32 weights of the reference's
+ * precision-preserving import (load_llama_prec(None), gguf/llama.rs:171-176) up to the order of the sum over k.
+ * K must hold whole blocks of the type and be a multiple of 32; bias may be NULL. A format-generic kernel (one warp
+ * per output row): the Q8_0 entries above are the fast path for Q8_0. */
+typedef struct fc_ggml_weight fc_ggml_weight;
+int fc_ggml_weight_upload(int device, int ggml_type, const void* raw, size_t nbytes, int N, int K, fc_ggml_weight** out);
+void fc_ggml_weight_free(fc_ggml_weight* w);
+int fc_ggml_linear(const fc_ggml_weight* w, const float* x, const float* bias, float* y, int M);
+/* Device pointers (x_dev 16-byte aligned); returns after the launch. */
+int fc_ggml_linear_dev(const fc_ggml_weight* w, const float* x_dev, const float* bias_dev, float* y_dev, int M, void* cuda_stream);
 uint16_t fc_f32_to_f16(float v);  /* gguf_write/blocks.rs:12-61 */
 float fc_f16_to_f32(uint16_t h);  /* gguf/dequant.rs:7-35 */
 /* rng.rs:9-48 xorshift64*: seed -> state (0 is remapped), draws advance *state. */
