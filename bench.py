@@ -303,7 +303,33 @@ def run_case(a):
         name = a.model if a.model.startswith("llama") else "llama-1b"
         sm = synth.llama_named(name, seed=0, math_mode=a.math)
         c = sm.dims
-        gm = CudaLlama.from_synth(sm, prec=None if a.packed < 0 else a.packed)
+        if a.native >= 0:
+            # every matrix as random blocks of one ggml type in a temporary GGUF file, kept in that format on the device
+            import tempfile
+            import numpy as np
+            from ferrum_cpu_b200 import gguf_file
+            vals, bb = {2: (32, 18), 6: (32, 22), 8: (32, 34), 12: (256, 144), 13: (256, 176), 14: (256, 210)}[a.native]
+            rng = np.random.default_rng(0)
+
+            def blocks(n):
+                raw = rng.integers(0, 256, size=(n // vals, bb), dtype=np.uint8)
+                for at in {2: [0], 6: [0], 8: [0], 12: [0, 2], 13: [0, 2], 14: [208]}[a.native]:
+                    raw[:, at:at + 2] = (rng.standard_normal(n // vals) * 0.01).astype(np.float16).view(np.uint8).reshape(-1, 2)
+                return raw.reshape(-1)
+            c = sm.dims
+            d, F, qd, kvd = c["d_model"], c["d_ff"], c["n_head"] * c["head_dim"], c["n_kv_head"] * c["head_dim"]
+            shapes = {"attn_q": qd * d, "attn_k": kvd * d, "attn_v": kvd * d, "attn_output": d * qd, "ffn_gate": F * d, "ffn_up": F * d,
+                      "ffn_down": d * F}
+            raw = {f"blk.{i}.{stem}.weight": (a.native, blocks(n)) for i in range(c["n_layer"]) for stem, n in shapes.items()}
+            raw["token_embd.weight"] = (a.native, blocks(c["vocab"] * d))
+            tmp = tempfile.TemporaryDirectory()
+            path = gguf_file.write_llama_gguf(os.path.join(tmp.name, "m.gguf"), sm, raw=raw)
+            gm = CudaLlama.from_gguf(path, prec="native")
+            name += f" native ggml type {a.native}"
+            weight_bytes = sum(v[1].size for v in raw.values())   # the tied head is the embedding table, read once per token
+        else:
+            gm = CudaLlama.from_synth(sm, prec=None if a.packed < 0 else a.packed)
+            weight_bytes = sm.q8_weight_bytes
         if a.packed >= 0:
             name += " packed int4" if a.packed else " packed int8"
         if a.case == "llama-decode":
@@ -314,7 +340,7 @@ def run_case(a):
                 gm.generate(prompt, a.tokens, sampling(temperature=0.0), cache=cache)
                 us = cache.last_decode_ms / a.tokens * 1e3
                 kv = c["n_layer"] * 2 * (a.prompt + a.tokens / 2) * kvd * 4
-                print(f"{name} decode {a.tokens} tokens: device {us:.1f} us/token, {(sm.q8_weight_bytes + kv) / us / 1e3:.0f} GB/s "
+                print(f"{name} decode {a.tokens} tokens: device {us:.1f} us/token, {(weight_bytes + kv) / us / 1e3:.0f} GB/s "
                       f"algorithmic, launches {fcb.take_launch_count()}")
         else:
             T = min(c["ctx"], 1024)
@@ -420,6 +446,7 @@ def main():
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--math", type=int, default=0, help="--case: 0 fp32 CUDA cores, 1 tcgen05 bf16x3")
     ap.add_argument("--kind", type=int, default=0, help="--case rowq: 0 int8, 1 int4")
+    ap.add_argument("--native", type=int, default=-1, help="--case llama-*: matrices kept in this ggml block format (2 Q4_0, 6 Q5_0, 8 Q8_0, 12 Q4_K, 13 Q5_K, 14 Q6_K) and decoded in the kernels")
     ap.add_argument("--packed", type=int, default=-1, help="--case llama-*: every Linear packed to per-row int8 (0) / int4 (1), as the reference's importer does")
     ap.add_argument("--mode", type=int, default=0, help="--case decode: 0 persistent kernel, 1 one kernel per operation")
     ap.add_argument("--trace", action="store_true", help="--case decode: print the phase timeline of one token")

@@ -123,6 +123,7 @@ SIGNATURES = {
     "fc_llama_free": (None, [C.c_void_p]),
     "fc_llama_load_gguf": (C.c_int, [C.c_char_p, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_void_p)]),
     "fc_llama_load_gguf_packed": (C.c_int, [C.c_char_p, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_void_p)]),
+    "fc_llama_load_gguf_native": (C.c_int, [C.c_char_p, C.c_int, C.c_int, C.POINTER(C.c_void_p)]),
     "fc_llama_create_packed": (C.c_int, [C.POINTER(FcLlamaConfig), C.POINTER(FcLlamaWeights), C.c_int, C.c_int, C.POINTER(C.c_void_p)]),
     "fc_llama_gguf_probe": (C.c_int, [C.c_char_p, C.POINTER(FcLlamaConfig)]),
     "fc_llama_forward_tokens": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),

@@ -189,8 +189,8 @@ int launch_sample(const float* in, int V, int from_probs, const fc_sampling& prm
 // x · dequant(W)ᵀ; rows of the same kind of table decoded by id (ids, or the queue entry at state->fed when ids is null).
 int launch_ggml_linear(const fc_ggml_weight* w, const float* x, const float* bias, const float* residual, float* y, int ldy, int M,
                        cudaStream_t st);
-int launch_ggml_rows(const fc_ggml_weight* w, const int* ids, const StepState* state, const int* queue, int R, float* x, int* error_flag,
-                     cudaStream_t st);
+int launch_ggml_rows(const fc_ggml_weight* w, const int* ids, StepState* state, const int* queue, int ctx, int R, float* x,
+                     int* error_flag, cudaStream_t st);
 int ggml_weight_rows(const fc_ggml_weight* w);
 int ggml_weight_cols(const fc_ggml_weight* w);
 

@@ -207,15 +207,23 @@ __global__ void __launch_bounds__(256) ggml_linear_kernel(LinArgs a) {
         }
 }
 
-// Rows ids[r] of a table kept in its block format, decoded: the embedding lookup (llm.rs:610-635 embeds by copying the
-// decoded row). One warp per row; bad ids raise the error word and leave the row zero.
-__global__ void ggml_rows_kernel(const uint8_t* raw, size_t row_bytes, int type, int N, int K, const int* ids, const StepState* state,
-                                 const int* queue, int R, float* x, int* error_flag) {
+// Rows ids[r] of a table kept in its block format, decoded: the embedding lookup (llm.rs:588-597 copies the decoded
+// row). One warp per row; a bad id raises the error word and leaves the row zero. With `state` (one row): the queued
+// token at the cache position, refused like a bad id when the context is full (llm.rs:610-618, :720-730), nothing at
+// all once the stream is done or in error.
+__global__ void ggml_rows_kernel(const uint8_t* raw, size_t row_bytes, int type, int N, int K, const int* ids, StepState* state,
+                                 const int* queue, int ctx, int R, float* x, int* error_flag) {
     const int lane = threadIdx.x & 31;
     const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (r >= R) return;
+    if (state && (state->done | state->error)) return;
     const int id = ids ? ids[r] : queue[state->fed];
-    if (id < 0 || id >= N) {
+    if (id < 0 || id >= N || (state && state->pos >= ctx)) {
+        if (state) {
+            __syncwarp();
+            if (lane == 0) state->error = FC_E_DIM;
+            return;
+        }
         if (lane == 0 && error_flag) atomicExch(error_flag, FC_E_DIM);
         for (int c = lane; c < K; c += 32) x[(size_t)r * K + c] = 0.0f;
         return;
@@ -242,9 +250,9 @@ int launch_ggml_linear(const fc_ggml_weight* w, const float* x, const float* bia
     return FC_OK;
 }
 
-int launch_ggml_rows(const fc_ggml_weight* w, const int* ids, const StepState* state, const int* queue, int R, float* x, int* error_flag,
-                     cudaStream_t st) {
-    ggml_rows_kernel<<<(R + 7) / 8, 256, 0, st>>>(w->raw, w->row_bytes, w->type, w->N, w->K, ids, state, queue, R, x, error_flag);
+int launch_ggml_rows(const fc_ggml_weight* w, const int* ids, StepState* state, const int* queue, int ctx, int R, float* x,
+                     int* error_flag, cudaStream_t st) {
+    ggml_rows_kernel<<<(R + 7) / 8, 256, 0, st>>>(w->raw, w->row_bytes, w->type, w->N, w->K, ids, state, queue, ctx, R, x, error_flag);
     FC_LAUNCHED();
     return FC_OK;
 }

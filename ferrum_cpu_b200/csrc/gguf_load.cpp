@@ -15,6 +15,7 @@
 #include <vector>
 
 #include "../../include/ferrum_cuda.h"
+#include "llama_native.h"
 
 namespace fc {
 int fail(int code, const char* fmt, ...);
@@ -321,7 +322,20 @@ struct ParsedLlama {
     std::vector<fc_llama_layer> layers;
     fc_llama_weights w{};
     std::vector<std::vector<float>> owned_f32;
+    // the same matrices as the file stores them (for the model that keeps them in their block formats)
+    fc::RawTensor raw_tok, raw_out;
+    std::vector<fc::RawLlamaLayer> raw_layers;
 };
+
+// The stored form of a tensor that tensor() has already validated.
+fc::RawTensor raw_of(const File& f, const std::string& name) {
+    const Tensor& t = f.tensors.find(name)->second;
+    fc::RawTensor r;
+    r.type = (int)t.type;
+    r.data = f.bytes.data() + f.data + t.offset;
+    r.nbytes = (size_t)t.nbytes;
+    return r;
+}
 
 bool has_tensor(const File& f, const std::string& name) { return f.tensors.find(name) != f.tensors.end(); }
 
@@ -407,7 +421,9 @@ int parse_llama(const File& f, int math_mode, int ctx_cap, ParsedLlama* p) {
     const uint8_t* b = nullptr;
     if ((rc = tensor(f, "token_embd.weight", T_Q8_0, d, V, &b)) != FC_OK) return rc;
     p->w.token_embd_q8 = b;
+    p->raw_tok = raw_of(f, "token_embd.weight");
     p->layers.resize(L);
+    p->raw_layers.resize(L);
     for (int i = 0; i < L; ++i) {
         fc_llama_layer& lw = p->layers[i];
         const std::string n = "blk." + std::to_string(i) + ".";
@@ -418,22 +434,29 @@ int parse_llama(const File& f, int math_mode, int ctx_cap, ParsedLlama* p) {
         if ((rc = f32_owned(f, p, n + "attn_norm.weight", d, &lw.attn_norm)) != FC_OK) return rc;
         if ((rc = tensor(f, n + "attn_q.weight", T_Q8_0, d, q_dim, &b)) != FC_OK) return rc;
         lw.wq_q8 = b;
+        p->raw_layers[i].wq = raw_of(f, n + "attn_q.weight");
         if ((rc = tensor(f, n + "attn_k.weight", T_Q8_0, d, kv_dim, &b)) != FC_OK) return rc;
         lw.wk_q8 = b;
+        p->raw_layers[i].wk = raw_of(f, n + "attn_k.weight");
         if ((rc = tensor(f, n + "attn_v.weight", T_Q8_0, d, kv_dim, &b)) != FC_OK) return rc;
         lw.wv_q8 = b;
+        p->raw_layers[i].wv = raw_of(f, n + "attn_v.weight");
         if ((rc = tensor(f, n + "attn_output.weight", T_Q8_0, q_dim, d, &b)) != FC_OK) return rc;
         lw.wo_q8 = b;
+        p->raw_layers[i].wo = raw_of(f, n + "attn_output.weight");
         if (has_tensor(f, n + "attn_q.bias") && (rc = f32_owned(f, p, n + "attn_q.bias", q_dim, &lw.bq)) != FC_OK) return rc;
         if (has_tensor(f, n + "attn_k.bias") && (rc = f32_owned(f, p, n + "attn_k.bias", kv_dim, &lw.bk)) != FC_OK) return rc;
         if (has_tensor(f, n + "attn_v.bias") && (rc = f32_owned(f, p, n + "attn_v.bias", kv_dim, &lw.bv)) != FC_OK) return rc;
         if ((rc = f32_owned(f, p, n + "ffn_norm.weight", d, &lw.ffn_norm)) != FC_OK) return rc;
         if ((rc = tensor(f, n + "ffn_gate.weight", T_Q8_0, d, F, &b)) != FC_OK) return rc;
         lw.gate_q8 = b;
+        p->raw_layers[i].gate = raw_of(f, n + "ffn_gate.weight");
         if ((rc = tensor(f, n + "ffn_up.weight", T_Q8_0, d, F, &b)) != FC_OK) return rc;
         lw.up_q8 = b;
+        p->raw_layers[i].up = raw_of(f, n + "ffn_up.weight");
         if ((rc = tensor(f, n + "ffn_down.weight", T_Q8_0, F, d, &b)) != FC_OK) return rc;
         lw.down_q8 = b;
+        p->raw_layers[i].down = raw_of(f, n + "ffn_down.weight");
     }
     if ((rc = f32_owned(f, p, "output_norm.weight", d, &p->w.output_norm)) != FC_OK) return rc;
     if (has_tensor(f, "output.bias"))
@@ -442,6 +465,7 @@ int parse_llama(const File& f, int math_mode, int ctx_cap, ParsedLlama* p) {
     if (!tied) {
         if ((rc = tensor(f, "output.weight", T_Q8_0, d, V, &b)) != FC_OK) return rc;
         p->w.output_q8 = b;
+        p->raw_out = raw_of(f, "output.weight");
     }
     p->w.layers = p->layers.data();
     fc_llama_config& c = p->cfg;
@@ -509,6 +533,18 @@ static int load_llama_file(const char* path, int device, int math_mode, int ctx_
 
 int fc_llama_load_gguf(const char* path, int device, int math_mode, int ctx_cap, fc_llama** out) {
     return load_llama_file(path, device, math_mode, ctx_cap, -1, out);
+}
+
+int fc_llama_load_gguf_native(const char* path, int device, int ctx_cap, fc_llama** out) {
+    if (!path || !out) return fail(FC_E_ARG, "fc_llama_load_gguf_native: bad argument");
+    *out = nullptr;
+    File f;
+    int rc = read_file(path, &f);
+    if (rc != FC_OK) return rc;
+    ParsedLlama p;
+    rc = parse_llama(f, FC_MATH_FP32, ctx_cap, &p);
+    if (rc != FC_OK) return rc;
+    return fc::llama_create_native(&p.cfg, &p.w, p.raw_tok, p.raw_out, p.raw_layers.data(), device, out);
 }
 
 int fc_llama_load_gguf_packed(const char* path, int device, int ctx_cap, int kind, fc_llama** out) {

@@ -6,6 +6,7 @@
 #include <cstring>
 #include <vector>
 
+#include "llama_native.h"
 #include "llama_ops.cuh"
 
 using namespace fc;
@@ -43,12 +44,20 @@ struct fc_llama {
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     float last_score_ms = 0.0f;
     bool force_fp32 = false;         // the batched prime keeps the cache rows at fp32 rounding
-    // Every Linear packed as the reference's importer packs it (Gguf::load_llama(kind), gguf/llama.rs:13-27,164-171):
-    // per-input-row int8 / int4 QWeights, run by ops::qlinear. prec < 0: the Q8_0 matrices above are what runs.
+    // prec < 0: the Q8_0 matrices above are what runs. FC_Q_INT8 / FC_Q_INT4: every Linear packed as the reference's
+    // importer packs it (Gguf::load_llama(kind), gguf/llama.rs:13-27,164-171) to a per-input-row QWeight, run by
+    // ops::qlinear. kNative: every matrix kept in the file's own block format and decoded inside the product, which is
+    // the reference's f32 import (load_llama_prec(None), gguf/llama.rs:171-176) without the expansion; no Q8_0 copies.
+    static constexpr int kNative = 2;
     int prec = -1;
-    struct PackedLayer { fc_rowq *wq = nullptr, *wk = nullptr, *wv = nullptr, *wo = nullptr, *gate = nullptr, *up = nullptr, *down = nullptr; };
+    struct Lin {                      // one Linear of the packed / native model: exactly one of the two is set
+        fc_rowq* rq = nullptr;
+        fc_ggml_weight* gw = nullptr;
+    };
+    struct PackedLayer { Lin wq, wk, wv, wo, gate, up, down; };
     std::vector<PackedLayer> packed;
-    fc_rowq* packed_head = nullptr;
+    Lin packed_head;
+    fc_ggml_weight* native_tok = nullptr;   // the embedding table in its block format (kNative)
 };
 
 struct fc_llama_cache {
@@ -221,6 +230,10 @@ int forward_rows(fc_llama* m, int B, int T, fc_llama_cache* fill = nullptr) {
     return launch_llama_rmsnorm(m->x, m->out_norm, c.norm_eps, R, d, m->n, nullptr, st);
 }
 
+int lin_apply(const fc_llama::Lin& l, const float* x, const float* bias, const float* residual, float* y, int ldy, int M, cudaStream_t st) {
+    return l.rq ? launch_rowq_linear(l.rq, x, bias, residual, y, ldy, M, st) : launch_ggml_linear(l.gw, x, bias, residual, y, ldy, M, st);
+}
+
 // FeedForward::forward (llm.rs:417-428) on separate gate and up rows: h = silu(gate) * up.
 __global__ void silu_mul_kernel(const float* __restrict__ g, const float* __restrict__ u, size_t n, float* __restrict__ h) {
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
@@ -248,16 +261,16 @@ int packed_block(fc_llama* m, int l, int R, float* x, float* n, float* qkv, floa
     cudaStream_t st = m->st;
     FC_TRY(launch_llama_rmsnorm(x, L.attn_norm, c.norm_eps, R, d, n, state, st));
     const float* b = L.qkv_b;
-    FC_TRY(launch_rowq_linear(P.wq, n, b, nullptr, qkv, m->qkv_dim, R, st));
-    FC_TRY(launch_rowq_linear(P.wk, n, b ? b + m->q_dim : nullptr, nullptr, qkv + m->q_dim, m->qkv_dim, R, st));
-    FC_TRY(launch_rowq_linear(P.wv, n, b ? b + m->q_dim + m->kv_dim : nullptr, nullptr, qkv + m->q_dim + m->kv_dim, m->qkv_dim, R, st));
+    FC_TRY(lin_apply(P.wq, n, b, nullptr, qkv, m->qkv_dim, R, st));
+    FC_TRY(lin_apply(P.wk, n, b ? b + m->q_dim : nullptr, nullptr, qkv + m->q_dim, m->qkv_dim, R, st));
+    FC_TRY(lin_apply(P.wv, n, b ? b + m->q_dim + m->kv_dim : nullptr, nullptr, qkv + m->q_dim + m->kv_dim, m->qkv_dim, R, st));
     FC_TRY(attend());
-    FC_TRY(launch_rowq_linear(P.wo, att, nullptr, x, x, d, R, st));
+    FC_TRY(lin_apply(P.wo, att, nullptr, x, x, d, R, st));
     FC_TRY(launch_llama_rmsnorm(x, L.ffn_norm, c.norm_eps, R, d, n, state, st));
-    FC_TRY(launch_rowq_linear(P.gate, n, nullptr, nullptr, gu, F, R, st));
-    FC_TRY(launch_rowq_linear(P.up, n, nullptr, nullptr, gu + (size_t)R * F, F, R, st));
+    FC_TRY(lin_apply(P.gate, n, nullptr, nullptr, gu, F, R, st));
+    FC_TRY(lin_apply(P.up, n, nullptr, nullptr, gu + (size_t)R * F, F, R, st));
     FC_TRY(launch_silu_mul(gu, gu + (size_t)R * F, (size_t)R * F, hid, st));
-    return launch_rowq_linear(P.down, hid, nullptr, x, x, d, R, st);
+    return lin_apply(P.down, hid, nullptr, x, x, d, R, st);
 }
 
 int forward_rows_packed(fc_llama* m, int B, int T, fc_llama_cache* fill) {
@@ -265,7 +278,8 @@ int forward_rows_packed(fc_llama* m, int B, int T, fc_llama_cache* fill) {
     const int R = B * T, d = c.d_model;
     cudaStream_t st = m->st;
     FC_CUDA(cudaMemsetAsync(m->err_d, 0, sizeof(int), st));
-    FC_TRY(launch_llama_embed_rows(m->tok, m->ids_d, R, m->x, m->err_d, st));
+    if (m->native_tok) FC_TRY(launch_ggml_rows(m->native_tok, m->ids_d, nullptr, nullptr, c.ctx, R, m->x, m->err_d, st));
+    else FC_TRY(launch_llama_embed_rows(m->tok, m->ids_d, R, m->x, m->err_d, st));
     for (int l = 0; l < c.n_layer; ++l) {
         FC_TRY(packed_block(m, l, R, m->x, m->n, m->qkv, m->att, m->gu, m->hid, nullptr, [&]() -> int {
             FC_TRY(launch_llama_rope_rows(m->qkv, R, m->qkv_dim, T, c.n_head, c.n_kv_head, m->q_dim, c.head_dim, c.rope_dim,
@@ -306,7 +320,7 @@ int score_tail(fc_llama* m, int R) {
     const int d = m->cfg.d_model, ldl = m->head.N_pad;
     for (int r0 = 0; r0 < R; r0 += m->head_chunk) {
         const int rows = std::min(m->head_chunk, R - r0);
-        if (m->prec >= 0) FC_TRY(launch_rowq_linear(m->packed_head, m->n + (size_t)r0 * d, nullptr, nullptr, m->logits, ldl, rows, m->st));
+        if (m->prec >= 0) FC_TRY(lin_apply(m->packed_head, m->n + (size_t)r0 * d, nullptr, nullptr, m->logits, ldl, rows, m->st));
         else FC_TRY(gemm(m, m->head, m->n + (size_t)r0 * d, nullptr, nullptr, m->logits, rows, ldl));
         FC_TRY(launch_llama_score_rows(m->logits, ldl, m->cfg.vocab, m->targets_d + r0, rows, m->lp_d + r0, m->gr_d + r0, m->st));
     }
@@ -366,7 +380,8 @@ int launch_step_packed(fc_llama_cache* s, int with_head) {
     const fc_llama_config& c = m->cfg;
     cudaStream_t st = m->st;
     const size_t layer_stride = (size_t)c.ctx * m->kv_dim;
-    FC_TRY(launch_llama_embed_step(m->tok, c.ctx, s->queue, s->state, s->x, st));
+    if (m->native_tok) FC_TRY(launch_ggml_rows(m->native_tok, nullptr, s->state, s->queue, c.ctx, 1, s->x, nullptr, st));
+    else FC_TRY(launch_llama_embed_step(m->tok, c.ctx, s->queue, s->state, s->x, st));
     for (int l = 0; l < c.n_layer; ++l) {
         float* kc = s->kc + l * layer_stride;
         float* vc = s->vc + l * layer_stride;
@@ -377,7 +392,7 @@ int launch_step_packed(fc_llama_cache* s, int with_head) {
     }
     if (with_head) {
         FC_TRY(launch_llama_rmsnorm(s->x, m->out_norm, c.norm_eps, 1, c.d_model, s->n, nullptr, st));
-        FC_TRY(launch_rowq_linear(m->packed_head, s->n, nullptr, nullptr, s->logits, m->head.N_pad, 1, st));
+        FC_TRY(lin_apply(m->packed_head, s->n, nullptr, nullptr, s->logits, m->head.N_pad, 1, st));
     }
     return launch_step_advance_pdl(s->state, st);
 }
@@ -457,7 +472,7 @@ int prime_window(fc_llama_cache* s, const int32_t* ids, int n) {
     FC_LAUNCHED();
     // logits of the last row: the final norm was applied by forward_rows
     if (m->prec >= 0)
-        FC_TRY(launch_rowq_linear(m->packed_head, m->n + (size_t)(n - 1) * c.d_model, nullptr, nullptr, s->logits, m->head.N_pad, 1, st));
+        FC_TRY(lin_apply(m->packed_head, m->n + (size_t)(n - 1) * c.d_model, nullptr, nullptr, s->logits, m->head.N_pad, 1, st));
     else
         FC_TRY(launch_gemv_q8_stream(m->head, m->n + (size_t)(n - 1) * c.d_model, nullptr, 0.0f, nullptr, nullptr, EPI_NONE, s->logits,
                                      s->state, s->status, st));
@@ -470,7 +485,8 @@ int prime_window(fc_llama_cache* s, const int32_t* ids, int n) {
 
 extern "C" {
 
-int fc_llama_create(const fc_llama_config* cfg, const fc_llama_weights* w, int device, fc_llama** out) {
+// `matrices`: upload the Q8_0 matrices (false for the model that keeps them in their file formats).
+static int create_impl(const fc_llama_config* cfg, const fc_llama_weights* w, int device, bool matrices, fc_llama** out) {
     if (!cfg || !w || !out || !w->layers) return fail(FC_E_ARG, "fc_llama_create: null argument");
     *out = nullptr;
     const fc_llama_config& c = *cfg;
@@ -505,9 +521,15 @@ int fc_llama_create(const fc_llama_config* cfg, const fc_llama_weights* w, int d
         FC_CUDA(cudaEventCreate(&m->ev1));
         cudaStream_t st = m->st;
         const int d = c.d_model, F = c.d_ff;
-        FC_TRY(upload_q8(m->arena, w->token_embd_q8, c.vocab, d, &m->tok, st));
-        if (c.tied || !w->output_q8) m->head = m->tok;
-        else FC_TRY(upload_q8(m->arena, w->output_q8, c.vocab, d, &m->head, st));
+        if (matrices) {
+            FC_TRY(upload_q8(m->arena, w->token_embd_q8, c.vocab, d, &m->tok, st));
+            if (c.tied || !w->output_q8) m->head = m->tok;
+            else FC_TRY(upload_q8(m->arena, w->output_q8, c.vocab, d, &m->head, st));
+        } else {
+            // only the shape of the head is used (the row stride of the logits)
+            m->head.N = c.vocab; m->head.K = d; m->head.N_pad = (c.vocab + 127) & ~127;
+            m->tok = m->head;
+        }
         FC_TRY(upload_f32(m->arena, w->output_norm, d, &m->out_norm, st));
         // apply_rope (llm.rs:172): freq_i = (base as f64).powf(-2 i / rope_dim) as f32
         const int half = c.rope_dim / 2;
@@ -524,10 +546,12 @@ int fc_llama_create(const fc_llama_config* cfg, const fc_llama_weights* w, int d
         for (int l = 0; l < c.n_layer; ++l) {
             const fc_llama_layer& h = w->layers[l];
             LlamaLayerDev& L = m->layers[l];
-            FC_TRY(upload_fused(m->arena, {{h.wq_q8, m->q_dim}, {h.wk_q8, m->kv_dim}, {h.wv_q8, m->kv_dim}}, d, &L.qkv, st));
-            FC_TRY(upload_q8(m->arena, h.wo_q8, d, m->q_dim, &L.wo, st));
-            FC_TRY(upload_interleaved(m->arena, h.gate_q8, h.up_q8, F, d, &L.gateup, st));
-            FC_TRY(upload_q8(m->arena, h.down_q8, d, F, &L.down, st));
+            if (matrices) {
+                FC_TRY(upload_fused(m->arena, {{h.wq_q8, m->q_dim}, {h.wk_q8, m->kv_dim}, {h.wv_q8, m->kv_dim}}, d, &L.qkv, st));
+                FC_TRY(upload_q8(m->arena, h.wo_q8, d, m->q_dim, &L.wo, st));
+                FC_TRY(upload_interleaved(m->arena, h.gate_q8, h.up_q8, F, d, &L.gateup, st));
+                FC_TRY(upload_q8(m->arena, h.down_q8, d, F, &L.down, st));
+            }
             FC_TRY(upload_f32(m->arena, h.attn_norm, d, &L.attn_norm, st));
             FC_TRY(upload_f32(m->arena, h.ffn_norm, d, &L.ffn_norm, st));
             if (h.bq || h.bk || h.bv) {
@@ -546,6 +570,10 @@ int fc_llama_create(const fc_llama_config* cfg, const fc_llama_weights* w, int d
     if (rc != FC_OK) { fc_llama_free(m); return rc; }
     *out = m;
     return FC_OK;
+}
+
+int fc_llama_create(const fc_llama_config* cfg, const fc_llama_weights* w, int device, fc_llama** out) {
+    return create_impl(cfg, w, device, true, out);
 }
 
 // A Q8_0 tensor [n_out][n_in] as the reference's importer packs it: decoded (gguf/dequant.rs:37-49), transposed to
@@ -572,16 +600,16 @@ int fc_llama_create_packed(const fc_llama_config* cfg, const fc_llama_weights* w
         for (int l = 0; l < c.n_layer; ++l) {
             const fc_llama_layer& h = w->layers[l];
             fc_llama::PackedLayer& P = m->packed[l];
-            FC_TRY(pack_linear(device, h.wq_q8, m->q_dim, c.d_model, kind, &P.wq));
-            FC_TRY(pack_linear(device, h.wk_q8, m->kv_dim, c.d_model, kind, &P.wk));
-            FC_TRY(pack_linear(device, h.wv_q8, m->kv_dim, c.d_model, kind, &P.wv));
-            FC_TRY(pack_linear(device, h.wo_q8, c.d_model, m->q_dim, kind, &P.wo));
-            FC_TRY(pack_linear(device, h.gate_q8, c.d_ff, c.d_model, kind, &P.gate));
-            FC_TRY(pack_linear(device, h.up_q8, c.d_ff, c.d_model, kind, &P.up));
-            FC_TRY(pack_linear(device, h.down_q8, c.d_model, c.d_ff, kind, &P.down));
+            FC_TRY(pack_linear(device, h.wq_q8, m->q_dim, c.d_model, kind, &P.wq.rq));
+            FC_TRY(pack_linear(device, h.wk_q8, m->kv_dim, c.d_model, kind, &P.wk.rq));
+            FC_TRY(pack_linear(device, h.wv_q8, m->kv_dim, c.d_model, kind, &P.wv.rq));
+            FC_TRY(pack_linear(device, h.wo_q8, c.d_model, m->q_dim, kind, &P.wo.rq));
+            FC_TRY(pack_linear(device, h.gate_q8, c.d_ff, c.d_model, kind, &P.gate.rq));
+            FC_TRY(pack_linear(device, h.up_q8, c.d_ff, c.d_model, kind, &P.up.rq));
+            FC_TRY(pack_linear(device, h.down_q8, c.d_model, c.d_ff, kind, &P.down.rq));
         }
         // the LM head: `output.weight`, or the token embedding transposed when tied (gguf/llama.rs:304-311)
-        FC_TRY(pack_linear(device, (c.tied || !w->output_q8) ? w->token_embd_q8 : w->output_q8, c.vocab, c.d_model, kind, &m->packed_head));
+        FC_TRY(pack_linear(device, (c.tied || !w->output_q8) ? w->token_embd_q8 : w->output_q8, c.vocab, c.d_model, kind, &m->packed_head.rq));
         m->prec = kind;
         return FC_OK;
     };
@@ -594,9 +622,11 @@ void fc_llama_free(fc_llama* m) {
     if (!m) return;
     cudaSetDevice(m->device);
     if (m->st) cudaStreamSynchronize(m->st);
+    auto drop = [](fc_llama::Lin& l) { fc_rowq_free(l.rq); fc_ggml_weight_free(l.gw); l = fc_llama::Lin(); };
     for (auto& P : m->packed)
-        for (fc_rowq* q : {P.wq, P.wk, P.wv, P.wo, P.gate, P.up, P.down}) fc_rowq_free(q);
-    fc_rowq_free(m->packed_head);
+        for (fc_llama::Lin* l : {&P.wq, &P.wk, &P.wv, &P.wo, &P.gate, &P.up, &P.down}) drop(*l);
+    drop(m->packed_head);
+    fc_ggml_weight_free(m->native_tok);
     m->ws_arena.release();
     m->arena.release();
     if (m->ev0) cudaEventDestroy(m->ev0);
@@ -616,7 +646,7 @@ int fc_llama_forward_tokens(fc_llama* m, const int32_t* ids, int n, float* logit
     FC_TRY(forward_rows(m, 1, n));
     for (int r0 = 0; r0 < n; r0 += m->head_chunk) {
         const int rows = std::min(m->head_chunk, n - r0);
-        if (m->prec >= 0) FC_TRY(launch_rowq_linear(m->packed_head, m->n + (size_t)r0 * d, nullptr, nullptr, m->logits, ldl, rows, m->st));
+        if (m->prec >= 0) FC_TRY(lin_apply(m->packed_head, m->n + (size_t)r0 * d, nullptr, nullptr, m->logits, ldl, rows, m->st));
         else FC_TRY(gemm(m, m->head, m->n + (size_t)r0 * d, nullptr, nullptr, m->logits, rows, ldl));
         FC_CUDA(cudaMemcpy2DAsync(logits + (size_t)r0 * V, (size_t)V * 4, m->logits, (size_t)ldl * 4, (size_t)V * 4, rows,
                                   cudaMemcpyDeviceToHost, m->st));
@@ -877,3 +907,38 @@ int fc_llama_generate(fc_llama_cache* s, const int32_t* prompt, int n, int max_n
 float fc_llama_last_decode_ms(const fc_llama_cache* s) { return s ? s->last_decode_ms : 0.0f; }
 
 }  // extern "C"
+
+namespace fc {
+int llama_create_native(const fc_llama_config* cfg, const fc_llama_weights* w, const RawTensor& tok, const RawTensor& output,
+                        const RawLlamaLayer* layers, int device, fc_llama** out) {
+    FC_TRY(create_impl(cfg, w, device, false, out));
+    fc_llama* m = *out;
+    const fc_llama_config& c = m->cfg;
+    auto up = [&](const RawTensor& t, int n_out, int n_in, fc_ggml_weight** dst) -> int {
+        if (!t.data) return fail(FC_E_FORMAT, "a required tensor is missing");
+        return fc_ggml_weight_upload(device, t.type, t.data, t.nbytes, n_out, n_in, dst);
+    };
+    auto build = [&]() -> int {
+        FC_TRY(up(tok, c.vocab, c.d_model, &m->native_tok));
+        m->packed.resize(c.n_layer);
+        for (int l = 0; l < c.n_layer; ++l) {
+            const RawLlamaLayer& h = layers[l];
+            fc_llama::PackedLayer& P = m->packed[l];
+            FC_TRY(up(h.wq, m->q_dim, c.d_model, &P.wq.gw));
+            FC_TRY(up(h.wk, m->kv_dim, c.d_model, &P.wk.gw));
+            FC_TRY(up(h.wv, m->kv_dim, c.d_model, &P.wv.gw));
+            FC_TRY(up(h.wo, c.d_model, m->q_dim, &P.wo.gw));
+            FC_TRY(up(h.gate, c.d_ff, c.d_model, &P.gate.gw));
+            FC_TRY(up(h.up, c.d_ff, c.d_model, &P.up.gw));
+            FC_TRY(up(h.down, c.d_model, c.d_ff, &P.down.gw));
+        }
+        // the LM head: output.weight, or the embedding table itself when tied (gguf/llama.rs:304-311)
+        FC_TRY(up((c.tied || !output.data) ? tok : output, c.vocab, c.d_model, &m->packed_head.gw));
+        m->prec = fc_llama::kNative;
+        return FC_OK;
+    };
+    const int rc = build();
+    if (rc != FC_OK) { fc_llama_free(m); *out = nullptr; }
+    return rc;
+}
+}  // namespace fc

@@ -80,6 +80,9 @@ class CudaLlama:
         self.config.math_mode = math_mode
         if prec is None:
             check(_lib.lib().fc_llama_load_gguf(str(path).encode(), device, math_mode, ctx_cap, C.byref(self._h)))
+        elif prec == "native":
+            # load_llama_prec(None): the file's own blocks, decoded inside the kernels
+            check(_lib.lib().fc_llama_load_gguf_native(str(path).encode(), device, ctx_cap, C.byref(self._h)))
         else:
             check(_lib.lib().fc_llama_load_gguf_packed(str(path).encode(), device, ctx_cap, int(prec), C.byref(self._h)))
         return self

@@ -155,6 +155,7 @@ extern "C" {
     pub fn fc_llama_free(m: *mut fc_llama);
     pub fn fc_llama_load_gguf(path: *const c_char, device: c_int, math_mode: c_int, ctx_cap: c_int, out: *mut *mut fc_llama) -> c_int;
     pub fn fc_llama_load_gguf_packed(path: *const c_char, device: c_int, ctx_cap: c_int, kind: c_int, out: *mut *mut fc_llama) -> c_int;
+    pub fn fc_llama_load_gguf_native(path: *const c_char, device: c_int, ctx_cap: c_int, out: *mut *mut fc_llama) -> c_int;
     pub fn fc_llama_create_packed(cfg: *const fc_llama_config, w: *const fc_llama_weights, device: c_int, kind: c_int, out: *mut *mut fc_llama) -> c_int;
     pub fn fc_llama_gguf_probe(path: *const c_char, out: *mut fc_llama_config) -> c_int;
     pub fn fc_llama_forward_tokens(m: *mut fc_llama, ids: *const i32, n: c_int, logits: *mut f32) -> c_int;

@@ -229,10 +229,12 @@ impl Drop for MirrorFlag {
 }
 
 /// Weight precision of an imported decoder, as `Gguf::load_llama(kind)` / `load_llama_prec(None)` choose it
-/// (gguf/llama.rs:164-176): the file's own blocks brought to Q8_0 (the fast path of this crate), or every Linear
-/// re-packed to a per-input-row int8 / int4 `QWeight` and run by `ops::qlinear`, which is what `ferrum_core` computes.
+/// (gguf/llama.rs:164-176): the file's own blocks brought to Q8_0 (the fast path of this crate), every Linear
+/// re-packed to a per-input-row int8 / int4 `QWeight` and run by `ops::qlinear` (what `load_llama(kind)` computes), or
+/// `Native`: every matrix kept in the file's block format and decoded inside the kernels (what `load_llama_prec(None)`
+/// computes, at the file's footprint).
 #[derive(Clone, Copy, Debug, PartialEq, Eq)]
-pub enum LlamaWeights { AsStored, PackedInt8, PackedInt4 }
+pub enum LlamaWeights { AsStored, PackedInt8, PackedInt4, Native }
 
 /// A llama / qwen2 architecture model resident on one GPU: `LlamaModel` of llm.rs:549-565.
 pub struct CudaLlama {
@@ -253,6 +255,7 @@ impl CudaLlama {
             LlamaWeights::AsStored => unsafe { ffi::fc_llama_load_gguf(c_path.as_ptr(), dev, math as c_int, cap, &mut raw) },
             LlamaWeights::PackedInt8 => unsafe { ffi::fc_llama_load_gguf_packed(c_path.as_ptr(), dev, cap, ffi::FC_Q_INT8, &mut raw) },
             LlamaWeights::PackedInt4 => unsafe { ffi::fc_llama_load_gguf_packed(c_path.as_ptr(), dev, cap, ffi::FC_Q_INT4, &mut raw) },
+            LlamaWeights::Native => unsafe { ffi::fc_llama_load_gguf_native(c_path.as_ptr(), dev, cap, &mut raw) },
         })?;
         Ok(Self { raw, vocab: cfg.vocab as usize, _not_send: PhantomData })
     }

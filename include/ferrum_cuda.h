@@ -408,6 +408,13 @@ int fc_llama_load_gguf(const char* path, int device, int math_mode, int ctx_cap,
 /* Gguf::load_llama(kind) (gguf/llama.rs:164-171) from the file: fc_llama_load_gguf followed by the packing of
  * fc_llama_create_packed. */
 int fc_llama_load_gguf_packed(const char* path, int device, int ctx_cap, int kind, fc_llama** out);
+/* The reference's precision-preserving import (load_llama_prec(None), gguf/llama.rs:171-176: every tensor decoded to
+ * f32, nothing re-quantised) without the expansion: every matrix stays on the device in the file's own block format
+ * (Q4_0, Q5_0, Q8_0, Q4_1, Q5_1, Q2_K .. Q6_K, f16, f32: its file footprint, no Q8_0 copy), the embedding rows and
+ * the Linears decode it inside their kernels (fc_ggml_linear), bit-identical weights, fp32 arithmetic. Rows must hold
+ * whole blocks of their type (256 for the K-quants). All fc_llama_* calls work on the result; one kernel per
+ * operation, the decode step captured in a CUDA graph. */
+int fc_llama_load_gguf_native(const char* path, int device, int ctx_cap, fc_llama** out);
 int fc_llama_gguf_probe(const char* path, fc_llama_config* out);
 /* LlamaModel::forward_tokens (llm.rs:622-635): n ids -> logits [n][vocab] (host buffer). */
 int fc_llama_forward_tokens(fc_llama* m, const int32_t* ids, int n, float* logits);

@@ -346,6 +346,30 @@ void fo_llama_pack(void* mp, int kind) {
         for (Lin* l : {&L.wq, &L.wk, &L.wv, &L.wo, &L.gate, &L.up, &L.down}) l->pack(kind);
     m.head.pack(kind);
 }
+// load_llama_prec(None) (gguf/llama.rs:171-176): a matrix replaced by f32 values [n_out][n_in] decoded from the file
+// (stored as Ferrum's [n_in][n_out], gguf/llama.rs:143-144). which: 0..6 = wq, wk, wv, wo, gate, up, down of `layer`;
+// 7 = the LM head; 8 = the embedding table [vocab][d] (kept as is).
+int fo_llama_set_f32(void* mp, int layer, int which, const float* w, int n_out, int n_in) {
+    Model& m = *(Model*)mp;
+    if (which == 8) {
+        if ((size_t)n_out * n_in != m.tok.size()) return -1;
+        m.tok.assign(w, w + m.tok.size());
+        return 0;
+    }
+    Lin* l = nullptr;
+    if (which == 7) l = &m.head;
+    else {
+        if (layer < 0 || layer >= (int)m.layers.size() || which < 0 || which > 6) return -1;
+        Layer& L = m.layers[layer];
+        Lin* all[7] = {&L.wq, &L.wk, &L.wv, &L.wo, &L.gate, &L.up, &L.down};
+        l = all[which];
+    }
+    if (l->out != n_out || l->in != n_in) return -1;
+    for (int o = 0; o < n_out; ++o)
+        for (int i = 0; i < n_in; ++i) l->w[(size_t)i * n_out + o] = w[(size_t)o * n_in + i];
+    l->kind = -1;
+    return 0;
+}
 void fo_llama_free(void* m) { delete (Model*)m; }
 
 int fo_llama_forward_tokens(void* m, const int32_t* ids, int n, float* logits) { return forward_tokens(*(Model*)m, ids, n, logits); }

@@ -68,6 +68,7 @@ def lib():
         L.fo_llama_free.argtypes = [C.c_void_p]
         L.fo_llama_pack.argtypes = [C.c_void_p, C.c_int]
         L.fo_llama_pack.restype = None
+        L.fo_llama_set_f32.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int]
         L.fo_llama_forward_tokens.restype = C.c_int
         L.fo_llama_forward_tokens.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
         L.fo_llama_cache_create.restype, L.fo_llama_cache_create.argtypes = C.c_void_p, [C.c_void_p]
@@ -310,6 +311,12 @@ class OracleLlama:
     @property
     def ok(self):
         return bool(self._m)
+
+    def set_f32(self, layer, which, w):
+        """load_llama_prec(None): matrix `which` (0..6 of `layer`, 7 the head, 8 the embedding table) as decoded f32
+        values [n_out][n_in]."""
+        w = np.ascontiguousarray(w, dtype=np.float32)
+        assert lib().fo_llama_set_f32(self._m, layer, which, _ptr(w), w.shape[0], w.shape[1]) == 0
 
     def forward_tokens(self, ids):
         ids = np.ascontiguousarray(ids, dtype=np.int32)
