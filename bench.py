@@ -2,7 +2,7 @@
 """Benchmark of the Q8_0 GPT-2 forward path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload ...] [--impl ours|reference]
-    python bench.py --case decode|score|linear|rowq|streams|llama-decode|llama-score [...]
+    python bench.py --case decode|score|linear|rowq|ggml-linear|streams|llama-decode|llama-score [...]
 
 Workloads (synthetic, seeded; shapes of the reference's configurations):
   decode        : GPT-2-small-shaped Q8_0 model, batch 1, 32-token prompt, 256 greedy tokens with a
@@ -297,6 +297,35 @@ def run_case(a):
             byts = a.k * a.n / (2 if a.kind else 1) + 4 * a.k + 4 * a.m * (a.k + a.n)
             print(f"rowq {'int4' if a.kind else 'int8'} M={a.m} K={a.k} N={a.n}: {ms * 1e3:.1f} us, {byts / ms / 1e6:.1f} GB/s")
         return
+    if a.case == "ggml-linear":
+        # one matrix kept in a ggml block format (--native: ggml type), decoded inside the product
+        import numpy as np
+        from ferrum_cpu_b200 import _lib
+        t = a.native if a.native >= 0 else 12
+        vals, bb = {2: (32, 18), 6: (32, 22), 8: (32, 34), 12: (256, 144), 13: (256, 176), 14: (256, 210)}[t]
+        rng = np.random.default_rng(0)
+        raw = rng.integers(0, 256, size=(a.n * a.k // vals, bb), dtype=np.uint8)
+        for at in {2: [0], 6: [0], 8: [0], 12: [0, 2], 13: [0, 2], 14: [208]}[t]:
+            raw[:, at:at + 2] = (rng.standard_normal(raw.shape[0]) * 0.01).astype(np.float16).view(np.uint8).reshape(-1, 2)
+        h = C.c_void_p()
+        rc = _lib.lib().fc_ggml_weight_upload(0, t, raw.ctypes.data_as(C.c_void_p), raw.size, a.n, a.k, C.byref(h))
+        assert rc == 0, rc
+        x = torch.randn(a.m, a.k, device="cuda")
+        y = torch.empty(a.m, a.n, device="cuda")
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+        st = torch.cuda.current_stream().cuda_stream
+        for _ in range(a.reps):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            _lib.lib().fc_ggml_linear_dev(h, C.c_void_p(x.data_ptr()), None, C.c_void_p(y.data_ptr()), a.m, C.c_void_p(st))
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1)
+            byts = raw.size + 4 * a.m * (a.k + a.n)
+            print(f"ggml type {t} M={a.m} K={a.k} N={a.n}: {ms * 1e3:.1f} us, {byts / ms / 1e6:.1f} GB/s")
+        _lib.lib().fc_ggml_weight_free(h)
+        return
     if a.case.startswith("llama"):
         from ferrum_cpu_b200.engine import sampling
         from ferrum_cpu_b200.llama import CudaLlama
@@ -433,7 +462,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", choices=["decode", "score", "both", "streams-medium", "score-medium", "sweep", "tiny", "llama-1b"],
                     default="both", help="see the module docstring")
-    ap.add_argument("--case", choices=["decode", "score", "linear", "rowq", "streams", "llama-decode", "llama-score"], default=None,
+    ap.add_argument("--case", choices=["decode", "score", "linear", "rowq", "ggml-linear", "streams", "llama-decode", "llama-score"], default=None,
                     help="run one small self-terminating case (for profiler captures) instead of a workload")
     ap.add_argument("--model", default="small")
     ap.add_argument("--tokens", type=int, default=8)

@@ -57,7 +57,7 @@ __host__ __device__ inline Fmt fmt_of(int t) {
 
 // The 32 values of sub-block sb of the (super-)block at b, in the order they have in the row: positions
 // 32 sb .. 32 sb + 31 of the block's 32 or 256 values. The arithmetic follows gguf/dequant.rs line by line.
-__device__ void dequant32(int t, const uint8_t* b, int sb, float* out) {
+__device__ __forceinline__ void dequant32(int t, const uint8_t* b, int sb, float* out) {
     switch (t) {
         case FC_GGML_F32:
             for (int j = 0; j < 32; ++j) { uint32_t u = b[4 * j] | (b[4 * j + 1] << 8) | (b[4 * j + 2] << 16) | ((uint32_t)b[4 * j + 3] << 24); out[j] = __uint_as_float(u); }
@@ -168,32 +168,53 @@ struct LinArgs {
     const float* x; const float* bias; const float* residual; float* y; int ldy, M;
 };
 
-// grid.x: groups of (blockDim.x / 32) output rows, grid.y: passes of MT activation rows.
+// grid.x: groups of (blockDim.x / 32) output rows, grid.y: passes of MT activation rows. A warp brings the bytes of 32
+// sub-blocks of its row into shared memory with coalesced loads (2 or 4 bytes per lane: the blocks are only 2-byte
+// aligned in general) and every lane decodes its own sub-block from there: byte-wise global loads of the blocks stall
+// on their latency and throttle the load queue (5.0 and 1.5 stalls per issue, 65 us for a 16384 x 2048 Q4_K matrix).
+constexpr int STAGE_BYTES = 32 * 128;      // the widest 32 sub-blocks: f32
+
+// T: the ggml type, a compile-time constant so that each instance carries one decoder only.
+template <int T>
 __global__ void __launch_bounds__(256) ggml_linear_kernel(LinArgs a) {
-    const int lane = threadIdx.x & 31;
-    const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    __shared__ __align__(16) uint8_t stage_all[8 * STAGE_BYTES];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int n = blockIdx.x * (blockDim.x >> 5) + warp;
     if (n >= a.N) return;
+    uint8_t* stage = stage_all + warp * STAGE_BYTES;
     const int m0 = blockIdx.y * MT, mt = min(MT, a.M - m0);
-    const Fmt f = fmt_of(a.type);
+    const Fmt f = fmt_of(T);
     const int per = f.vals >> 5;                               // 32-value sub-blocks per block
     const int n_sub = a.K >> 5;
     const uint8_t* row = a.raw + (size_t)n * a.row_bytes;
     float acc[MT];
 #pragma unroll
     for (int m = 0; m < MT; ++m) acc[m] = 0.0f;
-    for (int s = lane; s < n_sub; s += 32) {
-        float w[32];
-        dequant32(a.type, row + (size_t)(s / per) * f.bytes, s % per, w);
-        for (int m = 0; m < mt; ++m) {
-            const float4* xr = (const float4*)(a.x + (size_t)(m0 + m) * a.K + 32 * s);
-            float t = 0.0f;
+    for (int s0 = 0; s0 < n_sub; s0 += 32) {
+        const int b0 = s0 / per, b1 = (min(s0 + 32, n_sub) + per - 1) / per;       // blocks of this chunk
+        const uint8_t* src = row + (size_t)b0 * f.bytes;
+        const int len = (b1 - b0) * f.bytes;
+        if ((((uintptr_t)src | (uintptr_t)len) & 3) == 0)
+            for (int i = lane; i < (len >> 2); i += 32) ((uint32_t*)stage)[i] = __ldg((const uint32_t*)src + i);
+        else
+            for (int i = lane; i < (len >> 1); i += 32) ((uint16_t*)stage)[i] = __ldg((const uint16_t*)src + i);
+        __syncwarp();
+        const int s = s0 + lane;
+        if (s < n_sub) {
+            float w[32];
+            dequant32(T, stage + (size_t)(s / per - b0) * f.bytes, s % per, w);
+            for (int m = 0; m < mt; ++m) {
+                const float4* xr = (const float4*)(a.x + (size_t)(m0 + m) * a.K + 32 * s);
+                float t = 0.0f;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const float4 v = xr[j];
-                t = fmaf(v.x, w[4 * j], t); t = fmaf(v.y, w[4 * j + 1], t); t = fmaf(v.z, w[4 * j + 2], t); t = fmaf(v.w, w[4 * j + 3], t);
+                for (int j = 0; j < 8; ++j) {
+                    const float4 v = xr[j];
+                    t = fmaf(v.x, w[4 * j], t); t = fmaf(v.y, w[4 * j + 1], t); t = fmaf(v.z, w[4 * j + 2], t); t = fmaf(v.w, w[4 * j + 3], t);
+                }
+                acc[m] += t;
             }
-            acc[m] += t;
         }
+        __syncwarp();
     }
 #pragma unroll
     for (int m = 0; m < MT; ++m)
@@ -245,7 +266,14 @@ int launch_ggml_linear(const fc_ggml_weight* w, const float* x, const float* bia
     if (ldy < w->N) return fail(FC_E_SHAPE, "ggml linear: row stride %d below %d columns", ldy, w->N);
     LinArgs a{w->raw, w->row_bytes, w->type, w->N, w->K, x, bias, residual, y, ldy, M};
     const dim3 grid((w->N + 7) / 8, (M + MT - 1) / MT);
-    ggml_linear_kernel<<<grid, 256, 0, st>>>(a);
+    switch (w->type) {
+#define FC_CASE(T) case T: ggml_linear_kernel<T><<<grid, 256, 0, st>>>(a); break;
+        FC_CASE(FC_GGML_F32) FC_CASE(FC_GGML_F16) FC_CASE(FC_GGML_Q4_0) FC_CASE(FC_GGML_Q4_1) FC_CASE(FC_GGML_Q5_0) FC_CASE(FC_GGML_Q5_1)
+        FC_CASE(FC_GGML_Q8_0) FC_CASE(FC_GGML_Q8_1) FC_CASE(FC_GGML_Q2_K) FC_CASE(FC_GGML_Q3_K) FC_CASE(FC_GGML_Q4_K) FC_CASE(FC_GGML_Q5_K)
+        FC_CASE(FC_GGML_Q6_K)
+#undef FC_CASE
+        default: return fail(FC_E_FORMAT, "ggml type %d", w->type);
+    }
     FC_LAUNCHED();
     return FC_OK;
 }
