@@ -132,8 +132,9 @@ constexpr int SK_MAX_SPLITS = 8;
 // (its own ring in shared memory, cp.async) before it waits for that kernel (programmatic dependent
 // launch): the weight stream of one product overlaps the tail of the kernel before it, and HBM sees
 // RG * 544 B * depth per warp in flight instead of one block at a time.
-template <int NT, int RG>
-__global__ void __launch_bounds__(512) skinny_q8_kernel(const SkArgs a) {
+// MAXT: the largest block the instance is launched with (512, or 1024 for the narrow tiles whose registers allow it).
+template <int NT, int RG, int MAXT = 512>
+__global__ void __launch_bounds__(MAXT) skinny_q8_kernel(const SkArgs a) {
     extern __shared__ __align__(16) unsigned char sk_smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int nwarps = blockDim.x >> 5;
@@ -676,7 +677,7 @@ __global__ void batch_init_kernel(int S, int pos0, int* done, int* n_out, int* c
     if (s < S) { done[s] = 0; n_out[s] = 0; cur[s] = 0; }
 }
 
-template <int NT, int RG>
+template <int NT, int RG, int MAXT = 512>
 int launch_skinny_nt(const SkArgs& a, int warps, int col_groups, int splits, cudaStream_t st) {
     auto bytes = [](int w, int depth) {
         return (size_t)w * (depth * RG * 544 + 4 * NT * RED_LD * sizeof(float));
@@ -686,13 +687,13 @@ int launch_skinny_nt(const SkArgs& a, int warps, int col_groups, int splits, cud
     int dev = 0;
     FC_CUDA(cudaGetDevice(&dev));
     if (dev < 64 && !attr[dev]) {
-        FC_CUDA(cudaFuncSetAttribute(skinny_q8_kernel<NT, RG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemCap));
+        FC_CUDA(cudaFuncSetAttribute(skinny_q8_kernel<NT, RG, MAXT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemCap));
         attr[dev] = true;
     }
     SkArgs b = a;
     while (b.depth > 1 && bytes(warps, b.depth) > kSmemCap) --b.depth;   // a shallower ring when the slots are large
     if (bytes(warps, b.depth) > kSmemCap) return fail(FC_E_SHAPE, "the lock-step product does not fit shared memory");
-    FC_CUDA(launch_dep(skinny_q8_kernel<NT, RG>, dim3((a.N + 16 * RG - 1) / (16 * RG), col_groups, splits), dim3(warps * 32),
+    FC_CUDA(launch_dep(skinny_q8_kernel<NT, RG, MAXT>, dim3((a.N + 16 * RG - 1) / (16 * RG), col_groups, splits), dim3(warps * 32),
                        bytes(warps, b.depth), st, b));
     ++g_launches;
     return FC_OK;
@@ -733,13 +734,17 @@ int launch_skinny_q8(const QFrag& w, int S, const void* xp, const float* bias, i
     // warps split a CTA's K range: at least two 32-wide blocks each, at most 8 warps
     // A warp's K slice is a chain of dependent steps (block landed -> fragments -> MMAs -> scaled add), about 0.3 us
     // per k-block whatever the width: the slices are kept to two or three blocks by using up to 16 warps.
-    const int warps = std::min(out.max_warps, kb_cta >= 32 ? 16 : kb_cta >= 16 ? 8 : kb_cta >= 8 ? 4 : kb_cta >= 4 ? 2 : 1);
+    int warps = std::min(out.max_warps, kb_cta >= 32 ? 16 : kb_cta >= 16 ? 8 : kb_cta >= 8 ? 4 : kb_cta >= 4 ? 2 : 1);
+    // a chain on its own, at most 8 streams, a long K: 32 warps (three or four blocks each) on the narrowest tile
+    const bool wide_block = out.max_warps >= 16 && cols == 16 && kb_cta >= 96 && (w.N + 31) / 32 * splits < 2 * 148;
+    if (wide_block) warps = 32;
     a.depth = std::max(1, std::min(SK_DEPTH, (kb_cta + warps - 1) / warps));
     if (cols <= 32) {
         // few streams: a chain on its own is bound by latency and takes 32 rows per CTA only when that still leaves
         // every SM several CTAs; chains that share the GPU are bound by throughput, and 32 rows halve the activation
         // fragments read from L2 per weight
         const bool wide = (w.N + 31) / 32 * splits >= 2 * 148 || out.max_warps < 16;
+        if (wide_block) return launch_skinny_nt<2, 1, 1024>(a, warps, 1, splits, st);
         if (cols == 16) return wide ? launch_skinny_nt<2, 2>(a, warps, 1, splits, st) : launch_skinny_nt<2, 1>(a, warps, 1, splits, st);
         return wide ? launch_skinny_nt<4, 2>(a, warps, 1, splits, st) : launch_skinny_nt<4, 1>(a, warps, 1, splits, st);
     }
