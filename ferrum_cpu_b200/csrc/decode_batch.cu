@@ -735,8 +735,8 @@ int launch_skinny_q8(const QFrag& w, int S, const void* xp, const float* bias, i
     // A warp's K slice is a chain of dependent steps (block landed -> fragments -> MMAs -> scaled add), about 0.3 us
     // per k-block whatever the width: the slices are kept to two or three blocks by using up to 16 warps.
     int warps = std::min(out.max_warps, kb_cta >= 32 ? 16 : kb_cta >= 16 ? 8 : kb_cta >= 8 ? 4 : kb_cta >= 4 ? 2 : 1);
-    // a chain on its own, at most 8 streams, a long K: 32 warps (three or four blocks each) on the narrowest tile
-    const bool wide_block = out.max_warps >= 16 && cols == 16 && kb_cta >= 96 && (w.N + 31) / 32 * splits < 2 * 148;
+    // a chain on its own, at most 16 streams, a long K: 32 warps (three or four blocks each) on the 16-row tile
+    const bool wide_block = out.max_warps >= 16 && cols <= 32 && kb_cta >= 96 && (w.N + 31) / 32 * splits < 2 * 148;
     if (wide_block) warps = 32;
     a.depth = std::max(1, std::min(SK_DEPTH, (kb_cta + warps - 1) / warps));
     if (cols <= 32) {
@@ -744,7 +744,7 @@ int launch_skinny_q8(const QFrag& w, int S, const void* xp, const float* bias, i
         // every SM several CTAs; chains that share the GPU are bound by throughput, and 32 rows halve the activation
         // fragments read from L2 per weight
         const bool wide = (w.N + 31) / 32 * splits >= 2 * 148 || out.max_warps < 16;
-        if (wide_block) return launch_skinny_nt<2, 1, 1024>(a, warps, 1, splits, st);
+        if (wide_block) return cols == 16 ? launch_skinny_nt<2, 1, 1024>(a, warps, 1, splits, st) : launch_skinny_nt<4, 1, 1024>(a, warps, 1, splits, st);
         if (cols == 16) return wide ? launch_skinny_nt<2, 2>(a, warps, 1, splits, st) : launch_skinny_nt<2, 1>(a, warps, 1, splits, st);
         return wide ? launch_skinny_nt<4, 2>(a, warps, 1, splits, st) : launch_skinny_nt<4, 1>(a, warps, 1, splits, st);
     }
