@@ -1460,6 +1460,7 @@ struct BatchView {
     float **kcs, **vcs;
     cudaStream_t st;
     int max_warps;                     // per CTA of the products: fewer when several groups run side by side
+    bool long_k_block;                 // the 32-warp tile of the long-K products: up to two groups
 };
 
 static BatchView batch_view(fc_model* m, int s0, int S, int group_index, cudaStream_t st, int n_groups = 1) {
@@ -1482,6 +1483,7 @@ static BatchView batch_view(fc_model* m, int s0, int S, int group_index, cudaStr
     v.kcs = b.kcs + o; v.vcs = b.vcs + o;
     v.st = st;
     v.max_warps = n_groups > 1 ? 8 : 16;
+    v.long_k_block = n_groups <= 2;
     return v;
 }
 
@@ -1493,7 +1495,7 @@ static int batch_head_and_pick(fc_model* m, const BatchView& v, int eos, const f
     BatchCtx& b = m->batch;
     FC_TRY(launch_ln_rows_f16(x, part, n_part, part_bias, x_other, m->lnfg, m->lnfb, v.S, c.d_model, v.xp, v.st));
     SkinnyOut out;
-    out.max_warps = v.max_warps;
+    out.max_warps = v.max_warps; out.long_k_block = v.long_k_block;
     out.y = v.logits; out.ldy = m->head.N_pad;
     FC_TRY(launch_skinny_q8(b.head, v.S, v.xp, nullptr, EPI_NONE, out, nullptr, v.st));
     return launch_pick_batch(v.logits, m->head.N_pad, c.vocab, v.S, eos, v.cur, v.done, v.n_out, v.out_tok, b.out_cap, v.pos, advance, v.st);
@@ -1529,7 +1531,7 @@ static int batch_launch_step(fc_model* m, const BatchView& v, int eos) {
     // x <- x + (W in + bias): as partial sums for the next LayerNorm, or finished in the epilogue
     auto project_add = [&](const QFrag& w, const void* in, const float* bias) -> int {
         SkinnyOut o;
-        o.max_warps = v.max_warps;
+        o.max_warps = v.max_warps; o.long_k_block = v.long_k_block;
         if (split_k) {
             o.part = v.part;
             FC_TRY(launch_skinny_q8(w, S, in, nullptr, EPI_NONE, o, &n_part, st));
@@ -1541,6 +1543,7 @@ static int batch_launch_step(fc_model* m, const BatchView& v, int eos) {
     };
     SkinnyOut oq, oh;
     oq.max_warps = oh.max_warps = v.max_warps;
+    oq.long_k_block = oh.long_k_block = v.long_k_block;
     oq.y = v.qkv_f; oq.ldy = 3 * d;
     oh.planes = v.hp; oh.ldp = F;
     for (int l = 0; l < c.n_layer; ++l) {

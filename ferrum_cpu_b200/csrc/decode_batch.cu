@@ -735,8 +735,10 @@ int launch_skinny_q8(const QFrag& w, int S, const void* xp, const float* bias, i
     // A warp's K slice is a chain of dependent steps (block landed -> fragments -> MMAs -> scaled add), about 0.3 us
     // per k-block whatever the width: the slices are kept to two or three blocks by using up to 16 warps.
     int warps = std::min(out.max_warps, kb_cta >= 32 ? 16 : kb_cta >= 16 ? 8 : kb_cta >= 8 ? 4 : kb_cta >= 4 ? 2 : 1);
-    // a chain on its own, at most 16 streams, a long K: 32 warps (three or four blocks each) on the 16-row tile
-    const bool wide_block = out.max_warps >= 16 && cols <= 32 && kb_cta >= 96 && (w.N + 31) / 32 * splits < 2 * 148;
+    // at most 16 streams and a long K (the down-projection): 32 warps (three or four blocks each) on the 16-row tile, in
+    // a chain on its own and with two chains side by side (two groups of 16 on the 24-block shape: 31.6 k -> 34.0 k
+    // tokens/s; with four groups 48.9 k -> 48.3 k, so not there)
+    const bool wide_block = out.long_k_block && cols <= 32 && kb_cta >= 96 && (w.N + 31) / 32 * splits < 2 * 148;
     if (wide_block) warps = 32;
     a.depth = std::max(1, std::min(SK_DEPTH, (kb_cta + warps - 1) / warps));
     if (cols <= 32) {

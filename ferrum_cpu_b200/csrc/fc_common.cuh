@@ -254,6 +254,7 @@ struct SkinnyOut {
     int ldp = 0;
     float* part = nullptr;
     int max_warps = 16;   // warps per CTA; 8 when several chains of step kernels share the GPU (two or three CTAs per SM then)
+    bool long_k_block = true;   // 32 warps on the 16-row tile for long K (up to 16 streams); off when more than two chains share the GPU
 };
 int skinny_max_splits();
 int launch_skinny_q8(const QFrag& w, int S, const void* xp, const float* bias, int epi, const SkinnyOut& out, int* splits_used,
