@@ -731,7 +731,7 @@ int launch_skinny_q8(const QFrag& w, int S, const void* xp, const float* bias, i
     if (out.part) splits = std::max(1, std::min(SK_MAX_SPLITS, nkb / 8));
     if (splits_used) *splits_used = splits;
     const int kb_cta = (nkb + splits - 1) / splits;
-    // warps split a CTA's K range: at least two 32-wide blocks each, at most 8 warps
+    // warps split a CTA's K range: at least two 32-wide blocks each
     // A warp's K slice is a chain of dependent steps (block landed -> fragments -> MMAs -> scaled add), about 0.3 us
     // per k-block whatever the width: the slices are kept to two or three blocks by using up to 16 warps.
     int warps = std::min(out.max_warps, kb_cta >= 32 ? 16 : kb_cta >= 16 ? 8 : kb_cta >= 8 ? 4 : kb_cta >= 4 ? 2 : 1);
